@@ -1,0 +1,458 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+bias, +residual, SwiGLU/GELU
+// epilogues), fp32 accumulation in TMEM.
+//
+// One kernel serves both serving regimes:
+//   * decode (M <= 128 tokens): "swapped" — the weight rows run along the UMMA M dimension (128 per tile)
+//     and the few tokens along UMMA N, so no tensor-core rows are wasted and the kernel is a pure weight
+//     stream. Split-K spreads a skinny weight over all 148 SMs; partials meet in a scratch workspace and the
+//     last CTA of a tile reduces them in a fixed order (deterministic) and runs the epilogue.
+//   * prefill / DiT (large M): tokens along UMMA M, weight rows along UMMA N (tile 128 x 256 or 128 x 128).
+//
+// Structure per CTA (192 threads): warp 0 = TMA producer, warp 1 = UMMA issuer and TMEM owner, warps 2-5 =
+// epilogue (one TMEM lane quarter each). Operand tiles are K-major, 64 bf16 (128 bytes) wide, SWIZZLE_128B,
+// moved by non-multicast TMA through a multi-stage mbarrier ring.
+//
+// Counterpart in the reference: every dense projection there is a cuBLAS call through F.linear
+// (mstar/model/components/distributed/linear.py:8-419, mstar/model/components/mlp.py).
+#include <cuda.h>
+#include "common.cuh"
+#include "host_common.h"
+
+namespace mstar {
+
+struct GemmParams {
+    int M, N, K;               // logical problem: C[M,N] = A[M,K] B[N,K]^T
+    int swap;                  // 1: P operand (UMMA M) = B rows, Q operand (UMMA N) = A rows
+    int splits;                // split-K factor (grid.z)
+    int kblocks_per_split;     // 64-wide K blocks handled by one split
+    int kblocks_total;
+    int epilogue;              // 0 none, 1 SwiGLU on interleaved (gate,up) output columns, 2 GELU(tanh)
+    int out_f32;               // 1: C is fp32
+    int ldc;                   // elements
+    int ld_res;                // elements
+    void* C;
+    const __nv_bfloat16* bias;      // [N] or null
+    const __nv_bfloat16* residual;  // [M, ld_res] or null
+    float* workspace;               // split-K partials
+    unsigned int* counters;         // one per output tile, zero on entry, zero again on exit
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+    float out_scale;                // multiplies the accumulator before bias (1.0 by default)
+};
+
+constexpr int BM = 128;  // UMMA M (P-tile rows)
+constexpr int BK = 64;   // bf16 elements per K block = 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;
+
+__host__ __device__ constexpr int gemm_stage_bytes(int BN) { return BM * BK * 2 + BN * BK * 2; }
+__host__ __device__ constexpr int gemm_smem_bytes(int BN, int stages) {
+    return stages * gemm_stage_bytes(BN) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+
+// Apply bias / activation / residual to a run of 32 accumulator values and store them.
+// non-swapped: the thread owns output row m and 32 consecutive columns starting at n0.
+template <bool OUT_F32>
+__device__ __forceinline__ void store_row_chunk(const GemmParams& p, int m, int n0, float* v, int ncols) {
+    if (m >= p.M) return;
+    if (p.out_scale != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= p.out_scale;
+    }
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < ncols && n0 + i < p.N) v[i] += __bfloat162float(p.bias[n0 + i]);
+    }
+    if (p.epilogue == 1) {
+        // (gate, up) interleaved along n: out column = n/2
+        const int o0 = n0 >> 1;
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc + o0;
+        const int half = ncols >> 1;
+        const int No = p.N >> 1;
+        if (half == 16 && o0 + 16 <= No && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float a = silu_f(v[4 * i]) * v[4 * i + 1];
+                float b = silu_f(v[4 * i + 2]) * v[4 * i + 3];
+                w[i] = pack_bf16x2(a, b);
+            }
+            reinterpret_cast<uint4*>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            for (int i = 0; i < half; ++i)
+                if (o0 + i < No) out[i] = __float2bfloat16(silu_f(v[2 * i]) * v[2 * i + 1]);
+        }
+        return;
+    }
+    if (p.epilogue == 2) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+    }
+    if (p.residual != nullptr) {
+        const __nv_bfloat16* r = p.residual + (size_t)m * p.ld_res + n0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < ncols && n0 + i < p.N) v[i] += __bfloat162float(r[i]);
+    }
+    if constexpr (OUT_F32) {
+        float* out = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n0;
+        if (ncols == 32 && n0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(out)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < ncols; ++i)
+                if (n0 + i < p.N) out[i] = v[i];
+        }
+    } else {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc + n0;
+        if (ncols == 32 && n0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(out)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        } else {
+            for (int i = 0; i < ncols; ++i)
+                if (n0 + i < p.N) out[i] = __float2bfloat16(v[i]);
+        }
+    }
+}
+
+// swapped: the thread owns output column n (a weight row) and `ncols` consecutive token rows from m0.
+// Lanes of a warp hold consecutive n, so each row's store is one contiguous segment per warp.
+template <bool OUT_F32>
+__device__ __forceinline__ void store_col_chunk(const GemmParams& p, int n, int m0, float* v, int ncols) {
+    const bool n_ok = n < p.N;
+    float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (i >= ncols) break;
+        const int m = m0 + i;
+        float x = v[i] * p.out_scale + b;
+        if (p.epilogue == 1) {
+            // rows 2j (gate) / 2j+1 (up) of the weight sit in neighbouring lanes
+            float other = __shfl_xor_sync(0xffffffffu, x, 1);
+            if ((n & 1) == 0 && n_ok && m < p.M) {
+                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + (n >> 1)] =
+                    __float2bfloat16(silu_f(x) * other);
+            }
+            continue;
+        }
+        if (p.epilogue == 2) x = gelu_tanh_f(x);
+        if (n_ok && m < p.M) {
+            if (p.residual != nullptr) x += __bfloat162float(p.residual[(size_t)m * p.ld_res + n]);
+            if constexpr (OUT_F32)
+                reinterpret_cast<float*>(p.C)[(size_t)m * p.ldc + n] = x;
+            else
+                reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + n] = __float2bfloat16(x);
+        }
+    }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                         const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGE_BYTES = gemm_stage_bytes(BN);
+    constexpr int P_BYTES = BM * BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort, [1] is_last
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile_p = blockIdx.x;
+    const int tile_q = blockIdx.y;
+    const int split = blockIdx.z;
+    const int kb_begin = split * p.kblocks_per_split;
+    int kb_end = kb_begin + p.kblocks_per_split;
+    if (kb_end > p.kblocks_total) kb_end = p.kblocks_total;
+    const int nkb = kb_end - kb_begin;  // host guarantees >= 1
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        flags[0] = 0;
+        flags[1] = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmP);
+        tma_prefetch_desc(&tmQ);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1, p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 1, i, s);
+                    flags[0] = 1;
+                    break;
+                }
+                if (flags[0]) break;
+                uint8_t* sp = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                const int kx = (kb_begin + i) * BK;
+                tma_load_2d(sp, &tmP, &full_bar[s], kx, tile_p * BM);
+                tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kx, tile_q * BN);
+                issued = i + 1;
+            }
+            if (flags[0]) {
+                // error path: let copies already in flight land before the CTA leaves
+                for (int i = (issued > STAGES ? issued - STAGES : 0); i < issued; ++i)
+                    mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1, 1000000ull);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1);
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!mbar_wait(&full_bar[s], ph, p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 2, i, s);
+                    flags[0] = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sp = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t da = umma_smem_desc_sw128(sp);
+                const uint64_t db = umma_smem_desc_sw128(sp + P_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // +32 bytes per K slice inside the 128-byte swizzle atom (encoded >> 4)
+                    umma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok) umma_commit(acc_bar);
+        }
+    } else {
+        // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;  // accumulator row (TMEM lane) owned by this thread
+        bool ok = mbar_wait(acc_bar, 0, p.wait_limit_ns + 500000000ull);
+        if (!ok) {
+            report_status(p.status, KID_GEMM, 3, 0, 0);
+            flags[0] = 1;
+        }
+        tc_fence_after();
+        const int pidx = tile_p * BM + row;  // index along the P operand's rows
+        constexpr int CH = BN < 32 ? BN : 32;
+        const int tile_lin = tile_q * gridDim.x + tile_p;
+        bool do_final = ok;
+
+        if (ok && p.splits > 1) {
+            // 1) publish this split's partial tile: layout [col][row] so that a warp writes 128 B per column
+            float* wsp = p.workspace + ((size_t)(split * gridDim.x * gridDim.y + tile_lin)) * (BM * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
+                if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < CH; ++i) __stcg(&wsp[(size_t)(c0 + i) * BM + row], __uint_as_float(r[i]));
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                unsigned int old = atomicAdd(&p.counters[tile_lin], 1u);
+                flags[1] = (old == (unsigned int)(p.splits - 1)) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            do_final = flags[1] != 0;
+            if (do_final) __threadfence();
+        }
+
+        if (do_final) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                float v[32];
+                if (p.splits > 1) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                    for (int z = 0; z < p.splits; ++z) {
+                        const float* wsp =
+                            p.workspace + ((size_t)(z * gridDim.x * gridDim.y + tile_lin)) * (BM * BN);
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) v[i] += __ldcg(&wsp[(size_t)(c0 + i) * BM + row]);
+                    }
+                } else {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
+                    if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
+                }
+                const int qidx = tile_q * BN + c0;
+                if (p.swap) {
+                    if (p.out_f32) store_col_chunk<true>(p, pidx, qidx, v, CH);
+                    else store_col_chunk<false>(p, pidx, qidx, v, CH);
+                } else {
+                    if (p.out_f32) store_row_chunk<true>(p, pidx, qidx, v, CH);
+                    else store_row_chunk<false>(p, pidx, qidx, v, CH);
+                }
+            }
+            if (p.splits > 1 && threadIdx.x == 64) p.counters[tile_lin] = 0u;  // ready for the next launch
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
+                       cudaStream_t stream) {
+    constexpr int smem = gemm_smem_bytes(BN, STAGES);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
+        configured = true;
+    }
+    gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, smem, stream>>>(tmP, tmQ, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error("gemm: launch failed", e);
+    return 0;
+}
+
+}  // namespace mstar
+
+using namespace mstar;
+
+// Workspace bytes needed for a given problem (0 when no split-K is used). Also returns the split factor.
+MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, int* splits_out,
+                              long long* ws_bytes_out, int* tiles_out) {
+    const int kblocks = (K + BK - 1) / BK;
+    int swap = (M <= 128) ? 1 : 0;
+    int bn;
+    int tiles_p, tiles_q;
+    if (swap) {
+        bn = 16;
+        while (bn < M) bn <<= 1;  // 16,32,64,128
+        tiles_p = (N + BM - 1) / BM;
+        tiles_q = 1;
+    } else {
+        bn = (N % 256 == 0 || N >= 2048) ? 256 : 128;
+        if (N <= 128) bn = 128;
+        tiles_p = (M + BM - 1) / BM;
+        tiles_q = (N + bn - 1) / bn;
+    }
+    const int tiles = tiles_p * tiles_q;
+    int splits = 1;
+    const int sms = device_sm_count();
+    if (tiles < sms) {
+        splits = sms / tiles;
+        // keep at least 4 K blocks per split so the pipeline has something to stream
+        int max_splits = kblocks / 4;
+        if (max_splits < 1) max_splits = 1;
+        if (splits > max_splits) splits = max_splits;
+        if (splits > 32) splits = 32;
+        if (splits < 1) splits = 1;
+    }
+    int kpb = (kblocks + splits - 1) / splits;
+    splits = (kblocks + kpb - 1) / kpb;  // no empty split
+    if (swap_out) *swap_out = swap;
+    if (bn_out) *bn_out = bn;
+    if (splits_out) *splits_out = splits;
+    if (tiles_out) *tiles_out = tiles;
+    if (ws_bytes_out) *ws_bytes_out = splits > 1 ? (long long)splits * tiles * BM * bn * 4 : 0;
+    return 0;
+}
+
+// C[M,N] = A[M,K] * B[N,K]^T with optional bias[N], residual[M,N] and epilogue.
+// A, B bf16 row-major with leading dimensions lda, ldb (elements, multiples of 8); C bf16 or fp32.
+// epilogue 1 (SwiGLU): B's rows interleave (gate_j, up_j); C has N/2 columns.
+MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                              const void* bias, const void* residual, int ld_res, int epilogue, int out_f32,
+                              float out_scale, void* workspace, long long workspace_bytes, void* counters,
+                              int n_counters, int force_splits, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+        return set_error("gemm: operands must be 16-byte aligned with leading dimensions multiple of 8", cudaSuccess);
+    int swap, bn, splits, tiles;
+    long long ws_need;
+    mstar_gemm_plan(M, N, K, &swap, &bn, &splits, &ws_need, &tiles);
+    const int kblocks = (K + BK - 1) / BK;
+    if (force_splits > 0) {
+        splits = force_splits > kblocks ? kblocks : force_splits;
+        int kpb = (kblocks + splits - 1) / splits;
+        splits = (kblocks + kpb - 1) / kpb;
+        ws_need = splits > 1 ? (long long)splits * tiles * BM * bn * 4 : 0;
+    }
+    if (splits > 1 && (workspace == nullptr || ws_need > workspace_bytes || tiles > n_counters)) {
+        splits = 1;  // no scratch available: fall back to a single pass over K
+    }
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.swap = swap;
+    p.splits = splits;
+    p.kblocks_total = kblocks;
+    p.kblocks_per_split = (kblocks + splits - 1) / splits;
+    p.epilogue = epilogue;
+    p.out_f32 = out_f32;
+    p.ldc = ldc;
+    p.ld_res = ld_res;
+    p.C = C;
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+    p.workspace = reinterpret_cast<float*>(workspace);
+    p.counters = reinterpret_cast<unsigned int*>(counters);
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    p.out_scale = out_scale;
+
+    const void* Pp = swap ? B : A;
+    const void* Qp = swap ? A : B;
+    const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
+    const int ldP = swap ? ldb : lda, ldQ = swap ? lda : ldb;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_bf16(&tmP, Pp, rowsP, K, ldP, BM, BK)) return -1;
+    if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
+    dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
+    switch (bn) {
+        case 16: return launch_gemm<16, 10>(tmP, tmQ, p, grid, stream);
+        case 32: return launch_gemm<32, 10>(tmP, tmQ, p, grid, stream);
+        case 64: return launch_gemm<64, 8>(tmP, tmQ, p, grid, stream);
+        case 128: return launch_gemm<128, 6>(tmP, tmQ, p, grid, stream);
+        case 256: return launch_gemm<256, 4>(tmP, tmQ, p, grid, stream);
+    }
+    return set_error("gemm: unsupported tile", cudaSuccess);
+}

@@ -1,0 +1,23 @@
+// Host-side helpers shared by all kernel launchers of the library: last-error text, the device status word,
+// the wait limit for device-side waits, and TMA tensor-map encoding through the driver entry point (looked up
+// at run time, so the library links against cudart only).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "common.cuh"
+
+namespace mstar {
+
+int set_error(const char* msg, cudaError_t e);      // stores the message, returns -1
+KernelStatus* status_ptr();                         // device pointer of this process' status word (lazily made)
+unsigned long long wait_limit_ns();
+int device_sm_count();
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements); box =
+// box_rows x box_cols, SWIZZLE_128B (box_cols * 2 bytes must be 128).
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, int rows, int cols, int ld, int box_rows, int box_cols);
+// Generic form: up to 5 dims, sizes/strides innermost first, strides in bytes (stride[0] implied by elem size).
+int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const unsigned long long* dims,
+              const unsigned long long* strides_bytes, const unsigned int* box, int swizzle_128b);
+
+}  // namespace mstar

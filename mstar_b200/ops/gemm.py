@@ -1,0 +1,113 @@
+"""Dense projections: ``y = x @ w.T (+bias) (+residual)`` with optional SwiGLU / GELU epilogue.
+
+GPU path: the hand-written tcgen05 kernel of ``csrc/gemm_tcgen05.cu`` (TMEM accumulators, TMA-fed, split-K
+through a scratch workspace for skinny decode shapes). CPU path and test oracle: ``linear_ref`` in fp32.
+
+Reference counterpart: cuBLAS through ``F.linear`` in mstar/model/components/distributed/linear.py:8-419 and
+mstar/model/components/mlp.py (SwiGLU is a separate elementwise op there).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+EPILOGUE_NONE = 0
+EPILOGUE_SWIGLU = 1   # weight rows interleave (gate_j, up_j); output has N/2 columns
+EPILOGUE_GELU = 2
+
+_WORKSPACES: dict[tuple[int, int], tuple[torch.Tensor, torch.Tensor]] = {}
+WORKSPACE_BYTES = 96 << 20
+N_COUNTERS = 1 << 16
+
+
+def workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Split-K scratch (fp32 partial tiles) and per-tile arrival counters for the current stream.
+    One pair per (device, stream) so that kernels on different streams never share scratch."""
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = (torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device),
+              torch.zeros(N_COUNTERS, dtype=torch.int32, device=device))
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
+    """Stack gate and up projection weights row-interleaved: row 2j = gate_j, row 2j+1 = up_j, which is the
+    layout the SwiGLU epilogue expects (the pair lands in neighbouring accumulator columns / lanes)."""
+    assert gate_w.shape == up_w.shape
+    out = torch.stack([gate_w, up_w], dim=1)
+    return out.reshape(2 * gate_w.shape[0], *gate_w.shape[1:]).contiguous()
+
+
+def linear_ref(x, w, bias=None, residual=None, epilogue=EPILOGUE_NONE, out_dtype=None, out_scale=1.0):
+    """fp32 PyTorch oracle with the same rounding points as the kernel (one rounding at the output)."""
+    out_dtype = out_dtype or x.dtype
+    y = F.linear(x.float(), w.float()) * out_scale
+    if bias is not None:
+        y = y + bias.float()
+    if epilogue == EPILOGUE_SWIGLU:
+        g, u = y[..., 0::2], y[..., 1::2]
+        y = F.silu(g) * u
+    elif epilogue == EPILOGUE_GELU:
+        y = F.gelu(y, approximate="tanh")
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype)
+
+
+def gemm_plan(M: int, N: int, K: int) -> dict:
+    lib = _lib.kernels()
+    swap, bn, splits, tiles = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    ws = ctypes.c_longlong()
+    lib.mstar_gemm_plan(M, N, K, ctypes.byref(swap), ctypes.byref(bn), ctypes.byref(splits), ctypes.byref(ws),
+                        ctypes.byref(tiles))
+    return dict(swap=swap.value, bn=bn.value, splits=splits.value, ws_bytes=ws.value, tiles=tiles.value)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None, epilogue: int = EPILOGUE_NONE,
+           out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
+           out_scale: float = 1.0, force_splits: int = 0) -> torch.Tensor:
+    """x: [..., K], w: [N, K] -> [..., N] (N/2 for the SwiGLU epilogue)."""
+    if not _lib.use_cuda(x, w):
+        return linear_ref(x, w, bias, residual, epilogue, out_dtype, out_scale)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
+    K = x.shape[-1]
+    N = w.shape[0]
+    assert w.shape[1] == K
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    if w.stride(-1) != 1 or w.stride(0) % 8:
+        w = w.contiguous()
+    M = x2.shape[0]
+    n_out = N // 2 if epilogue == EPILOGUE_SWIGLU else N
+    out_dtype = out_dtype or x.dtype
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    else:
+        assert out.dtype == out_dtype and out.stride(-1) == 1
+    out2 = out.reshape(-1, n_out) if out.dim() != 2 else out
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, n_out)
+        assert res2.dtype == torch.bfloat16 and res2.stride(-1) == 1
+    if M == 0:
+        return out.reshape(*x.shape[:-1], n_out)
+    ws, counters = workspace(x.device)
+    rc = _lib.kernels().mstar_gemm_bf16(
+        ctypes.c_void_p(x2.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(out2.data_ptr()),
+        M, N, K, x2.stride(0), w.stride(0), out2.stride(0),
+        ctypes.c_void_p(_lib.ptr(bias)), ctypes.c_void_p(_lib.ptr(res2)),
+        res2.stride(0) if res2 is not None else 0, int(epilogue), 1 if out_dtype == torch.float32 else 0,
+        ctypes.c_float(out_scale), ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(ws.numel()),
+        ctypes.c_void_p(counters.data_ptr()), counters.numel(), int(force_splits),
+        ctypes.c_void_p(_lib.stream_ptr()))
+    _lib.check(rc, "mstar_gemm_bf16")
+    return out.reshape(*x.shape[:-1], n_out)

@@ -1,0 +1,32 @@
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
+    config.addinivalue_line("markers", "multigpu: needs 2 or more CUDA devices")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords or "multigpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _kernel_status_clean(request):
+    """After every GPU test, the device status word must be clean (no bounded wait ran out)."""
+    yield
+    if "gpu" in request.keywords and torch.cuda.is_available():
+        from mstar_b200.ops import _lib
+        if request.node.get_closest_marker("expects_status") is None:
+            code = _lib.read_status(clear=True)[0]
+            assert code == 0, f"kernel status word set: {code:#x}"
