@@ -124,7 +124,12 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int tin = sh[2];
     const int q_begin = p.q_indptr[req];
     const int q_len = p.q_indptr[req + 1] - q_begin;
-    const int kv_len = p.kv_lens[req];
+    int kv_len = p.kv_lens[req];
+    if (p.paged) {
+        // never read past the pages the request owns, whatever the length array says
+        const int cap = (p.page_indptr[req + 1] - p.page_indptr[req]) * p.page_size;
+        if (kv_len > cap) kv_len = cap;
+    }
     const int tok0 = tin * p.toks_per_tile;                      // first token of the tile inside the request
     int ntok = q_len - tok0;
     if (ntok > p.toks_per_tile) ntok = p.toks_per_tile;

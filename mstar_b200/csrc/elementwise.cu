@@ -186,7 +186,8 @@ struct RopeParams {
     __nv_bfloat16* k_out;  // dense [T, Hkv, D] or null
     __nv_bfloat16* v_out;
     __nv_bfloat16* cache;  // paged cache of this layer or null
-    const int* positions;  // [n_axes, T]
+    const int* positions;  // [n_axes, pos_stride], first T entries of each axis used
+    long long pos_stride;
     const float* inv_freq;  // [rot_dim/2]
     const signed char* axis_of_freq;  // [rot_dim/2] or null (axis 0)
     const __nv_bfloat16* q_norm_w;  // [D] or null
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
                 x1 = __bfloat162float(__float2bfloat16(x1 * inv * w1));
             }
             const int axis = p.axis_of_freq ? p.axis_of_freq[i] : 0;
-            const float ang = (float)p.positions[(size_t)axis * p.T + t] * p.inv_freq[i];
+            const float ang = (float)p.positions[(size_t)axis * p.pos_stride + t] * p.inv_freq[i];
             float sn, cs;
             sincosf(ang, &sn, &cs);
             const float y0 = (x0 * cs - x1 * sn) * qs, y1 = (x1 * cs + x0 * sn) * qs;
@@ -405,17 +406,19 @@ __global__ void affine_kernel(const float* x, __nv_bfloat16* out_bf16, float* ou
 }
 
 // Decode-loop state advance, on device so that a captured step can be replayed without host planning:
-//   kv_lens[b] += 1; positions[b] = kv_lens_new - 1 (the slot of the next token); input_ids[b] = sampled[b]
+//   kv_lens[b] += 1; positions[:, b] += 1; cache_pos[b] += 1; input_ids[b] = sampled[b]
+//   Entries with kv_lens == 0 are padding of a captured batch and never advance.
 __global__ void advance_decode_kernel(int* kv_lens, int* positions, int* cache_pos, long long* input_ids,
-                                      const long long* sampled, const int* active, int B) {
+                                      const long long* sampled, const int* active, int B, int n_axes,
+                                      int pos_stride) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
-    if (active && !active[b]) return;
-    const int n = kv_lens[b] + 1;
-    kv_lens[b] = n;
-    positions[b] = n - 1;
-    if (cache_pos) cache_pos[b] = n - 1;
     if (input_ids && sampled) input_ids[b] = sampled[b];
+    if (active && !active[b]) return;
+    if (kv_lens[b] <= 0) return;
+    kv_lens[b] += 1;
+    for (int a = 0; a < n_axes; ++a) positions[(size_t)a * pos_stride + b] += 1;
+    if (cache_pos) cache_pos[b] += 1;
 }
 
 }  // namespace mstar
@@ -445,14 +448,14 @@ MSTAR_API int mstar_norm(const void* x, const void* residual, void* residual_out
 }
 
 MSTAR_API int mstar_rope_kv(const void* qkv, long long ld_qkv, void* q_out, void* k_out, void* v_out, void* cache,
-                            const int* positions, const float* inv_freq, const signed char* axis_of_freq,
-                            const void* q_norm_w, const void* k_norm_w, const int* token_req, const int* cache_pos,
+                            const int* positions, long long pos_stride, const float* inv_freq,
+                            const signed char* axis_of_freq, const void* q_norm_w, const void* k_norm_w, const int* token_req, const int* cache_pos,
                             const int* page_indptr, const int* page_indices, int T, int Hq, int Hkv, int D,
                             int rot_dim, int page_size, int interleaved, int gemma_norm, float norm_eps,
                             float q_scale, void* stream_) {
     if (T <= 0) return 0;
     RopeParams p{(const __nv_bfloat16*)qkv, ld_qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out,
-                 (__nv_bfloat16*)v_out, (__nv_bfloat16*)cache, positions, inv_freq, axis_of_freq,
+                 (__nv_bfloat16*)v_out, (__nv_bfloat16*)cache, positions, pos_stride, inv_freq, axis_of_freq,
                  (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, token_req, cache_pos, page_indptr,
                  page_indices, T, Hq, Hkv, D, rot_dim, page_size, interleaved, gemma_norm, norm_eps, q_scale};
     rope_kv_kernel<<<T, 256, 0, (cudaStream_t)stream_>>>(p);
@@ -513,10 +516,11 @@ MSTAR_API int mstar_affine(const float* x, void* out_bf16, float* out_f32, long 
 }
 
 MSTAR_API int mstar_advance_decode(int* kv_lens, int* positions, int* cache_pos, long long* input_ids,
-                                   const long long* sampled, const int* active, int B, void* stream_) {
+                                   const long long* sampled, const int* active, int B, int n_axes, int pos_stride,
+                                   void* stream_) {
     if (B <= 0) return 0;
     advance_decode_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream_>>>(kv_lens, positions, cache_pos,
-                                                                             input_ids, sampled, active, B);
+                                                                             input_ids, sampled, active, B, n_axes, pos_stride);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : set_error("advance launch", e);
 }

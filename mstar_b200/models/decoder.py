@@ -1,0 +1,260 @@
+"""Generic GQA transformer decoder over the paged KV pool, tensor-parallel aware.
+
+One implementation serves the Llama-3.2 (Orpheus), Qwen2.5 (BAGEL und/gen experts), Qwen3 (Higgs, Qwen3-TTS
+talker), Qwen3-MoE (Qwen3-Omni thinker/talker) and tiny test backbones; differences are configuration:
+qkv bias, per-head QK-norm, rope flavour (plain / llama-3 scaled / multi-axis mRoPE), tied embeddings, MoE
+layers, sliding window.
+
+Per layer and step the kernels are: fused add+RMSNorm -> QKV GEMM (tcgen05) -> QK-norm+RoPE+KV-write ->
+paged attention (tcgen05) -> o_proj GEMM [+ TP reduce] -> fused add+RMSNorm -> gate_up GEMM with SwiGLU
+epilogue -> down GEMM [+ TP reduce]. Under tensor parallelism the row-parallel GEMMs hand their partial sums to
+``tp_reduce`` (fused one-shot all-reduce over the symmetric heap, NCCL all-reduce as the baseline).
+
+Reference counterparts: mstar/model/orpheus/components/language_model.py (115), mstar/model/components/
+distributed/{linear,attention,mlp,embedding}.py, mstar/model/qwen3_omni/components/thinker.py:188-259.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+
+from ..engine.cache_manager import BatchContext
+from ..ops import attention as attn_ops
+from ..ops import elementwise as ew
+from ..ops import gemm, norm as norm_ops, rope as rope_ops
+from ..parallel.comm import CommGroup
+
+
+@dataclass
+class DecoderConfig:
+    hidden_size: int = 256
+    num_layers: int = 2
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    intermediate_size: int = 688
+    vocab_size: int = 32000
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e6
+    rope_llama3: dict | None = None
+    mrope_sections: list[int] | None = None
+    mrope_interleaved: bool = True
+    qkv_bias: bool = False
+    qk_norm: bool = False
+    tie_embeddings: bool = False
+    sliding_window: int = 0
+    has_lm_head: bool = True
+    has_embedding: bool = True
+    # MoE (0 experts = dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    moe_layers: list[int] | None = None      # None = all layers when num_experts > 0
+    dtype: torch.dtype = torch.bfloat16
+    init_std: float = 0.02
+
+    @property
+    def n_pos_axes(self) -> int:
+        return 3 if self.mrope_sections else 1
+
+
+def _param(shape, dtype, device):
+    return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=False)
+
+
+def tp_reduce(x: torch.Tensor, tp: CommGroup) -> torch.Tensor:
+    """Sum row-parallel partials over the TP group (fused symmetric-heap path when attached)."""
+    if tp.size == 1:
+        return x
+    if tp.symm is not None and x.is_cuda:
+        return tp.symm.all_reduce(x)
+    return tp.all_reduce(x)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int, tp: CommGroup, device):
+        super().__init__()
+        self.cfg, self.layer_idx, self.tp = cfg, layer_idx, tp
+        assert cfg.num_heads % tp.size == 0
+        self.Hq = cfg.num_heads // tp.size
+        self.Hkv = max(1, cfg.num_kv_heads // tp.size)
+        self.D = cfg.head_dim
+        H = cfg.hidden_size
+        self.qkv_proj = _param(((self.Hq + 2 * self.Hkv) * self.D, H), cfg.dtype, device)
+        self.qkv_bias = _param(((self.Hq + 2 * self.Hkv) * self.D,), cfg.dtype, device) if cfg.qkv_bias else None
+        self.o_proj = _param((H, self.Hq * self.D), cfg.dtype, device)
+        self.q_norm = _param((self.D,), cfg.dtype, device) if cfg.qk_norm else None
+        self.k_norm = _param((self.D,), cfg.dtype, device) if cfg.qk_norm else None
+
+    def forward(self, h: torch.Tensor, ctx: BatchContext, rope: "RopeTables") -> torch.Tensor:
+        qkv = gemm.linear(h, self.qkv_proj, bias=self.qkv_bias)
+        kv = ctx.kv(self.layer_idx) if ctx.kv_layers else None
+        q, _, _ = rope_ops.rope_kv(qkv, ctx.positions, rope.inv_freq, self.Hq, self.Hkv, self.D,
+                                   axis_of_freq=rope.axis_of_freq, q_norm_w=self.q_norm, k_norm_w=self.k_norm,
+                                   norm_eps=self.cfg.rms_eps, cache=kv, token_req=ctx.token_req,
+                                   cache_pos=ctx.cache_pos, page_indptr=ctx.plan.page_indptr,
+                                   page_indices=ctx.plan.page_indices)
+        a = attn_ops.attention(q, ctx.plan, kv_cache=kv)
+        o = gemm.linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj)
+        return tp_reduce(o, self.tp)
+
+
+class GatedMLP(nn.Module):
+    """SwiGLU MLP; gate and up rows are stored interleaved so that the activation runs in the GEMM epilogue."""
+
+    def __init__(self, hidden: int, inter: int, tp: CommGroup, dtype, device):
+        super().__init__()
+        self.tp = tp
+        assert inter % tp.size == 0
+        self.F = inter // tp.size
+        self.gate_up_proj = _param((2 * self.F, hidden), dtype, device)
+        self.down_proj = _param((hidden, self.F), dtype, device)
+
+    def forward(self, h: torch.Tensor, reduce: bool = True) -> torch.Tensor:
+        g = gemm.linear(h, self.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
+        d = gemm.linear(g, self.down_proj)
+        return tp_reduce(d, self.tp) if reduce else d
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int, tp: CommGroup, device):
+        super().__init__()
+        self.cfg = cfg
+        self.input_layernorm = _param((cfg.hidden_size,), cfg.dtype, device)
+        self.post_attention_layernorm = _param((cfg.hidden_size,), cfg.dtype, device)
+        self.self_attn = Attention(cfg, layer_idx, tp, device)
+        is_moe = cfg.num_experts > 0 and (cfg.moe_layers is None or layer_idx in cfg.moe_layers)
+        if is_moe:
+            from .moe import SparseMoeBlock
+            self.mlp = SparseMoeBlock(cfg, tp, device)
+        else:
+            self.mlp = GatedMLP(cfg.hidden_size, cfg.intermediate_size, tp, cfg.dtype, device)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None, ctx: BatchContext, rope) -> tuple:
+        if residual is None:
+            residual = x
+            h, _ = norm_ops.norm(x, self.input_layernorm, self.cfg.rms_eps)
+        else:
+            h, residual = norm_ops.norm(x, self.input_layernorm, self.cfg.rms_eps, residual=residual)
+        a = self.self_attn(h, ctx, rope)
+        h, residual = norm_ops.norm(a, self.post_attention_layernorm, self.cfg.rms_eps, residual=residual)
+        return self.mlp(h), residual
+
+
+class RopeTables:
+    def __init__(self, cfg: DecoderConfig, device):
+        self.inv_freq = rope_ops.make_inv_freq(cfg.head_dim, cfg.rope_theta, device, llama3=cfg.rope_llama3)
+        self.axis_of_freq = None
+        if cfg.mrope_sections:
+            self.axis_of_freq = rope_ops.mrope_axis_table(cfg.mrope_sections, cfg.mrope_interleaved).to(device)
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: DecoderConfig, tp: CommGroup | None = None, device="cpu"):
+        super().__init__()
+        self.cfg = cfg
+        self.tp = tp or CommGroup.trivial()
+        self.device_ = torch.device(device)
+        H, V = cfg.hidden_size, cfg.vocab_size
+        self.embed_tokens = _param((V, H), cfg.dtype, device) if cfg.has_embedding else None
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, self.tp, device) for i in range(cfg.num_layers)])
+        self.norm = _param((H,), cfg.dtype, device)
+        self.lm_head = None
+        if cfg.has_lm_head and not cfg.tie_embeddings:
+            self.lm_head = _param((V, H), cfg.dtype, device)
+        self.rope = RopeTables(cfg, device)
+
+    # ---- weights ----
+    @torch.no_grad()
+    def init_random(self, seed: int = 0) -> "DecoderLM":
+        """N(0, init_std) weights from a CPU generator, norms at one. Sharded ranks draw the full tensor and keep
+        their slice, so TP ranks hold slices of the same model."""
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        cfg, tp = self.cfg, self.tp
+        std = cfg.init_std
+
+        def draw(shape):
+            return torch.randn(shape, generator=g, dtype=torch.float32) * std
+
+        if self.embed_tokens is not None:
+            self.embed_tokens.copy_(draw(self.embed_tokens.shape).to(cfg.dtype))
+        Hq, Hkv, D, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_size
+        for layer in self.layers:
+            at = layer.self_attn
+            q, k, v = draw((Hq * D, H)), draw((Hkv * D, H)), draw((Hkv * D, H))
+            at.qkv_proj.copy_(shard_qkv(q, k, v, Hq, Hkv, D, tp.rank, tp.size).to(cfg.dtype))
+            if at.qkv_bias is not None:
+                at.qkv_bias.zero_()
+            o = draw((H, Hq * D))
+            at.o_proj.copy_(o[:, tp.rank * at.Hq * D:(tp.rank + 1) * at.Hq * D].to(cfg.dtype))
+            if at.q_norm is not None:
+                at.q_norm.fill_(1.0)
+                at.k_norm.fill_(1.0)
+            layer.input_layernorm.fill_(1.0)
+            layer.post_attention_layernorm.fill_(1.0)
+            if isinstance(layer.mlp, GatedMLP):
+                F = cfg.intermediate_size
+                gt, up, dn = draw((F, H)), draw((F, H)), draw((H, F))
+                load_gated_mlp(layer.mlp, gt, up, dn, tp.rank, tp.size, cfg.dtype)
+            else:
+                layer.mlp.init_random(g, std)
+        self.norm.fill_(1.0)
+        if self.lm_head is not None:
+            self.lm_head.copy_(draw(self.lm_head.shape).to(cfg.dtype))
+        return self
+
+    def head_weight(self) -> torch.Tensor:
+        return self.lm_head if self.lm_head is not None else self.embed_tokens
+
+    # ---- forward ----
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return ew.embed(input_ids.reshape(-1), self.embed_tokens)
+
+    def forward_hidden(self, x: torch.Tensor, ctx: BatchContext) -> torch.Tensor:
+        """x: [T, H] input embeddings -> final-normed hidden states [T, H]."""
+        residual = None
+        for layer in self.layers:
+            x, residual = layer(x, residual, ctx, self.rope)
+        h, _ = norm_ops.norm(x, self.norm, self.cfg.rms_eps, residual=residual)
+        return h
+
+    def logits(self, hidden_rows: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+        return gemm.linear(hidden_rows, self.head_weight(), out_dtype=out_dtype)
+
+    def forward(self, ctx: BatchContext, input_ids: torch.Tensor | None = None,
+                inputs_embeds: torch.Tensor | None = None, all_logits: bool = False,
+                return_hidden: bool = False):
+        x = inputs_embeds if inputs_embeds is not None else self.embed(input_ids)
+        h = self.forward_hidden(x, ctx)
+        if return_hidden and not self.cfg.has_lm_head:
+            return h
+        rows = h if all_logits else h.index_select(0, ctx.logit_rows)
+        lg = self.logits(rows)
+        return (lg, h) if return_hidden else lg
+
+
+def shard_qkv(q, k, v, Hq, Hkv, D, rank, size):
+    """Rows of the fused QKV weight (or bias) held by one TP rank: its q heads, then its k heads, then v heads.
+    KV heads are replicated when there are fewer of them than ranks."""
+    hq = Hq // size
+    qs = q[rank * hq * D:(rank + 1) * hq * D]
+    if Hkv >= size:
+        hk = Hkv // size
+        ks, vs = k[rank * hk * D:(rank + 1) * hk * D], v[rank * hk * D:(rank + 1) * hk * D]
+    else:
+        rep = size // Hkv
+        i = rank // rep
+        ks, vs = k[i * D:(i + 1) * D], v[i * D:(i + 1) * D]
+    return torch.cat([qs, ks, vs], dim=0)
+
+
+@torch.no_grad()
+def load_gated_mlp(mlp: GatedMLP, gate, up, down, rank, size, dtype):
+    F = gate.shape[0] // size
+    gs, us = gate[rank * F:(rank + 1) * F], up[rank * F:(rank + 1) * F]
+    mlp.gate_up_proj.copy_(gemm.interleave_gate_up(gs, us).to(dtype))
+    mlp.down_proj.copy_(down[:, rank * F:(rank + 1) * F].to(dtype))

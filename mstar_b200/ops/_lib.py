@@ -12,6 +12,8 @@ from pathlib import Path
 
 import torch
 
+from . import _counters
+
 _LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
 _KERNELS = None
 _RUNTIME = None
@@ -64,6 +66,7 @@ def use_cuda(*tensors: torch.Tensor) -> bool:
 
 
 def check(rc: int, what: str) -> None:
+    _counters.bump()
     if rc != 0:
         msg = kernels().mstar_last_error().decode(errors="replace")
         raise RuntimeError(f"{what} failed: {msg}")

@@ -143,19 +143,25 @@ def affine(x: torch.Tensor, a: float, b: float, out_dtype=torch.bfloat16) -> tor
 
 
 def advance_decode(kv_lens, positions, cache_pos=None, input_ids=None, sampled=None, active=None):
-    """kv_lens += 1; positions = cache_pos = kv_lens - 1; input_ids = sampled (rows with active == 0 untouched)."""
+    """One decode step forward on the device: kv_lens += 1, positions (all axes) += 1, cache_pos += 1,
+    input_ids = sampled. Entries with kv_lens == 0 (padding) or active == 0 keep their plan."""
     B = kv_lens.numel()
+    pos2 = positions if positions.dim() > 1 else positions.reshape(1, B)
     if not _lib.use_cuda(kv_lens):
-        m = torch.ones(B, dtype=torch.bool) if active is None else active.bool()
-        kv_lens[m] += 1
-        positions[m] = kv_lens[m] - 1
-        if cache_pos is not None:
-            cache_pos[m] = kv_lens[m] - 1
+        m = kv_lens > 0
+        if active is not None:
+            m &= active.bool()
         if input_ids is not None and sampled is not None:
-            input_ids[m] = sampled[m]
+            input_ids.copy_(sampled)
+        kv_lens[m] += 1
+        pos2[:, m] += 1
+        if cache_pos is not None:
+            cache_pos[m] += 1
         return
+    assert pos2.stride(1) == 1
     rc = _lib.kernels().mstar_advance_decode(ctypes.c_void_p(kv_lens.data_ptr()), ctypes.c_void_p(positions.data_ptr()),
                                              ctypes.c_void_p(_lib.ptr(cache_pos)), ctypes.c_void_p(_lib.ptr(input_ids)),
                                              ctypes.c_void_p(_lib.ptr(sampled)), ctypes.c_void_p(_lib.ptr(active)),
-                                             int(B), ctypes.c_void_p(_lib.stream_ptr()))
+                                             int(B), int(pos2.shape[0]), int(pos2.stride(0)),
+                                             ctypes.c_void_p(_lib.stream_ptr()))
     _lib.check(rc, "mstar_advance_decode")

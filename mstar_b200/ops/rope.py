@@ -122,7 +122,7 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, 
             write_kv_ref(cache, k, v, token_req, cache_pos, page_indptr, page_indices)
         return q, (k if dense_kv else None), (v if dense_kv else None)
     assert qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1
-    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32 and positions.stride(-1) == 1
     if q_out is None:
         q_out = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
     k_out = v_out = None
@@ -135,7 +135,8 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, 
     rc = _lib.kernels().mstar_rope_kv(
         ctypes.c_void_p(qkv.data_ptr()), ctypes.c_longlong(qkv.stride(0)), ctypes.c_void_p(q_out.data_ptr()),
         ctypes.c_void_p(_lib.ptr(k_out)), ctypes.c_void_p(_lib.ptr(v_out)), ctypes.c_void_p(_lib.ptr(cache)),
-        ctypes.c_void_p(positions.data_ptr()), ctypes.c_void_p(inv_freq.data_ptr()),
+        ctypes.c_void_p(positions.data_ptr()),
+        ctypes.c_longlong(positions.stride(0) if positions.dim() > 1 else T), ctypes.c_void_p(inv_freq.data_ptr()),
         ctypes.c_void_p(_lib.ptr(axis_of_freq)), ctypes.c_void_p(_lib.ptr(q_norm_w)),
         ctypes.c_void_p(_lib.ptr(k_norm_w)), ctypes.c_void_p(_lib.ptr(token_req)),
         ctypes.c_void_p(_lib.ptr(cache_pos)), ctypes.c_void_p(_lib.ptr(page_indptr)),

@@ -128,12 +128,19 @@ class SamplerState:
         self._slot_of: dict[str, int] = {}
 
     def assign(self, request_id: str, cfg: SamplingConfig, seed: int | None = None,
-               prompt_ids: torch.Tensor | None = None) -> int:
+               prompt_ids: torch.Tensor | None = None, slot: int | None = None) -> int:
+        """Bind a request to a slot (a specific one when ``slot`` is given) and load its parameters."""
         if request_id in self._slot_of:
             return self._slot_of[request_id]
         if not self._free:
             raise RuntimeError("sampler: no free slot")
-        s = self._free.pop()
+        if slot is not None:
+            if slot not in self._free:
+                raise RuntimeError(f"sampler: slot {slot} is taken")
+            self._free.remove(slot)
+            s = slot
+        else:
+            s = self._free.pop()
         self._slot_of[request_id] = s
         self.temperature[s] = float(cfg.temperature)
         self.top_k[s] = int(cfg.top_k)

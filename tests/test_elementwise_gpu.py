@@ -94,7 +94,7 @@ def test_small_elementwise():
     _close(xn, xr, 1e-4)
     _close(v, vr, 1e-3)
     kv = torch.tensor([5, 9], dtype=torch.int32).cuda()
-    pos = torch.zeros(2, dtype=torch.int32).cuda()
+    pos = torch.tensor([4, 8], dtype=torch.int32).cuda()
     ids2 = torch.zeros(2, dtype=torch.int64).cuda()
     E.advance_decode(kv, pos, None, ids2, torch.tensor([11, 12]).cuda())
     assert kv.tolist() == [6, 10] and pos.tolist() == [5, 9] and ids2.tolist() == [11, 12]
