@@ -98,6 +98,9 @@ def main():
     ap.add_argument("--gen-tokens", type=int, default=1200)
     ap.add_argument("--ttft-samples", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="run ONE eager decode step between cudaProfilerStart/Stop and exit (for ncu "
+                         "--profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -162,6 +165,18 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.profile_step:
+        live = {i: r for i, r in enumerate(eng._rows) if r is not None}
+        ctx = eng._plan_rows(live, C)
+        ctx.plan.splits = eng._graph_splits.get(C, 1)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng._decode_body(ctx)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "one eager decode step", "batch": C}))
+        return
 
     sampler = ClockSampler(local)
     # ---- (1) end to end through the public API ----
