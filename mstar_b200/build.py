@@ -37,7 +37,8 @@ def _digest(path: Path, extra: str) -> str:
     h.update(extra.encode())
     h.update(path.read_bytes())
     # headers are few and small: fold all of them in so that a header edit rebuilds every object
-    for hdr in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((CSRC / "runtime").glob("*.h"))):
+    for hdr in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.inc")) +
+                      list((CSRC / "runtime").glob("*.h"))):
         h.update(hdr.read_bytes())
     return h.hexdigest()
 

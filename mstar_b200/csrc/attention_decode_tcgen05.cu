@@ -1,0 +1,285 @@
+// Paged-KV decode attention with the roles of keys and queries swapped on the tensor core.
+//
+// A decode step has only G = Hq/Hkv query rows per (request, kv head) — far too few to fill the 128-row UMMA M
+// dimension. Here the 128 KEYS of a tile take the M dimension instead:
+//     S^T[key, col] = K_tile[128 x D] * Q^T[D x 16]          (A = K tile, K-major; B = Q rows, N = 16)
+//     O^T[d,  col] += V_tile^T[D x 128] * P^T[128 x 16]       (A = V tile as MN-major operand; B = P^T, N = 16)
+// so every TMEM lane / softmax thread owns one key (then one head-dim row d) and handles only <= 16 values per
+// tile instead of a 128-wide score row. Columns are (token, head-in-group) pairs; up to 16 / G new tokens per
+// request are supported (plain decode uses one).
+//
+// Per tile: TMA brings K and V pages (3-stage ring), UMMA 1 -> the 4 softmax warps read S^T (16 columns), reduce
+// the column maxima across the 128 keys (warp shuffles + one named barrier), write P^T as bf16 into the swizzled
+// K-major B tile, UMMA 2 -> fold O^T tile into 16 fp32 registers per thread with the running rescale. Row sums
+// stay thread-private until the end. Split-KV partials are merged by the last CTA of a (request, kv head).
+//
+// Reference counterparts: FlashInfer BatchDecodeWithPagedKVCacheWrapper (mstar/utils/flashinfer_utils.py:293-489),
+// Triton dense-KV decode kernel (mstar/utils/attention.py:6-134).
+#include <cuda.h>
+#include "common.cuh"
+#include "host_common.h"
+
+namespace mstar {
+
+struct DecAttnParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    long long q_tok_stride, o_tok_stride;
+    const int* q_indptr;
+    const int* kv_lens;
+    const int* page_indptr;
+    const int* page_indices;
+    int B, Hq, Hkv, G, page_size, causal, window, splits;
+    float scale_log2;
+    float* ws_o;              // [splits, T*Hq, D]
+    float* ws_ml;             // [splits, T*Hq, 2]
+    unsigned int* counters;   // [B * Hkv]
+    long long ws_rows;
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+
+constexpr int DA_KEYS = 128;
+constexpr int DA_COLS = 16;
+constexpr int DA_STAGES = 3;
+constexpr int DA_HD = 128;
+constexpr int DA_K_BYTES = DA_KEYS * DA_HD * 2;     // 32 KB
+constexpr int DA_STAGE = 2 * DA_K_BYTES;            // K + V
+constexpr int DA_Q_BYTES = DA_COLS * DA_HD * 2;     // 4 KB
+constexpr int DA_P_BYTES = DA_COLS * DA_KEYS * 2;   // 4 KB
+constexpr int DA_SMEM = DA_Q_BYTES + DA_P_BYTES + DA_STAGES * DA_STAGE + 1024 + 1024;
+
+__global__ void __launch_bounds__(192, 1)
+attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                           const DecAttnParams p) {
+    constexpr int TMEM_S0 = 0, TMEM_S1 = 16, TMEM_O = 32, TMEM_COLS = 64;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;                         // [2 atoms][16 rows][128 B]
+    uint8_t* sP = smem + DA_Q_BYTES;            // [2 atoms][16 rows][128 B]  (P^T: rows = columns c, K = keys)
+    uint8_t* sKV = sP + DA_P_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + DA_STAGES * DA_STAGE);
+    uint64_t* k_full = bars;                    // [3]
+    uint64_t* v_full = bars + 3;                // [3]
+    uint64_t* kv_empty = bars + 6;              // [3]
+    uint64_t* s_full = bars + 9;                // [2]
+    uint64_t* s_empty = bars + 11;              // [2]
+    uint64_t* p_full = bars + 13;
+    uint64_t* o_full = bars + 14;
+    uint64_t* o_empty = bars + 15;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* sh = reinterpret_cast<volatile int*>(tmem_slot + 1);   // [0] abort [1] last-split flag
+    float* red = reinterpret_cast<float*>(const_cast<int*>(sh) + 4);     // [2][4 warps][16] max exchange, then sums
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int q_begin = p.q_indptr[req];
+    const int q_len = p.q_indptr[req + 1] - q_begin;
+    int ncols = q_len * p.G;
+    if (ncols > DA_COLS) ncols = DA_COLS;       // host guarantees q_len * G <= 16
+    int kv_len = p.kv_lens[req];
+    const int npages = p.page_indptr[req + 1] - p.page_indptr[req];
+    if (kv_len > npages * p.page_size) kv_len = npages * p.page_size;
+    const int qpos0 = kv_len - q_len;
+    int key_begin = 0;
+    if (p.window > 0) { key_begin = qpos0 - p.window + 1; if (key_begin < 0) key_begin = 0; }
+    const int tile_first = key_begin / DA_KEYS;
+    const int tile_last = kv_len > 0 ? (kv_len - 1) / DA_KEYS : -1;
+    int nt_all = tile_last - tile_first + 1;
+    if (nt_all < 0 || q_len <= 0) nt_all = 0;
+    const int per = (nt_all + p.splits - 1) / p.splits;
+    const int jt0 = tile_first + split * per;
+    int jt1 = jt0 + per;
+    if (jt1 > tile_last + 1) jt1 = tile_last + 1;
+    const int ntiles = jt1 > jt0 ? jt1 - jt0 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+        mbar_init(&s_empty[0], 128); mbar_init(&s_empty[1], 128);
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        mbar_init(o_empty, 128);
+        sh[0] = 0; sh[1] = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    if (warp == 2) {
+        // Q rows -> swizzled K-major B tile: lane c < 16 copies row c (zero rows beyond ncols)
+        if (lane < DA_COLS) {
+            const int c = lane, tl = c / p.G, g = c - tl * p.G;
+            const bool valid = c < ncols;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                p.q + (size_t)(q_begin + (valid ? tl : 0)) * p.q_tok_stride + (size_t)(kvh * p.G + (valid ? g : 0)) * DA_HD);
+#pragma unroll
+            for (int ch = 0; ch < DA_HD / 8; ++ch) {
+                const uint4 v = valid ? src[ch] : make_uint4(0, 0, 0, 0);
+                const int atom = ch >> 3, cc = ch & 7;
+                *reinterpret_cast<uint4*>(sQ + atom * (DA_COLS * 128) + c * 128 + ((cc ^ (c & 7)) << 4)) = v;
+            }
+        }
+        fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // =========================== TMA producer ===========================
+        if (lane == 0 && ntiles > 0) {
+            tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmV);
+            const int ppt = DA_KEYS / p.page_size;
+            const int* pages = p.page_indices + p.page_indptr[req];
+            int issued = 0;
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % DA_STAGES;
+                const uint32_t ph = (i / DA_STAGES) & 1;
+                if (!mbar_wait(&kv_empty[s], ph ^ 1, p.wait_limit_ns)) {
+                    report_status(p.status, KID_ATTN_DECODE, 1, i, s);
+                    sh[0] = 1;
+                    break;
+                }
+                if (sh[0]) break;
+                uint8_t* sK = sKV + s * DA_STAGE;
+                uint8_t* sV = sK + DA_K_BYTES;
+                const int jt = jt0 + i;
+                mbar_expect_tx(&k_full[s], DA_K_BYTES);
+                mbar_expect_tx(&v_full[s], DA_K_BYTES);
+                for (int pg = 0; pg < ppt; ++pg) {
+                    int pi = jt * ppt + pg;
+                    if (pi >= npages) pi = npages - 1;
+                    const int page = pages[pi];
+                    const int row_off = pg * p.page_size * 128;
+                    tma_load_4d(sK + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
+                    tma_load_4d(sK + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
+                }
+                for (int pg = 0; pg < ppt; ++pg) {
+                    int pi = jt * ppt + pg;
+                    if (pi >= npages) pi = npages - 1;
+                    const int page = pages[pi];
+                    const int row_off = pg * p.page_size * 128;
+                    tma_load_4d(sV + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
+                    tma_load_4d(sV + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
+                }
+                issued = i + 1;
+            }
+            if (sh[0]) {
+                for (int i = (issued > DA_STAGES ? issued - DA_STAGES : 0); i < issued; ++i) {
+                    mbar_wait(&k_full[i % DA_STAGES], (i / DA_STAGES) & 1, 1000000ull);
+                    mbar_wait(&v_full[i % DA_STAGES], (i / DA_STAGES) & 1, 1000000ull);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== UMMA issuer ===========================
+        if (lane == 0 && ntiles > 0) {
+            constexpr uint32_t idesc_s = umma_idesc(DA_KEYS, DA_COLS, 1, 1);                  // K tile x Q^T
+            constexpr uint32_t idesc_o = umma_idesc(DA_HD, DA_COLS, 1, 1) | (1u << 15);       // A (V^T) MN-major
+            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            bool ok = true;
+            auto issue_s = [&](int i) -> bool {
+                const int s = i % DA_STAGES;
+                if (!mbar_wait(&k_full[s], (i / DA_STAGES) & 1, p.wait_limit_ns)) {
+                    report_status(p.status, KID_ATTN_DECODE, 2, i, s);
+                    return false;
+                }
+                if (i >= 2 && !mbar_wait(&s_empty[i & 1], ((i >> 1) - 1) & 1, p.wait_limit_ns)) {
+                    report_status(p.status, KID_ATTN_DECODE, 3, i, 0);
+                    return false;
+                }
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sKV + s * DA_STAGE);
+                const uint32_t d = tmem_base + ((i & 1) ? TMEM_S1 : TMEM_S0);
+#pragma unroll
+                for (int k = 0; k < DA_HD / 16; ++k) {
+                    const uint32_t aoff = (k >> 2) * (DA_KEYS * 128) + (k & 3) * 32;
+                    const uint32_t boff = (k >> 2) * (DA_COLS * 128) + (k & 3) * 32;
+                    umma_f16_ss(d, umma_smem_desc_sw128(k_addr + aoff), umma_smem_desc_sw128(q_addr + boff), idesc_s,
+                                k != 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[i & 1]);
+                return true;
+            };
+            ok = issue_s(0);
+            for (int i = 0; ok && i < ntiles; ++i) {
+                const int s = i % DA_STAGES;
+                if (i + 1 < ntiles) ok = issue_s(i + 1);
+                if (!ok) break;
+                if (!mbar_wait(p_full, i & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 4, i, 0); ok = false; break; }
+                if (!mbar_wait(&v_full[s], (i / DA_STAGES) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 5, i, 0); ok = false; break; }
+                if (i >= 1 && !mbar_wait(o_empty, (i - 1) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 6, i, 0); ok = false; break; }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sKV + s * DA_STAGE + DA_K_BYTES);
+#pragma unroll
+                for (int k = 0; k < DA_KEYS / 16; ++k) {
+                    // A = V^T: M (= d) is the contiguous dimension. LBO = distance of the two 64-wide d atoms,
+                    // SBO = distance of 8-key groups; one K step = 16 keys = 2048 bytes.
+                    uint64_t da = umma_smem_desc_sw128(v_addr + k * 2048);
+                    da = (da & ~(uint64_t(0x3fff) << 16)) | (uint64_t((DA_KEYS * 128) >> 4) << 16);
+                    const uint32_t boff = (k >> 2) * (DA_COLS * 128) + (k & 3) * 32;
+                    umma_f16_ss(tmem_base + TMEM_O, da, umma_smem_desc_sw128(p_addr + boff), idesc_o, k != 0 ? 1u : 0u);
+                }
+                umma_commit(o_full);
+                umma_commit(&kv_empty[s]);
+            }
+            if (!ok) sh[0] = 1;
+        }
+    } else {
+#include "attention_decode_softmax.inc"
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace mstar
+
+using namespace mstar;
+
+MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_stride, long long o_tok_stride,
+                                     const int* q_indptr, const int* kv_lens, int B, int T_q, int Hq, int Hkv, int D,
+                                     const void* kcache, int num_pages, int page_size, const int* page_indptr,
+                                     const int* page_indices, int causal, int window, float scale, int splits,
+                                     float* ws_o, float* ws_ml, void* counters, void* stream_) {
+    if (B <= 0) return 0;
+    if (D != DA_HD) return set_error("attention_decode: head_dim must be 128", cudaSuccess);
+    if (Hq % Hkv || Hq / Hkv > DA_COLS) return set_error("attention_decode: GQA group must divide and be <= 16", cudaSuccess);
+    if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)))
+        return set_error("attention_decode: page_size must be a power of two in [8, 128]", cudaSuccess);
+    DecAttnParams p;
+    p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+    p.q_tok_stride = q_tok_stride; p.o_tok_stride = o_tok_stride;
+    p.q_indptr = q_indptr; p.kv_lens = kv_lens; p.page_indptr = page_indptr; p.page_indices = page_indices;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.page_size = page_size;
+    p.causal = causal; p.window = window; p.splits = splits < 1 ? 1 : splits;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = (unsigned int*)counters;
+    p.ws_rows = (long long)T_q * Hq;
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    if (p.splits > 1 && (!ws_o || !ws_ml || !counters)) return set_error("attention_decode: split-KV needs scratch", cudaSuccess);
+    unsigned long long dims[4] = {(unsigned long long)D, (unsigned long long)page_size, (unsigned long long)Hkv,
+                                  (unsigned long long)num_pages};
+    unsigned long long strides[4] = {2ull, (unsigned long long)D * 2, (unsigned long long)page_size * D * 2,
+                                     2ull * Hkv * page_size * D * 2};
+    unsigned int box[4] = {64u, (unsigned int)page_size, 1u, 1u};
+    CUtensorMap tmK, tmV;
+    const __nv_bfloat16* kc = (const __nv_bfloat16*)kcache;
+    if (make_tmap(&tmK, kc, 2, 4, dims, strides, box, 1)) return -1;
+    if (make_tmap(&tmV, kc + (size_t)Hkv * page_size * D, 2, 4, dims, strides, box, 1)) return -1;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DA_SMEM);
+        if (e != cudaSuccess) return set_error("attention_decode: cudaFuncSetAttribute failed", e);
+        configured = true;
+    }
+    dim3 grid(B, Hkv, p.splits);
+    attn_decode_tcgen05_kernel<<<grid, 192, DA_SMEM, (cudaStream_t)stream_>>>(tmK, tmV, p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : set_error("attention_decode: launch failed", e);
+}

@@ -120,12 +120,22 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
     for (int i = tid; i < SP_BINS; i += SP_NT) { hist_mass[i] = 0.f; hist_cnt[i] = 0; }
     __syncthreads();
     float z = 0.f;
-    for (int i = tid; i < p.V; i += SP_NT) {
-        const float e = __expf(logit_at(i) - mx);
-        z += e;
-        const uint32_t key = __float_as_uint(e) >> 8;     // 24-bit monotone key (sign bit is 0)
-        atomicAdd(&hist_mass[key >> 12], e);
-        atomicAdd(&hist_cnt[key >> 12], 1);
+    {
+        // run-length aggregation: neighbouring elements often fall into the same bin (flat distributions put most
+        // of the vocabulary into a handful of bins), so a thread flushes to shared memory only when the bin changes
+        int cur = -1, ccnt = 0;
+        float cmass = 0.f;
+        for (int i = tid; i < p.V; i += SP_NT) {
+            const float e = __expf(logit_at(i) - mx);
+            z += e;
+            const int bin = (int)((__float_as_uint(e) >> 8) >> 12);     // top 12 of a 24-bit monotone key
+            if (bin != cur) {
+                if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
+                cur = bin; cmass = 0.f; ccnt = 0;
+            }
+            cmass += e; ++ccnt;
+        }
+        if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
     }
     z = warp_sum(z);
     if (lane == 0) red_f[warp] = z;
@@ -165,13 +175,22 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         // second level inside bin b1
         for (int i = tid; i < SP_BINS; i += SP_NT) { hist_mass[i] = 0.f; hist_cnt[i] = 0; }
         __syncthreads();
-        for (int i = tid; i < p.V; i += SP_NT) {
-            const float e = __expf(logit_at(i) - mx);
-            const uint32_t key = __float_as_uint(e) >> 8;
-            if ((int)(key >> 12) == b1) {
-                atomicAdd(&hist_mass[key & 0xfff], e);
-                atomicAdd(&hist_cnt[key & 0xfff], 1);
+        {
+            int cur = -1, ccnt = 0;
+            float cmass = 0.f;
+            for (int i = tid; i < p.V; i += SP_NT) {
+                const float e = __expf(logit_at(i) - mx);
+                const uint32_t key = __float_as_uint(e) >> 8;
+                if ((int)(key >> 12) == b1) {
+                    const int bin = (int)(key & 0xfff);
+                    if (bin != cur) {
+                        if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
+                        cur = bin; cmass = 0.f; ccnt = 0;
+                    }
+                    cmass += e; ++ccnt;
+                }
             }
+            if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
         }
         __syncthreads();
         if (tid == 0) {

@@ -194,7 +194,8 @@ class BatchedCacheManager:
             splits = attn_ops.choose_splits(Bp, cfg.num_kv_heads, ntiles, max_kv) if max(q_lens, default=1) == 1 else 1
         plan = attn_ops.AttnPlan(q_indptr=buf.d("q_indptr"), kv_lens=buf.d("kv_lens"), batch=Bp, num_q_tokens=T,
                                  num_q_tiles=ntiles, page_indptr=buf.d("page_indptr"),
-                                 page_indices=buf.d("page_indices"), splits=splits, causal=causal, window=window)
+                                 page_indices=buf.d("page_indices"), splits=splits, causal=causal, window=window,
+                                 max_q_len=max(list(q_lens) + [1]))
         ctx = BatchContext(plan=plan, positions=buf.d("positions").view(self.n_pos_axes, -1)[:, :T]
                            if self.n_pos_axes > 1 else buf.d("positions")[:T],
                            token_req=buf.d("token_req")[:T], cache_pos=buf.d("cache_pos")[:T],

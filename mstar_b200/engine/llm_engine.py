@@ -282,7 +282,7 @@ class LLMEngine:
         plan = attn_ops.AttnPlan(q_indptr=buf.d("q_indptr"), kv_lens=buf.d("kv_lens"), batch=B, num_q_tokens=B,
                                  num_q_tiles=ntiles, page_indptr=buf.d("page_indptr"),
                                  page_indices=buf.d("page_indices"), splits=splits, causal=True,
-                                 window=self.cfg.sliding_window)
+                                 window=self.cfg.sliding_window, max_q_len=1)
         from .cache_manager import BatchContext
         positions = buf.d("positions").view(cm.n_pos_axes, -1)[:, :B] if cm.n_pos_axes > 1 else buf.d("positions")[:B]
         return BatchContext(plan=plan, positions=positions, token_req=buf.d("token_req")[:B],

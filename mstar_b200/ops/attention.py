@@ -36,6 +36,7 @@ class AttnPlan:
     splits: int = 1
     causal: bool = True
     window: int = 0
+    max_q_len: int = 0              # largest q_len of the batch when known (1 = plain decode); 0 = unknown
 
 
 def count_q_tiles(q_lens, group: int) -> int:
@@ -145,8 +146,23 @@ def attention(q: torch.Tensor, plan: AttnPlan, *, kv_cache: torch.Tensor | None 
     splits = max(1, int(plan.splits))
     ws_o = ws_ml = cnt = 0
     if splits > 1:
-        s = _scratch(q.device, T * Hq, D, splits, plan.num_q_tiles * Hkv)
+        s = _scratch(q.device, T * Hq, D, splits, max(plan.num_q_tiles, plan.batch) * Hkv)
         ws_o, ws_ml, cnt = s["o"].data_ptr(), s["ml"].data_ptr(), s["c"].data_ptr()
+    G = Hq // Hkv
+    if paged and D == 128 and 0 < plan.max_q_len and plan.max_q_len * G <= 16:
+        # decode: keys on the UMMA M dimension (csrc/attention_decode_tcgen05.cu); no lse output in this path
+        if not lse:
+            rc = _lib.kernels().mstar_attention_decode(
+                ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                ctypes.c_longlong(q.stride(0)), ctypes.c_longlong(out.stride(0)),
+                ctypes.c_void_p(plan.q_indptr.data_ptr()), ctypes.c_void_p(plan.kv_lens.data_ptr()),
+                int(plan.batch), int(T), int(Hq), int(Hkv), int(D), ctypes.c_void_p(kp), int(num_pages),
+                int(page_size), ctypes.c_void_p(plan.page_indptr.data_ptr()),
+                ctypes.c_void_p(plan.page_indices.data_ptr()), 1 if plan.causal else 0, int(plan.window),
+                ctypes.c_float(scale), splits, ctypes.c_void_p(ws_o), ctypes.c_void_p(ws_ml), ctypes.c_void_p(cnt),
+                ctypes.c_void_p(_lib.stream_ptr()))
+            _lib.check(rc, "mstar_attention_decode")
+            return out
     rc = _lib.kernels().mstar_attention(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(out.data_ptr()),
         ctypes.c_longlong(q.stride(0)), ctypes.c_longlong(out.stride(0)),

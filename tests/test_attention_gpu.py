@@ -41,8 +41,24 @@ def _close(a, b, tol=2e-2):
 def test_paged_decode(Hq, Hkv, D, ps):
     kv_lens = [1, 17, 128, 129, 700, 1300]
     q, cache, plan = _paged_case([1] * len(kv_lens), kv_lens, Hq, Hkv, D, ps)
+    ref = A.attention_ref(q, plan, kv_cache=cache)
+    _close(A.attention(q, plan, kv_cache=cache), ref)       # general kernel (q_len unknown)
+    plan.max_q_len = 1                                       # swapped decode kernel when D == 128
+    _close(A.attention(q, plan, kv_cache=cache), ref)
+
+
+def test_decode_kernel_multi_token_window_and_splits():
+    """Swapped decode kernel: 2 new tokens per request (causal inside the pair), sliding window, split-KV."""
+    q, cache, plan = _paged_case([2, 1, 2], [500, 1, 1030], 24, 8, 128, 128, seed=21)
+    plan.max_q_len = 2
+    ref = A.attention_ref(q, plan, kv_cache=cache)
+    _close(A.attention(q, plan, kv_cache=cache), ref)
+    plan.splits = 4
     out = A.attention(q, plan, kv_cache=cache)
-    _close(out, A.attention_ref(q, plan, kv_cache=cache))
+    _close(out, ref)
+    assert torch.equal(out, A.attention(q, plan, kv_cache=cache))
+    plan.window, plan.splits = 300, 1
+    _close(A.attention(q, plan, kv_cache=cache), A.attention_ref(q, plan, kv_cache=cache))
 
 
 @pytest.mark.parametrize("splits", [2, 5])
@@ -50,6 +66,7 @@ def test_paged_decode_split_kv(splits):
     kv_lens = [3000, 130, 1]
     q, cache, plan = _paged_case([1] * 3, kv_lens, 24, 8, 128, 128, seed=3)
     plan.splits = splits
+    plan.max_q_len = 0
     out = A.attention(q, plan, kv_cache=cache)
     ref = A.attention_ref(q, plan, kv_cache=cache)
     _close(out, ref)
