@@ -41,15 +41,19 @@ struct DecAttnParams {
 
 constexpr int DA_KEYS = 128;
 constexpr int DA_COLS = 16;
-constexpr int DA_STAGES = 3;
 constexpr int DA_HD = 128;
-constexpr int DA_K_BYTES = DA_KEYS * DA_HD * 2;     // 32 KB
-constexpr int DA_STAGE = 2 * DA_K_BYTES;            // K + V
+constexpr int DA_K_BYTES = DA_KEYS * DA_HD * 2;     // 32 KB (one K or V tile)
 constexpr int DA_Q_BYTES = DA_COLS * DA_HD * 2;     // 4 KB
 constexpr int DA_P_BYTES = DA_COLS * DA_KEYS * 2;   // 4 KB
-constexpr int DA_SMEM = DA_Q_BYTES + DA_P_BYTES + DA_STAGES * DA_STAGE + 1024 + 1024;
+__host__ __device__ constexpr int da_smem_bytes(int ks, int vs) {
+    return DA_Q_BYTES + DA_P_BYTES + (ks + vs) * DA_K_BYTES + 1024 + 1024;
+}
 
-__global__ void __launch_bounds__(192, 1)
+// KS / VS: depth of the K and V tile rings. <1,1> keeps a CTA at 74 KB so that three CTAs share an SM and hide
+// each other's per-tile latency chain (the regime of batched decode); deeper rings serve small grids, where one
+// CTA per SM must prefetch for itself. NC: number of accumulator columns kept in registers (>= q_len * G).
+template <int KS, int VS, int NC, int MINB>
+__global__ void __launch_bounds__(192, MINB)
 attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                            const DecAttnParams p) {
     constexpr int TMEM_S0 = 0, TMEM_S1 = 16, TMEM_O = 32, TMEM_COLS = 64;
@@ -57,26 +61,30 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                         // [2 atoms][16 rows][128 B]
     uint8_t* sP = smem + DA_Q_BYTES;            // [2 atoms][16 rows][128 B]  (P^T: rows = columns c, K = keys)
-    uint8_t* sKV = sP + DA_P_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + DA_STAGES * DA_STAGE);
-    uint64_t* k_full = bars;                    // [3]
-    uint64_t* v_full = bars + 3;                // [3]
-    uint64_t* kv_empty = bars + 6;              // [3]
-    uint64_t* s_full = bars + 9;                // [2]
-    uint64_t* s_empty = bars + 11;              // [2]
-    uint64_t* p_full = bars + 13;
-    uint64_t* o_full = bars + 14;
-    uint64_t* o_empty = bars + 15;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint8_t* sK = sP + DA_P_BYTES;              // K ring
+    uint8_t* sV = sK + KS * DA_K_BYTES;         // V ring
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VS * DA_K_BYTES);
+    uint64_t* k_full = bars;                    // [KS] (<= 4)
+    uint64_t* v_full = bars + 4;                // [VS]
+    uint64_t* k_empty = bars + 8;               // [KS]
+    uint64_t* v_empty = bars + 12;              // [VS]
+    uint64_t* s_full = bars + 16;               // [2]
+    uint64_t* s_empty = bars + 18;              // [2]
+    uint64_t* p_full = bars + 20;
+    uint64_t* o_full = bars + 21;
+    uint64_t* o_empty = bars + 22;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
     volatile int* sh = reinterpret_cast<volatile int*>(tmem_slot + 1);   // [0] abort [1] last-split flag
     float* red = reinterpret_cast<float*>(const_cast<int*>(sh) + 4);     // [2][4 warps][16] max exchange, then sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();     // the plan arrays, q and the KV pages all come from earlier kernels of the step
     const int q_begin = p.q_indptr[req];
     const int q_len = p.q_indptr[req + 1] - q_begin;
     int ncols = q_len * p.G;
-    if (ncols > DA_COLS) ncols = DA_COLS;       // host guarantees q_len * G <= 16
+    if (ncols > NC) ncols = NC;                 // host picks NC >= q_len * G
     int kv_len = p.kv_lens[req];
     const int npages = p.page_indptr[req + 1] - p.page_indptr[req];
     if (kv_len > npages * p.page_size) kv_len = npages * p.page_size;
@@ -94,7 +102,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     const int ntiles = jt1 > jt0 ? jt1 - jt0 : 0;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 9; ++i) mbar_init(&bars[i], 1);
+        for (int i = 0; i < 16; ++i) mbar_init(&bars[i], 1);
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
         mbar_init(&s_empty[0], 128); mbar_init(&s_empty[1], 128);
         mbar_init(p_full, 128);
@@ -132,44 +140,56 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
             tma_prefetch_desc(&tmV);
             const int ppt = DA_KEYS / p.page_size;
             const int* pages = p.page_indices + p.page_indptr[req];
-            int issued = 0;
+            int issued_k = 0, issued_v = 0;
             for (int i = 0; i < ntiles; ++i) {
-                const int s = i % DA_STAGES;
-                const uint32_t ph = (i / DA_STAGES) & 1;
-                if (!mbar_wait(&kv_empty[s], ph ^ 1, p.wait_limit_ns)) {
-                    report_status(p.status, KID_ATTN_DECODE, 1, i, s);
-                    sh[0] = 1;
-                    break;
-                }
-                if (sh[0]) break;
-                uint8_t* sK = sKV + s * DA_STAGE;
-                uint8_t* sV = sK + DA_K_BYTES;
                 const int jt = jt0 + i;
-                mbar_expect_tx(&k_full[s], DA_K_BYTES);
-                mbar_expect_tx(&v_full[s], DA_K_BYTES);
-                for (int pg = 0; pg < ppt; ++pg) {
-                    int pi = jt * ppt + pg;
-                    if (pi >= npages) pi = npages - 1;
-                    const int page = pages[pi];
-                    const int row_off = pg * p.page_size * 128;
-                    tma_load_4d(sK + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
-                    tma_load_4d(sK + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
+                {
+                    const int s = i % KS;
+                    if (!mbar_wait(&k_empty[s], ((i / KS) & 1) ^ 1, p.wait_limit_ns)) {
+                        report_status(p.status, KID_ATTN_DECODE, 1, i, s);
+                        sh[0] = 1;
+                        break;
+                    }
+                    if (sh[0]) break;
+                    uint8_t* dst = sK + s * DA_K_BYTES;
+                    mbar_expect_tx(&k_full[s], DA_K_BYTES);
+                    for (int pg = 0; pg < ppt; ++pg) {
+                        int pi = jt * ppt + pg;
+                        if (pi >= npages) pi = npages - 1;
+                        const int page = pages[pi];
+                        const int row_off = pg * p.page_size * 128;
+                        tma_load_4d(dst + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
+                        tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
+                    }
+                    issued_k = i + 1;
                 }
-                for (int pg = 0; pg < ppt; ++pg) {
-                    int pi = jt * ppt + pg;
-                    if (pi >= npages) pi = npages - 1;
-                    const int page = pages[pi];
-                    const int row_off = pg * p.page_size * 128;
-                    tma_load_4d(sV + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
-                    tma_load_4d(sV + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
+                {
+                    const int s = i % VS;
+                    if (!mbar_wait(&v_empty[s], ((i / VS) & 1) ^ 1, p.wait_limit_ns)) {
+                        report_status(p.status, KID_ATTN_DECODE, 9, i, s);
+                        sh[0] = 1;
+                        break;
+                    }
+                    if (sh[0]) break;
+                    uint8_t* dst = sV + s * DA_K_BYTES;
+                    mbar_expect_tx(&v_full[s], DA_K_BYTES);
+                    for (int pg = 0; pg < ppt; ++pg) {
+                        int pi = jt * ppt + pg;
+                        if (pi >= npages) pi = npages - 1;
+                        const int page = pages[pi];
+                        const int row_off = pg * p.page_size * 128;
+                        tma_load_4d(dst + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
+                        tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
+                    }
+                    issued_v = i + 1;
                 }
-                issued = i + 1;
             }
             if (sh[0]) {
-                for (int i = (issued > DA_STAGES ? issued - DA_STAGES : 0); i < issued; ++i) {
-                    mbar_wait(&k_full[i % DA_STAGES], (i / DA_STAGES) & 1, 1000000ull);
-                    mbar_wait(&v_full[i % DA_STAGES], (i / DA_STAGES) & 1, 1000000ull);
-                }
+                // error path: let copies already in flight land before the CTA leaves
+                for (int i = (issued_k > KS ? issued_k - KS : 0); i < issued_k; ++i)
+                    mbar_wait(&k_full[i % KS], (i / KS) & 1, 1000000ull);
+                for (int i = (issued_v > VS ? issued_v - VS : 0); i < issued_v; ++i)
+                    mbar_wait(&v_full[i % VS], (i / VS) & 1, 1000000ull);
             }
         }
     } else if (warp == 1) {
@@ -180,8 +200,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
             const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
             bool ok = true;
             auto issue_s = [&](int i) -> bool {
-                const int s = i % DA_STAGES;
-                if (!mbar_wait(&k_full[s], (i / DA_STAGES) & 1, p.wait_limit_ns)) {
+                const int s = i % KS;
+                if (!mbar_wait(&k_full[s], (i / KS) & 1, p.wait_limit_ns)) {
                     report_status(p.status, KID_ATTN_DECODE, 2, i, s);
                     return false;
                 }
@@ -190,7 +210,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
                     return false;
                 }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(sKV + s * DA_STAGE);
+                const uint32_t k_addr = smem_u32(sK + s * DA_K_BYTES);
                 const uint32_t d = tmem_base + ((i & 1) ? TMEM_S1 : TMEM_S0);
 #pragma unroll
                 for (int k = 0; k < DA_HD / 16; ++k) {
@@ -200,18 +220,19 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
                                 k != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[i & 1]);
+                umma_commit(&k_empty[s]);
                 return true;
             };
             ok = issue_s(0);
             for (int i = 0; ok && i < ntiles; ++i) {
-                const int s = i % DA_STAGES;
+                const int s = i % VS;
                 if (i + 1 < ntiles) ok = issue_s(i + 1);
                 if (!ok) break;
                 if (!mbar_wait(p_full, i & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 4, i, 0); ok = false; break; }
-                if (!mbar_wait(&v_full[s], (i / DA_STAGES) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 5, i, 0); ok = false; break; }
+                if (!mbar_wait(&v_full[s], (i / VS) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 5, i, 0); ok = false; break; }
                 if (i >= 1 && !mbar_wait(o_empty, (i - 1) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DECODE, 6, i, 0); ok = false; break; }
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(sKV + s * DA_STAGE + DA_K_BYTES);
+                const uint32_t v_addr = smem_u32(sV + s * DA_K_BYTES);
 #pragma unroll
                 for (int k = 0; k < DA_KEYS / 16; ++k) {
                     // A = V^T: M (= d) is the contiguous dimension. LBO = distance of the two 64-wide d atoms,
@@ -222,7 +243,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
                     umma_f16_ss(tmem_base + TMEM_O, da, umma_smem_desc_sw128(p_addr + boff), idesc_o, k != 0 ? 1u : 0u);
                 }
                 umma_commit(o_full);
-                umma_commit(&kv_empty[s]);
+                umma_commit(&v_empty[s]);
             }
             if (!ok) sh[0] = 1;
         }
@@ -245,10 +266,11 @@ MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_s
                                      const int* q_indptr, const int* kv_lens, int B, int T_q, int Hq, int Hkv, int D,
                                      const void* kcache, int num_pages, int page_size, const int* page_indptr,
                                      const int* page_indices, int causal, int window, float scale, int splits,
-                                     float* ws_o, float* ws_ml, void* counters, void* stream_) {
+                                     int max_q_len, float* ws_o, float* ws_ml, void* counters, void* stream_) {
     if (B <= 0) return 0;
     if (D != DA_HD) return set_error("attention_decode: head_dim must be 128", cudaSuccess);
-    if (Hq % Hkv || Hq / Hkv > DA_COLS) return set_error("attention_decode: GQA group must divide and be <= 16", cudaSuccess);
+    if (Hq % Hkv || max_q_len < 1 || max_q_len * (Hq / Hkv) > DA_COLS)
+        return set_error("attention_decode: q_len * (Hq / Hkv) must be in [1, 16]", cudaSuccess);
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)))
         return set_error("attention_decode: page_size must be a power of two in [8, 128]", cudaSuccess);
     DecAttnParams p;
@@ -272,14 +294,35 @@ MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_s
     const __nv_bfloat16* kc = (const __nv_bfloat16*)kcache;
     if (make_tmap(&tmK, kc, 2, 4, dims, strides, box, 1)) return -1;
     if (make_tmap(&tmV, kc + (size_t)Hkv * page_size * D, 2, 4, dims, strides, box, 1)) return -1;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DA_SMEM);
-        if (e != cudaSuccess) return set_error("attention_decode: cudaFuncSetAttribute failed", e);
-        configured = true;
-    }
     dim3 grid(B, Hkv, p.splits);
-    attn_decode_tcgen05_kernel<<<grid, 192, DA_SMEM, (cudaStream_t)stream_>>>(tmK, tmV, p);
+    const long long ctas = (long long)B * Hkv * p.splits;
+    const int ncols_max = max_q_len * p.G;
+    const bool many = ctas > 2LL * device_sm_count();
+    cudaStream_t stream = (cudaStream_t)stream_;
+#define MSTAR_DA_LAUNCH(KS, VS, NC, MINB)                                                                        \
+    do {                                                                                                          \
+        static bool configured = false;                                                                           \
+        constexpr int smem = da_smem_bytes(KS, VS);                                                               \
+        if (!configured) {                                                                                        \
+            cudaError_t e_ = cudaFuncSetAttribute(attn_decode_tcgen05_kernel<KS, VS, NC, MINB>,                   \
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem);             \
+            if (e_ != cudaSuccess) return set_error("attention_decode: cudaFuncSetAttribute failed", e_);         \
+            configured = true;                                                                                    \
+        }                                                                                                         \
+        cudaError_t le_ = launch_pdl(attn_decode_tcgen05_kernel<KS, VS, NC, MINB>, grid, dim3(192), smem, stream,  \
+                                     tmK, tmV, p);                                                                \
+        if (le_ != cudaSuccess) return set_error("attention_decode: launch failed", le_);                         \
+    } while (0)
+    if (many) {
+        if (ncols_max <= 4) MSTAR_DA_LAUNCH(1, 1, 4, 3);
+        else if (ncols_max <= 8) MSTAR_DA_LAUNCH(1, 1, 8, 3);
+        else MSTAR_DA_LAUNCH(1, 1, 16, 2);
+    } else {
+        if (ncols_max <= 4) MSTAR_DA_LAUNCH(3, 3, 4, 1);
+        else if (ncols_max <= 8) MSTAR_DA_LAUNCH(3, 3, 8, 1);
+        else MSTAR_DA_LAUNCH(3, 3, 16, 1);
+    }
+#undef MSTAR_DA_LAUNCH
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : set_error("attention_decode: launch failed", e);
 }

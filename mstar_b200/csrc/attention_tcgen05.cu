@@ -99,6 +99,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = blockIdx.y;
     const int split = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();     // plan arrays, q and K/V all come from earlier kernels
 
     // ---- locate this CTA's (request, q tile): tiles are numbered request by request ----
     if (threadIdx.x == 0) {
@@ -471,8 +473,7 @@ static int launch_attn(const CUtensorMap& tmK, const CUtensorMap& tmV, const Att
         if (e != cudaSuccess) return set_error("attention: cudaFuncSetAttribute failed", e);
         configured = true;
     }
-    attn_tcgen05_kernel<HD><<<grid, 192, smem, stream>>>(tmK, tmV, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(attn_tcgen05_kernel<HD>, grid, dim3(192), smem, stream, tmK, tmV, p);
     return e == cudaSuccess ? 0 : set_error("attention: launch failed", e);
 }
 

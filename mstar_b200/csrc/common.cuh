@@ -50,6 +50,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 #define MSTAR_WAIT_LIMIT_NS_DEFAULT 2000000000ull
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream still runs; it must call pdl_wait() before it reads anything the
+// predecessor wrote and before its own first global write. Without the attribute both calls are no-ops.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // shared-memory helpers
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

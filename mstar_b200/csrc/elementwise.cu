@@ -51,6 +51,8 @@ struct NormParams {
 
 template <int NT, int MAXV>
 __global__ void __launch_bounds__(NT) norm_kernel(const NormParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
     const int row = blockIdx.x;
     if (row >= p.rows) return;
@@ -202,6 +204,8 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     if (t >= p.T) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -293,6 +297,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
 // ------------------------------------------------------------------------------------------------------------
 // out[r, i] = act(x[r, i]) * x[r, I + i]   (x: [rows, 2I] halves layout)  act: 0 silu, 1 gelu-tanh
 __global__ void act_mul_kernel(const __nv_bfloat16* x, __nv_bfloat16* out, long long rows, int I, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long n = rows * (long long)I;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < n;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -306,6 +312,8 @@ __global__ void act_mul_kernel(const __nv_bfloat16* x, __nv_bfloat16* out, long 
 // out[t, :] = table[ids[t] - vocab_start, :] if the id falls in [vocab_start, vocab_end), else 0
 __global__ void embed_gather_kernel(const long long* ids, const __nv_bfloat16* table, __nv_bfloat16* out, int T,
                                     int hidden, long long vocab_start, long long vocab_end, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     if (t >= T) return;
     const long long id = ids[t];
@@ -331,6 +339,8 @@ __global__ void embed_gather_kernel(const long long* ids, const __nv_bfloat16* t
 __global__ void gated_residual_kernel(const __nv_bfloat16* x, const __nv_bfloat16* y, const __nv_bfloat16* gate,
                                       __nv_bfloat16* out, long long rows, int hidden, int rows_per_mod,
                                       long long gate_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long n = rows * (long long)hidden;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < n;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -353,6 +363,8 @@ struct CfgParams {
     int renorm;
 };
 __global__ void __launch_bounds__(128) cfg_combine_kernel(const CfgParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
     const int r = blockIdx.x;
     if (r >= p.rows) return;
@@ -398,6 +410,8 @@ __global__ void __launch_bounds__(128) cfg_combine_kernel(const CfgParams p) {
 // uint8 / float image -> [-1, 1] (or any affine): out = x * a + b
 __global__ void affine_kernel(const float* x, __nv_bfloat16* out_bf16, float* out_f32, long long n, float a,
                               float b) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const float y = x[i] * a + b;
         if (out_bf16) out_bf16[i] = __float2bfloat16(y);
@@ -411,6 +425,8 @@ __global__ void affine_kernel(const float* x, __nv_bfloat16* out_bf16, float* ou
 __global__ void advance_decode_kernel(int* kv_lens, int* positions, int* cache_pos, long long* input_ids,
                                       const long long* sampled, const int* active, int B, int n_axes,
                                       int pos_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     if (input_ids && sampled) input_ids[b] = sampled[b];
@@ -438,12 +454,12 @@ MSTAR_API int mstar_norm(const void* x, const void* residual, void* residual_out
                  rows_per_mod > 0 ? rows_per_mod : 1, mod_stride, eps, layernorm, gemma};
     cudaStream_t s = (cudaStream_t)stream_;
     const int nvec = hidden / 8;
-    if (nvec <= 128) norm_kernel<128, 1><<<rows, 128, 0, s>>>(p);
-    else if (nvec <= 256) norm_kernel<128, 2><<<rows, 128, 0, s>>>(p);
-    else if (nvec <= 512) norm_kernel<256, 2><<<rows, 256, 0, s>>>(p);
-    else if (nvec <= 1024) norm_kernel<256, 4><<<rows, 256, 0, s>>>(p);
-    else norm_kernel<256, 8><<<rows, 256, 0, s>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e;
+    if (nvec <= 128) e = launch_pdl(norm_kernel<128, 1>, dim3(rows), dim3(128), 0, s, p);
+    else if (nvec <= 256) e = launch_pdl(norm_kernel<128, 2>, dim3(rows), dim3(128), 0, s, p);
+    else if (nvec <= 512) e = launch_pdl(norm_kernel<256, 2>, dim3(rows), dim3(256), 0, s, p);
+    else if (nvec <= 1024) e = launch_pdl(norm_kernel<256, 4>, dim3(rows), dim3(256), 0, s, p);
+    else e = launch_pdl(norm_kernel<256, 8>, dim3(rows), dim3(256), 0, s, p);
     return e == cudaSuccess ? 0 : set_error("norm launch", e);
 }
 
@@ -458,8 +474,7 @@ MSTAR_API int mstar_rope_kv(const void* qkv, long long ld_qkv, void* q_out, void
                  (__nv_bfloat16*)v_out, (__nv_bfloat16*)cache, positions, pos_stride, inv_freq, axis_of_freq,
                  (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, token_req, cache_pos, page_indptr,
                  page_indices, T, Hq, Hkv, D, rot_dim, page_size, interleaved, gemma_norm, norm_eps, q_scale};
-    rope_kv_kernel<<<T, 256, 0, (cudaStream_t)stream_>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(rope_kv_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream_, p);
     return e == cudaSuccess ? 0 : set_error("rope_kv launch", e);
 }
 
@@ -481,9 +496,8 @@ MSTAR_API int mstar_embed_gather(const long long* ids, const void* table, void* 
                                  long long vocab_start, long long vocab_end, float scale, void* stream_) {
     if (T <= 0) return 0;
     if (hidden % 8) return set_error("embed: hidden must be a multiple of 8", cudaSuccess);
-    embed_gather_kernel<<<T, 128, 0, (cudaStream_t)stream_>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out,
-                                                              T, hidden, vocab_start, vocab_end, scale);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(embed_gather_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream_, ids,
+                               (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, hidden, vocab_start, vocab_end, scale);
     return e == cudaSuccess ? 0 : set_error("embed launch", e);
 }
 

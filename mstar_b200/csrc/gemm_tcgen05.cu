@@ -121,67 +121,89 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int m, int 
     }
 }
 
-// swapped: the thread owns output column n (a weight row) and `ncols` consecutive token rows from m0.
-// Values go through a shared-memory staging tile [token][n] in fp32 so that the global stores are 16 bytes per
-// lane and contiguous along n (2-byte-per-lane stores straight from the accumulator layout cost ~0.2 us per
-// token row on B200).
-__device__ __forceinline__ void stage_col_chunk(const GemmParams& p, float* stage, int row_elems, int nl, int n,
-                                                int ml0, float* v, int ncols) {
-    const bool n_ok = n < p.N;
-    const float b = (p.bias != nullptr && n_ok) ? __bfloat162float(p.bias[n]) : 0.0f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if (i < ncols) {
-            float x = v[i] * p.out_scale + b;
-            if (p.epilogue == 1) {
-                // rows 2j (gate) / 2j+1 (up) of the weight sit in neighbouring lanes
-                const float other = __shfl_xor_sync(0xffffffffu, x, 1);
-                if ((nl & 1) == 0) stage[(ml0 + i) * row_elems + (nl >> 1)] = silu_f(x) * other;
-            } else {
-                if (p.epilogue == 2) x = gelu_tanh_f(x);
-                stage[(ml0 + i) * row_elems + nl] = x;
-            }
-        }
-    }
-}
-
-// Copy the staged tile out: rows = tokens, row_elems outputs per row starting at output column n_base.
+// Swapped layout epilogue. Accumulators are first dumped raw into a shared-memory tile [token][weight row] (fp32;
+// a few dozen instructions, so that the once-per-CTA epilogue does not pay instruction-cache misses for 32
+// unrolled copies of the activation code), then one compact loop applies scale / bias / activation / residual
+// and writes 16 bytes per lane, contiguous along the output columns.
 template <bool OUT_F32>
-__device__ __forceinline__ void copy_out_staged(const GemmParams& p, const float* stage, int row_elems, int rows,
-                                                int m_base, int n_base, int n_limit, int tid) {
-    constexpr int EPV = OUT_F32 ? 4 : 8;                 // elements per 16-byte store
-    const int units_per_row = row_elems / EPV;
+__device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* stage, int rows, int m_base,
+                                             int n_in_base, int tid) {
+    constexpr int EPV = OUT_F32 ? 4 : 8;                 // outputs per 16-byte store
+    const int ipo = p.epilogue == 1 ? 2 : 1;             // accumulator columns per output (SwiGLU pairs)
+    const int row_out = BM / ipo;
+    const int units_per_row = row_out / EPV;
     const int total = rows * units_per_row;
-    const bool vec_ok = (p.ldc % EPV == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (n_base % EPV == 0) &&
+    const int n_out_base = n_in_base / ipo;
+    const int n_limit = p.N / ipo;
+    const bool vec_ok = (p.ldc % EPV == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
                         (p.residual == nullptr || (p.ld_res % 8 == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
     for (int u = tid; u < total; u += 128) {
         const int r = u / units_per_row, c = (u - r * units_per_row) * EPV;
-        const int m = m_base + r, n = n_base + c;
+        const int m = m_base + r, n = n_out_base + c;
         if (m >= p.M || n >= n_limit) continue;
+        const float* sp = stage + r * BM + c * ipo;
         float x[EPV];
-        const float4* sp = reinterpret_cast<const float4*>(stage + r * row_elems + c);
-        float4 t0 = sp[0];
-        x[0] = t0.x; x[1] = t0.y; x[2] = t0.z; x[3] = t0.w;
-        if constexpr (!OUT_F32) {
-            float4 t1 = sp[1];
-            x[4] = t1.x; x[5] = t1.y; x[6] = t1.z; x[7] = t1.w;
-        }
-        if (vec_ok && n + EPV <= n_limit) {
-            if (p.residual != nullptr) {
-                if constexpr (OUT_F32) {
-                    const __nv_bfloat16* rr = p.residual + (size_t)m * p.ld_res + n;
+        const bool full = n + EPV <= n_limit;
+        if (ipo == 2) {
+            float in[2 * EPV];
 #pragma unroll
-                    for (int j = 0; j < EPV; ++j) x[j] += __bfloat162float(rr[j]);
+            for (int j = 0; j < 2 * EPV; j += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(sp + j);
+                in[j] = t.x; in[j + 1] = t.y; in[j + 2] = t.z; in[j + 3] = t.w;
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 2 * EPV; ++j) {
+                    const int nb = n_in_base + c * 2 + j;
+                    in[j] = in[j] * p.out_scale + (nb < p.N ? __bfloat162float(p.bias[nb]) : 0.f);
+                }
+            } else if (p.out_scale != 1.0f) {
+#pragma unroll
+                for (int j = 0; j < 2 * EPV; ++j) in[j] *= p.out_scale;
+            }
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) x[j] = silu_f(in[2 * j]) * in[2 * j + 1];
+        } else {
+#pragma unroll
+            for (int j = 0; j < EPV; j += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(sp + j);
+                x[j] = t.x; x[j + 1] = t.y; x[j + 2] = t.z; x[j + 3] = t.w;
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < EPV; ++j)
+                    x[j] = x[j] * p.out_scale + (n + j < n_limit ? __bfloat162float(p.bias[n + j]) : 0.f);
+            } else if (p.out_scale != 1.0f) {
+#pragma unroll
+                for (int j = 0; j < EPV; ++j) x[j] *= p.out_scale;
+            }
+            if (p.epilogue == 2) {
+#pragma unroll
+                for (int j = 0; j < EPV; ++j) x[j] = gelu_tanh_f(x[j]);
+            }
+        }
+        if (p.residual != nullptr) {
+            if (vec_ok && full) {
+                const __nv_bfloat16* rp = p.residual + (size_t)m * p.ld_res + n;
+                if constexpr (OUT_F32) {
+                    const uint2 rv = *reinterpret_cast<const uint2*>(rp);
+                    const float2 f0 = unpack_bf16x2(rv.x), f1 = unpack_bf16x2(rv.y);
+                    x[0] += f0.x; x[1] += f0.y; x[2] += f1.x; x[3] += f1.y;
                 } else {
-                    uint4 rv = *reinterpret_cast<const uint4*>(p.residual + (size_t)m * p.ld_res + n);
-                    uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                    const uint4 rv = *reinterpret_cast<const uint4*>(rp);
+                    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        float2 f = unpack_bf16x2(rw[j]);
+                        const float2 f = unpack_bf16x2(rw[j]);
                         x[2 * j] += f.x; x[2 * j + 1] += f.y;
                     }
                 }
+            } else {
+                for (int j = 0; j < EPV; ++j)
+                    if (n + j < n_limit) x[j] += __bfloat162float(p.residual[(size_t)m * p.ld_res + n + j]);
             }
+        }
+        if (vec_ok && full) {
             if constexpr (OUT_F32) {
                 *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n) =
                     make_float4(x[0], x[1], x[2], x[3]);
@@ -193,17 +215,15 @@ __device__ __forceinline__ void copy_out_staged(const GemmParams& p, const float
         } else {
             for (int j = 0; j < EPV; ++j) {
                 if (n + j >= n_limit) break;
-                float y = x[j];
-                if (p.residual != nullptr) y += __bfloat162float(p.residual[(size_t)m * p.ld_res + n + j]);
-                if constexpr (OUT_F32) reinterpret_cast<float*>(p.C)[(size_t)m * p.ldc + n + j] = y;
-                else reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + n + j] = __float2bfloat16(y);
+                if constexpr (OUT_F32) reinterpret_cast<float*>(p.C)[(size_t)m * p.ldc + n + j] = x[j];
+                else reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)m * p.ldc + n + j] = __float2bfloat16(x[j]);
             }
         }
     }
 }
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, int STAGES, int MINB>
+__global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                          const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -226,6 +246,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     int kb_end = kb_begin + p.kblocks_per_split;
     if (kb_end > p.kblocks_total) kb_end = p.kblocks_total;
     const int nkb = kb_end - kb_begin;  // host guarantees >= 1
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -254,7 +275,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
+            // The weight operand does not depend on the previous kernel: when it is the P operand (decode), fill
+            // the ring with weight tiles first, and only then wait for the predecessor before touching activations.
+            const int npre = p.swap ? (nkb < STAGES ? nkb : STAGES) : 0;
+            for (int i = 0; i < npre; ++i) {
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                tma_load_2d(smem + i * STAGE_BYTES, &tmP, &full_bar[i], (kb_begin + i) * BK, tile_p * BM);
+            }
+            pdl_wait();
+            for (int i = 0; i < npre; ++i)
+                tma_load_2d(smem + i * STAGE_BYTES + P_BYTES, &tmQ, &full_bar[i], (kb_begin + i) * BK, tile_q * BN);
+            issued = npre;
+            for (int i = npre; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1, p.wait_limit_ns)) {
@@ -307,6 +339,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;  // accumulator row (TMEM lane) owned by this thread
+        pdl_wait();
         bool ok = mbar_wait(acc_bar, 0, p.wait_limit_ns + 500000000ull);
         if (!ok) {
             report_status(p.status, KID_GEMM, 3, 0, 0);
@@ -365,7 +398,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                 const int qidx = tile_q * BN + c0;
                 if (p.swap) {
                     // the pipeline stages are idle by now (all TMA loads consumed): reuse them as staging tile
-                    stage_col_chunk(p, reinterpret_cast<float*>(smem), p.epilogue == 1 ? BM / 2 : BM, row, pidx, c0, v, CH);
+                    float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) stage[(c0 + i) * BM + row] = v[i];
                 } else {
                     if (p.out_f32) store_row_chunk<true>(p, pidx, qidx, v, CH);
                     else store_row_chunk<false>(p, pidx, qidx, v, CH);
@@ -373,11 +408,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             }
             if (p.swap) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int row_elems = p.epilogue == 1 ? BM / 2 : BM;
-                const int n_base = p.epilogue == 1 ? (tile_p * BM) / 2 : tile_p * BM;
-                const int n_limit = p.epilogue == 1 ? p.N / 2 : p.N;
-                if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), row_elems, BN, tile_q * BN, n_base, n_limit, threadIdx.x - 64);
-                else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), row_elems, BN, tile_q * BN, n_base, n_limit, threadIdx.x - 64);
+                if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
+                else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
             }
             if (p.splits > 1 && threadIdx.x == 64) p.counters[tile_lin] = 0u;  // ready for the next launch
         }
@@ -393,19 +425,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MINB>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
     constexpr int smem = gemm_smem_bytes(BN, STAGES);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
         configured = true;
     }
-    gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, 192, smem, stream>>>(tmP, tmQ, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
     return 0;
 }
@@ -435,8 +466,9 @@ MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, i
     const int tiles = tiles_p * tiles_q;
     int splits = 1;
     const int sms = device_sm_count();
-    if (tiles < sms) {
-        splits = sms / tiles;
+    const int target = swap ? 2 * sms : sms;   // decode kernels run two CTAs per SM
+    if (tiles < target) {
+        splits = target / tiles;
         // keep at least 4 K blocks per split so the pipeline has something to stream
         int max_splits = kblocks / 4;
         if (max_splits < 1) max_splits = 1;
@@ -506,11 +538,15 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
     dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
     switch (bn) {
-        case 16: return launch_gemm<16, 10>(tmP, tmQ, p, grid, stream);
-        case 32: return launch_gemm<32, 10>(tmP, tmQ, p, grid, stream);
-        case 64: return launch_gemm<64, 8>(tmP, tmQ, p, grid, stream);
-        case 128: return launch_gemm<128, 6>(tmP, tmQ, p, grid, stream);
-        case 256: return launch_gemm<256, 4>(tmP, tmQ, p, grid, stream);
+        // decode tiles: 4 stages keep a CTA under 100 KB so that two CTAs share an SM and one CTA's prologue /
+        // epilogue overlaps the other's weight stream
+        case 16: return launch_gemm<16, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 32: return launch_gemm<32, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
+        case 128:
+            if (swap) return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
+            return launch_gemm<128, 6, 1>(tmP, tmQ, p, grid, stream);
+        case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
     }
     return set_error("gemm: unsupported tile", cudaSuccess);
 }

@@ -1,5 +1,6 @@
 // Library-wide host state: error text, status word, wait limit, TMA descriptor encoding.
 #include <string.h>
+#include <stdlib.h>
 #include <stdio.h>
 #include <mutex>
 #include "host_common.h"
@@ -36,6 +37,15 @@ KernelStatus* status_ptr() {
 }
 
 unsigned long long wait_limit_ns() { return g_wait_limit; }
+
+static int g_pdl = -1;
+bool pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("MSTAR_PDL");
+        g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl == 1;
+}
 
 int device_sm_count() {
     if (g_sms == 0) {
@@ -127,3 +137,4 @@ MSTAR_API unsigned int mstar_read_status(unsigned int* out4, int clear) {
 MSTAR_API void mstar_set_wait_limit_ns(unsigned long long ns) { g_wait_limit = ns; }
 MSTAR_API unsigned long long mstar_get_wait_limit_ns() { return g_wait_limit; }
 MSTAR_API int mstar_sm_count() { return device_sm_count(); }
+MSTAR_API void mstar_set_pdl(int on) { g_pdl = on ? 1 : 0; }

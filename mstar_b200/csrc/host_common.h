@@ -20,4 +20,24 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, int rows, int cols, in
 int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const unsigned long long* dims,
               const unsigned long long* strides_bytes, const unsigned int* box, int swizzle_128b);
 
+bool pdl_enabled();
+
+// Launch with the programmatic-stream-serialization attribute (when enabled), so that the kernel's prologue and
+// its independent prefetches overlap the tail of the previous kernel in the stream.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace mstar

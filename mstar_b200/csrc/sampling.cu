@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
     __shared__ float sh_f[4];
     __shared__ int sh_i[4];
     const int row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int slot = p.row_slot ? p.row_slot[row] : row;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const void* lg = reinterpret_cast<const char*>(p.logits) + (size_t)row * p.ld * (F32 ? 4 : 2);
@@ -307,8 +309,7 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
     SampleParams p{logits, ld, is_f32, B, V, temperature, top_k, top_p, rep_penalty, seed, offset, seen, row_slot,
                    out, out_prob, u_override};
     cudaStream_t s = (cudaStream_t)stream_;
-    if (is_f32) sample_kernel<true><<<B, SP_NT, 0, s>>>(p);
-    else sample_kernel<false><<<B, SP_NT, 0, s>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = is_f32 ? launch_pdl(sample_kernel<true>, dim3(B), dim3(SP_NT), 0, s, p)
+                           : launch_pdl(sample_kernel<false>, dim3(B), dim3(SP_NT), 0, s, p);
     return e == cudaSuccess ? 0 : set_error("sample launch", e);
 }

@@ -278,7 +278,7 @@ class LLMEngine:
         ntiles = B
         splits = self._graph_splits.get(B) if self.use_graphs and hasattr(self, "_graph_splits") else None
         if splits is None:
-            splits = attn_ops.choose_splits(B, cm.config.num_kv_heads, ntiles, max_kv)
+            splits = attn_ops.choose_splits(B, cm.config.num_kv_heads, ntiles, max_kv, sm_count=3 * 148)
         plan = attn_ops.AttnPlan(q_indptr=buf.d("q_indptr"), kv_lens=buf.d("kv_lens"), batch=B, num_q_tokens=B,
                                  num_q_tiles=ntiles, page_indptr=buf.d("page_indptr"),
                                  page_indices=buf.d("page_indices"), splits=splits, causal=True,
@@ -295,7 +295,8 @@ class LLMEngine:
         from ..ops import attention as attn_ops
         if not hasattr(self, "_graph_splits"):
             self._graph_splits = {}
-        splits = attn_ops.choose_splits(B, self.cache.config.num_kv_heads, B, self.cache.config.max_seq_len)
+        splits = attn_ops.choose_splits(B, self.cache.config.num_kv_heads, B, self.cache.config.max_seq_len,
+                                        sm_count=3 * 148)
         self._graph_splits[B] = splits
         ctx.plan.splits = splits
         attn_ops.reserve_scratch(self.device, B * self.model.layers[0].self_attn.Hq, self.cfg.head_dim, splits,

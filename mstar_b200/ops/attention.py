@@ -159,8 +159,8 @@ def attention(q: torch.Tensor, plan: AttnPlan, *, kv_cache: torch.Tensor | None 
                 int(plan.batch), int(T), int(Hq), int(Hkv), int(D), ctypes.c_void_p(kp), int(num_pages),
                 int(page_size), ctypes.c_void_p(plan.page_indptr.data_ptr()),
                 ctypes.c_void_p(plan.page_indices.data_ptr()), 1 if plan.causal else 0, int(plan.window),
-                ctypes.c_float(scale), splits, ctypes.c_void_p(ws_o), ctypes.c_void_p(ws_ml), ctypes.c_void_p(cnt),
-                ctypes.c_void_p(_lib.stream_ptr()))
+                ctypes.c_float(scale), splits, int(plan.max_q_len), ctypes.c_void_p(ws_o), ctypes.c_void_p(ws_ml),
+                ctypes.c_void_p(cnt), ctypes.c_void_p(_lib.stream_ptr()))
             _lib.check(rc, "mstar_attention_decode")
             return out
     rc = _lib.kernels().mstar_attention(
