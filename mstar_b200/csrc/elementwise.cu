@@ -226,6 +226,17 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
         }
     }
     (void)cache_tok;
+    // the rotation angles depend on the token only: compute cos/sin once, every head reuses them
+    __shared__ float s_cos[256], s_sin[256];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int axis = p.axis_of_freq ? p.axis_of_freq[i] : 0;
+        const float ang = (float)p.positions[(size_t)axis * p.pos_stride + t] * p.inv_freq[i];
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        s_cos[i] = cs;
+        s_sin[i] = sn;
+    }
+    __syncthreads();
     for (int hidx = warp; hidx < nheads; hidx += nwarps) {
         const bool is_q = hidx < p.Hq;
         const bool is_k = !is_q && hidx < p.Hq + p.Hkv;
@@ -272,10 +283,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
                 x0 = __bfloat162float(__float2bfloat16(x0 * inv * w0));
                 x1 = __bfloat162float(__float2bfloat16(x1 * inv * w1));
             }
-            const int axis = p.axis_of_freq ? p.axis_of_freq[i] : 0;
-            const float ang = (float)p.positions[(size_t)axis * p.pos_stride + t] * p.inv_freq[i];
-            float sn, cs;
-            sincosf(ang, &sn, &cs);
+            const float sn = s_sin[i], cs = s_cos[i];
             const float y0 = (x0 * cs - x1 * sn) * qs, y1 = (x1 * cs + x0 * sn) * qs;
             const __nv_bfloat16 b0 = __float2bfloat16(y0), b1 = __float2bfloat16(y1);
             if (dst) { dst[i0] = b0; dst[i1] = b1; }

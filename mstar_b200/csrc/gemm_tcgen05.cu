@@ -466,7 +466,7 @@ MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, i
     const int tiles = tiles_p * tiles_q;
     int splits = 1;
     const int sms = device_sm_count();
-    const int target = swap ? 2 * sms : sms;   // decode kernels run two CTAs per SM
+    const int target = sms;
     if (tiles < target) {
         splits = target / tiles;
         // keep at least 4 K blocks per split so the pipeline has something to stream

@@ -42,7 +42,7 @@ static int g_pdl = -1;
 bool pdl_enabled() {
     if (g_pdl < 0) {
         const char* e = getenv("MSTAR_PDL");
-        g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+        g_pdl = (e != nullptr && e[0] == '1') ? 1 : 0;   // opt-in: MSTAR_PDL=1
     }
     return g_pdl == 1;
 }

@@ -1,7 +1,7 @@
 // Token sampling in one kernel per step: repetition penalty over the seen-token mask, temperature, top-k,
 // top-p, one Philox draw per row, and the seen-mask update. One CTA per row, vocabulary up to a few 100k.
 //
-// Selection of the nucleus without a sort: two 4096-bin histograms over the float bit pattern of the
+// Selection of the nucleus without a sort: three 8-bit radix passes over the float bit pattern of the
 // probabilities (monotone for positive floats) give a 24-bit threshold key; the kept set is
 // {p : key(p) >= threshold}, the smallest such set whose mass reaches top_p and whose size respects top_k
 // (ties at the threshold are kept). The draw walks the kept probabilities in vocabulary order.
@@ -47,7 +47,6 @@ struct SampleParams {
 };
 
 constexpr int SP_NT = 1024;
-constexpr int SP_BINS = 4096;
 
 template <bool F32>
 __device__ __forceinline__ float load_logit(const void* base, long long i) {
@@ -57,8 +56,11 @@ __device__ __forceinline__ float load_logit(const void* base, long long i) {
 
 template <bool F32>
 __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
-    __shared__ float hist_mass[SP_BINS];
-    __shared__ int hist_cnt[SP_BINS];
+    extern __shared__ unsigned long long sp_dyn[];                 // per-warp radix histograms (fixed-point mass)
+    unsigned long long* hist_mass = sp_dyn;                                        // [32 warps][256]
+    unsigned int* hist_cnt = reinterpret_cast<unsigned int*>(sp_dyn + (SP_NT / 32) * 256);   // [32 warps][256]
+    __shared__ float merged_mass[256];
+    __shared__ int merged_cnt[256];
     __shared__ float red_f[32];
     __shared__ int red_i[32];
     __shared__ float sh_f[4];
@@ -118,27 +120,9 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         return;
     }
 
-    // ---- pass 2: partition function + first-level histogram of e = exp(x - max) in (0, 1] ----
-    for (int i = tid; i < SP_BINS; i += SP_NT) { hist_mass[i] = 0.f; hist_cnt[i] = 0; }
-    __syncthreads();
+    // ---- pass 2: partition function ----
     float z = 0.f;
-    {
-        // run-length aggregation: neighbouring elements often fall into the same bin (flat distributions put most
-        // of the vocabulary into a handful of bins), so a thread flushes to shared memory only when the bin changes
-        int cur = -1, ccnt = 0;
-        float cmass = 0.f;
-        for (int i = tid; i < p.V; i += SP_NT) {
-            const float e = __expf(logit_at(i) - mx);
-            z += e;
-            const int bin = (int)((__float_as_uint(e) >> 8) >> 12);     // top 12 of a 24-bit monotone key
-            if (bin != cur) {
-                if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
-                cur = bin; cmass = 0.f; ccnt = 0;
-            }
-            cmass += e; ++ccnt;
-        }
-        if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
-    }
+    for (int i = tid; i < p.V; i += SP_NT) z += __expf(logit_at(i) - mx);
     z = warp_sum(z);
     if (lane == 0) red_f[warp] = z;
     __syncthreads();
@@ -154,61 +138,68 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
     if (top_k <= 0 || top_k > p.V) top_k = p.V;
     const bool filter = (top_p < 1.0f) || (top_k < p.V);
     uint32_t thr_key = 0;          // keep keys >= thr_key
-    float kept_mass = z;
     if (filter) {
+        // Three radix levels of 8 bits over the 24-bit key. Every warp owns a private 256-bin histogram
+        // (fixed-point mass, 2^-24 units, and count); lanes that hit the same bin are merged with
+        // match_any + reduce_add before ONE lane updates the bin, so no atomics and no contention, whatever
+        // the shape of the distribution.
         const float need = top_p * z;
-        // walk the bins from the top: thread 0 only (4096 steps at most, usually a few hundred)
-        if (tid == 0) {
-            float acc = 0.f; int cnt = 0; int b = SP_BINS - 1;
-            for (; b >= 0; --b) {
-                const float mb = hist_mass[b]; const int cb = hist_cnt[b];
-                if (cb == 0) continue;
-                if (acc + mb >= need || cnt + cb >= top_k) break;
-                acc += mb; cnt += cb;
-            }
-            if (b < 0) b = 0;
-            sh_i[1] = b; sh_f[2] = acc; sh_i[2] = cnt;
-        }
-        __syncthreads();
-        const int b1 = sh_i[1];
-        const float acc1 = sh_f[2];
-        const int cnt1 = sh_i[2];
-        __syncthreads();
-        // second level inside bin b1
-        for (int i = tid; i < SP_BINS; i += SP_NT) { hist_mass[i] = 0.f; hist_cnt[i] = 0; }
-        __syncthreads();
-        {
-            int cur = -1, ccnt = 0;
-            float cmass = 0.f;
-            for (int i = tid; i < p.V; i += SP_NT) {
-                const float e = __expf(logit_at(i) - mx);
-                const uint32_t key = __float_as_uint(e) >> 8;
-                if ((int)(key >> 12) == b1) {
-                    const int bin = (int)(key & 0xfff);
-                    if (bin != cur) {
-                        if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
-                        cur = bin; cmass = 0.f; ccnt = 0;
-                    }
-                    cmass += e; ++ccnt;
+        unsigned long long* wmass = hist_mass + warp * 256;
+        unsigned int* wcnt = hist_cnt + warp * 256;
+        uint32_t prefix = 0;            // key bits decided so far (aligned to the top)
+        float acc_mass = 0.f;           // mass / count of keys strictly above the undecided range
+        int acc_cnt = 0;
+        const int iters = (p.V + SP_NT - 1) / SP_NT;
+#pragma unroll 1
+        for (int level = 0; level < 3; ++level) {
+            const int shift = 16 - 8 * level;
+            for (int i = lane; i < 256; i += 32) { wmass[i] = 0ull; wcnt[i] = 0u; }
+            __syncwarp();
+            for (int it = 0; it < iters; ++it) {
+                const int i = tid + it * SP_NT;
+                uint32_t bin = 0xffffffffu;
+                unsigned int fx = 0;
+                if (i < p.V) {
+                    const float e = __expf(logit_at(i) - mx);
+                    const uint32_t key = __float_as_uint(e) >> 8;
+                    const bool in_range = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
+                    if (in_range) { bin = (key >> shift) & 0xffu; fx = (unsigned int)(e * 16777216.0f); }
                 }
+                const unsigned int peers = __match_any_sync(0xffffffffu, bin);
+                const unsigned int sum = __reduce_add_sync(peers, fx);
+                if (bin != 0xffffffffu && lane == __ffs(peers) - 1) {
+                    wmass[bin] += sum;
+                    wcnt[bin] += __popc(peers);
+                }
+                __syncwarp();
             }
-            if (ccnt) { atomicAdd(&hist_mass[cur], cmass); atomicAdd(&hist_cnt[cur], ccnt); }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            float acc = acc1; int cnt = cnt1; int b = SP_BINS - 1;
-            for (; b >= 0; --b) {
-                const float mb = hist_mass[b]; const int cb = hist_cnt[b];
-                if (cb == 0) continue;
-                acc += mb; cnt += cb;
-                if (acc >= need || cnt >= top_k) break;
+            __syncthreads();
+            // merge the 32 warp histograms: thread t < 256 owns bin t (results into warp 0's arrays)
+            if (tid < 256) {
+                unsigned long long m = 0ull; unsigned int c = 0u;
+                for (int w = 0; w < SP_NT / 32; ++w) { m += hist_mass[w * 256 + tid]; c += hist_cnt[w * 256 + tid]; }
+                merged_mass[tid] = (float)m * (1.0f / 16777216.0f);
+                merged_cnt[tid] = (int)c;
             }
-            if (b < 0) b = 0;
-            sh_i[3] = b; sh_f[3] = acc;
+            __syncthreads();
+            if (tid == 0) {
+                float acc = acc_mass; int cnt = acc_cnt; int bsel = 255;
+                for (; bsel >= 0; --bsel) {
+                    const float mb = merged_mass[bsel]; const int cb = merged_cnt[bsel];
+                    if (cb == 0) continue;
+                    if (acc + mb >= need || cnt + cb >= top_k) break;     // the threshold lies inside this bin
+                    acc += mb; cnt += cb;
+                }
+                if (bsel < 0) bsel = 0;
+                sh_i[1] = bsel; sh_f[2] = acc; sh_i[2] = cnt;
+            }
+            __syncthreads();
+            prefix |= (uint32_t)sh_i[1] << shift;
+            acc_mass = sh_f[2];
+            acc_cnt = sh_i[2];
+            __syncthreads();
         }
-        __syncthreads();
-        thr_key = ((uint32_t)b1 << 12) | (uint32_t)sh_i[3];
-        kept_mass = sh_f[3];
+        thr_key = prefix;
     }
 
     // ---- draw ----
@@ -220,7 +211,7 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         philox4x32_10((uint32_t)off, (uint32_t)(off >> 32), 0u, 0u, (uint32_t)sd, (uint32_t)(sd >> 32), r);
         u = ((r[0] >> 8) + 0.5f) * (1.0f / 16777216.0f);
     }
-    // kept_mass from the histograms is summed in a different order than below; recompute it in walk order
+    // mass of the kept set, summed in walk order
     const int chunk = (p.V + SP_NT - 1) / SP_NT;
     const int i0 = tid * chunk, i1 = min(p.V, i0 + chunk);
     float local = 0.f;
@@ -294,7 +285,6 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         if (p.out_prob) p.out_prob[row] = __expf(logit_at(tok) - mx) / total;
         if (p.seen) p.seen[(size_t)slot * p.V + tok] = 1;
     }
-    (void)kept_mass;
 }
 
 }  // namespace mstar
@@ -309,7 +299,15 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
     SampleParams p{logits, ld, is_f32, B, V, temperature, top_k, top_p, rep_penalty, seed, offset, seen, row_slot,
                    out, out_prob, u_override};
     cudaStream_t s = (cudaStream_t)stream_;
-    cudaError_t e = is_f32 ? launch_pdl(sample_kernel<true>, dim3(B), dim3(SP_NT), 0, s, p)
-                           : launch_pdl(sample_kernel<false>, dim3(B), dim3(SP_NT), 0, s, p);
+    constexpr int smem = (SP_NT / 32) * 256 * 12;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e1 = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e2 = cudaFuncSetAttribute(sample_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) return set_error("sample: cudaFuncSetAttribute failed", e1 != cudaSuccess ? e1 : e2);
+        configured = true;
+    }
+    cudaError_t e = is_f32 ? launch_pdl(sample_kernel<true>, dim3(B), dim3(SP_NT), smem, s, p)
+                           : launch_pdl(sample_kernel<false>, dim3(B), dim3(SP_NT), smem, s, p);
     return e == cudaSuccess ? 0 : set_error("sample launch", e);
 }
