@@ -1,0 +1,436 @@
+// Collectives over the symmetric heap: every rank maps every peer's heap (plain peer pointers over NVLink, no
+// TMA and no multicast loads from peer memory). Signals are 32-bit epoch words written with release stores at
+// system scope and polled with acquire loads; every poll is bounded and reports through the status word
+// instead of hanging, so a missing peer turns into an error code on the host.
+//
+//   * allreduce_oneshot   small messages (decode): every rank copies its partial into its own heap slot, raises
+//                         its flag at every peer, then sums all ranks' partials in rank order (identical
+//                         result on every rank, which tensor-parallel greedy decoding relies on).
+//   * allreduce_twoshot   large messages: rank r reduces slice r of the rows from all peers and stores the sum
+//                         into every rank's output (reduce-scatter + all-gather in one kernel).
+//   * a2a_heads           Ulysses exchange: [S_local, H, D] -> every peer gets its head group of these rows
+//                         written straight into its [S_total, H / P, D] buffer (and the reverse direction).
+//   * cfg_combine_peer    classifier-free guidance with the branches on different GPUs: the combine rank reads
+//                         the peers' velocities over NVLink and applies guidance + renorm + Euler step.
+//   * peer_barrier        device-side barrier over the flags (replaces a host barrier per forward).
+//
+// Reference counterparts: CommGroup all_reduce / all_to_all through NCCL (mstar/distributed/communication.py:
+// 67-162), row-parallel all-reduce call sites (mstar/model/components/distributed/linear.py:415), Ulysses
+// (mstar/model/components/distributed/sequence_parallel.py:84-176), CFG branch exchange over the tensor
+// transport (mstar/model/bagel/submodules.py:1411-1570), per-forward tp barrier
+// (mstar/engine/kv_cache_engine.py:1016).
+#include "common.cuh"
+#include "host_common.h"
+
+namespace mstar {
+
+constexpr int MAX_RANKS = 8;
+
+struct PeerTable {
+    void* buf[MAX_RANKS];            // base of each rank's data region
+    unsigned int* flags[MAX_RANKS];  // base of each rank's flag region: [channel][MAX_RANKS]
+    int world, rank;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Wait until *flag >= target (epochs only grow; wrap-around after 2^31 steps is handled by the signed compare).
+__device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int target, unsigned long long limit_ns) {
+    if ((int)(ld_acquire_sys(flag) - target) >= 0) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned int it = 0;
+    while ((int)(ld_acquire_sys(flag) - target) < 0) {
+        if ((++it & 0xffu) == 0u) {
+            if (globaltimer_ns() - t0 > limit_ns) return false;
+            __nanosleep(64);
+        }
+    }
+    return true;
+}
+
+// Signal every peer on `channel` with `epoch`, then wait for every peer's signal on the same channel.
+// Called by ONE thread of a CTA after the CTA's data stores were fenced (__threadfence_system by the writers).
+__device__ __forceinline__ bool signal_and_wait_all(const PeerTable& t, int channel, unsigned int epoch,
+                                                    KernelStatus* status, unsigned long long limit_ns, int phase) {
+    for (int p = 0; p < t.world; ++p)
+        if (p != t.rank) st_release_sys(t.flags[p] + (size_t)channel * MAX_RANKS + t.rank, epoch);
+    bool ok = true;
+    for (int p = 0; p < t.world; ++p) {
+        if (p == t.rank) continue;
+        if (!wait_flag(t.flags[t.rank] + (size_t)channel * MAX_RANKS + p, epoch, limit_ns)) {
+            report_status(status, KID_COMM, phase, p, channel);
+            ok = false;
+        }
+    }
+    return ok;
+}
+
+struct ARParams {
+    PeerTable t;
+    const __nv_bfloat16* in;     // local partial [n]
+    __nv_bfloat16* out;          // local result [n]
+    const __nv_bfloat16* residual;   // optional, added after the sum
+    long long n;                 // elements (multiple of 8)
+    long long slot_bytes;        // data region is split into 2 slots used in turn (parity of the epoch)
+    unsigned int* epoch;         // local device word: number of completed calls on this channel set
+    unsigned int* arrive;        // local device word: CTA arrival counter (reset by the last CTA)
+    int channel_base;            // flag channels [channel_base, channel_base + gridDim.x)
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+
+// One-shot: grid-stride over 16-byte vectors; CTA b owns vectors [b*chunk, (b+1)*chunk) and flag channel b.
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const ARParams p) {
+    __shared__ int s_ok;
+    __shared__ unsigned int s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) { s_epoch = *p.epoch + 1; s_ok = 1; }
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int parity = epoch & 1;
+    const long long nvec = p.n >> 3;
+    const long long per = (nvec + gridDim.x - 1) / gridDim.x;
+    const long long v0 = (long long)blockIdx.x * per;
+    long long v1 = v0 + per;
+    if (v1 > nvec) v1 = nvec;
+    uint4* mine = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[p.t.rank]) + parity * p.slot_bytes);
+    const uint4* src = reinterpret_cast<const uint4*>(p.in);
+    for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) mine[v] = src[v];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!signal_and_wait_all(p.t, p.channel_base + blockIdx.x, epoch, p.status, p.wait_limit_ns, 1)) s_ok = 0;
+    }
+    __syncthreads();
+    if (s_ok) {
+        for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int r = 0; r < p.t.world; ++r) {
+                const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes)[v];
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                }
+            }
+            if (p.residual != nullptr) {
+                const uint4 x = reinterpret_cast<const uint4*>(p.residual)[v];
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                }
+            }
+            reinterpret_cast<uint4*>(p.out)[v] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                            pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        }
+    }
+    // the last CTA of the launch publishes the new epoch for the next call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        if (old == gridDim.x - 1) {
+            *p.arrive = 0u;
+            *p.epoch = epoch;
+        }
+    }
+}
+
+// Two-shot: rank r owns vectors [r*share, (r+1)*share); it sums that slice from every rank's slot and stores the
+// result into every rank's `gather` region (second half of the slot), then signals; everyone copies out.
+__global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const ARParams p) {
+    __shared__ int s_ok;
+    __shared__ unsigned int s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) { s_epoch = *p.epoch + 1; s_ok = 1; }
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int parity = epoch & 1;
+    const long long nvec = p.n >> 3;
+    const int W = p.t.world, R = p.t.rank;
+    const long long half_bytes = p.slot_bytes >> 1;      // [partials | gathered result]
+    // phase 1: publish my partial (CTA-sliced), signal on channel b
+    const long long per = (nvec + gridDim.x - 1) / gridDim.x;
+    const long long v0 = (long long)blockIdx.x * per;
+    long long v1 = v0 + per;
+    if (v1 > nvec) v1 = nvec;
+    char* my_slot = reinterpret_cast<char*>(p.t.buf[R]) + parity * p.slot_bytes;
+    const uint4* src = reinterpret_cast<const uint4*>(p.in);
+    for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) reinterpret_cast<uint4*>(my_slot)[v] = src[v];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!signal_and_wait_all(p.t, p.channel_base + blockIdx.x, epoch, p.status, p.wait_limit_ns, 2)) s_ok = 0;
+    }
+    __syncthreads();
+    // phase 2: reduce my share of this CTA's vectors, store to everyone's gather region
+    if (s_ok) {
+        const long long share = (v1 - v0 + W - 1) / W;
+        const long long a = v0 + R * share;
+        long long b = a + share;
+        if (b > v1) b = v1;
+        for (long long v = a + threadIdx.x; v < b; v += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int r = 0; r < W; ++r) {
+                const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes)[v];
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                }
+            }
+            const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+            for (int r = 0; r < W; ++r)
+                reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[r]) + parity * p.slot_bytes + half_bytes)[v] = o;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && s_ok) {
+        // second signal round uses its own channel range [base + grid, base + 2 * grid)
+        if (!signal_and_wait_all(p.t, p.channel_base + gridDim.x + blockIdx.x, epoch, p.status, p.wait_limit_ns, 3)) s_ok = 0;
+    }
+    __syncthreads();
+    if (s_ok) {
+        const uint4* g = reinterpret_cast<const uint4*>(my_slot + half_bytes);
+        for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+            uint4 x = g[v];
+            if (p.residual != nullptr) {
+                const uint4 rsd = reinterpret_cast<const uint4*>(p.residual)[v];
+                const uint32_t a4[4] = {x.x, x.y, x.z, x.w}, b4[4] = {rsd.x, rsd.y, rsd.z, rsd.w};
+                uint32_t o4[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 fa = unpack_bf16x2(a4[j]), fb = unpack_bf16x2(b4[j]);
+                    o4[j] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+                }
+                x = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+            reinterpret_cast<uint4*>(p.out)[v] = x;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        if (old == gridDim.x - 1) {
+            *p.arrive = 0u;
+            *p.epoch = epoch;
+        }
+    }
+}
+
+// Device-side barrier over one flag channel (one CTA, one thread does the signalling).
+struct BarrierParams {
+    PeerTable t;
+    unsigned int* epoch;
+    int channel;
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+__global__ void peer_barrier_kernel(const BarrierParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        const unsigned int e = *p.epoch + 1;
+        __threadfence_system();
+        signal_and_wait_all(p.t, p.channel, e, p.status, p.wait_limit_ns, 4);
+        *p.epoch = e;
+    }
+}
+
+// Ulysses head <-> sequence exchange by peer stores.
+//   forward  (scatter heads, gather sequence): src [S_local, H, D] on each rank; rank q receives, for its head
+//            group, rows [seq_off[r], seq_off[r] + S_local_r) of dst [S_total, H/P, D] from rank r.
+//   backward (scatter sequence, gather heads): src [S_total, H/P, D]; rank q receives its rows with rank r's
+//            head group into dst [S_local_q, H, D].
+struct A2AParams {
+    PeerTable t;
+    const __nv_bfloat16* src;
+    long long dst_offset_bytes;   // destination buffer offset inside every rank's data region
+    int forward;
+    int H, D;                      // full head count, head dim
+    int seq_off[MAX_RANKS + 1];    // row offsets of the ranks' sequence shards
+    unsigned int* epoch;
+    unsigned int* arrive;
+    int channel_base;
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+__global__ void __launch_bounds__(256) a2a_heads_kernel(const A2AParams p) {
+    __shared__ unsigned int s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) s_epoch = *p.epoch + 1;
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int W = p.t.world, R = p.t.rank;
+    const int Hp = p.H / W;
+    const int vec_per_head = p.D >> 3;
+    const int S_total = p.seq_off[W];
+    if (p.forward) {
+        const int S_local = p.seq_off[R + 1] - p.seq_off[R];
+        const long long total = (long long)S_local * p.H * vec_per_head;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+            const int v = (int)(i % vec_per_head);
+            const long long hs = i / vec_per_head;
+            const int h = (int)(hs % p.H);
+            const long long s = hs / p.H;
+            const int q = h / Hp, hl = h - q * Hp;
+            const uint4 x = reinterpret_cast<const uint4*>(p.src)[i];
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + p.dst_offset_bytes);
+            dst[((long long)(p.seq_off[R] + s) * Hp + hl) * vec_per_head + v] = x;
+        }
+    } else {
+        const long long total = (long long)S_total * Hp * vec_per_head;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+            const int v = (int)(i % vec_per_head);
+            const long long hs = i / vec_per_head;
+            const int hl = (int)(hs % Hp);
+            const int s = (int)(hs / Hp);
+            int q = 0;
+            while (q + 1 < W && s >= p.seq_off[q + 1]) ++q;
+            const uint4 x = reinterpret_cast<const uint4*>(p.src)[i];
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + p.dst_offset_bytes);
+            dst[((long long)(s - p.seq_off[q]) * p.H + R * Hp + hl) * vec_per_head + v] = x;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // grid-wide completion: the last CTA signals the peers and waits for theirs
+    __shared__ int s_last;
+    if (threadIdx.x == 0) {
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        s_last = (old == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence_system();
+        signal_and_wait_all(p.t, p.channel_base, epoch, p.status, p.wait_limit_ns, 5);
+        *p.arrive = 0u;
+        *p.epoch = epoch;
+    }
+}
+
+// CFG-parallel combine: velocities of the branches live at `v_offset_bytes` in the data region of ranks
+// cond_rank / uncond_rank / img_rank (img_rank < 0: two-branch guidance). Runs on the combine rank after the
+// branch ranks have raised their flags on `channel`; reads the peers' tensors over NVLink.
+struct CfgPeerParams {
+    PeerTable t;
+    long long v_offset_bytes;
+    int cond_rank, uncond_rank, img_rank;
+    const float* x;
+    float* x_next;
+    float* v_out;
+    int rows, cols;
+    float s_text, s_img, dt, renorm_min;
+    int renorm;
+    unsigned int* epoch;
+    unsigned int* arrive;
+    int channel;
+    int wait_peers;
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+__device__ __forceinline__ void cfg_publish_epoch(const CfgPeerParams& p, unsigned int e) {
+    // the last CTA of the launch publishes the consumed epoch (every CTA has read the old value by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        if (old == gridDim.x - 1) {
+            *p.arrive = 0u;
+            if (p.wait_peers) *p.epoch = e;
+        }
+    }
+}
+__global__ void __launch_bounds__(128) cfg_combine_peer_kernel(const CfgPeerParams p) {
+    __shared__ float red[32];
+    __shared__ int s_ok;
+    __shared__ unsigned int s_e;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        s_ok = 1;
+        s_e = *p.epoch + 1;
+        if (p.wait_peers) {
+            const unsigned int e = s_e;
+            const int rk[3] = {p.cond_rank, p.uncond_rank, p.img_rank};
+            for (int i = 0; i < 3; ++i) {
+                if (rk[i] < 0 || rk[i] == p.t.rank) continue;
+                if (!wait_flag(p.t.flags[p.t.rank] + (size_t)p.channel * MAX_RANKS + rk[i], e, p.wait_limit_ns)) {
+                    report_status(p.status, KID_CFG, 1, rk[i], p.channel);
+                    s_ok = 0;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (!s_ok) { cfg_publish_epoch(p, s_e); return; }
+    const int r = blockIdx.x;
+    const size_t base = (size_t)r * p.cols;
+    const float* vc = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.t.buf[p.cond_rank]) + p.v_offset_bytes);
+    const float* vu = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.t.buf[p.uncond_rank]) + p.v_offset_bytes);
+    const float* vi = p.img_rank >= 0
+        ? reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.t.buf[p.img_rank]) + p.v_offset_bytes) : nullptr;
+    float nc = 0.f, nv = 0.f;
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+        const float c = vc[base + i], u = vu[base + i];
+        float v = u + p.s_text * (c - u);
+        if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
+        nc += c * c; nv += v * v;
+    }
+    float scale = 1.f;
+    if (p.renorm) {
+        nc = warp_sum(nc); nv = warp_sum(nv);
+        if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = nc; red[4 + (threadIdx.x >> 5)] = nv; }
+        __syncthreads();
+        nc = red[0] + red[1] + red[2] + red[3];
+        nv = red[4] + red[5] + red[6] + red[7];
+        scale = fminf(fmaxf(sqrtf(nc) / (sqrtf(nv) + 1e-8f), p.renorm_min), 1.f);
+    }
+    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+        const float c = vc[base + i], u = vu[base + i];
+        float v = u + p.s_text * (c - u);
+        if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
+        v *= scale;
+        if (p.v_out) p.v_out[base + i] = v;
+        if (p.x_next) p.x_next[base + i] = p.x[base + i] + p.dt * v;
+    }
+    cfg_publish_epoch(p, s_e);
+}
+
+// Raise this rank's flag on `channel` at rank `dst` (after earlier kernels' stores to the heap): one thread.
+struct SignalParams { PeerTable t; unsigned int* epoch; int channel; int dst; int bump_epoch; };
+__global__ void peer_signal_kernel(const SignalParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        const unsigned int e = *p.epoch + 1;
+        __threadfence_system();
+        st_release_sys(p.t.flags[p.dst] + (size_t)p.channel * MAX_RANKS + p.t.rank, e);
+        if (p.bump_epoch) *p.epoch = e;
+    }
+}
+
+}  // namespace mstar
+
+#include "comm_host.inc"

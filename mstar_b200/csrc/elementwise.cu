@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
         s_sin[i] = sn;
     }
     __syncthreads();
-    for (int hidx = warp; hidx < nheads; hidx += nwarps) {
+    for (int hidx = blockIdx.y * nwarps + warp; hidx < nheads; hidx += nwarps * gridDim.y) {
         const bool is_q = hidx < p.Hq;
         const bool is_k = !is_q && hidx < p.Hq + p.Hkv;
         const __nv_bfloat16* src = row + (size_t)hidx * D;
@@ -482,7 +482,9 @@ MSTAR_API int mstar_rope_kv(const void* qkv, long long ld_qkv, void* q_out, void
                  (__nv_bfloat16*)v_out, (__nv_bfloat16*)cache, positions, pos_stride, inv_freq, axis_of_freq,
                  (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, token_req, cache_pos, page_indptr,
                  page_indices, T, Hq, Hkv, D, rot_dim, page_size, interleaved, gemma_norm, norm_eps, q_scale};
-    cudaError_t e = launch_pdl(rope_kv_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream_, p);
+    const int nheads = Hq + 2 * Hkv;
+    const int gy = T >= 1024 ? 1 : (nheads + 7) / 8;   // few tokens: one warp per head across several CTAs
+    cudaError_t e = launch_pdl(rope_kv_kernel, dim3(T, gy), dim3(256), 0, (cudaStream_t)stream_, p);
     return e == cudaSuccess ? 0 : set_error("rope_kv launch", e);
 }
 

@@ -1,0 +1,151 @@
+"""Symmetric heap: one buffer per rank of a group, mapped into every rank's address space, plus flag words for
+device-side signalling. The allocation and the handle exchange use ``torch.distributed._symmetric_memory``
+(bootstrap plumbing over the NCCL/gloo store); everything that moves data afterwards is this library's own
+kernels (``csrc/comm.cu``, the fused GEMM epilogue) issuing plain peer loads / stores over NVLink.
+
+Layout of every rank's heap:
+    [ reduce slots: 2 x slot_bytes ][ user region: user_bytes ][ flags: n_channels x 8 x u32 ]
+Local (non-shared) state words hold the epochs of the channel sets.
+
+Reference counterparts: NCCL process groups through torch.distributed (mstar/distributed/communication.py:
+214-263) — collectives there are separate library kernels between the GEMMs; here the heap lets a kernel read or
+write a peer's memory while it computes.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+MAX_RANKS = 8
+N_CHANNELS = 1024
+# channel map
+CH_ALLREDUCE = 0          # [0, 512): all-reduce CTAs (two rounds of up to 256)
+CH_BARRIER = 512
+CH_A2A = 513              # [513, 521)
+CH_CFG = 528
+CH_GEMM_AR = 544          # [544, 1024): fused GEMM + all-reduce tiles
+
+
+class SymmetricHeap:
+    def __init__(self, group: "dist.ProcessGroup", ranks: list[int], rank: int, device,
+                 slot_bytes: int = 32 << 20, user_bytes: int = 64 << 20):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.device = torch.device(device)
+        self.world = len(ranks)
+        self.rank = ranks.index(rank)
+        self.slot_bytes = slot_bytes
+        self.user_bytes = user_bytes
+        self.flag_bytes = N_CHANNELS * MAX_RANKS * 4
+        total = 2 * slot_bytes + user_bytes + self.flag_bytes
+        gname = group.group_name if hasattr(group, "group_name") else group
+        try:
+            symm_mem.enable_symm_mem_for_group(gname)      # needed on older torch, a no-op warning on newer
+        except Exception:
+            pass
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group=gname)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(ptrs) == self.world
+        self.base_ptrs = ptrs
+        self._bufs = (ctypes.c_void_p * MAX_RANKS)(*([ctypes.c_void_p(p) for p in ptrs] + [None] * (MAX_RANKS - self.world)))
+        fl = [p + 2 * slot_bytes + user_bytes for p in ptrs]
+        self._flags = (ctypes.c_void_p * MAX_RANKS)(*([ctypes.c_void_p(p) for p in fl] + [None] * (MAX_RANKS - self.world)))
+        self.user_offset = 2 * slot_bytes
+        # local state: [epoch, arrive] pairs per channel set
+        self.state = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self._user_cursor = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+        self.group = group
+
+    # ---- user region carving (same order on every rank => symmetric offsets) ----
+    def alloc_user(self, nbytes: int, align: int = 256) -> int:
+        off = (self._user_cursor + align - 1) // align * align
+        if off + nbytes > self.user_bytes:
+            raise MemoryError("symmetric heap user region exhausted")
+        self._user_cursor = off + nbytes
+        return self.user_offset + off
+
+    def local_view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.buf[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def _state_ptr(self, idx: int) -> ctypes.c_void_p:
+        return ctypes.c_void_p(self.state.data_ptr() + idx * 8)
+
+    # ---- collectives ----
+    def all_reduce(self, x: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                   mode: int = 0) -> torch.Tensor:
+        """Sum of ``x`` (bf16, contiguous, numel % 8 == 0) over the group; every rank gets the identical result."""
+        assert x.dtype == torch.bfloat16 and x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        rc = _lib.kernels().mstar_allreduce(self._bufs, self._flags, self.world, self.rank,
+                                            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                            ctypes.c_void_p(_lib.ptr(residual)), ctypes.c_longlong(x.numel()),
+                                            ctypes.c_longlong(self.slot_bytes), self._state_ptr(0), CH_ALLREDUCE, 128,
+                                            int(mode), ctypes.c_void_p(_lib.stream_ptr()))
+        if rc < 0:
+            _lib.check(rc, "mstar_allreduce")
+        return out
+
+    def barrier(self) -> None:
+        rc = _lib.kernels().mstar_peer_barrier(self._bufs, self._flags, self.world, self.rank, self._state_ptr(1),
+                                               CH_BARRIER, ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_peer_barrier")
+
+    def a2a_heads(self, src: torch.Tensor, dst_offset: int, forward: bool, H: int, D: int, seq_off: list[int]) -> None:
+        """Ulysses exchange by peer stores into the tensor at ``dst_offset`` of every rank's heap; returns after
+        the peers' stores into this rank's tensor are visible to later kernels of the stream."""
+        assert src.dtype == torch.bfloat16 and src.is_contiguous()
+        so = (ctypes.c_int * (MAX_RANKS + 1))(*(list(seq_off) + [seq_off[-1]] * (MAX_RANKS + 1 - len(seq_off))))
+        rc = _lib.kernels().mstar_a2a_heads(self._bufs, self._flags, self.world, self.rank,
+                                            ctypes.c_void_p(src.data_ptr()), ctypes.c_longlong(dst_offset),
+                                            1 if forward else 0, int(H), int(D), so, self._state_ptr(2), CH_A2A,
+                                            ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_a2a_heads")
+
+    def signal(self, dst_rank: int, channel: int = CH_CFG, state_idx: int = 3, bump: bool = True) -> None:
+        rc = _lib.kernels().mstar_peer_signal(self._bufs, self._flags, self.world, self.rank,
+                                              self._state_ptr(state_idx), int(channel), int(dst_rank),
+                                              1 if bump else 0, ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_peer_signal")
+
+    def cfg_combine(self, v_offset: int, cond_rank: int, uncond_rank: int, img_rank: int, x: torch.Tensor,
+                    dt: float, s_text: float, s_img: float = 1.0, renorm: bool = False, renorm_min: float = 0.0,
+                    wait_peers: bool = True):
+        """Guidance combine on this rank, reading the branch velocities (fp32 [rows, cols] at ``v_offset`` of the
+        branch ranks' heaps) over NVLink. Returns (x_next, v)."""
+        rows, cols = x.shape
+        x = x.float().contiguous()
+        x_next, v = torch.empty_like(x), torch.empty_like(x)
+        rc = _lib.kernels().mstar_cfg_combine_peer(
+            self._bufs, self._flags, self.world, self.rank, ctypes.c_longlong(v_offset), int(cond_rank),
+            int(uncond_rank), int(img_rank), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x_next.data_ptr()),
+            ctypes.c_void_p(v.data_ptr()), int(rows), int(cols), ctypes.c_float(s_text), ctypes.c_float(s_img),
+            ctypes.c_float(dt), 1 if renorm else 0, ctypes.c_float(renorm_min), self._state_ptr(3), CH_CFG,
+            1 if wait_peers else 0, ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_cfg_combine_peer")
+        return x_next, v
+
+    # ---- table for fused kernels ----
+    def tables(self):
+        return self._bufs, self._flags
+
+
+def attach_symmetric_heap(group, device, **kw) -> SymmetricHeap | None:
+    """Create the heap for a ``CommGroup`` and hang it on ``group.symm``. Returns None (and leaves the NCCL path
+    in place) for trivial groups or CPU ranks."""
+    if group.size <= 1 or not torch.cuda.is_available():
+        return None
+    heap = SymmetricHeap(group.group, group.ranks, group.global_rank, device, **kw)
+    group.symm = heap
+    return heap

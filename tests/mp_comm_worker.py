@@ -1,0 +1,110 @@
+"""Child program of the multi-GPU communication tests (one process per GPU under torchrun). Exits non-zero on a
+mismatch; rank 0 prints one line per check."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from mstar_b200.ops import _lib  # noqa: E402
+from mstar_b200.parallel.comm import init_from_env  # noqa: E402
+from mstar_b200.parallel.symm import attach_symmetric_heap  # noqa: E402
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    g = init_from_env()
+    W, R = g.size, g.rank
+    heap = attach_symmetric_heap(g, dev, slot_bytes=16 << 20, user_bytes=32 << 20)
+    ok = True
+
+    def check(name, cond):
+        nonlocal ok
+        flag = torch.tensor([1 if cond else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if R == 0:
+            print(f"{name}: {'ok' if flag.item() else 'FAIL'}", flush=True)
+        ok = ok and bool(flag.item())
+
+    # ---- all-reduce, both algorithms, several sizes, repeated (epochs / slot parity) ----
+    for mode, n in [(1, 8), (1, 64 * 3072), (2, 64 * 3072), (2, 1024 * 3072 + 8), (0, 4096 * 1024)]:
+        for it in range(3):
+            gen = torch.Generator().manual_seed(100 * it + n % 97)
+            parts = [torch.randn(n, generator=gen).to(torch.bfloat16) for _ in range(W)]
+            x = parts[R].to(dev)
+            res = torch.randn(n, generator=gen).to(torch.bfloat16).to(dev)
+            out = heap.all_reduce(x, residual=res, mode=mode)
+            ref = sum(p.float() for p in parts) + res.float().cpu()
+            err = (out.float().cpu() - ref).abs().max().item()
+            gathered = [torch.empty_like(out) for _ in range(W)]
+            dist.all_gather(gathered, out)
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            check(f"allreduce mode={mode} n={n} it={it} err={err:.3g}", err < 0.05 * max(1.0, ref.abs().max().item()) and same)
+    # against NCCL
+    x = torch.randn(64 * 3072, device=dev).to(torch.bfloat16)
+    y = x.clone()
+    dist.all_reduce(y)
+    out = heap.all_reduce(x)
+    check("allreduce vs nccl", (out.float() - y.float()).abs().max().item() < 0.1)
+
+    # ---- barrier ----
+    for _ in range(5):
+        heap.barrier()
+    torch.cuda.synchronize()
+    check("barrier", _lib.read_status(clear=False)[0] == 0)
+
+    # ---- Ulysses all-to-all, uneven sequence shards, both directions ----
+    H, D = 8, 128
+    shards = [37 + 5 * r for r in range(W)]
+    seq_off = [0]
+    for s in shards:
+        seq_off.append(seq_off[-1] + s)
+    S = seq_off[-1]
+    gen = torch.Generator().manual_seed(7)
+    full = torch.randn(S, H, D, generator=gen).to(torch.bfloat16)
+    mine = full[seq_off[R]:seq_off[R + 1]].contiguous().to(dev)
+    off_f = heap.alloc_user(S * (H // W) * D * 2)
+    off_b = heap.alloc_user(max(shards) * H * D * 2)
+    heap.a2a_heads(mine, off_f, True, H, D, seq_off)
+    got = heap.local_view(off_f, (S, H // W, D), torch.bfloat16)
+    want = full[:, R * (H // W):(R + 1) * (H // W)].to(dev)
+    check("a2a forward", torch.equal(got, want))
+    heap.a2a_heads(got.contiguous(), off_b, False, H, D, seq_off)
+    back = heap.local_view(off_b, (shards[R], H, D), torch.bfloat16)
+    check("a2a backward", torch.equal(back, mine))
+
+    # ---- CFG-parallel combine: rank 0 = cond + combine, rank 1 = uncond ----
+    from mstar_b200.ops.elementwise import cfg_combine_ref
+    rows, cols = 256, 64
+    v_off = heap.alloc_user(rows * cols * 4)
+    gen = torch.Generator().manual_seed(11)
+    vs = [torch.randn(rows, cols, generator=gen) for _ in range(W)]
+    xx = torch.randn(rows, cols, generator=gen)
+    for it in range(2):
+        heap.local_view(v_off, (rows, cols), torch.float32).copy_(vs[R].to(dev) + it)
+        if R != 0:
+            heap.signal(0)
+        if R == 0:
+            xn, v = heap.cfg_combine(v_off, 0, 1, -1, xx.to(dev), dt=-0.02, s_text=4.0, renorm=True)
+            xr, vr = cfg_combine_ref(vs[0] + it, vs[1] + it, xx, -0.02, 4.0, renorm=True)
+            good = (xn.cpu() - xr).abs().max().item() < 1e-4
+        else:
+            good = True
+        if W > 2 and R > 1:
+            pass
+        check(f"cfg combine it={it}", good)
+        heap.barrier()
+    torch.cuda.synchronize()
+    code = _lib.read_status(clear=True)[0]
+    check("status word clean", code == 0)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,27 @@
+"""Symmetric-heap collectives on 2+ GPUs (child processes under torchrun)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script, nproc, extra_env=None, timeout=600):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+           "--nproc-per-node", str(nproc), os.path.join(ROOT, "tests", script)]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_heap_collectives():
+    n = min(torch.cuda.device_count(), 4)
+    n = 2 if n < 4 else 4
+    res = _run("mp_comm_worker.py", n)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "FAIL" not in res.stdout
