@@ -17,8 +17,22 @@
 #include <cuda.h>
 #include "common.cuh"
 #include "host_common.h"
+#include "comm_device.cuh"
 
 namespace mstar {
+
+// Optional tensor-parallel reduction fused into the epilogue (decode layout): every rank publishes its partial
+// output tile in its symmetric-heap slot, raises the tile's flag at the peers, waits (bounded) for theirs and
+// sums all ranks' tiles in rank order over NVLink, so the transfer of one tile overlaps the math of the others.
+struct GemmAllReduce {
+    PeerTable t;
+    long long slot_bytes;       // two slots per rank, used in turn
+    unsigned int* epoch;        // local: completed fused calls
+    unsigned int* arrive;       // local: tiles finished in this launch
+    int channel_base;
+    int enabled;
+};
+
 
 struct GemmParams {
     int M, N, K;               // logical problem: C[M,N] = A[M,K] B[N,K]^T
@@ -38,6 +52,7 @@ struct GemmParams {
     KernelStatus* status;
     unsigned long long wait_limit_ns;
     float out_scale;                // multiplies the accumulator before bias (1.0 by default)
+    GemmAllReduce ar;
 };
 
 constexpr int BM = 128;  // UMMA M (P-tile rows)
@@ -222,6 +237,91 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* s
     }
 }
 
+// Swapped-layout epilogue with the cross-rank sum. stage: [rows][BM] fp32 partial of this rank.
+__device__ __noinline__ void copy_out_allreduce(const GemmParams& p, const float* stage, int rows, int m_base,
+                                                int n_base, int tile_lin, int ntiles, int tid, volatile int* flags) {
+    const GemmAllReduce& ar = p.ar;
+    if (tid == 0) flags[2] = (int)(*ar.epoch + 1u);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const unsigned int epoch = (unsigned int)flags[2];
+    const long long slot_off = (long long)(epoch & 1u) * ar.slot_bytes;
+    constexpr int EPV = 8;
+    const int units_per_row = BM / EPV;
+    const int total = rows * units_per_row;
+    // 1) my partial tile -> my slot (bf16, same [M][N] layout as the output)
+    __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(ar.t.buf[ar.t.rank]) + slot_off);
+    for (int u = tid; u < total; u += 128) {
+        const int r = u / units_per_row, c = (u - r * units_per_row) * EPV;
+        const int m = m_base + r, n = n_base + c;
+        if (m >= p.M || n >= p.N) continue;
+        const float* sp = stage + r * BM + c;
+        float x[EPV];
+#pragma unroll
+        for (int j = 0; j < EPV; j += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(sp + j);
+            x[j] = t4.x; x[j + 1] = t4.y; x[j + 2] = t4.z; x[j + 3] = t4.w;
+        }
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) {
+            x[j] *= p.out_scale;
+            if (p.bias != nullptr && n + j < p.N) x[j] += __bfloat162float(p.bias[n + j]);
+        }
+        *reinterpret_cast<uint4*>(mine + (size_t)m * p.N + n) =
+            make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    // 2) flags: tell the peers this tile is published, wait for theirs
+    if (tid == 0) {
+        const bool ok = signal_and_wait_all(ar.t, ar.channel_base + tile_lin, epoch, p.status, p.wait_limit_ns, 0x40);
+        flags[3] = ok ? 1 : 0;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    // 3) sum all ranks' tiles in rank order, add the residual, store
+    if (flags[3]) {
+        for (int u = tid; u < total; u += 128) {
+            const int r = u / units_per_row, c = (u - r * units_per_row) * EPV;
+            const int m = m_base + r, n = n_base + c;
+            if (m >= p.M || n >= p.N) continue;
+            float acc[EPV];
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) acc[j] = 0.f;
+            for (int q = 0; q < ar.t.world; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(ar.t.buf[q]) + slot_off) + (size_t)m * p.N + n);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                }
+            }
+            if (p.residual != nullptr) {
+                const uint4 v = *reinterpret_cast<const uint4*>(p.residual + (size_t)m * p.ld_res + n);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                }
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc + n) =
+                make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                           pack_bf16x2(acc[6], acc[7]));
+        }
+    }
+    // 4) the last tile of the launch publishes the epoch for the next fused call
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int old = atomicAdd(ar.arrive, 1u);
+        if (old == (unsigned int)(ntiles - 1)) {
+            *ar.arrive = 0u;
+            *ar.epoch = epoch;
+        }
+    }
+}
+
 template <int BN, int STAGES, int MINB>
 __global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
@@ -235,7 +335,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_bar = empty_bar + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
-    volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort, [1] is_last
+    volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort, [1] is_last, [2] epoch, [3] peers ok
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -408,7 +508,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             }
             if (p.swap) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
+                if (p.ar.enabled) copy_out_allreduce(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, tile_lin, gridDim.x * gridDim.y, threadIdx.x - 64, flags);
+                else if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
                 else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
             }
             if (p.splits > 1 && threadIdx.x == 64) p.counters[tile_lin] = 0u;  // ready for the next launch
@@ -444,6 +545,26 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
 }  // namespace mstar
 
 using namespace mstar;
+static GemmAllReduce g_next_ar = {};
+
+// Arms the tensor-parallel reduction for the NEXT mstar_gemm_bf16 call of this thread of control: the output is
+// summed over the ranks of the table inside the GEMM epilogue. state: two local device words [epoch, arrive].
+MSTAR_API int mstar_gemm_arm_allreduce(void* const* bufs, void* const* flags, int world, int rank,
+                                       long long slot_bytes, void* state, int channel_base) {
+    if (world < 1 || world > MAX_RANKS) return set_error("gemm+allreduce: bad world size", cudaSuccess);
+    for (int i = 0; i < MAX_RANKS; ++i) {
+        g_next_ar.t.buf[i] = i < world ? bufs[i] : nullptr;
+        g_next_ar.t.flags[i] = i < world ? reinterpret_cast<unsigned int*>(flags[i]) : nullptr;
+    }
+    g_next_ar.t.world = world;
+    g_next_ar.t.rank = rank;
+    g_next_ar.slot_bytes = slot_bytes;
+    g_next_ar.epoch = reinterpret_cast<unsigned int*>(state);
+    g_next_ar.arrive = g_next_ar.epoch + 1;
+    g_next_ar.channel_base = channel_base;
+    g_next_ar.enabled = 1;
+    return 0;
+}
 
 // Workspace bytes needed for a given problem (0 when no split-K is used). Also returns the split factor.
 MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, int* splits_out,
@@ -528,6 +649,15 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     p.status = status_ptr();
     p.wait_limit_ns = wait_limit_ns();
     p.out_scale = out_scale;
+    p.ar = g_next_ar;
+    g_next_ar.enabled = 0;
+    if (p.ar.enabled) {
+        if (!swap || epilogue != 0 || out_f32 || (N % 8) || ldc % 8 || (residual && ld_res % 8))
+            return set_error("gemm+allreduce: needs the decode layout (M <= 128), bf16 output, no activation, N % 8 == 0", cudaSuccess);
+        if ((long long)M * N * 2 > p.ar.slot_bytes) return set_error("gemm+allreduce: output does not fit the heap slot", cudaSuccess);
+        if ((long long)tiles * splits > 2LL * device_sm_count())
+            return set_error("gemm+allreduce: grid must be co-resident", cudaSuccess);
+    }
 
     const void* Pp = swap ? B : A;
     const void* Qp = swap ? A : B;

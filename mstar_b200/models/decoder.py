@@ -66,6 +66,16 @@ def _param(shape, dtype, device):
     return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=False)
 
 
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, tp: CommGroup, bias: torch.Tensor | None = None):
+    """y = all_reduce(x_shard @ w_shard.T): fused into the GEMM epilogue over the symmetric heap when attached."""
+    if tp.size == 1:
+        return gemm.linear(x, w, bias=bias)
+    if tp.symm is not None and x.is_cuda:
+        return tp.symm.linear_all_reduce(x, w, bias=bias)
+    y = gemm.linear(x, w, bias=bias if tp.rank == 0 else None)
+    return tp.all_reduce(y)
+
+
 def tp_reduce(x: torch.Tensor, tp: CommGroup) -> torch.Tensor:
     """Sum row-parallel partials over the TP group (fused symmetric-heap path when attached)."""
     if tp.size == 1:
@@ -99,8 +109,7 @@ class Attention(nn.Module):
                                    cache_pos=ctx.cache_pos, page_indptr=ctx.plan.page_indptr,
                                    page_indices=ctx.plan.page_indices)
         a = attn_ops.attention(q, ctx.plan, kv_cache=kv)
-        o = gemm.linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj)
-        return tp_reduce(o, self.tp)
+        return row_parallel_linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj, self.tp)
 
 
 class GatedMLP(nn.Module):
@@ -116,8 +125,9 @@ class GatedMLP(nn.Module):
 
     def forward(self, h: torch.Tensor, reduce: bool = True) -> torch.Tensor:
         g = gemm.linear(h, self.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
-        d = gemm.linear(g, self.down_proj)
-        return tp_reduce(d, self.tp) if reduce else d
+        if not reduce:
+            return gemm.linear(g, self.down_proj)
+        return row_parallel_linear(g, self.down_proj, self.tp)
 
 
 class DecoderLayer(nn.Module):

@@ -59,6 +59,12 @@ class SymmetricHeap:
         # local state: [epoch, arrive] pairs per channel set
         self.state = torch.zeros(64, dtype=torch.int32, device=self.device)
         self._user_cursor = 0
+        # the fused GEMM + all-reduce epilogue has its own pair of slots (its epochs are independent of the
+        # stand-alone all-reduce, so the two must never share a slot)
+        self.gemm_slot_bytes = 8 << 20
+        goff = self.alloc_user(2 * self.gemm_slot_bytes)
+        self._gemm_bufs = (ctypes.c_void_p * MAX_RANKS)(
+            *([ctypes.c_void_p(p + goff) for p in ptrs] + [None] * (MAX_RANKS - self.world)))
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
         self.group = group
@@ -135,6 +141,23 @@ class SymmetricHeap:
             1 if wait_peers else 0, ctypes.c_void_p(_lib.stream_ptr()))
         _lib.check(rc, "mstar_cfg_combine_peer")
         return x_next, v
+
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                          residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel projection: ``sum_over_ranks(x_r @ w_r.T) (+bias) (+residual)`` in ONE kernel per rank —
+        the tcgen05 GEMM publishes each output tile in the heap and sums the peers' tiles in its epilogue.
+        Decode layout only (at most 128 rows); larger inputs take GEMM + stand-alone all-reduce."""
+        from ..ops import gemm
+        M = x.numel() // x.shape[-1]
+        N = w.shape[0]
+        if M > 128 or N % 8 or M * N * 2 > self.gemm_slot_bytes:
+            y = gemm.linear(x, w, bias=bias if self.rank == 0 else None)
+            return self.all_reduce(y.contiguous(), residual=residual)
+        rc = _lib.kernels().mstar_gemm_arm_allreduce(self._gemm_bufs, self._flags, self.world, self.rank,
+                                                     ctypes.c_longlong(self.gemm_slot_bytes), self._state_ptr(4),
+                                                     CH_GEMM_AR)
+        _lib.check(rc, "mstar_gemm_arm_allreduce")
+        return gemm.linear(x, w, bias=bias if self.rank == 0 else None, residual=residual)
 
     # ---- table for fused kernels ----
     def tables(self):

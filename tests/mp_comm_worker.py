@@ -51,6 +51,23 @@ def main():
     out = heap.all_reduce(x)
     check("allreduce vs nccl", (out.float() - y.float()).abs().max().item() < 0.1)
 
+    # ---- fused GEMM + all-reduce epilogue vs GEMM + NCCL all-reduce ----
+    from mstar_b200.ops import gemm
+    for (M, N, K) in [(64, 3072, 1536), (16, 3072, 4096), (1, 1024, 512), (128, 3072, 1536), (300, 1024, 512)]:
+        for it in range(3):
+            gen = torch.Generator().manual_seed(1000 + it)
+            xs = [torch.randn(M, K, generator=gen).to(torch.bfloat16) for _ in range(W)]
+            ws = [(torch.randn(N, K, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(W)]
+            bias = torch.randn(N, generator=gen).to(torch.bfloat16).to(dev)
+            res = torch.randn(M, N, generator=gen).to(torch.bfloat16).to(dev)
+            y = heap.linear_all_reduce(xs[R].to(dev), ws[R].to(dev), bias=bias, residual=res)
+            ref = sum(x.float() @ w.float().t() for x, w in zip(xs, ws)) + bias.float().cpu() + res.float().cpu()
+            err = (y.float().cpu() - ref).abs().max().item()
+            gathered = [torch.empty_like(y) for _ in range(W)]
+            dist.all_gather(gathered, y.contiguous())
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            check(f"gemm+allreduce M={M} N={N} K={K} it={it} err={err:.3g}", err < 0.06 * max(1.0, ref.abs().max().item()) and same)
+
     # ---- barrier ----
     for _ in range(5):
         heap.barrier()
