@@ -94,13 +94,20 @@ class SymmetricHeap:
         assert x.dtype == torch.bfloat16 and x.is_contiguous()
         if out is None:
             out = torch.empty_like(x)
-        rc = _lib.kernels().mstar_allreduce(self._bufs, self._flags, self.world, self.rank,
-                                            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
-                                            ctypes.c_void_p(_lib.ptr(residual)), ctypes.c_longlong(x.numel()),
-                                            ctypes.c_longlong(self.slot_bytes), self._state_ptr(0), CH_ALLREDUCE, 128,
-                                            int(mode), ctypes.c_void_p(_lib.stream_ptr()))
-        if rc < 0:
-            _lib.check(rc, "mstar_allreduce")
+        n = x.numel()
+        # messages larger than a heap slot go in slot-sized pieces (two-shot keeps partials and results in one slot)
+        piece = (self.slot_bytes // 4) // 8 * 8
+        xf, of = x.view(-1), out.view(-1)
+        rf = residual.view(-1) if residual is not None else None
+        for a in range(0, n, piece):
+            b = min(n, a + piece)
+            rc = _lib.kernels().mstar_allreduce(
+                self._bufs, self._flags, self.world, self.rank, ctypes.c_void_p(xf[a:b].data_ptr()),
+                ctypes.c_void_p(of[a:b].data_ptr()), ctypes.c_void_p(_lib.ptr(rf[a:b]) if rf is not None else 0),
+                ctypes.c_longlong(b - a), ctypes.c_longlong(self.slot_bytes), self._state_ptr(0), CH_ALLREDUCE, 128,
+                int(mode), ctypes.c_void_p(_lib.stream_ptr()))
+            if rc < 0:
+                _lib.check(rc, "mstar_allreduce")
         return out
 
     def barrier(self) -> None:
