@@ -1,0 +1,27 @@
+"""API-side request records. Reference counterpart: mstar/api_server/request_types.py."""
+from __future__ import annotations
+
+import queue
+import time
+from dataclasses import dataclass, field
+
+
+@dataclass
+class ResultChunk:
+    modality: str                 # text | audio | image | video | error
+    data: bytes = b""
+    metadata: dict = field(default_factory=dict)
+    final: bool = False
+    error_status: int | None = None
+
+
+@dataclass
+class PendingRequest:
+    request_id: str
+    output_modalities: list[str]
+    model_kwargs: dict
+    chunks: "queue.Queue[ResultChunk]" = field(default_factory=queue.Queue)
+    done: bool = False
+    t_submit: float = field(default_factory=time.time)
+    t_first_chunk: float | None = None
+    profile: dict = field(default_factory=dict)

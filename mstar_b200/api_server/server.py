@@ -1,0 +1,199 @@
+"""API server core: request registry, preprocessing (media loading + ``model.process_prompt``) on a worker thread
+pool, hand-off to the conductor, and delivery of result chunks back to waiting clients.
+
+Reference counterparts: ``APIServer`` (mstar/api_server/entrypoint.py:158-674: submit :251-305, result loop
+:359-577, TTL pruning, abort :652-668), ``PreprocessWorkerThread`` (mstar/api_server/data_worker.py:225-580).
+"""
+from __future__ import annotations
+
+import logging
+import queue
+import threading
+import time
+import uuid
+from concurrent.futures import ThreadPoolExecutor
+
+import torch
+
+from ..communication.tensors import TensorCommunicationManager
+from ..conductor.deployment import Deployment
+from ..utils import ipc_format as ipc
+from ..utils.ipc_format import ApiMessageType as AM
+from ..utils.ipc_format import ConductorMessageType as CM
+from ..utils.ipc_format import Message
+from .request_types import PendingRequest, ResultChunk
+
+log = logging.getLogger("mstar.api")
+
+_EXT_MODALITY = {".png": "image", ".jpg": "image", ".jpeg": "image", ".webp": "image", ".bmp": "image",
+                 ".wav": "audio", ".mp3": "audio", ".flac": "audio", ".ogg": "audio",
+                 ".mp4": "video", ".mov": "video", ".avi": "video", ".mkv": "video"}
+
+
+def modality_of(filename: str) -> str | None:
+    import os
+    return _EXT_MODALITY.get(os.path.splitext(filename)[1].lower())
+
+
+class APIServer:
+    def __init__(self, config, *, in_process: bool = True, request_timeout_s: float = 600.0, result_ttl_s: float = 300.0,
+                 log_stats: bool = False, **deploy_kw):
+        self.deployment = Deployment(config, in_process=in_process, **deploy_kw)
+        self.model = self.deployment.model
+        self.comm = self.deployment.api_comm
+        self.tensors = TensorCommunicationManager("api", "cpu", arena_prefix=self.deployment.prefix)
+        self.pending: dict[str, PendingRequest] = {}
+        self.lock = threading.Lock()
+        self.ready = threading.Event()
+        self.request_timeout_s, self.result_ttl_s, self.log_stats = request_timeout_s, result_ttl_s, log_stats
+        self.pre_pool = ThreadPoolExecutor(4, thread_name_prefix="preprocess")
+        self.running = True
+        self.stats = dict(submitted=0, completed=0, failed=0, aborted=0)
+        self._thread = threading.Thread(target=self._process_messages, daemon=True, name="api-results")
+
+    # ---- lifecycle ----
+    def start(self, wait_ready_s: float = 600.0) -> "APIServer":
+        self.deployment.start()
+        self._thread.start()
+        if not self.ready.wait(wait_ready_s):
+            raise TimeoutError("workers did not come up")
+        return self
+
+    def shutdown(self) -> None:
+        self.running = False
+        self.deployment.shutdown()
+        self.pre_pool.shutdown(wait=False)
+        self.tensors.close()
+
+    # ---- submission ----
+    def submit_request(self, text: str | None = None, files: list[tuple[str, bytes]] | None = None,
+                       input_modalities: list[str] | None = None, output_modalities: list[str] | None = None,
+                       model_kwargs: dict | None = None, request_id: str | None = None,
+                       tensors: dict | None = None) -> str:
+        rid = request_id or uuid.uuid4().hex
+        out_mod = output_modalities or ["text"]
+        pr = PendingRequest(rid, out_mod, dict(model_kwargs or {}))
+        with self.lock:
+            self.pending[rid] = pr
+        self.stats["submitted"] += 1
+        self.pre_pool.submit(self._preprocess, pr, text, files or [], input_modalities, tensors or {})
+        return rid
+
+    def _preprocess(self, pr: PendingRequest, text, files, input_modalities, tensors) -> None:
+        try:
+            named: dict[str, list[torch.Tensor]] = {k: list(v) for k, v in tensors.items()}
+            mods = list(input_modalities or (["text"] if text else []))
+            for fname, blob in files:
+                m = modality_of(fname)
+                if m is None:
+                    raise ValueError(f"cannot infer the modality of {fname!r}")
+                loader = {"image": self.model.load_image, "audio": self.model.load_audio, "video": self.model.load_video}[m]
+                named.setdefault(m, []).append(loader(blob))
+                if m not in mods:
+                    mods.append(m)
+            sigs = self.model.process_prompt(text, mods, pr.output_modalities, named, **pr.model_kwargs)
+            infos = {k: [self.tensors.prepare_for_remote(self.tensors.store_and_return_tensor_info(pr.request_id, t, persist=True), "conductor_workers")
+                         for t in v] for k, v in sigs.items()}
+            body = ipc.NewRequestConductor(pr.request_id, infos, mods, pr.output_modalities, {}, pr.model_kwargs)
+            self.comm.send("conductor", Message(CM.NEW_REQUEST, body))
+        except Exception as e:  # noqa: BLE001
+            log.exception("preprocess of %s failed", pr.request_id)
+            self._finish(pr, ResultChunk("error", f"{type(e).__name__}: {e}".encode(), final=True, error_status=400))
+
+    def abort_request(self, request_id: str) -> None:
+        with self.lock:
+            pr = self.pending.get(request_id)
+        if pr is None or pr.done:
+            return
+        self.stats["aborted"] += 1
+        self.comm.send("conductor", Message(CM.ABORT_REQUEST, ipc.AbortRequest(request_id)))
+        self._finish(pr, ResultChunk("error", b"aborted", final=True, error_status=499))
+
+    # ---- results ----
+    def _finish(self, pr: PendingRequest, last: ResultChunk | None = None) -> None:
+        if pr.done:
+            return
+        pr.done = True
+        pr.chunks.put(last or ResultChunk("done", final=True))
+        self.tensors.remove_request(pr.request_id)
+
+    def _process_messages(self) -> None:
+        last_prune = time.time()
+        while self.running:
+            for m in self.comm.recv_or_wake(0.05):
+                try:
+                    self._handle(m)
+                except Exception:  # noqa: BLE001
+                    log.exception("api: message %s failed", m.type)
+            if time.time() - last_prune > 5.0:
+                last_prune = time.time()
+                self._prune()
+
+    def _handle(self, m: Message) -> None:
+        if m.type == AM.SETUP_DONE:
+            self.ready.set()
+            return
+        b = m.body
+        with self.lock:
+            pr = self.pending.get(b.request_id)
+        if pr is None or pr.done:
+            if m.type == AM.RESULT_TENSORS and b.source_entity:     # still acknowledge, so the producer frees them
+                self.comm.send(b.source_entity, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, ipc.TensorReceived(
+                    b.request_id + "#emit", {ti.uuid: 1 for ti in b.tensors})))
+            return
+        if m.type == AM.RESULT_TENSORS:
+            ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
+            data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
+            if pr.t_first_chunk is None:
+                pr.t_first_chunk = time.time()
+            pr.chunks.put(ResultChunk(b.modality, data, dict(b.metadata)))
+            if b.source_entity:
+                self.comm.send(b.source_entity, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, ipc.TensorReceived(
+                    b.request_id + "#emit", {ti.uuid: 1 for ti in b.tensors})))
+        elif m.type == AM.REQUEST_COMPLETE:
+            pr.profile = b.profile
+            self.stats["completed"] += 1
+            if self.log_stats:
+                from ..profile.display import format_profile
+                log.info("%s", format_profile(pr.request_id, pr.profile, pr.t_submit, pr.t_first_chunk))
+            self._finish(pr)
+        elif m.type == AM.REQUEST_FAILED:
+            self.stats["failed"] += 1
+            self._finish(pr, ResultChunk("error", b.error_message.encode(), final=True, error_status=b.status))
+
+    def _prune(self) -> None:
+        now = time.time()
+        with self.lock:
+            for rid, pr in list(self.pending.items()):
+                if pr.done and now - pr.t_submit > self.result_ttl_s:
+                    del self.pending[rid]
+                elif not pr.done and now - pr.t_submit > self.request_timeout_s:
+                    self.comm.send("conductor", Message(CM.ABORT_REQUEST, ipc.AbortRequest(rid)))
+                    self._finish(pr, ResultChunk("error", b"request timed out", final=True, error_status=500))
+
+    def iter_result_chunks(self, request_id: str, timeout_s: float | None = None):
+        with self.lock:
+            pr = self.pending.get(request_id)
+        if pr is None:
+            raise KeyError(request_id)
+        deadline = time.time() + (timeout_s or self.request_timeout_s)
+        while True:
+            try:
+                c = pr.chunks.get(timeout=max(0.01, min(1.0, deadline - time.time())))
+            except queue.Empty:
+                if time.time() > deadline:
+                    self.abort_request(request_id)
+                    yield ResultChunk("error", b"request timed out", final=True, error_status=500)
+                    return
+                continue
+            if c.modality == "done":
+                return
+            yield c
+            if c.final:
+                return
+
+    def collect_results(self, request_id: str, timeout_s: float | None = None) -> dict[str, list[ResultChunk]]:
+        out: dict[str, list[ResultChunk]] = {}
+        for c in self.iter_result_chunks(request_id, timeout_s):
+            out.setdefault(c.modality, []).append(c)
+        return out

@@ -1,0 +1,129 @@
+"""Engine contract: ``execute_batch = prepare -> plan -> execute_forward -> postprocess -> finalize``, with
+per-request failure attribution and an allocation-failure envelope.
+
+Reference counterparts: ``NodeBatch`` / ``PreparedBatch`` / ``PlannedBatch`` / ``NodeOutput`` and ``BaseEngine``
+(mstar/engine/base.py:16-447; template :237-264, chunked execution :364-407).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass
+class NodeBatch:
+    node_name: str
+    graph_walk: str
+    request_ids: list[str]
+    inputs: dict[str, dict[str, list[torch.Tensor]]]     # request_id -> input name -> tensors
+    fwd_infos: dict                                       # request_id -> CurrentForwardPassInfo
+
+
+@dataclass
+class PreparedBatch:
+    batch: NodeBatch
+    node_inputs: list = field(default_factory=list)      # per kept request, in order
+    request_ids: list[str] = field(default_factory=list)
+    failed_requests: dict[str, str] = field(default_factory=dict)
+
+
+@dataclass
+class NodeOutput:
+    node_name: str
+    graph_walk: str
+    outputs: dict[str, dict[str, torch.Tensor]] = field(default_factory=dict)   # request_id -> edge name -> tensor
+    stop_loops: dict[str, set] = field(default_factory=dict)                    # request_id -> loop names
+    failed_requests: dict[str, str] = field(default_factory=dict)
+    allocation_failed: bool = False
+    allocation_failed_requests: list[str] = field(default_factory=list)
+    completion_event: object = None
+    timings: dict = field(default_factory=dict)
+
+
+class BaseEngine:
+    def __init__(self, node_names: list[str], device):
+        self.node_names = list(node_names)
+        self.device = torch.device(device)
+        self.submodules: dict[str, object] = {}
+
+    # template ------------------------------------------------------------------------------------
+    def execute_batch(self, batch: NodeBatch) -> NodeOutput:
+        prepared = self.prepare_batch(batch)
+        out = NodeOutput(batch.node_name, batch.graph_walk, failed_requests=dict(prepared.failed_requests))
+        if not prepared.request_ids:
+            return out
+        planned = self.plan(prepared)
+        raw = self.execute_forward(planned)
+        self.postprocess(planned, raw, out)
+        self.finalize_batch(planned, out)
+        return out
+
+    def prepare_batch(self, batch: NodeBatch) -> PreparedBatch:
+        """Per-request input preparation; a request whose preparation raises is failed alone."""
+        sub = self.submodules[batch.node_name]
+        prepared = PreparedBatch(batch)
+        for rid in batch.request_ids:
+            try:
+                ni = sub.prepare_inputs(batch.graph_walk, batch.fwd_infos[rid], batch.inputs.get(rid, {}))
+            except Exception as e:  # noqa: BLE001
+                prepared.failed_requests[rid] = f"prepare_inputs failed: {e!r}"
+                continue
+            prepared.node_inputs.append(ni)
+            prepared.request_ids.append(rid)
+        return prepared
+
+    def plan(self, prepared: PreparedBatch):
+        return prepared
+
+    def execute_forward(self, planned):
+        raise NotImplementedError
+
+    def postprocess(self, planned, raw, out: NodeOutput) -> None:
+        raise NotImplementedError
+
+    def finalize_batch(self, planned, out: NodeOutput) -> None:
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            out.completion_event = ev
+
+    # chunking ---------------------------------------------------------------------------------------
+    def execute_with_max_batch_size(self, batch: NodeBatch, max_bs: int) -> NodeOutput:
+        if len(batch.request_ids) <= max_bs:
+            return self.execute_batch(batch)
+        merged = NodeOutput(batch.node_name, batch.graph_walk)
+        for i in range(0, len(batch.request_ids), max_bs):
+            rids = batch.request_ids[i:i + max_bs]
+            part = self.execute_batch(NodeBatch(batch.node_name, batch.graph_walk, rids,
+                                                {r: batch.inputs.get(r, {}) for r in rids},
+                                                {r: batch.fwd_infos[r] for r in rids}))
+            merged.outputs.update(part.outputs)
+            merged.stop_loops.update(part.stop_loops)
+            merged.failed_requests.update(part.failed_requests)
+            merged.allocation_failed |= part.allocation_failed
+            merged.allocation_failed_requests += part.allocation_failed_requests
+            merged.completion_event = part.completion_event
+        return merged
+
+    # lifecycle --------------------------------------------------------------------------------------
+    def load_model(self, model, tp_group=None, sp_group=None) -> None:
+        for n in self.node_names:
+            self.submodules[n] = model.get_submodule(n, self.device, tp_group=tp_group,
+                                                     autocast_dtype=model.get_autocast_dtype(), sp_group=sp_group)
+
+    def warmup(self) -> None:
+        pass
+
+    def add_request(self, request_id: str, fwd_info) -> None:
+        pass
+
+    def remove_request(self, request_id: str) -> None:
+        for sub in self.submodules.values():
+            sub.cleanup_request(request_id)
+
+    def can_offload(self) -> bool:
+        return False
+
+    def offload_request(self, request_id: str) -> int:
+        return 0

@@ -1,0 +1,220 @@
+"""Engine for autoregressive nodes over the paged KV pool: owns the pool, the batch planner, the sampler and the
+CUDA-graph buckets of its nodes' decode steps.
+
+Dispatch per batch: captured graph (all entries decode one token, bucket available) > batched eager (packed
+varlen forward) > per-request fallback. Allocation failures never escape as exceptions: the batch comes back with
+``allocation_failed`` so the worker can offload a victim to the host pool or hold the requests.
+
+Reference counterparts: ``KVCacheEngine`` (mstar/engine/kv_cache_engine.py:136-1356: load_model :177-294, warmup
+:357-455, _execute_batched :517-635, _can_use_cuda_graph :701-781, execute_batch envelope :818-869, prepare_batch
+:897-999, execute_forward with the TP barrier :1001-1046, offload :1294-1349), BASIC_BATCHED decode graphs and
+in-graph sampling (mstar/engine/cuda_graph_runner.py:769-850,1308-1534,1866-1989).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..models.submodule_base import BATCHED_LOGITS, ModelInputsFromEngine
+from ..ops import _lib
+from ..ops import attention as attn_ops
+from ..ops.sampling import SamplerState, SamplingConfig
+from .base import BaseEngine, NodeBatch, NodeOutput, PreparedBatch
+from .cache_manager import BatchedCacheManager
+from .kv_store import AllocationFailedError, KVCacheConfig
+
+CAPTURE_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64]
+
+
+class KVCacheEngine(BaseEngine):
+    def __init__(self, node_names, device, kv_config: KVCacheConfig, *, vocab_size: int, max_batch: int = 64,
+                 max_tokens: int = 16384, n_pos_axes: int = 1, group: int = 1, use_cuda_graphs: bool | None = None,
+                 tp_group=None, track_seen: bool = True):
+        super().__init__(node_names, device)
+        self.kv_config = kv_config
+        self.cache = BatchedCacheManager(kv_config, device, max_batch=max_batch, max_tokens=max_tokens + max_batch,
+                                         n_pos_axes=n_pos_axes)
+        self.sampler = SamplerState(max_batch * 2, vocab_size, device, track_seen=track_seen)
+        self.max_batch, self.group = max_batch, group
+        self.tp_group = tp_group
+        self.use_graphs = (self.device.type == "cuda") if use_cuda_graphs is None else (use_cuda_graphs and self.device.type == "cuda")
+        self._graphs: dict[tuple, tuple] = {}
+        self._static_ids = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
+        self._static_tok = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
+        self.graph_hits = 0
+        self.graph_misses: dict[str, int] = {}
+        self.states: dict[str, dict] = {}
+
+    # ---- request lifecycle ----
+    def add_request(self, request_id: str, fwd_info) -> None:
+        if not self.cache.alloc.has_request(request_id):
+            self.cache.add_request(request_id)
+        sc = (fwd_info.sampling_config or {}).get("main", {})
+        cfg = SamplingConfig(self.sampler.vocab_size, **{k: sc[k] for k in
+                             ("temperature", "top_k", "top_p", "repetition_penalty", "ignore_eos") if k in sc})
+        self.sampler.assign(request_id, cfg, seed=fwd_info.random_seed or None)
+
+    def remove_request(self, request_id: str) -> None:
+        self.cache.remove_request(request_id)
+        self.sampler.release(request_id)
+        self.states.pop(request_id, None)
+        super().remove_request(request_id)
+
+    def get_per_label_seq_info(self, request_id: str) -> dict:
+        return self.cache.alloc.get_per_label_seq_info(request_id)
+
+    # ---- offload surface ----
+    def can_offload(self) -> bool:
+        return self.cache.alloc.cpu_pool is not None
+
+    def offload_request(self, request_id: str) -> int:
+        return self.cache.alloc.offload_request(request_id)
+
+    def pages_of(self, request_id: str) -> int:
+        return self.cache.alloc.pages_of(request_id)
+
+    # ---- template steps ----
+    def execute_batch(self, batch: NodeBatch) -> NodeOutput:
+        try:
+            return super().execute_batch(batch)
+        except AllocationFailedError as e:
+            out = NodeOutput(batch.node_name, batch.graph_walk, allocation_failed=True,
+                             allocation_failed_requests=list(batch.request_ids))
+            out.timings["allocation_error"] = str(e)
+            return out
+
+    def prepare_batch(self, batch: NodeBatch) -> PreparedBatch:
+        for rid in batch.request_ids:
+            if rid not in self.sampler._slot_of:
+                self.add_request(rid, batch.fwd_infos[rid])
+            if self.cache.alloc.is_offloaded(rid):
+                self.cache.alloc.reload_request(rid)      # may raise AllocationFailedError -> envelope
+        return super().prepare_batch(batch)
+
+    def plan(self, prepared: PreparedBatch):
+        b = prepared.batch
+        sub = self.submodules[b.node_name]
+        q_lens = [max(1, ni.input_seq_len) for ni in prepared.node_inputs]
+        labels = [sub.get_needed_cache_labels(b.graph_walk, b.fwd_infos[r])[0] for r in prepared.request_ids]
+        slots = [self.sampler.slot(r) for r in prepared.request_ids]
+        decode = all(q == 1 for q in q_lens)
+        B = len(q_lens)
+        bucket = None
+        if decode and self.use_graphs and sub.can_use_cuda_graphs(b.graph_walk):
+            bucket = next((s for s in CAPTURE_BATCH_SIZES if s >= B and s <= self.max_batch), None)
+            if bucket is None:
+                self.graph_misses["batch larger than the largest bucket"] = self.graph_misses.get("batch larger than the largest bucket", 0) + 1
+        elif self.use_graphs:
+            why = "prefill / multi-token step" if not decode else "node opted out"
+            self.graph_misses[why] = self.graph_misses.get(why, 0) + 1
+        custom = None
+        if any(ni.custom_pos_ids is not None for ni in prepared.node_inputs):
+            custom = torch.cat([ni.custom_pos_ids.reshape(ni.custom_pos_ids.shape[0] if ni.custom_pos_ids.dim() > 1 else 1, -1)
+                                for ni in prepared.node_inputs], dim=-1)
+        splits = None
+        if bucket is not None:
+            splits = attn_ops.choose_splits(bucket, self.kv_config.num_kv_heads, bucket, self.kv_config.max_seq_len,
+                                            sm_count=3 * 148)
+        ctx = self.cache.plan(prepared.request_ids, q_lens, labels=labels, row_slots=slots, pad_to_batch=bucket,
+                              group=self.group, slot=0 if bucket is not None else 1, custom_positions=custom,
+                              splits=splits)
+        prepared.ctx, prepared.bucket, prepared.q_lens = ctx, bucket, q_lens
+        return prepared
+
+    def _forward_logits(self, sub, walk, ei, node_inputs):
+        outs = sub.forward_batched(walk, ei, node_inputs)
+        return outs
+
+    def execute_forward(self, planned: PreparedBatch):
+        b = planned.batch
+        sub = self.submodules[b.node_name]
+        ctx = planned.ctx
+        if self.tp_group is not None and getattr(self.tp_group, "symm", None) is not None:
+            self.tp_group.symm.barrier()
+        ei = ModelInputsFromEngine(planned.request_ids, b.fwd_infos, cache_manager=self.cache, batch_context=ctx,
+                                   sampler=self.sampler,
+                                   per_request_states={r: self.states.setdefault(r, {}) for r in planned.request_ids})
+        B = len(planned.request_ids)
+        with torch.no_grad():
+            if planned.bucket is not None:
+                ids = torch.cat([ni.input_ids.reshape(-1)[-1:] for ni in planned.node_inputs]).to(self.device)
+                self._static_ids[:B].copy_(ids)
+                key = (b.node_name, b.graph_walk, planned.bucket)
+                entry = self._graphs.get(key)
+                if entry is None:
+                    entry = self._capture(key, sub, b.graph_walk, ei, planned)
+                entry[0].replay()
+                self.graph_hits += 1
+                tokens = self._static_tok[:B].clone()
+                raw = {"tokens": tokens, "extra": {k: v[:B].clone() if isinstance(v, torch.Tensor) else v
+                                                   for k, v in entry[1].items()}}
+            else:
+                sub.preprocess(b.graph_walk, ei, planned.node_inputs)
+                outs = sub.forward_batched(b.graph_walk, ei, planned.node_inputs)
+                raw = {"extra": {k: v for k, v in outs.items() if k != BATCHED_LOGITS}}
+                if BATCHED_LOGITS in outs:
+                    lg = outs[BATCHED_LOGITS]
+                    if lg.dtype not in (torch.float32, torch.bfloat16):
+                        lg = lg.float()
+                    raw["tokens"] = self.sampler.sample(lg.contiguous(), ctx.row_slot[:lg.shape[0]])
+        self.cache.advance_seq_lens(ctx)
+        return raw
+
+    def _capture(self, key, sub, walk, ei, planned):
+        """Capture model forward + sampling for one (node, walk, bucket). Inputs: the static id buffer and the
+        plan slot; outputs: the static token buffer (+ any extra tensors the node returns)."""
+        Bp = planned.bucket
+        ctx = planned.ctx
+        attn_ops.reserve_scratch(self.device, Bp * max(1, self.kv_config.num_qo_heads), self.kv_config.head_dim,
+                                 max(1, ctx.plan.splits), Bp * self.kv_config.num_kv_heads)
+        saved_off = self.sampler.offset.clone()
+        saved_seen = None if self.sampler.seen is None else self.sampler.seen.clone()
+
+        class _NI:      # node inputs view over the static id buffer
+            pass
+
+        def body():
+            outs = sub.forward_graph(walk, ei, self._static_ids[:Bp], ctx)
+            self.sampler.sample(outs[BATCHED_LOGITS], ctx.row_slot, out=self._static_tok[:Bp], advance=False)
+            self.sampler.offset.index_add_(0, ctx.row_slot.long(), torch.ones(Bp, dtype=torch.int64, device=self.device))
+            return {k: v for k, v in outs.items() if k != BATCHED_LOGITS}
+
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                body()
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                extra = body()
+        torch.cuda.current_stream().wait_stream(s)
+        self.sampler.offset.copy_(saved_off)
+        if saved_seen is not None:
+            self.sampler.seen.copy_(saved_seen)
+        self._graphs[key] = (g, extra)
+        return self._graphs[key]
+
+    def postprocess(self, planned: PreparedBatch, raw, out: NodeOutput) -> None:
+        b = planned.batch
+        sub = self.submodules[b.node_name]
+        tokens = raw.get("tokens")
+        host_tokens = tokens.tolist() if tokens is not None else None      # one D2H read per step
+        for i, (rid, ni) in enumerate(zip(planned.request_ids, planned.node_inputs)):
+            try:
+                r = {k: (v[i] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == len(planned.request_ids) else v)
+                     for k, v in raw.get("extra", {}).items()}
+                if tokens is not None:
+                    r["new_token"] = tokens[i:i + 1]
+                    r["new_token_host"] = host_tokens[i]
+                out.outputs[rid] = sub.postprocess(rid, b.fwd_infos[rid], r, ni)
+                stops = sub.check_stop(rid, b.fwd_infos[rid], r)
+                if stops:
+                    out.stop_loops[rid] = set(stops)
+            except Exception as e:  # noqa: BLE001
+                out.failed_requests[rid] = f"postprocess failed: {e!r}"
+
+    def check_status(self) -> None:
+        if self.device.type == "cuda":
+            code, block, a0, a1 = _lib.read_status(clear=True)
+            if code:
+                raise RuntimeError(f"kernel status {code:#x} (block {block}, aux {a0}, {a1})")

@@ -35,7 +35,8 @@ class TensorPointerInfo:
     source_tp_rank: int = 0
     shm_segment: str | None = None
     shm_offset: int = 0
-    device_index: int = -1          # >= 0: lives in that GPU's arena (peer-copyable over NVLink)
+    device_index: int = -1          # >= 0: lives on that GPU (peer-copyable over NVLink)
+    cuda_ipc: tuple | None = None   # CUDA IPC handle of the producer's allocation for cross-process GPU reads
 
     def clone(self) -> "TensorPointerInfo":
         return replace(self, dims=list(self.dims), stride=list(self.stride))
@@ -230,3 +231,23 @@ def entities_of(section: GraphSection) -> list[GraphSection]:
     for c in section.children():
         out.extend(entities_of(c))
     return out
+
+
+def restrict_section(section: GraphSection, keep: set[str]) -> GraphSection | None:
+    """The part of a walk that one worker runs: same composition, only the nodes in ``keep`` (None when the
+    section has none of them). Loops keep their name and iteration budget, so that workers sharing a loop count
+    iterations alike; edges that leave the kept set are routed to their owners by the worker."""
+    if isinstance(section, GraphNode):
+        return section if section.name in keep else None
+    if isinstance(section, Loop):
+        inner = restrict_section(section.section, keep)
+        if inner is None:
+            return None
+        return Loop(inner, section.max_iters, [e.clone() for e in section.outputs], section.name,
+                    [e.clone() for e in section.accumulated_outputs])
+    kids = [k for k in (restrict_section(c, keep) for c in section.children()) if k is not None]
+    if not kids:
+        return None
+    if len(kids) == 1:
+        return kids[0]
+    return type(section)(kids)

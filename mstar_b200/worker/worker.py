@@ -1,0 +1,467 @@
+"""Per-GPU worker: owns the engines of the nodes placed on its rank, keeps one ``WalkState`` per (request,
+partition), turns arriving signals into ready nodes, lets the micro-scheduler form batches, runs them on a GPU
+thread and routes the outputs — to a local node (no copy), to another worker (descriptor over the mesh, data by
+peer copy / arena), or to the client through the API server.
+
+Failure handling: a request whose stage fails is failed alone (``FAIL_REQUESTS`` to the conductor); an allocation
+failure offloads the request with the most pages to the host pool or holds the batch for a back-off; any other
+exception of the main loop fails the requests of the batch in flight and the loop goes on.
+
+Reference counterpart: ``Worker`` (mstar/worker/worker.py:117-2598), ``WorkerGraphsManager``
+(mstar/worker/node_manager_utils.py), TP lockstep through ``SCHEDULE_TP`` (:899-923), streaming routing (:660-757),
+allocation failure handling (:1252-1300), error containment (:1998-2079).
+"""
+from __future__ import annotations
+
+import logging
+import threading
+import time
+import traceback
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+
+import torch
+
+from ..communication.communicator import BaseCommunicator
+from ..communication.tensors import TensorCommunicationManager
+from ..engine.base import NodeBatch, NodeOutput
+from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, restrict_section
+from ..graph.walk_state import WalkState
+from ..streaming.stream_buffer import StreamBuffer
+from ..utils import ipc_format as ipc
+from ..utils.ipc_format import ConductorMessageType as CM
+from ..utils.ipc_format import Message
+from ..utils.ipc_format import WorkerMessageType as WM
+from ..utils.profiler import nvtx_range
+from .micro_scheduler import MicroScheduler
+
+log = logging.getLogger("mstar.worker")
+
+
+@dataclass
+class PerRequestInfo:
+    request_id: str
+    fwd_info: ipc.CurrentForwardPassInfo
+    walk_state: WalkState
+    worker_graph_ids: list[str]
+    worker_graph_to_workers: dict[str, list[str]]
+    partition_name: str = "default"
+    persist: dict[str, list] = field(default_factory=dict)
+    new_token_counts: dict[str, int] = field(default_factory=dict)
+    stream_buffers: dict[str, StreamBuffer] = field(default_factory=dict)
+    in_flight: int = 0
+    remove_pending: bool = False
+    t_start: float = field(default_factory=time.perf_counter)
+    timings: dict = field(default_factory=dict)
+
+
+class Worker:
+    def __init__(self, worker_id: str, rank: int, model, node_names: list[str], comm: BaseCommunicator,
+                 tensors: TensorCommunicationManager, engine_manager, *, node_to_workers: dict[str, list[str]],
+                 conductor_id: str = "conductor", api_id: str = "api", tp_followers: list[str] | None = None,
+                 is_tp_follower: bool = False, max_batch_size: int = 64, async_gpu: bool = True,
+                 heartbeat_s: float = 0.0):
+        self.worker_id, self.rank, self.model = worker_id, rank, model
+        self.node_names = set(node_names)
+        self.comm, self.tensors, self.engines = comm, tensors, engine_manager
+        self.node_to_workers = node_to_workers
+        self.conductor_id, self.api_id = conductor_id, api_id
+        self.tp_followers = tp_followers or []
+        self.is_tp_follower = is_tp_follower
+        self.scheduler = MicroScheduler(max_batch_size=max_batch_size, is_tp_follower=is_tp_follower)
+        self.walks = model.get_graph_walk_graphs()
+        self.topology = model.get_partition_topology()
+        self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
+        self.running = True
+        self.gpu_thread = ThreadPoolExecutor(1, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
+        self._pending = None       # (future, batch)
+        self.heartbeat_s = heartbeat_s
+        self._last_beat = time.monotonic()
+        self.phase_times: dict[str, list[float]] = {}
+        self.iterations = 0
+
+    # ------------------------------------------------------------------ messages
+    def _process_messages(self, msgs: list[Message]) -> None:
+        for m in msgs:
+            try:
+                t = m.type
+                if t == WM.NEW_REQUEST:
+                    self._on_new_request(m.body)
+                elif t == WM.INPUT_SIGNALS:
+                    self._on_input_signals(m.body)
+                elif t == WM.REMOVE_REQUEST:
+                    self._on_remove_request(m.body)
+                elif t == WM.STOP_LOOPS:
+                    self._on_stop_loops(m.body)
+                elif t == WM.SCHEDULE_TP:
+                    self.scheduler.push_tp_decision(m.body.node_name, m.body.graph_walk, m.body.request_ids)
+                elif t == WM.UNPERSIST_TENSORS:
+                    for u, n in m.body.uuid_to_ref_count.items():
+                        self.tensors.store.unpersist(u)
+                elif t == WM.TENSOR_RECEIVED:
+                    for u, n in m.body.successful_tensors.items():
+                        self.tensors.dereference(m.body.request_id, u, n)
+                elif t == WM.SHUTDOWN:
+                    self.running = False
+            except Exception as e:  # noqa: BLE001
+                rid = getattr(m.body, "request_id", None)
+                log.exception("worker %s: message %s failed", self.worker_id, m.type)
+                if rid:
+                    self._fail_requests({rid: f"{type(e).__name__}: {e}"})
+
+    def _section_for(self, walk: str):
+        sec = self.walks.get(walk)
+        if sec is None:
+            raise KeyError(f"unknown graph walk {walk!r}")
+        return restrict_section(sec, self.node_names)
+
+    def _on_new_request(self, b: ipc.NewRequest) -> None:
+        info = b.request_info
+        sec = self._section_for(info.graph_walk)
+        if sec is None:
+            return
+        key = (b.request_id, info.partition_name)
+        old = self.requests.get(key)
+        ws = WalkState(sec, b.request_id, on_release=lambda e, rid=b.request_id: self._release_edge(rid, e))
+        for loop_name, iters in (info.dynamic_loop_iter_counts or {}).items():
+            sc = ws.scopes.get(loop_name)
+            if sc is not None:
+                sc.loop = _with_max_iters(sc.loop, int(iters))
+        pri = PerRequestInfo(b.request_id, info, ws, b.partition_worker_graph_ids, b.worker_graph_to_workers,
+                             info.partition_name)
+        if old is not None:
+            pri.stream_buffers = old.stream_buffers
+            pri.persist = old.persist
+        self.requests[key] = pri
+        self._setup_streams(pri)
+        for e in b.initial_inputs:
+            self._ingest(pri, e)
+        self._refresh_ready(pri)
+
+    def _setup_streams(self, pri: PerRequestInfo) -> None:
+        if self.topology is None:
+            return
+        for c in self.topology.incoming(pri.partition_name):
+            if c.edge_name not in pri.stream_buffers:
+                pri.stream_buffers[c.edge_name] = StreamBuffer(pri.request_id, c.edge_name, c.from_partition,
+                                                               c.chunk_policy_factory())
+
+    def _on_input_signals(self, b: ipc.InputSignals) -> None:
+        pri = self.requests.get((b.request_id, b.partition_name))
+        if pri is None:
+            return
+        if b.request_info is not None and b.request_info.graph_walk != pri.fwd_info.graph_walk:
+            pri.fwd_info = b.request_info
+        for name in b.producer_done or ():
+            sb = pri.stream_buffers.get(name)
+            if sb is not None:
+                sb.signal_done()
+        for e in b.inputs:
+            self._ingest(pri, e)
+        self._refresh_ready(pri)
+
+    def _ingest(self, pri: PerRequestInfo, e: GraphEdge) -> None:
+        sb = pri.stream_buffers.get(e.name) if e.is_streaming else None
+        if sb is not None:
+            for ti in e.tensor_info:
+                sb.put(ti.uuid, self.tensors.read(ti))
+            return
+        pri.walk_state.ingest(e)
+
+    def _poll_stream_buffers(self) -> None:
+        for pri in list(self.requests.values()):
+            for name, sb in pri.stream_buffers.items():
+                target = next((n for n, st in pri.walk_state.nodes.items()
+                               if name in st.decl.streaming_inputs and name not in st.cur and not st.running), None)
+                if target is None or not sb.has_chunk_ready():
+                    continue
+                st = pri.walk_state.nodes[target]
+                if not st.is_ready_for_streaming() or st.done:
+                    continue
+                chunk = sb.pop_chunk()
+                data = chunk.data["data"]
+                t = data if isinstance(data, torch.Tensor) else torch.zeros(0, dtype=torch.int64)
+                ti = self.tensors.store_and_return_tensor_info(pri.request_id, t)
+                edge = GraphEdge(target, name, [ti], is_streaming=True, final_stream_chunk=chunk.is_final)
+                pri.walk_state.ingest(edge)
+                pri.fwd_info.step_metadata = dict(pri.fwd_info.step_metadata or {}, chunk_index=chunk.chunk_index,
+                                                  chunk_start=chunk.start_offset, final_chunk=chunk.is_final)
+                self._refresh_ready(pri)
+
+    def _refresh_ready(self, pri: PerRequestInfo) -> None:
+        for n in pri.walk_state.ready_nodes(allow_streaming=False):
+            self.scheduler.mark_ready(n, pri.fwd_info.graph_walk, _rk(pri))
+
+    def _on_remove_request(self, b: ipc.RemoveRequest) -> None:
+        for key in [k for k in self.requests if k[0] == b.request_id]:
+            pri = self.requests[key]
+            if pri.in_flight:
+                pri.remove_pending = True       # deferred: a batch with this request is on the GPU
+                continue
+            self._drop(key)
+        if b.source == ipc.MessageSource.CONDUCTOR:
+            for f in self.tp_followers:
+                self.comm.send(f, Message(WM.REMOVE_REQUEST, ipc.RemoveRequest(b.request_id, ipc.MessageSource.TP_RANK_0)))
+
+    def _drop(self, key) -> None:
+        pri = self.requests.pop(key, None)
+        if pri is None:
+            return
+        self.scheduler.remove_request(_rk(pri))
+        pri.walk_state.clear()
+        if not any(k[0] == key[0] for k in self.requests):
+            self.engines.remove_request(key[0])
+            self.tensors.remove_request(key[0])
+
+    def _on_stop_loops(self, b: ipc.StopLoops) -> None:
+        pri = self.requests.get((b.request_id, b.partition_name))
+        if pri is not None:
+            for ln in b.loop_names:
+                pri.walk_state.stop_loop(ln)
+
+    def _release_edge(self, request_id: str, e: GraphEdge) -> None:
+        for ti in e.tensor_info:
+            if ti.source_entity == self.worker_id:
+                self.tensors.dereference(request_id, ti.uuid)
+
+    # ------------------------------------------------------------------ batches
+    def _build_node_batch(self, node: str, walk: str, rkeys: list[str]) -> NodeBatch | None:
+        inputs, infos, rids = {}, {}, []
+        for rk in rkeys:
+            rid, part = rk.split("|", 1)
+            pri = self.requests.get((rid, part))
+            if pri is None:
+                continue
+            ins = {}
+            for name, edge in pri.walk_state.inputs_of(node).items():
+                ins[name] = [self.tensors.read(ti) for ti in edge.tensor_info]
+            pri.walk_state.mark_running(node)
+            pri.in_flight += 1
+            inputs[rid] = ins
+            infos[rid] = pri.fwd_info
+            rids.append(rid)
+        if not rids:
+            return None
+        b = NodeBatch(node, walk, rids, inputs, infos)
+        b.partitions = {rk.split("|", 1)[0]: rk.split("|", 1)[1] for rk in rkeys}
+        return b
+
+    def _execute(self, batch: NodeBatch) -> NodeOutput:
+        eng = self.engines.engine_for(batch.node_name)
+        with nvtx_range(f"{batch.node_name}:{batch.graph_walk}:{len(batch.request_ids)}"):
+            t0 = time.perf_counter()
+            out = eng.execute_batch(batch)
+            out.timings["execute_s"] = time.perf_counter() - t0
+        return out
+
+    def _postprocess_batch(self, batch: NodeBatch, out: NodeOutput) -> None:
+        if out.completion_event is not None:
+            out.completion_event.synchronize()
+        if out.allocation_failed:
+            self._handle_allocation_failure(batch, out)
+            return
+        if out.failed_requests:
+            self._fail_requests(out.failed_requests)
+        for rid in batch.request_ids:
+            pri = self.requests.get((rid, batch.partitions[rid]))
+            if pri is None:
+                continue
+            pri.in_flight -= 1
+            if rid in out.failed_requests:
+                continue
+            try:
+                self._complete_node(pri, batch, out.outputs.get(rid, {}), out.stop_loops.get(rid, set()))
+            except Exception as e:  # noqa: BLE001
+                log.exception("worker %s: routing outputs of %s failed", self.worker_id, rid)
+                self._fail_requests({rid: f"{type(e).__name__}: {e}"})
+            if pri.remove_pending and pri.in_flight == 0:
+                self._drop((rid, pri.partition_name))
+
+    def _complete_node(self, pri: PerRequestInfo, batch: NodeBatch, tensors: dict, stops: set) -> None:
+        ws = pri.walk_state
+        node = batch.node_name
+        for ln in stops:
+            ws.stop_loop(ln)
+        if stops:
+            self._broadcast_stops(pri, stops)
+        decl = ws.nodes[node].decl
+        edges = []
+        for e in decl.outputs:
+            t = tensors.get(e.name)
+            if t is None:
+                continue
+            ne = e.clone(with_tensors=False)
+            refs = sum(1 for o in decl.outputs if o.name == e.name)
+            if not isinstance(t, (list, tuple)):
+                t = [t]
+            # tensors on their way to the client outlive the request's teardown: they are released by the API
+            # server's TENSOR_RECEIVED acknowledgement, not by REMOVE_REQUEST
+            owner = pri.request_id + "#emit" if e.next_node == EMIT_TO_CLIENT else pri.request_id
+            ne.tensor_info = [self.tensors.store_and_return_tensor_info(owner, x, refs=refs, persist=e.persist)
+                              for x in t if isinstance(x, torch.Tensor)]
+            edges.append(ne)
+            if e.conductor_new_token:
+                pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + 1
+        comp = ws.complete(node, edges)
+        self._send_outputs(pri, comp.route)
+        self._refresh_ready(pri)
+        if comp.walk_done:
+            self._walk_done(pri)
+
+    def _send_outputs(self, pri: PerRequestInfo, edges: list[GraphEdge]) -> None:
+        by_worker: dict[str, list[GraphEdge]] = {}
+        for e in edges:
+            if e.persist:
+                pri.persist.setdefault(e.name, []).extend(e.tensor_info)
+            if e.next_node == EMPTY_DESTINATION:
+                continue
+            if e.next_node == EMIT_TO_CLIENT:
+                infos = [self.tensors.prepare_for_remote(ti, self.api_id) for ti in e.tensor_info]
+                self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS,
+                                                    ipc.ResultTensors(pri.request_id, e.output_modality or "text", infos,
+                                                                      {"name": e.name, "partition": pri.partition_name},
+                                                                      self.worker_id)))
+                continue
+            for w in self.node_to_workers.get(e.next_node, []):
+                by_worker.setdefault(w, []).append(e)
+        for w, es in by_worker.items():
+            if w == self.worker_id:
+                for e in es:
+                    self._ingest(pri, e)
+                continue
+            out_edges = []
+            for e in es:
+                c = e.clone(with_tensors=False)
+                c.tensor_info = [self.tensors.prepare_for_remote(ti, w) for ti in e.tensor_info]
+                out_edges.append(c)
+            part = pri.partition_name
+            if self.topology is not None:
+                for c in self.topology.outgoing(pri.partition_name):
+                    if any(e.name == c.edge_name for e in out_edges):
+                        part = c.to_partition
+            self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(pri.request_id, out_edges, None, part)))
+
+    def _broadcast_stops(self, pri: PerRequestInfo, stops: set) -> None:
+        peers = {w for ws_ in pri.worker_graph_to_workers.values() for w in ws_ if w != self.worker_id}
+        for w in peers:
+            self.comm.send(w, Message(WM.STOP_LOOPS, ipc.StopLoops(pri.request_id, set(stops), pri.partition_name)))
+
+    def _walk_done(self, pri: PerRequestInfo) -> None:
+        seq = {}
+        for eng in self.engines.engines:
+            if hasattr(eng, "get_per_label_seq_info"):
+                seq.update(eng.get_per_label_seq_info(pri.request_id))
+        if not self.is_tp_follower:
+            self.comm.send(self.conductor_id, Message(CM.WORKER_GRAPHS_DONE, ipc.WorkerGraphsDone(
+                pri.request_id, list(pri.worker_graph_ids), True, dict(pri.persist), dict(pri.new_token_counts), seq,
+                pri.partition_name, False, {}, pri.walk_state.loop_indices(),
+                {"walk_s": time.perf_counter() - pri.t_start}, pri.fwd_info.graph_walk)))
+        pri.persist = {}
+        pri.new_token_counts = {}
+
+    # ------------------------------------------------------------------ failures
+    def _fail_requests(self, errors: dict[str, str]) -> None:
+        if not errors:
+            return
+        self.comm.send(self.conductor_id, Message(CM.FAIL_REQUESTS, ipc.FailRequests(dict(errors))))
+        for rid in errors:
+            for key in [k for k in self.requests if k[0] == rid]:
+                pri = self.requests[key]
+                if pri.in_flight:
+                    pri.remove_pending = True
+                else:
+                    self._drop(key)
+
+    def _handle_allocation_failure(self, batch: NodeBatch, out: NodeOutput) -> None:
+        """Unwind the batch; free pages by offloading the request that holds the most, else back off."""
+        eng = self.engines.engine_for(batch.node_name)
+        rkeys = []
+        for rid in batch.request_ids:
+            pri = self.requests.get((rid, batch.partitions[rid]))
+            if pri is None:
+                continue
+            pri.in_flight -= 1
+            st = pri.walk_state.nodes[batch.node_name]
+            st.running = False
+            rkeys.append(_rk(pri))
+        freed = 0
+        if eng.can_offload():
+            others = [k[0] for k in self.requests if k[0] not in batch.request_ids]
+            victim = max(others or batch.request_ids, key=lambda r: eng.pages_of(r), default=None)
+            if victim is not None:
+                freed = eng.offload_request(victim)
+        self.scheduler.hold(rkeys, 0.0 if freed else 0.05)
+        for rk in rkeys:
+            self.scheduler.mark_ready(batch.node_name, batch.graph_walk, rk)
+
+    # ------------------------------------------------------------------ main loop
+    def step(self, block_s: float = 0.0) -> bool:
+        """One iteration of the main loop; returns True when something happened."""
+        self.iterations += 1
+        did = False
+        msgs = self.comm.recv_or_wake(block_s) if block_s > 0 else self.comm.drain()
+        if msgs:
+            self._process_messages(msgs)
+            did = True
+        self._poll_stream_buffers()
+        if self._pending is not None:
+            fut, batch = self._pending
+            if fut.done():
+                self._pending = None
+                self._finish(batch, fut)
+                did = True
+        if self._pending is None:
+            nxt = self.scheduler.get_next_batch()
+            if nxt is not None:
+                node, walk, rkeys = nxt
+                batch = self._build_node_batch(node, walk, rkeys)
+                if batch is not None:
+                    if not self.is_tp_follower:
+                        for f in self.tp_followers:
+                            self.comm.send(f, Message(WM.SCHEDULE_TP, ipc.ScheduleTPNode(node, walk, list(rkeys))))
+                    if self.gpu_thread is not None:
+                        self._pending = (self.gpu_thread.submit(self._execute, batch), batch)
+                    else:
+                        self._finish(batch, None)
+                    did = True
+        if self.heartbeat_s and time.monotonic() - self._last_beat > self.heartbeat_s:
+            self._last_beat = time.monotonic()
+            self.comm.send(self.conductor_id, Message(CM.HEARTBEAT, ipc.SetupDone(self.worker_id)))
+        return did
+
+    def _finish(self, batch: NodeBatch, fut) -> None:
+        try:
+            out = fut.result() if fut is not None else self._execute(batch)
+            self._postprocess_batch(batch, out)
+        except Exception as e:  # noqa: BLE001
+            log.error("worker %s: batch %s failed: %s\n%s", self.worker_id, batch.node_name, e, traceback.format_exc())
+            for rid in batch.request_ids:
+                pri = self.requests.get((rid, batch.partitions[rid]))
+                if pri is not None:
+                    pri.in_flight = max(0, pri.in_flight - 1)
+            self._fail_requests({rid: f"{type(e).__name__}: {e}" for rid in batch.request_ids})
+
+    def run(self) -> None:
+        self.comm.send(self.conductor_id, Message(CM.SETUP_DONE, ipc.SetupDone(self.worker_id)))
+        while self.running:
+            if self._pending is not None:
+                # a batch is on the GPU thread: sleep on the mailbox in short slices instead of spinning on the GIL
+                self.step(block_s=0.0 if self._pending[0].done() else 0.0005)
+            else:
+                self.step(block_s=0.0 if self.scheduler.has_ready() else 0.02)
+        self.shutdown()
+
+    def shutdown(self) -> None:
+        if self.gpu_thread is not None:
+            self.gpu_thread.shutdown(wait=True)
+
+
+def _rk(pri: PerRequestInfo) -> str:
+    return f"{pri.request_id}|{pri.partition_name}"
+
+
+def _with_max_iters(loop, n: int):
+    import copy
+    c = copy.copy(loop)
+    c.max_iters = n
+    return c
