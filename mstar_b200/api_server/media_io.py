@@ -1,0 +1,129 @@
+"""Media helpers on the host: data-URL / base64 decoding, PCM16 <-> WAV (also open-ended streaming headers),
+tensors -> PNG, frames (+audio) -> MP4 through ffmpeg when it is installed.
+
+Reference counterpart: mstar/api_server/media_io.py (272 lines).
+"""
+from __future__ import annotations
+
+import base64
+import io
+import shutil
+import struct
+import subprocess
+import tempfile
+import wave
+
+import numpy as np
+import torch
+
+
+def decode_media_ref(ref: str, allow_remote: bool = False) -> tuple[bytes, str]:
+    """``data:<mime>;base64,<payload>`` or bare base64 -> (bytes, mime). Remote URLs only when allowed."""
+    if ref.startswith("data:"):
+        head, payload = ref.split(",", 1)
+        mime = head[5:].split(";")[0] or "application/octet-stream"
+        return base64.b64decode(payload), mime
+    if ref.startswith(("http://", "https://")):
+        if not allow_remote:
+            raise ValueError("remote media references are disabled (MSTAR_ALLOW_REMOTE)")
+        import requests
+        r = requests.get(ref, timeout=30)
+        r.raise_for_status()
+        return r.content, r.headers.get("content-type", "application/octet-stream")
+    return base64.b64decode(ref), "application/octet-stream"
+
+
+def ext_for_mime(mime: str) -> str:
+    return {"image/png": ".png", "image/jpeg": ".jpg", "image/webp": ".webp", "audio/wav": ".wav", "audio/x-wav": ".wav",
+            "audio/mpeg": ".mp3", "video/mp4": ".mp4"}.get(mime, ".bin")
+
+
+def wav_header(sample_rate: int, channels: int = 1, n_bytes: int | None = None) -> bytes:
+    """44-byte PCM16 WAV header. ``n_bytes=None`` writes the open-ended sizes used for streaming."""
+    data = 0xFFFFFFFF - 36 if n_bytes is None else n_bytes
+    riff = 0xFFFFFFFF if n_bytes is None else 36 + n_bytes
+    return (b"RIFF" + struct.pack("<I", riff) + b"WAVEfmt " + struct.pack("<IHHIIHH", 16, 1, channels, sample_rate,
+            sample_rate * channels * 2, channels * 2, 16) + b"data" + struct.pack("<I", data))
+
+
+def float_to_pcm16(x: torch.Tensor) -> bytes:
+    return (x.detach().float().clamp(-1, 1) * 32767.0).round().to(torch.int16).cpu().numpy().tobytes()
+
+
+def pcm16_to_wav(pcm: bytes, sample_rate: int, channels: int = 1) -> bytes:
+    return wav_header(sample_rate, channels, len(pcm)) + pcm
+
+
+def pcm16_to_container(pcm: bytes, sample_rate: int, fmt: str = "wav", channels: int = 1) -> tuple[bytes, str]:
+    fmt = (fmt or "wav").lower()
+    if fmt == "pcm":
+        return pcm, "audio/pcm"
+    if fmt == "wav":
+        return pcm16_to_wav(pcm, sample_rate, channels), "audio/wav"
+    if shutil.which("ffmpeg") is None:
+        raise ValueError(f"response_format {fmt!r} needs ffmpeg; use wav or pcm")
+    out = subprocess.run(["ffmpeg", "-loglevel", "error", "-f", "s16le", "-ar", str(sample_rate), "-ac", str(channels),
+                          "-i", "pipe:0", "-f", fmt, "pipe:1"], input=pcm, capture_output=True, check=True)
+    return out.stdout, {"mp3": "audio/mpeg", "flac": "audio/flac", "opus": "audio/opus", "aac": "audio/aac"}.get(fmt, "application/octet-stream")
+
+
+def read_wav(path_or_bytes) -> tuple[torch.Tensor, int]:
+    f = io.BytesIO(path_or_bytes) if isinstance(path_or_bytes, (bytes, bytearray)) else path_or_bytes
+    with wave.open(f, "rb") as w:
+        sr, ch, n = w.getframerate(), w.getnchannels(), w.getnframes()
+        raw = w.readframes(n)
+        width = w.getsampwidth()
+    if width != 2:
+        raise ValueError("only PCM16 WAV input is supported")
+    x = torch.from_numpy(np.frombuffer(raw, dtype=np.int16).astype(np.float32) / 32768.0)
+    if ch > 1:
+        x = x.reshape(-1, ch).mean(-1)
+    return x, sr
+
+
+def tensor_to_png(img: torch.Tensor) -> bytes:
+    """[3, H, W] or [H, W, 3]; float in [-1, 1] / [0, 1] or uint8."""
+    from PIL import Image
+    t = img.detach().cpu()
+    if t.dim() == 3 and t.shape[0] in (1, 3):
+        t = t.permute(1, 2, 0)
+    if t.dtype != torch.uint8:
+        t = t.float()
+        if t.min() < 0:
+            t = (t + 1) / 2
+        t = (t.clamp(0, 1) * 255).round().to(torch.uint8)
+    arr = t.numpy()
+    if arr.shape[-1] == 1:
+        arr = arr[..., 0]
+    buf = io.BytesIO()
+    Image.fromarray(arr).save(buf, format="PNG")
+    return buf.getvalue()
+
+
+def png_to_data_url(png: bytes) -> str:
+    return "data:image/png;base64," + base64.b64encode(png).decode()
+
+
+def frames_to_mp4(frames: torch.Tensor, fps: float = 24.0, audio_pcm: bytes | None = None, sample_rate: int = 24000,
+                  channels: int = 1) -> bytes:
+    """[T, 3, H, W] frames -> H.264 MP4 (optionally with AAC audio). Needs ffmpeg on the host."""
+    if shutil.which("ffmpeg") is None:
+        raise RuntimeError("ffmpeg is not installed: cannot encode MP4")
+    t = frames.detach().cpu()
+    if t.dtype != torch.uint8:
+        t = t.float()
+        if t.min() < 0:
+            t = (t + 1) / 2
+        t = (t.clamp(0, 1) * 255).round().to(torch.uint8)
+    T, C, H, W = t.shape
+    raw = t.permute(0, 2, 3, 1).contiguous().numpy().tobytes()
+    with tempfile.TemporaryDirectory() as d:
+        cmd = ["ffmpeg", "-loglevel", "error", "-y", "-f", "rawvideo", "-pix_fmt", "rgb24", "-s", f"{W}x{H}", "-r", str(fps),
+               "-i", f"{d}/v.raw"]
+        open(f"{d}/v.raw", "wb").write(raw)
+        if audio_pcm:
+            open(f"{d}/a.raw", "wb").write(audio_pcm)
+            cmd += ["-f", "s16le", "-ar", str(sample_rate), "-ac", str(channels), "-i", f"{d}/a.raw", "-c:a", "aac", "-shortest"]
+        cmd += ["-c:v", "libx264", "-pix_fmt", "yuv420p", f"{d}/out.mp4"]
+        subprocess.run(cmd, check=True, capture_output=True)
+        return open(f"{d}/out.mp4", "rb").read()
