@@ -53,6 +53,14 @@ struct GemmParams {
     unsigned long long wait_limit_ns;
     float out_scale;                // multiplies the accumulator before bias (1.0 by default)
     GemmAllReduce ar;
+    // grouped (mixture-of-experts) mode, decode layout only: the token rows (Q operand) are sorted by expert in
+    // blocks of BN rows; block b multiplies with expert block_expert[b], whose weight rows start at
+    // block_expert[b] * N in the stacked [E * N, K] weight. Blocks at or beyond *num_blocks do nothing.
+    const int* block_expert;
+    const int* num_blocks;
+    const float* row_scale;         // optional per-token-row factor (routing weight), applied to the output row
+    void* const* row_dst;           // optional per-token-row destination pointers (expert-parallel combine: the
+                                    // row is stored straight into its owner's buffer, possibly on a peer GPU)
 };
 
 constexpr int BM = 128;  // UMMA M (P-tile rows)
@@ -196,6 +204,27 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* s
 #pragma unroll
                 for (int j = 0; j < EPV; ++j) x[j] = gelu_tanh_f(x[j]);
             }
+        }
+        if (p.row_scale != nullptr) {
+            const float rs = p.row_scale[m];
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) x[j] *= rs;
+        }
+        if (p.row_dst != nullptr) {
+            // expert-parallel combine: the destination row may live on a peer GPU; 16-byte peer stores
+            if constexpr (!OUT_F32) {
+                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.row_dst[m]);
+                if (drow != nullptr) {
+                    if (full) {
+                        *reinterpret_cast<uint4*>(drow + n) = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]),
+                                                                           pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+                    } else {
+                        for (int j = 0; j < EPV; ++j)
+                            if (n + j < n_limit) drow[n + j] = __float2bfloat16(x[j]);
+                    }
+                }
+            }
+            continue;
         }
         if (p.residual != nullptr) {
             if (vec_ok && full) {
@@ -347,6 +376,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     if (kb_end > p.kblocks_total) kb_end = p.kblocks_total;
     const int nkb = kb_end - kb_begin;  // host guarantees >= 1
     pdl_launch_dependents();
+    int p_row0 = tile_p * BM;       // first row of this tile in the P operand
+    if (p.block_expert != nullptr) {
+        pdl_wait();
+        if (tile_q >= *p.num_blocks) return;
+        p_row0 += p.block_expert[tile_q] * p.N;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -380,7 +415,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             const int npre = p.swap ? (nkb < STAGES ? nkb : STAGES) : 0;
             for (int i = 0; i < npre; ++i) {
                 mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-                tma_load_2d(smem + i * STAGE_BYTES, &tmP, &full_bar[i], (kb_begin + i) * BK, tile_p * BM);
+                tma_load_2d(smem + i * STAGE_BYTES, &tmP, &full_bar[i], (kb_begin + i) * BK, p_row0);
             }
             pdl_wait();
             for (int i = 0; i < npre; ++i)
@@ -398,7 +433,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                 uint8_t* sp = smem + s * STAGE_BYTES;
                 mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                 const int kx = (kb_begin + i) * BK;
-                tma_load_2d(sp, &tmP, &full_bar[s], kx, tile_p * BM);
+                tma_load_2d(sp, &tmP, &full_bar[s], kx, p_row0);
                 tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kx, tile_q * BN);
                 issued = i + 1;
             }
@@ -649,6 +684,10 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     p.status = status_ptr();
     p.wait_limit_ns = wait_limit_ns();
     p.out_scale = out_scale;
+    p.block_expert = nullptr;
+    p.num_blocks = nullptr;
+    p.row_scale = nullptr;
+    p.row_dst = nullptr;
     p.ar = g_next_ar;
     g_next_ar.enabled = 0;
     if (p.ar.enabled) {
@@ -679,4 +718,54 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
         case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
     }
     return set_error("gemm: unsupported tile", cudaSuccess);
+}
+
+// Grouped GEMM for mixture-of-experts layers (decode layout): rows of A are token copies sorted by expert in
+// blocks of `block_rows` (16, 32, 64 or 128); block b uses expert block_expert[b]. W is the stacked expert
+// weight [E * N, K]. C row i is the result of A row i (same sorted order), or is scattered through row_dst.
+//   epilogue 1: SwiGLU over interleaved (gate, up) rows of each expert (C has N/2 columns)
+//   row_scale:  optional per-row factor (routing weight); row_dst: optional per-row destination pointers
+MSTAR_API int mstar_moe_grouped_gemm(const void* A, const void* W, void* C, int capacity_rows, int N, int K, int E,
+                                     int block_rows, const int* block_expert, const int* num_blocks,
+                                     const float* row_scale, void* const* row_dst, int epilogue, int ldc,
+                                     void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (capacity_rows <= 0) return 0;
+    if (block_rows != 16 && block_rows != 32 && block_rows != 64 && block_rows != 128)
+        return set_error("moe gemm: block_rows must be 16, 32, 64 or 128", cudaSuccess);
+    if (K % 8 || N % 8 || capacity_rows % block_rows)
+        return set_error("moe gemm: K and N must be multiples of 8, capacity a multiple of block_rows", cudaSuccess);
+    GemmParams p;
+    p.M = capacity_rows; p.N = N; p.K = K;
+    p.swap = 1;
+    p.splits = 1;
+    p.kblocks_total = (K + BK - 1) / BK;
+    p.kblocks_per_split = p.kblocks_total;
+    p.epilogue = epilogue;
+    p.out_f32 = 0;
+    p.ldc = ldc;
+    p.ld_res = 0;
+    p.C = C;
+    p.bias = nullptr;
+    p.residual = nullptr;
+    p.workspace = nullptr;
+    p.counters = nullptr;
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    p.out_scale = 1.0f;
+    p.ar = GemmAllReduce{};
+    p.block_expert = block_expert;
+    p.num_blocks = num_blocks;
+    p.row_scale = row_scale;
+    p.row_dst = row_dst;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_bf16(&tmP, W, E * N, K, K, BM, BK)) return -1;
+    if (make_tmap_2d_bf16(&tmQ, A, capacity_rows, K, K, block_rows, BK)) return -1;
+    dim3 grid((N + BM - 1) / BM, capacity_rows / block_rows, 1);
+    switch (block_rows) {
+        case 16: return launch_gemm<16, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 32: return launch_gemm<32, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
+        default: return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
+    }
 }
