@@ -68,6 +68,26 @@ def main():
             same = all(torch.equal(gathered[0], t) for t in gathered)
             check(f"gemm+allreduce M={M} N={N} K={K} it={it} err={err:.3g}", err < 0.06 * max(1.0, ref.abs().max().item()) and same)
 
+    # ---- expert parallel MoE: dispatch / grouped GEMM / fused combine vs the dense oracle ----
+    from types import SimpleNamespace
+    from mstar_b200.models.moe import SparseMoeBlock
+    from mstar_b200.ops import moe as moe_ops
+    from mstar_b200.parallel.comm import CommGroup
+    mcfg = SimpleNamespace(hidden_size=512, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256,
+                           shared_expert_intermediate_size=0, norm_topk_prob=True, dtype=torch.bfloat16)
+    blk = SparseMoeBlock(mcfg, CommGroup.trivial(), dev, ep=g)
+    gen = torch.Generator().manual_seed(5)
+    blk.init_random(gen, 0.05)
+    full = SparseMoeBlock(mcfg, CommGroup.trivial(), "cpu")
+    full.init_random(torch.Generator().manual_seed(5), 0.05)
+    for it, T in enumerate([24, 7, 24]):
+        gx = torch.Generator().manual_seed(50 + it)
+        xs = [torch.randn(T, 512, generator=gx).to(torch.bfloat16) for _ in range(W)]
+        y = blk(xs[R].to(dev))
+        ref = moe_ops.moe_ref(xs[R], full.router, full.w13, full.w2, 4)
+        err = (y.float().cpu() - ref.float()).abs().max().item()
+        check(f"ep moe T={T} it={it} err={err:.3g}", err < 3e-2 * max(1.0, ref.float().abs().max().item()))
+
     # ---- barrier ----
     for _ in range(5):
         heap.barrier()
