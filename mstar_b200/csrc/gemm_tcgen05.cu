@@ -769,3 +769,105 @@ MSTAR_API int mstar_moe_grouped_gemm(const void* A, const void* W, void* C, int 
         default: return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in mstar_noalloc.h): the split-K scratch is a device array inside this
+// library image instead of caller-provided memory.
+// ---------------------------------------------------------------------------------------------
+#include <stdio.h>
+#include "mstar_noalloc.h"
+
+namespace {
+
+struct NoAllocScratch {
+    float partials[MSTAR_NOALLOC_WORKSPACE_BYTES / sizeof(float)];
+    unsigned int counters[MSTAR_NOALLOC_MAX_TILES];
+};
+// In host code this name is only a handle for the runtime's symbol table, not a device address; the address that a
+// kernel may use comes from cudaGetSymbolAddress (below), once per device.
+static __device__ __align__(256) NoAllocScratch g_noalloc_scratch;
+
+constexpr int kMaxDevices = 64;
+static NoAllocScratch* g_noalloc_ptr[kMaxDevices] = {};
+
+}  // namespace
+
+MSTAR_API int mstar_gemm_bf16_noalloc(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                      int ldc, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+        return set_error("gemm_noalloc: operands must be 16-byte aligned with leading dimensions multiple of 8", cudaSuccess);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error("gemm_noalloc: cudaGetDevice failed", e);
+    if (dev < 0 || dev >= kMaxDevices) return set_error("gemm_noalloc: device index out of range", cudaSuccess);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // set-up, once per device, with that device current
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) return set_error("gemm_noalloc: cudaGetSymbolAddress failed", e);
+        g_noalloc_ptr[dev] = static_cast<NoAllocScratch*>(p);
+    }
+    NoAllocScratch* scratch = g_noalloc_ptr[dev];
+
+    int swap, bn, splits, tiles;
+    long long ws_need;
+    mstar_gemm_plan(M, N, K, &swap, &bn, &splits, &ws_need, &tiles);
+    if (ws_need > (long long)MSTAR_NOALLOC_WORKSPACE_BYTES) {
+        char msg[200];
+        snprintf(msg, sizeof(msg), "gemm_noalloc: this problem's split-K plan needs %lld scratch bytes, the built-in "
+                 "maximum is %u", ws_need, (unsigned)MSTAR_NOALLOC_WORKSPACE_BYTES);
+        return set_error(msg, cudaSuccess);
+    }
+    if (splits > 1 && tiles > MSTAR_NOALLOC_MAX_TILES)
+        return set_error("gemm_noalloc: more output tiles than built-in arrival counters", cudaSuccess);
+    if (splits > 1) {
+        // counters must start at zero even if an earlier call was cut short
+        e = cudaMemsetAsync(scratch->counters, 0, sizeof(unsigned int) * (size_t)tiles, stream);
+        if (e != cudaSuccess) return set_error("gemm_noalloc: clearing the counters failed", e);
+    }
+    const int kblocks = (K + BK - 1) / BK;
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.swap = swap;
+    p.splits = splits;
+    p.kblocks_total = kblocks;
+    p.kblocks_per_split = (kblocks + splits - 1) / splits;
+    p.epilogue = 0;
+    p.out_f32 = 0;
+    p.ldc = ldc;
+    p.ld_res = 0;
+    p.C = C;
+    p.bias = nullptr;
+    p.residual = nullptr;
+    p.workspace = scratch->partials;
+    p.counters = scratch->counters;
+    p.status = nullptr;              // the shared status word is heap-allocated; this path keeps its waits bounded
+                                     // but reports nothing
+    p.wait_limit_ns = wait_limit_ns();
+    p.out_scale = 1.0f;
+    p.ar = GemmAllReduce{};
+    p.block_expert = nullptr;
+    p.num_blocks = nullptr;
+    p.row_scale = nullptr;
+    p.row_dst = nullptr;
+    const void* Pp = swap ? B : A;
+    const void* Qp = swap ? A : B;
+    const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
+    const int ldP = swap ? ldb : lda, ldQ = swap ? lda : ldb;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_bf16(&tmP, Pp, rowsP, K, ldP, BM, BK)) return -1;
+    if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
+    dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
+    switch (bn) {
+        case 16: return launch_gemm<16, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 32: return launch_gemm<32, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
+        case 128:
+            if (swap) return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
+            return launch_gemm<128, 6, 1>(tmP, tmQ, p, grid, stream);
+        case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
+    }
+    return set_error("gemm_noalloc: unsupported tile", cudaSuccess);
+}
