@@ -231,10 +231,24 @@ class Conductor:
         fpa = self.model.get_partition_forward_pass_args(ps.name, md, ps.persist)
         if fpa is None or fpa.request_done or not fpa.graph_walk:
             ps.done = True
+            self._send_producer_done(rd, ps.name)
             if all(p.done for p in rd.partitions.values()):
                 self._process_request_done(rd)
             return
         self._launch_walk(rd, ps, fpa)
+
+    def _send_producer_done(self, rd: RequestData, partition: str) -> None:
+        """Tell the consumers of this partition's streams that no more items will come (final flush)."""
+        topo = self.model.get_partition_topology()
+        if topo is None:
+            return
+        n2w = self.node_to_workers(rd)
+        for c in topo.outgoing(partition):
+            walks = self.partitions[c.to_partition].graph_walks
+            consumers = {n for w in walks for n, decl in self.walks[w].nodes().items() if c.edge_name in decl.streaming_inputs}
+            for w in {w for n in consumers for w in n2w.get(n, [])}:
+                self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(rd.request_id, [], None, c.to_partition,
+                                                                             {c.edge_name})))
 
     def _process_request_done(self, rd: RequestData) -> None:
         self.stats["completed"] += 1

@@ -135,7 +135,9 @@ class WalkState:
             return False
         # remember inputs that cross into a loop from outside: they are delivered again every iteration
         sc = st.scope
-        while sc is not None and sc.loop is not None:
+        # (stream chunks are consumed once: each iteration gets a fresh chunk from the stream buffer)
+        streaming = edge.is_streaming or edge.name in st.decl.streaming_inputs
+        while sc is not None and sc.loop is not None and not streaming:
             if edge.key() in sc.loop.external_inputs and edge.key() not in sc.saved_inputs:
                 sc.saved_inputs[edge.key()] = edge
             sc = sc.parent

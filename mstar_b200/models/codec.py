@@ -1,0 +1,123 @@
+"""Neural audio codec decoders (SNAC-style multi-scale residual VQ, and a generic code-to-waveform stack).
+
+Convolutions run on cuDNN (the plan keeps codec / VAE convolutions on the library until profiling puts them on the
+critical path); the Snake activation and the code lookup are plain tensor ops.
+
+Reference counterparts: SNAC decoder (mstar/model/orpheus/components/snac.py, 424 lines: Snake1d :43, LocalMHA :106,
+ResidualUnit :140, NoiseBlock :175, DecoderBlock :189, Decoder :239, VectorQuantize :275), Code2Wav
+(mstar/model/qwen3_omni/components/code2wav.py).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+
+class Snake1d(nn.Module):
+    def __init__(self, channels: int):
+        super().__init__()
+        self.alpha = nn.Parameter(torch.ones(1, channels, 1))
+
+    def forward(self, x):
+        a = self.alpha
+        return x + (1.0 / (a + 1e-9)) * torch.sin(a * x).pow(2)
+
+
+class ResidualUnit(nn.Module):
+    def __init__(self, dim: int, dilation: int, kernel: int = 7):
+        super().__init__()
+        pad = (kernel - 1) * dilation // 2
+        self.block = nn.Sequential(Snake1d(dim), nn.Conv1d(dim, dim, kernel, dilation=dilation, padding=pad),
+                                   Snake1d(dim), nn.Conv1d(dim, dim, 1))
+
+    def forward(self, x):
+        return x + self.block(x)
+
+
+class DecoderBlock(nn.Module):
+    def __init__(self, cin: int, cout: int, stride: int, noise: bool = False):
+        super().__init__()
+        self.up = nn.Sequential(Snake1d(cin), nn.ConvTranspose1d(cin, cout, 2 * stride, stride=stride,
+                                                                 padding=math.ceil(stride / 2), output_padding=stride % 2))
+        self.noise = nn.Conv1d(cout, cout, 1, bias=False) if noise else None
+        self.res = nn.Sequential(ResidualUnit(cout, 1), ResidualUnit(cout, 3), ResidualUnit(cout, 9))
+
+    def forward(self, x, noise_gen: torch.Generator | None = None):
+        x = self.up(x)
+        if self.noise is not None:
+            n = torch.randn((x.shape[0], 1, x.shape[2]), device=x.device, dtype=x.dtype, generator=noise_gen)
+            x = x + n * self.noise(x)
+        return self.res(x)
+
+
+class SnacDecoder(nn.Module):
+    """Codes of 3 resolutions (1 / 2 / 4 per 7-token frame) -> 24 kHz waveform; 2048 samples per frame."""
+
+    def __init__(self, codebook_size: int = 4096, codebook_dim: int = 8, latent_dim: int = 768, channels: int = 1024,
+                 rates=(8, 8, 4, 2), vq_strides=(4, 2, 1), noise: bool = True):
+        super().__init__()
+        self.vq_strides = list(vq_strides)
+        self.codebook_size = codebook_size
+        self.codebooks = nn.ModuleList([nn.Embedding(codebook_size, codebook_dim) for _ in vq_strides])
+        self.out_proj = nn.ModuleList([nn.Conv1d(codebook_dim, latent_dim, 1) for _ in vq_strides])
+        self.inp = nn.Conv1d(latent_dim, channels, 7, padding=3)
+        blocks, c = [], channels
+        for r in rates:
+            blocks.append(DecoderBlock(c, c // 2, r, noise))
+            c //= 2
+        self.blocks = nn.ModuleList(blocks)
+        self.out = nn.Sequential(Snake1d(c), nn.Conv1d(c, 1, 7, padding=3), nn.Tanh())
+        self.hop = math.prod(rates)
+
+    def latent(self, codes: list[torch.Tensor]) -> torch.Tensor:
+        """codes[l]: [B, T_l] ints with T_l = T_fine / vq_stride[l]."""
+        z = 0
+        for emb, proj, s, c in zip(self.codebooks, self.out_proj, self.vq_strides, codes):
+            e = proj(emb(c.clamp(0, self.codebook_size - 1)).transpose(1, 2))
+            z = z + e.repeat_interleave(s, dim=-1)
+        return z
+
+    def forward(self, codes: list[torch.Tensor], noise_gen=None) -> torch.Tensor:
+        x = self.inp(self.latent(codes))
+        for b in self.blocks:
+            x = b(x, noise_gen)
+        return self.out(x)[:, 0]
+
+
+def orpheus_tokens_to_codes(tokens: torch.Tensor, base_id: int, codebook_size: int = 4096) -> list[torch.Tensor]:
+    """[B, 7 * F] LLM audio tokens -> SNAC code layers ([B,F], [B,2F], [B,4F]). Token at slot s of a frame carries
+    code = id - base - 10 - s * codebook_size; slots (0) / (1,4) / (2,3,5,6) feed the coarse / middle / fine layer."""
+    B, n = tokens.shape
+    Fr = n // 7
+    t = tokens[:, :Fr * 7].reshape(B, Fr, 7).long()
+    slot = torch.arange(7, device=tokens.device)
+    c = (t - base_id - 10 - slot * codebook_size) % codebook_size
+    return [c[:, :, 0], c[:, :, [1, 4]].reshape(B, -1), c[:, :, [2, 3, 5, 6]].reshape(B, -1)]
+
+
+class Code2Wav(nn.Module):
+    """Generic multi-codebook code -> waveform stack (sum of code embeddings, causal conv upsampler)."""
+
+    def __init__(self, n_codebooks: int = 16, codebook_size: int = 2048, dim: int = 512, rates=(8, 5, 4, 3),
+                 channels: int = 512):
+        super().__init__()
+        self.emb = nn.ModuleList([nn.Embedding(codebook_size, dim) for _ in range(n_codebooks)])
+        self.inp = nn.Conv1d(dim, channels, 7, padding=3)
+        blocks, c = [], channels
+        for r in rates:
+            blocks.append(DecoderBlock(c, max(32, c // 2), r, False))
+            c = max(32, c // 2)
+        self.blocks = nn.ModuleList(blocks)
+        self.out = nn.Sequential(Snake1d(c), nn.Conv1d(c, 1, 7, padding=3), nn.Tanh())
+        self.hop = math.prod(rates)
+
+    def forward(self, codes: torch.Tensor) -> torch.Tensor:
+        """codes [B, n_codebooks, T] -> [B, T * hop]."""
+        z = sum(e(codes[:, i].clamp(0, e.num_embeddings - 1)) for i, e in enumerate(self.emb)).transpose(1, 2)
+        x = self.inp(z)
+        for b in self.blocks:
+            x = b(x)
+        return self.out(x)[:, 0]

@@ -1,0 +1,179 @@
+"""Orpheus-3B TTS: Llama-3.2-3B backbone that emits audio tokens, and a SNAC-style codec decoder fed through a
+sliding-window stream (window 28 tokens = 4 frames, stride 7 = 1 frame); every chunk yields the second frame's
+2048 samples.
+
+Nodes: ``LLM`` (KV-cache engine, tensor-parallel capable), ``snac_decoder`` (stateless, audio_codec flavor, fp32).
+Partitions: ``llm`` (walks prefill, decode) -> ``codec`` (walk snac_chunk) over the streaming edge ``audio_tokens``.
+
+Reference counterparts: mstar/model/orpheus/orpheus_model.py (walks :111-167, partitions :173-203, state machine
+:205-281, TP defaults :406-409), submodules.py, components/{language_model,snac}.py, config.py.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..api_server.media_io import float_to_pcm16
+from ..engine.kv_store import KVCacheConfig
+from ..graph.ir import EMIT_TO_CLIENT, GraphEdge, GraphNode, Loop
+from ..streaming import Connection, PartitionDefinition, PartitionTopology, SlidingWindowChunkPolicy, StreamingGraphEdge
+from .base import EngineType, ForwardPassArgs, Model
+from .codec import SnacDecoder, orpheus_tokens_to_codes
+from .decoder import DecoderConfig, DecoderLM
+from .llm_common import DecoderSubmodule, LMStateMachine, lm_walks
+from .orpheus_config import orpheus_3b_config
+from .submodule_base import NodeSubmodule
+
+CUSTOM_TOKEN_BASE = 128256
+END_TOKEN_IDS = (128009, 128260, 128261, 128257, 128258)
+VOICES = ["tara", "zoe", "zac", "jess", "leo", "mia", "julia", "leah"]
+
+
+class SnacSubmodule(NodeSubmodule):
+    def __init__(self, device, base_id: int, small: bool):
+        super().__init__(device, torch.float32)
+        kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
+        self.dec = SnacDecoder(**kw).to(device=device, dtype=torch.float32).eval()
+        self.base_id = base_id
+        self.gen = None
+
+    def get_stateless_flavor(self):
+        return "audio_codec"
+
+    def forward(self, graph_walk, engine_inputs, ni, **kw):
+        toks = ni.tensor_inputs.get("audio_tokens", [])
+        t = torch.cat([x.reshape(-1) for x in toks]) if toks else torch.zeros(0, dtype=torch.int64)
+        md = ni.kwargs
+        n = (t.numel() // 7) * 7
+        if n == 0:
+            return {"audio": torch.zeros(0), "final": bool(md.get("final_chunk"))}
+        codes = orpheus_tokens_to_codes(t[:n].reshape(1, n).to(self.device), self.base_id)
+        with torch.no_grad():
+            wav = self.dec(codes)[0]
+        frames = n // 7
+        # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows yield all
+        out = wav[2048:4096] if frames == 4 and not md.get("final_chunk") else wav
+        return {"audio": out.float().cpu(), "final": bool(md.get("final_chunk"))}
+
+    def postprocess(self, request_id, request_info, outputs, inputs):
+        return {"audio": outputs["audio"]}
+
+    def check_stop(self, request_id, request_info, outputs):
+        return {"snac_loop"} if outputs.get("final") or (request_info.step_metadata or {}).get("final_chunk") else set()
+
+
+class OrpheusModel(Model):
+    name = "orpheus"
+
+    def __init__(self, model_dir=None, skip_weight_loading=False, small: bool = False, page_size: int = 128,
+                 max_num_pages: int = 2048, **kw):
+        super().__init__(model_dir, skip_weight_loading, **kw)
+        self.small = small
+        if small:      # test-sized backbone with the real vocabulary layout
+            self.cfg = DecoderConfig(hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
+                                     intermediate_size=256, vocab_size=156940, rms_eps=1e-5, rope_theta=5e5,
+                                     tie_embeddings=True,
+                                     dtype=torch.bfloat16 if torch.cuda.is_available() else torch.float32)
+        else:
+            self.cfg = orpheus_3b_config()
+        self.page_size, self.max_num_pages = page_size, max_num_pages
+        self.sm = LMStateMachine()
+
+    # ---- structure ----
+    def get_graph_walk_graphs(self):
+        stream = StreamingGraphEdge("snac_decoder", "audio_tokens", target_partition="codec")
+        walks = lm_walks(modality="", stream_edge=stream)
+        snac = GraphNode("snac_decoder", {"audio_tokens"},
+                         [GraphEdge(EMIT_TO_CLIENT, "audio", output_modality="audio")], streaming_inputs={"audio_tokens"})
+        walks["snac_chunk"] = Loop(snac, max_iters=1 << 20, name="snac_loop")
+        return walks
+
+    def get_node_engine_types(self):
+        return {"LLM": EngineType.KV_CACHE, "snac_decoder": EngineType.STATELESS}
+
+    def get_partition_topology(self):
+        return PartitionTopology(["llm", "codec"], [Connection("llm", "codec", "audio_tokens",
+                                                               lambda: SlidingWindowChunkPolicy(28, 7))])
+
+    def get_partitions(self):
+        return [PartitionDefinition("llm", ["prefill", "decode"], "prefill"),
+                PartitionDefinition("codec", ["snac_chunk"], "snac_chunk", ["llm"])]
+
+    def get_kv_cache_config(self):
+        c = self.cfg
+        return [KVCacheConfig(c.num_layers, c.num_kv_heads, c.head_dim, max_seq_len=8192 if self.small else 131072,
+                              max_num_pages=self.max_num_pages, page_size=self.page_size, num_qo_heads=c.num_heads,
+                              nodes=["LLM"], dtype=c.dtype)]
+
+    def get_default_sharding_config(self):
+        return {"LLM": {"tp": True, "sp": False}}
+
+    def get_engine_hints(self, node):
+        c = self.cfg
+        return dict(vocab_size=c.vocab_size, group=c.num_heads // c.num_kv_heads, max_tokens=16384, track_seen=True)
+
+    def get_autocast_dtype(self):
+        return self.cfg.dtype
+
+    def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
+        if node_name == "LLM":
+            lm = DecoderLM(self.cfg, tp=tp_group, device=device)
+            if self.skip_weight_loading:
+                lm.init_random(0)
+            else:
+                from .loader import load_decoder_from_hf
+                load_decoder_from_hf(lm, self.model_dir)
+            return DecoderSubmodule(lm, device, eos_ids=END_TOKEN_IDS, token_edge="audio_tokens")
+        if node_name == "snac_decoder":
+            return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small)
+        raise KeyError(node_name)
+
+    # ---- request life cycle ----
+    def get_sampling_config(self, model_kwargs):
+        mk = dict(model_kwargs)
+        mk.setdefault("temperature", 0.6)
+        mk.setdefault("top_p", 0.8)
+        mk.setdefault("repetition_penalty", 1.3)
+        return super().get_sampling_config(mk)
+
+    def get_max_output_tokens(self, model_kwargs=None):
+        return int((model_kwargs or {}).get("max_tokens", 4096))
+
+    def process_prompt(self, prompt, input_modalities, output_modalities, tensors, voice: str = "tara", **kw):
+        text = f"{voice}: {prompt or ''}"
+        tok = self._tokenizer()
+        if tok is not None:
+            ids = tok(text)["input_ids"]
+        else:
+            parts = (prompt or "").split()
+            ids = [int(p) for p in parts] if parts and all(p.isdigit() for p in parts) else list(text.encode("utf-8"))
+        ids = [128259] + [i % self.cfg.vocab_size for i in ids] + [128009, 128260]
+        return {"input_ids": [torch.tensor(ids, dtype=torch.int64)]}
+
+    def _tokenizer(self):
+        if self.model_dir is None:
+            return None
+        if not hasattr(self, "_tok"):
+            try:
+                from transformers import AutoTokenizer
+                self._tok = AutoTokenizer.from_pretrained(self.model_dir)
+            except Exception:  # noqa: BLE001
+                self._tok = None
+        return self._tok
+
+    def get_initial_forward_pass_args(self, partition_name, input_modalities, output_modalities, input_signals,
+                                      model_kwargs):
+        if partition_name == "codec":
+            return ForwardPassArgs({"graph_walk": "snac_chunk"}, [])
+        return self.sm.initial(input_signals, self.get_max_output_tokens(model_kwargs))
+
+    def get_partition_forward_pass_args(self, partition_name, partition_metadata, persist_signals,
+                                        incoming_connections=None):
+        if partition_name == "codec":
+            return ForwardPassArgs(request_done=True)
+        return self.sm.next(partition_metadata, persist_signals)
+
+    def postprocess(self, output, modality, request_kwargs):
+        if modality == "audio":
+            return float_to_pcm16(output if isinstance(output, torch.Tensor) else torch.cat(list(output)))
+        ids = output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output)
+        return (" ".join(str(int(i)) for i in ids) + " ").encode()

@@ -1,0 +1,38 @@
+"""Orpheus-class TTS through the serving stack on CPU with a test-sized backbone: LLM partition streams audio
+tokens into the codec partition in sliding windows (28 / 7); audio chunks come back as PCM16."""
+import pytest
+
+from mstar_b200.api_server.server import APIServer
+
+CFG = {"model": "orpheus", "model_kwargs": {"small": True, "page_size": 16, "max_num_pages": 256},
+       "use_cuda_graphs": False,
+       "node_groups": [{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill", "decode"]},
+                       {"node_names": ["snac_decoder"], "ranks": [1], "graph_walks": ["snac_chunk"]}]}
+
+
+@pytest.fixture(scope="module")
+def server():
+    s = APIServer(CFG, in_process=True).start(120)
+    yield s
+    s.shutdown()
+
+
+def test_tts_streams_audio_chunks(server):
+    n_tokens = 7 * 9      # 9 frames
+    rid = server.submit_request("hello there", output_modalities=["audio"],
+                                model_kwargs=dict(max_tokens=n_tokens, ignore_eos=True, voice="leo"))
+    chunks = list(server.iter_result_chunks(rid, 300))
+    assert chunks and all(c.modality == "audio" for c in chunks), [c.modality for c in chunks][:5]
+    # windows: the first full window appears after 28 tokens, then one per frame, then the flush
+    sizes = [len(c.data) // 2 for c in chunks]
+    assert sizes.count(2048) >= 5
+    assert sum(sizes) >= 2048 * 6
+    assert server.deployment.conductor.stats["completed"] >= 1
+
+
+def test_two_requests_share_the_codec_worker(server):
+    rids = [server.submit_request(f"req {i}", output_modalities=["audio"],
+                                  model_kwargs=dict(max_tokens=35, ignore_eos=True)) for i in range(2)]
+    for rid in rids:
+        res = server.collect_results(rid, 300)
+        assert "error" not in res and len(res["audio"]) >= 2
