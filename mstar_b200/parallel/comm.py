@@ -44,10 +44,10 @@ class CommGroup:
         if self.size == 1:
             return x
         x = x.contiguous()
-        out = torch.empty((self.size, *x.shape), dtype=x.dtype, device=x.device)
+        out = torch.empty((self.size * x.shape[0], *x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x, group=self.group)
         dim = dim % x.dim()
-        return torch.cat(list(out.unbind(0)), dim=dim) if dim != 0 else out.reshape(-1, *x.shape[1:])
+        return torch.cat(list(out.chunk(self.size, 0)), dim=dim) if dim != 0 else out
 
     def reduce_scatter(self, x: torch.Tensor, dim: int = 0) -> torch.Tensor:
         if self.size == 1:
@@ -56,7 +56,12 @@ class CommGroup:
             x = x.transpose(0, dim)
         x = x.contiguous()
         out = torch.empty((x.shape[0] // self.size, *x.shape[1:]), dtype=x.dtype, device=x.device)
-        dist.reduce_scatter_tensor(out, x, group=self.group)
+        if x.is_cuda:
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+        else:       # gloo has no reduce-scatter
+            full = x.clone()
+            dist.all_reduce(full, group=self.group)
+            out.copy_(full.chunk(self.size, 0)[self.rank])
         return out.transpose(0, dim) if dim != 0 else out
 
     def broadcast(self, x: torch.Tensor, src: int = 0) -> torch.Tensor:

@@ -1,0 +1,55 @@
+"""CPU (gloo) ranks: CommGroup wrappers, Ulysses exchange fallback, TP decoder == single-rank decoder."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from mstar_b200.parallel.comm import init_from_env  # noqa: E402
+from mstar_b200.parallel.sequence_parallel import UlyssesExchange, gather_sequence, scatter_sequence  # noqa: E402
+
+
+def main():
+    g = init_from_env("gloo")
+    W, R = g.size, g.rank
+    x = torch.full((4,), float(R + 1))
+    assert g.all_reduce(x.clone()).tolist() == [3.0] * 4
+    assert g.all_gather(torch.tensor([float(R)]), 0).tolist() == [0.0, 1.0]
+    rs = g.reduce_scatter(torch.arange(4.0) + R)
+    assert rs.tolist() == ([1.0, 3.0] if R == 0 else [5.0, 7.0])
+    a2a = g.all_to_all(torch.tensor([10.0 * R, 10.0 * R + 1]))
+    assert a2a.tolist() == [0.0 + R, 10.0 + R]
+    # sequence scatter / gather with an uneven split
+    gen = torch.Generator().manual_seed(0)
+    full = torch.randn(7, 4, 8, generator=gen)
+    mine = scatter_sequence(full, g)
+    assert torch.equal(gather_sequence(mine, g, 7), full)
+    ex = UlyssesExchange(g, 7, 4, 4, 8, torch.float32)
+    q, k, v = ex.to_heads(mine, mine * 2, mine * 3)
+    assert torch.equal(q, full[:, R * 2:(R + 1) * 2]) and torch.equal(v, 3 * full[:, R * 2:(R + 1) * 2])
+    back = ex.to_sequence(q)
+    assert torch.equal(back, mine)
+    # tensor-parallel tiny decoder: both ranks produce the single-rank logits
+    from mstar_b200.engine.cache_manager import BatchedCacheManager
+    from mstar_b200.engine.kv_store import KVCacheConfig
+    from mstar_b200.models import tiny
+    ref_model = tiny.build_tiny()
+    tp_model = tiny.build_tiny(tp=g)
+    ids = torch.randint(0, 32000, (11,), generator=gen)
+
+    def logits(m, kvh):
+        kvc = KVCacheConfig(2, kvh, 64, max_seq_len=64, max_num_pages=8, page_size=16, num_qo_heads=4, dtype=torch.float32)
+        cm = BatchedCacheManager(kvc, "cpu", max_batch=2, max_tokens=64)
+        cm.add_request("r")
+        ctx = cm.plan(["r"], [11])
+        return m(ctx, input_ids=ids)
+    a, b = logits(ref_model, 2), logits(tp_model, 1)
+    assert (a - b).abs().max().item() < 1e-3, (a - b).abs().max().item()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
