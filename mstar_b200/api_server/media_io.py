@@ -127,3 +127,77 @@ def frames_to_mp4(frames: torch.Tensor, fps: float = 24.0, audio_pcm: bytes | No
         cmd += ["-c:v", "libx264", "-pix_fmt", "yuv420p", f"{d}/out.mp4"]
         subprocess.run(cmd, check=True, capture_output=True)
         return open(f"{d}/out.mp4", "rb").read()
+
+
+def _to_uint8_frames(frames: torch.Tensor) -> torch.Tensor:
+    t = frames.detach().cpu()
+    if t.dtype != torch.uint8:
+        t = t.float()
+        if t.min() < 0:
+            t = (t + 1) / 2
+        t = (t.clamp(0, 1) * 255).round().to(torch.uint8)
+    return t
+
+
+def frames_to_avi(frames: torch.Tensor, fps: float = 24.0, audio_pcm: bytes | None = None, sample_rate: int = 24000,
+                  channels: int = 1, quality: int = 90) -> bytes:
+    """[T, 3, H, W] frames -> Motion-JPEG AVI (optionally with one PCM16 audio stream), written here: the
+    container needs no external encoder. Audio is interleaved one block per frame."""
+    import struct
+
+    from PIL import Image
+    t = _to_uint8_frames(frames)
+    T, C, H, W = t.shape
+    arr = t.permute(0, 2, 3, 1).contiguous().numpy()
+    jpgs = []
+    for i in range(T):
+        buf = io.BytesIO()
+        Image.fromarray(arr[i]).save(buf, format="JPEG", quality=quality)
+        jpgs.append(buf.getvalue())
+
+    def chunk(cc: bytes, data: bytes) -> bytes:
+        return cc + struct.pack("<I", len(data)) + data + (b"\x00" if len(data) & 1 else b"")
+
+    def lst(kind: bytes, data: bytes) -> bytes:
+        return b"LIST" + struct.pack("<I", len(data) + 4) + kind + data
+
+    usec = int(round(1e6 / fps))
+    n_streams = 2 if audio_pcm else 1
+    max_jpg = max(len(j) for j in jpgs)
+    avih = struct.pack("<IIIIIIIIIIIIII", usec, int(max_jpg * fps), 0, 0x10, T, 0, n_streams, max_jpg, W, H, 0, 0, 0, 0)
+    scale = 1000
+    strh_v = struct.pack("<4s4sIHHIIIIIIIIhhhh", b"vids", b"MJPG", 0, 0, 0, 0, scale, int(round(fps * scale)), 0, T,
+                         max_jpg, 0xFFFFFFFF, 0, 0, 0, W, H)
+    strf_v = struct.pack("<IiiHH4sIiiII", 40, W, H, 1, 24, b"MJPG", W * H * 3, 0, 0, 0, 0)
+    hdrl = chunk(b"avih", avih) + lst(b"strl", chunk(b"strh", strh_v) + chunk(b"strf", strf_v))
+    blocks = []
+    if audio_pcm:
+        bps = 2 * channels
+        n_samples = len(audio_pcm) // bps
+        strh_a = struct.pack("<4s4sIHHIIIIIIIIhhhh", b"auds", b"\x01\x00\x00\x00", 0, 0, 0, 0, 1, sample_rate, 0,
+                             n_samples, sample_rate * bps, 0xFFFFFFFF, bps, 0, 0, 0, 0)
+        strf_a = struct.pack("<HHIIHH", 1, channels, sample_rate, sample_rate * bps, bps, 16)
+        hdrl += lst(b"strl", chunk(b"strh", strh_a) + chunk(b"strf", strf_a))
+        per = (n_samples + T - 1) // T * bps
+        blocks = [audio_pcm[i * per:(i + 1) * per] for i in range(T)]
+    movi, idx, off = b"", b"", 4
+    for i, j in enumerate(jpgs):
+        c = chunk(b"00dc", j)
+        idx += struct.pack("<4sIII", b"00dc", 0x10, off, len(j))
+        movi += c
+        off += len(c)
+        if blocks and blocks[i]:
+            c = chunk(b"01wb", blocks[i])
+            idx += struct.pack("<4sIII", b"01wb", 0x10, off, len(blocks[i]))
+            movi += c
+            off += len(c)
+    body = b"AVI " + lst(b"hdrl", hdrl) + lst(b"movi", movi) + chunk(b"idx1", idx)
+    return b"RIFF" + struct.pack("<I", len(body)) + body
+
+
+def frames_to_video(frames: torch.Tensor, fps: float = 24.0, audio_pcm: bytes | None = None,
+                    sample_rate: int = 24000, channels: int = 1) -> tuple[bytes, str]:
+    """(bytes, mime): H.264 MP4 when ffmpeg is on the host, else Motion-JPEG AVI."""
+    if shutil.which("ffmpeg") is not None:
+        return frames_to_mp4(frames, fps, audio_pcm, sample_rate, channels), "video/mp4"
+    return frames_to_avi(frames, fps, audio_pcm, sample_rate, channels), "video/x-msvideo"

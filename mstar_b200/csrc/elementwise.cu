@@ -343,19 +343,68 @@ __global__ void embed_gather_kernel(const long long* ids, const __nv_bfloat16* t
     }
 }
 
-// out = x + gate[row / rows_per_mod] * y      (gated residual of AdaLN blocks); gate may be null (plain add)
+// out = x + gate[row / rows_per_mod] * y      (gated residual of AdaLN blocks); gate may be null (plain add).
+// Eight bf16 per thread (16-byte loads and stores); hidden must be a multiple of 8.
 __global__ void gated_residual_kernel(const __nv_bfloat16* x, const __nv_bfloat16* y, const __nv_bfloat16* gate,
                                       __nv_bfloat16* out, long long rows, int hidden, int rows_per_mod,
                                       long long gate_stride) {
     pdl_launch_dependents();
     pdl_wait();
-    const long long n = rows * (long long)hidden;
+    const int hv = hidden >> 3;
+    const long long n = rows * (long long)hv;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < n;
          idx += (long long)gridDim.x * blockDim.x) {
-        const long long r = idx / hidden;
-        const int i = (int)(idx - r * hidden);
-        float g = gate ? __bfloat162float(gate[(r / rows_per_mod) * gate_stride + i]) : 1.0f;
-        out[idx] = __float2bfloat16(__bfloat162float(x[idx]) + g * __bfloat162float(y[idx]));
+        const long long r = idx / hv;
+        const int i = (int)(idx - r * hv) << 3;
+        const uint4 xv = *reinterpret_cast<const uint4*>(x + r * hidden + i);
+        const uint4 yv = *reinterpret_cast<const uint4*>(y + r * hidden + i);
+        uint4 gv = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);   // bf16 ones
+        if (gate) gv = *reinterpret_cast<const uint4*>(gate + (r / rows_per_mod) * gate_stride + i);
+        const uint32_t* xa = &xv.x; const uint32_t* ya = &yv.x; const uint32_t* ga = &gv.x;
+        uint4 ov; uint32_t* oa = &ov.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 xf = unpack_bf16x2(xa[j]), yf = unpack_bf16x2(ya[j]), gf = unpack_bf16x2(ga[j]);
+            oa[j] = pack_bf16x2(xf.x + gf.x * yf.x, xf.y + gf.y * yf.y);
+        }
+        *reinterpret_cast<uint4*>(out + r * hidden + i) = ov;
+    }
+}
+
+// Merge two partial attention results over disjoint key sets (a cached prefix and the fresh tokens):
+//   w_i = exp(lse_i - max) / sum, out = w_a * o_a + w_b * o_b.  lse = -inf marks an empty key set.
+// o_*: [rows = tokens * heads, D] bf16 with row stride D, lse_*: [rows] fp32. Optionally writes the merged lse.
+__global__ void attn_merge_kernel(const __nv_bfloat16* oa, const float* la, const __nv_bfloat16* ob, const float* lb,
+                                  __nv_bfloat16* out, float* lse_out, long long rows, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int dv = D >> 3;
+    const long long n = rows * (long long)dv;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < n;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / dv;
+        const int i = (int)(idx - r * dv) << 3;
+        const float a = la[r], b = lb[r];
+        const float m = fmaxf(a, b);
+        float wa = 0.f, wb = 0.f;
+        if (m > -INFINITY) {
+            const float ea = __expf(a - m), eb = __expf(b - m);
+            const float inv = 1.0f / (ea + eb);
+            wa = ea * inv; wb = eb * inv;
+            if (lse_out && i == 0) lse_out[r] = m + __logf(ea + eb);
+        } else if (lse_out && i == 0) {
+            lse_out[r] = -INFINITY;
+        }
+        const uint4 av = *reinterpret_cast<const uint4*>(oa + r * D + i);
+        const uint4 bv = *reinterpret_cast<const uint4*>(ob + r * D + i);
+        const uint32_t* aa = &av.x; const uint32_t* ba = &bv.x;
+        uint4 ov; uint32_t* o = &ov.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 af = unpack_bf16x2(aa[j]), bf = unpack_bf16x2(ba[j]);
+            o[j] = pack_bf16x2(wa * af.x + wb * bf.x, wa * af.y + wb * bf.y);
+        }
+        *reinterpret_cast<uint4*>(out + r * D + i) = ov;
     }
 }
 
@@ -514,11 +563,22 @@ MSTAR_API int mstar_embed_gather(const long long* ids, const void* table, void* 
 MSTAR_API int mstar_gated_residual(const void* x, const void* y, const void* gate, void* out, long long rows,
                                    int hidden, int rows_per_mod, long long gate_stride, void* stream_) {
     if (rows <= 0) return 0;
-    gated_residual_kernel<<<grid_for(rows * hidden, 256), 256, 0, (cudaStream_t)stream_>>>(
+    if (hidden % 8) return set_error("gated_residual: hidden must be a multiple of 8", cudaSuccess);
+    gated_residual_kernel<<<grid_for(rows * (hidden / 8), 256), 256, 0, (cudaStream_t)stream_>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, rows,
         hidden, rows_per_mod > 0 ? rows_per_mod : 1, gate_stride);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : set_error("gated_residual launch", e);
+}
+
+MSTAR_API int mstar_attn_merge(const void* oa, const float* la, const void* ob, const float* lb, void* out,
+                               float* lse_out, long long rows, int D, void* stream_) {
+    if (rows <= 0) return 0;
+    if (D % 8) return set_error("attn_merge: head dim must be a multiple of 8", cudaSuccess);
+    attn_merge_kernel<<<grid_for(rows * (D / 8), 256), 256, 0, (cudaStream_t)stream_>>>(
+        (const __nv_bfloat16*)oa, la, (const __nv_bfloat16*)ob, lb, (__nv_bfloat16*)out, lse_out, rows, D);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : set_error("attn_merge launch", e);
 }
 
 MSTAR_API int mstar_cfg_combine(const float* v_cond, const float* v_uncond, const float* v_img, const float* x,

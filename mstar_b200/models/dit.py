@@ -1,0 +1,352 @@
+"""Diffusion-transformer family. Two block styles share the kernels:
+
+``AdaLNDiT`` (Wan2.2-class): LayerNorm without affine + (shift, scale, gate) modulation from the timestep
+embedding, bidirectional self-attention with full-width q/k RMSNorm and 3-axis rotary embedding, cross-attention to
+a fixed text context (its K/V are projected once per request), GELU MLP. Classifier-free guidance runs as a batch
+of two sequences.
+
+``MoTGenTower`` (Cosmos3 / BAGEL-class "mixture of transformers"): a second set of decoder weights (the
+generation expert) that runs over the noisy latent tokens and attends to [cached prefix ‖ fresh tokens]; the
+prefix K/V were written to the paged pool by the understanding tower's prefill, the fresh K/V never enter the
+pool. The two key sets are attended separately (paged kernel, dense kernel) and merged by their log-sum-exps.
+Tensor parallel (column / row sharded projections) and Ulysses sequence parallel (rows sharded, heads exchanged
+around attention over the symmetric heap) compose as a [sp][tp] mesh.
+
+Fused on the GPU: norm + modulation in one kernel, q/k norm + rotary + K/V layout in one kernel, bias / GELU /
+SwiGLU / residual in the GEMM epilogue, gate * y + x in one kernel.
+
+Reference counterparts: Wan2.2 DiT (mstar/model/wan22/components/dit.py:225-364: block :225-274, rope :100-140,
+head :276-300), Cosmos3 transformer (mstar/model/cosmos3/components/transformer.py: forward_gen :372-382,
+timestep scatter-add :483-499, patchify :501-562, _sp_run_gen_layers :831-859, denoise_step_batched_cfg
+:943-1037), BAGEL MoT split (mstar/model/bagel/components/language_model.py:58-84).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+
+from ..ops import attention as attn_ops
+from ..ops import elementwise as ew_ops
+from ..ops import gemm
+from ..ops import norm as norm_ops
+from ..ops import rope as rope_ops
+from ..parallel.comm import CommGroup
+from ..parallel.sequence_parallel import UlyssesExchange
+from .decoder import DecoderConfig, _param, tp_reduce
+
+
+# ------------------------------------------------------------------ shared helpers
+def sinusoidal_embedding(t: torch.Tensor, dim: int, max_period: float = 10000.0) -> torch.Tensor:
+    """fp32 [n, dim]: cos half then sin half (the diffusers / Wan convention)."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    ang = t.float().reshape(-1, 1) * freqs[None]
+    return torch.cat([torch.cos(ang), torch.sin(ang)], dim=-1)
+
+
+def rope_axes_tables(head_dim: int, axes_dims: tuple[int, ...] | None, theta: float, device):
+    """inv_freq [D/2] fp32 and axis_of_freq [D/2] int8 for a rotary embedding whose frequency bands belong to
+    different position axes (t, h, w). Every axis gets its own geometric ladder over its own width."""
+    if not axes_dims:
+        return rope_ops.make_inv_freq(head_dim, theta, device), None
+    assert sum(axes_dims) == head_dim and all(d % 2 == 0 for d in axes_dims)
+    inv, ax = [], []
+    for a, d in enumerate(axes_dims):
+        inv.append(1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d)))
+        ax += [a] * (d // 2)
+    return torch.cat(inv).to(device), torch.tensor(ax, dtype=torch.int8, device=device)
+
+
+def grid_positions(F: int, H: int, W: int, device, offset: tuple[int, int, int] = (0, 0, 0)) -> torch.Tensor:
+    """int32 [3, F*H*W] (t, h, w) coordinates of a row-major latent token grid."""
+    t = torch.arange(F, dtype=torch.int32, device=device) + offset[0]
+    h = torch.arange(H, dtype=torch.int32, device=device) + offset[1]
+    w = torch.arange(W, dtype=torch.int32, device=device) + offset[2]
+    g = torch.stack(torch.meshgrid(t, h, w, indexing="ij"), dim=0)
+    return g.reshape(3, -1).contiguous()
+
+
+def patchify(x: torch.Tensor, patch: tuple[int, int, int]) -> tuple[torch.Tensor, tuple[int, int, int]]:
+    """[C, F, H, W] -> ([F' H' W', C pt ph pw], (F', H', W'))."""
+    C, F, H, W = x.shape
+    pt, ph, pw = patch
+    Fp, Hp, Wp = F // pt, H // ph, W // pw
+    x = x.reshape(C, Fp, pt, Hp, ph, Wp, pw).permute(1, 3, 5, 0, 2, 4, 6)
+    return x.reshape(Fp * Hp * Wp, C * pt * ph * pw).contiguous(), (Fp, Hp, Wp)
+
+
+def unpatchify(tok: torch.Tensor, grid: tuple[int, int, int], patch: tuple[int, int, int], C: int) -> torch.Tensor:
+    """[F' H' W', pt ph pw C] -> [C, F, H, W] (channel is the fastest index of a token, as the heads emit it)."""
+    Fp, Hp, Wp = grid
+    pt, ph, pw = patch
+    x = tok.reshape(Fp, Hp, Wp, pt, ph, pw, C).permute(6, 0, 3, 1, 4, 2, 5)
+    return x.reshape(C, Fp * pt, Hp * ph, Wp * pw).contiguous()
+
+
+def row_parallel(x, w, tp: CommGroup, bias=None, residual=None):
+    """sum over the TP group of x_shard @ w_shard.T, + bias, + residual (both fused when there is one rank)."""
+    if tp.size == 1:
+        return gemm.linear(x, w, bias=bias, residual=residual)
+    y = gemm.linear(x, w, bias=bias if tp.rank == 0 else None)
+    if tp.symm is not None and y.is_cuda:
+        return tp.symm.all_reduce(y.contiguous(), residual=residual)
+    y = tp.all_reduce(y)
+    return y if residual is None else (y.float() + residual.float()).to(y.dtype)
+
+
+@dataclass
+class DiTConfig:
+    hidden_size: int = 3072
+    num_layers: int = 30
+    num_heads: int = 24
+    head_dim: int = 128
+    ffn_dim: int = 14336
+    in_channels: int = 48
+    out_channels: int = 48
+    patch_size: tuple[int, int, int] = (1, 2, 2)
+    text_dim: int = 4096
+    text_len: int = 512
+    freq_dim: int = 256
+    rope_theta: float = 10000.0
+    eps: float = 1e-6
+    dtype: torch.dtype = torch.bfloat16
+    rope_axes: tuple[int, ...] = field(default_factory=tuple)     # () -> derived from head_dim (Wan split)
+
+    def axes(self) -> tuple[int, int, int]:
+        if self.rope_axes:
+            return tuple(self.rope_axes)
+        d = self.head_dim
+        return (d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6))
+
+
+def wan22_5b_config() -> DiTConfig:
+    return DiTConfig()
+
+
+# ------------------------------------------------------------------ AdaLN DiT (Wan2.2-class)
+class AdaLNBlock(nn.Module):
+    def __init__(self, cfg: DiTConfig, device):
+        super().__init__()
+        H, Fd, dt = cfg.hidden_size, cfg.ffn_dim, cfg.dtype
+        self.cfg = cfg
+        self.modulation = _param((6, H), torch.float32, device)
+        self.qkv_w, self.qkv_b = _param((3 * H, H), dt, device), _param((3 * H,), dt, device)
+        self.norm_q, self.norm_k = _param((H,), dt, device), _param((H,), dt, device)
+        self.o_w, self.o_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.norm3_w, self.norm3_b = _param((H,), dt, device), _param((H,), dt, device)
+        self.cq_w, self.cq_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.ckv_w, self.ckv_b = _param((2 * H, H), dt, device), _param((2 * H,), dt, device)
+        self.cnorm_q, self.cnorm_k = _param((H,), dt, device), _param((H,), dt, device)
+        self.co_w, self.co_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.ffn1_w, self.ffn1_b = _param((Fd, H), dt, device), _param((Fd,), dt, device)
+        self.ffn2_w, self.ffn2_b = _param((H, Fd), dt, device), _param((H,), dt, device)
+
+    def project_context(self, ctx: torch.Tensor):
+        """K/V of the text context for this block: [L_total, heads, D] each (done once per request)."""
+        c = self.cfg
+        kv = gemm.linear(ctx, self.ckv_w, bias=self.ckv_b)
+        H = c.hidden_size
+        k, _ = norm_ops.norm(kv[:, :H], self.cnorm_k, c.eps)
+        return (k.reshape(-1, c.num_heads, c.head_dim).contiguous(),
+                kv[:, H:].reshape(-1, c.num_heads, c.head_dim).contiguous())
+
+    def forward(self, x, mod, positions, rope, self_plan, cross_plan, ctx_kv):
+        """x: [T, H]; mod: [n_mod, 6, H] bf16 = modulation + timestep projection; T rows split evenly over n_mod."""
+        c = self.cfg
+        H, nh, D = c.hidden_size, c.num_heads, c.head_dim
+        inv_freq, axis = rope
+        # self-attention
+        h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 1], shift=mod[:, 0])
+        qkv = gemm.linear(h, self.qkv_w, bias=self.qkv_b)
+        norm_ops.norm(qkv[:, :H], self.norm_q, c.eps, out=qkv[:, :H])
+        norm_ops.norm(qkv[:, H:2 * H], self.norm_k, c.eps, out=qkv[:, H:2 * H])
+        q, k, v = rope_ops.rope_kv(qkv, positions, inv_freq, nh, nh, D, axis_of_freq=axis, interleaved=True,
+                                   dense_kv=True)
+        a = attn_ops.attention(q, self_plan, k=k, v=v)
+        y = gemm.linear(a.reshape(-1, H), self.o_w, bias=self.o_b)
+        x = ew_ops.gated_residual(x, y, mod[:, 2])
+        # cross-attention to the text context
+        h, _ = norm_ops.norm(x, self.norm3_w, c.eps, layernorm=True, bias=self.norm3_b)
+        q = gemm.linear(h, self.cq_w, bias=self.cq_b)
+        q, _ = norm_ops.norm(q, self.cnorm_q, c.eps)
+        a = attn_ops.attention(q.reshape(-1, nh, D), cross_plan, k=ctx_kv[0], v=ctx_kv[1])
+        x = gemm.linear(a.reshape(-1, H), self.co_w, bias=self.co_b, residual=x)
+        # MLP
+        h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 4], shift=mod[:, 3])
+        h = gemm.linear(h, self.ffn1_w, bias=self.ffn1_b, epilogue=gemm.EPILOGUE_GELU)
+        y = gemm.linear(h, self.ffn2_w, bias=self.ffn2_b)
+        return ew_ops.gated_residual(x, y, mod[:, 5])
+
+
+class AdaLNDiT(nn.Module):
+    def __init__(self, cfg: DiTConfig, device="cpu"):
+        super().__init__()
+        self.cfg, self.device = cfg, torch.device(device)
+        H, dt = cfg.hidden_size, cfg.dtype
+        pdim = cfg.in_channels * math.prod(cfg.patch_size)
+        self.patch_w, self.patch_b = _param((H, pdim), dt, device), _param((H,), dt, device)
+        self.text1_w, self.text1_b = _param((H, cfg.text_dim), dt, device), _param((H,), dt, device)
+        self.text2_w, self.text2_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.time1_w, self.time1_b = _param((H, cfg.freq_dim), dt, device), _param((H,), dt, device)
+        self.time2_w, self.time2_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.tproj_w, self.tproj_b = _param((6 * H, H), dt, device), _param((6 * H,), dt, device)
+        self.blocks = nn.ModuleList([AdaLNBlock(cfg, device) for _ in range(cfg.num_layers)])
+        self.head_mod = _param((2, H), torch.float32, device)
+        odim = cfg.out_channels * math.prod(cfg.patch_size)
+        self.head_w, self.head_b = _param((odim, H), dt, device), _param((odim,), dt, device)
+        self.rope = rope_axes_tables(cfg.head_dim, cfg.axes(), cfg.rope_theta, self.device)
+
+    def init_random(self, seed: int = 0) -> "AdaLNDiT":
+        g = torch.Generator().manual_seed(seed)
+        for n, p in self.named_parameters():
+            if "norm" in n and n.endswith(("_q", "_k", "3_w")):
+                p.data.fill_(1.0)
+            elif p.dim() == 1:
+                p.data.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+            elif "modulation" in n or "head_mod" in n:
+                p.data.copy_((torch.randn(p.shape, generator=g) * 0.1).to(p.dtype))
+            else:
+                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
+        return self
+
+    # -- once per request --
+    def encode_context(self, text_emb: torch.Tensor):
+        """text_emb: [L_total, text_dim] (all guidance branches packed) -> per-block (K, V)."""
+        c = gemm.linear(text_emb.to(self.cfg.dtype), self.text1_w, bias=self.text1_b, epilogue=gemm.EPILOGUE_GELU)
+        c = gemm.linear(c, self.text2_w, bias=self.text2_b)
+        return [blk.project_context(c) for blk in self.blocks]
+
+    # -- one denoising forward --
+    def forward(self, latents: torch.Tensor, timesteps: torch.Tensor, ctx_kv: list, ctx_lens: list[int]):
+        """latents: [B, C, F, H, W] (B guidance branches / requests of one shape); timesteps: [B] or [B, F'] (one
+        per latent frame: image-to-video keeps the first frame at t = 0). Returns the model output, same shape,
+        fp32."""
+        cfg = self.cfg
+        B = latents.shape[0]
+        toks, grid = [], None
+        for b in range(B):
+            t, grid = patchify(latents[b], cfg.patch_size)
+            toks.append(t)
+        S = toks[0].shape[0]
+        x = gemm.linear(torch.cat(toks).to(cfg.dtype), self.patch_w, bias=self.patch_b)
+        ts = timesteps.reshape(B, -1)
+        n_per = ts.shape[1]
+        assert S % n_per == 0
+        e = sinusoidal_embedding(ts.reshape(-1), cfg.freq_dim).to(cfg.dtype)
+        e = gemm.linear(e, self.time1_w, bias=self.time1_b)
+        e = gemm.linear(torch.nn.functional.silu(e.float()).to(cfg.dtype), self.time2_w, bias=self.time2_b)
+        e6 = gemm.linear(torch.nn.functional.silu(e.float()).to(cfg.dtype), self.tproj_w, bias=self.tproj_b,
+                         out_dtype=torch.float32).reshape(B * n_per, 6, cfg.hidden_size)
+        pos = grid_positions(*grid, self.device).repeat(1, B)
+        G = 1
+        self_plan = attn_ops.dense_plan([S] * B, [S] * B, G, self.device, causal=False)
+        cross_plan = attn_ops.dense_plan([S] * B, ctx_lens, G, self.device, causal=False)
+        for i, blk in enumerate(self.blocks):
+            mod = (blk.modulation.float()[None] + e6).to(cfg.dtype)
+            x = blk(x, mod, pos, self.rope, self_plan, cross_plan, ctx_kv[i])
+        hm = (self.head_mod.float()[None] + e.float().reshape(B * n_per, 1, -1)).to(cfg.dtype)
+        h, _ = norm_ops.norm(x, None, cfg.eps, layernorm=True, scale=hm[:, 1], shift=hm[:, 0])
+        out = gemm.linear(h, self.head_w, bias=self.head_b, out_dtype=torch.float32)
+        return torch.stack([unpatchify(out[b * S:(b + 1) * S], grid, cfg.patch_size, cfg.out_channels)
+                            for b in range(B)])
+
+
+# ------------------------------------------------------------------ generation expert of a mixture of transformers
+class MoTGenLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int, tp: CommGroup, device):
+        super().__init__()
+        self.cfg, self.layer_idx, self.tp = cfg, layer_idx, tp
+        H, D = cfg.hidden_size, cfg.head_dim
+        self.Hq, self.Hkv = cfg.num_heads // tp.size, max(1, cfg.num_kv_heads // tp.size)
+        self.F = cfg.intermediate_size // tp.size
+        dt = cfg.dtype
+        self.input_norm = _param((H,), dt, device)
+        self.qkv_proj = _param(((self.Hq + 2 * self.Hkv) * D, H), dt, device)
+        self.qkv_bias = _param(((self.Hq + 2 * self.Hkv) * D,), dt, device) if cfg.qkv_bias else None
+        self.q_norm = _param((D,), dt, device) if cfg.qk_norm else None
+        self.k_norm = _param((D,), dt, device) if cfg.qk_norm else None
+        self.o_proj = _param((H, self.Hq * D), dt, device)
+        self.post_norm = _param((H,), dt, device)
+        self.gate_up_proj = _param((2 * self.F, H), dt, device)
+        self.down_proj = _param((H, self.F), dt, device)
+
+
+class MoTGenTower(nn.Module):
+    """Generation-expert weights with the shape of the understanding decoder ``cfg``. ``forward`` runs the noisy
+    tokens of a batch of (request, guidance branch) entries; every entry has the same number of tokens."""
+
+    def __init__(self, cfg: DecoderConfig, tp: CommGroup | None = None, sp: CommGroup | None = None, device="cpu",
+                 rope_axes: tuple[int, ...] | None = None):
+        super().__init__()
+        self.cfg = cfg
+        self.tp = tp or CommGroup.trivial()
+        self.sp = sp or CommGroup.trivial()
+        self.device = torch.device(device)
+        self.layers = nn.ModuleList([MoTGenLayer(cfg, i, self.tp, device) for i in range(cfg.num_layers)])
+        self.final_norm = _param((cfg.hidden_size,), cfg.dtype, device)
+        if rope_axes is None and cfg.mrope_sections:
+            self.inv_freq = rope_ops.make_inv_freq(cfg.head_dim, cfg.rope_theta, self.device)
+            self.axis_of_freq = rope_ops.mrope_axis_table(cfg.mrope_sections, cfg.mrope_interleaved).to(self.device)
+        else:
+            self.inv_freq, self.axis_of_freq = rope_axes_tables(cfg.head_dim, rope_axes, cfg.rope_theta, self.device)
+        self._exchange: dict[tuple, UlyssesExchange] = {}
+
+    def init_random(self, seed: int = 1) -> "MoTGenTower":
+        g = torch.Generator().manual_seed(seed)
+        for n, p in self.named_parameters():
+            if "norm" in n:
+                p.data.fill_(1.0)
+            elif p.dim() == 1:
+                p.data.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+            else:
+                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
+        return self
+
+    def exchange(self, S_total: int) -> UlyssesExchange:
+        key = (S_total,)
+        ex = self._exchange.get(key)
+        if ex is None:
+            l0 = self.layers[0]
+            ex = UlyssesExchange(self.sp, S_total, l0.Hq, l0.Hkv, self.cfg.head_dim, self.cfg.dtype)
+            self._exchange[key] = ex
+        return ex
+
+    def forward(self, x: torch.Tensor, positions: torch.Tensor, self_plan, *, prefix_ctx=None,
+                S_total: int | None = None) -> torch.Tensor:
+        """x: [T_local, H] rows of this sequence-parallel rank (all rows when sp = 1); positions: int32
+        [axes, T_local]; self_plan: dense bidirectional plan over the FULL packed sequence (S_total rows);
+        prefix_ctx: BatchContext planned with ``write_cache=False, causal=False`` over the cached prefixes (its
+        q rows are the full packed sequence too), or None when no entry has a prefix."""
+        cfg = self.cfg
+        D = cfg.head_dim
+        sp = self.sp.size > 1
+        S_total = S_total if S_total is not None else x.shape[0]
+        ex = self.exchange(S_total) if sp else None
+        residual = None
+        for li, L in enumerate(self.layers):
+            h, residual = (norm_ops.norm(x, L.input_norm, cfg.rms_eps) if residual is None
+                           else norm_ops.norm(x, L.input_norm, cfg.rms_eps, residual=residual))
+            if residual is None:
+                residual = x.clone()      # the residual stream is updated in place; keep the caller's tensor
+            qkv = gemm.linear(h, L.qkv_proj, bias=L.qkv_bias)
+            q, k, v = rope_ops.rope_kv(qkv, positions, self.inv_freq, L.Hq, L.Hkv, D, axis_of_freq=self.axis_of_freq,
+                                       q_norm_w=L.q_norm, k_norm_w=L.k_norm, norm_eps=cfg.rms_eps, dense_kv=True)
+            if sp:
+                q, k, v = ex.to_heads(q, k, v)
+            if prefix_ctx is not None:
+                o_f, l_f = attn_ops.attention(q, self_plan, k=k, v=v, lse=True)
+                o_p, l_p = attn_ops.attention(q, prefix_ctx.plan, kv_cache=prefix_ctx.kv(li), lse=True)
+                a = attn_ops.attn_merge(o_p, l_p, o_f, l_f)
+            else:
+                a = attn_ops.attention(q, self_plan, k=k, v=v)
+            if sp:
+                a = ex.to_sequence(a)
+            x = row_parallel(a.reshape(a.shape[0], -1), L.o_proj, self.tp)
+            h, residual = norm_ops.norm(x, L.post_norm, cfg.rms_eps, residual=residual)
+            g = gemm.linear(h, L.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
+            x = row_parallel(g, L.down_proj, self.tp)
+        h, _ = norm_ops.norm(x, self.final_norm, cfg.rms_eps, residual=residual)
+        return h

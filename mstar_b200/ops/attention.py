@@ -187,3 +187,33 @@ def dense_plan(q_lens, kv_lens, group: int, device, causal: bool = False, window
                     kv_lens=torch.tensor(list(kv_lens), dtype=torch.int32, device=device),
                     kv_indptr=torch.tensor(ki, dtype=torch.int32, device=device), batch=len(q_lens),
                     num_q_tokens=qi[-1], num_q_tiles=count_q_tiles(q_lens, group), causal=causal, window=window)
+
+
+def attn_merge_ref(o_a, lse_a, o_b, lse_b):
+    m = torch.maximum(lse_a, lse_b)
+    safe = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    ea, eb = torch.exp(lse_a - safe), torch.exp(lse_b - safe)
+    den = (ea + eb).clamp_min(1e-38)
+    out = o_a.float() * (ea / den)[..., None] + o_b.float() * (eb / den)[..., None]
+    return out.to(o_a.dtype), torch.where(torch.isfinite(m), safe + torch.log(den), m)
+
+
+def attn_merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
+               out: torch.Tensor | None = None, lse: bool = False):
+    """Combine attention over two disjoint key sets (cached prefix | fresh tokens) from their outputs [T, H, D]
+    and log-sum-exps [T, H]. Reference counterpart: the dense-gen path concatenates prefix and fresh K/V before
+    one attention call (mstar/engine/cache_manager.py:1455-1485); here the prefix stays paged."""
+    if not _lib.use_cuda(o_a):
+        o, l = attn_merge_ref(o_a, lse_a, o_b, lse_b)
+        return (o, l) if lse else o
+    T, H, D = o_a.shape
+    assert o_a.is_contiguous() and o_b.is_contiguous() and lse_a.is_contiguous() and lse_b.is_contiguous()
+    if out is None:
+        out = torch.empty_like(o_a)
+    lse_t = torch.empty_like(lse_a) if lse else None
+    rc = _lib.kernels().mstar_attn_merge(
+        ctypes.c_void_p(o_a.data_ptr()), ctypes.c_void_p(lse_a.data_ptr()), ctypes.c_void_p(o_b.data_ptr()),
+        ctypes.c_void_p(lse_b.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(_lib.ptr(lse_t)),
+        ctypes.c_longlong(T * H), int(D), ctypes.c_void_p(_lib.stream_ptr()))
+    _lib.check(rc, "mstar_attn_merge")
+    return (out, lse_t) if lse else out

@@ -54,6 +54,9 @@ def norm(x: torch.Tensor, weight: torch.Tensor | None = None, eps: float = 1e-6,
         if residual is not None:
             residual.copy_(nr)
             nr = residual
+        if out is not None:
+            out.copy_(y.reshape(out.shape))
+            y = out
         return y, nr
     assert x.dtype == torch.bfloat16
     hidden = x.shape[-1]
