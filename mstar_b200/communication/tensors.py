@@ -64,6 +64,25 @@ class TensorStore:
                 return True
         return False
 
+    def adopt(self, uuid: str, owner: str, extra_refs: int = 1) -> bool:
+        """Move a tensor to another owner and add references (a tensor that became a client result after it was
+        stored as an intermediate must outlive the request's teardown)."""
+        with self._lock:
+            if uuid not in self._t:
+                return False
+            for s in self._by_request.values():
+                s.discard(uuid)
+            self._by_request.setdefault(owner, set()).add(uuid)
+            self._ref[uuid] = max(0, self._ref.get(uuid, 0)) + extra_refs
+            return True
+
+    def owner_of(self, uuid: str) -> str | None:
+        with self._lock:
+            for o, s in self._by_request.items():
+                if uuid in s:
+                    return o
+        return None
+
     def unpersist(self, uuid: str) -> None:
         with self._lock:
             self._persist.discard(uuid)

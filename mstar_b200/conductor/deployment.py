@@ -68,16 +68,24 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
     par = [wg for wg in mine if wg.tp_size * wg.sp_size > 1]
     if par and dist_init:
         groups = WorkerParallelGroups(rank, world)
+        def instance_tp_major(w):
+            # all ranks of the instance, tensor-parallel index slowest: shard i of a weight cut tp*sp ways is the
+            # sp-th part of tensor-parallel shard t (the head order that Ulysses produces inside a TP shard)
+            return tuple(w.ranks[s * w.tp_size + t] for t in range(w.tp_size) for s in range(w.sp_size))
         tuples = sorted({tuple(wg.tp_ranks(r)) for wg in wgs for r in wg.ranks} |
-                        {tuple(wg.sp_ranks(r)) for wg in wgs for r in wg.ranks})
+                        {tuple(wg.sp_ranks(r)) for wg in wgs for r in wg.ranks} |
+                        {instance_tp_major(wg) for wg in wgs if wg.tp_size > 1 and wg.sp_size > 1})
         groups.init_dist(dist_init, all_rank_tuples=[t for t in tuples if len(t) > 1])
         wg = par[0]
         tp_group = groups.group_for(wg.tp_ranks(rank))
         sp_group = groups.group_for(wg.sp_ranks(rank))
+        inst = (groups.group_for(instance_tp_major(wg)) if wg.tp_size > 1 and wg.sp_size > 1
+                else (tp_group if wg.sp_size == 1 else sp_group))
+        tp_group.instance = sp_group.instance = inst
         if device.type == "cuda":
             from ..parallel.symm import attach_symmetric_heap
-            for g in (tp_group, sp_group):
-                if g.size > 1:
+            for g in {id(x): x for x in (tp_group, sp_group, inst)}.values():
+                if g.size > 1 and g.symm is None:
                     attach_symmetric_heap(g, device)
     tensors = TensorCommunicationManager(worker_id_of(rank), device, arena_prefix=prefix)
     kv = cfg.get("kv_cache", {}) or {}
@@ -90,9 +98,10 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
                 n2w.setdefault(n, [])
                 if worker_id_of(r) not in n2w[n]:
                     n2w[n].append(worker_id_of(r))
-    leader_of = {r: wg.tp_ranks(r)[0] for wg in mine for r in wg.ranks if wg.tp_size > 1}
-    followers = [worker_id_of(r) for wg in mine if wg.tp_size > 1 and wg.tp_ranks(rank)[0] == rank
-                 for r in wg.tp_ranks(rank)[1:]]
+    # the ranks of one model instance (tp x sp) run every batch in lockstep behind the instance's first rank
+    leader_of = {r: wg.ranks[0] for wg in mine for r in wg.ranks if wg.tp_size * wg.sp_size > 1}
+    followers = [worker_id_of(r) for wg in mine if wg.tp_size * wg.sp_size > 1 and wg.ranks[0] == rank
+                 for r in wg.ranks[1:]]
     is_follower = rank in leader_of and leader_of[rank] != rank
     return Worker(worker_id_of(rank), rank, model, node_names, comm, tensors, em, node_to_workers=n2w,
                   tp_followers=followers, is_tp_follower=is_follower, max_batch_size=int(cfg.get("max_batch_size", 64)),

@@ -93,6 +93,11 @@ class KVCacheEngine(BaseEngine):
     def plan(self, prepared: PreparedBatch):
         b = prepared.batch
         sub = self.submodules[b.node_name]
+        if hasattr(sub, "custom_plan"):
+            # nodes that plan their own entries (several cache labels per request, reads without writes, ...)
+            prepared.ctx = sub.custom_plan(self.cache, b.graph_walk, prepared)
+            prepared.bucket, prepared.q_lens = None, list(prepared.ctx.q_lens)
+            return prepared
         q_lens = [max(1, ni.input_seq_len) for ni in prepared.node_inputs]
         labels = [sub.get_needed_cache_labels(b.graph_walk, b.fwd_infos[r])[0] for r in prepared.request_ids]
         slots = [self.sampler.slot(r) for r in prepared.request_ids]
@@ -150,7 +155,11 @@ class KVCacheEngine(BaseEngine):
             else:
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 outs = sub.forward_batched(b.graph_walk, ei, planned.node_inputs)
-                raw = {"extra": {k: v for k, v in outs.items() if k != BATCHED_LOGITS}}
+                if isinstance(outs, list):           # one dict per request, no sampling
+                    raw = {"per_request": outs}
+                    outs = {}
+                else:
+                    raw = {"extra": {k: v for k, v in outs.items() if k != BATCHED_LOGITS}}
                 if BATCHED_LOGITS in outs:
                     lg = outs[BATCHED_LOGITS]
                     if lg.dtype not in (torch.float32, torch.bfloat16):
@@ -201,8 +210,11 @@ class KVCacheEngine(BaseEngine):
         host_tokens = tokens.tolist() if tokens is not None else None      # one D2H read per step
         for i, (rid, ni) in enumerate(zip(planned.request_ids, planned.node_inputs)):
             try:
-                r = {k: (v[i] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == len(planned.request_ids) else v)
-                     for k, v in raw.get("extra", {}).items()}
+                if "per_request" in raw:
+                    r = dict(raw["per_request"][i])
+                else:
+                    r = {k: (v[i] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == len(planned.request_ids) else v)
+                         for k, v in raw.get("extra", {}).items()}
                 if tokens is not None:
                     r["new_token"] = tokens[i:i + 1]
                     r["new_token_host"] = host_tokens[i]

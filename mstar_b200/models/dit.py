@@ -294,15 +294,31 @@ class MoTGenTower(nn.Module):
             self.inv_freq, self.axis_of_freq = rope_axes_tables(cfg.head_dim, rope_axes, cfg.rope_theta, self.device)
         self._exchange: dict[tuple, UlyssesExchange] = {}
 
+    @torch.no_grad()
     def init_random(self, seed: int = 1) -> "MoTGenTower":
+        """Every rank draws the full tensors from the same generator and keeps its tensor-parallel slice."""
+        from .decoder import shard_qkv
         g = torch.Generator().manual_seed(seed)
-        for n, p in self.named_parameters():
-            if "norm" in n:
-                p.data.fill_(1.0)
-            elif p.dim() == 1:
-                p.data.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
-            else:
-                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
+        c, tp = self.cfg, self.tp
+        H, D, Hq, Hkv, Fi = c.hidden_size, c.head_dim, c.num_heads, c.num_kv_heads, c.intermediate_size
+
+        def draw(shape, fan):
+            return torch.randn(shape, generator=g) / math.sqrt(fan)
+        for L in self.layers:
+            q, k, v = draw((Hq * D, H), H), draw((Hkv * D, H), H), draw((Hkv * D, H), H)
+            L.qkv_proj.copy_(shard_qkv(q, k, v, Hq, Hkv, D, tp.rank, tp.size).to(c.dtype))
+            if L.qkv_bias is not None:
+                L.qkv_bias.zero_()
+            o = draw((H, Hq * D), Hq * D)
+            L.o_proj.copy_(o[:, tp.rank * L.Hq * D:(tp.rank + 1) * L.Hq * D].to(c.dtype))
+            gt, up, dn = draw((Fi, H), H), draw((Fi, H), H), draw((H, Fi), Fi)
+            sl = slice(tp.rank * L.F, (tp.rank + 1) * L.F)
+            L.gate_up_proj.copy_(gemm.interleave_gate_up(gt[sl], up[sl]).to(c.dtype))
+            L.down_proj.copy_(dn[:, sl].to(c.dtype))
+            for n in (L.input_norm, L.post_norm, L.q_norm, L.k_norm):
+                if n is not None:
+                    n.fill_(1.0)
+        self.final_norm.fill_(1.0)
         return self
 
     def exchange(self, S_total: int) -> UlyssesExchange:

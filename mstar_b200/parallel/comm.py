@@ -26,6 +26,7 @@ class CommGroup:
         self.size = len(self.ranks)
         self.rank = self.ranks.index(rank) if rank in self.ranks else 0
         self.symm = None   # SymmetricHeap attached by parallel.symm when available
+        self.instance = None   # group over all tp x sp ranks of the model instance (tensor-parallel index slowest)
 
     @classmethod
     def trivial(cls) -> "CommGroup":

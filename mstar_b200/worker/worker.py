@@ -316,6 +316,10 @@ class Worker:
             if e.next_node == EMPTY_DESTINATION:
                 continue
             if e.next_node == EMIT_TO_CLIENT:
+                emit_owner = pri.request_id + "#emit"
+                for ti in e.tensor_info:        # a loop's last output was stored as an intermediate: re-own it
+                    if self.tensors.store.owner_of(ti.uuid) not in (None, emit_owner):
+                        self.tensors.store.adopt(ti.uuid, emit_owner)
                 infos = [self.tensors.prepare_for_remote(ti, self.api_id) for ti in e.tensor_info]
                 self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS,
                                                     ipc.ResultTensors(pri.request_id, e.output_modality or "text", infos,

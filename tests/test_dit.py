@@ -165,3 +165,44 @@ def test_wan22_text_to_video_and_image_to_video(wan_server):
     c = wan_server.collect_results(wan_server.submit_request(
         "a red fox", output_modalities=["video"], model_kwargs=kw, tensors={"image": [torch.rand(3, 16, 16) * 2 - 1]}), 120)
     assert c["video"][0].data[:4] == b"RIFF" and c["video"][0].data != a["video"][0].data
+
+
+@pytest.fixture(scope="module")
+def cosmos_server():
+    from mstar_b200.api_server.server import APIServer
+    cfg = {"model": "cosmos3", "model_kwargs": {"small": True, "page_size": 16, "max_num_pages": 64},
+           "use_cuda_graphs": False,
+           "node_groups": [{"node_names": ["dit"], "ranks": [0]},
+                           {"node_names": ["vae_encoder", "vae_decoder", "audio_decoder"], "ranks": [1]}]}
+    s = APIServer(cfg, in_process=True).start(120)
+    yield s
+    s.shutdown()
+
+
+@pytest.mark.parametrize("outs,with_image", [(["image"], False), (["video"], False), (["video", "audio"], False),
+                                              (["action"], False), (["video"], True)])
+def test_cosmos3_walks(cosmos_server, outs, with_image):
+    kw = dict(num_steps=3, height=16, width=16, num_frames=5, negative_prompt="blurry", seed=3)
+    rid = cosmos_server.submit_request("a robot arm", output_modalities=outs, model_kwargs=kw,
+                                       tensors={"image": [torch.rand(3, 16, 16) * 2 - 1]} if with_image else None)
+    res = cosmos_server.collect_results(rid, 120)
+    assert set(res) == set(outs), res.keys()
+    if "image" in res:
+        assert res["image"][0].data[:4] == b"\x89PNG"
+    if "action" in res:
+        assert len(res["action"][0].data) == 16 * 32 * 4
+    # the request's pages went back to the pool
+    eng = cosmos_server.deployment.workers[0].engines.engine_for("dit")
+    assert eng.cache.alloc.pages_of(rid) == 0
+
+
+def test_cosmos3_tp2_sp2_matches_single_rank_on_gloo():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+           "--nproc-per-node", "4", os.path.join(root, "tests", "mp_cosmos_worker.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""),
+                         cwd=root)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
