@@ -44,7 +44,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -178,7 +178,10 @@ def main():
         print(json.dumps({"profiled": "one eager decode step", "batch": C}))
         return
 
+    # clocks are sampled across both timed regions (end-to-end steps, then device-timed replays): same load
     sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)          # nvidia-smi needs a moment before its first sample
     # ---- (1) end to end through the public API ----
     e2e = None
     if not args.no_e2e:
@@ -199,7 +202,6 @@ def main():
     graph = eng._graphs[C]
     live = {i: r for i, r in enumerate(eng._rows) if r is not None}
     barrier()
-    sampler.start()
     l0 = _counters.get()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
