@@ -41,14 +41,20 @@ class DecoderSubmodule(ARNodeSubmodule):
 
 
 def lm_walks(node: str = "LLM", loop_name: str = "decode_loop", max_iters: int = 2048, modality: str = "text",
-             stream_edge: GraphEdge | None = None) -> dict:
-    """prefill: one forward over the prompt; decode: a loop that feeds each sampled token back into the node."""
+             stream_edge: GraphEdge | None = None, prefill_inputs: set[str] | None = None,
+             pre_nodes: list | None = None) -> dict:
+    """prefill: one forward over the prompt; decode: a loop that feeds each sampled token back into the node.
+    ``pre_nodes`` (encoders whose outputs feed the prefill node as ``prefill_inputs``) run before the prefill."""
     def outs(extra):
         o = [GraphEdge(EMIT_TO_CLIENT, "new_token", output_modality=modality, conductor_new_token=True)] if modality else []
         if stream_edge is not None:
             o.append(stream_edge.clone())
         return o + extra
-    prefill = GraphNode(node, {"input_ids"}, outs([GraphEdge(EMPTY_DESTINATION, "last_token", persist=True)]))
+    prefill = GraphNode(node, {"input_ids"} | set(prefill_inputs or ()),
+                        outs([GraphEdge(EMPTY_DESTINATION, "last_token", persist=True)]))
+    if pre_nodes:
+        from ..graph.ir import Parallel, Sequential
+        prefill = Sequential([pre_nodes[0] if len(pre_nodes) == 1 else Parallel(list(pre_nodes)), prefill])
     step = GraphNode(node, {"tok"}, outs([GraphEdge(node, "tok")]))
     return {"prefill": prefill, "decode": Loop(step, max_iters=max_iters, name=loop_name)}
 
@@ -59,9 +65,10 @@ class LMStateMachine:
     def __init__(self, node: str = "LLM", loop_name: str = "decode_loop"):
         self.node, self.loop_name = node, loop_name
 
-    def initial(self, input_signals: dict, max_tokens: int) -> ForwardPassArgs:
+    def initial(self, input_signals: dict, max_tokens: int, extra_edges: list | None = None) -> ForwardPassArgs:
         return ForwardPassArgs({"graph_walk": "prefill", "max_tokens": max_tokens},
-                               [GraphEdge(self.node, "input_ids", list(input_signals.get("input_ids", [])))])
+                               [GraphEdge(self.node, "input_ids", list(input_signals.get("input_ids", [])))]
+                               + list(extra_edges or []))
 
     def next(self, metadata: dict, persist: dict) -> ForwardPassArgs:
         budget = metadata["max_tokens"] - metadata["tokens_out"]
