@@ -141,6 +141,7 @@ class KVCacheEngine(BaseEngine):
         B = len(planned.request_ids)
         with torch.no_grad():
             if planned.bucket is not None:
+                sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 ids = torch.cat([ni.input_ids.reshape(-1)[-1:] for ni in planned.node_inputs]).to(self.device)
                 self._static_ids[:B].copy_(ids)
                 key = (b.node_name, b.graph_walk, planned.bucket)
@@ -177,6 +178,9 @@ class KVCacheEngine(BaseEngine):
                                  max(1, ctx.plan.splits), Bp * self.kv_config.num_kv_heads)
         saved_off = self.sampler.offset.clone()
         saved_seen = None if self.sampler.seen is None else self.sampler.seen.clone()
+        # device state that the node carries from step to step: the warm-up and capture runs must not advance it
+        node_state = list(sub.capture_state()) if hasattr(sub, "capture_state") else []
+        saved_state = [t.clone() for t in node_state]
 
         class _NI:      # node inputs view over the static id buffer
             pass
@@ -200,6 +204,8 @@ class KVCacheEngine(BaseEngine):
         self.sampler.offset.copy_(saved_off)
         if saved_seen is not None:
             self.sampler.seen.copy_(saved_seen)
+        for t, sv in zip(node_state, saved_state):
+            t.copy_(sv)
         self._graphs[key] = (g, extra)
         return self._graphs[key]
 

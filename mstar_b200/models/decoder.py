@@ -54,6 +54,7 @@ class DecoderConfig:
     shared_expert_intermediate_size: int = 0
     norm_topk_prob: bool = True
     moe_layers: list[int] | None = None      # None = all layers when num_experts > 0
+    moe_expert_parallel: bool = False        # cut experts (not columns) over the tensor-parallel group
     dtype: torch.dtype = torch.bfloat16
     init_std: float = 0.02
 

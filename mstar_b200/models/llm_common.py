@@ -79,3 +79,82 @@ class LMStateMachine:
                                    [GraphEdge(self.node, "tok", last[-1:])],
                                    unpersist_tensors=[t.uuid for t in last])
         return ForwardPassArgs(request_done=True)
+
+
+class MultimodalDecoderSubmodule(DecoderSubmodule):
+    """Decoder LM whose prompt carries placeholder token ids that are replaced, row by row and in order, by
+    encoder features (audio frames, image patches) before the prefill forward. ``placeholders`` maps an input
+    edge name to the token id that marks its rows. Optional ``position_fn(ids, inputs, kwargs) -> int32 [3, T]``
+    supplies multi-axis rotary positions (and the position the decode continues from via ``pos_delta``).
+
+    Reference counterparts: the per-modality prefill walks of Qwen3-Omni (mstar/model/qwen3_omni/submodules.py,
+    prefill_text / prefill_audio / prefill_vision), Higgs-Audio (mstar/model/higgs_audio/submodules.py) and
+    BAGEL's ViT prefill (mstar/model/bagel/submodules.py); merged here into one packed prefill forward.
+    """
+
+    def __init__(self, lm, device, placeholders: dict[str, int], eos_ids=(), loop_name="decode_loop",
+                 token_edge="new_token", position_fn=None, emit_hidden: str | None = None):
+        super().__init__(lm, device, eos_ids=eos_ids, loop_name=loop_name, token_edge=token_edge)
+        self.placeholders, self.position_fn, self.emit_hidden = dict(placeholders), position_fn, emit_hidden
+
+    def prepare_inputs(self, graph_walk, fwd_info, inputs):
+        ni = super().prepare_inputs(graph_walk, fwd_info, inputs)
+        if self.position_fn is not None and ni.input_ids is not None and ni.input_ids.numel() > 1:
+            pos, delta = self.position_fn(ni.input_ids, inputs, ni.kwargs)
+            ni.custom_pos_ids = pos
+            ni.kwargs["_pos_delta"] = int(delta)
+        return ni
+
+    def preprocess(self, graph_walk, engine_inputs, inputs):
+        cm = engine_inputs.cache_manager
+        for ni in inputs:       # decode continues from the largest multimodal position, not from the token count
+            d = ni.kwargs.pop("_pos_delta", None)
+            if d is not None and cm is not None:
+                cm.set_custom_pos_advance(ni.request_id, "main", d)
+        return {}
+
+    def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
+        ids = torch.cat([ni.input_ids.reshape(-1) for ni in inputs]).to(self.device)
+        x = self.lm.embed(ids)
+        off = 0
+        for ni in inputs:
+            n = ni.input_ids.numel()
+            for edge, pid in self.placeholders.items():
+                feats = ni.tensor_inputs.get(edge)
+                if not feats:
+                    continue
+                f = torch.cat([t.reshape(-1, x.shape[-1]) for t in feats]).to(self.device, x.dtype)
+                rows = (ids[off:off + n] == pid).nonzero().reshape(-1) + off
+                if rows.numel() != f.shape[0]:
+                    raise ValueError(f"{edge}: {f.shape[0]} feature rows for {rows.numel()} placeholder tokens")
+                x[rows] = f
+            off += n
+        out = self.lm(engine_inputs.batch_context, inputs_embeds=x, return_hidden=self.emit_hidden is not None)
+        if self.emit_hidden is None:
+            return {BATCHED_LOGITS: out}
+        logits, hidden = out
+        return {BATCHED_LOGITS: logits, self.emit_hidden: hidden.index_select(0, engine_inputs.batch_context.logit_rows)}
+
+    def forward_graph(self, graph_walk, engine_inputs, static_ids, ctx):
+        if self.emit_hidden is None:
+            return {BATCHED_LOGITS: self.lm(ctx, input_ids=static_ids)}
+        logits, hidden = self.lm(ctx, input_ids=static_ids, return_hidden=True)
+        return {BATCHED_LOGITS: logits, self.emit_hidden: hidden.index_select(0, ctx.logit_rows)}
+
+    def postprocess(self, request_id, request_info, outputs, inputs):
+        out = super().postprocess(request_id, request_info, outputs, inputs)
+        if self.emit_hidden is not None and self.emit_hidden in outputs:
+            out[self.emit_hidden] = outputs[self.emit_hidden].reshape(1, -1)
+        return out
+
+
+def expand_placeholders(ids: list[int], placeholder: int, counts: list[int]) -> list[int]:
+    """Replace the i-th occurrence of ``placeholder`` by ``counts[i]`` copies of it."""
+    out, i = [], 0
+    for t in ids:
+        if t == placeholder and i < len(counts):
+            out.extend([placeholder] * counts[i])
+            i += 1
+        else:
+            out.append(t)
+    return out

@@ -20,6 +20,12 @@ def _param(shape, dtype, device):
 class SparseMoeBlock(nn.Module):
     def __init__(self, cfg, tp: CommGroup, device, ep: CommGroup | None = None):
         super().__init__()
+        # ``replicated``: the expert-parallel group is the tensor-parallel group itself; every rank holds the same
+        # tokens (attention output was all-reduced), runs only its own experts on them and the results are summed
+        # by one all-reduce. No dispatch traffic; the expert weights are cut by expert instead of by column.
+        self.replicated = False
+        if ep is None and getattr(cfg, "moe_expert_parallel", False) and tp.size > 1:
+            ep, self.replicated = tp, True
         self.cfg, self.tp, self.ep = cfg, tp, ep
         H, E, I = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size
         self.E, self.top_k = E, cfg.num_experts_per_tok
@@ -70,6 +76,11 @@ class SparseMoeBlock(nn.Module):
             s = self.shared(h, reduce=False)
             gate = torch.sigmoid(gemm.linear(h, self.shared_gate, out_dtype=torch.float32))
             add = (s.float() * gate).to(h.dtype)
+        if self.replicated:
+            from .decoder import tp_reduce
+            y = moe_ops.fused_moe(h, logits, self.w13, self.w2, self.top_k, self.cfg.norm_topk_prob,
+                                  self.expert_range, add=add)
+            return tp_reduce(y.contiguous(), self.tp)
         if self.ep is not None and self.ep.size > 1 and getattr(self.ep, "symm", None) is not None and h.is_cuda:
             from ..parallel.expert_parallel import ep_moe
             return ep_moe(self, h, logits, add)

@@ -47,6 +47,23 @@ def main():
         return m(ctx, input_ids=ids)
     a, b = logits(ref_model, 2), logits(tp_model, 1)
     assert (a - b).abs().max().item() < 1e-3, (a - b).abs().max().item()
+    # MoE decoder: column-sharded experts (TP) and expert-sharded experts over the same group both match one rank
+    from mstar_b200.models.decoder import DecoderConfig, DecoderLM
+    from mstar_b200.parallel.comm import CommGroup
+    for ep_mode in (False, True):
+        cfg = DecoderConfig(hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8, intermediate_size=64,
+                            vocab_size=64, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=16,
+                            shared_expert_intermediate_size=32, moe_expert_parallel=ep_mode, dtype=torch.float32)
+        one = DecoderLM(cfg, tp=CommGroup.trivial()).init_random(3)
+        two = DecoderLM(cfg, tp=g).init_random(3)
+        mids = torch.randint(0, 64, (9,), generator=gen)
+
+        def mlogits(m, kvh):
+            kvc = KVCacheConfig(2, kvh, 8, max_seq_len=64, max_num_pages=8, page_size=16, num_qo_heads=4, dtype=torch.float32)
+            cm = BatchedCacheManager(kvc, "cpu", max_batch=2, max_tokens=64)
+            return m(cm.plan(["r"], [9]), input_ids=mids)
+        d = (mlogits(one, 2) - mlogits(two, 1)).abs().max().item()
+        assert d < 1e-4, (ep_mode, d)
     dist.barrier()
     dist.destroy_process_group()
 

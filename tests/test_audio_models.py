@@ -59,3 +59,83 @@ def test_whisper_serving_two_requests(whisper_server):
     for rid in rids:
         res = whisper_server.collect_results(rid, 120)
         assert "error" not in res and len(res["text"]) == 5
+
+
+def test_higgs_audio_placeholders_are_replaced_by_encoder_frames():
+    from mstar_b200.api_server.server import APIServer
+    cfg = {"model": "higgs_audio", "model_kwargs": {"small": True}, "use_cuda_graphs": False,
+           "node_groups": [{"node_names": ["audio_encoder", "LLM"], "ranks": [0]}]}
+    s = APIServer(cfg, in_process=True).start(120)
+    try:
+        outs = []
+        for wav in (torch.randn(16000 * 5) * 0.1, torch.randn(16000 * 5) * 0.3, None):
+            rid = s.submit_request("transcribe", output_modalities=["text"], model_kwargs=dict(max_tokens=4),
+                                   tensors={"audio": [wav]} if wav is not None else None)
+            res = s.collect_results(rid, 120)
+            assert "error" not in res and len(res["text"]) == 4, res
+            outs.append(b"".join(c.data for c in res["text"]))
+        # 5 s of audio = two 4 s chunks = 2 * 200 placeholder rows; different audio changes the continuation
+        assert outs[0] != outs[1] or outs[0] != outs[2]
+    finally:
+        s.shutdown()
+
+
+def test_qwen3_tts_streams_left_context_chunks():
+    from mstar_b200.api_server.server import APIServer
+    cfg = {"model": "qwen3_tts", "model_kwargs": {"small": True}, "use_cuda_graphs": False,
+           "node_groups": [{"node_names": ["Talker"], "ranks": [0], "graph_walks": ["talker_prefill", "talker_decode"]},
+                           {"node_names": ["Codec"], "ranks": [1], "graph_walks": ["codec_chunk"]}]}
+    s = APIServer(cfg, in_process=True).start(120)
+    try:
+        rid = s.submit_request("hello world", output_modalities=["audio"], model_kwargs=dict(max_tokens=20, ignore_eos=True))
+        res = s.collect_results(rid, 120)
+        assert "error" not in res
+        # 20 tokens = 1 prefill sample + 19 decode steps = 19 complete frames of 4 samples (hop 2*2), 2 bytes each:
+        # chunks of 6 new frames (the context frames' samples are cut), then the flush
+        sizes = [len(c.data) for c in res["audio"]]
+        assert sum(sizes) == 19 * 4 * 2 and sizes[0] == 6 * 4 * 2, sizes
+    finally:
+        s.shutdown()
+
+
+@pytest.fixture(scope="module")
+def omni_server():
+    from mstar_b200.api_server.server import APIServer
+    cfg = {"model": "qwen3_omni", "model_kwargs": {"small": True}, "use_cuda_graphs": False,
+           "node_groups": [{"node_names": ["audio_encoder", "vision_encoder", "Thinker"], "ranks": [0]},
+                           {"node_names": ["Talker"], "ranks": [1]}, {"node_names": ["Code2Wav"], "ranks": [2]}]}
+    s = APIServer(cfg, in_process=True).start(120)
+    yield s
+    s.shutdown()
+
+
+def test_qwen3_omni_text_audio_image_in_text_out(omni_server):
+    s = omni_server
+    kw = dict(max_tokens=6, ignore_eos=True, temperature=0.0)
+    a = s.collect_results(s.submit_request("describe", output_modalities=["text"], model_kwargs=kw), 120)
+    b = s.collect_results(s.submit_request("describe", output_modalities=["text"], model_kwargs=kw,
+                                           tensors={"audio": [torch.randn(8000) * 0.1], "image": [torch.rand(3, 16, 16)]}), 120)
+    assert len(a["text"]) == 6 and len(b["text"]) == 6
+    assert b"".join(c.data for c in a["text"]) != b"".join(c.data for c in b["text"])
+    import time
+    time.sleep(0.3)
+    for w in s.deployment.workers:          # nothing of a text-only request stays behind on the speech workers
+        assert len(w.tensors.store) == 0, (w.worker_id, len(w.tensors.store))
+
+
+def test_qwen3_omni_speech_out_runs_three_partitions(omni_server):
+    s = omni_server
+    rid = s.submit_request("say hi", output_modalities=["text", "audio"],
+                           model_kwargs=dict(max_tokens=5, ignore_eos=True, max_audio_tokens=15))
+    res = s.collect_results(rid, 120)
+    assert "error" not in res and len(res["text"]) == 5
+    assert sum(len(c.data) for c in res["audio"]) == 15 * 4 * 2          # 15 decode iterations -> 15 complete frames
+
+
+def test_mrope_positions_for_image_spans():
+    from mstar_b200.models.qwen3_omni import IMAGE_TOKEN, mrope_positions
+    ids = torch.tensor([5, 6, IMAGE_TOKEN, IMAGE_TOKEN, IMAGE_TOKEN, IMAGE_TOKEN, 7, 8])
+    pos, delta = mrope_positions(ids, [(1, 2, 2)], IMAGE_TOKEN)
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[:, 2:6].tolist() == [[2, 2, 2, 2], [2, 2, 3, 3], [2, 3, 2, 3]]
+    assert pos[:, 6:].tolist() == [[4, 5]] * 3 and delta == 6 - 8
