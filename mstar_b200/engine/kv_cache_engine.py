@@ -94,10 +94,12 @@ class KVCacheEngine(BaseEngine):
         b = prepared.batch
         sub = self.submodules[b.node_name]
         if hasattr(sub, "custom_plan"):
-            # nodes that plan their own entries (several cache labels per request, reads without writes, ...)
-            prepared.ctx = sub.custom_plan(self.cache, b.graph_walk, prepared)
-            prepared.bucket, prepared.q_lens = None, list(prepared.ctx.q_lens)
-            return prepared
+            # nodes that plan their own entries (several cache labels per request, reads without writes, ...);
+            # None = this walk uses the default planning below
+            ctx = sub.custom_plan(self.cache, b.graph_walk, prepared)
+            if ctx is not None:
+                prepared.ctx, prepared.bucket, prepared.q_lens = ctx, None, list(ctx.q_lens)
+                return prepared
         q_lens = [max(1, ni.input_seq_len) for ni in prepared.node_inputs]
         labels = [sub.get_needed_cache_labels(b.graph_walk, b.fwd_infos[r])[0] for r in prepared.request_ids]
         slots = [self.sampler.slot(r) for r in prepared.request_ids]
@@ -156,8 +158,17 @@ class KVCacheEngine(BaseEngine):
             else:
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 outs = sub.forward_batched(b.graph_walk, ei, planned.node_inputs)
-                if isinstance(outs, list):           # one dict per request, no sampling
+                if isinstance(outs, list):           # one dict per request; logits rows (if any) are sampled
                     raw = {"per_request": outs}
+                    rows = [(i, o.pop(BATCHED_LOGITS)) for i, o in enumerate(outs) if BATCHED_LOGITS in o]
+                    if rows:
+                        slots = torch.tensor([self.sampler.slot(planned.request_ids[i]) for i, _ in rows],
+                                             dtype=torch.int32, device=self.device)
+                        lg = torch.cat([r.reshape(1, -1) for _, r in rows]).float().contiguous()
+                        toks = self.sampler.sample(lg, slots)
+                        for (i, _), t in zip(rows, toks.tolist()):
+                            outs[i]["new_token"] = torch.tensor([t], dtype=torch.int64)
+                            outs[i]["new_token_host"] = t
                     outs = {}
                 else:
                     raw = {"extra": {k: v for k, v in outs.items() if k != BATCHED_LOGITS}}

@@ -243,8 +243,13 @@ def restrict_section(section: GraphSection, keep: set[str]) -> GraphSection | No
         inner = restrict_section(section.section, keep)
         if inner is None:
             return None
-        return Loop(inner, section.max_iters, [e.clone() for e in section.outputs], section.name,
+        part = Loop(inner, section.max_iters, [e.clone() for e in section.outputs], section.name,
                     [e.clone() for e in section.accumulated_outputs])
+        # what is a loop-back and what comes from outside is a property of the WHOLE loop: a signal fed back by a
+        # node on another worker must not look like an outside input here (it would be re-delivered every iteration)
+        part.loop_back_inputs = {k for k in section.loop_back_inputs if k[1] in keep}
+        part.external_inputs = {k for k in section.external_inputs if k[1] in keep}
+        return part
     kids = [k for k in (restrict_section(c, keep) for c in section.children()) if k is not None]
     if not kids:
         return None

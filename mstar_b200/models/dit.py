@@ -330,6 +330,30 @@ class MoTGenTower(nn.Module):
             self._exchange[key] = ex
         return ex
 
+    def layer_qkv(self, li: int, x, residual, positions, ctx=None):
+        """Pre-attention half of layer ``li`` on a row subset: returns (q, k, v, residual). With ``ctx`` the K/V
+        rows are also written into the paged pool at the subset's cache slots."""
+        L, cfg = self.layers[li], self.cfg
+        h, residual = (norm_ops.norm(x, L.input_norm, cfg.rms_eps, residual=residual) if residual is not None
+                       else (norm_ops.norm(x, L.input_norm, cfg.rms_eps)[0], x.clone()))
+        qkv = gemm.linear(h, L.qkv_proj, bias=L.qkv_bias)
+        kw = {}
+        if ctx is not None:
+            kw = dict(cache=ctx["kv"], token_req=ctx["token_req"], cache_pos=ctx["cache_pos"],
+                      page_indptr=ctx["page_indptr"], page_indices=ctx["page_indices"])
+        q, k, v = rope_ops.rope_kv(qkv, positions, self.inv_freq, L.Hq, L.Hkv, cfg.head_dim,
+                                   axis_of_freq=self.axis_of_freq, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
+                                   norm_eps=cfg.rms_eps, dense_kv=ctx is None, **kw)
+        return q, k, v, residual
+
+    def layer_out(self, li: int, attn, residual):
+        """Post-attention half of layer ``li``: o_proj, post norm, MLP. Returns (x, residual)."""
+        L, cfg = self.layers[li], self.cfg
+        x = row_parallel(attn.reshape(attn.shape[0], -1), L.o_proj, self.tp)
+        h, residual = norm_ops.norm(x, L.post_norm, cfg.rms_eps, residual=residual)
+        g = gemm.linear(h, L.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
+        return row_parallel(g, L.down_proj, self.tp), residual
+
     def forward(self, x: torch.Tensor, positions: torch.Tensor, self_plan, *, prefix_ctx=None,
                 S_total: int | None = None) -> torch.Tensor:
         """x: [T_local, H] rows of this sequence-parallel rank (all rows when sp = 1); positions: int32
