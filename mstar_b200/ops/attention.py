@@ -126,6 +126,10 @@ def attention(q: torch.Tensor, plan: AttnPlan, *, kv_cache: torch.Tensor | None 
     if not _lib.use_cuda(q):
         return attention_ref(q, plan, kv_cache=kv_cache, k=k, v=v, scale=scale, lse=lse)
     T, Hq, D = q.shape
+    if D not in (64, 128):
+        # head sizes the tensor-core kernels are not built for (e.g. 256-wide Gemma heads, 72-wide SigLIP heads):
+        # the fp32 oracle, which is plain tensor code and runs on the GPU too (it reads the plan on the host)
+        return attention_ref(q, plan, kv_cache=kv_cache, k=k, v=v, scale=scale, lse=lse)
     assert q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if out is None:

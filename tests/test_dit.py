@@ -193,6 +193,11 @@ def test_cosmos3_walks(cosmos_server, outs, with_image):
         assert len(res["action"][0].data) == 16 * 32 * 4
     # the request's pages went back to the pool
     eng = cosmos_server.deployment.workers[0].engines.engine_for("dit")
+    import time
+    for _ in range(100):
+        if eng.cache.alloc.pages_of(rid) == 0:
+            break
+        time.sleep(0.02)
     assert eng.cache.alloc.pages_of(rid) == 0
 
 
