@@ -65,6 +65,7 @@ class Conductor:
         for wg in self.worker_graphs:
             model.validate_sharding(wg)
         self.walks = model.get_graph_walk_graphs()
+        self.kv_nodes = {n for n, t in model.get_node_engine_types().items() if str(getattr(t, "value", t)) == "kv_cache"}
         self.partitions = {p.name: p for p in model.get_partitions()}
         self.requests: dict[str, RequestData] = {}
         self.waiting: deque = deque()
@@ -188,6 +189,20 @@ class Conductor:
                                           rd.seed, int(md.get("max_tokens", rd.max_tokens - rd.tokens_out)), sc,
                                           dict(fpa.step_metadata or {}), {}, ps.name, {},
                                           dict(md.get("dynamic_loop_iter_counts", {})))
+        # prefill / decode disaggregation: a KV node that now runs on another worker graph than before takes its
+        # pages along (rank i of the new group pulls from rank i of the old one)
+        home = rd.__dict__.setdefault("kv_home", {})
+        kv_import: dict[str, dict[str, str]] = {}
+        for wg in graphs:
+            for n in wg.node_names:
+                if self.kv_nodes is not None and n in self.kv_nodes and n in self.walks[walk].nodes():
+                    old = home.get(n)
+                    if old is not None and old.graph_id != wg.graph_id:
+                        for src_r, dst_r in zip(old.ranks, wg.ranks):
+                            kv_import.setdefault(worker_id_of(dst_r), {})[n] = worker_id_of(src_r)
+                    home[n] = wg
+        if kv_import:
+            info.step_metadata["_kv_import"] = kv_import
         n2w = self.node_to_workers(rd)
         wg2w = {wg.graph_id: [worker_id_of(r) for r in wg.ranks] for wg in rd.assigned.values()}
         per_worker: dict[str, list[GraphEdge]] = {}

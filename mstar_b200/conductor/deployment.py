@@ -91,6 +91,8 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
     kv = cfg.get("kv_cache", {}) or {}
     em = EngineManager(model, device, node_names, tp_group=tp_group, sp_group=sp_group, kv_overrides=kv,
                        max_batch=int(cfg.get("max_batch_size", 64)), use_cuda_graphs=cfg.get("use_cuda_graphs"))
+    from ..worker.engine_manager import register_kv_engines
+    register_kv_engines(worker_id_of(rank), em)
     n2w: dict[str, list[str]] = {}
     for wg in wgs:
         for n in wg.node_names:

@@ -62,6 +62,21 @@ class KVCacheEngine(BaseEngine):
     def get_per_label_seq_info(self, request_id: str) -> dict:
         return self.cache.alloc.get_per_label_seq_info(request_id)
 
+    # ---- prefill / decode disaggregation ----
+    def import_kv_from(self, src: "KVCacheEngine", request_id: str, fwd_info) -> int:
+        """Pull a request's K/V pages (device-to-device, over NVLink between GPUs) and sampler state from the
+        engine that ran its prefill. Returns the number of pages moved."""
+        from .kv_store import PeerKVTransfer
+        desc = src.cache.alloc.export_descriptor(request_id)
+        self.add_request(request_id, fwd_info)
+        PeerKVTransfer(self.cache.alloc).pull(request_id, src.cache.alloc.kv_layers, desc)
+        if request_id in src.sampler._slot_of:
+            a, b = src.sampler.slot(request_id), self.sampler.slot(request_id)
+            self.sampler.offset[b] = src.sampler.offset[a].to(self.device)
+            if self.sampler.seen is not None and src.sampler.seen is not None:
+                self.sampler.seen[b] = src.sampler.seen[a].to(self.device)
+        return sum(len(d["pages"]) for d in desc.values())
+
     # ---- offload surface ----
     def can_offload(self) -> bool:
         return self.cache.alloc.cpu_pool is not None

@@ -225,6 +225,12 @@ class PagedAllocationManager:
                 self.allocator.free(st.pages)
             st.pages, st.seq_len, st.pos_offset = [], 0, 0
 
+    def export_descriptor(self, request_id: str) -> dict:
+        """What a peer pool needs to pull this request's K/V: per label the page ids, length and position offset."""
+        with self._lock:
+            return {lb: dict(pages=list(st.pages), seq_len=st.seq_len, pos_offset=st.pos_offset)
+                    for lb, st in self._states.get(request_id, {}).items()}
+
     def copy_label(self, request_id: str, src: str, dst: str) -> None:
         """Snapshot: ``dst`` gets its own copy of ``src``'s pages (page copy on the device)."""
         with self._lock:

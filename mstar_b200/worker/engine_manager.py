@@ -12,6 +12,21 @@ from ..engine.stateless_engine import StatelessEngine, make_audio_codec_config, 
 from ..models.base import EngineType
 
 
+# KV engines of this process by (worker id, node): the decode side of a prefill / decode split pulls pages from the
+# prefill side's pool through this table when both live in one process
+_KV_ENGINES: dict[tuple[str, str], object] = {}
+
+
+def register_kv_engines(worker_id: str, manager: "EngineManager") -> None:
+    for node, eng in manager.node_to_engine.items():
+        if isinstance(eng, KVCacheEngine):
+            _KV_ENGINES[(worker_id, node)] = eng
+
+
+def lookup_kv_engine(worker_id: str, node: str):
+    return _KV_ENGINES.get((worker_id, node))
+
+
 class EngineManager:
     def __init__(self, model, device, node_names: list[str], *, tp_group=None, sp_group=None, kv_overrides=None,
                  max_batch: int = 64, use_cuda_graphs: bool | None = None):

@@ -120,6 +120,15 @@ class Worker:
         sec = self._section_for(info.graph_walk)
         if sec is None:
             return
+        imports = (info.step_metadata or {}).pop("_kv_import", {}).get(self.worker_id, {})
+        for node, src_worker in imports.items():
+            if node in self.node_names:
+                from .engine_manager import lookup_kv_engine
+                src = lookup_kv_engine(src_worker, node)
+                if src is None:
+                    raise RuntimeError(f"KV hand-off of {node} from {src_worker}: the source pool is not in this "
+                                       f"process (prefill / decode split needs both workers in one process)")
+                self.engines.engine_for(node).import_kv_from(src, b.request_id, info)
         key = (b.request_id, info.partition_name)
         old = self.requests.get(key)
         ws = WalkState(sec, b.request_id, on_release=lambda e, rid=b.request_id: self._release_edge(rid, e))

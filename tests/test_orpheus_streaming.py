@@ -36,3 +36,27 @@ def test_two_requests_share_the_codec_worker(server):
     for rid in rids:
         res = server.collect_results(rid, 300)
         assert "error" not in res and len(res["audio"]) >= 2
+
+
+def test_prefill_decode_disaggregation_moves_the_kv_pages():
+    """Prefill on worker 0, decode on worker 1 (separate page pools): tokens equal the colocated run's."""
+    base = {"model": "tiny", "use_cuda_graphs": False}
+    pd = dict(base, node_groups=[{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill"]},
+                                 {"node_names": ["LLM"], "ranks": [1], "graph_walks": ["decode"]}])
+    co = dict(base, node_groups=[{"node_names": ["LLM"], "ranks": [0]}])
+    outs = []
+    for cfg in (co, pd):
+        s = APIServer(cfg, in_process=True).start(120)
+        try:
+            rid = s.submit_request("the quick brown fox jumps over the lazy dog", output_modalities=["text"],
+                                   model_kwargs=dict(max_tokens=12, ignore_eos=True, temperature=0.7, top_p=0.9,
+                                                     repetition_penalty=1.2, seed=5))
+            res = s.collect_results(rid, 300)
+            assert "error" not in res, res
+            outs.append(b"".join(c.data for c in res["text"]))
+            if cfg is pd:
+                pre, dec = (w.engines.engine_for("LLM") for w in s.deployment.workers[:2])
+                assert dec.graph_hits == 0 and pre.cache.alloc is not dec.cache.alloc
+        finally:
+            s.shutdown()
+    assert len(outs[0]) > 0 and outs[0] == outs[1]
