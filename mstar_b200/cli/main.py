@@ -52,8 +52,13 @@ def serve(args) -> None:
     server = APIServer(cfg, in_process=not args.multi_process, request_timeout_s=args.timeout,
                        log_stats=args.log_stats).start()
     if args.native_frontend:
-        from ..api_server.native_frontend import NativeFrontendBridge
-        NativeFrontendBridge(server, host=args.host, port=args.port).run_forever()
+        from ..api_server.native_frontend import NativeFrontend
+        fe = NativeFrontend(create_app(server, args.allow_remote_media), host=args.host, port=args.port).start()
+        try:
+            fe.wait()
+        finally:
+            fe.stop()
+            server.shutdown()
         return
     import uvicorn
     try:
