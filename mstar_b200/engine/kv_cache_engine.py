@@ -224,7 +224,7 @@ class KVCacheEngine(BaseEngine):
                 body()
             s.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
+            with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
                 extra = body()
         torch.cuda.current_stream().wait_stream(s)
         self.sampler.offset.copy_(saved_off)

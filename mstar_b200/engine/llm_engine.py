@@ -313,7 +313,7 @@ class LLMEngine:
             g = torch.cuda.CUDAGraph()
             from ..ops import _counters
             c0 = _counters.get()
-            with torch.cuda.graph(g, stream=s):
+            with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
                 self._decode_body(ctx)
             self.launches_per_decode_graph[B] = _counters.get() - c0
         torch.cuda.current_stream().wait_stream(s)

@@ -44,7 +44,7 @@ class PiecewiseCudaGraphRunner:
                     fn(*static_in)
                 s.synchronize()
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=s):
+                with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
                     static_out = fn(*static_in)
             torch.cuda.current_stream().wait_stream(s)
             entry = (g, static_in, static_out)

@@ -30,7 +30,7 @@ from ..ops import elementwise as ew
 from ..ops import gemm
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .decoder import DecoderConfig, DecoderLM, _param, row_parallel_linear
 from .dit import MoTGenTower, sinusoidal_embedding
 from .encoders import EncoderConfig, VisionEncoder
@@ -220,7 +220,7 @@ class BagelLLMSubmodule(ARNodeSubmodule):
         ni = ARNodeInputs(fwd_info.request_id, graph_walk, inputs, dict(fwd_info.step_metadata or {}))
         for key in ("input_ids", "tok"):
             if inputs.get(key):
-                ni.input_ids = torch.cat([t.reshape(-1) for t in inputs[key]]).to(torch.int64)
+                ni.input_ids = torch.cat([t.reshape(-1) for t in inputs[key]]).to(torch.int64).cpu()
                 ni.input_seq_len = int(ni.input_ids.numel())
                 break
         return ni
@@ -407,10 +407,11 @@ class BagelModel(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype = small, dt
         if small:
-            self.cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
-                                     intermediate_size=128, vocab_size=152064, qkv_bias=True, qk_norm=True, dtype=dt)
+            k = small_scale()
+            self.cfg = DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16 * k,
+                                     intermediate_size=128 * k, vocab_size=152064, qkv_bias=True, qk_norm=True, dtype=dt)
             self.vae_cfg = tiny_vae_config(2, 4)
-            self.vit_cfg, self.vit_patch = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 4
+            self.vit_cfg, self.vit_patch = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4
         else:
             self.cfg = bagel_7b_config(dt)
             self.vae_cfg = bagel_vae_config()

@@ -24,6 +24,12 @@ MAX_OUTPUT_TOKENS = 2048
 NameToTensorList = dict[str, list[torch.Tensor]]
 
 
+def small_scale() -> int:
+    """Width multiplier of the test-sized model variants: on a GPU they are widened so that every layer has a shape
+    the tensor-core kernels accept (64-wide heads, 16-byte aligned rows); on the CPU they stay minimal."""
+    return 4 if torch.cuda.is_available() else 1
+
+
 class EngineType(str, Enum):
     KV_CACHE = "kv_cache"
     STATELESS = "stateless"

@@ -27,7 +27,7 @@ from ..ops import attention as attn_ops
 from ..ops import gemm
 from ..parallel.comm import CommGroup
 from ..parallel.sequence_parallel import gather_sequence, sp_seq_split
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .codec import Code2Wav
 from .decoder import DecoderConfig, DecoderLM, _param
 from .dit import MoTGenTower, grid_positions, patchify, sinusoidal_embedding, unpatchify
@@ -231,8 +231,10 @@ class Cosmos3Model(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small = small
         if small:
-            self.cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=16,
-                                     intermediate_size=128, vocab_size=512, qk_norm=True, mrope_sections=[2, 3, 3],
+            k = small_scale()
+            self.cfg = DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=16 * k,
+                                     intermediate_size=128 * k, vocab_size=512, qk_norm=True,
+                                     mrope_sections=[2 * k, 3 * k, 3 * k],
                                      has_lm_head=False, dtype=dt)
             self.vae_cfg = tiny_vae_config(3, 4)
         else:

@@ -106,6 +106,7 @@ class TransformerEncoder(nn.Module):
         self.layers = nn.ModuleList([EncoderLayer(c, device) for _ in range(c.num_layers)])
         self.fn_w = _p((c.hidden_size,), c.dtype, device) if final_norm else None
         self.fn_b = _p((c.hidden_size,), c.dtype, device) if final_norm and c.norm == "layernorm" else None
+        self._plans: dict = {}
 
     def init_random(self, seed=0):
         g = torch.Generator().manual_seed(seed)
@@ -117,7 +118,13 @@ class TransformerEncoder(nn.Module):
         return self
 
     def forward(self, x: torch.Tensor, seq_lens: list[int], bias=None, rope=None, collect: list[int] | None = None):
-        plan = attn_ops.dense_plan(seq_lens, seq_lens, 1, x.device, causal=False)
+        # plans are cached per shape: a captured piece must not create tensors from host data
+        key = (tuple(seq_lens), str(x.device))
+        plan = self._plans.get(key)
+        if plan is None:
+            if len(self._plans) > 256:
+                self._plans.clear()
+            plan = self._plans[key] = attn_ops.dense_plan(seq_lens, seq_lens, 1, x.device, causal=False)
         taps = []
         for i, L in enumerate(self.layers):
             x = L(x, plan, bias, seq_lens, rope)

@@ -10,7 +10,7 @@ import torch
 
 from ..engine.kv_store import KVCacheConfig
 from ..graph.ir import GraphEdge, GraphNode
-from .base import EngineType, Model
+from .base import small_scale, EngineType, Model
 from .decoder import DecoderConfig, DecoderLM
 from .encoders import AudioEncoder, EncoderConfig, log_mel_spectrogram
 from .llm_common import LMStateMachine, MultimodalDecoderSubmodule, expand_placeholders, lm_walks
@@ -47,9 +47,10 @@ class HiggsAudioModel(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype = small, dt
         if small:
-            self.cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
-                                     intermediate_size=128, vocab_size=151936, qk_norm=True, tie_embeddings=True, dtype=dt)
-            self.enc_cfg, self.n_mels = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 16
+            k = small_scale()
+            self.cfg = DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16 * k,
+                                     intermediate_size=128 * k, vocab_size=151936, qk_norm=True, tie_embeddings=True, dtype=dt)
+            self.enc_cfg, self.n_mels = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 16
         else:      # Qwen3-1.7B backbone
             self.cfg = DecoderConfig(hidden_size=2048, num_layers=28, num_heads=16, num_kv_heads=8, head_dim=128,
                                      intermediate_size=6144, vocab_size=151936, qk_norm=True, tie_embeddings=True,

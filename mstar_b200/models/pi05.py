@@ -22,7 +22,7 @@ from ..ops import elementwise as ew
 from ..ops import gemm
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .dit import sinusoidal_embedding
 from .encoders import EncoderConfig, VisionEncoder
 from .submodule_base import ARNodeInputs, ARNodeSubmodule, NodeSubmodule
@@ -224,8 +224,10 @@ class Pi05Model(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype, self.horizon, self.action_dim, self.num_steps = small, dt, action_horizon, action_dim, num_steps
         if small:
-            self.kw = dict(vocab=1024, hidden=64, layers=2, heads=4, kv_heads=1, head_dim=16, ffn=128, a_hidden=32, a_ffn=64)
-            self.vit_cfg, self.patch = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 4
+            k = small_scale()
+            self.kw = dict(vocab=1024, hidden=64 * k, layers=2, heads=4, kv_heads=1, head_dim=16 * k, ffn=128 * k,
+                           a_hidden=32 * k, a_ffn=64 * k)
+            self.vit_cfg, self.patch = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4
             self.horizon = min(self.horizon, 8)
         else:
             self.kw = dict(vocab=257152, hidden=2048, layers=18, heads=8, kv_heads=1, head_dim=256, ffn=16384,

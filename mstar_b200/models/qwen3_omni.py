@@ -25,7 +25,7 @@ from ..engine.kv_store import KVCacheConfig
 from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, GraphNode, Loop
 from ..streaming import (Connection, FixedChunkPolicy, LeftContextChunkPolicy, PartitionDefinition, PartitionTopology,
                          StreamingGraphEdge)
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .codec import Code2Wav
 from .decoder import DecoderConfig, DecoderLM
 from .encoders import AudioEncoder, EncoderConfig, VisionEncoder, log_mel_spectrogram
@@ -40,9 +40,11 @@ IM_END, ENDOFTEXT = 151645, 151643
 
 def thinker_config(dtype, small=False, expert_parallel=False) -> DecoderConfig:
     if small:
-        return DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
-                             vocab_size=151936, qk_norm=True, mrope_sections=[2, 3, 3], num_experts=4,
-                             num_experts_per_tok=2, moe_intermediate_size=32, moe_expert_parallel=expert_parallel, dtype=dtype)
+        k = small_scale()
+        return DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16 * k,
+                             intermediate_size=128 * k, vocab_size=151936, qk_norm=True,
+                             mrope_sections=[2 * k, 3 * k, 3 * k], num_experts=4,
+                             num_experts_per_tok=2, moe_intermediate_size=32 * k, moe_expert_parallel=expert_parallel, dtype=dtype)
     return DecoderConfig(hidden_size=2048, num_layers=48, num_heads=32, num_kv_heads=4, head_dim=128,
                          intermediate_size=768, vocab_size=151936, rope_theta=1e6, qk_norm=True,
                          mrope_sections=[24, 20, 20], mrope_interleaved=True, num_experts=128, num_experts_per_tok=8,
@@ -51,9 +53,11 @@ def thinker_config(dtype, small=False, expert_parallel=False) -> DecoderConfig:
 
 def talker_config(dtype, small=False, expert_parallel=False) -> DecoderConfig:
     if small:
-        return DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
-                             vocab_size=128, qk_norm=True, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
-                             shared_expert_intermediate_size=64, moe_expert_parallel=expert_parallel, dtype=dtype)
+        k = small_scale()
+        return DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16 * k,
+                             intermediate_size=128 * k, vocab_size=128, qk_norm=True, num_experts=4,
+                             num_experts_per_tok=2, moe_intermediate_size=32 * k,
+                             shared_expert_intermediate_size=64 * k, moe_expert_parallel=expert_parallel, dtype=dtype)
     return DecoderConfig(hidden_size=1024, num_layers=20, num_heads=16, num_kv_heads=2, head_dim=128,
                          intermediate_size=384, vocab_size=3072, rope_theta=1e6, qk_norm=True, num_experts=128,
                          num_experts_per_tok=6, moe_intermediate_size=384, shared_expert_intermediate_size=768,
@@ -126,11 +130,12 @@ class Qwen3OmniModel(Model):
         self.t_cfg = thinker_config(dt, small, expert_parallel)
         self.k_cfg = talker_config(dt, small, expert_parallel)
         if small:
-            self.pred_cfg = DecoderConfig(hidden_size=32, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16,
-                                          intermediate_size=64, vocab_size=8, qk_norm=True, dtype=dt)
+            k = small_scale()
+            self.pred_cfg = DecoderConfig(hidden_size=32 * k, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16 * k,
+                                          intermediate_size=64 * k, vocab_size=8, qk_norm=True, dtype=dt)
             self.n_sub, self.codebook, self.codec_eos = 3, 64, 63
-            self.a_cfg, self.n_mels = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 16
-            self.v_cfg, self.patch, self.merge = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 4, 2
+            self.a_cfg, self.n_mels = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 16
+            self.v_cfg, self.patch, self.merge = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4, 2
             self.chunk, self.left = 6, 2
         else:
             self.pred_cfg = DecoderConfig(hidden_size=1024, num_layers=5, num_heads=16, num_kv_heads=8, head_dim=64,

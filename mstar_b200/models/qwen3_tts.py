@@ -14,7 +14,7 @@ from ..api_server.media_io import float_to_pcm16
 from ..engine.kv_store import KVCacheConfig
 from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, GraphNode, Loop
 from ..streaming import Connection, LeftContextChunkPolicy, PartitionDefinition, PartitionTopology, StreamingGraphEdge
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .codec import Code2Wav
 from .decoder import DecoderConfig, DecoderLM
 from .submodule_base import NodeSubmodule
@@ -76,10 +76,11 @@ class Qwen3TTSModel(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype = small, dt
         if small:
-            self.cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
-                                     intermediate_size=128, vocab_size=3072, qk_norm=True, dtype=dt)
-            self.pred_cfg = DecoderConfig(hidden_size=32, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16,
-                                          intermediate_size=64, vocab_size=8, qk_norm=True, dtype=dt)
+            k = small_scale()
+            self.cfg = DecoderConfig(hidden_size=64 * k, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16 * k,
+                                     intermediate_size=128 * k, vocab_size=3072, qk_norm=True, dtype=dt)
+            self.pred_cfg = DecoderConfig(hidden_size=32 * k, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16 * k,
+                                          intermediate_size=64 * k, vocab_size=8, qk_norm=True, dtype=dt)
             self.n_sub, self.codebook, self.text_vocab = 3, 64, 512
             self.chunk, self.left = 6, 2
         else:     # 1.7B-class talker, 5-layer predictor

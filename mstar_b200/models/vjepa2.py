@@ -23,7 +23,7 @@ from torch import nn
 from ..engine.piecewise_graph import PiecewiseCudaGraphRunner
 from ..graph.ir import EMIT_TO_CLIENT, GraphEdge, GraphNode, Loop, Sequential
 from ..ops import gemm
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .encoders import EncoderConfig, TransformerEncoder, VisionEncoder
 from .submodule_base import NodeSubmodule
 
@@ -91,7 +91,7 @@ class ActionConditionedPredictor(nn.Module):
         s = gemm.linear(states.reshape(B * T, -1).to(dt), self.state).reshape(B, T, 1, -1)
         seq = torch.cat([a, s, x], dim=2).reshape(B * T * (P + 2), -1).contiguous()
         L = T * (P + 2)
-        h = runner.run("ac_blocks", lambda z: self.blocks(z, [L] * B), seq)
+        h = runner.run(f"ac_blocks_{B}x{L}", lambda z: self.blocks(z, [L] * B), seq)
         last = h.reshape(B, T, P + 2, -1)[:, -1, 2:].reshape(B * P, -1).contiguous()
         return gemm.linear(last, self.out).reshape(B, P, E)
 
@@ -166,15 +166,16 @@ class VJepa2Model(Model):
         super().__init__(model_dir, skip_weight_loading, **kw)
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype = small, dt
+        k = small_scale()
         if small:
-            self.enc_cfg, self.patch = EncoderConfig(32, 1, 2, 16, 64, dtype=dt), 4
-            self.pred_cfg = EncoderConfig(32, 1, 2, 16, 64, dtype=dt)
+            self.enc_cfg, self.patch = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4
+            self.pred_cfg = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt)
             self.max_tokens = 256
         else:      # ViT-L encoder, 12-layer 384-wide predictor
             self.enc_cfg, self.patch = EncoderConfig(1024, 24, 16, 64, 4096, dtype=dt), 16
             self.pred_cfg = EncoderConfig(384, 12, 12, 32, 1536, dtype=dt)
             self.max_tokens = 32 * 16 * 16
-        self.ac_cfg = EncoderConfig(32, 1, 2, 16, 64, dtype=dt) if small else EncoderConfig(1024, 24, 16, 64, 4096, dtype=dt)
+        self.ac_cfg = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt) if small else EncoderConfig(1024, 24, 16, 64, 4096, dtype=dt)
         self.action_dim, self.state_dim = 7, 7
 
     def get_graph_walk_graphs(self):

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, GraphNode, Loop, Sequential
-from .base import EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .dit import AdaLNDiT, DiTConfig, wan22_5b_config
 from .encoders import T5Encoder
 from .schedulers import FlowUniPC
@@ -115,10 +115,12 @@ class Wan22Model(Model):
         self.small = small
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         if small:
-            self.dit_cfg = DiTConfig(hidden_size=64, num_layers=2, num_heads=4, head_dim=16, ffn_dim=128, in_channels=4,
-                                     out_channels=4, text_dim=32, text_len=16, dtype=dt, rope_axes=(4, 6, 6))
+            k = small_scale()
+            self.dit_cfg = DiTConfig(hidden_size=64 * k, num_layers=2, num_heads=4, head_dim=16 * k, ffn_dim=128 * k,
+                                     in_channels=4, out_channels=4, text_dim=32 * k, text_len=16, dtype=dt,
+                                     rope_axes=(4 * k, 6 * k, 6 * k))
             self.vae_cfg = tiny_vae_config(3, 4)
-            self.text = dict(vocab_size=512, hidden=32, layers=1, heads=2, head_dim=16, ffn=64)
+            self.text = dict(vocab_size=512, hidden=32 * k, layers=1, heads=2, head_dim=16 * k, ffn=64 * k)
         else:
             self.dit_cfg = wan22_5b_config()
             self.vae_cfg = wan22_vae_config()

@@ -24,7 +24,7 @@ from ..ops import elementwise as ew
 from ..ops import gemm
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
-from .base import EngineType, Model
+from .base import small_scale, EngineType, Model
 from .encoders import AudioEncoder, EncoderConfig, log_mel_spectrogram
 from .llm_common import LMStateMachine, lm_walks
 from .submodule_base import ARNodeSubmodule, BATCHED_LOGITS, NodeSubmodule
@@ -183,8 +183,9 @@ class WhisperModel(Model):
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype, self.max_batch = small, dt, max_batch
         if small:
-            self.enc_cfg = EncoderConfig(64, 2, 4, 16, 128, dtype=dt, eps=1e-5)
-            self.dec_kw = dict(vocab=51866, hidden=64, layers=2, heads=4, ffn=128)
+            k = small_scale()
+            self.enc_cfg = EncoderConfig(64 * k, 2, 4, 16 * k, 128 * k, dtype=dt, eps=1e-5)
+            self.dec_kw = dict(vocab=51866, hidden=64 * k, layers=2, heads=4, ffn=128 * k)
             self.n_mels, self.max_audio = 16, 200
         else:
             self.enc_cfg = EncoderConfig(1280, 32, 20, 64, 5120, dtype=dt, eps=1e-5)
@@ -201,7 +202,7 @@ class WhisperModel(Model):
 
     def get_kv_cache_config(self):
         d = WhisperDecoder.__init__.__defaults__
-        H, heads, layers = (64, 4, 2) if self.small else (1280, 20, 32)
+        H, heads, layers = (64 * small_scale(), 4, 2) if self.small else (1280, 20, 32)
         return [KVCacheConfig(layers, heads, H // heads, max_seq_len=448, max_num_pages=16 if self.small else 256,
                               page_size=16 if self.small else 128, num_qo_heads=heads, nodes=["decoder"], dtype=self.dtype)]
 

@@ -80,6 +80,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     K = x.shape[-1]
     N = w.shape[0]
     assert w.shape[1] == K
+    if (K % 8 or N % 8) and epilogue != EPILOGUE_SWIGLU and residual is None and out is None:
+        # odd widths (a 7-wide action vector, a 10-wide head): zero-pad to the 16-byte granularity of the TMA tiles
+        pk, pn = (-K) % 8, (-N) % 8
+        xp = F.pad(x.reshape(-1, K), (0, pk))
+        wp = F.pad(w, (0, pk, 0, pn))
+        bp = F.pad(bias, (0, pn)) if bias is not None else None
+        y = linear(xp, wp, bp, None, epilogue, out_dtype, None, out_scale, force_splits)
+        return y[:, :N].reshape(*x.shape[:-1], N)
     x2 = x.reshape(-1, K)
     if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
         x2 = x2.contiguous()
