@@ -68,8 +68,8 @@ constexpr int BK = 64;   // bf16 elements per K block = 128 bytes = one swizzle 
 constexpr int UMMA_K = 16;
 
 __host__ __device__ constexpr int gemm_stage_bytes(int BN) { return BM * BK * 2 + BN * BK * 2; }
-__host__ __device__ constexpr int gemm_smem_bytes(int BN, int stages) {
-    return stages * gemm_stage_bytes(BN) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+__host__ __device__ constexpr int gemm_smem_bytes(int BN, int stages, int ksub = 1) {
+    return stages * ksub * gemm_stage_bytes(BN) + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
 
 // Apply bias / activation / residual to a run of 32 accumulator values and store them.
@@ -351,14 +351,20 @@ __device__ __noinline__ void copy_out_allreduce(const GemmParams& p, const float
     }
 }
 
-template <int BN, int STAGES, int MINB>
+// KSUB: 64-wide K blocks per pipeline stage. With KSUB = 1 every TMA box takes 128 bytes from each of 128 weight
+// rows that lie a whole row pitch apart, and the next 128 bytes of those rows are only asked for a stage later: a
+// weight-streaming (decode) GEMM then opens a DRAM page per 128 bytes and measured 1.3-2.2 TB/s. With KSUB = 2 or 4
+// one stage asks for 256 or 512 contiguous bytes of every row back to back.
+template <int BN, int STAGES, int MINB, int KSUB = 1>
 __global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                          const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int STAGE_BYTES = gemm_stage_bytes(BN);
-    constexpr int P_BYTES = BM * BK * 2;
+    constexpr int P_BYTES = BM * BK * 2;                 // one 64-wide P sub-tile
+    constexpr int Q_BYTES = BN * BK * 2;                 // one 64-wide Q sub-tile
+    constexpr int STAGE_BYTES = KSUB * (P_BYTES + Q_BYTES);
+    constexpr int Q_OFF = KSUB * P_BYTES;                // Q sub-tiles follow the P sub-tiles of the stage
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
@@ -368,8 +374,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int tile_p = blockIdx.x;
-    const int tile_q = blockIdx.y;
+    // Blocks are scheduled x-fastest. Taking (x, y) as the tile directly makes a wave of CTAs share ONE Q tile and
+    // stream the whole P operand past it, once per Q tile (measured: 3.2 GB of DRAM reads for 157 MB of operands
+    // on 16384 x 9216 x 3072). Instead a wave covers a compact block of the tile grid: groups of GROUP_P tile rows,
+    // inside a group the P index runs fastest, so a wave touches ~16 P tiles x ~9 Q tiles and L2 serves the re-use.
+    int tile_p = blockIdx.x, tile_q = blockIdx.y;
+    {
+        constexpr int GROUP_P = 16;
+        const int tiles_p = gridDim.x, tiles_q = gridDim.y;
+        if (tiles_p >= 2 * GROUP_P && tiles_q > 1) {
+            const int lin = blockIdx.y * tiles_p + blockIdx.x;
+            const int per_group = GROUP_P * tiles_q;
+            const int group = lin / per_group, within = lin - group * per_group;
+            const int p0 = group * GROUP_P;
+            const int gp = min(GROUP_P, tiles_p - p0);
+            tile_p = p0 + within % gp;
+            tile_q = within / gp;
+        }
+    }
     const int split = blockIdx.z;
     const int kb_begin = split * p.kblocks_per_split;
     int kb_end = kb_begin + p.kblocks_per_split;
@@ -410,37 +432,49 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             int issued = 0;
+            const int ngroups = (nkb + KSUB - 1) / KSUB;           // pipeline steps of up to KSUB K blocks
+            auto group_subs = [&](int g) { return (nkb - g * KSUB) < KSUB ? (nkb - g * KSUB) : KSUB; };
             // The weight operand does not depend on the previous kernel: when it is the P operand (decode), fill
             // the ring with weight tiles first, and only then wait for the predecessor before touching activations.
-            const int npre = p.swap ? (nkb < STAGES ? nkb : STAGES) : 0;
-            for (int i = 0; i < npre; ++i) {
-                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-                tma_load_2d(smem + i * STAGE_BYTES, &tmP, &full_bar[i], (kb_begin + i) * BK, p_row0);
+            const int npre = p.swap ? (ngroups < STAGES ? ngroups : STAGES) : 0;
+            for (int g = 0; g < npre; ++g) {
+                const int ns = group_subs(g);
+                mbar_expect_tx(&full_bar[g], ns * (P_BYTES + Q_BYTES));
+                for (int u = 0; u < ns; ++u)
+                    tma_load_2d(smem + g * STAGE_BYTES + u * P_BYTES, &tmP, &full_bar[g],
+                                (kb_begin + g * KSUB + u) * BK, p_row0);
             }
             pdl_wait();
-            for (int i = 0; i < npre; ++i)
-                tma_load_2d(smem + i * STAGE_BYTES + P_BYTES, &tmQ, &full_bar[i], (kb_begin + i) * BK, tile_q * BN);
+            for (int g = 0; g < npre; ++g) {
+                const int ns = group_subs(g);
+                for (int u = 0; u < ns; ++u)
+                    tma_load_2d(smem + g * STAGE_BYTES + Q_OFF + u * Q_BYTES, &tmQ, &full_bar[g],
+                                (kb_begin + g * KSUB + u) * BK, tile_q * BN);
+            }
             issued = npre;
-            for (int i = npre; i < nkb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
+            for (int g = npre; g < ngroups; ++g) {
+                const int s = g % STAGES;
+                const uint32_t ph = (g / STAGES) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1, p.wait_limit_ns)) {
-                    report_status(p.status, KID_GEMM, 1, i, s);
+                    report_status(p.status, KID_GEMM, 1, g, s);
                     flags[0] = 1;
                     break;
                 }
                 if (flags[0]) break;
                 uint8_t* sp = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                const int kx = (kb_begin + i) * BK;
-                tma_load_2d(sp, &tmP, &full_bar[s], kx, p_row0);
-                tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kx, tile_q * BN);
-                issued = i + 1;
+                const int ns = group_subs(g);
+                mbar_expect_tx(&full_bar[s], ns * (P_BYTES + Q_BYTES));
+                for (int u = 0; u < ns; ++u) {
+                    const int kx = (kb_begin + g * KSUB + u) * BK;
+                    tma_load_2d(sp + u * P_BYTES, &tmP, &full_bar[s], kx, p_row0);
+                    tma_load_2d(sp + Q_OFF + u * Q_BYTES, &tmQ, &full_bar[s], kx, tile_q * BN);
+                }
+                issued = g + 1;
             }
             if (flags[0]) {
                 // error path: let copies already in flight land before the CTA leaves
-                for (int i = (issued > STAGES ? issued - STAGES : 0); i < issued; ++i)
-                    mbar_wait(&full_bar[i % STAGES], (i / STAGES) & 1, 1000000ull);
+                for (int g = (issued > STAGES ? issued - STAGES : 0); g < issued; ++g)
+                    mbar_wait(&full_bar[g % STAGES], (g / STAGES) & 1, 1000000ull);
             }
         }
     } else if (warp == 1) {
@@ -448,23 +482,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1);
             bool ok = true;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (i / STAGES) & 1;
+            const int ngroups = (nkb + KSUB - 1) / KSUB;
+            for (int g = 0; g < ngroups; ++g) {
+                const int s = g % STAGES;
+                const uint32_t ph = (g / STAGES) & 1;
                 if (!mbar_wait(&full_bar[s], ph, p.wait_limit_ns)) {
-                    report_status(p.status, KID_GEMM, 2, i, s);
+                    report_status(p.status, KID_GEMM, 2, g, s);
                     flags[0] = 1;
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t sp = smem_u32(smem + s * STAGE_BYTES);
-                const uint64_t da = umma_smem_desc_sw128(sp);
-                const uint64_t db = umma_smem_desc_sw128(sp + P_BYTES);
+                const int ns = (nkb - g * KSUB) < KSUB ? (nkb - g * KSUB) : KSUB;
+                for (int u = 0; u < ns; ++u) {
+                    const uint64_t da = umma_smem_desc_sw128(sp + u * P_BYTES);
+                    const uint64_t db = umma_smem_desc_sw128(sp + Q_OFF + u * Q_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // +32 bytes per K slice inside the 128-byte swizzle atom (encoded >> 4)
-                    umma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // +32 bytes per K slice inside the 128-byte swizzle atom (encoded >> 4)
+                        umma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (g | u | k) != 0 ? 1u : 0u);
+                    }
                 }
                 umma_commit(&empty_bar[s]);
             }
@@ -561,20 +599,65 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <int BN, int STAGES, int MINB>
+template <int BN, int STAGES, int MINB, int KSUB = 1>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
-    constexpr int smem = gemm_smem_bytes(BN, STAGES);
+    constexpr int smem = gemm_smem_bytes(BN, STAGES, KSUB);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
         configured = true;
     }
-    cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
+    cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
     return 0;
+}
+
+// Tile configuration by (Q tile width, layout). Decode (swapped) tiles stream weights: MSTAR_GEMM_KSUB picks how many
+// 64-wide K blocks one pipeline stage fetches (1, 2, 4; 22 = two blocks per stage with two CTAs per SM).
+static int dispatch_tile(int bn, int swap, const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p,
+                         dim3 grid, cudaStream_t stream) {
+    static int ksub = -1;
+    if (ksub < 0) {
+        const char* e = getenv("MSTAR_GEMM_KSUB");
+        ksub = e ? atoi(e) : 2;      // measured on the 3B decode step: 5.99 ms (1), 5.80 (2), 5.83 (4), 6.05 (22)
+    }
+    if (swap && ksub == 2) {
+        switch (bn) {
+            case 16: return launch_gemm<16, 4, 1, 2>(tmP, tmQ, p, grid, stream);
+            case 32: return launch_gemm<32, 4, 1, 2>(tmP, tmQ, p, grid, stream);
+            case 64: return launch_gemm<64, 4, 1, 2>(tmP, tmQ, p, grid, stream);
+            case 128: return launch_gemm<128, 3, 1, 2>(tmP, tmQ, p, grid, stream);
+        }
+    } else if (swap && ksub == 22) {
+        switch (bn) {
+            case 16: return launch_gemm<16, 3, 2, 2>(tmP, tmQ, p, grid, stream);
+            case 32: return launch_gemm<32, 2, 2, 2>(tmP, tmQ, p, grid, stream);
+            case 64: return launch_gemm<64, 2, 2, 2>(tmP, tmQ, p, grid, stream);
+            case 128: return launch_gemm<128, 3, 1, 2>(tmP, tmQ, p, grid, stream);
+        }
+    } else if (swap && ksub == 4) {
+        switch (bn) {
+            case 16: return launch_gemm<16, 3, 1, 4>(tmP, tmQ, p, grid, stream);
+            case 32: return launch_gemm<32, 2, 1, 4>(tmP, tmQ, p, grid, stream);
+            case 64: return launch_gemm<64, 2, 1, 4>(tmP, tmQ, p, grid, stream);
+            case 128: return launch_gemm<128, 3, 1, 2>(tmP, tmQ, p, grid, stream);
+        }
+    }
+    switch (bn) {
+        // decode tiles: 4 stages keep a CTA under 100 KB so that two CTAs share an SM and one CTA's prologue /
+        // epilogue overlaps the other's weight stream
+        case 16: return launch_gemm<16, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 32: return launch_gemm<32, 5, 2>(tmP, tmQ, p, grid, stream);
+        case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
+        case 128:
+            if (swap) return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
+            return launch_gemm<128, 6, 1>(tmP, tmQ, p, grid, stream);
+        case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
+    }
+    return set_error("gemm: unsupported tile", cudaSuccess);
 }
 
 }  // namespace mstar
@@ -706,18 +789,7 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     if (make_tmap_2d_bf16(&tmP, Pp, rowsP, K, ldP, BM, BK)) return -1;
     if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
     dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
-    switch (bn) {
-        // decode tiles: 4 stages keep a CTA under 100 KB so that two CTAs share an SM and one CTA's prologue /
-        // epilogue overlaps the other's weight stream
-        case 16: return launch_gemm<16, 5, 2>(tmP, tmQ, p, grid, stream);
-        case 32: return launch_gemm<32, 5, 2>(tmP, tmQ, p, grid, stream);
-        case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
-        case 128:
-            if (swap) return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
-            return launch_gemm<128, 6, 1>(tmP, tmQ, p, grid, stream);
-        case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
-    }
-    return set_error("gemm: unsupported tile", cudaSuccess);
+    return dispatch_tile(bn, swap, tmP, tmQ, p, grid, stream);
 }
 
 // Grouped GEMM for mixture-of-experts layers (decode layout): rows of A are token copies sorted by expert in
@@ -775,6 +847,7 @@ MSTAR_API int mstar_moe_grouped_gemm(const void* A, const void* W, void* C, int 
 // library image instead of caller-provided memory.
 // ---------------------------------------------------------------------------------------------
 #include <stdio.h>
+#include <stdlib.h>
 #include "mstar_noalloc.h"
 
 namespace {

@@ -80,9 +80,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     K = x.shape[-1]
     N = w.shape[0]
     assert w.shape[1] == K
-    if (K % 8 or N % 8) and epilogue != EPILOGUE_SWIGLU and residual is None and out is None:
-        # odd widths (a 7-wide action vector, a 10-wide head): zero-pad to the 16-byte granularity of the TMA tiles
-        pk, pn = (-K) % 8, (-N) % 8
+    if (K % 8 or (N % 8 and N * K <= (1 << 22))) and epilogue != EPILOGUE_SWIGLU and residual is None and out is None:
+        # odd widths (a 7-wide action vector, a 10-wide head): zero-pad to the 16-byte granularity of the TMA tiles.
+        # Only small weights are padded on the fly (a copy per call); a large matrix with an odd row COUNT runs as
+        # it is (the kernel handles a ragged last tile), and an odd row LENGTH should be padded once at load time.
+        pk, pn = (-K) % 8, ((-N) % 8 if N * K <= (1 << 22) else 0)
         xp = F.pad(x.reshape(-1, K), (0, pk))
         wp = F.pad(w, (0, pk, 0, pn))
         bp = F.pad(bias, (0, pn)) if bias is not None else None
