@@ -10,6 +10,8 @@
 //
 // Reference counterparts: Triton _fused_sampling_prep_kernel (mstar/utils/sampling.py:32-161) followed by
 // FlashInfer top_p / top_k_top_p sampling from probs (mstar/utils/sampling.py:581-682).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -46,7 +48,9 @@ struct SampleParams {
     float* u_override;           // [B] uniform draws supplied by the caller (tests), or null
 };
 
-constexpr int SP_NT = 1024;
+constexpr int SP_NT = 512;        // threads per CTA
+constexpr int SP_NW = SP_NT / 32;
+constexpr int SP_CL = 8;          // CTAs per row (one thread-block cluster) for large vocabularies
 
 template <bool F32>
 __device__ __forceinline__ float load_logit(const void* base, long long i) {
@@ -54,18 +58,29 @@ __device__ __forceinline__ float load_logit(const void* base, long long i) {
     else return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
 }
 
+// One thread-block CLUSTER per row: CTA c of the cluster owns the contiguous vocabulary slice
+// [c * slice, (c + 1) * slice). Row-wide quantities (max, partition function, radix histograms, kept mass) are
+// combined by every CTA reading its peers' partial results from distributed shared memory after a cluster barrier;
+// every CTA then takes the same decision, so nothing has to be sent back.
 template <bool F32>
-__global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p, const int cl) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ unsigned long long sp_dyn[];                 // per-warp radix histograms (fixed-point mass)
-    unsigned long long* hist_mass = sp_dyn;                                        // [32 warps][256]
-    unsigned int* hist_cnt = reinterpret_cast<unsigned int*>(sp_dyn + (SP_NT / 32) * 256);   // [32 warps][256]
-    __shared__ float merged_mass[256];
+    unsigned long long* hist_mass = sp_dyn;                                        // [SP_NW][256]
+    unsigned int* hist_cnt = reinterpret_cast<unsigned int*>(sp_dyn + SP_NW * 256);   // [SP_NW][256]
+    __shared__ float merged_mass[256];      // this CTA's histogram of the current level (read by the peers)
     __shared__ int merged_cnt[256];
+    __shared__ float tot_mass[256];         // cluster totals
+    __shared__ int tot_cnt[256];
     __shared__ float red_f[32];
     __shared__ int red_i[32];
+    __shared__ float xf[4];                 // exchanged partials: [0] max, [1] sum, [2] kept mass
+    __shared__ int xi[4];                   // [0] argmax, [1] picked token (-1: none)
     __shared__ float sh_f[4];
     __shared__ int sh_i[4];
-    const int row = blockIdx.x;
+    const int crank = cl > 1 ? (int)cluster.block_rank() : 0;
+    const int row = blockIdx.x / cl;
     pdl_launch_dependents();
     pdl_wait();
     const int slot = p.row_slot ? p.row_slot[row] : row;
@@ -76,17 +91,22 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
     const unsigned char* seen = p.seen ? p.seen + (size_t)slot * p.V : nullptr;
     const bool greedy = temp <= 0.f;
     const float inv_t = greedy ? 1.f : 1.f / temp;
+    const int slice = (p.V + cl - 1) / cl;
+    const int v0 = crank * slice, v1 = min(p.V, v0 + slice);      // this CTA's slice of the vocabulary
 
     auto logit_at = [&](int i) -> float {
         float x = load_logit<F32>(lg, i);
         if (seen && pen != 1.0f && seen[i]) x = x > 0.f ? x / pen : x * pen;
         return x * inv_t;
     };
+    auto csync = [&]() { if (cl > 1) cluster.sync(); else __syncthreads(); };
+    auto peer_f = [&](float* ptr, int r) -> float { return cl > 1 ? *cluster.map_shared_rank(ptr, r) : *ptr; };
+    auto peer_i = [&](int* ptr, int r) -> int { return cl > 1 ? *cluster.map_shared_rank(ptr, r) : *ptr; };
 
     // ---- pass 1: max (and argmax for greedy rows) ----
     float mx = -INFINITY;
     int amx = 0x7fffffff;
-    for (int i = tid; i < p.V; i += SP_NT) {
+    for (int i = v0 + tid; i < v1; i += SP_NT) {
         const float x = logit_at(i);
         if (x > mx) { mx = x; amx = i; }
     }
@@ -99,67 +119,62 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
     if (lane == 0) { red_f[warp] = mx; red_i[warp] = amx; }
     __syncthreads();
     if (warp == 0) {
-        mx = red_f[lane]; amx = red_i[lane];
+        mx = lane < SP_NW ? red_f[lane] : -INFINITY;
+        amx = lane < SP_NW ? red_i[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float om = __shfl_xor_sync(0xffffffffu, mx, o);
             const int oi = __shfl_xor_sync(0xffffffffu, amx, o);
             if (om > mx || (om == mx && oi < amx)) { mx = om; amx = oi; }
         }
-        if (lane == 0) { sh_f[0] = mx; sh_i[0] = amx; }
+        if (lane == 0) { xf[0] = mx; xi[0] = amx; }
     }
-    __syncthreads();
-    mx = sh_f[0];
+    csync();
+    mx = -INFINITY; amx = 0x7fffffff;
+    for (int r = 0; r < cl; ++r) {
+        const float om = peer_f(&xf[0], r);
+        const int oi = peer_i(&xi[0], r);
+        if (om > mx || (om == mx && oi < amx)) { mx = om; amx = oi; }
+    }
     if (greedy) {
-        if (tid == 0) {
-            const int tok = sh_i[0];
-            p.out[row] = tok;
+        if (crank == 0 && tid == 0) {
+            p.out[row] = amx;
             if (p.out_prob) p.out_prob[row] = 1.0f;
-            if (p.seen) p.seen[(size_t)slot * p.V + tok] = 1;
+            if (p.seen) p.seen[(size_t)slot * p.V + amx] = 1;
         }
+        csync();                  // peers may still be reading this CTA's shared memory
         return;
     }
 
-    // ---- pass 2: partition function ----
-    float z = 0.f;
-    for (int i = tid; i < p.V; i += SP_NT) z += __expf(logit_at(i) - mx);
-    z = warp_sum(z);
-    if (lane == 0) red_f[warp] = z;
-    __syncthreads();
-    if (warp == 0) {
-        float t = red_f[lane];
-        t = warp_sum(t);
-        if (lane == 0) sh_f[1] = t;
-    }
-    __syncthreads();
-    z = sh_f[1];
     const float top_p = p.top_p ? p.top_p[slot] : 1.0f;
     int top_k = p.top_k ? p.top_k[slot] : 0;
     if (top_k <= 0 || top_k > p.V) top_k = p.V;
     const bool filter = (top_p < 1.0f) || (top_k < p.V);
     uint32_t thr_key = 0;          // keep keys >= thr_key
-    if (filter) {
-        // Three radix levels of 8 bits over the 24-bit key. Every warp owns a private 256-bin histogram
-        // (fixed-point mass, 2^-24 units, and count); lanes that hit the same bin are merged with
-        // match_any + reduce_add before ONE lane updates the bin, so no atomics and no contention, whatever
-        // the shape of the distribution.
-        const float need = top_p * z;
+    float z = 0.f;
+    // Three radix levels of 8 bits over the 24-bit key of e = exp(logit - max). Every warp owns a private 256-bin
+    // histogram (fixed-point mass, 2^-24 units, and count); lanes that hit the same bin are merged with
+    // match_any + reduce_add before ONE lane updates the bin, so no atomics and no contention, whatever the shape
+    // of the distribution. The first level also yields the partition function (the sum of all bins).
+    {
         unsigned long long* wmass = hist_mass + warp * 256;
         unsigned int* wcnt = hist_cnt + warp * 256;
         uint32_t prefix = 0;            // key bits decided so far (aligned to the top)
         float acc_mass = 0.f;           // mass / count of keys strictly above the undecided range
         int acc_cnt = 0;
-        const int iters = (p.V + SP_NT - 1) / SP_NT;
+        float need = 0.f;
+        const int iters = (v1 - v0 + SP_NT - 1) / SP_NT;
+        const int levels = filter ? 3 : 1;
 #pragma unroll 1
-        for (int level = 0; level < 3; ++level) {
+        for (int level = 0; level < levels; ++level) {
             const int shift = 16 - 8 * level;
             for (int i = lane; i < 256; i += 32) { wmass[i] = 0ull; wcnt[i] = 0u; }
             __syncwarp();
             for (int it = 0; it < iters; ++it) {
-                const int i = tid + it * SP_NT;
+                const int i = v0 + tid + it * SP_NT;
                 uint32_t bin = 0xffffffffu;
                 unsigned int fx = 0;
-                if (i < p.V) {
+                if (i < v1) {
                     const float e = __expf(logit_at(i) - mx);
                     const uint32_t key = __float_as_uint(e) >> 8;
                     const bool in_range = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
@@ -174,18 +189,34 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
                 __syncwarp();
             }
             __syncthreads();
-            // merge the 32 warp histograms: thread t < 256 owns bin t (results into warp 0's arrays)
-            if (tid < 256) {
+            if (tid < 256) {          // this CTA's histogram: thread t owns bin t
                 unsigned long long m = 0ull; unsigned int c = 0u;
-                for (int w = 0; w < SP_NT / 32; ++w) { m += hist_mass[w * 256 + tid]; c += hist_cnt[w * 256 + tid]; }
+                for (int w = 0; w < SP_NW; ++w) { m += hist_mass[w * 256 + tid]; c += hist_cnt[w * 256 + tid]; }
                 merged_mass[tid] = (float)m * (1.0f / 16777216.0f);
                 merged_cnt[tid] = (int)c;
             }
+            csync();
+            if (tid < 256) {          // cluster totals, computed redundantly by every CTA
+                float m = 0.f; int c = 0;
+                for (int r = 0; r < cl; ++r) { m += peer_f(&merged_mass[tid], r); c += peer_i(&merged_cnt[tid], r); }
+                tot_mass[tid] = m; tot_cnt[tid] = c;
+            }
             __syncthreads();
+            if (level == 0) {
+                if (warp == 0) {
+                    float t = 0.f;
+                    for (int i = lane; i < 256; i += 32) t += tot_mass[i];
+                    t = warp_sum(t);
+                    if (lane == 0) sh_f[1] = t;
+                }
+                __syncthreads();
+                z = sh_f[1];
+                need = top_p * z;
+            }
             if (tid == 0) {
                 float acc = acc_mass; int cnt = acc_cnt; int bsel = 255;
                 for (; bsel >= 0; --bsel) {
-                    const float mb = merged_mass[bsel]; const int cb = merged_cnt[bsel];
+                    const float mb = tot_mass[bsel]; const int cb = tot_cnt[bsel];
                     if (cb == 0) continue;
                     if (acc + mb >= need || cnt + cb >= top_k) break;     // the threshold lies inside this bin
                     acc += mb; cnt += cb;
@@ -197,9 +228,9 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
             prefix |= (uint32_t)sh_i[1] << shift;
             acc_mass = sh_f[2];
             acc_cnt = sh_i[2];
-            __syncthreads();
+            csync();                  // every peer has read merged_* before the next level rewrites them
         }
-        thr_key = prefix;
+        if (filter) thr_key = prefix;
     }
 
     // ---- draw ----
@@ -211,15 +242,14 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         philox4x32_10((uint32_t)off, (uint32_t)(off >> 32), 0u, 0u, (uint32_t)sd, (uint32_t)(sd >> 32), r);
         u = ((r[0] >> 8) + 0.5f) * (1.0f / 16777216.0f);
     }
-    // mass of the kept set, summed in walk order
-    const int chunk = (p.V + SP_NT - 1) / SP_NT;
-    const int i0 = tid * chunk, i1 = min(p.V, i0 + chunk);
+    // mass of the kept set, summed in walk (vocabulary) order: thread t owns a contiguous piece of the CTA's slice
+    const int chunk = (v1 - v0 + SP_NT - 1) / SP_NT;
+    const int i0 = min(v1, v0 + tid * chunk), i1 = min(v1, i0 + chunk);
     float local = 0.f;
     for (int i = i0; i < i1; ++i) {
         const float e = __expf(logit_at(i) - mx);
         if ((__float_as_uint(e) >> 8) >= thr_key) local += e;
     }
-    // block exclusive scan of `local`
     float incl = local;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -227,24 +257,28 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
         if (lane >= o) incl += t;
     }
     if (lane == 31) red_f[warp] = incl;
+    if (tid == 0) xi[1] = -1;
     __syncthreads();
     if (warp == 0) {
-        float w = red_f[lane];
+        float w = lane < SP_NW ? red_f[lane] : 0.f;
         float wi = w;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float t = __shfl_up_sync(0xffffffffu, wi, o);
             if (lane >= o) wi += t;
         }
-        red_f[lane] = wi - w;            // exclusive warp offsets
-        if (lane == 31) sh_f[0] = wi;    // total
+        if (lane < SP_NW) red_f[lane] = wi - w;     // exclusive warp offsets
+        if (lane == 31) xf[2] = wi;                 // kept mass of this CTA's slice
     }
-    __syncthreads();
-    const float total = sh_f[0];
-    const float excl = red_f[warp] + incl - local;
+    csync();
+    float before = 0.f, total = 0.f;                // kept mass of the lower slices / of the whole row
+    for (int r = 0; r < cl; ++r) {
+        const float m = peer_f(&xf[2], r);
+        if (r < crank) before += m;
+        total += m;
+    }
+    const float excl = before + red_f[warp] + incl - local;
     const float target = u * total;
-    if (tid == 0) sh_i[0] = -1;
-    __syncthreads();
     if (local > 0.f && target >= excl && target < excl + local) {
         float acc = excl;
         int pick = -1, last = -1;
@@ -257,34 +291,36 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p) {
             }
         }
         if (pick < 0) pick = last;
-        atomicMax(&sh_i[0], pick);
+        atomicMax(&xi[1], pick);
     }
-    __syncthreads();
-    if (tid == 0) {
-        int tok = sh_i[0];
-        if (tok < 0) tok = sh_i[0] = -2;   // rounding left the target outside every chunk: fall back below
-    }
-    __syncthreads();
-    if (sh_i[0] == -2) {
-        // fallback: last kept index (target == total up to rounding)
+    // rounding can leave the target outside every piece: remember the last kept index as the fallback
+    {
         int last = -1;
-        for (int i = i0; i < i1; ++i) {
-            const float e = __expf(logit_at(i) - mx);
-            if ((__float_as_uint(e) >> 8) >= thr_key) last = i;
+        if (local > 0.f)
+            for (int i = i1 - 1; i >= i0; --i) {
+                const float e = __expf(logit_at(i) - mx);
+                if ((__float_as_uint(e) >> 8) >= thr_key) { last = i; break; }
+            }
+        last = warp_max_i(last);
+        if (lane == 0) red_i[warp] = last;
+        __syncthreads();
+        if (tid == 0) {
+            int l = -1;
+            for (int w = 0; w < SP_NW; ++w) l = max(l, red_i[w]);
+            xi[2] = l;
         }
-        __syncthreads();
-        if (tid == 0) sh_i[0] = -1;
-        __syncthreads();
-        if (last >= 0) atomicMax(&sh_i[0], last);
-        __syncthreads();
     }
-    if (tid == 0) {
-        int tok = sh_i[0];
+    csync();
+    if (crank == 0 && tid == 0) {
+        int tok = -1, last = -1;
+        for (int r = 0; r < cl; ++r) { tok = max(tok, peer_i(&xi[1], r)); last = max(last, peer_i(&xi[2], r)); }
+        if (tok < 0) tok = last;
         if (tok < 0) tok = 0;
         p.out[row] = tok;
         if (p.out_prob) p.out_prob[row] = __expf(logit_at(tok) - mx) / total;
         if (p.seen) p.seen[(size_t)slot * p.V + tok] = 1;
     }
+    csync();                          // keep shared memory alive until rank 0 has read it
 }
 
 }  // namespace mstar
@@ -299,7 +335,7 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
     SampleParams p{logits, ld, is_f32, B, V, temperature, top_k, top_p, rep_penalty, seed, offset, seen, row_slot,
                    out, out_prob, u_override};
     cudaStream_t s = (cudaStream_t)stream_;
-    constexpr int smem = (SP_NT / 32) * 256 * 12;
+    constexpr int smem = SP_NW * 256 * 12;
     static bool configured = false;
     if (!configured) {
         cudaError_t e1 = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -307,7 +343,22 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
         if (e1 != cudaSuccess || e2 != cudaSuccess) return set_error("sample: cudaFuncSetAttribute failed", e1 != cudaSuccess ? e1 : e2);
         configured = true;
     }
-    cudaError_t e = is_f32 ? launch_pdl(sample_kernel<true>, dim3(B), dim3(SP_NT), smem, s, p)
-                           : launch_pdl(sample_kernel<false>, dim3(B), dim3(SP_NT), smem, s, p);
+    const int cl = V >= 16384 ? SP_CL : 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(B * cl);
+    cfg.blockDim = dim3(SP_NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = is_f32 ? cudaLaunchKernelEx(&cfg, sample_kernel<true>, p, cl)
+                           : cudaLaunchKernelEx(&cfg, sample_kernel<false>, p, cl);
     return e == cudaSuccess ? 0 : set_error("sample launch", e);
 }
