@@ -62,7 +62,8 @@ struct AttnSmem {
     static constexpr int V_BYTES = AT_BN * HD * 2;
     static constexpr int P_BYTES = AT_BM * AT_BN * 2;
     static constexpr int STAGE = K_BYTES + V_BYTES;
-    static constexpr int TOTAL = Q_BYTES + AT_STAGES * STAGE + P_BYTES + 1024 + 256;
+    static constexpr int XCH_BYTES = 2 * AT_BM * 4;   // per-row exchange between the two threads of a row
+    static constexpr int TOTAL = Q_BYTES + AT_STAGES * STAGE + P_BYTES + 1024 + 256 + XCH_BYTES;
 };
 
 // swizzled K-major byte offset of (row, 16-byte chunk c) in a [atoms][rows][128 B] operand tile
@@ -71,8 +72,14 @@ __device__ __forceinline__ uint32_t sw128_offset(int rows, int row, int chunk) {
     return (uint32_t)(atom * rows * 128 + row * 128 + ((cc ^ (row & 7)) << 4));
 }
 
+// 10 warps: TMA producer, UMMA issuer, and EIGHT softmax warps. A query row is shared by two threads (warps w and
+// w + 4 reach the same TMEM lane quarter): one takes key columns 0-63 of every S tile and output dims 0-63, the
+// other the upper halves. With one softmax warp per scheduler the kernel was bound by the issue latency of that
+// single warp's dependent instructions (tensor pipe 14-22 % busy); two warps per scheduler overlap each other.
+constexpr int AT_THREADS = 320;
+
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const AttnParams p) {
     using SM = AttnSmem<HD>;
@@ -95,6 +102,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     uint64_t* o_empty = bars + 12;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* sh = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort [1] req [2] tile-in-req [3] last
+    float* xch = reinterpret_cast<float*>(sP + SM::P_BYTES + 256);       // [2 halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = blockIdx.y;
@@ -114,8 +122,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         sh[0] = 0; sh[1] = req; sh[2] = tin; sh[3] = 0;
         for (int i = 0; i < 6; ++i) mbar_init(&bars[i], 1);     // k_full, v_full, kv_empty
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(&s_empty[0], 128); mbar_init(&s_empty[1], 128);
-        mbar_init(p_full, 128);
+        mbar_init(&s_empty[0], 256); mbar_init(&s_empty[1], 256);
+        mbar_init(p_full, 256);
         mbar_init(o_full, 1);
         mbar_init(o_empty, 128);
         mbar_fence_init();
@@ -163,12 +171,13 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     // ---- Q tile -> swizzled smem (softmax warps; each thread owns one row) ----
     if (warp >= 2) {
         const int r = (warp & 3) * 32 + lane;
+        const int half = (warp - 2) >> 2;
         const int tl = r / p.G, g = r - tl * p.G;
         const bool valid = r < nrows;
         const uint4* src = reinterpret_cast<const uint4*>(
             p.q + (size_t)(q_begin + tok0 + (valid ? tl : 0)) * p.q_tok_stride + (size_t)(kvh * p.G + g) * HD);
 #pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
+        for (int c = half * (HD / 16); c < (half + 1) * (HD / 16); ++c) {
             uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
             *reinterpret_cast<uint4*>(sQ + sw128_offset(AT_BM, r, c)) = v;
         }
@@ -270,7 +279,7 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 if (!ok) break;
                 if (!mbar_wait(p_full, i & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DENSE, 4, i, 0); ok = false; break; }
                 if (!mbar_wait(&v_full[s], (i / AT_STAGES) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DENSE, 5, i, 0); ok = false; break; }
-                if (i >= 1 && !mbar_wait(o_empty, (i - 1) & 1, p.wait_limit_ns)) { report_status(p.status, KID_ATTN_DENSE, 6, i, 0); ok = false; break; }
+                // (the softmax warps finished any rescaling of O before they arrived on p_full)
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(sKV + s * SM::STAGE + SM::K_BYTES);
                 // V tile: [d atoms][keys][64 d] rows of 128 B. MN-major descriptor: LBO = distance between the
@@ -280,7 +289,8 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                     uint64_t db = umma_smem_desc_sw128(v_addr + k * 2048);
                     db = (db & ~(uint64_t(0x3fff) << 16)) | (uint64_t((AT_BN * 128) >> 4) << 16);
                     const uint32_t poff = (k >> 2) * (AT_BM * 128) + (k & 3) * 32;
-                    umma_f16_ss(tmem_base + TMEM_O, umma_smem_desc_sw128(p_addr + poff), db, idesc_pv, k != 0 ? 1u : 0u);
+                    // O accumulates in TMEM over all KV tiles of the CTA
+                    umma_f16_ss(tmem_base + TMEM_O, umma_smem_desc_sw128(p_addr + poff), db, idesc_pv, (i | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(o_full);
                 umma_commit(&kv_empty[s]);
@@ -288,18 +298,24 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             if (!ok) sh[0] = 1;
         }
     } else {
-        // =========================== softmax + accumulate (128 threads, one row each) ===========================
+        // =========================== softmax (256 threads, two per row) ===========================
         const int q4 = warp & 3;
+        const int half = (warp - 2) >> 2;            // which 64 key columns / 64 output dims this thread owns
+        constexpr int HB = AT_BN / 2;                // key columns per thread
+        constexpr int HO = HD / 2;                   // output dims per thread
         const int r = q4 * 32 + lane;
         const bool row_valid = r < nrows;
         const bool warp_valid = q4 * 32 < nrows;
         const int tl = r / p.G, g = r - tl * p.G;
         const int qpos = qpos0 + tl;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        const int pair_bar = 2 + q4;                 // named barrier of the two warps that share these rows
+        // The running maximum m is the reference of the exponentials; it is only moved (and O, which accumulates in
+        // TMEM, rescaled) when a tile's maximum exceeds it by more than RESCALE_T in log2 units. Until then the
+        // probabilities may grow up to 2^RESCALE_T, which bf16 and the fp32 accumulators hold without loss, and a
+        // tile costs one TMEM read of S instead of two reads of S plus a read-modify of O.
+        constexpr float RESCALE_T = 8.0f;
+        float m = -INFINITY, l = 0.f;                // l: this thread's half of the row sum
         bool ok = true;
         for (int i = 0; i < ntiles && ok; ++i) {
             if (!mbar_wait(&s_full[i & 1], (i >> 1) & 1, p.wait_limit_ns)) {
@@ -307,115 +323,157 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 sh[0] = 1; ok = false; break;
             }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + ((i & 1) ? TMEM_S1 : TMEM_S0);
-            const int k0 = (jt0 + i) * AT_BN;
+            const uint32_t s_addr = lane_addr + ((i & 1) ? TMEM_S1 : TMEM_S0) + half * HB;
+            const int k0 = (jt0 + i) * AT_BN + half * HB;       // first key of this thread's columns
             // visible keys for this row: [lo, hi)
             int hi = p.causal ? (qpos + 1) : kv_len;
             if (hi > kv_len) hi = kv_len;
             int lo = p.window > 0 ? qpos - p.window + 1 : 0;
-            const bool need_mask = (k0 + AT_BN > hi) || (k0 < lo);
+            const bool need_mask = (k0 + HB > hi) || (k0 < lo);
+            uint32_t sv[HB];                          // this thread's half row of S, read from TMEM once
             float alpha = 1.f;
             if (warp_valid) {
-                // pass 1: row max
-                float mx = -INFINITY;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_BN; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(s_addr + c0, v);
-                    tmem_ld_wait();
-                    if (need_mask) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const int kp = k0 + c0 + c;
-                            if (kp < hi && kp >= lo) mx = fmaxf(mx, __uint_as_float(v[c]));
-                        }
-                    } else {
+                for (int c0 = 0; c0 < HB; c0 += 32) tmem_ld32(s_addr + c0, sv + c0);
+                tmem_ld_wait();
+            }
+            tc_fence_before();
+            mbar_arrive(&s_empty[i & 1]);             // the S buffer may be overwritten by QK of tile i + 2
+            float mx = -INFINITY;
+            if (warp_valid) {
+                if (need_mask) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
+                    for (int c = 0; c < HB; ++c) {
+                        const int kp = k0 + c;
+                        if (kp < hi && kp >= lo) mx = fmaxf(mx, __uint_as_float(sv[c]));
                     }
+                } else {
+                    // four independent chains instead of one long dependent chain
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < HB; c += 4) {
+                        m0 = fmaxf(m0, __uint_as_float(sv[c]));
+                        m1 = fmaxf(m1, __uint_as_float(sv[c + 1]));
+                        m2 = fmaxf(m2, __uint_as_float(sv[c + 2]));
+                        m3 = fmaxf(m3, __uint_as_float(sv[c + 3]));
+                    }
+                    mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                 }
                 mx *= p.scale_log2;   // scale > 0, so max commutes with the scaling
-                const float m_new = fmaxf(m, mx);
-                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
-                m = m_new;
-                // pass 2: probabilities -> smem (bf16, swizzled K-major), row sum
-                float rs = 0.f;
+            }
+            // the row maximum over both halves
+            xch[half * AT_BM + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, xch[(half ^ 1) * AT_BM + r]);
+            const bool move = warp_valid && (mx > m + RESCALE_T || (m == -INFINITY && mx != -INFINITY));
+            if (move) {
+                alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mx);
+                m = mx;
+            }
+            // PV of the previous tile must have finished before O is rescaled or P is overwritten in shared memory
+            if (i >= 1 && !mbar_wait(o_full, (i - 1) & 1, p.wait_limit_ns)) {
+                report_status(p.status, KID_ATTN_DENSE, 8, i, 0);
+                sh[0] = 1; ok = false; break;
+            }
+            tc_fence_after();
+            if (i >= 1 && warp_valid && __any_sync(0xffffffffu, move)) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                for (int c0 = 0; c0 < HO; c0 += 32) {
                     uint32_t v[32];
-                    tmem_ld32(s_addr + c0, v);
+                    tmem_ld32(lane_addr + TMEM_O + half * HO + c0, v);
                     tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                    tmem_st32(lane_addr + TMEM_O + half * HO + c0, v);
+                }
+                tmem_st_wait();
+            }
+            if (warp_valid) {
+                const float neg_m = (m == -INFINITY) ? 0.f : -m;
+                const float sc = p.scale_log2;
+                float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+                for (int c0 = 0; c0 < HB; c0 += 32) {
                     uint32_t w[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        float p0 = exp2f(__uint_as_float(v[c]) * p.scale_log2 - m_use);
-                        float p1 = exp2f(__uint_as_float(v[c + 1]) * p.scale_log2 - m_use);
+                        float p0 = ex2_approx(fmaf(__uint_as_float(sv[c0 + c]), sc, neg_m));
+                        float p1 = ex2_approx(fmaf(__uint_as_float(sv[c0 + c + 1]), sc, neg_m));
                         if (need_mask) {
                             const int kp = k0 + c0 + c;
                             if (!(kp < hi && kp >= lo)) p0 = 0.f;
                             if (!(kp + 1 < hi && kp + 1 >= lo)) p1 = 0.f;
                         }
                         w[c >> 1] = pack_bf16x2(p0, p1);
-                        // the sum uses the rounded values, so that l matches what the tensor core multiplies
-                        float2 pr = unpack_bf16x2(w[c >> 1]);
-                        rs += pr.x + pr.y;
+                        rs0 += p0;
+                        rs1 += p1;
                     }
                     if (row_valid) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
-                            *reinterpret_cast<uint4*>(sP + sw128_offset(AT_BM, r, (c0 >> 3) + q)) =
+                            *reinterpret_cast<uint4*>(sP + sw128_offset(AT_BM, r, ((half * HB + c0) >> 3) + q)) =
                                 make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
                     }
                 }
-                l = l * alpha + rs;
+                l = l * alpha + (rs0 + rs1);
             }
             tc_fence_before();
-            mbar_arrive(&s_empty[i & 1]);
             fence_proxy_async_smem();
             mbar_arrive(p_full);
-            // fold O_tile into the accumulator
-            if (!mbar_wait(o_full, i & 1, p.wait_limit_ns)) {
-                report_status(p.status, KID_ATTN_DENSE, 8, i, 0);
-                sh[0] = 1; ok = false; break;
+            // the exchange slots are rewritten in the next iteration: both readers must be done with them
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        }
+        // the row sum over both halves
+        xch[half * AT_BM + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l += xch[(half ^ 1) * AT_BM + r];
+        // the accumulator: wait for the last PV, then read this thread's half of O from TMEM once
+        float o[HO];
+#pragma unroll
+        for (int i = 0; i < HO; ++i) o[i] = 0.f;
+        if (ok && ntiles > 0) {
+            if (!mbar_wait(o_full, (ntiles - 1) & 1, p.wait_limit_ns)) {
+                report_status(p.status, KID_ATTN_DENSE, 9, ntiles, 0);
+                sh[0] = 1; ok = false;
             }
             tc_fence_after();
-            if (warp_valid) {
+            if (ok && warp_valid) {
 #pragma unroll
-                for (int c0 = 0; c0 < HD; c0 += 32) {
+                for (int c0 = 0; c0 < HO; c0 += 32) {
                     uint32_t v[32];
-                    tmem_ld32(lane_addr + TMEM_O + c0, v);
+                    tmem_ld32(lane_addr + TMEM_O + half * HO + c0, v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c0 + c] = o[c0 + c] * alpha + __uint_as_float(v[c]);
+                    for (int c = 0; c < 32; ++c) o[c0 + c] = __uint_as_float(v[c]);
                 }
             }
             tc_fence_before();
-            mbar_arrive(o_empty);
         }
 
-        // ---- epilogue ----
+        // ---- epilogue: every thread handles its HO output dims ----
         const size_t tok = (size_t)(q_begin + tok0 + tl);
         const int head = kvh * p.G + g;
         bool do_final = ok;
         if (ok && p.splits > 1) {
             if (row_valid) {
                 const size_t wrow = tok * p.Hq + head;
-                float* wo = p.ws_o + ((size_t)split * p.ws_rows + wrow) * HD;
+                float* wo = p.ws_o + ((size_t)split * p.ws_rows + wrow) * HD + half * HO;
 #pragma unroll
-                for (int c = 0; c < HD; c += 4) __stcg(reinterpret_cast<float4*>(wo + c), make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]));
-                float* wm = p.ws_ml + ((size_t)split * p.ws_rows + wrow) * 2;
-                __stcg(wm, m);
-                __stcg(wm + 1, l);
+                for (int c = 0; c < HO; c += 4) __stcg(reinterpret_cast<float4*>(wo + c), make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]));
+                if (half == 0) {
+                    float* wm = p.ws_ml + ((size_t)split * p.ws_rows + wrow) * 2;
+                    __stcg(wm, m);
+                    __stcg(wm + 1, l);
+                }
             }
             __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             const int cidx = blockIdx.x * p.Hkv + kvh;
             if (threadIdx.x == 64) {
                 unsigned int old = atomicAdd(&p.counters[cidx], 1u);
                 sh[3] = (old == (unsigned int)(p.splits - 1)) ? 1 : 0;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             do_final = sh[3] != 0;
             if (do_final) {
                 __threadfence();
@@ -425,16 +483,16 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                     for (int z = 0; z < p.splits; ++z) mg = fmaxf(mg, __ldcg(p.ws_ml + ((size_t)z * p.ws_rows + wrow) * 2));
                     const float mg_use = (mg == -INFINITY) ? 0.f : mg;
 #pragma unroll
-                    for (int c = 0; c < HD; ++c) o[c] = 0.f;
+                    for (int c = 0; c < HO; ++c) o[c] = 0.f;
                     l = 0.f;
                     for (int z = 0; z < p.splits; ++z) {
                         const float* wm = p.ws_ml + ((size_t)z * p.ws_rows + wrow) * 2;
                         const float mz = __ldcg(wm), lz = __ldcg(wm + 1);
                         const float wgt = (mz == -INFINITY) ? 0.f : exp2f(mz - mg_use);
                         l += lz * wgt;
-                        const float* wo = p.ws_o + ((size_t)z * p.ws_rows + wrow) * HD;
+                        const float* wo = p.ws_o + ((size_t)z * p.ws_rows + wrow) * HD + half * HO;
 #pragma unroll
-                        for (int c = 0; c < HD; c += 4) {
+                        for (int c = 0; c < HO; c += 4) {
                             float4 t = __ldcg(reinterpret_cast<const float4*>(wo + c));
                             o[c] += t.x * wgt; o[c + 1] += t.y * wgt; o[c + 2] += t.z * wgt; o[c + 3] += t.w * wgt;
                         }
@@ -446,13 +504,13 @@ attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         }
         if (do_final && row_valid) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            uint4* dst = reinterpret_cast<uint4*>(p.out + tok * p.o_tok_stride + (size_t)head * HD);
+            uint4* dst = reinterpret_cast<uint4*>(p.out + tok * p.o_tok_stride + (size_t)head * HD + half * HO);
 #pragma unroll
-            for (int c = 0; c < HD; c += 8) {
+            for (int c = 0; c < HO; c += 8) {
                 dst[c >> 3] = make_uint4(pack_bf16x2(o[c] * inv, o[c + 1] * inv), pack_bf16x2(o[c + 2] * inv, o[c + 3] * inv),
                                          pack_bf16x2(o[c + 4] * inv, o[c + 5] * inv), pack_bf16x2(o[c + 6] * inv, o[c + 7] * inv));
             }
-            if (p.lse_out) p.lse_out[tok * p.Hq + head] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            if (p.lse_out && half == 0) p.lse_out[tok * p.Hq + head] = (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
     }
     tc_fence_before();
@@ -473,7 +531,7 @@ static int launch_attn(const CUtensorMap& tmK, const CUtensorMap& tmV, const Att
         if (e != cudaSuccess) return set_error("attention: cudaFuncSetAttribute failed", e);
         configured = true;
     }
-    cudaError_t e = launch_pdl(attn_tcgen05_kernel<HD>, grid, dim3(192), smem, stream, tmK, tmV, p);
+    cudaError_t e = launch_pdl(attn_tcgen05_kernel<HD>, grid, dim3(AT_THREADS), smem, stream, tmK, tmV, p);
     return e == cudaSuccess ? 0 : set_error("attention: launch failed", e);
 }
 

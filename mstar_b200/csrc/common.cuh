@@ -270,6 +270,13 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // ---------------------------------------------------------------------------------------------
 // small math / packing helpers
 // ---------------------------------------------------------------------------------------------
+// 2^x in one MUFU instruction (flush-to-zero; exp2f() adds range fix-ups that triple the instruction count of a
+// softmax inner loop)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
