@@ -338,21 +338,32 @@ class Worker:
             for w in self.node_to_workers.get(e.next_node, []):
                 by_worker.setdefault(w, []).append(e)
         for w, es in by_worker.items():
-            if w == self.worker_id:
-                for e in es:
-                    self._ingest(pri, e)
-                continue
-            out_edges = []
+            # edges of a streaming connection belong to the CONSUMER partition's request state, also when producer
+            # and consumer partitions share this worker (colocated placements)
+            groups: dict[str, list[GraphEdge]] = {}
             for e in es:
-                c = e.clone(with_tensors=False)
-                c.tensor_info = [self.tensors.prepare_for_remote(ti, w) for ti in e.tensor_info]
-                out_edges.append(c)
-            part = pri.partition_name
-            if self.topology is not None:
-                for c in self.topology.outgoing(pri.partition_name):
-                    if any(e.name == c.edge_name for e in out_edges):
-                        part = c.to_partition
-            self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(pri.request_id, out_edges, None, part)))
+                part = pri.partition_name
+                if self.topology is not None:
+                    for c in self.topology.outgoing(pri.partition_name):
+                        if e.name == c.edge_name:
+                            part = c.to_partition
+                groups.setdefault(part, []).append(e)
+            for part, ges in groups.items():
+                if w == self.worker_id:
+                    target = self.requests.get((pri.request_id, part))
+                    if target is not None:
+                        for e in ges:
+                            self._ingest(target, e)
+                        self._refresh_ready(target)
+                    else:       # the consumer partition's NEW_REQUEST has not arrived yet: deliver through the mailbox
+                        self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(pri.request_id, ges, None, part)))
+                    continue
+                out_edges = []
+                for e in ges:
+                    c = e.clone(with_tensors=False)
+                    c.tensor_info = [self.tensors.prepare_for_remote(ti, w) for ti in e.tensor_info]
+                    out_edges.append(c)
+                self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(pri.request_id, out_edges, None, part)))
 
     def _broadcast_stops(self, pri: PerRequestInfo, stops: set) -> None:
         peers = {w for ws_ in pri.worker_graph_to_workers.values() for w in ws_ if w != self.worker_id}

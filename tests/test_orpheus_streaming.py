@@ -60,3 +60,16 @@ def test_prefill_decode_disaggregation_moves_the_kv_pages():
         finally:
             s.shutdown()
     assert len(outs[0]) > 0 and outs[0] == outs[1]
+
+
+def test_colocated_partitions_share_one_worker():
+    """LLM and codec partitions on the same worker: the stream goes to the codec partition's request state."""
+    cfg = dict(CFG, node_groups=[{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill", "decode"]},
+                                 {"node_names": ["snac_decoder"], "ranks": [0], "graph_walks": ["snac_chunk"]}])
+    s = APIServer(cfg, in_process=True).start(120)
+    try:
+        rid = s.submit_request("hello there", output_modalities=["audio"], model_kwargs=dict(max_tokens=63, ignore_eos=True))
+        sizes = [len(c.data) for c in s.iter_result_chunks(rid, 300)]
+        assert sizes.count(4096) >= 5 and sum(sizes) >= 4096 * 8, sizes
+    finally:
+        s.shutdown()
