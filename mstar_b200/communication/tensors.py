@@ -33,6 +33,7 @@ class TensorStore:
         self._ref: dict[str, int] = {}
         self._persist: set[str] = set()
         self._by_request: dict[str, set[str]] = {}
+        self._owner: dict[str, str] = {}
         self._lock = threading.Lock()
 
     def put(self, request_id: str, t: torch.Tensor, uuid: str | None = None, refs: int = 1, persist: bool = False) -> str:
@@ -43,6 +44,7 @@ class TensorStore:
             if persist:
                 self._persist.add(uuid)
             self._by_request.setdefault(request_id, set()).add(uuid)
+            self._owner[uuid] = request_id
         return uuid
 
     def get(self, uuid: str) -> torch.Tensor | None:
@@ -70,18 +72,16 @@ class TensorStore:
         with self._lock:
             if uuid not in self._t:
                 return False
-            for s in self._by_request.values():
-                s.discard(uuid)
+            old = self._owner.get(uuid)
+            if old is not None and old in self._by_request:
+                self._by_request[old].discard(uuid)
             self._by_request.setdefault(owner, set()).add(uuid)
+            self._owner[uuid] = owner
             self._ref[uuid] = max(0, self._ref.get(uuid, 0)) + extra_refs
             return True
 
     def owner_of(self, uuid: str) -> str | None:
-        with self._lock:
-            for o, s in self._by_request.items():
-                if uuid in s:
-                    return o
-        return None
+        return self._owner.get(uuid)
 
     def unpersist(self, uuid: str) -> None:
         with self._lock:
@@ -93,8 +93,11 @@ class TensorStore:
         self._t.pop(uuid, None)
         self._ref.pop(uuid, None)
         self._persist.discard(uuid)
-        for s in self._by_request.values():
-            s.discard(uuid)
+        owner = self._owner.pop(uuid, None)
+        if owner is not None:
+            s = self._by_request.get(owner)
+            if s is not None:
+                s.discard(uuid)
 
     def remove_request(self, request_id: str) -> int:
         with self._lock:
@@ -103,6 +106,7 @@ class TensorStore:
                 self._t.pop(u, None)
                 self._ref.pop(u, None)
                 self._persist.discard(u)
+                self._owner.pop(u, None)
             return len(ids)
 
     def __len__(self) -> int:

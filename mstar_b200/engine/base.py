@@ -34,6 +34,7 @@ class NodeOutput:
     graph_walk: str
     outputs: dict[str, dict[str, torch.Tensor]] = field(default_factory=dict)   # request_id -> edge name -> tensor
     stop_loops: dict[str, set] = field(default_factory=dict)                    # request_id -> loop names
+    iterations: dict[str, int] = field(default_factory=dict)    # request_id -> loop iterations this execution covered
     failed_requests: dict[str, str] = field(default_factory=dict)
     allocation_failed: bool = False
     allocation_failed_requests: list[str] = field(default_factory=list)
@@ -46,17 +47,31 @@ class BaseEngine:
         self.node_names = list(node_names)
         self.device = torch.device(device)
         self.submodules: dict[str, object] = {}
+        self.phase_s = dict(prepare=0.0, plan=0.0, forward=0.0, postprocess=0.0)
 
     # template ------------------------------------------------------------------------------------
     def execute_batch(self, batch: NodeBatch) -> NodeOutput:
+        import time
+        t0 = time.perf_counter()
         prepared = self.prepare_batch(batch)
         out = NodeOutput(batch.node_name, batch.graph_walk, failed_requests=dict(prepared.failed_requests))
         if not prepared.request_ids:
             return out
+        t1 = time.perf_counter()
         planned = self.plan(prepared)
+        t2 = time.perf_counter()
         raw = self.execute_forward(planned)
+        t3 = time.perf_counter()
         self.postprocess(planned, raw, out)
+        t4 = time.perf_counter()
         self.finalize_batch(planned, out)
+        # host seconds of every phase (the forward's number is launch time only unless the phase synchronises)
+        ph = self.phase_s
+        ph["prepare"] += t1 - t0
+        ph["plan"] += t2 - t1
+        ph["forward"] += t3 - t2
+        ph["postprocess"] += t4 - t3
+        out.timings.update(prepare_s=t1 - t0, plan_s=t2 - t1, forward_s=t3 - t2, postprocess_s=t4 - t3)
         return out
 
     def prepare_batch(self, batch: NodeBatch) -> PreparedBatch:

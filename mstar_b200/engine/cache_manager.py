@@ -204,6 +204,12 @@ class BatchedCacheManager:
                            labels=list(labels), q_lens=list(q_lens), write_cache=write_cache)
         return ctx
 
+    def plan_snapshot(self, slot: int) -> torch.Tensor:
+        return self._slots[slot].dev.clone()
+
+    def plan_restore(self, slot: int, saved: torch.Tensor) -> None:
+        self._slots[slot].dev.copy_(saved)
+
     def advance_seq_lens(self, ctx: BatchContext, counts: list[int] | None = None) -> None:
         """Host-side bookkeeping after a forward that wrote K/V: seq_len += tokens written."""
         if not ctx.write_cache:
@@ -216,4 +222,5 @@ class BatchedCacheManager:
         """Decode only (one token per entry): kv_lens += 1, positions/cache slots move on, next input ids = the
         sampled tokens. Padded entries (kv_len 0 and token_req -1) are advanced too but stay without cache
         writes. Part of the captured step."""
-        ew_ops.advance_decode(ctx.plan.kv_lens, ctx.positions, ctx.cache_pos, input_ids, sampled)
+        B = ctx.batch
+        ew_ops.advance_decode(ctx.plan.kv_lens[:B], ctx.positions, ctx.cache_pos[:B], input_ids, sampled)

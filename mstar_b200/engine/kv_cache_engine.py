@@ -12,6 +12,8 @@ in-graph sampling (mstar/engine/cuda_graph_runner.py:769-850,1308-1534,1866-1989
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..models.submodule_base import BATCHED_LOGITS, ModelInputsFromEngine
@@ -28,8 +30,13 @@ CAPTURE_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64]
 class KVCacheEngine(BaseEngine):
     def __init__(self, node_names, device, kv_config: KVCacheConfig, *, vocab_size: int, max_batch: int = 64,
                  max_tokens: int = 16384, n_pos_axes: int = 1, group: int = 1, use_cuda_graphs: bool | None = None,
-                 tp_group=None, track_seen: bool = True):
+                 tp_group=None, track_seen: bool = True, decode_burst: int = 1):
         super().__init__(node_names, device)
+        # decode burst: one node execution replays the captured decode step up to this many times back to back
+        # (sampled tokens feed the next replay on the device), so the host-side cost of scheduling, routing and
+        # bookkeeping is paid once per burst instead of once per token
+        self.decode_burst = max(1, int(os.environ.get("MSTAR_DECODE_BURST", decode_burst)))
+        self._burst_buf = torch.zeros((self.decode_burst, max_batch), dtype=torch.int64, device=torch.device(device))
         self.kv_config = kv_config
         self.cache = BatchedCacheManager(kv_config, device, max_batch=max_batch, max_tokens=max_tokens + max_batch,
                                          n_pos_axes=n_pos_axes)
@@ -37,6 +44,11 @@ class KVCacheEngine(BaseEngine):
         self.max_batch, self.group = max_batch, group
         self.tp_group = tp_group
         self.use_graphs = (self.device.type == "cuda") if use_cuda_graphs is None else (use_cuda_graphs and self.device.type == "cuda")
+        # CPU stand-in for captured graphs (tests of the bucketed decode path and of decode bursts without a GPU):
+        # "capture" keeps the step closure, "replay" calls it
+        self.emulate_graphs = self.device.type != "cuda" and bool(os.environ.get("MSTAR_EMULATE_GRAPHS"))
+        if self.emulate_graphs and use_cuda_graphs is not False:
+            self.use_graphs = True
         self._graphs: dict[tuple, tuple] = {}
         self._static_ids = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
         self._static_tok = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
@@ -133,13 +145,17 @@ class KVCacheEngine(BaseEngine):
             custom = torch.cat([ni.custom_pos_ids.reshape(ni.custom_pos_ids.shape[0] if ni.custom_pos_ids.dim() > 1 else 1, -1)
                                 for ni in prepared.node_inputs], dim=-1)
         splits = None
+        burst = 1
         if bucket is not None:
             splits = attn_ops.choose_splits(bucket, self.kv_config.num_kv_heads, bucket, self.kv_config.max_seq_len,
                                             sm_count=3 * 148)
+            if self.decode_burst > 1:       # no request may run past its loop budget inside the burst
+                burst = max(1, min([self.decode_burst] + [int(ni.kwargs.get("_loop_remaining", 1))
+                                                           for ni in prepared.node_inputs]))
         ctx = self.cache.plan(prepared.request_ids, q_lens, labels=labels, row_slots=slots, pad_to_batch=bucket,
                               group=self.group, slot=0 if bucket is not None else 1, custom_positions=custom,
-                              splits=splits)
-        prepared.ctx, prepared.bucket, prepared.q_lens = ctx, bucket, q_lens
+                              splits=splits, lookahead_tokens=burst - 1)
+        prepared.ctx, prepared.bucket, prepared.q_lens, prepared.burst = ctx, bucket, q_lens, burst
         return prepared
 
     def _forward_logits(self, sub, walk, ei, node_inputs):
@@ -165,11 +181,19 @@ class KVCacheEngine(BaseEngine):
                 entry = self._graphs.get(key)
                 if entry is None:
                     entry = self._capture(key, sub, b.graph_walk, ei, planned)
-                entry[0].replay()
-                self.graph_hits += 1
+                k = getattr(planned, "burst", 1)
+                for j in range(k):
+                    entry[0].replay()           # the graph leaves the plan advanced and the sampled ids as next input
+                    self.graph_hits += 1
+                    if k > 1:
+                        self._burst_buf[j, :B].copy_(self._static_tok[:B])
                 tokens = self._static_tok[:B].clone()
-                raw = {"tokens": tokens, "extra": {k: v[:B].clone() if isinstance(v, torch.Tensor) else v
-                                                   for k, v in entry[1].items()}}
+                raw = {"tokens": tokens, "extra": {k_: v[:B].clone() if isinstance(v, torch.Tensor) else v
+                                                   for k_, v in entry[1].items()}}
+                if k > 1:
+                    raw["burst"] = self._burst_buf[:k, :B].t().contiguous()      # [B, k]
+                    self.cache.advance_seq_lens(ctx, counts=[k] * len(ctx.q_lens))
+                    return raw
             else:
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 outs = sub.forward_batched(b.graph_walk, ei, planned.node_inputs)
@@ -200,10 +224,13 @@ class KVCacheEngine(BaseEngine):
         plan slot; outputs: the static token buffer (+ any extra tensors the node returns)."""
         Bp = planned.bucket
         ctx = planned.ctx
-        attn_ops.reserve_scratch(self.device, Bp * max(1, self.kv_config.num_qo_heads), self.kv_config.head_dim,
-                                 max(1, ctx.plan.splits), Bp * self.kv_config.num_kv_heads)
+        if self.device.type == "cuda":
+            attn_ops.reserve_scratch(self.device, Bp * max(1, self.kv_config.num_qo_heads), self.kv_config.head_dim,
+                                     max(1, ctx.plan.splits), Bp * self.kv_config.num_kv_heads)
         saved_off = self.sampler.offset.clone()
         saved_seen = None if self.sampler.seen is None else self.sampler.seen.clone()
+        saved_plan = self.cache.plan_snapshot(0)
+        saved_ids = self._static_ids.clone()
         # device state that the node carries from step to step: the warm-up and capture runs must not advance it
         node_state = list(sub.capture_state()) if hasattr(sub, "capture_state") else []
         saved_state = [t.clone() for t in node_state]
@@ -215,8 +242,22 @@ class KVCacheEngine(BaseEngine):
             outs = sub.forward_graph(walk, ei, self._static_ids[:Bp], ctx)
             self.sampler.sample(outs[BATCHED_LOGITS], ctx.row_slot, out=self._static_tok[:Bp], advance=False)
             self.sampler.offset.index_add_(0, ctx.row_slot.long(), torch.ones(Bp, dtype=torch.int64, device=self.device))
+            # leave the device plan one token further and the sampled ids as the next input: a following replay
+            # (decode burst) continues without the host; a following plan() simply rewrites the plan
+            self.cache.advance_on_device(ctx, self._static_ids[:Bp], self._static_tok[:Bp])
             return {k: v for k, v in outs.items() if k != BATCHED_LOGITS}
 
+        if self.emulate_graphs:
+            class _Eager:
+                def __init__(self, fn):
+                    self.fn, self.extra = fn, {}
+
+                def replay(self):
+                    self.extra.update(self.fn())
+            g = _Eager(body)
+            extra = g.extra
+            self._graphs[key] = (g, extra)
+            return self._graphs[key]
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -230,6 +271,8 @@ class KVCacheEngine(BaseEngine):
         self.sampler.offset.copy_(saved_off)
         if saved_seen is not None:
             self.sampler.seen.copy_(saved_seen)
+        self.cache.plan_restore(0, saved_plan)
+        self._static_ids.copy_(saved_ids)
         for t, sv in zip(node_state, saved_state):
             t.copy_(sv)
         self._graphs[key] = (g, extra)
@@ -239,7 +282,9 @@ class KVCacheEngine(BaseEngine):
         b = planned.batch
         sub = self.submodules[b.node_name]
         tokens = raw.get("tokens")
-        host_tokens = tokens.tolist() if tokens is not None else None      # one D2H read per step
+        burst = raw.get("burst")
+        burst_host = burst.tolist() if burst is not None else None          # one D2H read per execution
+        host_tokens = tokens.tolist() if tokens is not None and burst is None else None
         for i, (rid, ni) in enumerate(zip(planned.request_ids, planned.node_inputs)):
             try:
                 if "per_request" in raw:
@@ -247,11 +292,27 @@ class KVCacheEngine(BaseEngine):
                 else:
                     r = {k: (v[i] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == len(planned.request_ids) else v)
                          for k, v in raw.get("extra", {}).items()}
-                if tokens is not None:
+                stops = None
+                if burst_host is not None:
+                    toks, n_valid = burst_host[i], len(burst_host[i])
+                    for j, t in enumerate(toks):        # cut the burst at the request's stop token
+                        stops = sub.check_stop(rid, b.fwd_infos[rid], {"new_token_host": t})
+                        if stops:
+                            n_valid = j + 1
+                            break
+                    if n_valid < len(toks):             # the positions written past the stop do not count
+                        label = planned.ctx.labels[i] if i < len(planned.ctx.labels) else "main"
+                        self.cache.alloc.get_state(rid, label).seq_len -= len(toks) - n_valid
+                    r["new_token"] = burst[i, n_valid - 1:n_valid]
+                    r["new_token_host"] = toks[n_valid - 1]
+                    r["burst_host"] = toks[:n_valid]
+                    out.iterations[rid] = n_valid
+                elif tokens is not None:
                     r["new_token"] = tokens[i:i + 1]
                     r["new_token_host"] = host_tokens[i]
                 out.outputs[rid] = sub.postprocess(rid, b.fwd_infos[rid], r, ni)
-                stops = sub.check_stop(rid, b.fwd_infos[rid], r)
+                if stops is None:
+                    stops = sub.check_stop(rid, b.fwd_infos[rid], r)
                 if stops:
                     out.stop_loops[rid] = set(stops)
             except Exception as e:  # noqa: BLE001

@@ -156,10 +156,13 @@ class WalkState:
         if sc is not None:
             sc.finish = True
 
-    def complete(self, node: str, outputs: list[GraphEdge] | None = None) -> Completion:
+    def complete(self, node: str, outputs: list[GraphEdge] | None = None, iterations: int = 1) -> Completion:
         """Node finished its forward for this iteration; ``outputs`` are its declared output edges with
-        tensor_info filled in (defaults to the declaration's edges)."""
+        tensor_info filled in (defaults to the declaration's edges). ``iterations`` > 1: the execution covered
+        that many iterations of the node's loop at once (a decode burst); the loop counter moves accordingly."""
         st = self.nodes[node]
+        if iterations > 1 and st.scope.loop is not None:
+            st.scope.curr_iter += iterations - 1
         res = Completion()
         outputs = list(st.decl.outputs) if outputs is None else list(outputs)
         st.running = False

@@ -95,7 +95,8 @@ def orpheus_tokens_to_codes(tokens: torch.Tensor, base_id: int, codebook_size: i
     t = tokens[:, :Fr * 7].reshape(B, Fr, 7).long()
     slot = torch.arange(7, device=tokens.device)
     c = (t - base_id - 10 - slot * codebook_size) % codebook_size
-    return [c[:, :, 0], c[:, :, [1, 4]].reshape(B, -1), c[:, :, [2, 3, 5, 6]].reshape(B, -1)]
+    # (slices, not index lists: the function also runs inside CUDA-graph capture, where host index data cannot be copied)
+    return [c[:, :, 0], c[:, :, 1:5:3].reshape(B, -1), torch.cat([c[:, :, 2:4], c[:, :, 5:7]], dim=2).reshape(B, -1)]
 
 
 class Code2Wav(nn.Module):

@@ -30,8 +30,15 @@ class DecoderSubmodule(ARNodeSubmodule):
         return True
 
     def postprocess(self, request_id, request_info, outputs, inputs):
-        tok = outputs["new_token"].to(torch.int64)
-        return {self.token_edge: tok, "tok": tok, "last_token": tok}
+        tok = outputs["new_token"].to(torch.int64)          # device view: feeds the next step
+        host = outputs.get("new_token_host")
+        # what leaves the node (client, stream buffers of other partitions) is a host tensor: the value was read back
+        # with the batch anyway, and consumers then never issue per-token device ops
+        if outputs.get("burst_host") is not None:           # a decode burst: all of its tokens leave together
+            out_tok = torch.tensor([int(t) for t in outputs["burst_host"]], dtype=torch.int64)
+        else:
+            out_tok = torch.tensor([int(host)], dtype=torch.int64) if host is not None else tok
+        return {self.token_edge: out_tok, "tok": tok, "last_token": tok}
 
     def check_stop(self, request_id, request_info, outputs):
         sc = (request_info.sampling_config or {}).get("main", {})

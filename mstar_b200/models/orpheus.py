@@ -39,20 +39,48 @@ class SnacSubmodule(NodeSubmodule):
     def get_stateless_flavor(self):
         return "audio_codec"
 
-    def forward(self, graph_walk, engine_inputs, ni, **kw):
+    def max_batch_size(self, graph_walk):
+        return 64
+
+    @staticmethod
+    def _tokens(ni) -> torch.Tensor:
         toks = ni.tensor_inputs.get("audio_tokens", [])
-        t = torch.cat([x.reshape(-1) for x in toks]) if toks else torch.zeros(0, dtype=torch.int64)
-        md = ni.kwargs
-        n = (t.numel() // 7) * 7
-        if n == 0:
-            return {"audio": torch.zeros(0), "final": bool(md.get("final_chunk"))}
-        codes = orpheus_tokens_to_codes(t[:n].reshape(1, n).to(self.device), self.base_id)
+        t = torch.cat([x.reshape(-1) for x in toks]).cpu() if toks else torch.zeros(0, dtype=torch.int64)
+        return t[:(t.numel() // 7) * 7]
+
+    def _decode(self, tokens: torch.Tensor, runner) -> torch.Tensor:
+        """tokens [B, n] (n a multiple of 7) -> waveforms [B, n / 7 * 2048]; replayed from a CUDA graph per shape."""
+        def fn(tk):
+            return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+        tk = tokens.to(self.device)
         with torch.no_grad():
-            wav = self.dec(codes)[0]
-        frames = n // 7
-        # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows yield all
-        out = wav[2048:4096] if frames == 4 and not md.get("final_chunk") else wav
-        return {"audio": out.float().cpu(), "final": bool(md.get("final_chunk"))}
+            if runner is not None and tk.is_cuda:
+                return runner.run(("snac", tuple(tk.shape)), fn, [tk]).clone()
+            return fn(tk)
+
+    def forward(self, graph_walk, engine_inputs, ni, **kw):
+        return self.forward_batched(graph_walk, engine_inputs, [ni])[0]
+
+    def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
+        """Requests whose chunks have the same length are decoded as one batch (streams that decode in lockstep
+        hand in their 28-token windows at the same step)."""
+        runner = (engine_inputs.preallocated_buffers or {}).get("graph_runner")
+        toks = [self._tokens(ni) for ni in inputs]
+        outs: list[dict | None] = [None] * len(inputs)
+        by_len: dict[int, list[int]] = {}
+        for i, t in enumerate(toks):
+            if t.numel() == 0:
+                outs[i] = {"audio": torch.zeros(0), "final": bool(inputs[i].kwargs.get("final_chunk"))}
+            else:
+                by_len.setdefault(t.numel(), []).append(i)
+        for n, idx in by_len.items():
+            wav = self._decode(torch.stack([toks[i] for i in idx]), runner).float().cpu()
+            for row, i in enumerate(idx):
+                final = bool(inputs[i].kwargs.get("final_chunk"))
+                # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows all
+                w = wav[row, 2048:4096] if n == 28 and not final else wav[row]
+                outs[i] = {"audio": w.contiguous(), "final": final}
+        return outs
 
     def postprocess(self, request_id, request_info, outputs, inputs):
         return {"audio": outputs["audio"]}
@@ -109,7 +137,9 @@ class OrpheusModel(Model):
 
     def get_engine_hints(self, node):
         c = self.cfg
-        return dict(vocab_size=c.vocab_size, group=c.num_heads // c.num_kv_heads, max_tokens=16384, track_seen=True)
+        # one audio frame (7 tokens) per node execution: the codec consumes whole frames anyway
+        return dict(vocab_size=c.vocab_size, group=c.num_heads // c.num_kv_heads, max_tokens=16384, track_seen=True,
+                    decode_burst=7)
 
     def get_autocast_dtype(self):
         return self.cfg.dtype

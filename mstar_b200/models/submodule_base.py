@@ -110,8 +110,12 @@ class ARNodeSubmodule(NodeSubmodule):
     def prepare_inputs(self, graph_walk: str, fwd_info, inputs: dict[str, list[torch.Tensor]]) -> ARNodeInputs:
         ids = None
         for key in ("input_ids", "tok", "new_token"):
-            if key in inputs and inputs[key]:
-                ids = torch.cat([t.reshape(-1) for t in inputs[key]]).to(torch.int64)
+            ts = inputs.get(key)
+            if ts:
+                # one tensor (every decode step): no concatenation kernel, no copy
+                ids = ts[0].reshape(-1) if len(ts) == 1 else torch.cat([t.reshape(-1) for t in ts])
+                if ids.dtype != torch.int64:
+                    ids = ids.to(torch.int64)
                 break
         return ARNodeInputs(fwd_info.request_id, graph_walk, inputs, dict(fwd_info.step_metadata or {}),
                             input_seq_len=0 if ids is None else int(ids.numel()), input_ids=ids)

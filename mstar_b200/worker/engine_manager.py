@@ -52,7 +52,8 @@ class EngineManager:
                                 max_tokens=sub_info.get("max_tokens", 16384),
                                 n_pos_axes=sub_info.get("n_pos_axes", 1), group=sub_info.get("group", 1),
                                 use_cuda_graphs=use_cuda_graphs, tp_group=tp_group,
-                                track_seen=sub_info.get("track_seen", True))
+                                track_seen=sub_info.get("track_seen", True),
+                                decode_burst=int(sub_info.get("decode_burst", 1)))
             eng.load_model(model, tp_group=tp_group, sp_group=sp_group)
             self.engines.append(eng)
             for n in mine:

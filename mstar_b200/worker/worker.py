@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import logging
 import threading
+import os
 import time
 import traceback
 from concurrent.futures import ThreadPoolExecutor
@@ -79,6 +80,10 @@ class Worker:
         self._last_beat = time.monotonic()
         self.phase_times: dict[str, list[float]] = {}
         self.iterations = 0
+        self._streaming_requests: set[tuple[str, str]] = set()      # request states that own stream buffers
+        # host time by phase of the main loop (seconds): where a step's latency goes when the GPU is not the limit
+        self.phase_s = dict(wait=0.0, messages=0.0, streams=0.0, finish=0.0, build=0.0, execute=0.0)
+        self.batches_by_node: dict[str, list] = {}
 
     # ------------------------------------------------------------------ messages
     def _process_messages(self, msgs: list[Message]) -> None:
@@ -154,6 +159,8 @@ class Worker:
             if c.edge_name not in pri.stream_buffers:
                 pri.stream_buffers[c.edge_name] = StreamBuffer(pri.request_id, c.edge_name, c.from_partition,
                                                                c.chunk_policy_factory())
+        if pri.stream_buffers:
+            self._streaming_requests.add((pri.request_id, pri.partition_name))
 
     def _on_input_signals(self, b: ipc.InputSignals) -> None:
         pri = self.requests.get((b.request_id, b.partition_name))
@@ -173,12 +180,23 @@ class Worker:
         sb = pri.stream_buffers.get(e.name) if e.is_streaming else None
         if sb is not None:
             for ti in e.tensor_info:
-                sb.put(ti.uuid, self.tensors.read(ti))
+                t = self.tensors.read(ti)
+                if isinstance(t, torch.Tensor) and t.dim() == 1 and t.numel() > 1:
+                    for i in range(t.numel()):      # a burst of items in one tensor
+                        sb.put(f"{ti.uuid}:{i}", t[i:i + 1])
+                else:
+                    sb.put(ti.uuid, t)
             return
         pri.walk_state.ingest(e)
 
     def _poll_stream_buffers(self) -> None:
-        for pri in list(self.requests.values()):
+        if not self._streaming_requests:
+            return
+        for key in list(self._streaming_requests):
+            pri = self.requests.get(key)
+            if pri is None:
+                self._streaming_requests.discard(key)
+                continue
             for name, sb in pri.stream_buffers.items():
                 target = next((n for n, st in pri.walk_state.nodes.items()
                                if name in st.decl.streaming_inputs and name not in st.cur and not st.running), None)
@@ -244,6 +262,10 @@ class Worker:
             ins = {}
             for name, edge in pri.walk_state.inputs_of(node).items():
                 ins[name] = [self.tensors.read(ti) for ti in edge.tensor_info]
+            sc = pri.walk_state.nodes[node].scope
+            if sc.loop is not None:          # iterations the node may still run (bound of a decode burst)
+                pri.fwd_info.step_metadata = dict(pri.fwd_info.step_metadata or {},
+                                                  _loop_remaining=max(1, sc.loop.max_iters - sc.curr_iter))
             pri.walk_state.mark_running(node)
             pri.in_flight += 1
             inputs[rid] = ins
@@ -260,7 +282,13 @@ class Worker:
         with nvtx_range(f"{batch.node_name}:{batch.graph_walk}:{len(batch.request_ids)}"):
             t0 = time.perf_counter()
             out = eng.execute_batch(batch)
-            out.timings["execute_s"] = time.perf_counter() - t0
+            dt = time.perf_counter() - t0
+            out.timings["execute_s"] = dt
+            self.phase_s["execute"] += dt
+            rec = self.batches_by_node.setdefault(f"{batch.node_name}:{batch.graph_walk}", [0, 0, 0.0])
+            rec[0] += 1
+            rec[1] += len(batch.request_ids)
+            rec[2] += dt
         return out
 
     def _postprocess_batch(self, batch: NodeBatch, out: NodeOutput) -> None:
@@ -279,14 +307,16 @@ class Worker:
             if rid in out.failed_requests:
                 continue
             try:
-                self._complete_node(pri, batch, out.outputs.get(rid, {}), out.stop_loops.get(rid, set()))
+                self._complete_node(pri, batch, out.outputs.get(rid, {}), out.stop_loops.get(rid, set()),
+                                    out.iterations.get(rid, 1))
             except Exception as e:  # noqa: BLE001
                 log.exception("worker %s: routing outputs of %s failed", self.worker_id, rid)
                 self._fail_requests({rid: f"{type(e).__name__}: {e}"})
             if pri.remove_pending and pri.in_flight == 0:
                 self._drop((rid, pri.partition_name))
 
-    def _complete_node(self, pri: PerRequestInfo, batch: NodeBatch, tensors: dict, stops: set) -> None:
+    def _complete_node(self, pri: PerRequestInfo, batch: NodeBatch, tensors: dict, stops: set,
+                       iterations: int = 1) -> None:
         ws = pri.walk_state
         node = batch.node_name
         for ln in stops:
@@ -310,8 +340,8 @@ class Worker:
                               for x in t if isinstance(x, torch.Tensor)]
             edges.append(ne)
             if e.conductor_new_token:
-                pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + 1
-        comp = ws.complete(node, edges)
+                pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + max(1, iterations)
+        comp = ws.complete(node, edges, iterations=iterations)
         self._send_outputs(pri, comp.route)
         self._refresh_ready(pri)
         if comp.walk_done:
@@ -423,22 +453,33 @@ class Worker:
         """One iteration of the main loop; returns True when something happened."""
         self.iterations += 1
         did = False
+        T = self.phase_s
+        t0 = time.perf_counter()
         msgs = self.comm.recv_or_wake(block_s) if block_s > 0 else self.comm.drain()
+        t1 = time.perf_counter()
+        T["wait"] += t1 - t0
         if msgs:
             self._process_messages(msgs)
             did = True
+        t2 = time.perf_counter()
+        T["messages"] += t2 - t1
         self._poll_stream_buffers()
+        t3 = time.perf_counter()
+        T["streams"] += t3 - t2
         if self._pending is not None:
             fut, batch = self._pending
             if fut.done():
                 self._pending = None
                 self._finish(batch, fut)
                 did = True
+                T["finish"] += time.perf_counter() - t3
         if self._pending is None:
             nxt = self.scheduler.get_next_batch()
             if nxt is not None:
                 node, walk, rkeys = nxt
+                tb = time.perf_counter()
                 batch = self._build_node_batch(node, walk, rkeys)
+                T["build"] += time.perf_counter() - tb
                 if batch is not None:
                     if not self.is_tp_follower:
                         for f in self.tp_followers:
@@ -466,6 +507,19 @@ class Worker:
             self._fail_requests({rid: f"{type(e).__name__}: {e}" for rid in batch.request_ids})
 
     def run(self) -> None:
+        prof_dir = os.environ.get("MSTAR_PROFILE_WORKER")
+        if prof_dir:          # host-side profile of the worker loop: one pstats file per worker
+            import profile as _profile          # per-thread (sys.setprofile); cProfile's hooks are process-wide
+            pr = _profile.Profile()
+            try:
+                pr.runcall(self._run_loop)
+            finally:
+                os.makedirs(prof_dir, exist_ok=True)
+                pr.dump_stats(os.path.join(prof_dir, f"{self.worker_id}.pstats"))
+            return
+        self._run_loop()
+
+    def _run_loop(self) -> None:
         self.comm.send(self.conductor_id, Message(CM.SETUP_DONE, ipc.SetupDone(self.worker_id)))
         while self.running:
             if self._pending is not None:
@@ -478,6 +532,10 @@ class Worker:
     def shutdown(self) -> None:
         if self.gpu_thread is not None:
             self.gpu_thread.shutdown(wait=True)
+        if os.environ.get("MSTAR_WORKER_STATS"):
+            log.warning("worker %s: loop iterations %d, host seconds by phase %s, batches (count, requests, seconds) %s",
+                        self.worker_id, self.iterations, {k: round(v, 3) for k, v in self.phase_s.items()},
+                        {k: (v[0], v[1], round(v[2], 3)) for k, v in self.batches_by_node.items()})
 
 
 def _rk(pri: PerRequestInfo) -> str:

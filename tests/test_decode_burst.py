@@ -1,0 +1,73 @@
+"""Decode bursts: several decode steps per node execution (device-side token feedback) give exactly the tokens of
+single-step decoding, stop at EOS inside a burst, respect the token budget, and feed stream buffers item by item.
+Runs on CPU with the engine's eager stand-in for captured graphs."""
+import os
+
+import pytest
+
+from mstar_b200.api_server.server import APIServer
+
+
+def _tokens(burst, graphs, eos_ids=(), **mk):
+    os.environ["MSTAR_EMULATE_GRAPHS"] = "1" if graphs else ""
+    os.environ["MSTAR_DECODE_BURST"] = str(burst)
+    try:
+        cfg = {"model": "tiny", "model_kwargs": {"dtype": "float32", "max_num_pages": 256, "eos_ids": list(eos_ids)},
+               "node_groups": [{"node_names": ["LLM"], "ranks": [0]}]}
+        s = APIServer(cfg, in_process=True).start(60)
+        try:
+            outs = []
+            rids = [s.submit_request(p, output_modalities=["text"], model_kwargs=dict(mk)) for p in ("1 2 3", "7 8 9 10 11")]
+            for r in rids:
+                res = s.collect_results(r, 120)
+                assert "error" not in res, res
+                outs.append(b"".join(c.data for c in res["text"]).decode().split())
+            eng = s.deployment.workers[0].engines.engine_for("LLM")
+            return outs, eng.graph_hits
+        finally:
+            s.shutdown()
+    finally:
+        os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
+        os.environ.pop("MSTAR_DECODE_BURST", None)
+
+
+def test_burst_decoding_equals_single_step_decoding():
+    kw = dict(max_tokens=23, ignore_eos=True, temperature=0.8, top_p=0.9, repetition_penalty=1.1, seed=11)
+    ref, hits0 = _tokens(1, False, **kw)
+    one, hits1 = _tokens(1, True, **kw)
+    five, hits5 = _tokens(5, True, **kw)
+    assert hits0 == 0 and hits1 > 0 and hits5 > 0
+    assert ref == one == five
+    assert all(len(t) == 23 for t in five)          # 1 prefill token + 22 decode tokens: budget respected in bursts
+
+
+def test_burst_is_cut_at_the_stop_token():
+    # greedy decoding of the tiny model: declare a token that appears mid-sequence the stop token
+    ref, _ = _tokens(1, True, max_tokens=16, ignore_eos=True, temperature=0.0)
+    stop = int(ref[0][6])
+    first = ref[0].index(str(stop))
+    out, _ = _tokens(4, True, eos_ids=[stop], max_tokens=16, temperature=0.0)
+    assert out[0] == ref[0][:first + 1]
+    one, _ = _tokens(1, True, eos_ids=[stop], max_tokens=16, temperature=0.0)
+    assert one == out
+
+
+def test_tts_stream_with_frame_sized_bursts():
+    """Orpheus-class model: bursts of 7 tokens (one audio frame) reach the codec's sliding window item by item."""
+    os.environ["MSTAR_EMULATE_GRAPHS"] = "1"
+    try:
+        cfg = {"model": "orpheus", "model_kwargs": {"small": True, "page_size": 16, "max_num_pages": 256},
+               "node_groups": [{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill", "decode"]},
+                               {"node_names": ["snac_decoder"], "ranks": [0], "graph_walks": ["snac_chunk"]}]}
+        s = APIServer(cfg, in_process=True).start(120)
+        try:
+            rid = s.submit_request("hello there", output_modalities=["audio"], model_kwargs=dict(max_tokens=63, ignore_eos=True))
+            sizes = [len(c.data) for c in s.iter_result_chunks(rid, 300)]
+            eng = s.deployment.workers[0].engines.engine_for("LLM")
+            assert eng.decode_burst == 7 and eng.graph_hits >= 56
+            # 63 tokens = 9 frames: six full windows (one frame of audio each) and the flush of the last three
+            assert sizes.count(4096) == 6 and sum(sizes) == 4096 * 9, sizes
+        finally:
+            s.shutdown()
+    finally:
+        os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
