@@ -25,6 +25,7 @@ class MicroScheduler:
         self._held: dict[str, float] = {}
         self._tp_queue: deque = deque()          # leader decisions waiting to be replayed
         self.node_limits: dict[str, int] = {}
+        self.limit_fn = None                      # optional (node, walk) -> largest batch the node accepts
 
     # ---- bookkeeping ----
     def mark_ready(self, node: str, walk: str, request_id: str) -> None:
@@ -81,6 +82,8 @@ class MicroScheduler:
             if not rids:
                 continue
             limit = min(self.max_batch_size, self.node_limits.get(key[0], self.max_batch_size))
+            if self.limit_fn is not None:
+                limit = max(1, min(limit, int(self.limit_fn(key[0], key[1]))))
             rids = rids[:limit]
             for r in rids:
                 self.ready[key].pop(r, None)

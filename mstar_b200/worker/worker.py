@@ -70,6 +70,7 @@ class Worker:
         self.tp_followers = tp_followers or []
         self.is_tp_follower = is_tp_follower
         self.scheduler = MicroScheduler(max_batch_size=max_batch_size, is_tp_follower=is_tp_follower)
+        self.scheduler.limit_fn = self._node_batch_limit
         self.walks = model.get_graph_walk_graphs()
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
@@ -113,6 +114,14 @@ class Worker:
                 log.exception("worker %s: message %s failed", self.worker_id, m.type)
                 if rid:
                     self._fail_requests({rid: f"{type(e).__name__}: {e}"})
+
+    def _node_batch_limit(self, node: str, walk: str) -> int:
+        """Largest batch the node's submodule takes for this walk (1 for nodes that run one request at a time)."""
+        try:
+            sub = self.engines.engine_for(node).submodules[node]
+            return int(sub.max_batch_size(walk)) if sub.can_batch(walk) else 1
+        except Exception:  # noqa: BLE001
+            return 1 << 30
 
     def _section_for(self, walk: str):
         sec = self.walks.get(walk)
