@@ -98,6 +98,8 @@ def main():
     ap.add_argument("--gen-tokens", type=int, default=1200)
     ap.add_argument("--ttft-samples", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-serving", action="store_true",
+                    help="skip the HTTP serving measurement (LLM + codec behind the C++ frontend, 1 GPU only)")
     ap.add_argument("--profile-step", action="store_true",
                     help="run ONE eager decode step between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off)")
@@ -257,6 +259,21 @@ def main():
     if e2e:
         out["e2e"] = {"value": round(tokens / t_e2e, 1), "unit": "tokens/s",
                       "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])}
+    if world == 1 and not args.no_e2e and not args.no_serving:
+        # the same measurement as the reference arm: the whole server (HTTP frontend, conductor, worker, LLM and
+        # codec partitions on this GPU), tokens counted from the audio the clients receive
+        del eng, model, graph
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            res = subprocess.run([sys.executable, "-m", "mstar_b200.bench.serve_tts", "--concurrency", str(C),
+                                  "--tokens", "1204"], capture_output=True, text=True, timeout=900,
+                                 cwd=os.path.dirname(os.path.abspath(__file__)))
+            line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+            out["serving_http"] = json.loads(line)
+        except Exception as e:  # noqa: BLE001
+            out["serving_http"] = {"error": f"{type(e).__name__}: {e}"}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

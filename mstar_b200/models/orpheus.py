@@ -33,6 +33,8 @@ class SnacSubmodule(NodeSubmodule):
         super().__init__(device, torch.float32)
         kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
         self.dec = SnacDecoder(**kw).to(device=device, dtype=torch.float32).eval()
+        if torch.device(device).type == "cuda":
+            torch.backends.cudnn.benchmark = True      # fixed shapes, replayed from graphs: let cuDNN pick per shape
         self.base_id = base_id
         self.gen = None
 

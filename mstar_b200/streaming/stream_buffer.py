@@ -106,6 +106,8 @@ class StreamBuffer:
     def _collate(items: list) -> dict:
         if not items:
             return {"data": None}
-        if isinstance(items[0], torch.Tensor):
+        if all(isinstance(i, torch.Tensor) for i in items):
             return {"data": items[0] if len(items) == 1 else torch.stack(items)}
+        if any(isinstance(i, torch.Tensor) for i in items):      # single-token tensors mixed with burst ints
+            return {"data": [int(i.reshape(-1)[0]) if isinstance(i, torch.Tensor) else i for i in items]}
         return {"data": items}

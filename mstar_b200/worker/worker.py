@@ -190,9 +190,9 @@ class Worker:
         if sb is not None:
             for ti in e.tensor_info:
                 t = self.tensors.read(ti)
-                if isinstance(t, torch.Tensor) and t.dim() == 1 and t.numel() > 1:
-                    for i in range(t.numel()):      # a burst of items in one tensor
-                        sb.put(f"{ti.uuid}:{i}", t[i:i + 1])
+                if isinstance(t, torch.Tensor) and t.dim() == 1 and t.numel() > 1 and not t.is_floating_point():
+                    for i, v in enumerate(t.tolist()):      # a burst of token ids in one tensor: plain ints
+                        sb.put(f"{ti.uuid}:{i}", v)
                 else:
                     sb.put(ti.uuid, t)
             return
@@ -216,7 +216,15 @@ class Worker:
                     continue
                 chunk = sb.pop_chunk()
                 data = chunk.data["data"]
-                t = data if isinstance(data, torch.Tensor) else torch.zeros(0, dtype=torch.int64)
+                if isinstance(data, torch.Tensor):
+                    t = data
+                elif isinstance(data, list) and data:
+                    if isinstance(data[0], torch.Tensor):
+                        t = torch.cat([d.reshape(-1) for d in data])
+                    else:
+                        t = torch.tensor(data, dtype=torch.int64)
+                else:
+                    t = torch.zeros(0, dtype=torch.int64)
                 ti = self.tensors.store_and_return_tensor_info(pri.request_id, t)
                 edge = GraphEdge(target, name, [ti], is_streaming=True, final_stream_chunk=chunk.is_final)
                 pri.walk_state.ingest(edge)
