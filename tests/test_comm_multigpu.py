@@ -25,3 +25,12 @@ def test_symmetric_heap_collectives():
     res = _run("mp_comm_worker.py", n)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "FAIL" not in res.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_cosmos3_tp2_sp2_on_four_gpus():
+    """Dual-pathway transformer on a tp2 x sp2 mesh of GPUs (symmetric-heap all-reduce and Ulysses exchange, prefix
+    tower cut four ways) against the same model on one GPU."""
+    res = _run("mp_cosmos_worker.py", 4, {"NCCL_NVLS_ENABLE": "0"})
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "matches one GPU" in res.stdout

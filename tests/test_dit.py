@@ -208,6 +208,6 @@ def test_cosmos3_tp2_sp2_matches_single_rank_on_gloo():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
            "--nproc-per-node", "4", os.path.join(root, "tests", "mp_cosmos_worker.py")]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""),
-                         cwd=root)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, CUDA_VISIBLE_DEVICES="", MSTAR_TEST_BACKEND="gloo"), cwd=root)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
