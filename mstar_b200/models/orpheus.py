@@ -33,8 +33,7 @@ class SnacSubmodule(NodeSubmodule):
         super().__init__(device, torch.float32)
         kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
         self.dec = SnacDecoder(**kw).to(device=device, dtype=torch.float32).eval()
-        if torch.device(device).type == "cuda":
-            torch.backends.cudnn.benchmark = True      # fixed shapes, replayed from graphs: let cuDNN pick per shape
+
         self.base_id = base_id
         self.gen = None
 
@@ -57,7 +56,12 @@ class SnacSubmodule(NodeSubmodule):
         tk = tokens.to(self.device)
         with torch.no_grad():
             if runner is not None and tk.is_cuda:
-                return runner.run(("snac", tuple(tk.shape)), fn, [tk]).clone()
+                # batch padded to a power of two: a handful of captured graphs serve every batch size
+                B = tk.shape[0]
+                Bp = 1 << (B - 1).bit_length()
+                if Bp != B:
+                    tk = torch.cat([tk, tk[:1].expand(Bp - B, -1)])
+                return runner.run(("snac", tuple(tk.shape)), fn, [tk])[:B].clone()
             return fn(tk)
 
     def forward(self, graph_walk, engine_inputs, ni, **kw):
