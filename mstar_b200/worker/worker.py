@@ -75,8 +75,14 @@ class Worker:
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
         self.running = True
-        self.gpu_thread = ThreadPoolExecutor(1, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
-        self._pending = None       # (future, batch)
+        # one batch in flight PER ENGINE (a KV-cache engine and a stateless engine that share the GPU overlap: each
+        # runs on its own CUDA stream, so a codec batch fills the bubbles of a decode burst); TP followers replay the
+        # leader's order strictly, one batch at a time
+        n_eng = 1 if is_tp_follower or tp_followers else max(1, len(getattr(engine_manager, "engines", [])))
+        self.gpu_thread = ThreadPoolExecutor(n_eng, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
+        self._max_in_flight = n_eng
+        self._in_flight: dict[int, tuple] = {}       # id(engine) -> (future, batch)
+        self._streams: dict[int, object] = {}        # id(engine) -> CUDA stream
         self.heartbeat_s = heartbeat_s
         self._last_beat = time.monotonic()
         self.phase_times: dict[str, list[float]] = {}
@@ -298,7 +304,15 @@ class Worker:
         eng = self.engines.engine_for(batch.node_name)
         with nvtx_range(f"{batch.node_name}:{batch.graph_walk}:{len(batch.request_ids)}"):
             t0 = time.perf_counter()
-            out = eng.execute_batch(batch)
+            if self._max_in_flight > 1 and eng.device.type == "cuda":
+                st = self._streams.get(id(eng))
+                if st is None:
+                    st = self._streams[id(eng)] = torch.cuda.Stream(device=eng.device)
+                with torch.cuda.stream(st):
+                    out = eng.execute_batch(batch)
+                    st.synchronize()        # outputs are handed to other engines / the host after this point
+            else:
+                out = eng.execute_batch(batch)
             dt = time.perf_counter() - t0
             out.timings["execute_s"] = dt
             self.phase_s["execute"] += dt
@@ -483,29 +497,35 @@ class Worker:
         self._poll_stream_buffers()
         t3 = time.perf_counter()
         T["streams"] += t3 - t2
-        if self._pending is not None:
-            fut, batch = self._pending
+        for eid, (fut, batch) in list(self._in_flight.items()):
             if fut.done():
-                self._pending = None
+                del self._in_flight[eid]
                 self._finish(batch, fut)
                 did = True
                 T["finish"] += time.perf_counter() - t3
-        if self._pending is None:
-            nxt = self.scheduler.get_next_batch()
-            if nxt is not None:
-                node, walk, rkeys = nxt
-                tb = time.perf_counter()
-                batch = self._build_node_batch(node, walk, rkeys)
-                T["build"] += time.perf_counter() - tb
-                if batch is not None:
-                    if not self.is_tp_follower:
-                        for f in self.tp_followers:
-                            self.comm.send(f, Message(WM.SCHEDULE_TP, ipc.ScheduleTPNode(node, walk, list(rkeys))))
-                    if self.gpu_thread is not None:
-                        self._pending = (self.gpu_thread.submit(self._execute, batch), batch)
-                    else:
-                        self._finish(batch, None)
-                    did = True
+                t3 = time.perf_counter()
+        while len(self._in_flight) < self._max_in_flight or self.gpu_thread is None:
+            busy = {k for k in self.scheduler.ready if id(self.engines.engine_for(k[0])) in self._in_flight} \
+                if self._in_flight else None
+            nxt = self.scheduler.get_next_batch(exclude=busy)
+            if nxt is None:
+                break
+            node, walk, rkeys = nxt
+            tb = time.perf_counter()
+            batch = self._build_node_batch(node, walk, rkeys)
+            T["build"] += time.perf_counter() - tb
+            if batch is None:
+                continue
+            if not self.is_tp_follower:
+                for f in self.tp_followers:
+                    self.comm.send(f, Message(WM.SCHEDULE_TP, ipc.ScheduleTPNode(node, walk, list(rkeys))))
+            did = True
+            if self.gpu_thread is not None:
+                eid = id(self.engines.engine_for(node))
+                self._in_flight[eid] = (self.gpu_thread.submit(self._execute, batch), batch)
+            else:
+                self._finish(batch, None)
+                break
         if self.heartbeat_s and time.monotonic() - self._last_beat > self.heartbeat_s:
             self._last_beat = time.monotonic()
             self.comm.send(self.conductor_id, Message(CM.HEARTBEAT, ipc.SetupDone(self.worker_id)))
@@ -539,9 +559,9 @@ class Worker:
     def _run_loop(self) -> None:
         self.comm.send(self.conductor_id, Message(CM.SETUP_DONE, ipc.SetupDone(self.worker_id)))
         while self.running:
-            if self._pending is not None:
-                # a batch is on the GPU thread: sleep on the mailbox in short slices instead of spinning on the GIL
-                self.step(block_s=0.0 if self._pending[0].done() else 0.0005)
+            if self._in_flight:
+                # batches are on the GPU threads: sleep on the mailbox in short slices instead of spinning on the GIL
+                self.step(block_s=0.0 if any(f.done() for f, _ in self._in_flight.values()) else 0.0005)
             else:
                 self.step(block_s=0.0 if self.scheduler.has_ready() else 0.02)
         self.shutdown()
