@@ -408,6 +408,23 @@ __global__ void attn_merge_kernel(const __nv_bfloat16* oa, const float* la, cons
     }
 }
 
+// Snake activation of neural audio codecs: y = x + sin^2(alpha_c * x) / alpha_c, alpha per channel, x: [B, C, T].
+// One pass over the tensor instead of the five elementwise kernels of the composed expression.
+template <typename T>
+__global__ void snake_kernel(const T* x, const float* alpha, T* out, long long n, int C, long long Tlen) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)((i / Tlen) % C);
+        const float a = alpha[c];
+        float v;
+        if constexpr (sizeof(T) == 4) v = x[i]; else v = __bfloat162float(x[i]);
+        const float sn = __sinf(a * v);
+        const float y = v + sn * sn / (a + 1e-9f);
+        if constexpr (sizeof(T) == 4) out[i] = y; else out[i] = __float2bfloat16(y);
+    }
+}
+
 // Classifier-free guidance combine + optional per-token renorm + Euler step, fp32 latents.
 //   v = v_uncond + s_text * (v_cond - v_uncond) [+ s_img * (v_cond_img - v_uncond_img) when given]
 //   renorm (mode 1, per row): v *= min(1, |v_cond| / |v|) with clamp [renorm_min, 1]
@@ -569,6 +586,16 @@ MSTAR_API int mstar_gated_residual(const void* x, const void* y, const void* gat
         hidden, rows_per_mod > 0 ? rows_per_mod : 1, gate_stride);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : set_error("gated_residual launch", e);
+}
+
+MSTAR_API int mstar_snake(const void* x, const float* alpha, void* out, long long n, int C, long long Tlen, int is_f32,
+                          void* stream_) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream_;
+    if (is_f32) snake_kernel<float><<<grid_for(n, 256), 256, 0, s>>>((const float*)x, alpha, (float*)out, n, C, Tlen);
+    else snake_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, s>>>((const __nv_bfloat16*)x, alpha, (__nv_bfloat16*)out, n, C, Tlen);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : set_error("snake launch", e);
 }
 
 MSTAR_API int mstar_attn_merge(const void* oa, const float* la, const void* ob, const float* lb, void* out,

@@ -165,3 +165,27 @@ def advance_decode(kv_lens, positions, cache_pos=None, input_ids=None, sampled=N
                                              int(B), int(pos2.shape[0]), int(pos2.stride(0)),
                                              ctypes.c_void_p(_lib.stream_ptr()))
     _lib.check(rc, "mstar_advance_decode")
+
+
+def snake_ref(x: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
+    a = alpha.reshape(1, -1, 1).float()
+    xf = x.float()
+    return (xf + torch.sin(a * xf).pow(2) / (a + 1e-9)).to(x.dtype)
+
+
+def snake(x: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
+    """Snake activation y = x + sin^2(alpha x) / alpha on [B, C, T] (alpha per channel), one fused kernel on the GPU.
+    Reference counterpart: Snake1d of the SNAC decoder (mstar/model/orpheus/components/snac.py:43), composed there
+    from separate elementwise ops."""
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+        return snake_ref(x, alpha)
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    a = alpha.reshape(-1).float().contiguous()
+    B, C, T = xc.shape
+    rc = _lib.kernels().mstar_snake(ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(a.data_ptr()),
+                                    ctypes.c_void_p(out.data_ptr()), ctypes.c_longlong(xc.numel()), int(C),
+                                    ctypes.c_longlong(T), 1 if x.dtype == torch.float32 else 0,
+                                    ctypes.c_void_p(_lib.stream_ptr()))
+    _lib.check(rc, "mstar_snake")
+    return out

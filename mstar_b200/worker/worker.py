@@ -78,7 +78,11 @@ class Worker:
         # one batch in flight PER ENGINE (a KV-cache engine and a stateless engine that share the GPU overlap: each
         # runs on its own CUDA stream, so a codec batch fills the bubbles of a decode burst); TP followers replay the
         # leader's order strictly, one batch at a time
-        n_eng = 1 if is_tp_follower or tp_followers else max(1, len(getattr(engine_manager, "engines", [])))
+        # (measured on the colocated TTS placement: the two engines slow each other down and the sum does not
+        # improve, 5.85k vs 6.41k tokens/s, so concurrency is opt-in)
+        n_eng = 1
+        if os.environ.get("MSTAR_ENGINE_CONCURRENCY") and not (is_tp_follower or tp_followers):
+            n_eng = max(1, len(getattr(engine_manager, "engines", [])))
         self.gpu_thread = ThreadPoolExecutor(n_eng, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
         self._max_in_flight = n_eng
         self._in_flight: dict[int, tuple] = {}       # id(engine) -> (future, batch)

@@ -144,3 +144,14 @@ def test_sampling_distribution_and_bf16():
     st.offset.zero_()
     tok2 = st.sample(logits, torch.arange(B, dtype=torch.int32).cuda())
     assert torch.equal(tok, tok2)
+
+
+def test_snake_activation_matches_reference():
+    from mstar_b200.ops import elementwise as E
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(3, 20, 257, generator=g)
+    a = torch.rand(1, 20, 1, generator=g) + 0.5
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        ref = E.snake_ref(x.to(dt), a)
+        out = E.snake(x.to(dt).cuda(), a.cuda())
+        assert (out.float().cpu() - ref.float()).abs().max().item() < tol
