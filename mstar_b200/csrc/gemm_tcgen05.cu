@@ -597,6 +597,167 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Persistent variant for large token-major GEMMs (M > 128, one K split): one CTA per SM walks the tile list.
+// Two TMEM accumulators of BN columns: while the four epilogue warps drain tile i (TMEM -> registers -> bias /
+// activation / residual -> global), the UMMA warp is already accumulating tile i + 1 into the other buffer and the
+// TMA warp is prefetching its operands; barrier set-up, TMEM allocation and pipeline fill are paid once per CTA
+// instead of once per tile. Tiles are visited in the grouped order of the non-persistent kernel.
+// ---------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                            const GemmParams p, const int tiles_p, const int tiles_q) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int P_BYTES = BM * BK * 2;
+    constexpr int STAGE_BYTES = gemm_stage_bytes(BN);
+    constexpr int TMEM_COLS = 2 * BN;
+    static_assert(TMEM_COLS <= 512, "two accumulators must fit in TMEM");
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;      // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles = tiles_p * tiles_q;
+    const int nkb = p.kblocks_total;
+    pdl_launch_dependents();
+    auto tile_coords = [&](int lin, int& tp, int& tq) {
+        constexpr int GROUP_P = 16;
+        if (tiles_p >= 2 * GROUP_P && tiles_q > 1) {
+            const int per_group = GROUP_P * tiles_q;
+            const int group = lin / per_group, within = lin - group * per_group;
+            const int p0 = group * GROUP_P;
+            const int gp = min(GROUP_P, tiles_p - p0);
+            tp = p0 + within % gp;
+            tq = within / gp;
+        } else {
+            tp = lin % tiles_p;
+            tq = lin / tiles_p;
+        }
+    };
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        flags[0] = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmP); tma_prefetch_desc(&tmQ); }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            long long g = 0;          // running k-block count over all tiles of this CTA: stage and phase
+            int issued = 0;
+            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += gridDim.x) {
+                int tp, tq;
+                tile_coords(t, tp, tq);
+                for (int kb = 0; kb < nkb; ++kb, ++g) {
+                    const int s = (int)(g % STAGES);
+                    const uint32_t ph = (uint32_t)((g / STAGES) & 1);
+                    if (g >= STAGES && !mbar_wait(&empty_bar[s], ph ^ 1, p.wait_limit_ns)) {
+                        report_status(p.status, KID_GEMM, 11, t, kb);
+                        flags[0] = 1;
+                        break;
+                    }
+                    uint8_t* sp = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    tma_load_2d(sp, &tmP, &full_bar[s], kb * BK, tp * BM);
+                    tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kb * BK, tq * BN);
+                    ++issued;
+                }
+            }
+            if (flags[0]) {      // let copies in flight land before the CTA leaves
+                const long long lo = g > STAGES ? g - STAGES : 0;
+                for (long long i = lo; i < g; ++i) mbar_wait(&full_bar[i % STAGES], (uint32_t)((i / STAGES) & 1), 1000000ull);
+            }
+            (void)issued;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1);
+            long long g = 0;
+            int it = 0;
+            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += gridDim.x, ++it) {
+                const int a = it & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                if (it >= 2 && !mbar_wait(&acc_empty[a], (uint32_t)(((it >> 1) - 1) & 1), p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 12, t, it);
+                    flags[0] = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(a * BN);
+                bool ok = true;
+                for (int kb = 0; kb < nkb; ++kb, ++g) {
+                    const int s = (int)(g % STAGES);
+                    const uint32_t ph = (uint32_t)((g / STAGES) & 1);
+                    if (!mbar_wait(&full_bar[s], ph, p.wait_limit_ns)) {
+                        report_status(p.status, KID_GEMM, 13, t, kb);
+                        flags[0] = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sp = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = umma_smem_desc_sw128(sp);
+                    const uint64_t db = umma_smem_desc_sw128(sp + P_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_f16_ss(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;
+        int it = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+            const int a = it & 1;
+            if (!mbar_wait(&acc_full[a], (uint32_t)((it >> 1) & 1), p.wait_limit_ns + 500000000ull)) {
+                report_status(p.status, KID_GEMM, 14, t, it);
+                flags[0] = 1;
+                break;
+            }
+            tc_fence_after();
+            int tp, tq;
+            tile_coords(t, tp, tq);
+            const int pidx = tp * BM + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * BN + c0), r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                const int qidx = tq * BN + c0;
+                if (p.out_f32) store_row_chunk<true>(p, pidx, qidx, v, 32);
+                else store_row_chunk<false>(p, pidx, qidx, v, 32);
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[a]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 template <int BN, int STAGES, int MINB, int KSUB = 1>
@@ -611,6 +772,34 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
         configured = true;
     }
     cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
+    if (e != cudaSuccess) return set_error("gemm: launch failed", e);
+    return 0;
+}
+
+static bool persistent_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MSTAR_GEMM_PERSISTENT");
+        v = e ? atoi(e) : 1;
+    }
+    return v != 0;
+}
+
+template <int BN, int STAGES>
+static int launch_persistent(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
+                             cudaStream_t stream) {
+    constexpr int smem = gemm_smem_bytes(BN, STAGES);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
+        configured = true;
+    }
+    const int tiles = (int)(grid.x * grid.y);
+    const int ctas = tiles < device_sm_count() ? tiles : device_sm_count();
+    cudaError_t e = launch_pdl(gemm_bf16_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(192), smem, stream, tmP, tmQ, p,
+                               (int)grid.x, (int)grid.y);
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
     return 0;
 }
@@ -655,7 +844,10 @@ static int dispatch_tile(int bn, int swap, const CUtensorMap& tmP, const CUtenso
         case 128:
             if (swap) return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
             return launch_gemm<128, 6, 1>(tmP, tmQ, p, grid, stream);
-        case 256: return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
+        case 256:
+            if (!swap && grid.z == 1 && p.block_expert == nullptr && !p.ar.enabled && persistent_enabled())
+                return launch_persistent<256, 4>(tmP, tmQ, p, grid, stream);
+            return launch_gemm<256, 4, 1>(tmP, tmQ, p, grid, stream);
     }
     return set_error("gemm: unsupported tile", cudaSuccess);
 }
