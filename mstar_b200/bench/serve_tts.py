@@ -62,12 +62,13 @@ def main():
     ap.add_argument("--small", action="store_true", help="test-sized weights (CPU smoke run)")
     ap.add_argument("--uvicorn", action="store_true", help="FastAPI / uvicorn frontend instead of mstar-server")
     ap.add_argument("--multi-process", action="store_true")
+    ap.add_argument("--codec-dtype", default="float32", choices=["float32", "bfloat16"])
     a = ap.parse_args()
     from ..api_server.app import create_app
     from ..api_server.server import APIServer
     cfg = {"model": "orpheus",
            "model_kwargs": {"small": a.small, "page_size": 16 if a.small else 128,
-                            "max_num_pages": 2048},
+                            "max_num_pages": 2048, "codec_dtype": a.codec_dtype},
            "max_batch_size": max(64, a.concurrency),
            "node_groups": [{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill", "decode"]},
                            {"node_names": ["snac_decoder"], "ranks": [0], "graph_walks": ["snac_chunk"]}]}
@@ -92,7 +93,8 @@ def main():
         except Exception:  # noqa: BLE001
             time.sleep(0.05)
     out = {"bench": "serve_tts", "concurrency": a.concurrency, "tokens_per_request": a.tokens,
-           "frontend": "uvicorn" if a.uvicorn else "mstar-server", "multi_process": a.multi_process}
+           "frontend": "uvicorn" if a.uvicorn else "mstar-server", "multi_process": a.multi_process,
+           "codec_dtype": a.codec_dtype}
     try:
         w = _Stream(url, "warm up", 28 * 3)
         w.start()

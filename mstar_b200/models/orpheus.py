@@ -29,8 +29,9 @@ VOICES = ["tara", "zoe", "zac", "jess", "leo", "mia", "julia", "leah"]
 
 
 class SnacSubmodule(NodeSubmodule):
-    def __init__(self, device, base_id: int, small: bool):
+    def __init__(self, device, base_id: int, small: bool, compute_dtype: torch.dtype = torch.float32):
         super().__init__(device, torch.float32)
+        self.compute_dtype = compute_dtype         # fp32 weights; bf16 runs the convolutions under autocast
         kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
         self.dec = SnacDecoder(**kw).to(device=device, dtype=torch.float32).eval()
 
@@ -52,6 +53,9 @@ class SnacSubmodule(NodeSubmodule):
     def _decode(self, tokens: torch.Tensor, runner) -> torch.Tensor:
         """tokens [B, n] (n a multiple of 7) -> waveforms [B, n / 7 * 2048]; replayed from a CUDA graph per shape."""
         def fn(tk):
+            if self.compute_dtype != torch.float32 and tk.is_cuda:
+                with torch.autocast("cuda", dtype=self.compute_dtype):
+                    return self.dec(orpheus_tokens_to_codes(tk, self.base_id)).float()
             return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
         tk = tokens.to(self.device)
         with torch.no_grad():
@@ -99,9 +103,10 @@ class OrpheusModel(Model):
     name = "orpheus"
 
     def __init__(self, model_dir=None, skip_weight_loading=False, small: bool = False, page_size: int = 128,
-                 max_num_pages: int = 2048, **kw):
+                 max_num_pages: int = 2048, codec_dtype: str = "float32", **kw):
         super().__init__(model_dir, skip_weight_loading, **kw)
         self.small = small
+        self.codec_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}[codec_dtype]
         if small:      # test-sized backbone with the real vocabulary layout
             self.cfg = DecoderConfig(hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
                                      intermediate_size=256, vocab_size=156940, rms_eps=1e-5, rope_theta=5e5,
@@ -160,7 +165,7 @@ class OrpheusModel(Model):
                 load_decoder_from_hf(lm, self.model_dir)
             return DecoderSubmodule(lm, device, eos_ids=END_TOKEN_IDS, token_edge="audio_tokens")
         if node_name == "snac_decoder":
-            return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small)
+            return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small, self.codec_dtype)
         raise KeyError(node_name)
 
     # ---- request life cycle ----
