@@ -1,0 +1,184 @@
+"""Fused compute + collective kernels over the symmetric NVLink heap, each timed against the NCCL form of the same
+step and against its roofline (the slower of FLOPs at the measured GEMM peak and bytes over one NVLink direction).
+
+Run one process per GPU:
+
+    python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc-per-node 2 \
+        -m mstar_b200.bench.comm
+
+Every figure is a CUDA-event time on the launching stream after warm-up, the maximum over ranks; rank 0 prints one
+JSON line per path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+LINK_GBS = 770.0          # measured peer copy, one direction, per GPU
+GEMM_TFLOPS = 1590.0      # measured cuBLAS bf16 burst
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        p = json.load(open(os.path.join(here, "MEASURED_PEAKS.json")))
+        return float(p.get("bf16_tflops", GEMM_TFLOPS)), float(p.get("hbm_gbs", 6650.0))
+    except Exception:  # noqa: BLE001
+        return GEMM_TFLOPS, 6650.0
+
+
+def timed(fn, iters, warmup, dev, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    t = torch.tensor([total / iters], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item() * 1e3          # microseconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=84480, help="sequence length of the Ulysses exchange")
+    args = ap.parse_args()
+
+    from ..ops import _lib, gemm
+    from ..ops.elementwise import cfg_combine
+    from ..parallel.comm import init_from_env
+    from ..parallel.symm import attach_symmetric_heap
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    g = init_from_env()
+    W, R = g.size, g.rank
+    heap = attach_symmetric_heap(g, dev, slot_bytes=64 << 20, user_bytes=768 << 20)
+    tflops, _ = _peaks()
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)      # larger than L2, written between iterations
+    rows = []
+
+    def report(**kw):
+        rows.append(kw)
+        if R == 0:
+            print(json.dumps(kw), flush=True)
+
+    # ---- decode all-reduce (64 x 3072 bf16), latency bound ----
+    x = torch.randn(64, 3072, device=dev).to(torch.bfloat16)
+    res = torch.randn(64, 3072, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(x)
+    t_ours = timed(lambda: heap.all_reduce(x, residual=res, out=out), args.iters, args.warmup, dev)
+    y = x.clone()
+
+    def nccl_ar():
+        y.copy_(x)
+        dist.all_reduce(y)
+        y.add_(res)
+    t_nccl = timed(nccl_ar, args.iters, args.warmup, dev)
+    report(path="all-reduce + residual, 64x3072 bf16", ranks=W, ours_us=round(t_ours, 2), nccl_us=round(t_nccl, 2))
+
+    # ---- DiT-sized all-reduce (the tokens of one sequence-parallel rank x hidden), bandwidth bound ----
+    xb = torch.randn(21120, 2048, device=dev).to(torch.bfloat16)
+    ob = torch.empty_like(xb)
+    t_ours = timed(lambda: heap.all_reduce(xb, out=ob), args.iters, args.warmup, dev, flush)
+    yb = xb.clone()
+    t_nccl = timed(lambda: dist.all_reduce(yb), args.iters, args.warmup, dev, flush)
+    link_us = 2 * (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
+    report(path="all-reduce, 21120x2048 bf16", ranks=W, ours_us=round(t_ours, 2), nccl_us=round(t_nccl, 2),
+           roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_ours, 3))
+
+    # ---- row-parallel projection: GEMM with the all-reduce in its epilogue (o_proj / down_proj of a decode step) ----
+    for (M, N, K, name) in [(64, 3072, 3072 // W, "o_proj"), (64, 3072, 8192 // W, "down_proj")]:
+        xa = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+        r2 = torch.randn(M, N, device=dev).to(torch.bfloat16)
+        t_f = timed(lambda: heap.linear_all_reduce(xa, w, residual=r2), args.iters, args.warmup, dev, flush)
+
+        def base():
+            yy = gemm.linear(xa, w)
+            dist.all_reduce(yy)
+            yy.add_(r2)
+        t_b = timed(base, args.iters, args.warmup, dev, flush)
+        t_g = timed(lambda: gemm.linear(xa, w, residual=r2), args.iters, args.warmup, dev, flush)
+        # roofline: the weight stream from HBM (N*K*2 bytes) against the partial tiles crossing NVLink
+        link_us = M * N * 2 * (W - 1) / (LINK_GBS * 1e3)
+        hbm_us = N * K * 2 / (_peaks()[1] * 1e3)
+        report(path=f"GEMM -> all-reduce fused ({name} {M}x{N}x{K} per rank)", ranks=W, fused_us=round(t_f, 2),
+               gemm_plus_nccl_us=round(t_b, 2), gemm_alone_us=round(t_g, 2),
+               roofline_us=round(max(link_us, hbm_us), 2), frac_of_roofline=round(max(link_us, hbm_us) / t_f, 3))
+
+    # ---- Ulysses head <-> sequence exchange by peer stores ----
+    H, D = 8, 128          # the heads of one tensor-parallel rank (16 heads, tp 2)
+    S = args.tokens // W * W
+    seq_off = [S // W * i for i in range(W + 1)]
+    mine = torch.randn(S // W, H, D, device=dev).to(torch.bfloat16)
+    off_f = heap.alloc_user(S * (H // W) * D * 2)
+    t_a2a = timed(lambda: heap.a2a_heads(mine, off_f, True, H, D, seq_off), args.iters, args.warmup, dev, flush)
+    src = mine.view(S // W, W, H // W, D).permute(1, 0, 2, 3).contiguous()
+    dst = torch.empty_like(src)
+
+    def nccl_a2a():
+        s2 = mine.view(S // W, W, H // W, D).permute(1, 0, 2, 3).contiguous()
+        dist.all_to_all_single(dst, s2)
+    t_na = timed(nccl_a2a, args.iters, args.warmup, dev, flush)
+    link_us = mine.numel() * 2 * (W - 1) / W / (LINK_GBS * 1e3)
+    report(path=f"Ulysses exchange, {S} tokens x {H} heads x {D}", ranks=W, ours_us=round(t_a2a, 2),
+           nccl_us=round(t_na, 2), roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_a2a, 3),
+           gbs_out_per_rank=round(mine.numel() * 2 * (W - 1) / W / t_a2a / 1e3, 1))
+
+    # ---- CFG-parallel gather fused with the guidance combine + Euler step (rank 0 combines) ----
+    rws, cols = 4096, 64 * 16          # a 1024x1024 image: 4096 latent tokens x (2x2x16) channels, fp32 velocities
+    v_off = heap.alloc_user(rws * cols * 4)
+    heap.local_view(v_off, (rws, cols), torch.float32).normal_()
+    xx = torch.randn(rws, cols, device=dev)
+    heap.barrier()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if R == 0:
+        def fused():
+            heap.cfg_combine(v_off, 0, 1, -1, xx, dt=-0.02, s_text=4.0, renorm=True, wait_peers=False)
+    else:
+        def fused():
+            pass
+    t_c = timed(fused, args.iters, args.warmup, dev, flush)
+    vu = torch.empty(rws, cols, device=dev)
+    vl = heap.local_view(v_off, (rws, cols), torch.float32)
+
+    def base_cfg():
+        if R == 1:
+            dist.send(vl, 0)
+        elif R == 0:
+            dist.recv(vu, 1)
+            cfg_combine(vl, vu, xx, -0.02, 4.0, renorm=True)
+    t_cb = timed(base_cfg, args.iters, args.warmup, dev, flush)
+    link_us = rws * cols * 4 / (LINK_GBS * 1e3)
+    report(path=f"CFG gather + combine + Euler step, {rws}x{cols} fp32", ranks=W, fused_us=round(t_c, 2),
+           nccl_recv_plus_combine_us=round(t_cb, 2), roofline_us=round(link_us, 2),
+           frac_of_roofline=round(link_us / t_c, 3))
+
+    torch.cuda.synchronize()
+    code = _lib.read_status(clear=True)[0]
+    if R == 0:
+        print(json.dumps({"status_word": int(code)}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

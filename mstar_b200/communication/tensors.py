@@ -122,6 +122,7 @@ class TensorCommunicationManager:
         self.use_cuda_ipc = use_cuda_ipc
         self._arena_prefix = arena_prefix
         self._arena: ShmArena | None = None
+        self._arena_lock = threading.Lock()
         self._arena_bytes = arena_segment_bytes
         self._reader: ShmArenaReader | None = None
         self.tx_bytes = 0
@@ -158,10 +159,11 @@ class TensorCommunicationManager:
             out.cuda_ipc = (st._share_cuda_(), tc.storage_offset())      # type: ignore[attr-defined]
             out.stride = list(tc.stride())
         else:
-            if self._arena is None:
-                prefix = self._arena_prefix or "mstar"
-                self._arena = ShmArena(f"{prefix}.{self.entity_id}.arena", segment_bytes=self._arena_bytes)
-            seg, off = self._arena.write(info.uuid, t)
+            with self._arena_lock:      # two preprocess threads may send their first tensors at the same moment
+                if self._arena is None:
+                    prefix = self._arena_prefix or "mstar"
+                    self._arena = ShmArena(f"{prefix}.{self.entity_id}.arena", segment_bytes=self._arena_bytes)
+                seg, off = self._arena.write(info.uuid, t)
             out.shm_segment = f"{self._arena.base_name}#{seg}"
             out.shm_offset = off
         self.tx_bytes += info.nbytes
@@ -178,10 +180,11 @@ class TensorCommunicationManager:
                 t = self._read_cuda_ipc(info)
             elif info.shm_segment:
                 base, seg = info.shm_segment.rsplit("#", 1)
-                if self._reader is None:
-                    self._reader = ShmArenaReader()
-                t = self._reader.view(base, int(seg), info.shm_offset, info.nbytes, dtype_from_name(info.dtype),
-                                      info.dims).clone()
+                with self._arena_lock:
+                    if self._reader is None:
+                        self._reader = ShmArenaReader()
+                    t = self._reader.view(base, int(seg), info.shm_offset, info.nbytes, dtype_from_name(info.dtype),
+                                          info.dims).clone()
             else:
                 raise KeyError(f"tensor {info.uuid} from {info.source_entity} is not reachable from {self.entity_id}")
             self.rx_bytes += info.nbytes

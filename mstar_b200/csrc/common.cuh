@@ -116,6 +116,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 }
 
 // ---------------------------------------------------------------------------------------------
+// thread-block clusters: rank, peer shared-memory addresses, cluster-wide barrier
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t cta_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
+// Every thread of every CTA of the cluster must call this; shared-memory writes made before it are visible to
+// the peers after it. The hardware barrier cannot time out, so it is only used where every CTA of the cluster
+// reaches it on every path (clusters are co-scheduled by the launch).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, never with cluster multicast)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

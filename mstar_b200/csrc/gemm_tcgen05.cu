@@ -38,6 +38,11 @@ struct GemmParams {
     int M, N, K;               // logical problem: C[M,N] = A[M,K] B[N,K]^T
     int swap;                  // 1: P operand (UMMA M) = B rows, Q operand (UMMA N) = A rows
     int splits;                // split-K factor (grid.z)
+    int w_packed = 0;          // 1: the weight operand B is stored tile by tile: [ceil(N/128)][ceil(K/64)] tiles of
+                               //    128 rows x 64 columns, each 16 KB contiguous (one TMA box = one DRAM burst run)
+    unsigned long long* trace = nullptr;   // optional [CTAs][8] globaltimer stamps of the CTA's phases (bench only)
+    int cluster_reduce = 0;    // 1: the splits of a tile form one thread-block cluster (1, 1, splits) and sum their
+                               //    partial tiles through distributed shared memory (decode layout only)
     int kblocks_per_split;     // 64-wide K blocks handled by one split
     int kblocks_total;
     int epilogue;              // 0 none, 1 SwiGLU on interleaved (gate,up) output columns, 2 GELU(tanh)
@@ -62,6 +67,13 @@ struct GemmParams {
     void* const* row_dst;           // optional per-token-row destination pointers (expert-parallel combine: the
                                     // row is stored straight into its owner's buffer, possibly on a peer GPU)
 };
+
+#define MSTAR_TRACE(i)                                                                                      \
+    do {                                                                                                    \
+        if (p.trace != nullptr)                                                                             \
+            p.trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = \
+                globaltimer_ns();                                                                           \
+    } while (0)
 
 constexpr int BM = 128;  // UMMA M (P-tile rows)
 constexpr int BK = 64;   // bf16 elements per K block = 128 bytes = one swizzle atom
@@ -398,6 +410,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     if (kb_end > p.kblocks_total) kb_end = p.kblocks_total;
     const int nkb = kb_end - kb_begin;  // host guarantees >= 1
     pdl_launch_dependents();
+    if (threadIdx.x == 0) MSTAR_TRACE(0);
     int p_row0 = tile_p * BM;       // first row of this tile in the P operand
     if (p.block_expert != nullptr) {
         pdl_wait();
@@ -427,10 +440,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) MSTAR_TRACE(1);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            // packed weights: tile (row tile t, K block kb) starts at row (t * kblocks_total + kb) * 128 of a
+            // [tiles * 128, 64] matrix; the weight is the P operand in the decode layout, the Q operand otherwise
+            const bool p_packed = p.w_packed && p.swap, q_packed = p.w_packed && !p.swap;
+            auto load_P = [&](uint8_t* dst, uint64_t* bar, int kb) {
+                if (p_packed) tma_load_2d(dst, &tmP, bar, 0, ((p_row0 / BM) * p.kblocks_total + kb) * BM);
+                else tma_load_2d(dst, &tmP, bar, kb * BK, p_row0);
+            };
+            auto load_Q = [&](uint8_t* dst, uint64_t* bar, int kb) {
+                if (q_packed) {
+#pragma unroll
+                    for (int h = 0; h < (BN >= 128 ? BN / 128 : 1); ++h)
+                        tma_load_2d(dst + h * (128 * BK * 2), &tmQ, bar, 0,
+                                    ((tile_q * (BN / 128) + h) * p.kblocks_total + kb) * 128);
+                } else {
+                    tma_load_2d(dst, &tmQ, bar, kb * BK, tile_q * BN);
+                }
+            };
             int issued = 0;
             const int ngroups = (nkb + KSUB - 1) / KSUB;           // pipeline steps of up to KSUB K blocks
             auto group_subs = [&](int g) { return (nkb - g * KSUB) < KSUB ? (nkb - g * KSUB) : KSUB; };
@@ -441,17 +472,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                 const int ns = group_subs(g);
                 mbar_expect_tx(&full_bar[g], ns * (P_BYTES + Q_BYTES));
                 for (int u = 0; u < ns; ++u)
-                    tma_load_2d(smem + g * STAGE_BYTES + u * P_BYTES, &tmP, &full_bar[g],
-                                (kb_begin + g * KSUB + u) * BK, p_row0);
+                    load_P(smem + g * STAGE_BYTES + u * P_BYTES, &full_bar[g], kb_begin + g * KSUB + u);
             }
             pdl_wait();
             for (int g = 0; g < npre; ++g) {
                 const int ns = group_subs(g);
                 for (int u = 0; u < ns; ++u)
-                    tma_load_2d(smem + g * STAGE_BYTES + Q_OFF + u * Q_BYTES, &tmQ, &full_bar[g],
-                                (kb_begin + g * KSUB + u) * BK, tile_q * BN);
+                    load_Q(smem + g * STAGE_BYTES + Q_OFF + u * Q_BYTES, &full_bar[g], kb_begin + g * KSUB + u);
             }
             issued = npre;
+            MSTAR_TRACE(2);
             for (int g = npre; g < ngroups; ++g) {
                 const int s = g % STAGES;
                 const uint32_t ph = (g / STAGES) & 1;
@@ -465,9 +495,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                 const int ns = group_subs(g);
                 mbar_expect_tx(&full_bar[s], ns * (P_BYTES + Q_BYTES));
                 for (int u = 0; u < ns; ++u) {
-                    const int kx = (kb_begin + g * KSUB + u) * BK;
-                    tma_load_2d(sp + u * P_BYTES, &tmP, &full_bar[s], kx, p_row0);
-                    tma_load_2d(sp + Q_OFF + u * Q_BYTES, &tmQ, &full_bar[s], kx, tile_q * BN);
+                    load_P(sp + u * P_BYTES, &full_bar[s], kb_begin + g * KSUB + u);
+                    load_Q(sp + Q_OFF + u * Q_BYTES, &full_bar[s], kb_begin + g * KSUB + u);
                 }
                 issued = g + 1;
             }
@@ -493,6 +522,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                     break;
                 }
                 tc_fence_after();
+                if (g == 0) MSTAR_TRACE(3);
                 const uint32_t sp = smem_u32(smem + s * STAGE_BYTES);
                 const int ns = (nkb - g * KSUB) < KSUB ? (nkb - g * KSUB) : KSUB;
                 for (int u = 0; u < ns; ++u) {
@@ -507,6 +537,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                 umma_commit(&empty_bar[s]);
             }
             if (ok) umma_commit(acc_bar);
+            MSTAR_TRACE(4);
         }
     } else {
         // ---------------- epilogue warps (TMEM lane quarter = warp % 4) ----------------
@@ -519,12 +550,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             flags[0] = 1;
         }
         tc_fence_after();
+        if (threadIdx.x == 64) MSTAR_TRACE(5);
         const int pidx = tile_p * BM + row;  // index along the P operand's rows
         constexpr int CH = BN < 32 ? BN : 32;
         const int tile_lin = tile_q * gridDim.x + tile_p;
         bool do_final = ok;
 
-        if (ok && p.splits > 1) {
+        if (p.cluster_reduce) {
+            // the partial tile goes to this CTA's staging tile; the cluster sums the tiles after the role branches
+            do_final = false;
+            if (ok) {
+                float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += CH) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
+                    if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) stage[(c0 + i) * BM + row] = __uint_as_float(r[i]);
+                }
+            }
+        } else if (ok && p.splits > 1) {
             // 1) publish this split's partial tile: layout [col][row] so that a warp writes 128 B per column
             float* wsp = p.workspace + ((size_t)(split * gridDim.x * gridDim.y + tile_lin)) * (BM * BN);
 #pragma unroll 1
@@ -587,9 +634,52 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             }
             if (p.splits > 1 && threadIdx.x == 64) p.counters[tile_lin] = 0u;  // ready for the next launch
         }
+        if (threadIdx.x == 64) MSTAR_TRACE(6);
         tc_fence_before();
     }
+    if (p.cluster_reduce) {
+        // Split-K without a trip through global memory: every CTA of the cluster holds the partial tile of its K
+        // range in shared memory [token][weight row]. After the cluster barrier CTA k sums token rows
+        // [k * rows / splits, (k + 1) * rows / splits) over all peers (fixed order: deterministic) into its own copy
+        // of those rows, which no peer reads, and finishes them (bias / activation / residual / store). The second
+        // barrier keeps every CTA's shared memory alive until its peers have read it.
+        __syncwarp();
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int tid = threadIdx.x - 64;
+            const int nsp = p.splits;
+            const int crank = (int)cluster_ctarank();
+            const int m_base = tile_q * BN;
+            int vr = p.M - m_base;
+            vr = vr > BN ? BN : (vr < 0 ? 0 : vr);
+            const int r0 = crank * vr / nsp, r1 = (crank + 1) * vr / nsp;
+            float* stage = reinterpret_cast<float*>(smem);
+            if (r1 > r0 && !flags[0]) {
+                uint32_t peer[8];
+                const uint32_t sbase = smem_u32(stage);
+#pragma unroll
+                for (int z = 0; z < 8; ++z) peer[z] = cluster_map_shared(sbase, (uint32_t)(z < nsp ? z : 0));
+                for (int e = r0 * (BM / 4) + tid; e < r1 * (BM / 4); e += 128) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int z = 0; z < 8; ++z) {
+                        if (z < nsp) {
+                            const float4 v = ld_cluster_f4(peer[z] + (uint32_t)e * 16u);
+                            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                        }
+                    }
+                    reinterpret_cast<float4*>(stage)[e] = acc;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (p.out_f32) copy_out_staged<true>(p, stage + r0 * BM, r1 - r0, m_base + r0, tile_p * BM, tid);
+                else copy_out_staged<false>(p, stage + r0 * BM, r1 - r0, m_base + r0, tile_p * BM, tid);
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();
+    }
     __syncthreads();
+    if (threadIdx.x == 0) MSTAR_TRACE(7);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -670,7 +760,14 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
                     uint8_t* sp = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                     tma_load_2d(sp, &tmP, &full_bar[s], kb * BK, tp * BM);
-                    tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kb * BK, tq * BN);
+                    if (p.w_packed) {
+#pragma unroll
+                        for (int h = 0; h < BN / 128; ++h)
+                            tma_load_2d(sp + P_BYTES + h * (128 * BK * 2), &tmQ, &full_bar[s], 0,
+                                        ((tq * (BN / 128) + h) * nkb + kb) * 128);
+                    } else {
+                        tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kb * BK, tq * BN);
+                    }
                     ++issued;
                 }
             }
@@ -760,6 +857,17 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
+// Split-K through a thread-block cluster (MSTAR_GEMM_CLUSTER=0 turns it off); cleared when a cluster launch fails.
+static bool g_cluster_reduce_ok = true;
+static bool cluster_reduce_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MSTAR_GEMM_CLUSTER");
+        v = e ? atoi(e) : 1;
+    }
+    return v != 0 && g_cluster_reduce_ok;
+}
+
 template <int BN, int STAGES, int MINB, int KSUB = 1>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
@@ -770,6 +878,20 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
         configured = true;
+    }
+    if (p.cluster_reduce) {
+        cudaError_t e = launch_pdl_cluster_z(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem,
+                                             stream, grid.z, tmP, tmQ, p);
+        if (e == cudaSuccess) return 0;
+        // this cluster shape cannot be launched here: remember it and take the scratch-buffer reduction
+        (void)cudaGetLastError();
+        g_cluster_reduce_ok = false;
+        if (p.workspace == nullptr) return set_error("gemm: cluster launch failed and no split-K scratch was given", e);
+        GemmParams q = p;
+        q.cluster_reduce = 0;
+        e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, q);
+        if (e != cudaSuccess) return set_error("gemm: launch failed", e);
+        return 0;
     }
     cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
@@ -856,6 +978,12 @@ static int dispatch_tile(int bn, int swap, const CUtensorMap& tmP, const CUtenso
 
 using namespace mstar;
 static GemmAllReduce g_next_ar = {};
+static unsigned long long* g_trace = nullptr;
+
+// Phase stamps for the benchmark: a device buffer of [CTAs][8] 64-bit words filled by later mstar_gemm_bf16 launches
+// (entry, prologue done, first loads issued, first tile landed, last UMMA issued, accumulator ready, epilogue done,
+// CTA exit), or null to stop.
+MSTAR_API void mstar_gemm_set_trace(void* buf) { g_trace = reinterpret_cast<unsigned long long*>(buf); }
 
 // Arms the tensor-parallel reduction for the NEXT mstar_gemm_bf16 call of this thread of control: the output is
 // summed over the ranks of the table inside the GEMM epilogue. state: two local device words [epoch, arrive].
@@ -923,10 +1051,10 @@ MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, i
 MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                               const void* bias, const void* residual, int ld_res, int epilogue, int out_f32,
                               float out_scale, void* workspace, long long workspace_bytes, void* counters,
-                              int n_counters, int force_splits, void* stream_) {
+                              int n_counters, int force_splits, int b_packed, void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    if ((lda % 8) || (!b_packed && (ldb % 8)) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
         return set_error("gemm: operands must be 16-byte aligned with leading dimensions multiple of 8", cudaSuccess);
     int swap, bn, splits, tiles;
     long long ws_need;
@@ -973,13 +1101,23 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
             return set_error("gemm+allreduce: grid must be co-resident", cudaSuccess);
     }
 
+    p.cluster_reduce = (swap && splits > 1 && splits <= 8 && !p.ar.enabled && cluster_reduce_enabled()) ? 1 : 0;
+    p.w_packed = b_packed ? 1 : 0;
+    p.trace = g_trace;
+    if (b_packed && !swap && bn < 128) return set_error("gemm: packed weights need a 128- or 256-wide tile", cudaSuccess);
+
     const void* Pp = swap ? B : A;
     const void* Qp = swap ? A : B;
     const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
     const int ldP = swap ? ldb : lda, ldQ = swap ? lda : ldb;
     CUtensorMap tmP, tmQ;
-    if (make_tmap_2d_bf16(&tmP, Pp, rowsP, K, ldP, BM, BK)) return -1;
-    if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
+    const int packed_rows = ((N + 127) / 128) * kblocks * 128;
+    if (b_packed && swap) {
+        if (make_tmap_2d_bf16(&tmP, Pp, packed_rows, BK, BK, BM, BK)) return -1;
+    } else if (make_tmap_2d_bf16(&tmP, Pp, rowsP, K, ldP, BM, BK)) return -1;
+    if (b_packed && !swap) {
+        if (make_tmap_2d_bf16(&tmQ, Qp, packed_rows, BK, BK, 128, BK)) return -1;
+    } else if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
     dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
     return dispatch_tile(bn, swap, tmP, tmQ, p, grid, stream);
 }

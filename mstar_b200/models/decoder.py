@@ -174,6 +174,8 @@ class DecoderLM(nn.Module):
         self.embed_tokens = _param((V, H), cfg.dtype, device) if cfg.has_embedding else None
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, self.tp, device) for i in range(cfg.num_layers)])
         self.norm = _param((H,), cfg.dtype, device)
+        self._head_packed = None
+        self._packed = False
         self.lm_head = None
         if cfg.has_lm_head and not cfg.tie_embeddings:
             self.lm_head = _param((V, H), cfg.dtype, device)
@@ -218,8 +220,42 @@ class DecoderLM(nn.Module):
             self.lm_head.copy_(draw(self.lm_head.shape).to(cfg.dtype))
         return self
 
-    def head_weight(self) -> torch.Tensor:
+    def head_weight(self):
+        if self._head_packed is not None:
+            return self._head_packed
         return self.lm_head if self.lm_head is not None else self.embed_tokens
+
+    @torch.no_grad()
+    def pack_weights(self) -> "DecoderLM":
+        """Re-store the projection weights tile by tile (``gemm.PackedWeight``) for the weight-streaming GEMMs of
+        the decode step. CUDA only; call after the weights are loaded. A tied embedding keeps its plain table for
+        the token gather and gets a packed copy for the output head."""
+        if self.embed_tokens.device.type != "cuda" or self._packed:
+            return self
+
+        def repack(mod, name):
+            w = getattr(mod, name)
+            if isinstance(w, gemm.PackedWeight) or w is None or w.shape[1] % 8:
+                return
+            pw = gemm.pack_weight(w.data)
+            delattr(mod, name)
+            setattr(mod, name, pw)
+
+        for layer in self.layers:
+            repack(layer.self_attn, "qkv_proj")
+            repack(layer.self_attn, "o_proj")
+            if isinstance(layer.mlp, GatedMLP):
+                repack(layer.mlp, "gate_up_proj")
+                repack(layer.mlp, "down_proj")
+        if self.cfg.has_lm_head:
+            hw = self.lm_head if self.lm_head is not None else self.embed_tokens
+            self._head_packed = gemm.pack_weight(hw.data)
+            if self.lm_head is not None:
+                del self.lm_head
+                self.lm_head = None
+        self._packed = True
+        torch.cuda.empty_cache()
+        return self
 
     # ---- forward ----
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:

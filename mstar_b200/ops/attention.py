@@ -11,6 +11,7 @@ FlashInfer's paged wrappers (mstar/utils/flashinfer_utils.py:70-489, mstar/engin
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from dataclasses import dataclass
 
@@ -46,6 +47,9 @@ def count_q_tiles(q_lens, group: int) -> int:
 
 def choose_splits(batch: int, num_kv_heads: int, num_q_tiles: int, max_kv_len: int, sm_count: int = 148) -> int:
     """Split-KV factor: fill the SMs when the batch is small and the context is long."""
+    forced = os.environ.get("MSTAR_DECODE_SPLITS")
+    if forced:
+        return max(1, int(forced))
     ctas = max(1, num_q_tiles * num_kv_heads)
     ktiles = max(1, (max_kv_len + 127) // 128)
     if ctas >= sm_count or ktiles <= 2:

@@ -44,6 +44,41 @@ def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor
     return out.reshape(2 * gate_w.shape[0], *gate_w.shape[1:]).contiguous()
 
 
+class PackedWeight:
+    """A [N, K] bf16 weight stored tile by tile for streaming: ``[ceil(N/128)][ceil(K/64)]`` tiles of 128 rows x 64
+    columns, each 16 KB contiguous, zero-padded at the ragged edges. One TMA box of the GEMM kernels is then one
+    contiguous run in DRAM instead of 128 separate 128-byte pieces a row pitch apart. ``linear`` accepts it in place
+    of the plain weight on CUDA; ``unpack`` gives the plain matrix back."""
+
+    __slots__ = ("data", "shape")
+
+    def __init__(self, data: torch.Tensor, shape: tuple[int, int]):
+        self.data, self.shape = data, tuple(shape)
+
+    @property
+    def device(self):
+        return self.data.device
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    def unpack(self) -> torch.Tensor:
+        N, K = self.shape
+        tn, tk = (N + 127) // 128, (K + 63) // 64
+        w = self.data.view(tn, tk, 128, 64).permute(0, 2, 1, 3).reshape(tn * 128, tk * 64)
+        return w[:N, :K].contiguous()
+
+
+def pack_weight(w: torch.Tensor) -> PackedWeight:
+    assert w.dim() == 2 and w.dtype == torch.bfloat16
+    N, K = w.shape
+    tn, tk = (N + 127) // 128, (K + 63) // 64
+    wp = F.pad(w, (0, tk * 64 - K, 0, tn * 128 - N)) if (N % 128 or K % 64) else w
+    data = wp.view(tn, 128, tk, 64).permute(0, 2, 1, 3).contiguous().view(tn * tk * 128, 64)
+    return PackedWeight(data, (N, K))
+
+
 def linear_ref(x, w, bias=None, residual=None, epilogue=EPILOGUE_NONE, out_dtype=None, out_scale=1.0):
     """fp32 PyTorch oracle with the same rounding points as the kernel (one rounding at the output)."""
     out_dtype = out_dtype or x.dtype
@@ -73,14 +108,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None, epilogue: int = EPILOGUE_NONE,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
            out_scale: float = 1.0, force_splits: int = 0) -> torch.Tensor:
-    """x: [..., K], w: [N, K] -> [..., N] (N/2 for the SwiGLU epilogue)."""
-    if not _lib.use_cuda(x, w):
+    """x: [..., K], w: [N, K] (or a ``PackedWeight``) -> [..., N] (N/2 for the SwiGLU epilogue)."""
+    packed = isinstance(w, PackedWeight)
+    if packed and not _lib.use_cuda(x, w.data):
+        w, packed = w.unpack(), False
+    if not packed and not _lib.use_cuda(x, w):
         return linear_ref(x, w, bias, residual, epilogue, out_dtype, out_scale)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
     K = x.shape[-1]
     N = w.shape[0]
     assert w.shape[1] == K
-    if (K % 8 or (N % 8 and N * K <= (1 << 22))) and epilogue != EPILOGUE_SWIGLU and residual is None and out is None:
+    if packed:
+        assert K % 8 == 0, "packed weights need K % 8 == 0"
+        if x.numel() // K > 128 and N <= 128:
+            w, packed = w.unpack(), False      # the token-major kernel has no packed path for tiles under 128 rows
+    if not packed and (K % 8 or (N % 8 and N * K <= (1 << 22))) and epilogue != EPILOGUE_SWIGLU and residual is None and out is None:
         # odd widths (a 7-wide action vector, a 10-wide head): zero-pad to the 16-byte granularity of the TMA tiles.
         # Only small weights are padded on the fly (a copy per call); a large matrix with an odd row COUNT runs as
         # it is (the kernel handles a ragged last tile), and an odd row LENGTH should be padded once at load time.
@@ -93,8 +135,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     x2 = x.reshape(-1, K)
     if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
         x2 = x2.contiguous()
-    if w.stride(-1) != 1 or w.stride(0) % 8:
+    if not packed and (w.stride(-1) != 1 or w.stride(0) % 8):
         w = w.contiguous()
+    wt = w.data if packed else w
     M = x2.shape[0]
     n_out = N // 2 if epilogue == EPILOGUE_SWIGLU else N
     out_dtype = out_dtype or x.dtype
@@ -112,12 +155,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
         return out.reshape(*x.shape[:-1], n_out)
     ws, counters = workspace(x.device)
     rc = _lib.kernels().mstar_gemm_bf16(
-        ctypes.c_void_p(x2.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(out2.data_ptr()),
-        M, N, K, x2.stride(0), w.stride(0), out2.stride(0),
+        ctypes.c_void_p(x2.data_ptr()), ctypes.c_void_p(wt.data_ptr()), ctypes.c_void_p(out2.data_ptr()),
+        M, N, K, x2.stride(0), wt.stride(0), out2.stride(0),
         ctypes.c_void_p(_lib.ptr(bias)), ctypes.c_void_p(_lib.ptr(res2)),
         res2.stride(0) if res2 is not None else 0, int(epilogue), 1 if out_dtype == torch.float32 else 0,
         ctypes.c_float(out_scale), ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(ws.numel()),
-        ctypes.c_void_p(counters.data_ptr()), counters.numel(), int(force_splits),
+        ctypes.c_void_p(counters.data_ptr()), counters.numel(), int(force_splits), 1 if packed else 0,
         ctypes.c_void_p(_lib.stream_ptr()))
     _lib.check(rc, "mstar_gemm_bf16")
     return out.reshape(*x.shape[:-1], n_out)
