@@ -5,6 +5,7 @@
 // Reference counterparts (Triton / FlashInfer / torch elementwise): mstar/utils/attention.py:137-286,447-501
 // (qk-norm+rope, rope, rms_norm), mstar/utils/adarms_norm.py:31-77, mstar/utils/flashinfer_utils.py:25-50,273-290,
 // mstar/model/pi05/kernels/image_normalize.py:39, mstar/model/bagel/submodules.py:1005-1100 (CFG combine).
+#include <cuda_fp8.h>
 #include "common.cuh"
 #include "host_common.h"
 
@@ -586,6 +587,59 @@ MSTAR_API int mstar_gated_residual(const void* x, const void* y, const void* gat
         hidden, rows_per_mod > 0 ? rows_per_mod : 1, gate_stride);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : set_error("gated_residual launch", e);
+}
+
+// Activation quantisation for the block-scaled fp8 GEMM: one scale per token row and 128-wide K block
+// (scale = max|x| / 448), e4m3 bytes out, scales written transposed ([K block][token]) as the GEMM reads them.
+// One warp per (row, K block): four elements per lane. Optional row gather (src_row[r], negative = zero row) serves
+// the mixture-of-experts path, which quantises the token copies in expert order.
+namespace mstar {
+__global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ src_row,
+                                       int src_div, unsigned char* __restrict__ out, long long ldo,
+                                       float* __restrict__ scale_t, int ld_s, int rows, int K) {
+    const int kblocks = (K + 127) / 128;
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= (long long)rows * kblocks) return;
+    const int r = (int)(w / kblocks), kb = (int)(w - (long long)r * kblocks);
+    long long sr = r;
+    if (src_row != nullptr) {
+        const int q = src_row[r];
+        sr = q < 0 ? -1 : q / src_div;
+    }
+    const int k0 = kb * 128 + lane * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sr >= 0 && k0 < K) {       // K is a multiple of 4
+        const uint2 raw = *reinterpret_cast<const uint2*>(x + sr * ldx + k0);
+        const float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax, 1e-12f) * (1.0f / 448.0f);
+    const float inv = 1.0f / scale;
+    if (k0 < K) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            packed |= (uint32_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+        *reinterpret_cast<uint32_t*>(out + (long long)r * ldo + k0) = packed;
+    }
+    if (lane == 0) scale_t[(long long)kb * ld_s + r] = scale;
+}
+}  // namespace mstar
+
+MSTAR_API int mstar_quant_fp8_1x128(const void* x, long long ldx, const int* src_row, int src_div, void* out,
+                                    long long ldo, float* scale_t, int ld_s, int rows, int K, void* stream_) {
+    if (rows <= 0) return 0;
+    if (K % 4 || ldx % 4 || ldo % 4) return set_error("quant_fp8: K and the leading dimensions must be multiples of 4", cudaSuccess);
+    const long long warps = (long long)rows * ((K + 127) / 128);
+    const long long blocks = (warps * 32 + 255) / 256;
+    quant_fp8_1x128_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream_>>>(
+        (const __nv_bfloat16*)x, ldx, src_row, src_div < 1 ? 1 : src_div, (unsigned char*)out, ldo, scale_t, ld_s, rows, K);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : set_error("quant_fp8 launch", e);
 }
 
 MSTAR_API int mstar_snake(const void* x, const float* alpha, void* out, long long n, int C, long long Tlen, int is_f32,

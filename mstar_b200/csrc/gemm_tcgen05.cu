@@ -160,9 +160,12 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int m, int 
 // a few dozen instructions, so that the once-per-CTA epilogue does not pay instruction-cache misses for 32
 // unrolled copies of the activation code), then one compact loop applies scale / bias / activation / residual
 // and writes 16 bytes per lane, contiguous along the output columns.
+// dry: run every instruction but keep the stores off. The epilogue warps call it once while the main loop streams,
+// so that the real call after the last UMMA finds its code in the instruction cache (each CTA is the first on its SM
+// for a one-wave decode GEMM: the cold epilogue measured 7 us of a 26 us kernel).
 template <bool OUT_F32>
 __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* stage, int rows, int m_base,
-                                             int n_in_base, int tid) {
+                                             int n_in_base, int tid, bool dry = false) {
     constexpr int EPV = OUT_F32 ? 4 : 8;                 // outputs per 16-byte store
     const int ipo = p.epilogue == 1 ? 2 : 1;             // accumulator columns per output (SwiGLU pairs)
     const int row_out = BM / ipo;
@@ -226,7 +229,7 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* s
             // expert-parallel combine: the destination row may live on a peer GPU; 16-byte peer stores
             if constexpr (!OUT_F32) {
                 __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.row_dst[m]);
-                if (drow != nullptr) {
+                if (drow != nullptr && !dry) {
                     if (full) {
                         *reinterpret_cast<uint4*>(drow + n) = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]),
                                                                            pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
@@ -259,6 +262,7 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* s
                     if (n + j < n_limit) x[j] += __bfloat162float(p.residual[(size_t)m * p.ld_res + n + j]);
             }
         }
+        if (dry) continue;
         if (vec_ok && full) {
             if constexpr (OUT_F32) {
                 *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n) =
@@ -370,7 +374,7 @@ __device__ __noinline__ void copy_out_allreduce(const GemmParams& p, const float
 template <int BN, int STAGES, int MINB, int KSUB = 1>
 __global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                         const GemmParams p) {
+                         const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int P_BYTES = BM * BK * 2;                 // one 64-wide P sub-tile
@@ -544,6 +548,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;  // accumulator row (TMEM lane) owned by this thread
         pdl_wait();
+        if (p.swap && !p.ar.enabled) {
+            // instruction-cache warm-up (see copy_out_staged); reads an untouched corner of the staging area
+            if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), 1, tile_q * BN, tile_p * BM, threadIdx.x - 64, true);
+            else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), 1, tile_q * BN, tile_p * BM, threadIdx.x - 64, true);
+        }
         bool ok = mbar_wait(acc_bar, 0, p.wait_limit_ns + 500000000ull);
         if (!ok) {
             report_status(p.status, KID_GEMM, 3, 0, 0);
@@ -696,7 +705,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                            const GemmParams p, const int tiles_p, const int tiles_q) {
+                            const __grid_constant__ GemmParams p, const int tiles_p, const int tiles_q) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int P_BYTES = BM * BK * 2;
@@ -855,6 +864,200 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
 }
 
 // ---------------------------------------------------------------------------------------------
+// Block-scaled fp8 GEMM (e4m3 operands): C[m,n] = sum over 128-wide K blocks kb of
+//     a_scale[m, kb] * w_scale[n / 128, kb] * sum_{k in kb} A8[m,k] * W8[n,k]
+// (1 x 128 activation scales, 128 x 128 weight scales). One K block is 128 bytes = one swizzle atom = four
+// kind::f8f6f4 UMMAs (K = 32). The tensor core cannot apply a different scale per K block inside one accumulation,
+// so each K block is accumulated on its own into one of TWO TMEM buffers; the four epilogue warps drain buffer
+// kb & 1 (tcgen05.ld), multiply by the block's scales and add into fp32 registers while the UMMA warp is already
+// filling the other buffer with block kb + 1. Both layouts of the bf16 kernel: decode (weights on UMMA M, one weight
+// scale per tile and K block, one activation scale per accumulator column) and token-major (tokens on UMMA M).
+// The grouped mixture-of-experts form uses the decode layout with the bf16 kernel's block -> expert table.
+// ---------------------------------------------------------------------------------------------
+struct Fp8Scales {
+    const float* a_scale_t;   // [kblocks, ld_as]: scale of token t and K block kb at kb * ld_as + t
+    const float* w_scale;     // [ceil(rows / 128), kblocks] over the (stacked) weight rows
+    int ld_as;
+};
+
+constexpr int F8_BK = 128;    // fp8 elements (= bytes) per K block
+
+__host__ __device__ constexpr int gemm_fp8_smem_bytes(int BN, int stages) {
+    return stages * (BM * F8_BK + BN * F8_BK) + 1024 /*alignment*/ + 1024 /*scales*/ + 256 /*barriers*/;
+}
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(192, 1)
+gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                            const __grid_constant__ GemmParams p, const Fp8Scales sc) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int P_BYTES = BM * F8_BK;
+    constexpr int Q_BYTES = BN * F8_BK;
+    constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    constexpr int ACC_COLS = BN < 32 ? 32 : BN;          // columns of one accumulator buffer
+    constexpr int TMEM_COLS = 2 * ACC_COLS;
+    static_assert(TMEM_COLS <= 512 && BN <= 128, "two accumulators of at most 128 columns");
+    float* scale_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);           // [2][128]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 1024);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;      // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_p = blockIdx.x, tile_q = blockIdx.y;
+    const int nkb = p.kblocks_total;
+    pdl_launch_dependents();
+    int p_row0 = tile_p * BM;
+    if (p.block_expert != nullptr) {
+        pdl_wait();
+        if (tile_q >= *p.num_blocks) return;
+        p_row0 += p.block_expert[tile_q] * p.N;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        flags[0] = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmP); tma_prefetch_desc(&tmQ); }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();
+            int issued = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)((kb / STAGES) & 1);
+                if (kb >= STAGES && !mbar_wait(&empty_bar[s], ph ^ 1, p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 21, kb, s);
+                    flags[0] = 1;
+                    break;
+                }
+                if (flags[0]) break;
+                uint8_t* sp = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(sp, &tmP, &full_bar[s], kb * F8_BK, p_row0);
+                tma_load_2d(sp + P_BYTES, &tmQ, &full_bar[s], kb * F8_BK, tile_q * BN);
+                issued = kb + 1;
+            }
+            if (flags[0]) {      // let copies in flight land before the CTA leaves
+                for (int g = (issued > STAGES ? issued - STAGES : 0); g < issued; ++g)
+                    mbar_wait(&full_bar[g % STAGES], (uint32_t)((g / STAGES) & 1), 1000000ull);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BM, BN, 0, 0);      // e4m3 x e4m3 -> f32
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                const int a = kb & 1;
+                if (!mbar_wait(&full_bar[s], (uint32_t)((kb / STAGES) & 1), p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 22, kb, s);
+                    flags[0] = 1;
+                    break;
+                }
+                // the epilogue must have drained this accumulator buffer (K block kb - 2)
+                if (kb >= 2 && !mbar_wait(&acc_empty[a], (uint32_t)(((kb >> 1) - 1) & 1), p.wait_limit_ns)) {
+                    report_status(p.status, KID_GEMM, 23, kb, a);
+                    flags[0] = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sp = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t da = umma_smem_desc_sw128(sp);
+                const uint64_t db = umma_smem_desc_sw128(sp + P_BYTES);
+                const uint32_t d = tmem_base + (uint32_t)(a * ACC_COLS);
+#pragma unroll
+                for (int k = 0; k < F8_BK / 32; ++k)      // 32 bytes per K slice inside the swizzle atom (encoded >> 4)
+                    umma_f8_ss(d, da + 2 * k, db + 2 * k, idesc, k != 0 ? 1u : 0u);
+                umma_commit(&empty_bar[s]);
+                umma_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        const int q4 = warp & 3;
+        const int row = q4 * 32 + lane;          // accumulator row (TMEM lane) of this thread
+        const int tid = threadIdx.x - 64;
+        const int pidx = tile_p * BM + row;
+        pdl_wait();
+        float acc[BN];
+#pragma unroll
+        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        const float* wsc = sc.w_scale + (size_t)((SWAP ? p_row0 : tile_q * BN) / 128) * nkb;
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int a = kb & 1;
+            float rowfac;
+            if constexpr (SWAP) {
+                // one weight scale for the tile, one activation scale per column: staged through shared memory
+                rowfac = wsc[kb];
+                if (tid < BN) {
+                    const int t = tile_q * BN + tid;
+                    scale_s[a * 128 + tid] = t < p.M ? sc.a_scale_t[(size_t)kb * sc.ld_as + t] : 0.f;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            } else {
+                rowfac = (pidx < p.M ? sc.a_scale_t[(size_t)kb * sc.ld_as + pidx] : 0.f) * wsc[kb];
+            }
+            if (!mbar_wait(&acc_full[a], (uint32_t)((kb >> 1) & 1), p.wait_limit_ns + 500000000ull)) {
+                report_status(p.status, KID_GEMM, 24, kb, a);
+                flags[0] = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            constexpr int CH = BN < 32 ? BN : 32;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * ACC_COLS + c0);
+                if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    if constexpr (SWAP) acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
+                    else acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac, acc[c0 + i]);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[a]);
+        }
+        if (ok) {
+            if constexpr (SWAP) {
+                // every UMMA has completed (its accumulator was read above): the pipeline stages are free
+                float* stage = reinterpret_cast<float*>(smem);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < BN; ++j) stage[j * BM + row] = acc[j];
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (p.out_f32) copy_out_staged<true>(p, stage, BN, tile_q * BN, tile_p * BM, tid);
+                else copy_out_staged<false>(p, stage, BN, tile_q * BN, tile_p * BM, tid);
+            } else {
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (p.out_f32) store_row_chunk<true>(p, pidx, tile_q * BN + c0, &acc[c0], 32);
+                    else store_row_chunk<false>(p, pidx, tile_q * BN + c0, &acc[c0], 32);
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 // Split-K through a thread-block cluster (MSTAR_GEMM_CLUSTER=0 turns it off); cleared when a cluster launch fails.
@@ -880,9 +1083,56 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
         configured = true;
     }
     if (p.cluster_reduce) {
-        cudaError_t e = launch_pdl_cluster_z(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem,
-                                             stream, grid.z, tmP, tmQ, p);
+        // Clusters are placed inside one GPC each, so a split factor that does not divide the GPCs' SM counts well
+        // leaves SMs unusable and the grid runs in two waves (measured: 24 clusters of 6 CTAs did, 24 of 4 do not).
+        // Ask the runtime how many clusters of each size are co-resident and take the largest factor, at most the
+        // planned one, whose clusters all fit.
+        static int max_active[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+        const int tiles = (int)(grid.x * grid.y);
+        int use = 0;
+        for (int sp = (int)grid.z; sp >= 2 && use == 0; --sp) {
+            if (max_active[sp] == 0) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(grid.x, grid.y, sp);
+                cfg.blockDim = dim3(192);
+                cfg.dynamicSmemBytes = smem;
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = sp;
+                cfg.attrs = at; cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, &cfg) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    n = -1;
+                }
+                max_active[sp] = n > 0 ? n : -1;
+            }
+            if (max_active[sp] >= tiles) use = sp;
+        }
+        GemmParams pc = p;
+        dim3 gc = grid;
+        if (use >= 2 && use != (int)grid.z) {
+            const int kpb = (p.kblocks_total + use - 1) / use;
+            pc.splits = (p.kblocks_total + kpb - 1) / kpb;
+            pc.kblocks_per_split = kpb;
+            gc.z = pc.splits;
+        }
+        cudaError_t e = cudaErrorInvalidConfiguration;
+        if (use >= 2 && gc.z >= 2)
+            e = launch_pdl_cluster_z(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, gc, dim3(192), smem, stream, gc.z,
+                                     tmP, tmQ, pc);
+        else if (use >= 2) {       // the K range collapsed to one split
+            pc.cluster_reduce = 0;
+            e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, gc, dim3(192), smem, stream, tmP, tmQ, pc);
+        }
         if (e == cudaSuccess) return 0;
+        if (use == 0 && p.workspace != nullptr) {       // no cluster size fits this grid: scratch-buffer reduction
+            GemmParams q = p;
+            q.cluster_reduce = 0;
+            e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, q);
+            if (e != cudaSuccess) return set_error("gemm: launch failed", e);
+            return 0;
+        }
         // this cluster shape cannot be launched here: remember it and take the scratch-buffer reduction
         (void)cudaGetLastError();
         g_cluster_reduce_ok = false;
@@ -1170,6 +1420,146 @@ MSTAR_API int mstar_moe_grouped_gemm(const void* A, const void* W, void* C, int 
         case 64: return launch_gemm<64, 4, 2>(tmP, tmQ, p, grid, stream);
         default: return launch_gemm<128, 3, 2>(tmP, tmQ, p, grid, stream);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// fp8 (e4m3) block-scaled GEMM entry points
+// ---------------------------------------------------------------------------------------------
+namespace mstar {
+
+static int make_tmap_2d_u8(CUtensorMap* out, const void* base, long long rows, int cols, long long ld, int box_rows) {
+    unsigned long long dims[2] = {(unsigned long long)cols, (unsigned long long)rows};
+    unsigned long long strides[2] = {1ull, (unsigned long long)ld};
+    unsigned int box[2] = {(unsigned int)F8_BK, (unsigned int)box_rows};
+    return make_tmap(out, base, 1, 2, dims, strides, box, 1);
+}
+
+template <int BN, int STAGES, bool SWAP>
+static int launch_fp8(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, const Fp8Scales& sc,
+                      dim3 grid, cudaStream_t stream) {
+    constexpr int smem = gemm_fp8_smem_bytes(BN, STAGES);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error("gemm_fp8: cudaFuncSetAttribute failed", e);
+        configured = true;
+    }
+    cudaError_t e = launch_pdl(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP>, grid, dim3(192), smem, stream, tmP, tmQ,
+                               p, sc);
+    if (e != cudaSuccess) return set_error("gemm_fp8: launch failed", e);
+    return 0;
+}
+
+static int dispatch_fp8(int bn, int swap, const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p,
+                        const Fp8Scales& sc, dim3 grid, cudaStream_t stream) {
+    if (swap) {
+        switch (bn) {
+            case 16: return launch_fp8<16, 8, true>(tmP, tmQ, p, sc, grid, stream);
+            case 32: return launch_fp8<32, 8, true>(tmP, tmQ, p, sc, grid, stream);
+            case 64: return launch_fp8<64, 8, true>(tmP, tmQ, p, sc, grid, stream);
+            case 128: return launch_fp8<128, 6, true>(tmP, tmQ, p, sc, grid, stream);
+        }
+    } else if (bn == 128) {
+        return launch_fp8<128, 6, false>(tmP, tmQ, p, sc, grid, stream);
+    }
+    return set_error("gemm_fp8: unsupported tile", cudaSuccess);
+}
+
+static void fill_fp8_params(GemmParams& p, int M, int N, int K, int swap, int epilogue, int out_f32, int ldc, void* C) {
+    p.M = M; p.N = N; p.K = K;
+    p.swap = swap;
+    p.splits = 1;
+    p.kblocks_total = (K + F8_BK - 1) / F8_BK;
+    p.kblocks_per_split = p.kblocks_total;
+    p.epilogue = epilogue;
+    p.out_f32 = out_f32;
+    p.ldc = ldc;
+    p.ld_res = 0;
+    p.C = C;
+    p.bias = nullptr;
+    p.residual = nullptr;
+    p.workspace = nullptr;
+    p.counters = nullptr;
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    p.out_scale = 1.0f;
+    p.ar = GemmAllReduce{};
+    p.block_expert = nullptr;
+    p.num_blocks = nullptr;
+    p.row_scale = nullptr;
+    p.row_dst = nullptr;
+}
+
+}  // namespace mstar
+
+// C[M,N] = (A8 * a_scale) (W8 * w_scale)^T (+bias, +residual, epilogue as in mstar_gemm_bf16).
+// A8 [M,K] and W8 [N,K] are e4m3 bytes, row-major, leading dimensions multiples of 16; a_scale_t is fp32
+// [ceil(K/128), ld_as] (one scale per token and 128-wide K block, token index contiguous, ld_as >= the token count
+// rounded up to the tile); w_scale is fp32 [ceil(N/128), ceil(K/128)].
+MSTAR_API int mstar_gemm_fp8(const void* A8, const void* a_scale_t, int ld_as, const void* W8, const void* w_scale,
+                             void* C, int M, int N, int K, int lda, int ldb, int ldc, const void* bias,
+                             const void* residual, int ld_res, int epilogue, int out_f32, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(A8) & 15) || (reinterpret_cast<uintptr_t>(W8) & 15))
+        return set_error("gemm_fp8: operands must be 16-byte aligned with leading dimensions multiple of 16", cudaSuccess);
+    const int swap = M <= 128 ? 1 : 0;
+    int bn = 128;
+    if (swap) {
+        bn = 16;
+        while (bn < M) bn <<= 1;
+        if (ld_as < bn) return set_error("gemm_fp8: activation scale rows must be padded to the token tile", cudaSuccess);
+    }
+    GemmParams p;
+    fill_fp8_params(p, M, N, K, swap, epilogue, out_f32, ldc, C);
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+    p.ld_res = ld_res;
+    Fp8Scales sc;
+    sc.a_scale_t = reinterpret_cast<const float*>(a_scale_t);
+    sc.w_scale = reinterpret_cast<const float*>(w_scale);
+    sc.ld_as = ld_as;
+    const void* Pp = swap ? W8 : A8;
+    const void* Qp = swap ? A8 : W8;
+    const int rowsP = swap ? N : M, rowsQ = swap ? M : N;
+    const int ldP = swap ? ldb : lda, ldQ = swap ? lda : ldb;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_u8(&tmP, Pp, rowsP, K, ldP, BM)) return -1;
+    if (make_tmap_2d_u8(&tmQ, Qp, rowsQ, K, ldQ, bn)) return -1;
+    dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, 1);
+    return dispatch_fp8(bn, swap, tmP, tmQ, p, sc, grid, stream);
+}
+
+// Grouped form for mixture-of-experts layers: as mstar_moe_grouped_gemm with e4m3 token rows (scales
+// [ceil(K/128), ld_as] over the sorted rows) and stacked e4m3 expert weights [E * N, K] (N a multiple of 128; scales
+// [E * N / 128, ceil(K/128)]).
+MSTAR_API int mstar_moe_grouped_gemm_fp8(const void* A8, const void* a_scale_t, int ld_as, const void* W8,
+                                         const void* w_scale, void* C, int capacity_rows, int N, int K, int E,
+                                         int block_rows, const int* block_expert, const int* num_blocks,
+                                         const float* row_scale, void* const* row_dst, int epilogue, int ldc,
+                                         void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (capacity_rows <= 0) return 0;
+    if (block_rows != 16 && block_rows != 32 && block_rows != 64 && block_rows != 128)
+        return set_error("moe gemm fp8: block_rows must be 16, 32, 64 or 128", cudaSuccess);
+    if (K % 16 || N % 128 || capacity_rows % block_rows || ld_as < capacity_rows)
+        return set_error("moe gemm fp8: K % 16, N % 128, capacity % block_rows and ld_as >= capacity are required", cudaSuccess);
+    GemmParams p;
+    fill_fp8_params(p, capacity_rows, N, K, 1, epilogue, 0, ldc, C);
+    p.block_expert = block_expert;
+    p.num_blocks = num_blocks;
+    p.row_scale = row_scale;
+    p.row_dst = row_dst;
+    Fp8Scales sc;
+    sc.a_scale_t = reinterpret_cast<const float*>(a_scale_t);
+    sc.w_scale = reinterpret_cast<const float*>(w_scale);
+    sc.ld_as = ld_as;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_u8(&tmP, W8, (long long)E * N, K, K, BM)) return -1;
+    if (make_tmap_2d_u8(&tmQ, A8, capacity_rows, K, K, block_rows)) return -1;
+    dim3 grid((N + BM - 1) / BM, capacity_rows / block_rows, 1);
+    return dispatch_fp8(block_rows, 1, tmP, tmQ, p, sc, grid, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -226,6 +226,14 @@ class DecoderLM(nn.Module):
         return self.lm_head if self.lm_head is not None else self.embed_tokens
 
     @torch.no_grad()
+    def quantize_moe_fp8(self) -> "DecoderLM":
+        """Block-scaled e4m3 expert weights for every mixture-of-experts layer (after the weights are loaded)."""
+        for layer in self.layers:
+            if hasattr(layer.mlp, "quantize_fp8"):
+                layer.mlp.quantize_fp8()
+        return self
+
+    @torch.no_grad()
     def pack_weights(self) -> "DecoderLM":
         """Re-store the projection weights tile by tile (``gemm.PackedWeight``) for the weight-streaming GEMMs of
         the decode step. CUDA only; call after the weights are loaded. A tied embedding keeps its plain table for

@@ -69,6 +69,19 @@ class SparseMoeBlock(nn.Module):
             load_gated_mlp(self.shared, draw((F_, H)), draw((F_, H)), draw((H, F_)), self.tp.rank, self.tp.size, cfg.dtype)
             self.shared_gate.copy_(draw((1, H)).to(cfg.dtype))
 
+    @torch.no_grad()
+    def quantize_fp8(self) -> "SparseMoeBlock":
+        """Re-store the expert weights as block-scaled e4m3 (128 x 128 scales); the expert GEMMs then quantise
+        their activations per 1 x 128 block and run the fp8 grouped kernel. Router and shared expert stay bf16.
+        Needs expert widths that are multiples of 128 (the scale block); other shapes are left as they are."""
+        from ..ops import gemm_fp8
+        if isinstance(self.w13, gemm_fp8.Fp8Weight) or (2 * self.I_local) % 128 or self.cfg.hidden_size % 128:
+            return self
+        w13, w2 = gemm_fp8.quantize_weight(self.w13.data), gemm_fp8.quantize_weight(self.w2.data)
+        del self.w13, self.w2
+        self.w13, self.w2 = w13, w2
+        return self
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         logits = gemm.linear(h, self.router, out_dtype=torch.float32)
         add = None
@@ -81,7 +94,9 @@ class SparseMoeBlock(nn.Module):
             y = moe_ops.fused_moe(h, logits, self.w13, self.w2, self.top_k, self.cfg.norm_topk_prob,
                                   self.expert_range, add=add)
             return tp_reduce(y.contiguous(), self.tp)
-        if self.ep is not None and self.ep.size > 1 and getattr(self.ep, "symm", None) is not None and h.is_cuda:
+        fp8 = not isinstance(self.w13, torch.Tensor)
+        if self.ep is not None and self.ep.size > 1 and getattr(self.ep, "symm", None) is not None and h.is_cuda \
+                and not fp8:
             from ..parallel.expert_parallel import ep_moe
             return ep_moe(self, h, logits, add)
         y = moe_ops.fused_moe(h, logits, self.w13, self.w2, self.top_k, self.cfg.norm_topk_prob,

@@ -123,8 +123,10 @@ class Qwen3OmniModel(Model):
     name = "qwen3_omni"
 
     def __init__(self, model_dir=None, skip_weight_loading=False, small: bool = False, expert_parallel: bool = False,
-                 max_num_pages: int | None = None, **kw):
+                 max_num_pages: int | None = None, fp8_experts: bool = False, **kw):
         super().__init__(model_dir, skip_weight_loading, **kw)
+        # block-scaled e4m3 expert weights (1 x 128 activation / 128 x 128 weight scales) in the thinker and talker
+        self.fp8_experts = fp8_experts
         dt = torch.bfloat16 if torch.cuda.is_available() else torch.float32
         self.small, self.dtype = small, dt
         self.t_cfg = thinker_config(dt, small, expert_parallel)
@@ -221,6 +223,8 @@ class Qwen3OmniModel(Model):
                 load_decoder_from_hf(lm, self.model_dir, prefix="thinker.model.", head_name="thinker.lm_head.weight")
             else:
                 lm.init_random(0)
+            if self.fp8_experts:
+                lm.quantize_moe_fp8()
             return MultimodalDecoderSubmodule(lm, device, {"audio_features": AUDIO_TOKEN, "image_features": IMAGE_TOKEN},
                                               eos_ids=(IM_END, ENDOFTEXT), loop_name="thinker_loop",
                                               position_fn=self._position_fn, emit_hidden="thinker_out")
@@ -231,6 +235,8 @@ class Qwen3OmniModel(Model):
                 load_decoder_from_hf(lm, self.model_dir, prefix="talker.model.", head_name="talker.codec_head.weight")
             else:
                 lm.init_random(2)
+            if self.fp8_experts:
+                lm.quantize_moe_fp8()
             pred = CodePredictor(self.pred_cfg, self.k_cfg.hidden_size, self.n_sub, self.codebook, device).init_random(3)
             return TalkerSubmodule(lm, pred, device, num_slots=64, codec_eos=self.codec_eos, cond_edge="thinker_out",
                                    cond_is_ids=False, cond_dim=self.t_cfg.hidden_size, loop_name="talker_loop")

@@ -131,7 +131,18 @@ def attention(q: torch.Tensor, plan: AttnPlan, *, kv_cache: torch.Tensor | None 
         return attention_ref(q, plan, kv_cache=kv_cache, k=k, v=v, scale=scale, lse=lse)
     T, Hq, D = q.shape
     if D not in (64, 128):
-        # head sizes the tensor-core kernels are not built for (e.g. 256-wide Gemma heads, 72-wide SigLIP heads):
+        if kv_cache is None and D < 128 and q.dtype == torch.bfloat16 and out is None:
+            # dense attention with an odd head size (72-wide SigLIP heads, 80-wide ViT heads): zero columns added
+            # to q and k leave the scores unchanged and zero columns of v give zero output columns, so the tensor-core
+            # kernel runs on the next size it is built for and the padding is cut off again
+            Dp = 64 if D < 64 else 128
+            pad = (0, Dp - D)
+            qp, kp_, vp_ = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+            res = attention(qp, plan, k=kp_, v=vp_, scale=scale if scale is not None else 1.0 / math.sqrt(D), lse=lse)
+            if lse:
+                return res[0][..., :D].contiguous(), res[1]
+            return res[..., :D].contiguous()
+        # head sizes the tensor-core kernels are not built for (256-wide Gemma heads, paged caches of odd widths):
         # the fp32 oracle, which is plain tensor code and runs on the GPU too (it reads the plan on the host)
         return attention_ref(q, plan, kv_cache=kv_cache, k=k, v=v, scale=scale, lse=lse)
     assert q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == D

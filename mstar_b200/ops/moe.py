@@ -4,7 +4,8 @@ stores over the symmetric heap.
 
 GPU: csrc/moe.cu + the grouped mode of csrc/gemm_tcgen05.cu. Oracle: ``moe_ref`` (dense loop over experts, fp32).
 Reference counterparts: ``fused_experts`` / ``moe_align_block_size`` (mstar/utils/fused_moe/*), TP-MoE block
-(mstar/model/components/moe.py:378-591). The reference has no expert parallelism and no fp8 path.
+(mstar/model/components/moe.py:378-591). The reference has no expert parallelism and no fp8 path; here expert
+weights given as ``gemm_fp8.Fp8Weight`` run the block-scaled e4m3 grouped GEMM.
 """
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ import ctypes
 import torch
 import torch.nn.functional as F
 
-from . import _lib, gemm
+from . import _lib, gemm, gemm_fp8
 
 
 def route_ref(logits: torch.Tensor, top_k: int, renorm: bool = True):
@@ -97,6 +98,25 @@ def fused_moe(x: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor, w
     E = router_logits.shape[1]
     E_local, I = w13.shape[0], w2.shape[2]
     e0, e1 = expert_range or (0, E)
+    fp8 = isinstance(w13, gemm_fp8.Fp8Weight)
+    if fp8 and not _lib.use_cuda(x):
+        # CPU oracle of the fp8 path: same routing, activations quantised per 1 x 128 block before each expert GEMM
+        ids, w = route_ref(router_logits, top_k, renorm)
+        w13f, w2f = w13.dequant(), w2.dequant()
+        out = torch.zeros(T, H, dtype=torch.float32)
+        for e in range(e0, e1):
+            m = ids == e
+            rows = m.any(-1).nonzero().flatten()
+            if rows.numel():
+                q, st = gemm_fp8.quantize_act_ref(x[rows])
+                gu = F.linear(gemm_fp8._dequant_act(q, st), w13f[e - e0])
+                h = (F.silu(gu[:, 0::2]) * gu[:, 1::2]).to(x.dtype)
+                q2, st2 = gemm_fp8.quantize_act_ref(h)
+                y = F.linear(gemm_fp8._dequant_act(q2, st2), w2f[e - e0])
+                out[rows] += ((w * m)[rows].sum(-1, keepdim=True) * y).to(x.dtype).float()
+        if add is not None:
+            out += add.float()
+        return out.to(x.dtype)
     if not _lib.use_cuda(x):
         ids, w = route_ref(router_logits, top_k, renorm)
         out = torch.zeros(T, H, dtype=torch.float32)
@@ -117,6 +137,23 @@ def fused_moe(x: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor, w
     _lib.check(L.mstar_moe_topk(_p(router_logits), T, E, top_k, 1 if renorm else 0, _p(ws.topk_ids), _p(ws.topk_w), s), "moe_topk")
     _lib.check(L.mstar_moe_align(_p(ws.topk_ids), _p(ws.topk_w), T * top_k, E, br, ws.capacity, e0, e1, _p(ws.sorted_pair),
                                  _p(ws.sorted_w), _p(ws.pos_of_pair), _p(ws.block_expert), _p(ws.num_blocks), s), "moe_align")
+    if fp8:
+        # token copies are gathered in expert order and quantised in one kernel; the SwiGLU output is quantised again
+        # for the second expert GEMM
+        x8, xs = gemm_fp8.quantize_act(x, src_row=ws.sorted_pair, src_div=top_k, rows=ws.capacity)
+        _lib.check(L.mstar_moe_grouped_gemm_fp8(_p(x8), _p(xs), int(xs.stride(0)), _p(w13.data), _p(w13.scale),
+                                                _p(ws.h_sorted), ws.capacity, 2 * I, H, E_local, br, _p(ws.block_expert),
+                                                _p(ws.num_blocks), None, None, gemm.EPILOGUE_SWIGLU, I, s),
+                   "moe_grouped_gemm_fp8 1")
+        h8, hs = gemm_fp8.quantize_act(ws.h_sorted[:ws.capacity])
+        _lib.check(L.mstar_moe_grouped_gemm_fp8(_p(h8), _p(hs), int(hs.stride(0)), _p(w2.data), _p(w2.scale),
+                                                _p(ws.y_sorted), ws.capacity, H, I, E_local, br, _p(ws.block_expert),
+                                                _p(ws.num_blocks), _p(ws.sorted_w), None, 0, H, s),
+                   "moe_grouped_gemm_fp8 2")
+        out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+        _lib.check(L.mstar_moe_unpermute(_p(ws.y_sorted), _p(ws.pos_of_pair), None, T, top_k, H, ctypes.c_longlong(H),
+                                         _p(out), _p(add), s), "moe_unpermute")
+        return out
     _lib.check(L.mstar_moe_permute(_p(x), _p(ws.sorted_pair), ws.capacity, H, top_k, _p(ws.x_sorted), None, s), "moe_permute")
     _lib.check(L.mstar_moe_grouped_gemm(_p(ws.x_sorted), _p(w13), _p(ws.h_sorted), ws.capacity, 2 * I, H, E_local, br,
                                         _p(ws.block_expert), _p(ws.num_blocks), None, None, gemm.EPILOGUE_SWIGLU, I, s),

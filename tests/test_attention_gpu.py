@@ -103,6 +103,24 @@ def test_dense_varlen(causal):
     _close(A.attention(q, plan, k=k, v=v), A.attention_ref(q, plan, k=k, v=v))
 
 
+@pytest.mark.parametrize("D", [72, 40, 96])
+def test_dense_odd_head_sizes_run_on_the_padded_kernel(D):
+    """Encoder head sizes between the kernel's 64 and 128 (SigLIP 72, ViT 80 / 96) and below 64."""
+    g = torch.Generator().manual_seed(17)
+    Hq = Hkv = 6
+    q_lens = [300, 77]
+    q = torch.randn(sum(q_lens), Hq, D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(sum(q_lens), Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(sum(q_lens), Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    plan = A.dense_plan(q_lens, q_lens, 1, "cuda", causal=False)
+    from mstar_b200.ops import _counters
+    n0 = _counters.get()
+    got = A.attention(q, plan, k=k, v=v)
+    assert _counters.get() > n0, "the tensor-core kernel must have been launched"
+    assert got.shape == q.shape
+    _close(got, A.attention_ref(q, plan, k=k, v=v))
+
+
 def test_dense_cross_attention_from_fused_buffer():
     """K/V as strided views (cross attention: q_len != kv_len, non-causal)."""
     g = torch.Generator().manual_seed(13)
