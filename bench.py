@@ -206,14 +206,14 @@ def main():
     barrier()
     l0 = _counters.get()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s1 = eng.stats["decode_steps"]
     ev0.record()
     for _ in range(args.steps):
-        eng._plan_rows(live, C)          # the step's plan upload is part of the step
-        graph.replay()
-        for r in live.values():
-            eng.cache.alloc.get_state(r.request_id, "main").seq_len += 1
+        eng.step()                       # plan upload of step n + 1 overlaps the replay of step n, as in serving
+    eng._drain()
     ev1.record()
     torch.cuda.synchronize()
+    assert eng.stats["decode_steps"] - s1 == args.steps
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
     eng.check_status()

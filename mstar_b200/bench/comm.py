@@ -6,8 +6,9 @@ Run one process per GPU:
     python -m torch.distributed.run --standalone --local-addr 127.0.0.1 --nproc-per-node 2 \
         -m mstar_b200.bench.comm
 
-Every figure is a CUDA-event time on the launching stream after warm-up, the maximum over ranks; rank 0 prints one
-JSON line per path.
+Every figure is a CUDA-event time around a captured graph of back-to-back calls, after warm-up, the maximum over
+ranks; operands that would otherwise stay in the L2 rotate through more memory than it holds. Rank 0 prints one JSON
+line per path.
 """
 from __future__ import annotations
 
@@ -31,23 +32,50 @@ def _peaks():
         return GEMM_TFLOPS, 6650.0
 
 
-def timed(fn, iters, warmup, dev, flush=None):
-    for _ in range(warmup):
-        fn()
+def timed(fn, iters, warmup, dev, capture=True):
+    """Device time of one call: ``iters`` calls are captured in one CUDA graph and replayed between two events, so
+    neither the host's launch cost nor the skew between the ranks' hosts is in the figure (a rank that arrives early
+    only waits once, at the first call). ``fn`` takes the call index, for operands that rotate through more memory
+    than the L2 holds. Falls back to back-to-back eager launches when the capture fails."""
+    for i in range(warmup):
+        fn(i)
     torch.cuda.synchronize()
     dist.barrier()
-    torch.cuda.synchronize()
-    total = 0.0
-    for _ in range(iters):
-        if flush is not None:
-            flush.add_(1)
+    graph = None
+    try:
+        if not capture:
+            raise RuntimeError("eager timing requested")
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
+                for i in range(iters):
+                    fn(i)
+        torch.cuda.current_stream().wait_stream(s)
+        graph = g
+    except Exception:  # noqa: BLE001
+        torch.cuda.synchronize()
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    use_graph = bool(ok.item())
+    best = None
+    for _ in range(3):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(iters):
+                fn(i)
         e1.record()
         torch.cuda.synchronize()
-        total += e0.elapsed_time(e1)
-    t = torch.tensor([total / iters], dtype=torch.float64, device=dev)
+        t = e0.elapsed_time(e1) / iters
+        best = t if best is None else min(best, t)
+    t = torch.tensor([best], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.item() * 1e3          # microseconds
 
@@ -71,7 +99,6 @@ def main():
     W, R = g.size, g.rank
     heap = attach_symmetric_heap(g, dev, slot_bytes=64 << 20, user_bytes=768 << 20)
     tflops, _ = _peaks()
-    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)      # larger than L2, written between iterations
     rows = []
 
     def report(**kw):
@@ -83,10 +110,10 @@ def main():
     x = torch.randn(64, 3072, device=dev).to(torch.bfloat16)
     res = torch.randn(64, 3072, device=dev).to(torch.bfloat16)
     out = torch.empty_like(x)
-    t_ours = timed(lambda: heap.all_reduce(x, residual=res, out=out), args.iters, args.warmup, dev)
+    t_ours = timed(lambda i: heap.all_reduce(x, residual=res, out=out), args.iters, args.warmup, dev)
     y = x.clone()
 
-    def nccl_ar():
+    def nccl_ar(i):
         y.copy_(x)
         dist.all_reduce(y)
         y.add_(res)
@@ -96,9 +123,9 @@ def main():
     # ---- DiT-sized all-reduce (the tokens of one sequence-parallel rank x hidden), bandwidth bound ----
     xb = torch.randn(21120, 2048, device=dev).to(torch.bfloat16)
     ob = torch.empty_like(xb)
-    t_ours = timed(lambda: heap.all_reduce(xb, out=ob), args.iters, args.warmup, dev, flush)
+    t_ours = timed(lambda i: heap.all_reduce(xb, out=ob), args.iters, args.warmup, dev)
     yb = xb.clone()
-    t_nccl = timed(lambda: dist.all_reduce(yb), args.iters, args.warmup, dev, flush)
+    t_nccl = timed(lambda i: dist.all_reduce(yb), args.iters, args.warmup, dev)
     link_us = 2 * (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
     report(path="all-reduce, 21120x2048 bf16", ranks=W, ours_us=round(t_ours, 2), nccl_us=round(t_nccl, 2),
            roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_ours, 3))
@@ -106,16 +133,17 @@ def main():
     # ---- row-parallel projection: GEMM with the all-reduce in its epilogue (o_proj / down_proj of a decode step) ----
     for (M, N, K, name) in [(64, 3072, 3072 // W, "o_proj"), (64, 3072, 8192 // W, "down_proj")]:
         xa = torch.randn(M, K, device=dev).to(torch.bfloat16)
-        w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+        nw = max(2, (192 << 20) // (N * K * 2) + 1)          # weight copies: together larger than the L2
+        ws = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(nw)]
         r2 = torch.randn(M, N, device=dev).to(torch.bfloat16)
-        t_f = timed(lambda: heap.linear_all_reduce(xa, w, residual=r2), args.iters, args.warmup, dev, flush)
+        t_f = timed(lambda i: heap.linear_all_reduce(xa, ws[i % nw], residual=r2), args.iters, args.warmup, dev)
 
-        def base():
-            yy = gemm.linear(xa, w)
+        def base(i):
+            yy = gemm.linear(xa, ws[i % nw])
             dist.all_reduce(yy)
             yy.add_(r2)
-        t_b = timed(base, args.iters, args.warmup, dev, flush)
-        t_g = timed(lambda: gemm.linear(xa, w, residual=r2), args.iters, args.warmup, dev, flush)
+        t_b = timed(base, args.iters, args.warmup, dev)
+        t_g = timed(lambda i: gemm.linear(xa, ws[i % nw], residual=r2), args.iters, args.warmup, dev)
         # roofline: the weight stream from HBM (N*K*2 bytes) against the partial tiles crossing NVLink
         link_us = M * N * 2 * (W - 1) / (LINK_GBS * 1e3)
         hbm_us = N * K * 2 / (_peaks()[1] * 1e3)
@@ -129,14 +157,14 @@ def main():
     seq_off = [S // W * i for i in range(W + 1)]
     mine = torch.randn(S // W, H, D, device=dev).to(torch.bfloat16)
     off_f = heap.alloc_user(S * (H // W) * D * 2)
-    t_a2a = timed(lambda: heap.a2a_heads(mine, off_f, True, H, D, seq_off), args.iters, args.warmup, dev, flush)
+    t_a2a = timed(lambda i: heap.a2a_heads(mine, off_f, True, H, D, seq_off), args.iters, args.warmup, dev)
     src = mine.view(S // W, W, H // W, D).permute(1, 0, 2, 3).contiguous()
     dst = torch.empty_like(src)
 
-    def nccl_a2a():
+    def nccl_a2a(i):
         s2 = mine.view(S // W, W, H // W, D).permute(1, 0, 2, 3).contiguous()
         dist.all_to_all_single(dst, s2)
-    t_na = timed(nccl_a2a, args.iters, args.warmup, dev, flush)
+    t_na = timed(nccl_a2a, args.iters, args.warmup, dev)
     link_us = mine.numel() * 2 * (W - 1) / W / (LINK_GBS * 1e3)
     report(path=f"Ulysses exchange, {S} tokens x {H} heads x {D}", ranks=W, ours_us=round(t_a2a, 2),
            nccl_us=round(t_na, 2), roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_a2a, 3),
@@ -151,22 +179,22 @@ def main():
     torch.cuda.synchronize()
     dist.barrier()
     if R == 0:
-        def fused():
+        def fused(i):
             heap.cfg_combine(v_off, 0, 1, -1, xx, dt=-0.02, s_text=4.0, renorm=True, wait_peers=False)
     else:
-        def fused():
+        def fused(i):
             pass
-    t_c = timed(fused, args.iters, args.warmup, dev, flush)
+    t_c = timed(fused, args.iters, args.warmup, dev)
     vu = torch.empty(rws, cols, device=dev)
     vl = heap.local_view(v_off, (rws, cols), torch.float32)
 
-    def base_cfg():
+    def base_cfg(i):
         if R == 1:
             dist.send(vl, 0)
         elif R == 0:
             dist.recv(vu, 1)
             cfg_combine(vl, vu, xx, -0.02, 4.0, renorm=True)
-    t_cb = timed(base_cfg, args.iters, args.warmup, dev, flush)
+    t_cb = timed(base_cfg, args.iters, args.warmup, dev, capture=False)     # NCCL send / recv: eager launches
     link_us = rws * cols * 4 / (LINK_GBS * 1e3)
     report(path=f"CFG gather + combine + Euler step, {rws}x{cols} fp32", ranks=W, fused_us=round(t_c, 2),
            nccl_recv_plus_combine_us=round(t_cb, 2), roofline_us=round(link_us, 2),

@@ -16,6 +16,7 @@
 // Reference counterparts: FlashInfer BatchDecodeWithPagedKVCacheWrapper (mstar/utils/flashinfer_utils.py:293-489),
 // Triton dense-KV decode kernel (mstar/utils/attention.py:6-134).
 #include <cuda.h>
+#include <stdlib.h>
 #include "common.cuh"
 #include "host_common.h"
 
@@ -55,7 +56,7 @@ __host__ __device__ constexpr int da_smem_bytes(int ks, int vs) {
 template <int KS, int VS, int NC, int MINB>
 __global__ void __launch_bounds__(192, MINB)
 attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                           const DecAttnParams p) {
+                           const __grid_constant__ DecAttnParams p) {
     constexpr int TMEM_S0 = 0, TMEM_S1 = 16, TMEM_O = 32, TMEM_COLS = 64;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -313,7 +314,19 @@ MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_s
                                      tmK, tmV, p);                                                                \
         if (le_ != cudaSuccess) return set_error("attention_decode: launch failed", le_);                         \
     } while (0)
-    if (many) {
+    // MSTAR_DA_RING (tuning aid): 21 = two K tiles + one V tile, two CTAs per SM; 22 = two of each, one CTA per SM
+    static int ring = -1;
+    if (ring < 0) {
+        const char* e = getenv("MSTAR_DA_RING");
+        ring = e ? atoi(e) : 0;
+    }
+    if (many && ring == 21 && ncols_max <= 4) {
+        MSTAR_DA_LAUNCH(2, 1, 4, 2);
+    } else if (many && ring == 22 && ncols_max <= 4) {
+        MSTAR_DA_LAUNCH(2, 2, 4, 1);
+    } else if (many && ring == 33 && ncols_max <= 4) {
+        MSTAR_DA_LAUNCH(3, 3, 4, 1);
+    } else if (many) {
         if (ncols_max <= 4) MSTAR_DA_LAUNCH(1, 1, 4, 3);
         else if (ncols_max <= 8) MSTAR_DA_LAUNCH(1, 1, 8, 3);
         else MSTAR_DA_LAUNCH(1, 1, 16, 2);

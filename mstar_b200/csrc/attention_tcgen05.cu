@@ -81,7 +81,7 @@ constexpr int AT_THREADS = 320;
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                    const AttnParams p) {
+                    const __grid_constant__ AttnParams p) {
     using SM = AttnSmem<HD>;
     constexpr int KATOMS = HD / 64;           // 64-element (128-byte) atoms along the head dim
     constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256;

@@ -40,7 +40,7 @@ struct ARParams {
 };
 
 // One-shot: grid-stride over 16-byte vectors; CTA b owns vectors [b*chunk, (b+1)*chunk) and flag channel b.
-__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const ARParams p) {
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ ARParams p) {
     __shared__ int s_ok;
     __shared__ unsigned int s_epoch;
     pdl_launch_dependents();
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const ARParams p
 
 // Two-shot: rank r owns vectors [r*share, (r+1)*share); it sums that slice from every rank's slot and stores the
 // result into every rank's `gather` region (second half of the slot), then signals; everyone copies out.
-__global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const ARParams p) {
+__global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_constant__ ARParams p) {
     __shared__ int s_ok;
     __shared__ unsigned int s_epoch;
     pdl_launch_dependents();
@@ -136,23 +136,43 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const ARParams p
         const long long a = v0 + R * share;
         long long b = a + share;
         if (b > v1) b = v1;
-        for (long long v = a + threadIdx.x; v < b; v += blockDim.x) {
-            float acc[8];
+        // four vectors per thread and trip: every peer load is an NVLink round trip, and only loads that are in
+        // flight together hide it (one vector per trip measured 0.37 of the link rate on 86 MB)
+        constexpr int UN = 8;
+        for (long long v = a + threadIdx.x; v < b; v += (long long)blockDim.x * UN) {
+            float acc[UN][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int u = 0; u < UN; ++u)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
             for (int r = 0; r < W; ++r) {
-                const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes)[v];
-                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                const uint4* src_r = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes);
+                uint4 x[UN];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = unpack_bf16x2(w[j]);
-                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+                for (int u = 0; u < UN; ++u) {
+                    const long long vu = v + (long long)u * blockDim.x;
+                    x[u] = vu < b ? src_r[vu] : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < UN; ++u) {
+                    const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = unpack_bf16x2(w[j]);
+                        acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y;
+                    }
                 }
             }
-            const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-            for (int r = 0; r < W; ++r)
-                reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[r]) + parity * p.slot_bytes + half_bytes)[v] = o;
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const long long vu = v + (long long)u * blockDim.x;
+                if (vu < b) {
+                    const uint4 o = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                                               pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+                    for (int r = 0; r < W; ++r)
+                        reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[r]) + parity * p.slot_bytes + half_bytes)[vu] = o;
+                }
+            }
         }
     }
     __threadfence_system();
@@ -199,7 +219,7 @@ struct BarrierParams {
     KernelStatus* status;
     unsigned long long wait_limit_ns;
 };
-__global__ void peer_barrier_kernel(const BarrierParams p) {
+__global__ void peer_barrier_kernel(const __grid_constant__ BarrierParams p) {
     pdl_launch_dependents();
     pdl_wait();
     if (threadIdx.x == 0) {
@@ -228,7 +248,7 @@ struct A2AParams {
     KernelStatus* status;
     unsigned long long wait_limit_ns;
 };
-__global__ void __launch_bounds__(256) a2a_heads_kernel(const A2AParams p) {
+__global__ void __launch_bounds__(256) a2a_heads_kernel(const __grid_constant__ A2AParams p) {
     __shared__ unsigned int s_epoch;
     pdl_launch_dependents();
     pdl_wait();
@@ -315,7 +335,8 @@ __device__ __forceinline__ void cfg_publish_epoch(const CfgPeerParams& p, unsign
         }
     }
 }
-__global__ void __launch_bounds__(128) cfg_combine_peer_kernel(const CfgPeerParams p) {
+constexpr int CFG_STAGE_MAX_COLS = 8192;      // 32 KB of shared memory for the staged row
+__global__ void __launch_bounds__(128) cfg_combine_peer_kernel(const __grid_constant__ CfgPeerParams p) {
     __shared__ float red[32];
     __shared__ int s_ok;
     __shared__ unsigned int s_e;
@@ -344,12 +365,38 @@ __global__ void __launch_bounds__(128) cfg_combine_peer_kernel(const CfgPeerPara
     const float* vu = reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.t.buf[p.uncond_rank]) + p.v_offset_bytes);
     const float* vi = p.img_rank >= 0
         ? reinterpret_cast<const float*>(reinterpret_cast<const char*>(p.t.buf[p.img_rank]) + p.v_offset_bytes) : nullptr;
+    // One pass over the peers' rows: 16-byte loads (a peer load is an NVLink round trip; the first version read
+    // every value twice with 4-byte loads and reached 0.27 of the link rate), the combined velocity parked in
+    // shared memory for the second pass that applies the row's renormalisation.
+    extern __shared__ float vrow[];          // [cols] when it fits (host passes the size), else the row is re-read
+    const bool staged = p.cols <= CFG_STAGE_MAX_COLS;
+    const bool vec = (p.cols & 3) == 0 && (p.v_offset_bytes & 15) == 0;
     float nc = 0.f, nv = 0.f;
-    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
-        const float c = vc[base + i], u = vu[base + i];
-        float v = u + p.s_text * (c - u);
-        if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
-        nc += c * c; nv += v * v;
+    if (vec) {
+        const float4* vc4 = reinterpret_cast<const float4*>(vc + base);
+        const float4* vu4 = reinterpret_cast<const float4*>(vu + base);
+        const float4* vi4 = vi ? reinterpret_cast<const float4*>(vi + base) : nullptr;
+        for (int i = threadIdx.x; i < (p.cols >> 2); i += blockDim.x) {
+            const float4 c = vc4[i], u = vu4[i];
+            float4 v = make_float4(u.x + p.s_text * (c.x - u.x), u.y + p.s_text * (c.y - u.y),
+                                   u.z + p.s_text * (c.z - u.z), u.w + p.s_text * (c.w - u.w));
+            if (vi4) {
+                const float4 im = vi4[i];
+                v = make_float4(im.x + p.s_img * (v.x - im.x), im.y + p.s_img * (v.y - im.y),
+                                im.z + p.s_img * (v.z - im.z), im.w + p.s_img * (v.w - im.w));
+            }
+            nc += c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
+            nv += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            if (staged) reinterpret_cast<float4*>(vrow)[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+            const float c = vc[base + i], u = vu[base + i];
+            float v = u + p.s_text * (c - u);
+            if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
+            nc += c * c; nv += v * v;
+            if (staged) vrow[i] = v;
+        }
     }
     float scale = 1.f;
     if (p.renorm) {
@@ -360,20 +407,39 @@ __global__ void __launch_bounds__(128) cfg_combine_peer_kernel(const CfgPeerPara
         nv = red[4] + red[5] + red[6] + red[7];
         scale = fminf(fmaxf(sqrtf(nc) / (sqrtf(nv) + 1e-8f), p.renorm_min), 1.f);
     }
-    for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
-        const float c = vc[base + i], u = vu[base + i];
-        float v = u + p.s_text * (c - u);
-        if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
-        v *= scale;
-        if (p.v_out) p.v_out[base + i] = v;
-        if (p.x_next) p.x_next[base + i] = p.x[base + i] + p.dt * v;
+    // each thread re-reads exactly the elements it wrote, so no barrier is needed for the staged row
+    if (staged && vec) {
+        for (int i = threadIdx.x; i < (p.cols >> 2); i += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(vrow)[i];
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+            if (p.v_out) reinterpret_cast<float4*>(p.v_out + base)[i] = v;
+            if (p.x_next) {
+                const float4 x = reinterpret_cast<const float4*>(p.x + base)[i];
+                reinterpret_cast<float4*>(p.x_next + base)[i] =
+                    make_float4(x.x + p.dt * v.x, x.y + p.dt * v.y, x.z + p.dt * v.z, x.w + p.dt * v.w);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < p.cols; i += blockDim.x) {
+            float v;
+            if (staged) {
+                v = vrow[i];
+            } else {
+                const float c = vc[base + i], u = vu[base + i];
+                v = u + p.s_text * (c - u);
+                if (vi) { const float im = vi[base + i]; v = im + p.s_img * (v - im); }
+            }
+            v *= scale;
+            if (p.v_out) p.v_out[base + i] = v;
+            if (p.x_next) p.x_next[base + i] = p.x[base + i] + p.dt * v;
+        }
     }
     cfg_publish_epoch(p, s_e);
 }
 
 // Raise this rank's flag on `channel` at rank `dst` (after earlier kernels' stores to the heap): one thread.
 struct SignalParams { PeerTable t; unsigned int* epoch; int channel; int dst; int bump_epoch; };
-__global__ void peer_signal_kernel(const SignalParams p) {
+__global__ void peer_signal_kernel(const __grid_constant__ SignalParams p) {
     pdl_launch_dependents();
     pdl_wait();
     if (threadIdx.x == 0) {

@@ -51,7 +51,7 @@ struct NormParams {
 };
 
 template <int NT, int MAXV>
-__global__ void __launch_bounds__(NT) norm_kernel(const NormParams p) {
+__global__ void __launch_bounds__(NT) norm_kernel(const __grid_constant__ NormParams p) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];
@@ -204,7 +204,7 @@ struct RopeParams {
     float attn_scale_q;  // multiplies q after rope (1.0 = off)
 };
 
-__global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
+__global__ void __launch_bounds__(256) rope_kv_kernel(const __grid_constant__ RopeParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -437,7 +437,7 @@ struct CfgParams {
     float s_text, s_img, dt, renorm_min;
     int renorm;
 };
-__global__ void __launch_bounds__(128) cfg_combine_kernel(const CfgParams p) {
+__global__ void __launch_bounds__(128) cfg_combine_kernel(const __grid_constant__ CfgParams p) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];

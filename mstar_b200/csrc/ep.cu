@@ -27,7 +27,7 @@ struct EpDispatchParams {
     int* send_counters;           // local [world], zero on entry
 };
 
-__global__ void __launch_bounds__(128) ep_dispatch_kernel(const EpDispatchParams p) {
+__global__ void __launch_bounds__(128) ep_dispatch_kernel(const __grid_constant__ EpDispatchParams p) {
     __shared__ int s_dst, s_slot;
     pdl_launch_dependents();
     pdl_wait();
@@ -72,7 +72,7 @@ struct EpPrepareParams {
     float* w_flat;
     void** dst_flat;      // [world * cap] destination row pointers (source ranks' combine buffers)
 };
-__global__ void ep_prepare_kernel(const EpPrepareParams p) {
+__global__ void ep_prepare_kernel(const __grid_constant__ EpPrepareParams p) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -63,7 +63,7 @@ __device__ __forceinline__ float load_logit(const void* base, long long i) {
 // combined by every CTA reading its peers' partial results from distributed shared memory after a cluster barrier;
 // every CTA then takes the same decision, so nothing has to be sent back.
 template <bool F32>
-__global__ void __launch_bounds__(SP_NT) sample_kernel(const SampleParams p, const int cl) {
+__global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ SampleParams p, const int cl) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ unsigned long long sp_dyn[];                 // per-warp radix histograms (fixed-point mass)

@@ -157,7 +157,7 @@ class SymmetricHeap:
         from ..ops import gemm
         M = x.numel() // x.shape[-1]
         N = w.shape[0]
-        if M > 128 or N % 8 or M * N * 2 > self.gemm_slot_bytes:
+        if M > 128 or N % 8 or self.world * M * N * 2 > self.gemm_slot_bytes:
             y = gemm.linear(x, w, bias=bias if self.rank == 0 else None)
             return self.all_reduce(y.contiguous(), residual=residual)
         rc = _lib.kernels().mstar_gemm_arm_allreduce(self._gemm_bufs, self._flags, self.world, self.rank,
