@@ -39,7 +39,13 @@ struct ARParams {
     unsigned long long wait_limit_ns;
 };
 
-// One-shot: grid-stride over 16-byte vectors; CTA b owns vectors [b*chunk, (b+1)*chunk) and flag channel b.
+// Both kernels PUSH: a rank stores its data into its peers' slots with plain 16-byte stores over NVLink (which
+// pipeline without waiting for anything), raises one flag per CTA slice, waits (bounded) for the peers' flags and
+// then reads only local memory. The first versions pulled (each rank loading the peers' slots): every loop trip paid
+// an NVLink round trip, 0.37-0.40 of the link rate on 86 MB where NCCL reached 0.57.
+//
+// One-shot: CTA b owns vectors [b*per, (b+1)*per) and flag channel b. Slot layout: region q (n elements) holds rank
+// q's input. Traffic out per rank: (W - 1) * n. Used for small messages and for two ranks.
 __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ ARParams p) {
     __shared__ int s_ok;
     __shared__ unsigned int s_epoch;
@@ -49,14 +55,18 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
     __syncthreads();
     const unsigned int epoch = s_epoch;
     const int parity = epoch & 1;
+    const int W = p.t.world, R = p.t.rank;
     const long long nvec = p.n >> 3;
     const long long per = (nvec + gridDim.x - 1) / gridDim.x;
     const long long v0 = (long long)blockIdx.x * per;
     long long v1 = v0 + per;
     if (v1 > nvec) v1 = nvec;
-    uint4* mine = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[p.t.rank]) + parity * p.slot_bytes);
     const uint4* src = reinterpret_cast<const uint4*>(p.in);
-    for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) mine[v] = src[v];
+    for (int q = 0; q < W; ++q) {
+        if (q == R) continue;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + parity * p.slot_bytes) + (long long)R * nvec;
+        for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) dst[v] = src[v];
+    }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -64,12 +74,13 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
     }
     __syncthreads();
     if (s_ok) {
+        const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[R]) + parity * p.slot_bytes);
         for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            for (int r = 0; r < p.t.world; ++r) {
-                const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes)[v];
+            for (int r = 0; r < W; ++r) {       // rank order on every rank: bit-identical results
+                const uint4 x = r == R ? src[v] : __ldcg(mine + (long long)r * nvec + v);
                 const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -102,8 +113,11 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
     }
 }
 
-// Two-shot: rank r owns vectors [r*share, (r+1)*share); it sums that slice from every rank's slot and stores the
-// result into every rank's `gather` region (second half of the slot), then signals; everyone copies out.
+// Two-shot (more than two ranks, large messages): inside CTA b's slice rank r owns the share [a_r, b_r). Phase 1
+// (reduce-scatter by push): every rank stores its part of share r into rank r's slot, region [source rank], at the
+// vector's own index. Phase 2: the owner sums its share in rank order, writes its own output and pushes the sum into
+// every peer's gather region (second half of the slot). Phase 3: everyone copies the other shares from its gather
+// region to the output. Traffic out per rank: 2 * (W - 1) / W * n.
 __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_constant__ ARParams p) {
     __shared__ int s_ok;
     __shared__ unsigned int s_epoch;
@@ -115,64 +129,70 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_con
     const int parity = epoch & 1;
     const long long nvec = p.n >> 3;
     const int W = p.t.world, R = p.t.rank;
-    const long long half_bytes = p.slot_bytes >> 1;      // [partials | gathered result]
-    // phase 1: publish my partial (CTA-sliced), signal on channel b
+    const long long half_bytes = p.slot_bytes >> 1;      // [shares received | gathered result]
     const long long per = (nvec + gridDim.x - 1) / gridDim.x;
     const long long v0 = (long long)blockIdx.x * per;
     long long v1 = v0 + per;
     if (v1 > nvec) v1 = nvec;
-    char* my_slot = reinterpret_cast<char*>(p.t.buf[R]) + parity * p.slot_bytes;
+    const long long share = (v1 > v0 ? (v1 - v0 + W - 1) / W : 0);
+    // the receive area of a slot is W regions of `cap` vectors; a vector of CTA b's share sits at b * share + offset
+    const long long cap = (long long)gridDim.x * ((per + W - 1) / W);
+    const long long share_cap = (per + W - 1) / W;
     const uint4* src = reinterpret_cast<const uint4*>(p.in);
-    for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) reinterpret_cast<uint4*>(my_slot)[v] = src[v];
+    // phase 1
+    for (int q = 0; q < W; ++q) {
+        if (q == R) continue;
+        const long long a = v0 + q * share;
+        long long b = a + share;
+        if (b > v1) b = v1;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + parity * p.slot_bytes) +
+                     (long long)R * cap + (long long)blockIdx.x * share_cap;
+        for (long long v = a + threadIdx.x; v < b; v += blockDim.x) dst[v - a] = src[v];
+    }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         if (!signal_and_wait_all(p.t, p.channel_base + blockIdx.x, epoch, p.status, p.wait_limit_ns, 2)) s_ok = 0;
     }
     __syncthreads();
-    // phase 2: reduce my share of this CTA's vectors, store to everyone's gather region
+    const long long a = v0 + R * share;
+    long long b = a + share;
+    if (b > v1) b = v1;
+    // phase 2
     if (s_ok) {
-        const long long share = (v1 - v0 + W - 1) / W;
-        const long long a = v0 + R * share;
-        long long b = a + share;
-        if (b > v1) b = v1;
-        // four vectors per thread and trip: every peer load is an NVLink round trip, and only loads that are in
-        // flight together hide it (one vector per trip measured 0.37 of the link rate on 86 MB)
-        constexpr int UN = 8;
-        for (long long v = a + threadIdx.x; v < b; v += (long long)blockDim.x * UN) {
-            float acc[UN][8];
+        const uint4* recv = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[R]) + parity * p.slot_bytes) +
+                            (long long)blockIdx.x * share_cap;
+        for (long long v = a + threadIdx.x; v < b; v += blockDim.x) {
+            float acc[8];
 #pragma unroll
-            for (int u = 0; u < UN; ++u)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
             for (int r = 0; r < W; ++r) {
-                const uint4* src_r = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[r]) + parity * p.slot_bytes);
-                uint4 x[UN];
+                const uint4 x = r == R ? src[v] : __ldcg(recv + (long long)r * cap + (v - a));
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                for (int u = 0; u < UN; ++u) {
-                    const long long vu = v + (long long)u * blockDim.x;
-                    x[u] = vu < b ? src_r[vu] : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int u = 0; u < UN; ++u) {
-                    const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = unpack_bf16x2(w[j]);
-                        acc[u][2 * j] += f.x; acc[u][2 * j + 1] += f.y;
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w[j]);
+                    acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
                 }
             }
+            const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+            for (int r = 0; r < W; ++r)
+                if (r != R)
+                    reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[r]) + parity * p.slot_bytes + half_bytes)[v] = o;
+            uint4 x = o;
+            if (p.residual != nullptr) {
+                const uint4 rsd = reinterpret_cast<const uint4*>(p.residual)[v];
+                const uint32_t a4[4] = {x.x, x.y, x.z, x.w}, b4[4] = {rsd.x, rsd.y, rsd.z, rsd.w};
+                uint32_t o4[4];
 #pragma unroll
-            for (int u = 0; u < UN; ++u) {
-                const long long vu = v + (long long)u * blockDim.x;
-                if (vu < b) {
-                    const uint4 o = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
-                                               pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
-                    for (int r = 0; r < W; ++r)
-                        reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[r]) + parity * p.slot_bytes + half_bytes)[vu] = o;
+                for (int j = 0; j < 4; ++j) {
+                    const float2 fa = unpack_bf16x2(a4[j]), fb = unpack_bf16x2(b4[j]);
+                    o4[j] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
                 }
+                x = make_uint4(o4[0], o4[1], o4[2], o4[3]);
             }
+            reinterpret_cast<uint4*>(p.out)[v] = x;
         }
     }
     __threadfence_system();
@@ -182,10 +202,12 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_con
         if (!signal_and_wait_all(p.t, p.channel_base + gridDim.x + blockIdx.x, epoch, p.status, p.wait_limit_ns, 3)) s_ok = 0;
     }
     __syncthreads();
+    // phase 3: the other ranks' shares
     if (s_ok) {
-        const uint4* g = reinterpret_cast<const uint4*>(my_slot + half_bytes);
+        const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[R]) + parity * p.slot_bytes + half_bytes);
         for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-            uint4 x = g[v];
+            if (v >= a && v < b) continue;
+            uint4 x = __ldcg(g + v);
             if (p.residual != nullptr) {
                 const uint4 rsd = reinterpret_cast<const uint4*>(p.residual)[v];
                 const uint32_t a4[4] = {x.x, x.y, x.z, x.w}, b4[4] = {rsd.x, rsd.y, rsd.z, rsd.w};

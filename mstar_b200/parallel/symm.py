@@ -96,7 +96,12 @@ class SymmetricHeap:
             out = torch.empty_like(x)
         n = x.numel()
         # messages larger than a heap slot go in slot-sized pieces (two-shot keeps partials and results in one slot)
-        piece = (self.slot_bytes // 4) // 8 * 8
+        # (one-shot: one region per rank in the slot; two-shot: received shares + margin | gathered result)
+        one_shot = mode == 1 or (mode == 0 and self.world <= 2)
+        if one_shot:
+            piece = (self.slot_bytes // (2 * self.world)) // 8 * 8
+        else:
+            piece = ((self.slot_bytes // 2 - (64 << 10)) // 2) // 8 * 8
         xf, of = x.view(-1), out.view(-1)
         rf = residual.view(-1) if residual is not None else None
         for a in range(0, n, piece):
