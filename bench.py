@@ -149,8 +149,10 @@ def main():
     # every replica gets the same synthetic load (seeded per replica)
     g = torch.Generator().manual_seed(1234 + rank // tp.size)
     plens = torch.randint(32, 129, (C,), generator=g).tolist()
-    done = torch.randint(0, args.gen_tokens, (C,), generator=g).tolist()
     total_new = args.steps * 2 + args.warmup * 2 + 8
+    # tokens already generated when the measurement starts: drawn so that the contexts stay inside the workload's range
+    # (prompt + up to gen_tokens) while the timed steps add to them
+    done = torch.randint(0, max(1, args.gen_tokens - total_new), (C,), generator=g).tolist()
     for i in range(C):
         ids = torch.randint(0, cfg.vocab_size, (plens[i] + done[i],), generator=g).tolist()
         eng.add_request(f"req{rank}_{i}", ids, total_new, samp)

@@ -65,8 +65,8 @@ def main():
         _lib.kernels().mstar_gemm_set_trace(ctypes.c_void_p(0))
         t = tr[tr[:, 0] > 0].cpu().double()
         t0 = t[:, 0].min()
-        names = ["entry", "prologue done", "first loads issued", "first tile landed", "last umma issued",
-                 "accumulator ready", "epilogue done", "exit"]
+        names = ["entry", "prologue done", "accumulator staged in shared memory", "first tile landed",
+                 "last umma issued", "accumulator ready", "epilogue (or partial tile) done", "cluster slice stored"]
         rows = {}
         for i, nme in enumerate(names):
             c = t[:, i][t[:, i] > 0] - t0

@@ -164,8 +164,20 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int m, int 
 // so that the real call after the last UMMA finds its code in the instruction cache (each CTA is the first on its SM
 // for a one-wave decode GEMM: the cold epilogue measured 7 us of a 26 us kernel).
 template <bool OUT_F32>
-__device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* stage, int rows, int m_base,
+__device__ __noinline__ void copy_out_staged(const GemmParams& pp, const float* stage, int rows, int m_base,
                                              int n_in_base, int tid, bool dry = false) {
+    // The kernel parameters are reached through a reference here, and the loop below stores to global memory: read
+    // from the reference inside the loop, every field would be re-loaded after every store (measured: 4 us for eight
+    // trips per thread). Local copies live in registers.
+    struct {
+        int M, N, ldc, ld_res, epilogue;
+        float out_scale;
+        void* C;
+        const __nv_bfloat16* bias;
+        const __nv_bfloat16* residual;
+        const float* row_scale;
+        void* const* row_dst;
+    } p = {pp.M, pp.N, pp.ldc, pp.ld_res, pp.epilogue, pp.out_scale, pp.C, pp.bias, pp.residual, pp.row_scale, pp.row_dst};
     constexpr int EPV = OUT_F32 ? 4 : 8;                 // outputs per 16-byte store
     const int ipo = p.epilogue == 1 ? 2 : 1;             // accumulator columns per output (SwiGLU pairs)
     const int row_out = BM / ipo;
@@ -289,9 +301,18 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& p, const float* s
 // the peers' flags every read is local. An earlier pull version (each rank reading the peers' slots) paid one NVLink
 // round trip per loop iteration: 57 us per fused GEMM against 18 us for the GEMM alone. Every rank adds the same
 // bf16-rounded contributions in rank order, so all ranks hold bit-identical results.
-__device__ __noinline__ void copy_out_allreduce(const GemmParams& p, float* stage, int rows, int m_base, int n_base,
+__device__ __noinline__ void copy_out_allreduce(const GemmParams& pp, float* stage, int rows, int m_base, int n_base,
                                                 int unit, int nunits, int tid, volatile int* flags) {
-    const GemmAllReduce& ar = p.ar;
+    const GemmAllReduce ar = pp.ar;          // local copies: see copy_out_staged
+    struct {
+        int M, N, ldc, ld_res;
+        float out_scale;
+        void* C;
+        const __nv_bfloat16* bias;
+        const __nv_bfloat16* residual;
+        KernelStatus* status;
+        unsigned long long wait_limit_ns;
+    } p = {pp.M, pp.N, pp.ldc, pp.ld_res, pp.out_scale, pp.C, pp.bias, pp.residual, pp.status, pp.wait_limit_ns};
     if (tid == 0) flags[2] = (int)(*ar.epoch + 1u);
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const unsigned int epoch = (unsigned int)flags[2];
@@ -511,7 +532,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                     load_Q(smem + g * STAGE_BYTES + Q_OFF + u * Q_BYTES, &full_bar[g], kb_begin + g * KSUB + u);
             }
             issued = npre;
-            MSTAR_TRACE(2);
             for (int g = npre; g < ngroups; ++g) {
                 const int s = g % STAGES;
                 const uint32_t ph = (g / STAGES) & 1;
@@ -663,6 +683,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             }
             if (p.swap) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) MSTAR_TRACE(2);
                 if (p.ar.enabled) copy_out_allreduce(p, reinterpret_cast<float*>(smem), BN, tile_q * BN, tile_p * BM, tile_lin, gridDim.x * gridDim.y, threadIdx.x - 64, flags);
                 else if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
                 else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), BN, tile_q * BN, tile_p * BM, threadIdx.x - 64);
@@ -720,11 +741,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                                    tile_lin * nsp + crank, (int)(gridDim.x * gridDim.y) * nsp, tid, flags);
             }
         }
+        if (threadIdx.x == 64) MSTAR_TRACE(7);
         __syncwarp();
         cluster_sync_all();
     }
     __syncthreads();
-    if (threadIdx.x == 0) MSTAR_TRACE(7);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -922,8 +943,11 @@ __host__ __device__ constexpr int gemm_fp8_smem_bytes(int BN, int stages) {
     return stages * (BM * F8_BK + BN * F8_BK) + 1024 /*alignment*/ + 1024 /*scales*/ + 256 /*barriers*/;
 }
 
-template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(192, 1)
+// EW: epilogue warps, 4 or 8. With 8 (token-major layout) two warps share a TMEM lane quarter and take half of the
+// accumulator columns each: at large M the per-K-block drain (tcgen05.ld + one FMA per element) by four warps took
+// longer than the block's four UMMAs.
+template <int BN, int STAGES, bool SWAP, int EW = 4>
+__global__ void __launch_bounds__(64 + EW * 32, 1)
 gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                             const __grid_constant__ GemmParams p, const __grid_constant__ Fp8Scales sc) {
     extern __shared__ uint8_t smem_raw[];
@@ -934,6 +958,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     constexpr int ACC_COLS = BN < 32 ? 32 : BN;          // columns of one accumulator buffer
     constexpr int TMEM_COLS = 2 * ACC_COLS;
     static_assert(TMEM_COLS <= 512 && BN <= 128, "two accumulators of at most 128 columns");
+    static_assert(EW == 4 || (EW == 8 && !SWAP && BN >= 64), "eight epilogue warps: token-major layout only");
+    constexpr int NCOL = BN / (EW / 4);                  // accumulator columns per epilogue thread
     float* scale_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);           // [2][128]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 1024);
     uint64_t* empty_bar = full_bar + STAGES;
@@ -954,7 +980,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EW * 32); }
         flags[0] = 0;
         mbar_fence_init();
     }
@@ -1023,25 +1049,39 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
         const int row = q4 * 32 + lane;          // accumulator row (TMEM lane) of this thread
         const int tid = threadIdx.x - 64;
         const int pidx = tile_p * BM + row;
+        const int cb = ((warp - 2) >> 2) * NCOL; // first accumulator column of this thread
         pdl_wait();
-        float acc[BN];
+        float acc[NCOL];
 #pragma unroll
-        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        for (int j = 0; j < NCOL; ++j) acc[j] = 0.f;
         const float* wsc = sc.w_scale + (size_t)((SWAP ? p_row0 : tile_q * BN) / 128) * nkb;
         bool ok = true;
+        // The scales of K block kb + 1 are fetched while block kb is drained: a scale load at the top of every trip
+        // put a global-memory round trip (long scoreboard) in front of each block's FMAs, longer than the block's UMMAs.
+        auto load_w = [&](int kb) { return kb < nkb ? __ldg(wsc + kb) : 0.f; };
+        auto load_a = [&](int kb) {
+            if (kb >= nkb) return 0.f;
+            if constexpr (SWAP) {
+                const int t = tile_q * BN + tid;
+                return (tid < BN && t < p.M) ? __ldg(sc.a_scale_t + (size_t)kb * sc.ld_as + t) : 0.f;
+            } else {
+                return pidx < p.M ? __ldg(sc.a_scale_t + (size_t)kb * sc.ld_as + pidx) : 0.f;
+            }
+        };
+        float w_next = load_w(0), a_next = load_a(0);
         for (int kb = 0; kb < nkb; ++kb) {
             const int a = kb & 1;
+            const float w_cur = w_next, a_cur = a_next;
+            w_next = load_w(kb + 1);
+            a_next = load_a(kb + 1);
             float rowfac;
             if constexpr (SWAP) {
                 // one weight scale for the tile, one activation scale per column: staged through shared memory
-                rowfac = wsc[kb];
-                if (tid < BN) {
-                    const int t = tile_q * BN + tid;
-                    scale_s[a * 128 + tid] = t < p.M ? sc.a_scale_t[(size_t)kb * sc.ld_as + t] : 0.f;
-                }
+                rowfac = w_cur;
+                if (tid < BN) scale_s[a * 128 + tid] = a_cur;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             } else {
-                rowfac = (pidx < p.M ? sc.a_scale_t[(size_t)kb * sc.ld_as + pidx] : 0.f) * wsc[kb];
+                rowfac = a_cur * w_cur;
             }
             if (!mbar_wait(&acc_full[a], (uint32_t)((kb >> 1) & 1), p.wait_limit_ns + 500000000ull)) {
                 report_status(p.status, KID_GEMM, 24, kb, a);
@@ -1050,17 +1090,39 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
                 break;
             }
             tc_fence_after();
-            constexpr int CH = BN < 32 ? BN : 32;
+            constexpr int CH = NCOL < 32 ? NCOL : 32;
+            if constexpr (NCOL >= 64) {
+                // two 32-column loads in flight per wait
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += CH) {
-                uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * ACC_COLS + c0);
-                if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
-                tmem_ld_wait();
+                for (int c0 = 0; c0 < NCOL; c0 += 64) {
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * ACC_COLS + cb + c0);
+                    tmem_ld32(taddr, r0);
+                    tmem_ld32(taddr + 32, r1);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < CH; ++i) {
-                    if constexpr (SWAP) acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
-                    else acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac, acc[c0 + i]);
+                    for (int i = 0; i < 32; ++i) {
+                        if constexpr (SWAP) {
+                            acc[c0 + i] = fmaf(__uint_as_float(r0[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
+                            acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), rowfac * scale_s[a * 128 + c0 + 32 + i], acc[c0 + 32 + i]);
+                        } else {
+                            acc[c0 + i] = fmaf(__uint_as_float(r0[i]), rowfac, acc[c0 + i]);
+                            acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), rowfac, acc[c0 + 32 + i]);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c0 = 0; c0 < NCOL; c0 += CH) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * ACC_COLS + cb + c0);
+                    if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) {
+                        if constexpr (SWAP) acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
+                        else acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac, acc[c0 + i]);
+                    }
                 }
             }
             tc_fence_before();
@@ -1078,9 +1140,9 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
                 else copy_out_staged<false>(p, stage, BN, tile_q * BN, tile_p * BM, tid);
             } else {
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (p.out_f32) store_row_chunk<true>(p, pidx, tile_q * BN + c0, &acc[c0], 32);
-                    else store_row_chunk<false>(p, pidx, tile_q * BN + c0, &acc[c0], 32);
+                for (int c0 = 0; c0 < NCOL; c0 += 32) {
+                    if (p.out_f32) store_row_chunk<true>(p, pidx, tile_q * BN + cb + c0, &acc[c0], 32);
+                    else store_row_chunk<false>(p, pidx, tile_q * BN + cb + c0, &acc[c0], 32);
                 }
             }
         }
@@ -1267,8 +1329,8 @@ static GemmAllReduce g_next_ar = {};
 static unsigned long long* g_trace = nullptr;
 
 // Phase stamps for the benchmark: a device buffer of [CTAs][8] 64-bit words filled by later mstar_gemm_bf16 launches
-// (entry, prologue done, first loads issued, first tile landed, last UMMA issued, accumulator ready, epilogue done,
-// CTA exit), or null to stop.
+// (entry, prologue done, accumulator staged, first tile landed, last UMMA issued, accumulator ready, epilogue done,
+// cluster slice stored), or null to stop.
 MSTAR_API void mstar_gemm_set_trace(void* buf) { g_trace = reinterpret_cast<unsigned long long*>(buf); }
 
 // Arms the tensor-parallel reduction for the NEXT mstar_gemm_bf16 call of this thread of control: the output is
@@ -1472,19 +1534,19 @@ static int make_tmap_2d_u8(CUtensorMap* out, const void* base, long long rows, i
     return make_tmap(out, base, 1, 2, dims, strides, box, 1);
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int EW = 4>
 static int launch_fp8(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, const Fp8Scales& sc,
                       dim3 grid, cudaStream_t stream) {
     constexpr int smem = gemm_fp8_smem_bytes(BN, STAGES);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP, EW>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm_fp8: cudaFuncSetAttribute failed", e);
         configured = true;
     }
-    cudaError_t e = launch_pdl(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP>, grid, dim3(192), smem, stream, tmP, tmQ,
-                               p, sc);
+    cudaError_t e = launch_pdl(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP, EW>, grid, dim3(64 + EW * 32), smem, stream,
+                               tmP, tmQ, p, sc);
     if (e != cudaSuccess) return set_error("gemm_fp8: launch failed", e);
     return 0;
 }
@@ -1499,7 +1561,7 @@ static int dispatch_fp8(int bn, int swap, const CUtensorMap& tmP, const CUtensor
             case 128: return launch_fp8<128, 6, true>(tmP, tmQ, p, sc, grid, stream);
         }
     } else if (bn == 128) {
-        return launch_fp8<128, 6, false>(tmP, tmQ, p, sc, grid, stream);
+        return launch_fp8<128, 6, false, 8>(tmP, tmQ, p, sc, grid, stream);
     }
     return set_error("gemm_fp8: unsupported tile", cudaSuccess);
 }
