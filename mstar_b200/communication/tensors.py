@@ -141,6 +141,10 @@ class TensorCommunicationManager:
                                  source_entity=self.entity_id,
                                  device_index=t.device.index if t.is_cuda else -1)
 
+    def is_local(self, entity: str) -> bool:
+        """True when ``entity``'s tensor store lives in this process (its descriptors resolve without a transport)."""
+        return entity in _PROCESS_STORES
+
     def prepare_for_remote(self, info: TensorPointerInfo, dst_entity: str) -> TensorPointerInfo:
         """Make a descriptor resolvable by ``dst_entity``. In-process consumers need nothing; others get a CUDA
         IPC handle (GPU tensors) or an arena block (host tensors)."""

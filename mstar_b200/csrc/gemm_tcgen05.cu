@@ -418,7 +418,10 @@ __device__ __noinline__ void copy_out_allreduce(const GemmParams& pp, float* sta
 // rows that lie a whole row pitch apart, and the next 128 bytes of those rows are only asked for a stage later: a
 // weight-streaming (decode) GEMM then opens a DRAM page per 128 bytes and measured 1.3-2.2 TB/s. With KSUB = 2 or 4
 // one stage asks for 256 or 512 contiguous bytes of every row back to back.
-template <int BN, int STAGES, int MINB, int KSUB = 1>
+// SWAP: the layout is a template parameter so that a decode launch carries no token-major epilogue code (and the
+// other way round): the once-per-CTA code of a one-wave decode GEMM stalled on instruction fetch (ncu no_instruction
+// 4.9 per issue with both layouts compiled into one kernel).
+template <int BN, int STAGES, int MINB, int KSUB = 1, bool SWAP = true>
 __global__ void __launch_bounds__(192, MINB)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                          const __grid_constant__ GemmParams p) {
@@ -498,7 +501,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         if (lane == 0) {
             // packed weights: tile (row tile t, K block kb) starts at row (t * kblocks_total + kb) * 128 of a
             // [tiles * 128, 64] matrix; the weight is the P operand in the decode layout, the Q operand otherwise
-            const bool p_packed = p.w_packed && p.swap, q_packed = p.w_packed && !p.swap;
+            const bool p_packed = p.w_packed && SWAP, q_packed = p.w_packed && !SWAP;
             auto load_P = [&](uint8_t* dst, uint64_t* bar, int kb) {
                 if (p_packed) tma_load_2d(dst, &tmP, bar, 0, ((p_row0 / BM) * p.kblocks_total + kb) * BM);
                 else tma_load_2d(dst, &tmP, bar, kb * BK, p_row0);
@@ -518,7 +521,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
             auto group_subs = [&](int g) { return (nkb - g * KSUB) < KSUB ? (nkb - g * KSUB) : KSUB; };
             // The weight operand does not depend on the previous kernel: when it is the P operand (decode), fill
             // the ring with weight tiles first, and only then wait for the predecessor before touching activations.
-            const int npre = p.swap ? (ngroups < STAGES ? ngroups : STAGES) : 0;
+            const int npre = SWAP ? (ngroups < STAGES ? ngroups : STAGES) : 0;
             for (int g = 0; g < npre; ++g) {
                 const int ns = group_subs(g);
                 mbar_expect_tx(&full_bar[g], ns * (P_BYTES + Q_BYTES));
@@ -594,7 +597,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;  // accumulator row (TMEM lane) owned by this thread
         pdl_wait();
-        if (p.swap && !p.ar.enabled) {
+        if (SWAP && !p.ar.enabled) {
             // instruction-cache warm-up (see copy_out_staged); reads an untouched corner of the staging area
             if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), 1, tile_q * BN, tile_p * BM, threadIdx.x - 64, true);
             else copy_out_staged<false>(p, reinterpret_cast<const float*>(smem), 1, tile_q * BN, tile_p * BM, threadIdx.x - 64, true);
@@ -671,7 +674,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                     for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
                 }
                 const int qidx = tile_q * BN + c0;
-                if (p.swap) {
+                if (SWAP) {
                     // the pipeline stages are idle by now (all TMA loads consumed): reuse them as staging tile
                     float* stage = reinterpret_cast<float*>(smem);
 #pragma unroll
@@ -681,7 +684,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
                     else store_row_chunk<false>(p, pidx, qidx, v, CH);
                 }
             }
-            if (p.swap) {
+            if (SWAP) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) MSTAR_TRACE(2);
                 if (p.ar.enabled) copy_out_allreduce(p, reinterpret_cast<float*>(smem), BN, tile_q * BN, tile_p * BM, tile_lin, gridDim.x * gridDim.y, threadIdx.x - 64, flags);
@@ -956,16 +959,20 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     constexpr int Q_BYTES = BN * F8_BK;
     constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
     constexpr int ACC_COLS = BN < 32 ? 32 : BN;          // columns of one accumulator buffer
-    constexpr int TMEM_COLS = 2 * ACC_COLS;
-    static_assert(TMEM_COLS <= 512 && BN <= 128, "two accumulators of at most 128 columns");
+    // Four accumulator buffers (all 512 TMEM columns at BN = 128): the hand-over of one buffer (commit -> mbarrier ->
+    // tcgen05.ld -> FMAs -> arrive -> UMMA warp wakes) takes several times the block's four UMMAs, and with two
+    // buffers the tensor pipe was busy 25 % of the time.
+    constexpr int NACC = 4;
+    constexpr int TMEM_COLS = NACC * ACC_COLS;
+    static_assert(TMEM_COLS <= 512 && BN <= 128, "four accumulators of at most 128 columns");
     static_assert(EW == 4 || (EW == 8 && !SWAP && BN >= 64), "eight epilogue warps: token-major layout only");
     constexpr int NCOL = BN / (EW / 4);                  // accumulator columns per epilogue thread
     float* scale_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);           // [2][128]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 1024);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_full = empty_bar + STAGES;      // [2]
-    uint64_t* acc_empty = acc_full + 2;           // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* acc_full = empty_bar + STAGES;      // [NACC]
+    uint64_t* acc_empty = acc_full + NACC;        // [NACC]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NACC);
     volatile int* flags = reinterpret_cast<volatile int*>(tmem_slot + 1);  // [0] abort
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -980,7 +987,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EW * 32); }
+        for (int a = 0; a < NACC; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EW * 32); }
         flags[0] = 0;
         mbar_fence_init();
     }
@@ -1020,14 +1027,14 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             constexpr uint32_t idesc = umma_idesc(BM, BN, 0, 0);      // e4m3 x e4m3 -> f32
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
-                const int a = kb & 1;
+                const int a = kb % NACC;
                 if (!mbar_wait(&full_bar[s], (uint32_t)((kb / STAGES) & 1), p.wait_limit_ns)) {
                     report_status(p.status, KID_GEMM, 22, kb, s);
                     flags[0] = 1;
                     break;
                 }
-                // the epilogue must have drained this accumulator buffer (K block kb - 2)
-                if (kb >= 2 && !mbar_wait(&acc_empty[a], (uint32_t)(((kb >> 1) - 1) & 1), p.wait_limit_ns)) {
+                // the epilogue must have drained this accumulator buffer (K block kb - NACC)
+                if (kb >= NACC && !mbar_wait(&acc_empty[a], (uint32_t)(((kb / NACC) - 1) & 1), p.wait_limit_ns)) {
                     report_status(p.status, KID_GEMM, 23, kb, a);
                     flags[0] = 1;
                     break;
@@ -1070,7 +1077,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
         };
         float w_next = load_w(0), a_next = load_a(0);
         for (int kb = 0; kb < nkb; ++kb) {
-            const int a = kb & 1;
+            const int a = kb % NACC;          // accumulator buffer
+            const int sb = kb & 1;            // scale staging buffer
             const float w_cur = w_next, a_cur = a_next;
             w_next = load_w(kb + 1);
             a_next = load_a(kb + 1);
@@ -1078,12 +1086,12 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             if constexpr (SWAP) {
                 // one weight scale for the tile, one activation scale per column: staged through shared memory
                 rowfac = w_cur;
-                if (tid < BN) scale_s[a * 128 + tid] = a_cur;
+                if (tid < BN) scale_s[sb * 128 + tid] = a_cur;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             } else {
                 rowfac = a_cur * w_cur;
             }
-            if (!mbar_wait(&acc_full[a], (uint32_t)((kb >> 1) & 1), p.wait_limit_ns + 500000000ull)) {
+            if (!mbar_wait(&acc_full[a], (uint32_t)((kb / NACC) & 1), p.wait_limit_ns + 500000000ull)) {
                 report_status(p.status, KID_GEMM, 24, kb, a);
                 flags[0] = 1;
                 ok = false;
@@ -1103,8 +1111,8 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if constexpr (SWAP) {
-                            acc[c0 + i] = fmaf(__uint_as_float(r0[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
-                            acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), rowfac * scale_s[a * 128 + c0 + 32 + i], acc[c0 + 32 + i]);
+                            acc[c0 + i] = fmaf(__uint_as_float(r0[i]), rowfac * scale_s[sb * 128 + c0 + i], acc[c0 + i]);
+                            acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), rowfac * scale_s[sb * 128 + c0 + 32 + i], acc[c0 + 32 + i]);
                         } else {
                             acc[c0 + i] = fmaf(__uint_as_float(r0[i]), rowfac, acc[c0 + i]);
                             acc[c0 + 32 + i] = fmaf(__uint_as_float(r1[i]), rowfac, acc[c0 + 32 + i]);
@@ -1120,7 +1128,7 @@ gemm_fp8_blockscaled_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
-                        if constexpr (SWAP) acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac * scale_s[a * 128 + c0 + i], acc[c0 + i]);
+                        if constexpr (SWAP) acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac * scale_s[sb * 128 + c0 + i], acc[c0 + i]);
                         else acc[c0 + i] = fmaf(__uint_as_float(r[i]), rowfac, acc[c0 + i]);
                     }
                 }
@@ -1173,12 +1181,14 @@ template <int BN, int STAGES, int MINB, int KSUB = 1>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
                        cudaStream_t stream) {
     constexpr int smem = gemm_smem_bytes(BN, STAGES, KSUB);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    using KernelFn = void (*)(CUtensorMap, CUtensorMap, GemmParams);
+    const KernelFn kern = p.swap ? static_cast<KernelFn>(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB, true>)
+                                 : static_cast<KernelFn>(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB, false>);
+    static bool configured[2] = {false, false};
+    if (!configured[p.swap ? 1 : 0]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
-        configured = true;
+        configured[p.swap ? 1 : 0] = true;
     }
     if (p.cluster_reduce) {
         // Clusters are placed inside one GPC each, so a split factor that does not divide the GPCs' SM counts well
@@ -1199,7 +1209,7 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
                 at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = sp;
                 cfg.attrs = at; cfg.numAttrs = 1;
                 int n = 0;
-                if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, &cfg) != cudaSuccess) {
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
                     (void)cudaGetLastError();
                     n = -1;
                 }
@@ -1217,17 +1227,17 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
         }
         cudaError_t e = cudaErrorInvalidConfiguration;
         if (use >= 2 && gc.z >= 2)
-            e = launch_pdl_cluster_z(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, gc, dim3(192), smem, stream, gc.z,
+            e = launch_pdl_cluster_z(kern, gc, dim3(192), smem, stream, gc.z,
                                      tmP, tmQ, pc);
         else if (use >= 2) {       // the K range collapsed to one split
             pc.cluster_reduce = 0;
-            e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, gc, dim3(192), smem, stream, tmP, tmQ, pc);
+            e = launch_pdl(kern, gc, dim3(192), smem, stream, tmP, tmQ, pc);
         }
         if (e == cudaSuccess) return 0;
         if (use == 0 && p.workspace != nullptr) {       // no cluster size fits this grid: scratch-buffer reduction
             GemmParams q = p;
             q.cluster_reduce = 0;
-            e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, q);
+            e = launch_pdl(kern, grid, dim3(192), smem, stream, tmP, tmQ, q);
             if (e != cudaSuccess) return set_error("gemm: launch failed", e);
             return 0;
         }
@@ -1237,11 +1247,11 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
         if (p.workspace == nullptr) return set_error("gemm: cluster launch failed and no split-K scratch was given", e);
         GemmParams q = p;
         q.cluster_reduce = 0;
-        e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, q);
+        e = launch_pdl(kern, grid, dim3(192), smem, stream, tmP, tmQ, q);
         if (e != cudaSuccess) return set_error("gemm: launch failed", e);
         return 0;
     }
-    cudaError_t e = launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB>, grid, dim3(192), smem, stream, tmP, tmQ, p);
+    cudaError_t e = launch_pdl(kern, grid, dim3(192), smem, stream, tmP, tmQ, p);
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
     return 0;
 }

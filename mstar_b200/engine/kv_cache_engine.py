@@ -89,6 +89,48 @@ class KVCacheEngine(BaseEngine):
                 self.sampler.seen[b] = src.sampler.seen[a].to(self.device)
         return sum(len(d["pages"]) for d in desc.values())
 
+    def export_kv(self, request_id: str) -> tuple[dict, dict[str, torch.Tensor]]:
+        """The hand-off of a request to a pool in ANOTHER process: per label the pages gathered into one tensor
+        ``[layers, pages, 2, kv_heads, page, head_dim]`` (sent like any tensor edge: a CUDA IPC handle between GPU
+        processes, the shared-memory arena between CPU ones), plus page counts, lengths and the sampler's state."""
+        desc = self.cache.alloc.export_descriptor(request_id)
+        meta: dict = {"labels": {}, "sampler": None}
+        tensors: dict[str, torch.Tensor] = {}
+        for label, d in desc.items():
+            meta["labels"][label] = dict(n_pages=len(d["pages"]), seq_len=d["seq_len"], pos_offset=d["pos_offset"])
+            if d["pages"]:
+                idx = torch.tensor(d["pages"], dtype=torch.long, device=self.device)
+                tensors[f"kv:{label}"] = torch.stack([layer.index_select(0, idx) for layer in self.cache.alloc.kv_layers])
+        if request_id in self.sampler._slot_of:
+            a = self.sampler.slot(request_id)
+            meta["sampler"] = dict(offset=int(self.sampler.offset[a].item()))
+            if self.sampler.seen is not None:
+                tensors["sampler:seen"] = self.sampler.seen[a].clone()
+        return meta, tensors
+
+    def import_kv(self, request_id: str, fwd_info, meta: dict, tensors: dict[str, torch.Tensor]) -> int:
+        """Counterpart of ``export_kv`` on the receiving pool. Returns the number of pages stored."""
+        self.add_request(request_id, fwd_info)
+        alloc = self.cache.alloc
+        moved = 0
+        for label, d in meta["labels"].items():
+            alloc.reset_label(request_id, label)
+            st = alloc.get_state(request_id, label)
+            if d["n_pages"]:
+                st.pages = alloc.allocator.allocate(d["n_pages"])
+                di = torch.tensor(st.pages, dtype=torch.long, device=self.device)
+                t = tensors[f"kv:{label}"].to(self.device)
+                for li, layer in enumerate(alloc.kv_layers):
+                    layer[di] = t[li].to(layer.dtype)
+                moved += d["n_pages"]
+            st.seq_len, st.pos_offset = d["seq_len"], d["pos_offset"]
+        if meta.get("sampler") is not None:
+            b = self.sampler.slot(request_id)
+            self.sampler.offset[b] = meta["sampler"]["offset"]
+            if self.sampler.seen is not None and "sampler:seen" in tensors:
+                self.sampler.seen[b] = tensors["sampler:seen"].to(self.device)
+        return moved
+
     # ---- offload surface ----
     def can_offload(self) -> bool:
         return self.cache.alloc.cpu_pool is not None

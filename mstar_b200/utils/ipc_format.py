@@ -23,6 +23,8 @@ class WorkerMessageType(str, Enum):
     STOP_LOOPS = "stop_loops"
     SHUTDOWN = "shutdown"
     HEARTBEAT = "heartbeat"
+    KV_EXPORT = "kv_export"          # decode-side worker -> prefill-side worker: send me this request's pages
+    KV_IMPORT = "kv_import"          # prefill-side worker -> decode-side worker: descriptors of the packed pages
 
 
 class ConductorMessageType(str, Enum):
@@ -103,6 +105,22 @@ class TensorReceived:
     request_id: str
     successful_tensors: dict[str, int] = field(default_factory=dict)
     failed_tensor_ids: list[str] = field(default_factory=list)
+
+
+@dataclass
+class KVExport:
+    request_id: str
+    node_name: str
+    reply_to: str
+
+
+@dataclass
+class KVImport:
+    request_id: str
+    node_name: str
+    source_worker: str
+    meta: dict = field(default_factory=dict)
+    tensor_info: dict = field(default_factory=dict)      # name -> TensorPointerInfo
 
 
 @dataclass

@@ -52,6 +52,7 @@ class PerRequestInfo:
     stream_buffers: dict[str, StreamBuffer] = field(default_factory=dict)
     in_flight: int = 0
     remove_pending: bool = False
+    kv_wait: set = field(default_factory=set)      # KV nodes whose pages are still on their way from another process
     t_start: float = field(default_factory=time.perf_counter)
     timings: dict = field(default_factory=dict)
 
@@ -95,6 +96,7 @@ class Worker:
         # host time by phase of the main loop (seconds): where a step's latency goes when the GPU is not the limit
         self.phase_s = dict(wait=0.0, messages=0.0, streams=0.0, finish=0.0, build=0.0, execute=0.0)
         self.batches_by_node: dict[str, list] = {}
+        self._kv_early: dict[tuple[str, str], ipc.KVImport] = {}     # KV_IMPORT that overtook its NEW_REQUEST
 
     # ------------------------------------------------------------------ messages
     def _process_messages(self, msgs: list[Message]) -> None:
@@ -117,6 +119,10 @@ class Worker:
                 elif t == WM.TENSOR_RECEIVED:
                     for u, n in m.body.successful_tensors.items():
                         self.tensors.dereference(m.body.request_id, u, n)
+                elif t == WM.KV_EXPORT:
+                    self._on_kv_export(m.body)
+                elif t == WM.KV_IMPORT:
+                    self._on_kv_import(m.body)
                 elif t == WM.SHUTDOWN:
                     self.running = False
             except Exception as e:  # noqa: BLE001
@@ -145,13 +151,17 @@ class Worker:
         if sec is None:
             return
         imports = (info.step_metadata or {}).pop("_kv_import", {}).get(self.worker_id, {})
+        remote_kv: set[str] = set()
         for node, src_worker in imports.items():
             if node in self.node_names:
                 from .engine_manager import lookup_kv_engine
                 src = lookup_kv_engine(src_worker, node)
                 if src is None:
-                    raise RuntimeError(f"KV hand-off of {node} from {src_worker}: the source pool is not in this "
-                                       f"process (prefill / decode split needs both workers in one process)")
+                    # the pool that ran the prefill lives in another process: ask its worker for the pages and keep
+                    # the node unscheduled until they are in this pool
+                    remote_kv.add(node)
+                    self.comm.send(src_worker, Message(WM.KV_EXPORT, ipc.KVExport(b.request_id, node, self.worker_id)))
+                    continue
                 self.engines.engine_for(node).import_kv_from(src, b.request_id, info)
         key = (b.request_id, info.partition_name)
         old = self.requests.get(key)
@@ -165,11 +175,16 @@ class Worker:
         if old is not None:
             pri.stream_buffers = old.stream_buffers
             pri.persist = old.persist
+        pri.kv_wait = remote_kv
         self.requests[key] = pri
         self._setup_streams(pri)
         for e in b.initial_inputs:
             self._ingest(pri, e)
         self._refresh_ready(pri)
+        for node in list(remote_kv):
+            early = self._kv_early.pop((b.request_id, node), None)
+            if early is not None:
+                self._on_kv_import(early)
 
     def _setup_streams(self, pri: PerRequestInfo) -> None:
         if self.topology is None:
@@ -244,7 +259,36 @@ class Worker:
 
     def _refresh_ready(self, pri: PerRequestInfo) -> None:
         for n in pri.walk_state.ready_nodes(allow_streaming=False):
+            if n in pri.kv_wait:
+                continue
             self.scheduler.mark_ready(n, pri.fwd_info.graph_walk, _rk(pri))
+
+    # ------------------------------------------------------------------ KV hand-off between processes
+    def _on_kv_export(self, b: ipc.KVExport) -> None:
+        """Prefill side: pack the request's pages and hand the descriptors to the worker that asked."""
+        eng = self.engines.engine_for(b.node_name)
+        meta, tensors = eng.export_kv(b.request_id)
+        infos = {}
+        for name, t in tensors.items():
+            ti = self.tensors.store_and_return_tensor_info(b.request_id, t)
+            infos[name] = self.tensors.prepare_for_remote(ti, b.reply_to)
+        self.comm.send(b.reply_to, Message(WM.KV_IMPORT, ipc.KVImport(b.request_id, b.node_name, self.worker_id, meta, infos)))
+
+    def _on_kv_import(self, b: ipc.KVImport) -> None:
+        """Decode side: store the pages, acknowledge the tensors, release the node."""
+        pris = [p for (rid, _), p in self.requests.items() if rid == b.request_id and b.node_name in p.kv_wait]
+        if not pris:
+            self._kv_early[(b.request_id, b.node_name)] = b      # the NEW_REQUEST is still on its way
+            return
+        pri = pris[0]
+        tensors = {name: self.tensors.read(ti, self.tensors.device) for name, ti in b.tensor_info.items()}
+        self.engines.engine_for(b.node_name).import_kv(b.request_id, pri.fwd_info, b.meta, tensors)
+        if b.tensor_info:
+            self.comm.send(b.source_worker, Message(WM.TENSOR_RECEIVED, ipc.TensorReceived(
+                b.request_id, {ti.uuid: 1 for ti in b.tensor_info.values()})))
+        for p in pris:
+            p.kv_wait.discard(b.node_name)
+            self._refresh_ready(p)
 
     def _on_remove_request(self, b: ipc.RemoveRequest) -> None:
         for key in [k for k in self.requests if k[0] == b.request_id]:
@@ -386,6 +430,12 @@ class Worker:
         by_worker: dict[str, list[GraphEdge]] = {}
         for e in edges:
             if e.persist:
+                # a persisted tensor can be handed by the conductor to ANY worker in a later walk (prefill / decode
+                # split): when some worker lives in another process, publish it now (arena block or CUDA IPC handle),
+                # since only the owner can do that
+                peers = {w for ws_ in self.node_to_workers.values() for w in ws_}
+                if any(not self.tensors.is_local(w) for w in peers):
+                    e.tensor_info = [self.tensors.prepare_for_remote(ti, "*") for ti in e.tensor_info]
                 pri.persist.setdefault(e.name, []).extend(e.tensor_info)
             if e.next_node == EMPTY_DESTINATION:
                 continue

@@ -36,3 +36,27 @@ def test_processes_over_shm_mesh_and_worker_death(monkeypatch):
         assert b"stopped responding" in res["error"][0].data
     finally:
         s.shutdown()
+
+
+def test_prefill_decode_split_across_processes_moves_the_kv_pages(monkeypatch):
+    """Prefill worker and decode worker as separate OS processes with separate page pools: the decode side asks the
+    prefill side for the request's pages (packed into one tensor per label, carried by the shared-memory arena
+    between CPU processes; a CUDA IPC handle between GPU processes) and produces the colocated run's tokens."""
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    base = {"model": "tiny", "model_kwargs": {"dtype": "float32", "max_num_pages": 128}, "use_cuda_graphs": False}
+    pd = dict(base, node_groups=[{"node_names": ["LLM"], "ranks": [0], "graph_walks": ["prefill"]},
+                                 {"node_names": ["LLM"], "ranks": [1], "graph_walks": ["decode"]}])
+    co = dict(base, node_groups=[{"node_names": ["LLM"], "ranks": [0]}])
+    outs = []
+    for cfg in (co, pd):
+        s = APIServer(cfg, in_process=False, heartbeat_s=0.5, heartbeat_timeout_s=20).start(180)
+        try:
+            rids = [s.submit_request(f"{i} 2 3 4 5 6 7 8 9", model_kwargs=dict(max_tokens=10, temperature=0.7, top_p=0.9,
+                                                                              repetition_penalty=1.2, seed=5 + i))
+                    for i in range(3)]
+            res = [s.collect_results(r, 120) for r in rids]
+            assert all("error" not in r for r in res), res
+            outs.append([_tokens(r) for r in res])
+        finally:
+            s.shutdown()
+    assert all(len(t) == 10 for t in outs[0]) and outs[0] == outs[1]
