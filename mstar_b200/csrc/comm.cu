@@ -65,7 +65,14 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
     for (int q = 0; q < W; ++q) {
         if (q == R) continue;
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + parity * p.slot_bytes) + (long long)R * nvec;
-        for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) dst[v] = src[v];
+        // four local loads in flight per thread before the four peer stores (one load per trip left the copy bound by
+        // the local load latency: 0.48 of the link rate on 86 MB)
+        long long v = v0 + threadIdx.x;
+        for (; v + 3LL * blockDim.x < v1; v += 4LL * blockDim.x) {
+            const uint4 a0 = src[v], a1 = src[v + blockDim.x], a2 = src[v + 2LL * blockDim.x], a3 = src[v + 3LL * blockDim.x];
+            dst[v] = a0; dst[v + blockDim.x] = a1; dst[v + 2LL * blockDim.x] = a2; dst[v + 3LL * blockDim.x] = a3;
+        }
+        for (; v < v1; v += blockDim.x) dst[v] = src[v];
     }
     __threadfence_system();
     __syncthreads();
@@ -75,6 +82,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
     __syncthreads();
     if (s_ok) {
         const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[R]) + parity * p.slot_bytes);
+#pragma unroll 4
         for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
             float acc[8];
 #pragma unroll
