@@ -79,9 +79,35 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     float* red = reinterpret_cast<float*>(const_cast<int*>(sh) + 4);     // [2][4 warps][16] max exchange, then sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int req = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int split = blockIdx.z;
     pdl_launch_dependents();
     pdl_wait();     // the plan arrays, q and the KV pages all come from earlier kernels of the step
+    // Longest context first: CTAs are handed out in linear order, and a long request that starts late sets the
+    // kernel's length (contexts of one batch differ by 10x). CTA number lin works on the (lin / Hkv)-th longest
+    // request; every CTA finds it by ranking the batch's kv_lens itself (B values), so the host plan is unchanged.
+    __shared__ int sh_req;
+    __shared__ int sh_len[256];
+    {
+        const int lin = blockIdx.y * gridDim.x + blockIdx.x;
+        const int target = lin / p.Hkv;
+        if (p.B <= 256) {
+            for (int t = threadIdx.x; t < p.B; t += blockDim.x) sh_len[t] = p.kv_lens[t];
+            __syncthreads();
+            for (int t = threadIdx.x; t < p.B; t += blockDim.x) {
+                const int mine = sh_len[t];
+                int rank = 0;
+                for (int o = 0; o < p.B; ++o) {
+                    const int other = sh_len[o];
+                    rank += (other > mine || (other == mine && o < t)) ? 1 : 0;
+                }
+                if (rank == target) sh_req = t;
+            }
+        } else if (threadIdx.x == 0) {
+            sh_req = target;          // larger batches keep the natural order
+        }
+        __syncthreads();
+    }
+    const int req = sh_req, kvh = (int)((blockIdx.y * gridDim.x + blockIdx.x) % p.Hkv);
     const int q_begin = p.q_indptr[req];
     const int q_len = p.q_indptr[req + 1] - q_begin;
     int ncols = q_len * p.G;
