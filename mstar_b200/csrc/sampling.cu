@@ -48,7 +48,7 @@ struct SampleParams {
     float* u_override;           // [B] uniform draws supplied by the caller (tests), or null
 };
 
-constexpr int SP_NT = 512;        // threads per CTA
+constexpr int SP_NT = 256;        // threads per CTA: 64 rows x 8 CTAs fit in ONE wave at four CTAs per SM (512 threads ran two)
 constexpr int SP_NW = SP_NT / 32;
 constexpr int SP_CL = 8;          // CTAs per row (one thread-block cluster) for large vocabularies
 
