@@ -46,6 +46,9 @@ struct SampleParams {
     long long* out;              // [B]
     float* out_prob;             // [B] probability of the sampled token (optional)
     float* u_override;           // [B] uniform draws supplied by the caller (tests), or null
+    float* escratch;             // [B, V] fp32 scratch or null: exp(logit - max) of every element, written by the first
+                                 // radix level and read by every later pass (the penalty, temperature and exponential
+                                 // are then evaluated twice per element instead of six times)
 };
 
 constexpr int SP_NT = 256;        // threads per CTA: 64 rows x 8 CTAs fit in ONE wave at four CTAs per SM (512 threads ran two)
@@ -63,7 +66,7 @@ __device__ __forceinline__ float load_logit(const void* base, long long i) {
 // combined by every CTA reading its peers' partial results from distributed shared memory after a cluster barrier;
 // every CTA then takes the same decision, so nothing has to be sent back.
 template <bool F32>
-__global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ SampleParams p, const int cl) {
+__global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant__ SampleParams p, const int cl) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ unsigned long long sp_dyn[];                 // per-warp radix histograms (fixed-point mass)
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ S
         if (seen && pen != 1.0f && seen[i]) x = x > 0.f ? x / pen : x * pen;
         return x * inv_t;
     };
+    float* es = p.escratch ? p.escratch + (size_t)row * p.V : nullptr;
     auto csync = [&]() { if (cl > 1) cluster.sync(); else __syncthreads(); };
     auto peer_f = [&](float* ptr, int r) -> float { return cl > 1 ? *cluster.map_shared_rank(ptr, r) : *ptr; };
     auto peer_i = [&](int* ptr, int r) -> int { return cl > 1 ? *cluster.map_shared_rank(ptr, r) : *ptr; };
@@ -170,23 +174,46 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ S
             const int shift = 16 - 8 * level;
             for (int i = lane; i < 256; i += 32) { wmass[i] = 0ull; wcnt[i] = 0u; }
             __syncwarp();
-            for (int it = 0; it < iters; ++it) {
-                const int i = v0 + tid + it * SP_NT;
-                uint32_t bin = 0xffffffffu;
-                unsigned int fx = 0;
-                if (i < v1) {
-                    const float e = __expf(logit_at(i) - mx);
-                    const uint32_t key = __float_as_uint(e) >> 8;
-                    const bool in_range = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
-                    if (in_range) { bin = (key >> shift) & 0xffu; fx = (unsigned int)(e * 16777216.0f); }
+            // Eight elements are loaded before the first warp-wide match: the match / syncwarp pair keeps the compiler
+            // from moving the next trip's loads above it, so one element per trip paid a memory round trip each
+            // (a row took 270 us however few rows there were).
+            constexpr int PF = 8;
+            for (int it0 = 0; it0 < iters; it0 += PF) {
+                float ev[PF];
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const int i = v0 + tid + (it0 + u) * SP_NT;
+                    if (it0 + u < iters && i < v1) {
+                        if (es != nullptr && level > 0) {
+                            ev[u] = es[i];
+                        } else {
+                            ev[u] = __expf(logit_at(i) - mx);
+                            if (es != nullptr) es[i] = ev[u];
+                        }
+                    } else {
+                        ev[u] = -1.f;
+                    }
                 }
-                const unsigned int peers = __match_any_sync(0xffffffffu, bin);
-                const unsigned int sum = __reduce_add_sync(peers, fx);
-                if (bin != 0xffffffffu && lane == __ffs(peers) - 1) {
-                    wmass[bin] += sum;
-                    wcnt[bin] += __popc(peers);
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    uint32_t bin = 0xffffffffu;
+                    unsigned int fx = 0;
+                    if (ev[u] >= 0.f) {
+                        const uint32_t key = __float_as_uint(ev[u]) >> 8;
+                        const bool in_range = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
+                        if (in_range) { bin = (key >> shift) & 0xffu; fx = (unsigned int)(ev[u] * 16777216.0f); }
+                    }
+                    // below the first level almost no element lies in the undecided range: skip the warp-wide match
+                    if (__any_sync(0xffffffffu, bin != 0xffffffffu)) {
+                        const unsigned int peers = __match_any_sync(0xffffffffu, bin);
+                        const unsigned int sum = __reduce_add_sync(peers, fx);
+                        if (bin != 0xffffffffu && lane == __ffs(peers) - 1) {
+                            wmass[bin] += sum;
+                            wcnt[bin] += __popc(peers);
+                        }
+                        __syncwarp();
+                    }
                 }
-                __syncwarp();
             }
             __syncthreads();
             if (tid < 256) {          // this CTA's histogram: thread t owns bin t
@@ -246,8 +273,9 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ S
     const int chunk = (v1 - v0 + SP_NT - 1) / SP_NT;
     const int i0 = min(v1, v0 + tid * chunk), i1 = min(v1, i0 + chunk);
     float local = 0.f;
+    auto e_at = [&](int i) -> float { return es != nullptr ? es[i] : __expf(logit_at(i) - mx); };
     for (int i = i0; i < i1; ++i) {
-        const float e = __expf(logit_at(i) - mx);
+        const float e = e_at(i);
         if ((__float_as_uint(e) >> 8) >= thr_key) local += e;
     }
     float incl = local;
@@ -283,7 +311,7 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ S
         float acc = excl;
         int pick = -1, last = -1;
         for (int i = i0; i < i1; ++i) {
-            const float e = __expf(logit_at(i) - mx);
+            const float e = e_at(i);
             if ((__float_as_uint(e) >> 8) >= thr_key) {
                 last = i;
                 acc += e;
@@ -298,7 +326,7 @@ __global__ void __launch_bounds__(SP_NT) sample_kernel(const __grid_constant__ S
         int last = -1;
         if (local > 0.f)
             for (int i = i1 - 1; i >= i0; --i) {
-                const float e = __expf(logit_at(i) - mx);
+                const float e = e_at(i);
                 if ((__float_as_uint(e) >> 8) >= thr_key) { last = i; break; }
             }
         last = warp_max_i(last);
@@ -330,10 +358,11 @@ using namespace mstar;
 MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, int V, const float* temperature,
                            const int* top_k, const float* top_p, const float* rep_penalty,
                            const unsigned long long* seed, const unsigned long long* offset, unsigned char* seen,
-                           const int* row_slot, long long* out, float* out_prob, float* u_override, void* stream_) {
+                           const int* row_slot, long long* out, float* out_prob, float* u_override, float* escratch,
+                           void* stream_) {
     if (B <= 0) return 0;
     SampleParams p{logits, ld, is_f32, B, V, temperature, top_k, top_p, rep_penalty, seed, offset, seen, row_slot,
-                   out, out_prob, u_override};
+                   out, out_prob, u_override, escratch};
     cudaStream_t s = (cudaStream_t)stream_;
     constexpr int smem = SP_NW * 256 * 12;
     static bool configured = false;

@@ -124,8 +124,18 @@ class SamplerState:
         self.seed = torch.zeros(num_slots, dtype=torch.int64, device=d)
         self.offset = torch.zeros(num_slots, dtype=torch.int64, device=d)
         self.seen = torch.zeros((num_slots, vocab_size), dtype=torch.uint8, device=d) if track_seen else None
+        # scratch of the kernel: exp(logit - max) per element, written once and read by the later passes
+        self._es = (torch.empty((num_slots, vocab_size), dtype=torch.float32, device=d)
+                    if torch.device(d).type == "cuda" and vocab_size >= 16384 else None)
         self._free = list(range(num_slots - 1, -1, -1))
         self._slot_of: dict[str, int] = {}
+
+    def _escratch(self, rows: int, vocab: int, device):
+        if self._es is None or vocab != self._es.shape[1]:
+            return None
+        if rows > self._es.shape[0]:
+            self._es = torch.empty((rows, vocab), dtype=torch.float32, device=device)
+        return self._es
 
     def assign(self, request_id: str, cfg: SamplingConfig, seed: int | None = None,
                prompt_ids: torch.Tensor | None = None, slot: int | None = None) -> int:
@@ -190,7 +200,7 @@ class SamplerState:
                 ctypes.c_void_p(self.seed.data_ptr()), ctypes.c_void_p(self.offset.data_ptr()),
                 ctypes.c_void_p(_lib.ptr(self.seen)), ctypes.c_void_p(row_slot.data_ptr()),
                 ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(0), ctypes.c_void_p(_lib.ptr(u)),
-                ctypes.c_void_p(_lib.stream_ptr()))
+                ctypes.c_void_p(_lib.ptr(self._escratch(B, V, logits.device))), ctypes.c_void_p(_lib.stream_ptr()))
             _lib.check(rc, "mstar_sample")
         if advance:
             self.offset.index_add_(0, row_slot.long(), torch.ones(B, dtype=torch.int64, device=self.offset.device))
