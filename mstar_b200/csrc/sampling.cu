@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
     const unsigned char* seen = p.seen ? p.seen + (size_t)slot * p.V : nullptr;
     const bool greedy = temp <= 0.f;
     const float inv_t = greedy ? 1.f : 1.f / temp;
-    const int slice = (p.V + cl - 1) / cl;
+    const int slice = ((p.V + cl - 1) / cl + 3) & ~3;      // multiples of four: 16-byte reads of the scratch below
     const int v0 = crank * slice, v1 = min(p.V, v0 + slice);      // this CTA's slice of the vocabulary
 
     auto logit_at = [&](int i) -> float {
@@ -270,13 +270,25 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
         u = ((r[0] >> 8) + 0.5f) * (1.0f / 16777216.0f);
     }
     // mass of the kept set, summed in walk (vocabulary) order: thread t owns a contiguous piece of the CTA's slice
-    const int chunk = (v1 - v0 + SP_NT - 1) / SP_NT;
+    const int chunk = ((v1 - v0 + SP_NT - 1) / SP_NT + 3) & ~3;
     const int i0 = min(v1, v0 + tid * chunk), i1 = min(v1, i0 + chunk);
     float local = 0.f;
     auto e_at = [&](int i) -> float { return es != nullptr ? es[i] : __expf(logit_at(i) - mx); };
-    for (int i = i0; i < i1; ++i) {
-        const float e = e_at(i);
-        if ((__float_as_uint(e) >> 8) >= thr_key) local += e;
+    {
+        int i = i0;
+        if (es != nullptr && (p.V & 3) == 0) {      // rows, slices and chunks all start on 16-byte boundaries
+            for (; i + 4 <= i1; i += 4) {
+                const float4 e4 = *reinterpret_cast<const float4*>(es + i);
+                const float ee[4] = {e4.x, e4.y, e4.z, e4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if ((__float_as_uint(ee[j]) >> 8) >= thr_key) local += ee[j];
+            }
+        }
+        for (; i < i1; ++i) {
+            const float e = e_at(i);
+            if ((__float_as_uint(e) >> 8) >= thr_key) local += e;
+        }
     }
     float incl = local;
 #pragma unroll
