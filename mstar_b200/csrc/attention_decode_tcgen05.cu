@@ -86,19 +86,23 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     // kernel's length (contexts of one batch differ by 10x). CTA number lin works on the (lin / Hkv)-th longest
     // request; every CTA finds it by ranking the batch's kv_lens itself (B values), so the host plan is unchanged.
     __shared__ int sh_req;
-    __shared__ int sh_len[256];
+    __shared__ __align__(16) int sh_len[256];
     {
         const int lin = blockIdx.y * gridDim.x + blockIdx.x;
         const int target = lin / p.Hkv;
         if (p.B <= 256) {
-            for (int t = threadIdx.x; t < p.B; t += blockDim.x) sh_len[t] = p.kv_lens[t];
+            const int Bp = (p.B + 3) & ~3;
+            for (int t = threadIdx.x; t < Bp; t += blockDim.x) sh_len[t] = t < p.B ? p.kv_lens[t] : -1;
             __syncthreads();
             for (int t = threadIdx.x; t < p.B; t += blockDim.x) {
                 const int mine = sh_len[t];
                 int rank = 0;
-                for (int o = 0; o < p.B; ++o) {
-                    const int other = sh_len[o];
-                    rank += (other > mine || (other == mine && o < t)) ? 1 : 0;
+                for (int o = 0; o < Bp; o += 4) {          // 16-byte broadcast reads; padding entries (-1) never outrank
+                    const int4 v = *reinterpret_cast<const int4*>(&sh_len[o]);
+                    rank += (v.x > mine || (v.x == mine && o < t)) ? 1 : 0;
+                    rank += (v.y > mine || (v.y == mine && o + 1 < t)) ? 1 : 0;
+                    rank += (v.z > mine || (v.z == mine && o + 2 < t)) ? 1 : 0;
+                    rank += (v.w > mine || (v.w == mine && o + 3 < t)) ? 1 : 0;
                 }
                 if (rank == target) sh_req = t;
             }
@@ -138,6 +142,43 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
         sh[0] = 0; sh[1] = 0;
         mbar_fence_init();
     }
+    // K / V tile i of this CTA -> ring slot (thread 0 only). The first tile is requested right after the barriers
+    // exist, before the Q rows are staged and TMEM is allocated: the page-table reads and the first DRAM round trip
+    // then run under the rest of the prologue (a CTA of a short context has only ~5 tiles to amortise its start).
+    const int ppt = DA_KEYS / p.page_size;
+    const int* pages = p.page_indices + p.page_indptr[req];
+    auto issue_k = [&](int i) {
+        const int jt = jt0 + i, s = i % KS;
+        uint8_t* dst = sK + s * DA_K_BYTES;
+        mbar_expect_tx(&k_full[s], DA_K_BYTES);
+        for (int pg = 0; pg < ppt; ++pg) {
+            int pi = jt * ppt + pg;
+            if (pi >= npages) pi = npages - 1;
+            const int page = pages[pi];
+            const int row_off = pg * p.page_size * 128;
+            tma_load_4d(dst + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
+            tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
+        }
+    };
+    auto issue_v = [&](int i) {
+        const int jt = jt0 + i, s = i % VS;
+        uint8_t* dst = sV + s * DA_K_BYTES;
+        mbar_expect_tx(&v_full[s], DA_K_BYTES);
+        for (int pg = 0; pg < ppt; ++pg) {
+            int pi = jt * ppt + pg;
+            if (pi >= npages) pi = npages - 1;
+            const int page = pages[pi];
+            const int row_off = pg * p.page_size * 128;
+            tma_load_4d(dst + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
+            tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
+        }
+    };
+    if (threadIdx.x == 0 && ntiles > 0) {
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        issue_k(0);
+        issue_v(0);
+    }
     if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
     if (warp == 2) {
         // Q rows -> swizzled K-major B tile: lane c < 16 copies row c (zero rows beyond ncols)
@@ -163,13 +204,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     if (warp == 0) {
         // =========================== TMA producer ===========================
         if (lane == 0 && ntiles > 0) {
-            tma_prefetch_desc(&tmK);
-            tma_prefetch_desc(&tmV);
-            const int ppt = DA_KEYS / p.page_size;
-            const int* pages = p.page_indices + p.page_indptr[req];
-            int issued_k = 0, issued_v = 0;
-            for (int i = 0; i < ntiles; ++i) {
-                const int jt = jt0 + i;
+            int issued_k = 1, issued_v = 1;          // tile 0 went out in the prologue
+            for (int i = 1; i < ntiles; ++i) {
                 {
                     const int s = i % KS;
                     if (!mbar_wait(&k_empty[s], ((i / KS) & 1) ^ 1, p.wait_limit_ns)) {
@@ -178,16 +214,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
                         break;
                     }
                     if (sh[0]) break;
-                    uint8_t* dst = sK + s * DA_K_BYTES;
-                    mbar_expect_tx(&k_full[s], DA_K_BYTES);
-                    for (int pg = 0; pg < ppt; ++pg) {
-                        int pi = jt * ppt + pg;
-                        if (pi >= npages) pi = npages - 1;
-                        const int page = pages[pi];
-                        const int row_off = pg * p.page_size * 128;
-                        tma_load_4d(dst + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
-                        tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
-                    }
+                    issue_k(i);
                     issued_k = i + 1;
                 }
                 {
@@ -198,16 +225,7 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
                         break;
                     }
                     if (sh[0]) break;
-                    uint8_t* dst = sV + s * DA_K_BYTES;
-                    mbar_expect_tx(&v_full[s], DA_K_BYTES);
-                    for (int pg = 0; pg < ppt; ++pg) {
-                        int pi = jt * ppt + pg;
-                        if (pi >= npages) pi = npages - 1;
-                        const int page = pages[pi];
-                        const int row_off = pg * p.page_size * 128;
-                        tma_load_4d(dst + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
-                        tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
-                    }
+                    issue_v(i);
                     issued_v = i + 1;
                 }
             }
