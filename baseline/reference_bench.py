@@ -277,10 +277,11 @@ def run_reference(args) -> dict:
                     os.killpg(proc.pid, 9)
                 except Exception:  # noqa: BLE001
                     pass
-        if os.environ.get("MSTAR_REF_KEEP_LOG"):
+        if os.environ.get("MSTAR_REF_KEEP_LOG"):       # directory to keep the server's log in
             try:
-                os.makedirs("gpurun_out", exist_ok=True)
-                shutil.copy(log_path, "gpurun_out/reference_server.log")
+                keep = os.environ["MSTAR_REF_KEEP_LOG"]
+                os.makedirs(keep, exist_ok=True)
+                shutil.copy(log_path, os.path.join(keep, "reference_server.log"))
             except Exception:  # noqa: BLE001
                 pass
         shutil.rmtree(work, ignore_errors=True)
