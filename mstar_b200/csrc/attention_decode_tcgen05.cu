@@ -346,13 +346,13 @@ MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_s
     cudaStream_t stream = (cudaStream_t)stream_;
 #define MSTAR_DA_LAUNCH(KS, VS, NC, MINB)                                                                        \
     do {                                                                                                          \
-        static bool configured = false;                                                                           \
+        static PerDeviceFlag configured;                                                                           \
         constexpr int smem = da_smem_bytes(KS, VS);                                                               \
-        if (!configured) {                                                                                        \
+        if (!configured()) {                                                                                        \
             cudaError_t e_ = cudaFuncSetAttribute(attn_decode_tcgen05_kernel<KS, VS, NC, MINB>,                   \
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, smem);             \
             if (e_ != cudaSuccess) return set_error("attention_decode: cudaFuncSetAttribute failed", e_);         \
-            configured = true;                                                                                    \
+            configured() = true;                                                                                    \
         }                                                                                                         \
         cudaError_t le_ = launch_pdl(attn_decode_tcgen05_kernel<KS, VS, NC, MINB>, grid, dim3(192), smem, stream,  \
                                      tmK, tmV, p);                                                                \

@@ -525,11 +525,11 @@ template <int HD>
 static int launch_attn(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, dim3 grid,
                        cudaStream_t stream) {
     constexpr int smem = AttnSmem<HD>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured()) {
         cudaError_t e = cudaFuncSetAttribute(attn_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("attention: cudaFuncSetAttribute failed", e);
-        configured = true;
+        configured() = true;
     }
     cudaError_t e = launch_pdl(attn_tcgen05_kernel<HD>, grid, dim3(AT_THREADS), smem, stream, tmK, tmV, p);
     return e == cudaSuccess ? 0 : set_error("attention: launch failed", e);

@@ -1184,18 +1184,19 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
     using KernelFn = void (*)(CUtensorMap, CUtensorMap, GemmParams);
     const KernelFn kern = p.swap ? static_cast<KernelFn>(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB, true>)
                                  : static_cast<KernelFn>(gemm_bf16_tcgen05_kernel<BN, STAGES, MINB, KSUB, false>);
-    static bool configured[2] = {false, false};
-    if (!configured[p.swap ? 1 : 0]) {
+    static PerDeviceFlag configured[2];
+    if (!configured[p.swap ? 1 : 0]()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
-        configured[p.swap ? 1 : 0] = true;
+        configured[p.swap ? 1 : 0]() = true;
     }
     if (p.cluster_reduce) {
         // Clusters are placed inside one GPC each, so a split factor that does not divide the GPCs' SM counts well
         // leaves SMs unusable and the grid runs in two waves (measured: 24 clusters of 6 CTAs did, 24 of 4 do not).
         // Ask the runtime how many clusters of each size are co-resident and take the largest factor, at most the
         // planned one, whose clusters all fit.
-        static int max_active[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+        static int max_active_dev[kMaxDevices][9] = {};
+        int* max_active = max_active_dev[current_device()];
         const int tiles = (int)(grid.x * grid.y);
         int use = 0;
         for (int sp = (int)grid.z; sp >= 2 && use == 0; --sp) {
@@ -1269,12 +1270,12 @@ template <int BN, int STAGES>
 static int launch_persistent(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, dim3 grid,
                              cudaStream_t stream) {
     constexpr int smem = gemm_smem_bytes(BN, STAGES);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm: cudaFuncSetAttribute failed", e);
-        configured = true;
+        configured() = true;
     }
     const int tiles = (int)(grid.x * grid.y);
     const int ctas = tiles < device_sm_count() ? tiles : device_sm_count();
@@ -1548,12 +1549,12 @@ template <int BN, int STAGES, bool SWAP, int EW = 4>
 static int launch_fp8(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, const Fp8Scales& sc,
                       dim3 grid, cudaStream_t stream) {
     constexpr int smem = gemm_fp8_smem_bytes(BN, STAGES);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured()) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP, EW>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return set_error("gemm_fp8: cudaFuncSetAttribute failed", e);
-        configured = true;
+        configured() = true;
     }
     cudaError_t e = launch_pdl(gemm_fp8_blockscaled_kernel<BN, STAGES, SWAP, EW>, grid, dim3(64 + EW * 32), smem, stream,
                                tmP, tmQ, p, sc);
@@ -1690,7 +1691,6 @@ struct NoAllocScratch {
 // kernel may use comes from cudaGetSymbolAddress (below), once per device.
 static __device__ __align__(256) NoAllocScratch g_noalloc_scratch;
 
-constexpr int kMaxDevices = 64;
 static NoAllocScratch* g_noalloc_ptr[kMaxDevices] = {};
 
 }  // namespace
@@ -1746,8 +1746,8 @@ MSTAR_API int mstar_gemm_bf16_noalloc(const void* A, const void* B, void* C, int
     p.residual = nullptr;
     p.workspace = scratch->partials;
     p.counters = scratch->counters;
-    p.status = nullptr;              // the shared status word is heap-allocated; this path keeps its waits bounded
-                                     // but reports nothing
+    p.status = nullptr;              // the status word is allocated memory, which this path must not create: its
+                                     // waits stay bounded but a timeout is not reported (stated in the header)
     p.wait_limit_ns = wait_limit_ns();
     p.out_scale = 1.0f;
     p.ar = GemmAllReduce{};

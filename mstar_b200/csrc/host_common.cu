@@ -8,9 +8,9 @@
 namespace mstar {
 
 static char g_err[512] = "";
-static KernelStatus* g_status = nullptr;
+static KernelStatus* g_status[kMaxDevices] = {};
 static unsigned long long g_wait_limit = MSTAR_WAIT_LIMIT_NS_DEFAULT;
-static int g_sms = 0;
+static int g_sms[kMaxDevices] = {};
 static std::mutex g_mu;
 
 int set_error(const char* msg, cudaError_t e) {
@@ -22,18 +22,25 @@ int set_error(const char* msg, cudaError_t e) {
     return -1;
 }
 
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+    return dev < kMaxDevices ? dev : kMaxDevices - 1;
+}
+
 KernelStatus* status_ptr() {
-    if (g_status == nullptr) {
+    const int dev = current_device();
+    if (g_status[dev] == nullptr) {
         std::lock_guard<std::mutex> lk(g_mu);
-        if (g_status == nullptr) {
+        if (g_status[dev] == nullptr) {
             KernelStatus* p = nullptr;
-            if (cudaMalloc(&p, sizeof(KernelStatus)) == cudaSuccess) {
+            if (cudaMalloc(&p, sizeof(KernelStatus)) == cudaSuccess) {      // lands on the current device
                 cudaMemset(p, 0, sizeof(KernelStatus));
-                g_status = p;
+                g_status[dev] = p;
             }
         }
     }
-    return g_status;
+    return g_status[dev];
 }
 
 unsigned long long wait_limit_ns() { return g_wait_limit; }
@@ -50,15 +57,15 @@ bool pdl_enabled() {
 }
 
 int device_sm_count() {
-    if (g_sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            g_sms = n;
+    const int dev = current_device();
+    if (g_sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            g_sms[dev] = n;
         else
-            g_sms = 148;
+            g_sms[dev] = 148;
     }
-    return g_sms;
+    return g_sms[dev];
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -134,6 +141,16 @@ MSTAR_API unsigned int mstar_read_status(unsigned int* out4, int clear) {
     }
     if (clear && h.code != 0) cudaMemset(p, 0, sizeof(h));
     return h.code;
+}
+
+// Queues a copy of the current device's status word (16 bytes) into `host_dst16` (pinned host memory) on `stream`:
+// a serving loop reads the word with the batch's results, after the event it already waits for, instead of paying
+// a synchronous copy per batch. The word is not cleared; mstar_read_status(.., 1) does that once a code was seen.
+MSTAR_API int mstar_status_copy_async(void* host_dst16, void* stream) {
+    KernelStatus* p = status_ptr();
+    if (p == nullptr) return set_error("status word could not be allocated", cudaSuccess);
+    cudaError_t e = cudaMemcpyAsync(host_dst16, p, sizeof(KernelStatus), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : set_error("status copy failed", e);
 }
 
 MSTAR_API void mstar_set_wait_limit_ns(unsigned long long ns) { g_wait_limit = ns; }

@@ -8,10 +8,22 @@
 
 namespace mstar {
 
+// CUDA state is per device while a process may drive several GPUs (one worker thread per GPU): everything the
+// launchers cache (status word, kernel attributes already set, SM count, cluster occupancy) is indexed by device.
+constexpr int kMaxDevices = 64;
+int current_device();                               // index of the current CUDA device, clamped to [0, kMaxDevices)
+
+// "Has this been done on the current device yet?" flag for one-time per-device set-up such as
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize), which applies to the function on ONE device only.
+struct PerDeviceFlag {
+    bool done[kMaxDevices] = {};
+    bool& operator()() { return done[current_device()]; }
+};
+
 int set_error(const char* msg, cudaError_t e);      // stores the message, returns -1
-KernelStatus* status_ptr();                         // device pointer of this process' status word (lazily made)
+KernelStatus* status_ptr();                         // status word of the CURRENT device (lazily made, one per device)
 unsigned long long wait_limit_ns();
-int device_sm_count();
+int device_sm_count();                              // SM count of the current device
 
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements); box =
 // box_rows x box_cols, SWIZZLE_128B (box_cols * 2 bytes must be 128).

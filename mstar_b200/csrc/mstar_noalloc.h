@@ -20,16 +20,22 @@ extern "C" {
 #define MSTAR_NOALLOC_WORKSPACE_BYTES (16u << 20)   /* fp32 partial tiles */
 #define MSTAR_NOALLOC_MAX_TILES 4096                /* one arrival counter per output tile */
 
-// C[M,N] = A[M,K] * B[N,K]^T, bf16 operands and output, fp32 accumulation: the same tcgen05 kernel, tile plan and
-// split-K reduction as mstar_gemm_bf16 (no bias / residual / activation), so results are bitwise identical to
-// that entry point for the same problem.
+// C[M,N] = A[M,K] * B[N,K]^T, bf16 operands and output, fp32 accumulation, no bias / residual / activation. It is
+// the same tcgen05 kernel and tile plan as mstar_gemm_bf16, but the split-K partial sums always meet in the
+// scratch array, while the regular entry point may sum them through a thread-block cluster with another split
+// factor. The two therefore add the same products in a different order: results agree within bf16 rounding of
+// the output, not bit for bit.
 //
 // Scratch lives in a file-scope device array of MSTAR_NOALLOC_WORKSPACE_BYTES (+ counters); every GPU that loads
 // the library carries it until the process exits. The entry point calls no cudaMalloc / cudaFree and no
 // allocating library routine.
 //
-// * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and configures the
-//   kernel; make that first call before any CUDA stream capture on that device.
+// * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and sets the
+//   kernel's shared-memory attribute for that device; make that first call before any CUDA stream capture on
+//   that device.
+// * Device-side waits in this path are bounded like everywhere in the library, but a wait that runs out is NOT
+//   reported: the library's status word lives in allocated memory, which this entry point must not create, so the
+//   kernel is given none. After such a timeout the output tile is incomplete and the call still returns 0.
 // * All calls share the one array. Two calls that can overlap on the GPU (different streams, or a capture
 //   replayed concurrently) race on it: serialise them. The counters are cleared on the stream at every call;
 //   the partial-tile area is fully rewritten before it is read, so leftovers of earlier calls are harmless.

@@ -377,12 +377,12 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
                    out, out_prob, u_override, escratch};
     cudaStream_t s = (cudaStream_t)stream_;
     constexpr int smem = SP_NW * 256 * 12;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceFlag configured;
+    if (!configured()) {
         cudaError_t e1 = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         cudaError_t e2 = cudaFuncSetAttribute(sample_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e1 != cudaSuccess || e2 != cudaSuccess) return set_error("sample: cudaFuncSetAttribute failed", e1 != cudaSuccess ? e1 : e2);
-        configured = true;
+        configured() = true;
     }
     const int cl = V >= 16384 ? SP_CL : 1;
     cudaLaunchConfig_t cfg = {};

@@ -39,6 +39,7 @@ class NodeOutput:
     allocation_failed: bool = False
     allocation_failed_requests: list[str] = field(default_factory=list)
     completion_event: object = None
+    status_host: object = None        # pinned int32[4]: the device status word as of the end of this batch
     timings: dict = field(default_factory=dict)
 
 
@@ -99,9 +100,34 @@ class BaseEngine:
 
     def finalize_batch(self, planned, out: NodeOutput) -> None:
         if self.device.type == "cuda":
+            # the device status word travels with the batch: a bounded wait that ran out inside one of its kernels
+            # (a late or lost TP / SP peer, a stuck mbarrier) must fail the batch, not stream partial output
+            from ..ops import _lib
+            if not hasattr(self, "_status_ring"):
+                self._status_ring = [torch.zeros(4, dtype=torch.int32).pin_memory() for _ in range(8)]
+                self._status_i = 0
+            self._status_i = (self._status_i + 1) % len(self._status_ring)
+            out.status_host = self._status_ring[self._status_i]
+            _lib.status_copy_async(out.status_host)
             ev = torch.cuda.Event()
             ev.record()
             out.completion_event = ev
+
+    def check_batch_status(self, out: NodeOutput) -> str | None:
+        """After the batch's completion event: None when every kernel ran to its end, else what gave up (the word is
+        cleared so the next batch starts clean). Engines of a TP / SP instance also mark themselves unhealthy: the
+        peers' collectives are out of step after a timeout."""
+        st = out.status_host
+        if st is None:
+            return None
+        code = int(st[0])
+        if code == 0:
+            return None
+        from ..ops import _lib
+        _lib.read_status(clear=True)
+        if getattr(self, "tp_group", None) is not None and getattr(self.tp_group, "size", 1) > 1:
+            self.unhealthy = True
+        return f"device status {code:#x}: {_lib.decode_status(code)} (block {int(st[1])}, aux {int(st[2])}, {int(st[3])})"
 
     # chunking ---------------------------------------------------------------------------------------
     def execute_with_max_batch_size(self, batch: NodeBatch, max_bs: int) -> NodeOutput:

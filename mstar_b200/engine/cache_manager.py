@@ -128,11 +128,12 @@ class BatchedCacheManager:
              causal: bool = True, window: int = 0, write_cache: bool = True,
              custom_positions: torch.Tensor | None = None, row_slots: list[int] | None = None,
              pad_to_batch: int | None = None, lookahead_tokens: int = 0, group: int = 1,
-             slot: int = 0, splits: int | None = None) -> BatchContext:
+             slot: int = 0, splits: int | None = None, pad_row_slot: int = 0) -> BatchContext:
         """Reserve pages for the new tokens and write the device plan. Entries are (request, label) pairs.
         ``pad_to_batch`` pads with empty entries (one token, no keys, no cache write) up to a captured batch size;
         ``lookahead_tokens`` reserves pages for that many future decode tokens so that device-side advance can run
-        ahead of the host."""
+        ahead of the host. ``pad_row_slot`` is the sampler slot that padding rows use: it must belong to no request,
+        because the captured step samples every row and updates the slot's seen-token mask and draw counter."""
         B = len(request_ids)
         labels = labels or ["main"] * B
         cfg = self.config
@@ -179,7 +180,7 @@ class BatchedCacheManager:
         cpos[:T] = tok_pos
         treq[:T] = np.where(real, ent, -1) if write_cache else -1
         rslot[:B] = np.asarray(row_slots, dtype=np.int32) if row_slots is not None else np.arange(B, dtype=np.int32)
-        rslot[B:Bp] = 0
+        rslot[B:Bp] = pad_row_slot
         lrows[:Bp] = qi[1:Bp + 1].astype(np.int64) - 1
         kvi[:Bp + 1] = 0
         max_kv = int(kl[:Bp].max()) if Bp else 0

@@ -40,7 +40,7 @@ class KVCacheEngine(BaseEngine):
         self.kv_config = kv_config
         self.cache = BatchedCacheManager(kv_config, device, max_batch=max_batch, max_tokens=max_tokens + max_batch,
                                          n_pos_axes=n_pos_axes)
-        self.sampler = SamplerState(max_batch * 2, vocab_size, device, track_seen=track_seen)
+        self.sampler = SamplerState(max_batch * 2 + 1, vocab_size, device, track_seen=track_seen, reserve_pad_slot=True)
         self.max_batch, self.group = max_batch, group
         self.tp_group = tp_group
         self.use_graphs = (self.device.type == "cuda") if use_cuda_graphs is None else (use_cuda_graphs and self.device.type == "cuda")
@@ -196,7 +196,7 @@ class KVCacheEngine(BaseEngine):
                                                            for ni in prepared.node_inputs]))
         ctx = self.cache.plan(prepared.request_ids, q_lens, labels=labels, row_slots=slots, pad_to_batch=bucket,
                               group=self.group, slot=0 if bucket is not None else 1, custom_positions=custom,
-                              splits=splits, lookahead_tokens=burst - 1)
+                              splits=splits, lookahead_tokens=burst - 1, pad_row_slot=self.sampler.pad_slot)
         prepared.ctx, prepared.bucket, prepared.q_lens, prepared.burst = ctx, bucket, q_lens, burst
         return prepared
 

@@ -329,6 +329,8 @@ class LLMEngine:
     def _preempt(self, req: GenRequest) -> None:
         """Release a request's KV and requeue it with its generated prefix as part of the prompt."""
         self._drain()
+        if req.finished:          # the tokens still in flight completed it: nothing left to recompute
+            return
         self._rows[req.row] = None
         self.cache.remove_request(req.request_id)
         self.sampler.release(req.request_id)

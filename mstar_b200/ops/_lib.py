@@ -88,6 +88,22 @@ def read_status(clear: bool = True) -> tuple[int, int, int, int]:
     return tuple(int(x) for x in buf)
 
 
+def status_copy_async(pinned: torch.Tensor) -> None:
+    """Queue a copy of the current device's status word into ``pinned`` (int32[4], pinned host memory) on the
+    current stream; the caller reads it after synchronising with an event recorded behind the copy."""
+    rc = kernels().mstar_status_copy_async(ctypes.c_void_p(pinned.data_ptr()), ctypes.c_void_p(stream_ptr()))
+    if rc != 0:
+        raise RuntimeError("status copy failed: " + kernels().mstar_last_error().decode(errors="replace"))
+
+
+def decode_status(code: int) -> str:
+    """Readable form of a status code: which kernel gave up in which phase."""
+    names = {1: "gemm", 2: "attention", 3: "decode attention", 4: "expert gemm", 5: "collective", 6: "gemm+all-reduce",
+             7: "ulysses exchange", 8: "cfg combine", 9: "expert dispatch/combine", 10: "test", 11: "gemm+reduce-scatter",
+             12: "all-gather+gemm", 13: "sharded sampler"}
+    return f"{names.get(code >> 16, 'kernel ' + str(code >> 16))} wait ran out in phase {code & 0xffff}"
+
+
 def set_wait_limit_ns(ns: int) -> None:
     kernels().mstar_set_wait_limit_ns(int(ns))
 

@@ -114,7 +114,11 @@ def sample_ref(logits, temperature, top_k, top_p, rep_penalty, seeds, offsets, s
 class SamplerState:
     """Slot-indexed sampling parameters on the device. A request owns one slot for its lifetime."""
 
-    def __init__(self, num_slots: int, vocab_size: int, device, track_seen: bool = False):
+    def __init__(self, num_slots: int, vocab_size: int, device, track_seen: bool = False,
+                 reserve_pad_slot: bool = False):
+        """``reserve_pad_slot`` keeps the last slot out of the free list (``pad_slot``): the padding rows of a
+        bucketed batch sample with it (greedy, no penalty), so that they never touch a live request's seen-token
+        mask or draw counter."""
         self.num_slots, self.vocab_size, self.device = num_slots, vocab_size, torch.device(device)
         d = self.device
         self.temperature = torch.zeros(num_slots, dtype=torch.float32, device=d)
@@ -127,7 +131,8 @@ class SamplerState:
         # scratch of the kernel: exp(logit - max) per element, written once and read by the later passes
         self._es = (torch.empty((num_slots, vocab_size), dtype=torch.float32, device=d)
                     if torch.device(d).type == "cuda" and vocab_size >= 16384 else None)
-        self._free = list(range(num_slots - 1, -1, -1))
+        self.pad_slot = num_slots - 1 if reserve_pad_slot else None
+        self._free = list(range(num_slots - (2 if reserve_pad_slot else 1), -1, -1))
         self._slot_of: dict[str, int] = {}
 
     def _escratch(self, rows: int, vocab: int, device):

@@ -373,6 +373,12 @@ class Worker:
     def _postprocess_batch(self, batch: NodeBatch, out: NodeOutput) -> None:
         if out.completion_event is not None:
             out.completion_event.synchronize()
+        bad = self.engines.engine_for(batch.node_name).check_batch_status(out)
+        if bad is not None:
+            # a kernel of this batch left through its timeout exit: its output is partial, fail every request of it
+            log.error("worker %s: %s:%s %s", self.worker_id, batch.node_name, batch.graph_walk, bad)
+            out.failed_requests = {rid: bad for rid in batch.request_ids}
+            out.allocation_failed = False
         if out.allocation_failed:
             self._handle_allocation_failure(batch, out)
             return

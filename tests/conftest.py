@@ -10,6 +10,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
     config.addinivalue_line("markers", "multigpu: needs 2 or more CUDA devices")
+    config.addinivalue_line("markers", "expects_status: the test makes a bounded device wait run out on purpose and "
+                                       "reads the status word itself")
 
 
 def pytest_collection_modifyitems(config, items):

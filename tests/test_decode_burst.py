@@ -71,3 +71,38 @@ def test_tts_stream_with_frame_sized_bursts():
             s.shutdown()
     finally:
         os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
+
+
+def _run_requests(prompts, **mk):
+    """Tokens of each prompt when all of them are submitted together (one decode batch, padded to its bucket)."""
+    os.environ["MSTAR_EMULATE_GRAPHS"] = "1"
+    os.environ["MSTAR_DECODE_BURST"] = "1"
+    try:
+        cfg = {"model": "tiny", "model_kwargs": {"dtype": "float32", "max_num_pages": 256},
+               "node_groups": [{"node_names": ["LLM"], "ranks": [0]}]}
+        s = APIServer(cfg, in_process=True).start(60)
+        try:
+            rids = [s.submit_request(p, output_modalities=["text"], request_id=f"pad-{p.replace(' ', '_')}",
+                                     model_kwargs=dict(mk)) for p in prompts]
+            outs = {}
+            for p, r in zip(prompts, rids):
+                res = s.collect_results(r, 120)
+                assert "error" not in res, res
+                outs[p] = b"".join(c.data for c in res["text"]).decode().split()
+            return outs
+        finally:
+            s.shutdown()
+    finally:
+        os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
+        os.environ.pop("MSTAR_DECODE_BURST", None)
+
+
+def test_padding_rows_do_not_disturb_a_seeded_penalised_request():
+    """Three requests decode in the bucket of four: the padding row samples with the sampler's reserved slot, so a
+    request's repetition-penalty mask and draw counter are the same as when it runs alone in the bucket of one."""
+    kw = dict(max_tokens=20, ignore_eos=True, temperature=0.9, top_p=0.95, repetition_penalty=1.3, seed=5)
+    prompts = ["1 2 3", "4 5 6 7", "9 8 7 6 5"]
+    together = _run_requests(prompts, **kw)
+    for p in prompts:
+        alone = _run_requests([p], **kw)
+        assert alone[p] == together[p], p

@@ -74,3 +74,27 @@ def test_bad_prompt_fails_only_that_request(server):
     res = server.collect_results(rid, 30)
     assert res["error"][0].error_status == 400
     assert _gen(server, [9, 9, 9], 2)
+
+
+def test_kernel_timeout_status_fails_the_batch_and_the_server_goes_on(server):
+    """A kernel whose bounded wait ran out reports through the device status word that travels with every batch.
+    Made on the host here: the engine's status check answers once as if the word had been set. The requests of that
+    batch must fail (no partial tokens delivered as a success) and later requests must be served."""
+    eng = server.deployment.workers[0].engines.engine_for("LLM")
+    real = eng.check_batch_status
+    fired = []
+
+    def once(out):
+        if not fired and out.graph_walk == "decode":
+            fired.append(1)
+            return "device status 0x50001: collective wait ran out in phase 1 (block 0, aux 1, 0)"
+        return real(out)
+    eng.check_batch_status = once
+    try:
+        rid = server.submit_request("1 2 3 4", model_kwargs=dict(max_tokens=50, temperature=0.0))
+        res = server.collect_results(rid, 60)
+        assert "error" in res and "wait ran out" in res["error"][0].data.decode(errors="replace"), res
+    finally:
+        eng.check_batch_status = real
+    assert fired
+    assert _gen(server, [4, 4, 4], 3)
