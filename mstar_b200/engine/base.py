@@ -18,6 +18,9 @@ class NodeBatch:
     request_ids: list[str]
     inputs: dict[str, dict[str, list[torch.Tensor]]]     # request_id -> input name -> tensors
     fwd_infos: dict                                       # request_id -> CurrentForwardPassInfo
+    # launched before the previous execution of the same node for the same requests was read back: its inputs are
+    # the outputs that execution left on the device (a worker only sets this on engines that ``can_speculate``)
+    speculative: bool = False
 
 
 @dataclass
@@ -43,6 +46,22 @@ class NodeOutput:
     timings: dict = field(default_factory=dict)
 
 
+@dataclass
+class PendingBatch:
+    """A batch whose GPU work is queued but whose results have not been read back: the hand-over between
+    ``launch_batch`` (never waits for the GPU) and ``collect_batch`` (reads results; cheap once ``ready()``)."""
+    batch: NodeBatch
+    out: NodeOutput
+    planned: object = None
+    raw: object = None
+    event: object = None              # recorded behind the batch's last kernel and result copy
+    iterations: int = 1               # loop iterations every request of the batch covers (decode burst length)
+    t_launch: tuple = ()
+
+    def ready(self) -> bool:
+        return self.event is None or self.event.query()
+
+
 class BaseEngine:
     def __init__(self, node_names: list[str], device):
         self.node_names = list(node_names)
@@ -52,28 +71,56 @@ class BaseEngine:
 
     # template ------------------------------------------------------------------------------------
     def execute_batch(self, batch: NodeBatch) -> NodeOutput:
+        return self.collect_batch(self.launch_batch(batch))
+
+    def launch_batch(self, batch: NodeBatch) -> PendingBatch:
+        """prepare -> plan -> forward: queues the batch's GPU work and the copies of what the host will read, records
+        an event behind them and returns without waiting. A worker launches the next batch (a speculative one
+        included) while this one still runs, and calls ``collect_batch`` once ``pending.ready()``."""
         import time
         t0 = time.perf_counter()
         prepared = self.prepare_batch(batch)
         out = NodeOutput(batch.node_name, batch.graph_walk, failed_requests=dict(prepared.failed_requests))
+        pend = PendingBatch(batch, out)
         if not prepared.request_ids:
-            return out
+            return pend
         t1 = time.perf_counter()
         planned = self.plan(prepared)
         t2 = time.perf_counter()
-        raw = self.execute_forward(planned)
-        t3 = time.perf_counter()
-        self.postprocess(planned, raw, out)
-        t4 = time.perf_counter()
+        pend.planned = planned
+        pend.raw = self.execute_forward(planned)
+        pend.iterations = max(1, int(getattr(planned, "burst", 1) or 1))
         self.finalize_batch(planned, out)
+        pend.event = out.completion_event
+        t3 = time.perf_counter()
         # host seconds of every phase (the forward's number is launch time only unless the phase synchronises)
         ph = self.phase_s
         ph["prepare"] += t1 - t0
         ph["plan"] += t2 - t1
         ph["forward"] += t3 - t2
-        ph["postprocess"] += t4 - t3
-        out.timings.update(prepare_s=t1 - t0, plan_s=t2 - t1, forward_s=t3 - t2, postprocess_s=t4 - t3)
+        out.timings.update(prepare_s=t1 - t0, plan_s=t2 - t1, forward_s=t3 - t2)
+        return pend
+
+    def collect_batch(self, pend: PendingBatch) -> NodeOutput:
+        """Wait for the batch (no wait when ``pend.ready()``), read its results and run the per-request
+        postprocessing and stop checks."""
+        import time
+        out = pend.out
+        if pend.planned is None:
+            return out
+        if pend.event is not None:
+            pend.event.synchronize()
+        t3 = time.perf_counter()
+        self.postprocess(pend.planned, pend.raw, out)
+        dt = time.perf_counter() - t3
+        self.phase_s["postprocess"] += dt
+        out.timings["postprocess_s"] = dt
         return out
+
+    def can_speculate(self, node_name: str, graph_walk: str) -> bool:
+        """May the next loop iteration of this node be launched from the device-resident outputs of the one still
+        running (``NodeBatch.speculative``)?"""
+        return False
 
     def prepare_batch(self, batch: NodeBatch) -> PreparedBatch:
         """Per-request input preparation; a request whose preparation raises is failed alone."""

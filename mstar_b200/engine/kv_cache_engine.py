@@ -20,7 +20,7 @@ from ..models.submodule_base import BATCHED_LOGITS, ModelInputsFromEngine
 from ..ops import _lib
 from ..ops import attention as attn_ops
 from ..ops.sampling import SamplerState, SamplingConfig
-from .base import BaseEngine, NodeBatch, NodeOutput, PreparedBatch
+from .base import BaseEngine, NodeBatch, NodeOutput, PendingBatch, PreparedBatch
 from .cache_manager import BatchedCacheManager
 from .kv_store import AllocationFailedError, KVCacheConfig
 
@@ -37,6 +37,13 @@ class KVCacheEngine(BaseEngine):
         # bookkeeping is paid once per burst instead of once per token
         self.decode_burst = max(1, int(os.environ.get("MSTAR_DECODE_BURST", decode_burst)))
         self._burst_buf = torch.zeros((self.decode_burst, max_batch), dtype=torch.int64, device=torch.device(device))
+        # sampled ids travel to the host through a ring of pinned buffers with an asynchronous copy behind the last
+        # replay, so a following (speculative) batch can be queued before this one's tokens are read
+        _cuda = torch.device(device).type == "cuda"
+        self._host_ring = [torch.zeros((self.decode_burst, max_batch), dtype=torch.int64, pin_memory=_cuda)
+                           for _ in range(4)]
+        self._host_i = 0
+        self._last_graph_key = None       # (node, walk, bucket, request ids) of the last captured-step execution
         self.kv_config = kv_config
         self.cache = BatchedCacheManager(kv_config, device, max_batch=max_batch, max_tokens=max_tokens + max_batch,
                                          n_pos_axes=n_pos_axes)
@@ -142,14 +149,21 @@ class KVCacheEngine(BaseEngine):
         return self.cache.alloc.pages_of(request_id)
 
     # ---- template steps ----
-    def execute_batch(self, batch: NodeBatch) -> NodeOutput:
+    def launch_batch(self, batch: NodeBatch) -> PendingBatch:
         try:
-            return super().execute_batch(batch)
+            return super().launch_batch(batch)
         except AllocationFailedError as e:
             out = NodeOutput(batch.node_name, batch.graph_walk, allocation_failed=True,
                              allocation_failed_requests=list(batch.request_ids))
             out.timings["allocation_error"] = str(e)
-            return out
+            return PendingBatch(batch, out)
+
+    def can_speculate(self, node_name: str, graph_walk: str) -> bool:
+        """The captured decode step leaves the sampled ids as its own next input and the plan advanced on the
+        device, so iteration N+1 of a decode loop needs nothing from the host but page reservations."""
+        sub = self.submodules.get(node_name)
+        return bool(self.use_graphs and sub is not None and sub.can_use_cuda_graphs(graph_walk)
+                    and self._last_graph_key is not None and self._last_graph_key[:2] == (node_name, graph_walk))
 
     def prepare_batch(self, batch: NodeBatch) -> PreparedBatch:
         for rid in batch.request_ids:
@@ -169,7 +183,7 @@ class KVCacheEngine(BaseEngine):
             if ctx is not None:
                 prepared.ctx, prepared.bucket, prepared.q_lens = ctx, None, list(ctx.q_lens)
                 return prepared
-        q_lens = [max(1, ni.input_seq_len) for ni in prepared.node_inputs]
+        q_lens = [1 if b.speculative else max(1, ni.input_seq_len) for ni in prepared.node_inputs]
         labels = [sub.get_needed_cache_labels(b.graph_walk, b.fwd_infos[r])[0] for r in prepared.request_ids]
         slots = [self.sampler.slot(r) for r in prepared.request_ids]
         decode = all(q == 1 for q in q_lens)
@@ -217,12 +231,20 @@ class KVCacheEngine(BaseEngine):
         with torch.no_grad():
             if planned.bucket is not None:
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
-                ids = torch.cat([ni.input_ids.reshape(-1)[-1:] for ni in planned.node_inputs]).to(self.device)
-                self._static_ids[:B].copy_(ids)
                 key = (b.node_name, b.graph_walk, planned.bucket)
+                run_key = key + (tuple(planned.request_ids),)
+                if b.speculative:
+                    # the previous execution (same rows, still running or just finished) left its sampled ids in the
+                    # static input buffer: nothing to copy
+                    if self._last_graph_key != run_key:
+                        raise RuntimeError("speculative batch does not continue the engine's last execution")
+                else:
+                    ids = torch.cat([ni.input_ids.reshape(-1)[-1:] for ni in planned.node_inputs]).to(self.device)
+                    self._static_ids[:B].copy_(ids)
                 entry = self._graphs.get(key)
                 if entry is None:
                     entry = self._capture(key, sub, b.graph_walk, ei, planned)
+                self._last_graph_key = run_key
                 k = getattr(planned, "burst", 1)
                 for j in range(k):
                     entry[0].replay()           # the graph leaves the plan advanced and the sampled ids as next input
@@ -232,11 +254,18 @@ class KVCacheEngine(BaseEngine):
                 tokens = self._static_tok[:B].clone()
                 raw = {"tokens": tokens, "extra": {k_: v[:B].clone() if isinstance(v, torch.Tensor) else v
                                                    for k_, v in entry[1].items()}}
+                self._host_i = (self._host_i + 1) % len(self._host_ring)
+                hb = self._host_ring[self._host_i]
                 if k > 1:
                     raw["burst"] = self._burst_buf[:k, :B].t().contiguous()      # [B, k]
+                    hb[:k, :B].copy_(self._burst_buf[:k, :B], non_blocking=True)
+                    raw["burst_host"] = hb[:k, :B]
                     self.cache.advance_seq_lens(ctx, counts=[k] * len(ctx.q_lens))
                     return raw
+                hb[0, :B].copy_(tokens, non_blocking=True)
+                raw["tokens_host"] = hb[0, :B]
             else:
+                self._last_graph_key = None
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 outs = sub.forward_batched(b.graph_walk, ei, planned.node_inputs)
                 if isinstance(outs, list):           # one dict per request; logits rows (if any) are sampled
@@ -325,8 +354,11 @@ class KVCacheEngine(BaseEngine):
         sub = self.submodules[b.node_name]
         tokens = raw.get("tokens")
         burst = raw.get("burst")
-        burst_host = burst.tolist() if burst is not None else None          # one D2H read per execution
-        host_tokens = tokens.tolist() if tokens is not None and burst is None else None
+        # the ids were copied to pinned host memory behind the last replay (captured path): plain reads here
+        burst_host = raw["burst_host"].t().tolist() if burst is not None else None
+        host_tokens = None
+        if tokens is not None and burst is None:
+            host_tokens = raw["tokens_host"].tolist() if "tokens_host" in raw else tokens.tolist()
         for i, (rid, ni) in enumerate(zip(planned.request_ids, planned.node_inputs)):
             try:
                 if "per_request" in raw:

@@ -28,6 +28,17 @@ END_TOKEN_IDS = (128009, 128260, 128261, 128257, 128258)
 VOICES = ["tara", "zoe", "zac", "jess", "leo", "mia", "julia", "leah"]
 
 
+class _HostRows:
+    """A slice of a pinned host buffer that a queued device-to-host copy fills: read it after the batch's event."""
+    __slots__ = ("buf", "row", "lo", "hi")
+
+    def __init__(self, buf, row, lo, hi):
+        self.buf, self.row, self.lo, self.hi = buf, row, lo, hi
+
+    def get(self) -> torch.Tensor:
+        return self.buf[self.row, self.lo:self.hi].clone()
+
+
 class SnacSubmodule(NodeSubmodule):
     def __init__(self, device, base_id: int, small: bool, compute_dtype: torch.dtype = torch.float32):
         super().__init__(device, torch.float32)
@@ -51,29 +62,46 @@ class SnacSubmodule(NodeSubmodule):
         return t[:(t.numel() // 7) * 7]
 
     def _decode(self, tokens: torch.Tensor, runner) -> torch.Tensor:
-        """tokens [B, n] (n a multiple of 7) -> waveforms [B, n / 7 * 2048]; replayed from a CUDA graph per shape."""
+        """tokens [B, n] (n a multiple of 7, host) -> waveforms [B, n / 7 * 2048] on the device; replayed from a CUDA
+        graph per shape. On a GPU the result is a view of the graph's static output: copy it out on the same stream."""
         def fn(tk):
             if self.compute_dtype != torch.float32 and tk.is_cuda:
                 with torch.autocast("cuda", dtype=self.compute_dtype):
                     return self.dec(orpheus_tokens_to_codes(tk, self.base_id)).float()
             return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
-        tk = tokens.to(self.device)
         with torch.no_grad():
-            if runner is not None and tk.is_cuda:
+            if runner is not None and self.device.type == "cuda":
                 # batch padded to a power of two: a handful of captured graphs serve every batch size
-                B = tk.shape[0]
+                B = tokens.shape[0]
                 Bp = 1 << (B - 1).bit_length()
+                stage = self._pinned(("tok", Bp, tokens.shape[1]), (Bp, tokens.shape[1]), torch.int64)
+                stage[:B].copy_(tokens)
                 if Bp != B:
-                    tk = torch.cat([tk, tk[:1].expand(Bp - B, -1)])
-                return runner.run(("snac", tuple(tk.shape)), fn, [tk])[:B].clone()
-            return fn(tk)
+                    stage[B:] = stage[0]
+                tk = stage.to(self.device, non_blocking=True)
+                return runner.run(("snac", tuple(tk.shape)), fn, [tk])[:B]
+            return fn(tokens.to(self.device))
+
+    def _pinned(self, key, shape, dtype) -> torch.Tensor:
+        """Next buffer of a small ring of pinned host buffers per shape: a buffer is reused only four batches later,
+        long after the copy that used it has run."""
+        if not hasattr(self, "_pin"):
+            self._pin = {}
+        ring = self._pin.setdefault(key, [[], 0])
+        if len(ring[0]) < 4:
+            ring[0].append(torch.empty(shape, dtype=dtype, pin_memory=self.device.type == "cuda"))
+            return ring[0][-1]
+        ring[1] = (ring[1] + 1) % 4
+        return ring[0][ring[1]]
 
     def forward(self, graph_walk, engine_inputs, ni, **kw):
         return self.forward_batched(graph_walk, engine_inputs, [ni])[0]
 
     def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
         """Requests whose chunks have the same length are decoded as one batch (streams that decode in lockstep
-        hand in their 28-token windows at the same step)."""
+        hand in their 28-token windows at the same step). Nothing here waits for the GPU: the waveforms are copied
+        to pinned host memory behind the decode and sliced per request in ``postprocess``, which the engine calls
+        once the batch's event has passed."""
         runner = (engine_inputs.preallocated_buffers or {}).get("graph_runner")
         toks = [self._tokens(ni) for ni in inputs]
         outs: list[dict | None] = [None] * len(inputs)
@@ -84,16 +112,23 @@ class SnacSubmodule(NodeSubmodule):
             else:
                 by_len.setdefault(t.numel(), []).append(i)
         for n, idx in by_len.items():
-            wav = self._decode(torch.stack([toks[i] for i in idx]), runner).float().cpu()
+            wav = self._decode(torch.stack([toks[i] for i in idx]), runner).float()
+            if wav.is_cuda:
+                rows = 64 if len(idx) <= 64 else len(idx)
+                host = self._pinned(("wav", rows, wav.shape[1]), (rows, wav.shape[1]), torch.float32)
+                host[:len(idx)].copy_(wav, non_blocking=True)
+            else:
+                host = wav
             for row, i in enumerate(idx):
                 final = bool(inputs[i].kwargs.get("final_chunk"))
                 # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows all
-                w = wav[row, 2048:4096] if n == 28 and not final else wav[row]
-                outs[i] = {"audio": w.contiguous(), "final": final}
+                lo, hi = (2048, 4096) if n == 28 and not final else (0, host.shape[1])
+                outs[i] = {"audio": _HostRows(host, row, lo, hi), "final": final}
         return outs
 
     def postprocess(self, request_id, request_info, outputs, inputs):
-        return {"audio": outputs["audio"]}
+        a = outputs["audio"]
+        return {"audio": a.get() if isinstance(a, _HostRows) else a}
 
     def check_stop(self, request_id, request_info, outputs):
         return {"snac_loop"} if outputs.get("final") or (request_info.step_metadata or {}).get("final_chunk") else set()

@@ -18,6 +18,7 @@ import threading
 import os
 import time
 import traceback
+from collections import deque
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass, field
 
@@ -53,8 +54,25 @@ class PerRequestInfo:
     in_flight: int = 0
     remove_pending: bool = False
     kv_wait: set = field(default_factory=set)      # KV nodes whose pages are still on their way from another process
+    spec: dict = field(default_factory=dict)       # node -> id of the speculative flight that runs its NEXT iteration
+    spec_marked: set = field(default_factory=set)  # nodes marked running on behalf of such a flight
     t_start: float = field(default_factory=time.perf_counter)
     timings: dict = field(default_factory=dict)
+
+
+@dataclass
+class _Flight:
+    """One batch between its launch and the read-back of its results."""
+    fid: int
+    batch: NodeBatch
+    engine: object
+    fut: object = None                 # future of the launch (GPU work being queued on the launch thread)
+    pending: object = None             # PendingBatch once the launch returned
+    error: BaseException | None = None
+    speculative: bool = False
+    chain: int = 0                     # speculative launches in a row that led to this one
+    spec_tried: bool = False
+    t_submit: float = 0.0
 
 
 class Worker:
@@ -76,18 +94,22 @@ class Worker:
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
         self.running = True
-        # one batch in flight PER ENGINE (a KV-cache engine and a stateless engine that share the GPU overlap: each
-        # runs on its own CUDA stream, so a codec batch fills the bubbles of a decode burst); TP followers replay the
-        # leader's order strictly, one batch at a time
-        # (measured on the colocated TTS placement: the two engines slow each other down and the sum does not
-        # improve, 5.85k vs 6.41k tokens/s, so concurrency is opt-in)
-        n_eng = 1
-        if os.environ.get("MSTAR_ENGINE_CONCURRENCY") and not (is_tp_follower or tp_followers):
-            n_eng = max(1, len(getattr(engine_manager, "engines", [])))
-        self.gpu_thread = ThreadPoolExecutor(n_eng, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
-        self._max_in_flight = n_eng
-        self._in_flight: dict[int, tuple] = {}       # id(engine) -> (future, batch)
-        self._streams: dict[int, object] = {}        # id(engine) -> CUDA stream
+        # Execution pipeline. Launches (input preparation, planning, kernel / graph launches, queued result copies)
+        # run on ONE launch thread, so the CUDA stream sees them in submission order and never waits for the host;
+        # the main loop polls each flight's event and reads results back only when they are there. Every engine has
+        # its own queue of flights: while the decode burst N of a KV engine runs, burst N+1 is already queued behind
+        # it (speculation: its inputs are the ids that burst N leaves on the device), and codec / encoder batches of
+        # other engines are queued as soon as their inputs exist. The GPU goes from one batch to the next without
+        # waiting for scheduling, routing or bookkeeping.
+        self.gpu_thread = ThreadPoolExecutor(1, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
+        self._pipes: dict[int, deque] = {}           # id(engine) -> flights in launch order
+        self._next_fid = 0
+        lockstep = bool(is_tp_follower or tp_followers)
+        self._spec_enabled = bool(async_gpu and not lockstep and os.environ.get("MSTAR_SPECULATE", "1") != "0")
+        self._max_chain = int(os.environ.get("MSTAR_MAX_CONSECUTIVE_SPEC_STEPS", "1024"))
+        self._engine_streams = bool(os.environ.get("MSTAR_ENGINE_CONCURRENCY")) and not lockstep
+        self._streams: dict[int, object] = {}        # id(engine) -> CUDA stream (MSTAR_ENGINE_CONCURRENCY only)
+        self.spec_stats = dict(launched=0, discarded_rows=0, cancelled=0)
         self.heartbeat_s = heartbeat_s
         self._last_beat = time.monotonic()
         self.phase_times: dict[str, list[float]] = {}
@@ -348,31 +370,26 @@ class Worker:
         b.partitions = {rk.split("|", 1)[0]: rk.split("|", 1)[1] for rk in rkeys}
         return b
 
-    def _execute(self, batch: NodeBatch) -> NodeOutput:
-        eng = self.engines.engine_for(batch.node_name)
+    def _launch(self, fl: _Flight):
+        """Launch thread: queue the batch's GPU work; returns the engine's PendingBatch without waiting for it."""
+        eng, batch = fl.engine, fl.batch
         with nvtx_range(f"{batch.node_name}:{batch.graph_walk}:{len(batch.request_ids)}"):
             t0 = time.perf_counter()
-            if self._max_in_flight > 1 and eng.device.type == "cuda":
+            if self._engine_streams and eng.device.type == "cuda":
                 st = self._streams.get(id(eng))
                 if st is None:
                     st = self._streams[id(eng)] = torch.cuda.Stream(device=eng.device)
                 with torch.cuda.stream(st):
-                    out = eng.execute_batch(batch)
-                    st.synchronize()        # outputs are handed to other engines / the host after this point
+                    pend = eng.launch_batch(batch)
             else:
-                out = eng.execute_batch(batch)
-            dt = time.perf_counter() - t0
-            out.timings["execute_s"] = dt
-            self.phase_s["execute"] += dt
-            rec = self.batches_by_node.setdefault(f"{batch.node_name}:{batch.graph_walk}", [0, 0, 0.0])
-            rec[0] += 1
-            rec[1] += len(batch.request_ids)
-            rec[2] += dt
-        return out
+                pend = eng.launch_batch(batch)
+            self.phase_s["execute"] += time.perf_counter() - t0
+        return pend
 
-    def _postprocess_batch(self, batch: NodeBatch, out: NodeOutput) -> None:
+    def _postprocess_batch(self, batch: NodeBatch, out: NodeOutput, fl: _Flight | None = None) -> None:
         if out.completion_event is not None:
             out.completion_event.synchronize()
+        spec = fl is not None and fl.speculative
         bad = self.engines.engine_for(batch.node_name).check_batch_status(out)
         if bad is not None:
             # a kernel of this batch left through its timeout exit: its output is partial, fail every request of it
@@ -380,15 +397,28 @@ class Worker:
             out.failed_requests = {rid: bad for rid in batch.request_ids}
             out.allocation_failed = False
         if out.allocation_failed:
-            self._handle_allocation_failure(batch, out)
+            if spec:
+                self._cancel_speculation(fl)        # nothing was launched: the loop goes on through the scheduler
+            else:
+                self._handle_allocation_failure(batch, out)
             return
         if out.failed_requests:
             self._fail_requests(out.failed_requests)
+        node = batch.node_name
         for rid in batch.request_ids:
             pri = self.requests.get((rid, batch.partitions[rid]))
             if pri is None:
                 continue
             pri.in_flight -= 1
+            if spec:
+                if pri.spec.get(node) != fl.fid:
+                    # the loop ended (stop token, budget, abort) in the iteration before: this row's work is dropped
+                    self.spec_stats["discarded_rows"] += 1
+                    if pri.remove_pending and pri.in_flight == 0:
+                        self._drop((rid, pri.partition_name))
+                    continue
+                del pri.spec[node]
+                pri.spec_marked.discard(node)
             if rid in out.failed_requests:
                 continue
             try:
@@ -427,6 +457,16 @@ class Worker:
             if e.conductor_new_token:
                 pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + max(1, iterations)
         comp = ws.complete(node, edges, iterations=iterations)
+        if node in pri.spec:
+            st = ws.nodes[node]
+            if ws.done or st.scope.done or st.done or not st.is_ready():
+                # the loop ended with this iteration: whatever the speculative launch computes for this request is
+                # dropped when that flight is read back
+                del pri.spec[node]
+                ws.rollback_speculation(node)
+            else:
+                ws.mark_running(node)       # iteration N+1 is already queued on the GPU, fed from the device
+                pri.spec_marked.add(node)
         self._send_outputs(pri, comp.route)
         self._refresh_ready(pri)
         if comp.walk_done:
@@ -557,16 +597,14 @@ class Worker:
         self._poll_stream_buffers()
         t3 = time.perf_counter()
         T["streams"] += t3 - t2
-        for eid, (fut, batch) in list(self._in_flight.items()):
-            if fut.done():
-                del self._in_flight[eid]
-                self._finish(batch, fut)
-                did = True
-                T["finish"] += time.perf_counter() - t3
-                t3 = time.perf_counter()
-        while len(self._in_flight) < self._max_in_flight or self.gpu_thread is None:
-            busy = {k for k in self.scheduler.ready if id(self.engines.engine_for(k[0])) in self._in_flight} \
-                if self._in_flight else None
+        if self._pipes:
+            did |= self._advance_pipes()
+            T["finish"] += time.perf_counter() - t3
+        while True:
+            # an engine with flights takes no other batch: its next one is either the speculative continuation or
+            # whatever the scheduler picks once the queue has drained
+            busy = {k for k in self.scheduler.ready if id(self.engines.engine_for(k[0])) in self._pipes} \
+                if self._pipes else None
             nxt = self.scheduler.get_next_batch(exclude=busy)
             if nxt is None:
                 break
@@ -580,27 +618,139 @@ class Worker:
                 for f in self.tp_followers:
                     self.comm.send(f, Message(WM.SCHEDULE_TP, ipc.ScheduleTPNode(node, walk, list(rkeys))))
             did = True
-            if self.gpu_thread is not None:
-                eid = id(self.engines.engine_for(node))
-                self._in_flight[eid] = (self.gpu_thread.submit(self._execute, batch), batch)
-            else:
-                self._finish(batch, None)
+            self._submit(batch)
+            if self.gpu_thread is None:
                 break
         if self.heartbeat_s and time.monotonic() - self._last_beat > self.heartbeat_s:
             self._last_beat = time.monotonic()
             self.comm.send(self.conductor_id, Message(CM.HEARTBEAT, ipc.SetupDone(self.worker_id)))
         return did
 
-    def _finish(self, batch: NodeBatch, fut) -> None:
+    # ------------------------------------------------------------------ flights
+    def _submit(self, batch: NodeBatch, speculative: bool = False, chain: int = 0) -> _Flight:
+        eng = self.engines.engine_for(batch.node_name)
+        self._next_fid += 1
+        fl = _Flight(self._next_fid, batch, eng, speculative=speculative, chain=chain, t_submit=time.perf_counter())
+        if self.gpu_thread is None:          # synchronous mode: launch, wait, read back
+            try:
+                fl.pending = self._launch(fl)
+            except Exception as e:  # noqa: BLE001
+                fl.error = e
+            self._finish(fl)
+            return fl
+        fl.fut = self.gpu_thread.submit(self._launch, fl)
+        self._pipes.setdefault(id(eng), deque()).append(fl)
+        return fl
+
+    def _advance_pipes(self) -> bool:
+        """Take finished launches, read back the batches whose results are there (in launch order per engine) and
+        queue speculative continuations."""
+        did = False
+        for eid in list(self._pipes):
+            pipe = self._pipes[eid]
+            for fl in pipe:
+                if fl.pending is None and fl.error is None and fl.fut.done():
+                    try:
+                        fl.pending = fl.fut.result()
+                    except Exception as e:  # noqa: BLE001
+                        fl.error = e
+            # the continuation is queued FIRST (the sooner it sits behind the running batch, the less the GPU can
+            # idle), then the batches whose results are there are read back
+            if self._spec_enabled and len(pipe) == 1 and pipe[0].pending is not None and not pipe[0].spec_tried:
+                head = pipe[0]
+                head.spec_tried = True
+                nb = self._build_speculative_batch(head)
+                if nb is not None:
+                    self.spec_stats["launched"] += 1
+                    self._submit(nb, speculative=True, chain=head.chain + 1)
+                    did = True
+            while pipe and (pipe[0].error is not None or (pipe[0].pending is not None and pipe[0].pending.ready())):
+                self._finish(pipe.popleft())
+                did = True
+            if not pipe:
+                del self._pipes[eid]
+        return did
+
+    def _build_speculative_batch(self, fl: _Flight) -> NodeBatch | None:
+        """The next iteration of ``fl``'s loop node for the same requests, to be queued while ``fl`` still runs.
+        None when the engine cannot continue from device-resident outputs, when some request may end its loop with
+        the iteration in flight, when the chain is long enough, or when other work waits for this engine (a chain
+        must not starve new requests: it is cut as soon as the scheduler holds anything else for the engine)."""
+        b, pend, eng = fl.batch, fl.pending, fl.engine
+        node, walk = b.node_name, b.graph_walk
+        if fl.chain >= self._max_chain or pend.planned is None or pend.out.failed_requests or pend.out.allocation_failed:
+            return None
+        if not eng.can_speculate(node, walk):
+            return None
+        for k in self.scheduler.ready:
+            if self.engines.engine_for(k[0]) is eng and self.scheduler._eligible(k):
+                return None
+        pris, remaining = [], []
+        for rid in b.request_ids:
+            pri = self.requests.get((rid, b.partitions[rid]))
+            if pri is None or pri.remove_pending or node in pri.spec or pri.fwd_info.graph_walk != walk:
+                return None
+            ws = pri.walk_state
+            st = ws.nodes.get(node)
+            if st is None or not st.running or not ws.can_speculate(node):
+                return None
+            left = st.scope.loop.max_iters - st.scope.curr_iter - pend.iterations
+            if left < 1:
+                return None
+            pris.append(pri)
+            remaining.append(left)
+        infos = {}
+        for pri, left in zip(pris, remaining):
+            pri.fwd_info.step_metadata = dict(pri.fwd_info.step_metadata or {}, _loop_remaining=left)
+            pri.walk_state.begin_speculation(node)
+            pri.in_flight += 1
+            pri.spec[node] = self._next_fid + 1          # the id _submit gives the flight
+            infos[pri.request_id] = pri.fwd_info
+        nb = NodeBatch(node, walk, list(b.request_ids), {rid: {} for rid in b.request_ids}, infos, speculative=True)
+        nb.partitions = dict(b.partitions)
+        return nb
+
+    def _cancel_speculation(self, fl: _Flight) -> None:
+        """A speculative launch that queued nothing (page reservation failed): hand its requests back to the normal
+        path."""
+        self.spec_stats["cancelled"] += 1
+        node = fl.batch.node_name
+        for rid in fl.batch.request_ids:
+            pri = self.requests.get((rid, fl.batch.partitions[rid]))
+            if pri is None:
+                continue
+            pri.in_flight -= 1
+            if pri.spec.get(node) == fl.fid:
+                del pri.spec[node]
+                pri.walk_state.rollback_speculation(node)
+                if node in pri.spec_marked:          # iteration N was read back meanwhile: N+1 goes to the scheduler
+                    pri.spec_marked.discard(node)
+                    pri.walk_state.nodes[node].running = False
+                    self._refresh_ready(pri)
+            if pri.remove_pending and pri.in_flight == 0:
+                self._drop((rid, pri.partition_name))
+
+    def _finish(self, fl: _Flight) -> None:
+        batch = fl.batch
         try:
-            out = fut.result() if fut is not None else self._execute(batch)
-            self._postprocess_batch(batch, out)
+            if fl.error is not None:
+                raise fl.error
+            out = fl.engine.collect_batch(fl.pending)
+            dt = time.perf_counter() - fl.t_submit
+            out.timings["execute_s"] = dt
+            rec = self.batches_by_node.setdefault(f"{batch.node_name}:{batch.graph_walk}", [0, 0, 0.0])
+            rec[0] += 1
+            rec[1] += len(batch.request_ids)
+            rec[2] += dt
+            self._postprocess_batch(batch, out, fl)
         except Exception as e:  # noqa: BLE001
-            log.error("worker %s: batch %s failed: %s\n%s", self.worker_id, batch.node_name, e, traceback.format_exc())
+            log.error("worker %s: batch %s failed: %s\n%s", self.worker_id, batch.node_name, e,
+                      "".join(traceback.format_exception(type(e), e, e.__traceback__)))
             for rid in batch.request_ids:
                 pri = self.requests.get((rid, batch.partitions[rid]))
                 if pri is not None:
                     pri.in_flight = max(0, pri.in_flight - 1)
+                    pri.spec.pop(batch.node_name, None)
             self._fail_requests({rid: f"{type(e).__name__}: {e}" for rid in batch.request_ids})
 
     def run(self) -> None:
@@ -619,9 +769,10 @@ class Worker:
     def _run_loop(self) -> None:
         self.comm.send(self.conductor_id, Message(CM.SETUP_DONE, ipc.SetupDone(self.worker_id)))
         while self.running:
-            if self._in_flight:
-                # batches are on the GPU threads: sleep on the mailbox in short slices instead of spinning on the GIL
-                self.step(block_s=0.0 if any(f.done() for f, _ in self._in_flight.values()) else 0.0005)
+            if self._pipes:
+                # batches are being launched or run on the GPU: sleep on the mailbox in short slices instead of
+                # spinning on the GIL that the launch thread needs
+                self.step(block_s=0.0003)
             else:
                 self.step(block_s=0.0 if self.scheduler.has_ready() else 0.02)
         self.shutdown()
@@ -630,9 +781,11 @@ class Worker:
         if self.gpu_thread is not None:
             self.gpu_thread.shutdown(wait=True)
         if os.environ.get("MSTAR_WORKER_STATS"):
-            log.warning("worker %s: loop iterations %d, host seconds by phase %s, batches (count, requests, seconds) %s",
+            log.warning("worker %s: loop iterations %d, host seconds by phase %s, batches (count, requests, seconds "
+                        "from submission to read-back) %s, speculation %s, engine phases %s",
                         self.worker_id, self.iterations, {k: round(v, 3) for k, v in self.phase_s.items()},
-                        {k: (v[0], v[1], round(v[2], 3)) for k, v in self.batches_by_node.items()})
+                        {k: (v[0], v[1], round(v[2], 3)) for k, v in self.batches_by_node.items()}, self.spec_stats,
+                        [{k: round(v, 3) for k, v in e.phase_s.items()} for e in self.engines.engines])
 
 
 def _rk(pri: PerRequestInfo) -> str:

@@ -23,12 +23,41 @@ def _tokens(burst, graphs, eos_ids=(), **mk):
                 assert "error" not in res, res
                 outs.append(b"".join(c.data for c in res["text"]).decode().split())
             eng = s.deployment.workers[0].engines.engine_for("LLM")
+            _tokens.spec = dict(s.deployment.workers[0].spec_stats)
             return outs, eng.graph_hits
         finally:
             s.shutdown()
     finally:
         os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
         os.environ.pop("MSTAR_DECODE_BURST", None)
+
+
+def test_speculative_bursts_give_the_same_tokens_and_drop_rows_past_a_stop():
+    """While burst N is on the device the worker queues burst N+1 for the same requests (its inputs are the ids that
+    N leaves in the engine's static buffer). Tokens must equal the unspeculated run; a request that meets its stop
+    token in burst N has its row of burst N+1 dropped."""
+    kw = dict(max_tokens=41, ignore_eos=True, temperature=0.8, top_p=0.9, repetition_penalty=1.1, seed=11)
+    os.environ["MSTAR_SPECULATE"] = "0"
+    try:
+        ref, _ = _tokens(4, True, **kw)
+        assert _tokens.spec["launched"] == 0
+    finally:
+        os.environ.pop("MSTAR_SPECULATE", None)
+    got, _ = _tokens(4, True, **kw)
+    assert _tokens.spec["launched"] > 0, _tokens.spec
+    assert got == ref and all(len(t) == 41 for t in got)
+    # stop tokens: greedy run, then declare a mid-sequence token of the first request the stop token
+    plain, _ = _tokens(1, True, max_tokens=30, ignore_eos=True, temperature=0.0)
+    stop = int(plain[0][9])
+    first = plain[0].index(str(stop))
+    out, _ = _tokens(3, True, eos_ids=[stop], max_tokens=30, temperature=0.0)
+    assert out[0] == plain[0][:first + 1]
+    os.environ["MSTAR_SPECULATE"] = "0"
+    try:
+        unspec, _ = _tokens(3, True, eos_ids=[stop], max_tokens=30, temperature=0.0)
+    finally:
+        os.environ.pop("MSTAR_SPECULATE", None)
+    assert out == unspec
 
 
 def test_burst_decoding_equals_single_step_decoding():
