@@ -4,8 +4,12 @@ stock single-GPU Orpheus placement through its own launcher and HTTP API, with s
 What this harness adds is data only, because the machine has no network: a Hugging Face cache directory that
 holds random-init checkpoints in the layouts the reference downloads (Llama-3.2-3B names in safetensors, the SNAC
 decoder's ``config.json`` + ``pytorch_model.bin`` created from the reference's own SNAC class, and a byte-level
-tokenizer). The server is started with ``python -m mstar.api_server.entrypoint`` and a copy of the reference's
-``configs/orpheus_colocated.yaml``; 64 concurrent requests stream audio over ``POST /generate``.
+tokenizer). The server is started with ``python -m mstar.api_server.entrypoint`` and the reference's
+``configs/orpheus_colocated.yaml`` (one GPU), or the same file with every rank of the box listed in both node groups
+(N GPUs: ranks of a node group without ``tp_size`` are data-parallel replicas in the reference,
+mstar/conductor/conductor.py:475-506); 64 concurrent requests per GPU stream audio over ``POST /generate``. The load
+generator is the one the other arm uses (``mstar_b200/bench/tts_client.py``: a plain HTTP client, no part of either
+server), with the same warm-up: one request, then a short round at full concurrency.
 
 Metric: decode tokens/s of the box = audio tokens produced by all requests inside the measurement window divided
 by the window's wall-clock length at the client (the server is a black box; 7 tokens per 2048 samples of 16-bit
@@ -22,7 +26,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -41,6 +44,14 @@ node_groups:
     ranks: [0]
     graph_walks: [snac_chunk]
 """
+
+
+def stock_yaml(n_gpus: int) -> str:
+    """The reference's colocated Orpheus placement, with every rank listed when the box has more than one GPU."""
+    if n_gpus <= 1:
+        return STOCK_COLOCATED_YAML
+    ranks = ", ".join(str(r) for r in range(n_gpus))
+    return STOCK_COLOCATED_YAML.replace("ranks: [0]", f"ranks: [{ranks}]")
 
 
 def _unavailable(why: str) -> dict:
@@ -134,53 +145,9 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-class _Stream(threading.Thread):
-    """One request: POST /generate (NDJSON stream), records the arrival time and size of every audio chunk."""
-
-    def __init__(self, url: str, text: str, max_tokens: int):
-        super().__init__(daemon=True)
-        self.url, self.text, self.max_tokens = url, text, max_tokens
-        self.t_submit = self.t_first = self.t_done = None
-        self.chunks: list[tuple[float, int]] = []      # (time, audio bytes)
-        self.error = None
-
-    def run(self):
-        import base64
-
-        import requests
-        try:
-            self.t_submit = time.perf_counter()
-            data = {"text": self.text, "output_modalities": "audio", "streaming": "true",
-                    "model_kwargs": json.dumps({"max_output_tokens": self.max_tokens, "ignore_eos": True,
-                                                "voice": "tara"})}
-            with requests.post(self.url, data=data, stream=True, timeout=1800) as r:
-                r.raise_for_status()
-                for line in r.iter_lines():
-                    if not line:
-                        continue
-                    try:
-                        msg = json.loads(line)
-                    except Exception:  # noqa: BLE001
-                        continue
-                    payload = msg.get("data") or msg.get("audio") or ""
-                    nbytes = len(base64.b64decode(payload)) if isinstance(payload, str) and payload else 0
-                    if msg.get("modality") == "audio" and nbytes:
-                        now = time.perf_counter()
-                        if self.t_first is None:
-                            self.t_first = now
-                        self.chunks.append((now, nbytes))
-            self.t_done = time.perf_counter()
-        except Exception as e:  # noqa: BLE001
-            self.error = f"{type(e).__name__}: {e}"
-            self.t_done = time.perf_counter()
-
-
 def run_reference(args) -> dict:
     if not os.path.isdir(os.path.join(REF, "mstar")):
         return _unavailable("reference is not installed under baseline/_ref")
-    if args.gpus != 1:
-        return _unavailable("the reference's stock Orpheus configs place one model instance (1 or 2 GPUs); its "
-                            "launcher has no data-parallel replica mode to scale the same workload to N GPUs")
     try:
         import torch
         if not torch.cuda.is_available():
@@ -195,7 +162,7 @@ def run_reference(args) -> dict:
         build_synthetic_cache(cache)
         cfg_path = os.path.join(work, "orpheus_colocated.yaml")
         with open(cfg_path, "w") as f:
-            f.write(STOCK_COLOCATED_YAML)
+            f.write(stock_yaml(args.gpus))
         port = _free_port()
         env = dict(os.environ, PYTHONPATH=REF + os.pathsep + os.environ.get("PYTHONPATH", ""), HF_HUB_OFFLINE="1",
                    TRANSFORMERS_OFFLINE="1", HF_HOME=cache, MASTER_ADDR="127.0.0.1")
@@ -218,48 +185,43 @@ def run_reference(args) -> dict:
             tail = open(log_path).read()[-600:]
             return _unavailable(f"reference server did not come up (exit {proc.poll()}): {tail}")
         url = f"http://127.0.0.1:{port}/generate"
+        sys.path.insert(0, os.path.dirname(HERE))
+        from bench import shared_config
+        from mstar_b200.bench.tts_client import run_streams, summarize
         C = args.concurrency if hasattr(args, "concurrency") else 64
+        N = max(1, args.gpus)
+        total = C * N
         W, K = max(3, args.warmup), args.steps
-        # a short warm-up request, then C concurrent streams long enough to hold the window open
-        w = _Stream(url, "warm up", 28 * 3)
-        w.start()
-        w.join(600)
-        if w.error or not w.chunks:
+        kw = {"ignore_eos": True, "voice": "tara"}
+        # the same warm-up as the other arm: one request, then a short round at full concurrency
+        w = run_streams(url, 1, dict(kw, max_output_tokens=28 * 3), text="warm up")
+        if w[0]["error"] or not w[0]["chunks"]:
             tail = open(log_path).read()[-600:]
-            return _unavailable(f"reference warm-up request failed: {w.error or 'no audio'}: {tail}")
-        # 1204 tokens = 172 audio frames per request: the mean context over the run (about 600 tokens) matches the
-        # steady state that the other arm of the benchmark prefills (prompt + U(0, 1200) generated tokens)
-        max_tokens = 1204
-        streams = [_Stream(url, f"request number {i} says hello", max_tokens) for i in range(C)]
-        for s in streams:
-            s.start()
-        for s in streams:
-            s.join(1800)
-        bad = [s.error for s in streams if s.error or not s.chunks]
-        if bad:
-            return _unavailable(f"{len(bad)} of {C} reference requests failed: {bad[0]}")
-        t_open = max(s.t_first for s in streams)
-        t_close = min(s.t_done for s in streams)
-        if t_close <= t_open:
-            return _unavailable("measurement window is empty (requests did not overlap)")
+            return _unavailable(f"reference warm-up request failed: {w[0]['error'] or 'no audio'}: {tail}")
+        run_streams(url, total, dict(kw, max_output_tokens=56), text="warm {i}")
+        # 1204 tokens = 172 audio frames per request
+        max_tokens = getattr(args, "gen_tokens", 1204)
+        recs = run_streams(url, total, dict(kw, max_output_tokens=max_tokens))
         # bytes per sample from the chunk sizes (16-bit PCM unless the server sends float32)
-        nbytes = sum(b for s in streams for (t, b) in s.chunks if t_open < t <= t_close)
-        sample_bytes = 4 if all(b % 8192 == 0 for s in streams for (_, b) in s.chunks) else 2
-        tokens = nbytes / sample_bytes / 2048 * 7
-        dt = t_close - t_open
-        ttft = statistics.median((s.t_first - s.t_submit) * 1e3 for s in streams)
-        value = tokens / dt
-        return {"metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-                "ms_per_step": round(1e3 * C / value, 4), "higher_is_better": True, "scaling": "weak",
+        sample_bytes = 4 if all(b % 8192 == 0 for r in recs for (_, b) in r["chunks"]) else 2
+        try:
+            sm = summarize(recs, total, sample_bytes)
+        except RuntimeError as e:
+            tail = open(log_path).read()[-400:]
+            return _unavailable(f"{e} {tail}")
+        value = sm["tokens_per_s"]
+        return {"metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": N, "steps": K, "warmup": W,
+                "ms_per_step": round(1e3 * total / value, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "impl": "reference",
                 "data": "synthetic (random-init weights N(0,0.02) in the reference's checkpoint layout, byte tokenizer)",
-                "config": {"model": "orpheus-3b (reference stock configs/orpheus_colocated.yaml)", "global_batch": C,
-                           "seq_len": f"short prompt + up to {max_tokens} generated", "parallelism": "dp1",
-                           "timing": "wall clock at the HTTP client over the window in which all requests decode"},
-                "ttft_p50_ms": round(ttft, 2),
+                "config": dict(shared_config(N, C), placement="reference configs/orpheus_colocated.yaml"
+                               + (f" with ranks 0..{N - 1} in both node groups" if N > 1 else ""),
+                               timing="wall clock at the HTTP clients over the window in which all requests decode"),
+                "ttft_p50_ms": round(sm["ttfa_p50_ms"], 2),
                 "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": None,
-                        "d2h_bytes_per_step": None},
-                "window_s": round(dt, 3)}
+                        "d2h_bytes_per_step": None, "ttfa_p50_ms": round(sm["ttfa_p50_ms"], 2),
+                        "ttfa_p99_ms": round(sm["ttfa_p99_ms"], 2)},
+                "window_s": round(sm["window_s"], 3)}
     except Exception as e:  # noqa: BLE001
         tail = ""
         try:

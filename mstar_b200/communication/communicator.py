@@ -112,6 +112,8 @@ class ShmMeshCommunicator(BaseCommunicator):
         L.mstar_mesh_send.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_ulonglong]
         L.mstar_mesh_recv.restype = ctypes.c_longlong
         L.mstar_mesh_recv.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_ulonglong, ctypes.c_int]
+        L.mstar_mesh_recv_us.restype = ctypes.c_longlong
+        L.mstar_mesh_recv_us.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_ulonglong, ctypes.c_longlong]
         L.mstar_mesh_peek_size.restype = ctypes.c_longlong
         L.mstar_mesh_peek_size.argtypes = [ctypes.c_void_p]
         L.mstar_mesh_wake.argtypes = [ctypes.c_void_p]
@@ -136,8 +138,8 @@ class ShmMeshCommunicator(BaseCommunicator):
                 continue
             raise RuntimeError(f"mesh: send to {dst} failed (rc={rc})")
 
-    def _pop(self, timeout_ms: int) -> Message | None:
-        n = self.lib.mstar_mesh_recv(self.h, self._buf, len(self._buf), timeout_ms)
+    def _pop(self, timeout_us: int) -> Message | None:
+        n = self.lib.mstar_mesh_recv_us(self.h, self._buf, len(self._buf), timeout_us)
         if n == -3:     # buffer too small
             need = self.lib.mstar_mesh_peek_size(self.h)
             self._buf = ctypes.create_string_buffer(int(max(need, len(self._buf) * 2)))
@@ -155,7 +157,7 @@ class ShmMeshCommunicator(BaseCommunicator):
             out.append(m)
 
     def recv_or_wake(self, timeout_s: float = 0.05) -> list[Message]:
-        m = self._pop(int(timeout_s * 1000))
+        m = self._pop(int(timeout_s * 1e6))
         return ([m] if m is not None else []) + self.drain()
 
     def wake(self) -> None:

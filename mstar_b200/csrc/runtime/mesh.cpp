@@ -202,20 +202,26 @@ static long long try_pop(Mesh* m, char* out, unsigned long long cap_out, bool pe
     }
 }
 
-// Returns the payload length, 0 when nothing arrived within timeout_ms (0 = poll), -3 when `cap` is too small.
-MSTAR_RT_API long long mstar_mesh_recv(void* handle, char* out, unsigned long long cap, int timeout_ms) {
+// Returns the payload length, 0 when nothing arrived within timeout_us microseconds (0 = poll), -3 when `cap` is
+// too small. Sub-millisecond waits matter: a worker whose batches are on the GPU sleeps here in slices of a few
+// hundred microseconds, and a wait rounded down to zero would turn that into a spin.
+MSTAR_RT_API long long mstar_mesh_recv_us(void* handle, char* out, unsigned long long cap, long long timeout_us) {
     Mesh* m = static_cast<Mesh*>(handle);
     if (!m) return -1;
     long long n = try_pop(m, out, cap, false);
-    if (n != 0 || timeout_ms <= 0) return n;
+    if (n != 0 || timeout_us <= 0) return n;
     const uint32_t seen = m->own.hdr->futex_word.load(std::memory_order_acquire);
     n = try_pop(m, out, cap, false);
     if (n != 0) return n;
     timespec ts;
-    ts.tv_sec = timeout_ms / 1000;
-    ts.tv_nsec = (long)(timeout_ms % 1000) * 1000000L;
+    ts.tv_sec = (time_t)(timeout_us / 1000000);
+    ts.tv_nsec = (long)(timeout_us % 1000000) * 1000L;
     futex(&m->own.hdr->futex_word, FUTEX_WAIT, seen, &ts);
     return try_pop(m, out, cap, false);
+}
+
+MSTAR_RT_API long long mstar_mesh_recv(void* handle, char* out, unsigned long long cap, int timeout_ms) {
+    return mstar_mesh_recv_us(handle, out, cap, (long long)timeout_ms * 1000);
 }
 
 MSTAR_RT_API long long mstar_mesh_peek_size(void* handle) {

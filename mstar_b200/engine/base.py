@@ -10,6 +10,8 @@ from dataclasses import dataclass, field
 
 import torch
 
+from ..utils import io_counters
+
 
 @dataclass
 class NodeBatch:
@@ -156,6 +158,7 @@ class BaseEngine:
             self._status_i = (self._status_i + 1) % len(self._status_ring)
             out.status_host = self._status_ring[self._status_i]
             _lib.status_copy_async(out.status_host)
+            io_counters.add_d2h(16)
             ev = torch.cuda.Event()
             ev.record()
             out.completion_event = ev

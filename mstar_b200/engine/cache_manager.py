@@ -21,6 +21,7 @@ import torch
 
 from ..ops import attention as attn_ops
 from ..ops import elementwise as ew_ops
+from ..utils import io_counters
 from .kv_store import KVCacheConfig, PagedAllocationManager
 
 
@@ -84,6 +85,7 @@ class _PlanBuffers:
 
     def upload(self, used: int | None = None) -> None:
         self.dev.copy_(self.hosts[self.cur], non_blocking=True)
+        io_counters.add_h2d(self.total * 4)
         if self.cuda:
             ev = self.events[self.cur] or torch.cuda.Event()
             ev.record()

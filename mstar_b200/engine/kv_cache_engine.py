@@ -20,6 +20,7 @@ from ..models.submodule_base import BATCHED_LOGITS, ModelInputsFromEngine
 from ..ops import _lib
 from ..ops import attention as attn_ops
 from ..ops.sampling import SamplerState, SamplingConfig
+from ..utils import io_counters
 from .base import BaseEngine, NodeBatch, NodeOutput, PendingBatch, PreparedBatch
 from .cache_manager import BatchedCacheManager
 from .kv_store import AllocationFailedError, KVCacheConfig
@@ -44,6 +45,9 @@ class KVCacheEngine(BaseEngine):
                            for _ in range(4)]
         self._host_i = 0
         self._last_graph_key = None       # (node, walk, bucket, request ids) of the last captured-step execution
+        # device time of the captured decode steps (CUDA events around each burst), kept only when statistics are on
+        self._time_steps = _cuda and bool(os.environ.get("MSTAR_WORKER_STATS") or os.environ.get("MSTAR_WORKER_STATS_DIR"))
+        self.decode_device_ms, self.decode_steps = 0.0, 0
         self.kv_config = kv_config
         self.cache = BatchedCacheManager(kv_config, device, max_batch=max_batch, max_tokens=max_tokens + max_batch,
                                          n_pos_axes=n_pos_axes)
@@ -57,6 +61,7 @@ class KVCacheEngine(BaseEngine):
         if self.emulate_graphs and use_cuda_graphs is not False:
             self.use_graphs = True
         self._graphs: dict[tuple, tuple] = {}
+        self.launches_per_graph: dict[tuple, int] = {}     # this library's kernels recorded in each captured step
         self._static_ids = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
         self._static_tok = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
         self.graph_hits = 0
@@ -246,6 +251,10 @@ class KVCacheEngine(BaseEngine):
                     entry = self._capture(key, sub, b.graph_walk, ei, planned)
                 self._last_graph_key = run_key
                 k = getattr(planned, "burst", 1)
+                evs = None
+                if self._time_steps:
+                    evs = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    evs[0].record()
                 for j in range(k):
                     entry[0].replay()           # the graph leaves the plan advanced and the sampled ids as next input
                     self.graph_hits += 1
@@ -254,16 +263,21 @@ class KVCacheEngine(BaseEngine):
                 tokens = self._static_tok[:B].clone()
                 raw = {"tokens": tokens, "extra": {k_: v[:B].clone() if isinstance(v, torch.Tensor) else v
                                                    for k_, v in entry[1].items()}}
+                if evs is not None:
+                    evs[1].record()
+                    raw["timing"] = (evs, k)
                 self._host_i = (self._host_i + 1) % len(self._host_ring)
                 hb = self._host_ring[self._host_i]
                 if k > 1:
                     raw["burst"] = self._burst_buf[:k, :B].t().contiguous()      # [B, k]
                     hb[:k, :B].copy_(self._burst_buf[:k, :B], non_blocking=True)
                     raw["burst_host"] = hb[:k, :B]
+                    io_counters.add_d2h(k * B * 8)
                     self.cache.advance_seq_lens(ctx, counts=[k] * len(ctx.q_lens))
                     return raw
                 hb[0, :B].copy_(tokens, non_blocking=True)
                 raw["tokens_host"] = hb[0, :B]
+                io_counters.add_d2h(B * 8)
             else:
                 self._last_graph_key = None
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
@@ -336,8 +350,11 @@ class KVCacheEngine(BaseEngine):
                 body()
             s.synchronize()
             g = torch.cuda.CUDAGraph()
+            from ..ops import _counters
+            c0 = _counters.get()
             with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
                 extra = body()
+            self.launches_per_graph[key] = _counters.get() - c0
         torch.cuda.current_stream().wait_stream(s)
         self.sampler.offset.copy_(saved_off)
         if saved_seen is not None:
@@ -354,6 +371,10 @@ class KVCacheEngine(BaseEngine):
         sub = self.submodules[b.node_name]
         tokens = raw.get("tokens")
         burst = raw.get("burst")
+        if "timing" in raw:
+            (e0, e1), k_ = raw["timing"]
+            self.decode_device_ms += e0.elapsed_time(e1)
+            self.decode_steps += k_
         # the ids were copied to pinned host memory behind the last replay (captured path): plain reads here
         burst_host = raw["burst_host"].t().tolist() if burst is not None else None
         host_tokens = None

@@ -22,6 +22,7 @@ from .decoder import DecoderConfig, DecoderLM
 from .llm_common import DecoderSubmodule, LMStateMachine, lm_walks
 from .orpheus_config import orpheus_3b_config
 from .submodule_base import NodeSubmodule
+from ..utils import io_counters
 
 CUSTOM_TOKEN_BASE = 128256
 END_TOKEN_IDS = (128009, 128260, 128261, 128257, 128258)
@@ -79,6 +80,7 @@ class SnacSubmodule(NodeSubmodule):
                 if Bp != B:
                     stage[B:] = stage[0]
                 tk = stage.to(self.device, non_blocking=True)
+                io_counters.add_h2d(stage.numel() * 8)
                 return runner.run(("snac", tuple(tk.shape)), fn, [tk])[:B]
             return fn(tokens.to(self.device))
 
@@ -117,6 +119,7 @@ class SnacSubmodule(NodeSubmodule):
                 rows = 64 if len(idx) <= 64 else len(idx)
                 host = self._pinned(("wav", rows, wav.shape[1]), (rows, wav.shape[1]), torch.float32)
                 host[:len(idx)].copy_(wav, non_blocking=True)
+                io_counters.add_d2h(wav.numel() * 4)
             else:
                 host = wav
             for row, i in enumerate(idx):

@@ -777,9 +777,33 @@ class Worker:
                 self.step(block_s=0.0 if self.scheduler.has_ready() else 0.02)
         self.shutdown()
 
+    def stats(self) -> dict:
+        """Counters of this worker: host seconds by loop phase, batches per (node, walk), speculation, engine phases,
+        bytes copied between host and device, CUDA-graph replays."""
+        from ..utils import io_counters
+        return {"worker": self.worker_id, "iterations": self.iterations,
+                "phase_s": {k: round(v, 4) for k, v in self.phase_s.items()},
+                "batches": {k: {"count": v[0], "requests": v[1], "seconds": round(v[2], 4)}
+                            for k, v in self.batches_by_node.items()},
+                "speculation": dict(self.spec_stats),
+                "engines": [{"nodes": list(e.node_names), "phase_s": {k: round(v, 4) for k, v in e.phase_s.items()},
+                             "graph_replays": getattr(e, "graph_hits", 0),
+                             "decode_device_ms": round(getattr(e, "decode_device_ms", 0.0), 3),
+                             "decode_steps": getattr(e, "decode_steps", 0)} for e in self.engines.engines],
+                **io_counters.snapshot()}
+
     def shutdown(self) -> None:
         if self.gpu_thread is not None:
             self.gpu_thread.shutdown(wait=True)
+        stats_dir = os.environ.get("MSTAR_WORKER_STATS_DIR")
+        if stats_dir:
+            import json
+            try:
+                os.makedirs(stats_dir, exist_ok=True)
+                with open(os.path.join(stats_dir, f"{self.worker_id}.json"), "w") as f:
+                    json.dump(self.stats(), f)
+            except Exception:  # noqa: BLE001
+                log.exception("worker %s: could not write its stats", self.worker_id)
         if os.environ.get("MSTAR_WORKER_STATS"):
             log.warning("worker %s: loop iterations %d, host seconds by phase %s, batches (count, requests, seconds "
                         "from submission to read-back) %s, speculation %s, engine phases %s",
