@@ -47,7 +47,7 @@ def deployment_config(n_gpus: int, concurrency: int, *, small: bool = False, cod
 
 def run_serving(n_gpus: int = 1, concurrency: int = 64, tokens: int = 1204, *, small: bool = False,
                 uvicorn_frontend: bool = False, in_process: bool = False, codec_dtype: str = "float32", tp: int = 1,
-                warm_tokens: int = 56) -> dict:
+                warm_tokens: int = 56, trace_out: str | None = None) -> dict:
     """Start the deployment, warm it up (one request, then a short round at full concurrency that captures every
     batch bucket), run the measured round and shut down. Returns the summary with the workers' own counters."""
     from ..api_server.app import create_app
@@ -55,6 +55,8 @@ def run_serving(n_gpus: int = 1, concurrency: int = 64, tokens: int = 1204, *, s
     total = concurrency * max(1, n_gpus // tp)
     stats_dir = tempfile.mkdtemp(prefix="mstar_stats_")
     os.environ["MSTAR_WORKER_STATS_DIR"] = stats_dir
+    if trace_out:
+        os.environ["MSTAR_TRACE_WORKER"] = "1"
     cfg = deployment_config(n_gpus, concurrency, small=small, codec_dtype=codec_dtype, tp=tp)
     out = {"bench": "serve_tts", "n_gpus": n_gpus, "concurrency": total, "tokens_per_request": tokens,
            "frontend": "uvicorn" if uvicorn_frontend else "mstar-server", "multi_process": not in_process,
@@ -85,6 +87,9 @@ def run_serving(n_gpus: int = 1, concurrency: int = 64, tokens: int = 1204, *, s
             raise RuntimeError(f"warm-up failed: {w[0]['error'] or 'no audio'}")
         run_streams(url, total, dict(kw, max_tokens=warm_tokens), text="warm {i}")
         recs = run_streams(url, total, dict(kw, max_tokens=tokens))
+        if trace_out:
+            out["client"] = [{"t_submit": r["t_submit"], "t_first": r["t_first"], "t_done": r["t_done"],
+                              "n_chunks": len(r["chunks"])} for r in recs]
         s = summarize(recs, total)
         out.update(tokens_per_s=round(s["tokens_per_s"], 1), window_s=round(s["window_s"], 3),
                    ttfa_p50_ms=round(s["ttfa_p50_ms"], 1), ttfa_p99_ms=round(s["ttfa_p99_ms"], 1),
@@ -108,6 +113,13 @@ def run_serving(n_gpus: int = 1, concurrency: int = 64, tokens: int = 1204, *, s
             except Exception:  # noqa: BLE001
                 pass
     shutil.rmtree(stats_dir, ignore_errors=True)
+    if trace_out:
+        os.environ.pop("MSTAR_TRACE_WORKER", None)
+        with open(trace_out, "w") as f:
+            json.dump(out, f)
+        for w_ in out.get("workers", []):
+            w_.pop("trace", None)
+        out.pop("client", None)
     return out
 
 
@@ -121,9 +133,11 @@ def main():
     ap.add_argument("--uvicorn", action="store_true", help="FastAPI / uvicorn frontend instead of mstar-server")
     ap.add_argument("--in-process", action="store_true", help="conductor and workers as threads of this process")
     ap.add_argument("--codec-dtype", default="float32", choices=["float32", "bfloat16"])
+    ap.add_argument("--trace-out", default=None, help="write the workers' batch timeline and the clients' times here")
     a = ap.parse_args()
     print(json.dumps(run_serving(a.gpus, a.concurrency, a.tokens, small=a.small, uvicorn_frontend=a.uvicorn,
-                                 in_process=a.in_process, codec_dtype=a.codec_dtype, tp=a.tp)))
+                                 in_process=a.in_process, codec_dtype=a.codec_dtype, tp=a.tp,
+                                 trace_out=a.trace_out)))
 
 
 if __name__ == "__main__":

@@ -26,6 +26,10 @@ class MicroScheduler:
         self._tp_queue: deque = deque()          # leader decisions waiting to be replayed
         self.node_limits: dict[str, int] = {}
         self.limit_fn = None                      # optional (node, walk) -> largest batch the node accepts
+        # optional (node, walk, ready request ids, seconds since the first of them became ready) -> True to hold the
+        # batch back a little longer so that requests about to become ready join it
+        self.defer_fn = None
+        self._first_ready: dict[tuple[str, str], float] = {}
 
     # ---- bookkeeping ----
     def mark_ready(self, node: str, walk: str, request_id: str) -> None:
@@ -33,6 +37,8 @@ class MicroScheduler:
         if key not in self.ready:
             self.ready[key] = OrderedDict()
             self._rr.append(key)
+        if not self.ready[key]:
+            self._first_ready[key] = time.monotonic()
         self.ready[key][request_id] = None
 
     def unmark(self, node: str, walk: str, request_id: str) -> None:
@@ -81,12 +87,17 @@ class MicroScheduler:
             rids = self._eligible(key)
             if not rids:
                 continue
+            if self.defer_fn is not None and len(rids) < self.max_batch_size and self.defer_fn(
+                    key[0], key[1], rids, time.monotonic() - self._first_ready.get(key, 0.0)):
+                continue
             limit = min(self.max_batch_size, self.node_limits.get(key[0], self.max_batch_size))
             if self.limit_fn is not None:
                 limit = max(1, min(limit, int(self.limit_fn(key[0], key[1]))))
             rids = rids[:limit]
             for r in rids:
                 self.ready[key].pop(r, None)
+            if self.ready[key]:
+                self._first_ready[key] = time.monotonic()
             if self.policy == "round_robin":
                 self._rr.remove(key)
                 self._rr.append(key)

@@ -54,7 +54,7 @@ class PerRequestInfo:
     in_flight: int = 0
     remove_pending: bool = False
     kv_wait: set = field(default_factory=set)      # KV nodes whose pages are still on their way from another process
-    spec: dict = field(default_factory=dict)       # node -> id of the speculative flight that runs its NEXT iteration
+    spec: dict = field(default_factory=dict)       # node -> ids of the speculative flights that run its NEXT iterations
     spec_marked: set = field(default_factory=set)  # nodes marked running on behalf of such a flight
     t_start: float = field(default_factory=time.perf_counter)
     timings: dict = field(default_factory=dict)
@@ -90,6 +90,15 @@ class Worker:
         self.is_tp_follower = is_tp_follower
         self.scheduler = MicroScheduler(max_batch_size=max_batch_size, is_tp_follower=is_tp_follower)
         self.scheduler.limit_fn = self._node_batch_limit
+        self.scheduler.defer_fn = self._defer_batch
+        # batch gathering: a batch is held back for a moment while requests that would join it are still on the GPU in
+        # this worker (their next input is about to exist) or while new requests are still arriving in a burst;
+        # without it two groups of streams that got out of step keep alternating as two half batches for ever
+        self._gather_running_s = float(os.environ.get("MSTAR_GATHER_RUNNING_MS", "60")) / 1e3
+        self._gather_arrival_s = float(os.environ.get("MSTAR_GATHER_ARRIVAL_MS", "4")) / 1e3
+        self._last_arrival = 0.0
+        self._by_walk_node: dict[tuple[str, str], dict] = {}       # (node, walk) -> live request states that run it
+        self.trace = [] if os.environ.get("MSTAR_TRACE_WORKER") else None
         self.walks = model.get_graph_walk_graphs()
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
@@ -161,6 +170,38 @@ class Worker:
         except Exception:  # noqa: BLE001
             return 1 << 30
 
+    def _defer_batch(self, node: str, walk: str, rids: list, waited_s: float) -> bool:
+        """Hold this batch back? Yes while (a) requests are still arriving in a burst (a few milliseconds), or (b)
+        other live requests of the same walk will need this node too and are on the GPU right now, in this node or in
+        the node that feeds it (bounded by the gather window)."""
+        now = time.monotonic()
+        if waited_s < self._gather_arrival_s and now - self._last_arrival < 0.0015:
+            return True
+        if waited_s >= self._gather_running_s:
+            return False
+        have = set(rids)
+        for (rid, part), pri in self.requests.items():
+            if pri.in_flight <= 0 or pri.fwd_info.graph_walk != walk or f"{rid}|{part}" in have:
+                continue
+            st = pri.walk_state.nodes.get(node)
+            if st is not None and not st.scope.done and (st.running or not st.done):
+                return True
+        if self.topology is not None and self._streaming_requests:
+            # stream consumers: their producers run in another partition's request state of the same request
+            for (rid, part) in self._streaming_requests:
+                if f"{rid}|{part}" in have:
+                    continue
+                pri = self.requests.get((rid, part))
+                if pri is None or pri.fwd_info.graph_walk != walk or node not in pri.walk_state.nodes:
+                    continue
+                if pri.walk_state.nodes[node].scope.done:
+                    continue
+                for c in self.topology.incoming(part):
+                    src = self.requests.get((rid, c.from_partition))
+                    if src is not None and src.in_flight > 0:
+                        return True
+        return False
+
     def _section_for(self, walk: str):
         sec = self.walks.get(walk)
         if sec is None:
@@ -199,6 +240,9 @@ class Worker:
             pri.persist = old.persist
         pri.kv_wait = remote_kv
         self.requests[key] = pri
+        self._last_arrival = time.monotonic()
+        if self.trace is not None:
+            self.trace.append((time.monotonic(), "new_request", info.graph_walk, b.request_id))
         self._setup_streams(pri)
         for e in b.initial_inputs:
             self._ingest(pri, e)
@@ -411,13 +455,13 @@ class Worker:
                 continue
             pri.in_flight -= 1
             if spec:
-                if pri.spec.get(node) != fl.fid:
-                    # the loop ended (stop token, budget, abort) in the iteration before: this row's work is dropped
+                if fl.fid not in pri.spec.get(node, ()):
+                    # the loop ended (stop token, budget, abort) in an iteration before: this row's work is dropped
                     self.spec_stats["discarded_rows"] += 1
                     if pri.remove_pending and pri.in_flight == 0:
                         self._drop((rid, pri.partition_name))
                     continue
-                del pri.spec[node]
+                pri.spec[node].remove(fl.fid)
                 pri.spec_marked.discard(node)
             if rid in out.failed_requests:
                 continue
@@ -457,12 +501,12 @@ class Worker:
             if e.conductor_new_token:
                 pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + max(1, iterations)
         comp = ws.complete(node, edges, iterations=iterations)
-        if node in pri.spec:
+        if pri.spec.get(node):
             st = ws.nodes[node]
             if ws.done or st.scope.done or st.done or not st.is_ready():
-                # the loop ended with this iteration: whatever the speculative launch computes for this request is
-                # dropped when that flight is read back
-                del pri.spec[node]
+                # the loop ended with this iteration: whatever the speculative launches compute for this request is
+                # dropped when those flights are read back
+                pri.spec[node] = []
                 ws.rollback_speculation(node)
             else:
                 ws.mark_running(node)       # iteration N+1 is already queued on the GPU, fed from the device
@@ -631,6 +675,9 @@ class Worker:
         eng = self.engines.engine_for(batch.node_name)
         self._next_fid += 1
         fl = _Flight(self._next_fid, batch, eng, speculative=speculative, chain=chain, t_submit=time.perf_counter())
+        if self.trace is not None:
+            self.trace.append((time.monotonic(), "submit", f"{batch.node_name}:{batch.graph_walk}", len(batch.request_ids),
+                               int(speculative), fl.fid))
         if self.gpu_thread is None:          # synchronous mode: launch, wait, read back
             try:
                 fl.pending = self._launch(fl)
@@ -688,8 +735,10 @@ class Worker:
         pris, remaining = [], []
         for rid in b.request_ids:
             pri = self.requests.get((rid, b.partitions[rid]))
-            if pri is None or pri.remove_pending or node in pri.spec or pri.fwd_info.graph_walk != walk:
+            if pri is None or pri.remove_pending or pri.fwd_info.graph_walk != walk:
                 return None
+            if fl.speculative and fl.fid not in pri.spec.get(node, ()):
+                return None              # this request left the loop: the chain ends here
             ws = pri.walk_state
             st = ws.nodes.get(node)
             if st is None or not st.running or not ws.can_speculate(node):
@@ -704,7 +753,7 @@ class Worker:
             pri.fwd_info.step_metadata = dict(pri.fwd_info.step_metadata or {}, _loop_remaining=left)
             pri.walk_state.begin_speculation(node)
             pri.in_flight += 1
-            pri.spec[node] = self._next_fid + 1          # the id _submit gives the flight
+            pri.spec.setdefault(node, []).append(self._next_fid + 1)      # the id _submit gives the flight
             infos[pri.request_id] = pri.fwd_info
         nb = NodeBatch(node, walk, list(b.request_ids), {rid: {} for rid in b.request_ids}, infos, speculative=True)
         nb.partitions = dict(b.partitions)
@@ -720,8 +769,8 @@ class Worker:
             if pri is None:
                 continue
             pri.in_flight -= 1
-            if pri.spec.get(node) == fl.fid:
-                del pri.spec[node]
+            if fl.fid in pri.spec.get(node, ()):
+                pri.spec[node].remove(fl.fid)
                 pri.walk_state.rollback_speculation(node)
                 if node in pri.spec_marked:          # iteration N was read back meanwhile: N+1 goes to the scheduler
                     pri.spec_marked.discard(node)
@@ -737,6 +786,9 @@ class Worker:
                 raise fl.error
             out = fl.engine.collect_batch(fl.pending)
             dt = time.perf_counter() - fl.t_submit
+            if self.trace is not None:
+                self.trace.append((time.monotonic(), "collect", f"{batch.node_name}:{batch.graph_walk}",
+                                   len(batch.request_ids), int(fl.speculative), fl.fid))
             out.timings["execute_s"] = dt
             rec = self.batches_by_node.setdefault(f"{batch.node_name}:{batch.graph_walk}", [0, 0, 0.0])
             rec[0] += 1
@@ -750,7 +802,8 @@ class Worker:
                 pri = self.requests.get((rid, batch.partitions[rid]))
                 if pri is not None:
                     pri.in_flight = max(0, pri.in_flight - 1)
-                    pri.spec.pop(batch.node_name, None)
+                    if fl.fid in pri.spec.get(batch.node_name, ()):
+                        pri.spec[batch.node_name].remove(fl.fid)
             self._fail_requests({rid: f"{type(e).__name__}: {e}" for rid in batch.request_ids})
 
     def run(self) -> None:
@@ -790,6 +843,7 @@ class Worker:
                              "graph_replays": getattr(e, "graph_hits", 0),
                              "decode_device_ms": round(getattr(e, "decode_device_ms", 0.0), 3),
                              "decode_steps": getattr(e, "decode_steps", 0)} for e in self.engines.engines],
+                **({"trace": self.trace} if self.trace is not None else {}),
                 **io_counters.snapshot()}
 
     def shutdown(self) -> None:
