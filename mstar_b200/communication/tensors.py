@@ -18,7 +18,7 @@ import uuid as _uuid
 
 import torch
 
-from ..graph.ir import TensorPointerInfo
+from ..graph.ir import TensorPointerInfo, fast_uid
 from .arena import ShmArena, ShmArenaReader, dtype_from_name, dtype_name
 
 # process-wide registry of stores, so that entities living in one process hand tensors over by reference
@@ -37,7 +37,7 @@ class TensorStore:
         self._lock = threading.Lock()
 
     def put(self, request_id: str, t: torch.Tensor, uuid: str | None = None, refs: int = 1, persist: bool = False) -> str:
-        uuid = uuid or _uuid.uuid4().hex
+        uuid = uuid or fast_uid()
         with self._lock:
             self._t[uuid] = t
             self._ref[uuid] = refs
@@ -127,6 +127,9 @@ class TensorCommunicationManager:
         self._reader: ShmArenaReader | None = None
         self.tx_bytes = 0
         self.rx_bytes = 0
+        # per-transfer records feed the request profile; they are kept only while a profile is being collected
+        # (log_transfers), never on the plain serving path, where they would grow with every chunk sent
+        self.log_transfers = False
         self.tx_log: list[dict] = []
         self.rx_log: list[dict] = []
         with _PROCESS_LOCK:
@@ -171,7 +174,8 @@ class TensorCommunicationManager:
             out.shm_segment = f"{self._arena.base_name}#{seg}"
             out.shm_offset = off
         self.tx_bytes += info.nbytes
-        self.tx_log.append(dict(uuid=info.uuid, nbytes=info.nbytes, dst=dst_entity))
+        if self.log_transfers:
+            self.tx_log.append(dict(uuid=info.uuid, nbytes=info.nbytes, dst=dst_entity))
         return out
 
     # ---- consumer side ----
@@ -192,7 +196,8 @@ class TensorCommunicationManager:
             else:
                 raise KeyError(f"tensor {info.uuid} from {info.source_entity} is not reachable from {self.entity_id}")
             self.rx_bytes += info.nbytes
-            self.rx_log.append(dict(uuid=info.uuid, nbytes=info.nbytes, src=info.source_entity))
+            if self.log_transfers:
+                self.rx_log.append(dict(uuid=info.uuid, nbytes=info.nbytes, src=info.source_entity))
         if info.offset or info.source_tp_size > 1:
             pass    # sharded reads are resolved by parallel.sharding before the descriptor reaches this point
         if t.device != device:

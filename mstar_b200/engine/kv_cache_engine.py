@@ -376,38 +376,45 @@ class KVCacheEngine(BaseEngine):
             self.decode_device_ms += e0.elapsed_time(e1)
             self.decode_steps += k_
         # the ids were copied to pinned host memory behind the last replay (captured path): plain reads here
-        burst_host = raw["burst_host"].t().tolist() if burst is not None else None
+        burst_t = raw["burst_host"].t().contiguous() if burst is not None else None      # [B, k] host copy
+        burst_host = burst_t.tolist() if burst_t is not None else None
         host_tokens = None
         if tokens is not None and burst is None:
             host_tokens = raw["tokens_host"].tolist() if "tokens_host" in raw else tokens.tolist()
+        extra = raw.get("extra", {})
+        nreq = len(planned.request_ids)
+        per_row = {k: v for k, v in extra.items() if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == nreq}
         for i, (rid, ni) in enumerate(zip(planned.request_ids, planned.node_inputs)):
             try:
+                fi = b.fwd_infos[rid]
                 if "per_request" in raw:
                     r = dict(raw["per_request"][i])
+                elif per_row:
+                    r = {k: (per_row[k][i] if k in per_row else v) for k, v in extra.items()}
                 else:
-                    r = {k: (v[i] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == len(planned.request_ids) else v)
-                         for k, v in raw.get("extra", {}).items()}
+                    r = dict(extra)
                 stops = None
                 if burst_host is not None:
-                    toks, n_valid = burst_host[i], len(burst_host[i])
-                    for j, t in enumerate(toks):        # cut the burst at the request's stop token
-                        stops = sub.check_stop(rid, b.fwd_infos[rid], {"new_token_host": t})
-                        if stops:
-                            n_valid = j + 1
-                            break
+                    toks = burst_host[i]
+                    n_valid = len(toks)
+                    j = sub.first_stop_index(rid, fi, toks)      # cut the burst at the request's stop token
+                    if j is not None:
+                        n_valid = j + 1
+                        stops = sub.check_stop(rid, fi, {"new_token_host": toks[j]})
                     if n_valid < len(toks):             # the positions written past the stop do not count
                         label = planned.ctx.labels[i] if i < len(planned.ctx.labels) else "main"
                         self.cache.alloc.get_state(rid, label).seq_len -= len(toks) - n_valid
                     r["new_token"] = burst[i, n_valid - 1:n_valid]
                     r["new_token_host"] = toks[n_valid - 1]
                     r["burst_host"] = toks[:n_valid]
+                    r["burst_host_tensor"] = burst_t[i, :n_valid]
                     out.iterations[rid] = n_valid
                 elif tokens is not None:
                     r["new_token"] = tokens[i:i + 1]
                     r["new_token_host"] = host_tokens[i]
-                out.outputs[rid] = sub.postprocess(rid, b.fwd_infos[rid], r, ni)
-                if stops is None:
-                    stops = sub.check_stop(rid, b.fwd_infos[rid], r)
+                out.outputs[rid] = sub.postprocess(rid, fi, r, ni)
+                if stops is None and burst_host is None:
+                    stops = sub.check_stop(rid, fi, r)
                 if stops:
                     out.stop_loops[rid] = set(stops)
             except Exception as e:  # noqa: BLE001

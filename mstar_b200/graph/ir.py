@@ -11,8 +11,20 @@ Reference counterparts: ``TensorPointerInfo`` (mstar/graph/base.py:17-58), ``Gra
 """
 from __future__ import annotations
 
+import itertools as _itertools
+import os as _os
 import uuid as _uuid
 from dataclasses import dataclass, field, replace
+
+# Tensor ids must be unique across the processes of a deployment and are minted several times per request per decode
+# step: a random per-process prefix plus a counter costs a fraction of uuid4 (which reads the kernel's random pool).
+_UID_PREFIX = _os.urandom(6).hex()
+_UID_COUNTER = _itertools.count()
+
+
+def fast_uid() -> str:
+    return f"{_UID_PREFIX}{next(_UID_COUNTER):x}"
+
 
 EMIT_TO_CLIENT = "__emit_to_client__"
 EMPTY_DESTINATION = "__empty_destination__"
@@ -27,7 +39,7 @@ class TensorPointerInfo:
     nbytes: int
     address: int = 0
     stride: list[int] = field(default_factory=list)
-    uuid: str = field(default_factory=lambda: _uuid.uuid4().hex)
+    uuid: str = field(default_factory=fast_uid)
     source_session_id: str = ""
     source_entity: str = ""
     offset: int = 0
@@ -40,6 +52,16 @@ class TensorPointerInfo:
 
     def clone(self) -> "TensorPointerInfo":
         return replace(self, dims=list(self.dims), stride=list(self.stride))
+
+    def __reduce__(self):      # compact pickling: these cross process boundaries many times per decode step
+        return (_tpi_from_tuple, ((self.dims, self.dtype, self.nbytes, self.address, self.stride, self.uuid,
+                                   self.source_session_id, self.source_entity, self.offset, self.source_tp_size,
+                                   self.source_tp_rank, self.shm_segment, self.shm_offset, self.device_index,
+                                   self.cuda_ipc),))
+
+
+def _tpi_from_tuple(t):
+    return TensorPointerInfo(*t)
 
 
 @dataclass
@@ -59,7 +81,9 @@ class GraphEdge:
         return (self.name, self.next_node)
 
     def clone(self, with_tensors: bool = True) -> "GraphEdge":
-        return replace(self, tensor_info=list(self.tensor_info) if with_tensors else [])
+        return GraphEdge(self.next_node, self.name, list(self.tensor_info) if with_tensors else [], self.persist,
+                         self.conductor_new_token, self.is_streaming, self.output_modality, self.final_stream_chunk,
+                         self.total_fanin, self.shard_dim)
 
 
 @dataclass

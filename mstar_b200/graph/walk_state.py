@@ -265,15 +265,17 @@ class WalkState:
                 self._reset_scope_nodes(inner, rotate=rotate)
 
     # ------------------------------------------------------------------ speculation
-    def can_speculate(self, node: str) -> bool:
-        """May iteration N+1 of ``node`` be launched while iteration N still runs? True when the node sits alone
-        in a loop that will go on, and every input of N+1 is either its own loop-back output, an input from
-        outside the loop (delivered again each iteration) or already buffered."""
+    def can_speculate(self, node: str, ahead: int = 1, chained: bool = False) -> bool:
+        """May a further iteration of ``node`` be launched while earlier ones still run? True when the node sits
+        alone in a loop that will go on, and every input of the new iteration is either its own loop-back output,
+        an input from outside the loop (delivered again each iteration) or already buffered. ``ahead`` = iterations
+        already launched and not completed (1: only the running one); ``chained`` allows a speculative launch on
+        top of another speculative launch."""
         st = self.nodes[node]
         sc = st.scope
-        if sc.loop is None or not st.decl.enable_async_scheduling or st.speculating:
+        if sc.loop is None or not st.decl.enable_async_scheduling or (st.speculating and not chained):
             return False
-        if sc.finish or sc.curr_iter + 2 > sc.loop.max_iters:
+        if sc.finish or sc.curr_iter + ahead + 1 > sc.loop.max_iters:
             return False
         if len(sc.entity_names) != 1:
             return False

@@ -34,7 +34,9 @@ class DecoderSubmodule(ARNodeSubmodule):
         host = outputs.get("new_token_host")
         # what leaves the node (client, stream buffers of other partitions) is a host tensor: the value was read back
         # with the batch anyway, and consumers then never issue per-token device ops
-        if outputs.get("burst_host") is not None:           # a decode burst: all of its tokens leave together
+        if outputs.get("burst_host_tensor") is not None:    # a decode burst: all of its tokens leave together
+            out_tok = outputs["burst_host_tensor"]          # int64 host view of the batch's read-back, no copy
+        elif outputs.get("burst_host") is not None:
             out_tok = torch.tensor([int(t) for t in outputs["burst_host"]], dtype=torch.int64)
         else:
             out_tok = torch.tensor([int(host)], dtype=torch.int64) if host is not None else tok
@@ -45,6 +47,13 @@ class DecoderSubmodule(ARNodeSubmodule):
         if not sc.get("ignore_eos", False) and outputs.get("new_token_host") in self.eos_ids:
             return {self.loop_name}
         return set()
+
+    def first_stop_index(self, request_id, request_info, tokens):
+        sc = (request_info.sampling_config or {}).get("main", {})
+        if sc.get("ignore_eos", False) or not self.eos_ids:
+            return None
+        eos = self.eos_ids
+        return next((j for j, t in enumerate(tokens) if t in eos), None)
 
 
 def lm_walks(node: str = "LLM", loop_name: str = "decode_loop", max_iters: int = 2048, modality: str = "text",

@@ -29,15 +29,29 @@ END_TOKEN_IDS = (128009, 128260, 128261, 128257, 128258)
 VOICES = ["tara", "zoe", "zac", "jess", "leo", "mia", "julia", "leah"]
 
 
-class _HostRows:
-    """A slice of a pinned host buffer that a queued device-to-host copy fills: read it after the batch's event."""
-    __slots__ = ("buf", "row", "lo", "hi")
+class _HostBatch:
+    """A pinned host buffer that a queued device-to-host copy fills. The first read (after the batch's event) copies
+    the used rows out ONCE; every request's waveform is then a view of that copy."""
+    __slots__ = ("pinned", "rows", "copy")
 
-    def __init__(self, buf, row, lo, hi):
-        self.buf, self.row, self.lo, self.hi = buf, row, lo, hi
+    def __init__(self, pinned, rows):
+        self.pinned, self.rows, self.copy = pinned, rows, None
 
     def get(self) -> torch.Tensor:
-        return self.buf[self.row, self.lo:self.hi].clone()
+        if self.copy is None:
+            self.copy = self.pinned[:self.rows].clone()
+        return self.copy
+
+
+class _HostRows:
+    """One request's slice of a ``_HostBatch``."""
+    __slots__ = ("batch", "row", "lo", "hi")
+
+    def __init__(self, batch, row, lo, hi):
+        self.batch, self.row, self.lo, self.hi = batch, row, lo, hi
+
+    def get(self) -> torch.Tensor:
+        return self.batch.get()[self.row, self.lo:self.hi]
 
 
 class SnacSubmodule(NodeSubmodule):
@@ -122,11 +136,12 @@ class SnacSubmodule(NodeSubmodule):
                 io_counters.add_d2h(wav.numel() * 4)
             else:
                 host = wav
+            hb = _HostBatch(host, len(idx))
             for row, i in enumerate(idx):
                 final = bool(inputs[i].kwargs.get("final_chunk"))
                 # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows all
                 lo, hi = (2048, 4096) if n == 28 and not final else (0, host.shape[1])
-                outs[i] = {"audio": _HostRows(host, row, lo, hi), "final": final}
+                outs[i] = {"audio": _HostRows(hb, row, lo, hi), "final": final}
         return outs
 
     def postprocess(self, request_id, request_info, outputs, inputs):

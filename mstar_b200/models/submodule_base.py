@@ -120,6 +120,14 @@ class ARNodeSubmodule(NodeSubmodule):
         return ARNodeInputs(fwd_info.request_id, graph_walk, inputs, dict(fwd_info.step_metadata or {}),
                             input_seq_len=0 if ids is None else int(ids.numel()), input_ids=ids)
 
+    def first_stop_index(self, request_id: str, request_info, tokens: list[int]) -> int | None:
+        """Index of the first token of a decode burst at which ``check_stop`` asks for a stop, or None. Nodes with a
+        plain stop-token rule override this with something cheaper than one ``check_stop`` call per token."""
+        for j, t in enumerate(tokens):
+            if self.check_stop(request_id, request_info, {"new_token_host": t}):
+                return j
+        return None
+
     def filter_batched_output(self, outputs: dict, row: int) -> dict:
         return {k: (v[row] if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in outputs.items()}
 

@@ -56,6 +56,7 @@ class PerRequestInfo:
     kv_wait: set = field(default_factory=set)      # KV nodes whose pages are still on their way from another process
     spec: dict = field(default_factory=dict)       # node -> ids of the speculative flights that run its NEXT iterations
     spec_marked: set = field(default_factory=set)  # nodes marked running on behalf of such a flight
+    stream_targets: dict = field(default_factory=dict)   # streaming edge name -> node of this walk that consumes it
     t_start: float = field(default_factory=time.perf_counter)
     timings: dict = field(default_factory=dict)
 
@@ -116,14 +117,27 @@ class Worker:
         lockstep = bool(is_tp_follower or tp_followers)
         self._spec_enabled = bool(async_gpu and not lockstep and os.environ.get("MSTAR_SPECULATE", "1") != "0")
         self._max_chain = int(os.environ.get("MSTAR_MAX_CONSECUTIVE_SPEC_STEPS", "1024"))
-        self._engine_streams = bool(os.environ.get("MSTAR_ENGINE_CONCURRENCY")) and not lockstep
-        self._streams: dict[int, object] = {}        # id(engine) -> CUDA stream (MSTAR_ENGINE_CONCURRENCY only)
+        # flights of one engine that may be queued at once: the running batch plus this many speculative
+        # continuations (2: the GPU still has a queued batch while the host digests the results of the one that
+        # just finished, which takes about as long as a burst runs)
+        self._spec_depth = max(1, int(os.environ.get("MSTAR_SPEC_DEPTH", "2")))
+        # every engine launches on its own CUDA stream when the worker hosts several (MSTAR_ENGINE_STREAMS=0: one
+        # stream): a codec batch then does not queue behind the decode bursts that were launched ahead of it.
+        # Stateless engines (codecs, encoders) get the higher priority: their batches are short and sit on the
+        # latency path of a stream's next chunk. Outputs only change engines after their flight was read back, so
+        # no cross-stream waits are needed; device inputs are recorded on the consuming stream for the allocator.
+        n_eng = len(getattr(engine_manager, "engines", []) or [])
+        self._engine_streams = (os.environ.get("MSTAR_ENGINE_STREAMS", "1") != "0") and n_eng > 1 and not lockstep
+        self._streams: dict[int, object] = {}        # id(engine) -> CUDA stream
         self.spec_stats = dict(launched=0, discarded_rows=0, cancelled=0)
         self.heartbeat_s = heartbeat_s
         self._last_beat = time.monotonic()
         self.phase_times: dict[str, list[float]] = {}
         self.iterations = 0
         self._streaming_requests: set[tuple[str, str]] = set()      # request states that own stream buffers
+        # ... and those of them whose buffers or consumer nodes changed since they were last looked at: only these
+        # are polled (new items, producer done, consumer node finished an iteration, another input arrived)
+        self._stream_dirty: set[tuple[str, str]] = set()
         # host time by phase of the main loop (seconds): where a step's latency goes when the GPU is not the limit
         self.phase_s = dict(wait=0.0, messages=0.0, streams=0.0, finish=0.0, build=0.0, execute=0.0)
         self.batches_by_node: dict[str, list] = {}
@@ -261,6 +275,7 @@ class Worker:
                                                                c.chunk_policy_factory())
         if pri.stream_buffers:
             self._streaming_requests.add((pri.request_id, pri.partition_name))
+            self._stream_dirty.add((pri.request_id, pri.partition_name))
 
     def _on_input_signals(self, b: ipc.InputSignals) -> None:
         pri = self.requests.get((b.request_id, b.partition_name))
@@ -272,12 +287,15 @@ class Worker:
             sb = pri.stream_buffers.get(name)
             if sb is not None:
                 sb.signal_done()
+                self._stream_dirty.add((b.request_id, b.partition_name))
         for e in b.inputs:
             self._ingest(pri, e)
         self._refresh_ready(pri)
 
     def _ingest(self, pri: PerRequestInfo, e: GraphEdge) -> None:
         sb = pri.stream_buffers.get(e.name) if e.is_streaming else None
+        if pri.stream_buffers:
+            self._stream_dirty.add((pri.request_id, pri.partition_name))
         if sb is not None:
             for ti in e.tensor_info:
                 t = self.tensors.read(ti)
@@ -290,20 +308,24 @@ class Worker:
         pri.walk_state.ingest(e)
 
     def _poll_stream_buffers(self) -> None:
-        if not self._streaming_requests:
+        if not self._stream_dirty:
             return
-        for key in list(self._streaming_requests):
+        dirty, self._stream_dirty = self._stream_dirty, set()
+        for key in dirty:
             pri = self.requests.get(key)
             if pri is None:
                 self._streaming_requests.discard(key)
                 continue
+            nodes = pri.walk_state.nodes
             for name, sb in pri.stream_buffers.items():
-                target = next((n for n, st in pri.walk_state.nodes.items()
-                               if name in st.decl.streaming_inputs and name not in st.cur and not st.running), None)
-                if target is None or not sb.has_chunk_ready():
+                target = pri.stream_targets.get(name)
+                if target is None:
+                    target = next((n for n, st in nodes.items() if name in st.decl.streaming_inputs), "")
+                    pri.stream_targets[name] = target
+                st = nodes.get(target)
+                if st is None or name in st.cur or st.running or st.done or not sb.has_chunk_ready():
                     continue
-                st = pri.walk_state.nodes[target]
-                if not st.is_ready_for_streaming() or st.done:
+                if not st.is_ready_for_streaming():
                     continue
                 chunk = sb.pop_chunk()
                 data = chunk.data["data"]
@@ -422,7 +444,13 @@ class Worker:
             if self._engine_streams and eng.device.type == "cuda":
                 st = self._streams.get(id(eng))
                 if st is None:
-                    st = self._streams[id(eng)] = torch.cuda.Stream(device=eng.device)
+                    prio = 0 if hasattr(eng, "cache") else -1
+                    st = self._streams[id(eng)] = torch.cuda.Stream(device=eng.device, priority=prio)
+                for ins in batch.inputs.values():
+                    for ts in ins.values():
+                        for t in ts:
+                            if isinstance(t, torch.Tensor) and t.is_cuda:
+                                t.record_stream(st)
                 with torch.cuda.stream(st):
                     pend = eng.launch_batch(batch)
             else:
@@ -501,6 +529,8 @@ class Worker:
             if e.conductor_new_token:
                 pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + max(1, iterations)
         comp = ws.complete(node, edges, iterations=iterations)
+        if pri.stream_buffers:
+            self._stream_dirty.add((pri.request_id, pri.partition_name))
         if pri.spec.get(node):
             st = ws.nodes[node]
             if ws.done or st.scope.done or st.done or not st.is_ready():
@@ -703,14 +733,15 @@ class Worker:
                         fl.error = e
             # the continuation is queued FIRST (the sooner it sits behind the running batch, the less the GPU can
             # idle), then the batches whose results are there are read back
-            if self._spec_enabled and len(pipe) == 1 and pipe[0].pending is not None and not pipe[0].spec_tried:
-                head = pipe[0]
-                head.spec_tried = True
-                nb = self._build_speculative_batch(head)
-                if nb is not None:
-                    self.spec_stats["launched"] += 1
-                    self._submit(nb, speculative=True, chain=head.chain + 1)
-                    did = True
+            if self._spec_enabled and 1 <= len(pipe) <= self._spec_depth:
+                last = pipe[-1]
+                if last.pending is not None and last.error is None and not last.spec_tried:
+                    last.spec_tried = True
+                    nb = self._build_speculative_batch(last, pipe)
+                    if nb is not None:
+                        self.spec_stats["launched"] += 1
+                        self._submit(nb, speculative=True, chain=last.chain + 1)
+                        did = True
             while pipe and (pipe[0].error is not None or (pipe[0].pending is not None and pipe[0].pending.ready())):
                 self._finish(pipe.popleft())
                 did = True
@@ -718,13 +749,17 @@ class Worker:
                 del self._pipes[eid]
         return did
 
-    def _build_speculative_batch(self, fl: _Flight) -> NodeBatch | None:
+    def _build_speculative_batch(self, fl: _Flight, pipe) -> NodeBatch | None:
         """The next iteration of ``fl``'s loop node for the same requests, to be queued while ``fl`` still runs.
         None when the engine cannot continue from device-resident outputs, when some request may end its loop with
         the iteration in flight, when the chain is long enough, or when other work waits for this engine (a chain
         must not starve new requests: it is cut as soon as the scheduler holds anything else for the engine)."""
         b, pend, eng = fl.batch, fl.pending, fl.engine
         node, walk = b.node_name, b.graph_walk
+        if any(f.batch.node_name != node or f.batch.graph_walk != walk or f.pending is None or f.error is not None
+               or f.batch.request_ids != b.request_ids for f in pipe):
+            return None
+        queued_iters = sum(f.pending.iterations for f in pipe)      # iterations launched and not yet read back
         if fl.chain >= self._max_chain or pend.planned is None or pend.out.failed_requests or pend.out.allocation_failed:
             return None
         if not eng.can_speculate(node, walk):
@@ -741,9 +776,9 @@ class Worker:
                 return None              # this request left the loop: the chain ends here
             ws = pri.walk_state
             st = ws.nodes.get(node)
-            if st is None or not st.running or not ws.can_speculate(node):
+            if st is None or not st.running or not ws.can_speculate(node, ahead=len(pipe), chained=True):
                 return None
-            left = st.scope.loop.max_iters - st.scope.curr_iter - pend.iterations
+            left = st.scope.loop.max_iters - st.scope.curr_iter - queued_iters
             if left < 1:
                 return None
             pris.append(pri)
@@ -820,6 +855,10 @@ class Worker:
         self._run_loop()
 
     def _run_loop(self) -> None:
+        # the launch thread and this loop share the interpreter lock: with the default 5 ms switch interval each
+        # hand-over between them can stall a launch for milliseconds
+        import sys
+        sys.setswitchinterval(float(os.environ.get("MSTAR_PY_SWITCH_INTERVAL_SEC", "0.0002")))
         self.comm.send(self.conductor_id, Message(CM.SETUP_DONE, ipc.SetupDone(self.worker_id)))
         while self.running:
             if self._pipes:
