@@ -24,4 +24,8 @@ class PendingRequest:
     done: bool = False
     t_submit: float = field(default_factory=time.time)
     t_first_chunk: float | None = None
+    t_last_chunk: float | None = None
+    t_preprocessed: float | None = None
+    inputs: dict = field(default_factory=dict)        # modality -> [count, bytes]
+    outputs: dict = field(default_factory=dict)       # modality -> [count, bytes]
     profile: dict = field(default_factory=dict)

@@ -37,7 +37,11 @@ def modality_of(filename: str) -> str | None:
 
 class APIServer:
     def __init__(self, config, *, in_process: bool = True, request_timeout_s: float = 600.0, result_ttl_s: float = 300.0,
-                 log_stats: bool = False, **deploy_kw):
+                 log_stats: bool = False, log_stats_file: str | None = None, **deploy_kw):
+        if log_stats or log_stats_file:
+            from ..conductor.deployment import load_config
+            config = dict(load_config(config), log_stats=True)     # workers collect per-request profiles
+        self.log_stats_file = log_stats_file
         self.deployment = Deployment(config, in_process=in_process, **deploy_kw)
         self.model = self.deployment.model
         self.comm = self.deployment.api_comm
@@ -45,7 +49,8 @@ class APIServer:
         self.pending: dict[str, PendingRequest] = {}
         self.lock = threading.Lock()
         self.ready = threading.Event()
-        self.request_timeout_s, self.result_ttl_s, self.log_stats = request_timeout_s, result_ttl_s, log_stats
+        self.request_timeout_s, self.result_ttl_s = request_timeout_s, result_ttl_s
+        self.log_stats = bool(log_stats or log_stats_file)
         self.pre_pool = ThreadPoolExecutor(4, thread_name_prefix="preprocess")
         self.running = True
         self.stats = dict(submitted=0, completed=0, failed=0, aborted=0)
@@ -92,6 +97,13 @@ class APIServer:
                 if m not in mods:
                     mods.append(m)
             sigs = self.model.process_prompt(text, mods, pr.output_modalities, named, **pr.model_kwargs)
+            if text:
+                pr.inputs["text"] = [1, len(text.encode())]
+            for fname, blob in files:
+                rec = pr.inputs.setdefault(modality_of(fname) or "file", [0, 0])
+                rec[0] += 1
+                rec[1] += len(blob)
+            pr.t_preprocessed = time.time()
             infos = {k: [self.tensors.prepare_for_remote(self.tensors.store_and_return_tensor_info(pr.request_id, t, persist=True), "conductor_workers")
                          for t in v] for k, v in sigs.items()}
             body = ipc.NewRequestConductor(pr.request_id, infos, mods, pr.output_modalities, {}, pr.model_kwargs)
@@ -144,8 +156,12 @@ class APIServer:
         if m.type == AM.RESULT_TENSORS:
             ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
             data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
+            pr.t_last_chunk = time.time()
             if pr.t_first_chunk is None:
-                pr.t_first_chunk = time.time()
+                pr.t_first_chunk = pr.t_last_chunk
+            rec = pr.outputs.setdefault(b.modality, [0, 0])
+            rec[0] += 1
+            rec[1] += len(data) if isinstance(data, (bytes, bytearray)) else 0
             pr.chunks.put(ResultChunk(b.modality, data, dict(b.metadata)))
             if b.source_entity:
                 self.comm.send(b.source_entity, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, ipc.TensorReceived(
@@ -154,12 +170,32 @@ class APIServer:
             pr.profile = b.profile
             self.stats["completed"] += 1
             if self.log_stats:
-                from ..profile.display import format_profile
-                log.info("%s", format_profile(pr.request_id, pr.profile, pr.t_submit, pr.t_first_chunk))
+                from ..profile.display import render, write_profile
+                write_profile(render(self.request_profile(pr)), self.log_stats_file)
             self._finish(pr)
         elif m.type == AM.REQUEST_FAILED:
             self.stats["failed"] += 1
             self._finish(pr, ResultChunk("error", b.error_message.encode(), final=True, error_status=b.status))
+
+    def request_profile(self, pr: PendingRequest):
+        """The whole-request profile: this server's own timestamps and byte counts, the conductor's admission and
+        completion times, and the node timings and transfers that the workers reported with every finished walk."""
+        from ..profile.records import RequestProfile
+        rp = RequestProfile(pr.request_id, inputs=dict(pr.inputs), outputs=dict(pr.outputs),
+                            tokens_out=int(pr.profile.get("tokens_out", 0)))
+        t0 = pr.t_submit
+        pre = (pr.t_preprocessed - t0) if pr.t_preprocessed else None
+        cp = {"received": 0.0, "preprocessed": pre,
+              "first_chunk": (pr.t_first_chunk - t0) if pr.t_first_chunk else None,
+              "last_chunk": (pr.t_last_chunk - t0) if pr.t_last_chunk else None, "finished": time.time() - t0}
+        if pre is not None and "queue_s" in pr.profile:       # the conductor's clock starts when the request reaches it
+            cp["admitted"] = pre + pr.profile["queue_s"]
+            cp["conductor_done"] = pre + pr.profile.get("total_s", 0.0)
+        rp.checkpoints = cp
+        for w in pr.profile.get("walks", []):
+            if isinstance(w, dict) and w.get("profile"):
+                rp.merge_worker(w["profile"])
+        return rp
 
     def _prune(self) -> None:
         now = time.time()

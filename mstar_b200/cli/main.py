@@ -35,7 +35,8 @@ def add_serve_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--timeout", type=float, default=float(os.environ.get("MSTAR_REQUEST_TIMEOUT_S", 600)))
     ap.add_argument("--enable-nvtx", action="store_true")
     ap.add_argument("--log-level", default="INFO")
-    ap.add_argument("--log-stats", action="store_true")
+    ap.add_argument("--log-stats", action="store_true", help="print a per-request profile when a request completes")
+    ap.add_argument("--log-stats-file", default=None, help="append the per-request profiles to this file instead")
     ap.add_argument("--multi-process", action="store_true", help="one OS process per worker over the shm mesh")
     ap.add_argument("--native-frontend", action="store_true", help="serve HTTP from the C++ frontend (mstar-server)")
     ap.add_argument("--cache-dir", default=None)
@@ -50,7 +51,7 @@ def serve(args) -> None:
     profiler.enable(args.enable_nvtx)
     cfg = args.config or resolve_config(args.model)
     server = APIServer(cfg, in_process=not args.multi_process, request_timeout_s=args.timeout,
-                       log_stats=args.log_stats).start()
+                       log_stats=args.log_stats, log_stats_file=args.log_stats_file).start()
     if args.native_frontend:
         from ..api_server.native_frontend import NativeFrontend
         fe = NativeFrontend(create_app(server, args.allow_remote_media), host=args.host, port=args.port).start()

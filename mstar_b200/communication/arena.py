@@ -49,7 +49,17 @@ def _bind(lib):
     lib.mstar_arena_view_ptr.argtypes = [ctypes.c_void_p, ctypes.c_ulonglong]
     lib.mstar_arena_close_segment.argtypes = [ctypes.c_void_p]
     lib.mstar_arena_destroy.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.mstar_arena_pin.argtypes = [ctypes.c_void_p, ctypes.c_ulonglong]
+    lib.mstar_arena_pinned_bytes.restype = ctypes.c_ulonglong
+    lib.mstar_arena_pinned_bytes.argtypes = [ctypes.c_void_p]
+    lib.mstar_arena_pin_segment.argtypes = [ctypes.c_void_p]
+    lib.mstar_arena_set_pin_hooks.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     return lib
+
+
+def default_pin_budget() -> int:
+    """Bytes of arena memory a process may page-lock (``MSTAR_SHM_ARENA_PIN_MB``, default 1024; 0 turns pinning off)."""
+    return int(os.environ.get("MSTAR_SHM_ARENA_PIN_MB", "1024")) << 20
 
 
 def _tensor_at(ptr: int, nbytes: int, dtype: torch.dtype, dims) -> torch.Tensor:
@@ -68,6 +78,16 @@ class ShmArena:
         if not self.h:
             raise RuntimeError(f"arena: cannot create {base_name}")
         self._blocks: dict[str, tuple[int, int, float]] = {}     # uuid -> (segment, offset, time)
+
+    def pin(self, budget_bytes: int | None = None) -> int:
+        """Page-lock the segments for CUDA (``cudaHostRegister`` inside the C++ arena) so that copies between them
+        and a GPU are asynchronous DMA; at most ``budget_bytes`` in total, segments added later included. Returns the
+        number of pinned segments, -1 when the process has no CUDA runtime (the arena then stays pageable)."""
+        return int(self.lib.mstar_arena_pin(self.h, default_pin_budget() if budget_bytes is None else budget_bytes))
+
+    @property
+    def pinned_bytes(self) -> int:
+        return int(self.lib.mstar_arena_pinned_bytes(self.h))
 
     def write(self, uuid: str, t: torch.Tensor) -> tuple[int, int]:
         """Copy ``t`` (any device) into a fresh block; returns (segment, offset)."""
@@ -118,9 +138,11 @@ class ShmArena:
 class ShmArenaReader:
     """Consumer side: maps producers' segments on first use and hands out zero-copy views."""
 
-    def __init__(self):
+    def __init__(self, pin: bool = False):
         self.lib = _bind(_lib.runtime())
         self._segs: dict[tuple[str, int], int] = {}
+        self.pin = pin          # page-lock producers' segments as they are mapped (consumer uploads to a GPU)
+        self.pinned_segments = 0
 
     def view(self, base_name: str, seg: int, off: int, nbytes: int, dtype: torch.dtype, dims) -> torch.Tensor:
         key = (base_name, seg)
@@ -130,6 +152,8 @@ class ShmArenaReader:
             if not h:
                 raise FileNotFoundError(f"arena segment {base_name}.seg{seg} not found")
             self._segs[key] = h
+            if self.pin:
+                self.pinned_segments += int(self.lib.mstar_arena_pin_segment(h))
         ptr = self.lib.mstar_arena_view_ptr(h, off)
         if not ptr:
             raise ValueError("arena: offset outside the segment")

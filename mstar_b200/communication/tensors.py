@@ -170,6 +170,8 @@ class TensorCommunicationManager:
                 if self._arena is None:
                     prefix = self._arena_prefix or "mstar"
                     self._arena = ShmArena(f"{prefix}.{self.entity_id}.arena", segment_bytes=self._arena_bytes)
+                    if self.device.type == "cuda":       # device-to-host writes into the arena become plain DMA
+                        self._arena.pin()
                 seg, off = self._arena.write(info.uuid, t)
             out.shm_segment = f"{self._arena.base_name}#{seg}"
             out.shm_offset = off
@@ -190,7 +192,7 @@ class TensorCommunicationManager:
                 base, seg = info.shm_segment.rsplit("#", 1)
                 with self._arena_lock:
                     if self._reader is None:
-                        self._reader = ShmArenaReader()
+                        self._reader = ShmArenaReader(pin=self.device.type == "cuda")
                     t = self._reader.view(base, int(seg), info.shm_offset, info.nbytes, dtype_from_name(info.dtype),
                                           info.dims).clone()
             else:

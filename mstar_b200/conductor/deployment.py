@@ -107,7 +107,7 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
     is_follower = rank in leader_of and leader_of[rank] != rank
     return Worker(worker_id_of(rank), rank, model, node_names, comm, tensors, em, node_to_workers=n2w,
                   tp_followers=followers, is_tp_follower=is_follower, max_batch_size=int(cfg.get("max_batch_size", 64)),
-                  async_gpu=async_gpu, heartbeat_s=heartbeat_s)
+                  async_gpu=async_gpu, heartbeat_s=heartbeat_s, log_stats=bool(cfg.get("log_stats")))
 
 
 def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):

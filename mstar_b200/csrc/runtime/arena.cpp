@@ -14,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include <dlfcn.h>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -35,6 +36,7 @@ struct Segment {
     std::map<uint64_t, uint64_t> free_blocks;   // offset -> size, coalesced
     std::map<uint64_t, uint64_t> used;          // offset -> size
     bool owner = false;
+    bool pinned = false;                        // registered with the CUDA runtime (page-locked, DMA-able)
 };
 
 struct Arena {
@@ -45,7 +47,60 @@ struct Arena {
     std::vector<Segment> segs;
     std::mutex mu;
     uint64_t bytes_in_use = 0;
+    uint64_t pin_budget = 0;                    // bytes that may be page-locked; 0 = pinning off
+    uint64_t pinned_bytes = 0;
 };
+
+// ---- CUDA host registration -------------------------------------------------------------------------------
+// A mapped /dev/shm segment is ordinary pageable memory: a copy between it and a GPU goes through the driver's
+// staging buffer and blocks the calling thread. Registered with cudaHostRegister the segment is page-locked, copies
+// from and to it are true asynchronous DMA, and a consumer can upload an arriving tensor straight from the producer's
+// block. This library is built without CUDA: the two runtime entry points are looked up in an already loaded (or
+// loadable) libcudart at run time, and a process without a GPU simply gets "unavailable". Tests install their own
+// hooks instead.
+typedef int (*HostRegisterFn)(void*, size_t, unsigned int);
+typedef int (*HostUnregisterFn)(void*);
+HostRegisterFn g_register = nullptr;
+HostUnregisterFn g_unregister = nullptr;
+bool g_hooks_set = false;
+std::mutex g_pin_mu;
+
+bool resolve_cuda() {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    if (g_hooks_set) return g_register != nullptr;
+    g_hooks_set = true;
+    const char* names[] = {"libcudart.so.12", "libcudart.so.13", "libcudart.so"};
+    void* lib = nullptr;
+    for (const char* n : names) {
+        lib = dlopen(n, RTLD_NOW | RTLD_NOLOAD);        // the copy the process already uses, if any
+        if (lib) break;
+    }
+    for (const char* n : names) {
+        if (lib) break;
+        lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    }
+    if (!lib) return false;
+    g_register = reinterpret_cast<HostRegisterFn>(dlsym(lib, "cudaHostRegister"));
+    g_unregister = reinterpret_cast<HostUnregisterFn>(dlsym(lib, "cudaHostUnregister"));
+    if (!g_register || !g_unregister) g_register = nullptr;
+    return g_register != nullptr;
+}
+
+// Page-lock one mapped segment if the budget allows. Returns true when the segment is pinned afterwards.
+bool pin_segment(Segment& s, uint64_t* budget_left) {
+    if (s.pinned) return true;
+    if (!resolve_cuda() || (budget_left && *budget_left < s.bytes)) return false;
+    const unsigned int kPortable = 1;       // cudaHostRegisterPortable: valid in every CUDA context of the process
+    if (g_register(s.base, (size_t)s.bytes, kPortable) != 0) return false;
+    s.pinned = true;
+    if (budget_left) *budget_left -= s.bytes;
+    return true;
+}
+
+void unpin_segment(Segment& s) {
+    if (s.pinned && g_unregister) g_unregister(s.base);
+    s.pinned = false;
+}
 
 bool open_segment(Segment* s, const std::string& path, uint64_t bytes, bool create) {
     int fd = create ? ::open(path.c_str(), O_RDWR | O_CREAT | O_TRUNC, 0600) : ::open(path.c_str(), O_RDWR);
@@ -143,8 +198,51 @@ MSTAR_RT_API int mstar_arena_reserve(void* h, unsigned long long bytes, int* seg
         Segment s;
         const std::string path = "/dev/shm/" + a->base_name + ".seg" + std::to_string(a->segs.size());
         if (!open_segment(&s, path, a->segment_bytes, true)) return -1;
+        if (a->pin_budget > a->pinned_bytes) {          // a grown arena keeps its segments page-locked while the
+            uint64_t left = a->pin_budget - a->pinned_bytes;     // budget lasts; later segments stay pageable
+            if (pin_segment(s, &left)) a->pinned_bytes = a->pin_budget - left;
+        }
         a->segs.push_back(std::move(s));
     }
+}
+
+// Page-lock the arena's segments for CUDA (cudaHostRegister), at most `budget_bytes` in total; segments added
+// later are registered too while the budget lasts. Returns the number of pinned segments, or -1 when no CUDA
+// runtime can be found in this process (the arena keeps working with pageable memory).
+MSTAR_RT_API int mstar_arena_pin(void* h, unsigned long long budget_bytes) {
+    Arena* a = static_cast<Arena*>(h);
+    if (!a) return -1;
+    if (!resolve_cuda()) return -1;
+    std::lock_guard<std::mutex> lk(a->mu);
+    a->pin_budget = budget_bytes;
+    int n = 0;
+    for (auto& s : a->segs) {
+        if (!s.pinned && a->pin_budget > a->pinned_bytes) {
+            uint64_t left = a->pin_budget - a->pinned_bytes;
+            if (pin_segment(s, &left)) a->pinned_bytes = a->pin_budget - left;
+        }
+        n += s.pinned ? 1 : 0;
+    }
+    return n;
+}
+
+MSTAR_RT_API unsigned long long mstar_arena_pinned_bytes(void* h) {
+    Arena* a = static_cast<Arena*>(h);
+    return a ? a->pinned_bytes : 0;
+}
+
+// Consumer side: page-lock a mapped producer segment so that uploads from it are asynchronous. 1 = pinned.
+MSTAR_RT_API int mstar_arena_pin_segment(void* seg_handle) {
+    Segment* s = static_cast<Segment*>(seg_handle);
+    return (s && pin_segment(*s, nullptr)) ? 1 : 0;
+}
+
+// Replace the CUDA entry points (tests without a GPU install counting fakes; nullptr restores the run-time lookup).
+MSTAR_RT_API void mstar_arena_set_pin_hooks(HostRegisterFn reg, HostUnregisterFn unreg) {
+    std::lock_guard<std::mutex> lk(g_pin_mu);
+    g_register = reg;
+    g_unregister = unreg;
+    g_hooks_set = reg != nullptr;
 }
 
 // Returns 0, 1 when a canary around the block was overwritten (the block is freed anyway), -1 on a bad handle.
@@ -207,6 +305,7 @@ MSTAR_RT_API void* mstar_arena_view_ptr(void* seg_handle, unsigned long long off
 MSTAR_RT_API void mstar_arena_close_segment(void* seg_handle) {
     Segment* s = static_cast<Segment*>(seg_handle);
     if (!s) return;
+    unpin_segment(*s);
     munmap(s->base, s->bytes);
     delete s;
 }
@@ -215,6 +314,7 @@ MSTAR_RT_API void mstar_arena_destroy(void* h, int unlink_files) {
     Arena* a = static_cast<Arena*>(h);
     if (!a) return;
     for (auto& s : a->segs) {
+        unpin_segment(s);
         munmap(s.base, s.bytes);
         if (unlink_files) ::unlink(s.path.c_str());
     }

@@ -81,3 +81,33 @@ def oracle_generate(model: DecoderLM, prompts: list[list[int]], n_tokens: int = 
             ids.append(t)
         outs.append(gen)
     return outs
+
+
+@torch.no_grad()
+def oracle_violations(model: DecoderLM, prompts: list[list[int]], generated: list[list[int]], rel_tol: float = 2e-2):
+    """Teacher-forced check of greedy generations against the fp32 oracle. At every step the oracle scores the
+    prompt plus the tokens generated so far; the generated token must be the oracle's argmax, or its oracle logit
+    must lie within ``rel_tol`` x (largest |logit|) of the top one (a near tie that reduced-precision arithmetic may
+    resolve the other way). Returns (violations as (prompt, step, token, gap), exact-argmax fraction)."""
+    bad, exact, total = [], 0, 0
+    for pi, (p, gen) in enumerate(zip(prompts, generated)):
+        ids = list(p)
+        for step, t in enumerate(gen):
+            lg = oracle_logits(model, ids)
+            top = float(lg.max())
+            gap = top - float(lg[int(t)])
+            total += 1
+            if int(torch.argmax(lg)) == int(t):
+                exact += 1
+            elif gap > rel_tol * float(lg.abs().max()):
+                bad.append((pi, step, int(t), gap))
+            ids.append(int(t))
+    return bad, exact / max(1, total)
+
+
+def fp32_copy(model: DecoderLM) -> DecoderLM:
+    """The same weights (as stored, e.g. bf16-rounded) in an fp32 model on the CPU, for the oracle."""
+    m = build_tiny(device="cpu", dtype=torch.float32)
+    for (_, a), (_, b) in zip(m.named_parameters(), model.named_parameters()):
+        a.copy_(b.float().cpu())
+    return m

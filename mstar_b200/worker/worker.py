@@ -81,8 +81,14 @@ class Worker:
                  tensors: TensorCommunicationManager, engine_manager, *, node_to_workers: dict[str, list[str]],
                  conductor_id: str = "conductor", api_id: str = "api", tp_followers: list[str] | None = None,
                  is_tp_follower: bool = False, max_batch_size: int = 64, async_gpu: bool = True,
-                 heartbeat_s: float = 0.0):
+                 heartbeat_s: float = 0.0, log_stats: bool = False):
         self.worker_id, self.rank, self.model = worker_id, rank, model
+        # per-request profile (node timings, tensor transfers), collected only when the server logs request statistics
+        self.profile = None
+        if log_stats or os.environ.get("MSTAR_LOG_STATS"):
+            from ..profile.records import WorkerProfile
+            self.profile = WorkerProfile(worker_id)
+            tensors.log_transfers = True
         self.node_names = set(node_names)
         self.comm, self.tensors, self.engines = comm, tensors, engine_manager
         self.node_to_workers = node_to_workers
@@ -100,6 +106,7 @@ class Worker:
         self._last_arrival = 0.0
         self._by_walk_node: dict[tuple[str, str], dict] = {}       # (node, walk) -> live request states that run it
         self.trace = [] if os.environ.get("MSTAR_TRACE_WORKER") else None
+        self._done_queue: list | None = None      # walk-completion messages held back while a batch is being finished
         self.walks = model.get_graph_walk_graphs()
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
@@ -398,6 +405,8 @@ class Worker:
         if not any(k[0] == key[0] for k in self.requests):
             self.engines.remove_request(key[0])
             self.tensors.remove_request(key[0])
+            if self.profile is not None:
+                self.profile.drop(key[0])
 
     def _on_stop_loops(self, b: ipc.StopLoops) -> None:
         pri = self.requests.get((b.request_id, b.partition_name))
@@ -420,7 +429,7 @@ class Worker:
                 continue
             ins = {}
             for name, edge in pri.walk_state.inputs_of(node).items():
-                ins[name] = [self.tensors.read(ti) for ti in edge.tensor_info]
+                ins[name] = [self._read_input(rid, name, ti) for ti in edge.tensor_info]
             sc = pri.walk_state.nodes[node].scope
             if sc.loop is not None:          # iterations the node may still run (bound of a decode burst)
                 pri.fwd_info.step_metadata = dict(pri.fwd_info.step_metadata or {},
@@ -564,7 +573,7 @@ class Worker:
                 for ti in e.tensor_info:        # a loop's last output was stored as an intermediate: re-own it
                     if self.tensors.store.owner_of(ti.uuid) not in (None, emit_owner):
                         self.tensors.store.adopt(ti.uuid, emit_owner)
-                infos = [self.tensors.prepare_for_remote(ti, self.api_id) for ti in e.tensor_info]
+                infos = [self._publish(pri.request_id, e.name, ti, self.api_id) for ti in e.tensor_info]
                 self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS,
                                                     ipc.ResultTensors(pri.request_id, e.output_modality or "text", infos,
                                                                       {"name": e.name, "partition": pri.partition_name},
@@ -596,9 +605,28 @@ class Worker:
                 out_edges = []
                 for e in ges:
                     c = e.clone(with_tensors=False)
-                    c.tensor_info = [self.tensors.prepare_for_remote(ti, w) for ti in e.tensor_info]
+                    c.tensor_info = [self._publish(pri.request_id, e.name, ti, w) for ti in e.tensor_info]
                     out_edges.append(c)
                 self.comm.send(w, Message(WM.INPUT_SIGNALS, ipc.InputSignals(pri.request_id, out_edges, None, part)))
+
+    def _publish(self, request_id: str, edge: str, ti, dst: str):
+        """Make a tensor readable by ``dst`` (arena block / IPC handle when it lives in another process); the copy is
+        charged to the request's profile when statistics are on."""
+        if self.profile is None or self.tensors.is_local(dst):
+            return self.tensors.prepare_for_remote(ti, dst)
+        t0 = time.perf_counter()
+        out = self.tensors.prepare_for_remote(ti, dst)
+        self.profile.record_transfer(request_id, "tx", edge, self.worker_id, dst, ti.nbytes, time.perf_counter() - t0)
+        return out
+
+    def _read_input(self, request_id: str, edge: str, ti):
+        if self.profile is None or self.tensors.is_local(ti.source_entity):
+            return self.tensors.read(ti)
+        t0 = time.perf_counter()
+        t = self.tensors.read(ti)
+        self.profile.record_transfer(request_id, "rx", edge, ti.source_entity, self.worker_id, ti.nbytes,
+                                     time.perf_counter() - t0)
+        return t
 
     def _broadcast_stops(self, pri: PerRequestInfo, stops: set) -> None:
         peers = {w for ws_ in pri.worker_graph_to_workers.values() for w in ws_ if w != self.worker_id}
@@ -611,12 +639,21 @@ class Worker:
             if hasattr(eng, "get_per_label_seq_info"):
                 seq.update(eng.get_per_label_seq_info(pri.request_id))
         if not self.is_tp_follower:
-            self.comm.send(self.conductor_id, Message(CM.WORKER_GRAPHS_DONE, ipc.WorkerGraphsDone(
+            body = ipc.WorkerGraphsDone(
                 pri.request_id, list(pri.worker_graph_ids), True, dict(pri.persist), dict(pri.new_token_counts), seq,
                 pri.partition_name, False, {}, pri.walk_state.loop_indices(),
-                {"walk_s": time.perf_counter() - pri.t_start}, pri.fwd_info.graph_walk)))
+                {"walk_s": time.perf_counter() - pri.t_start}, pri.fwd_info.graph_walk)
+            if self._done_queue is not None:
+                self._done_queue.append(body)       # sent once the batch that ended the walk is in the profile
+            else:
+                self._send_walk_done(body)
         pri.persist = {}
         pri.new_token_counts = {}
+
+    def _send_walk_done(self, body) -> None:
+        if self.profile is not None:
+            body.timings["profile"] = self.profile.pop(body.request_id)
+        self.comm.send(self.conductor_id, Message(CM.WORKER_GRAPHS_DONE, body))
 
     # ------------------------------------------------------------------ failures
     def _fail_requests(self, errors: dict[str, str]) -> None:
@@ -821,6 +858,7 @@ class Worker:
                 raise fl.error
             out = fl.engine.collect_batch(fl.pending)
             dt = time.perf_counter() - fl.t_submit
+            t_post = time.perf_counter()
             if self.trace is not None:
                 self.trace.append((time.monotonic(), "collect", f"{batch.node_name}:{batch.graph_walk}",
                                    len(batch.request_ids), int(fl.speculative), fl.fid))
@@ -829,7 +867,19 @@ class Worker:
             rec[0] += 1
             rec[1] += len(batch.request_ids)
             rec[2] += dt
-            self._postprocess_batch(batch, out, fl)
+            self._done_queue = []
+            try:
+                self._postprocess_batch(batch, out, fl)
+            finally:
+                done, self._done_queue = self._done_queue, None
+            if self.profile is not None:
+                tm = out.timings
+                self.profile.record_batch(batch.node_name, batch.graph_walk, batch.request_ids,
+                                          launch_s=tm.get("prepare_s", 0.0) + tm.get("plan_s", 0.0) + tm.get("forward_s", 0.0),
+                                          flight_s=dt, post_s=tm.get("postprocess_s", 0.0) + time.perf_counter() - t_post,
+                                          iterations=out.iterations, speculative=fl.speculative)
+            for body in done:
+                self._send_walk_done(body)
         except Exception as e:  # noqa: BLE001
             log.error("worker %s: batch %s failed: %s\n%s", self.worker_id, batch.node_name, e,
                       "".join(traceback.format_exception(type(e), e, e.__traceback__)))

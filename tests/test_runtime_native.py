@@ -143,3 +143,39 @@ def test_arena_cross_process_zero_copy_and_canary():
     finally:
         ar.close()
     assert sweep_orphans(name) == 0
+
+
+def test_arena_segments_are_registered_with_cuda_within_the_pin_budget():
+    """``cudaHostRegister`` of arena segments, driven against counting stand-ins for the two CUDA runtime calls:
+    the first segment is pinned, a segment added by growth is pinned while the budget lasts, later ones stay
+    pageable, consumers pin the segments they map, and everything is unregistered on close."""
+    import ctypes
+    import uuid
+
+    import torch
+
+    from mstar_b200.communication.arena import ShmArena, ShmArenaReader, _bind
+    from mstar_b200.ops import _lib
+    lib = _bind(_lib.runtime())
+    calls = {"reg": [], "unreg": []}
+    REG = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint)
+    UNREG = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+    reg = REG(lambda p, n, flags: calls["reg"].append((p, n, flags)) or 0)
+    unreg = UNREG(lambda p: calls["unreg"].append(p) or 0)
+    lib.mstar_arena_set_pin_hooks(ctypes.cast(reg, ctypes.c_void_p), ctypes.cast(unreg, ctypes.c_void_p))
+    try:
+        seg = 1 << 20
+        a = ShmArena("t_pin_" + uuid.uuid4().hex[:8], segment_bytes=seg, max_segments=3)
+        assert a.pin(budget_bytes=2 * seg) == 1 and a.pinned_bytes == seg
+        assert calls["reg"][0][1] == seg and calls["reg"][0][2] == 1          # whole segment, portable flag
+        blob = torch.arange(200_000, dtype=torch.float32)                      # 800 KB: three of them need 3 segments
+        locs = [a.write(f"u{i}", blob + i) for i in range(3)]
+        assert a.num_segments == 3 and a.pinned_bytes == 2 * seg and len(calls["reg"]) == 2
+        r = ShmArenaReader(pin=True)
+        v = r.view(a.base_name, locs[2][0], locs[2][1], blob.numel() * 4, torch.float32, blob.shape)
+        assert torch.equal(v, blob + 2) and r.pinned_segments == 1 and len(calls["reg"]) == 3
+        r.close()
+        a.close()
+        assert len(calls["unreg"]) == 3
+    finally:
+        lib.mstar_arena_set_pin_hooks(None, None)
