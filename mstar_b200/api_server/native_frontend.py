@@ -63,7 +63,7 @@ class _RawMesh:
             need = self.lib.mstar_mesh_peek_size(self.h)
             self._buf = ctypes.create_string_buffer(int(max(need, 2 * len(self._buf))))
             n = self.lib.mstar_mesh_recv(self.h, self._buf, len(self._buf), 0)
-        return self._buf.raw[:n] if n > 0 else None
+        return ctypes.string_at(self._buf, n) if n > 0 else None
 
     def close(self):
         if self.h:
@@ -93,7 +93,8 @@ class NativeFrontend:
                                       "--max-connections", str(self.max_connections)])
         self.running = True
         threading.Thread(target=self._loop_thread, daemon=True, name="frontend-asgi").start()
-        threading.Thread(target=self._recv_thread, daemon=True, name="frontend-bridge").start()
+        self._bridge = threading.Thread(target=self._recv_thread, daemon=True, name="frontend-bridge")
+        self._bridge.start()
         deadline = time.time() + wait_s
         while time.time() < deadline:
             if self.proc.poll() is not None:
@@ -112,7 +113,12 @@ class NativeFrontend:
             except subprocess.TimeoutExpired:
                 self.proc.terminate()
         self.loop.call_soon_threadsafe(self.loop.stop)
-        self.mesh.close()
+        # the bridge thread may be blocked inside the mailbox's receive: the mailbox is unmapped only after it left
+        bridge = getattr(self, "_bridge", None)
+        if bridge is not None and bridge is not threading.current_thread():
+            bridge.join(2.0)
+        if bridge is None or not bridge.is_alive():
+            self.mesh.close()
 
     def wait(self) -> int:
         return self.proc.wait() if self.proc is not None else 0

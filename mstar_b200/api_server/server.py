@@ -66,6 +66,10 @@ class APIServer:
 
     def shutdown(self) -> None:
         self.running = False
+        # the result thread may be blocked inside the mailbox's receive (50 ms slices): let it leave before the
+        # deployment closes and unmaps that mailbox
+        if self._thread.is_alive() and self._thread is not threading.current_thread():
+            self._thread.join(2.0)
         self.deployment.shutdown()
         self.pre_pool.shutdown(wait=False)
         self.tensors.close()

@@ -146,7 +146,7 @@ class ShmMeshCommunicator(BaseCommunicator):
             n = self.lib.mstar_mesh_recv(self.h, self._buf, len(self._buf), 0)
         if n <= 0:
             return None
-        return pickle.loads(self._buf.raw[:n])
+        return pickle.loads(ctypes.string_at(self._buf, n))
 
     def drain(self) -> list[Message]:
         out = []

@@ -105,14 +105,31 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
     followers = [worker_id_of(r) for wg in mine if wg.tp_size * wg.sp_size > 1 and wg.ranks[0] == rank
                  for r in wg.ranks[1:]]
     is_follower = rank in leader_of and leader_of[rank] != rank
+    # a node that appears in several node groups with different walk filters is split by walk (prefill / decode
+    # disaggregation): only then do persisted tensors have to be readable from other processes
+    walks_of: dict[str, set] = {}
+    for g in cfg["node_groups"]:
+        for n in g.get("node_names", []):
+            walks_of.setdefault(n, set()).add(tuple(sorted(g.get("graph_walks") or [])))
+    split_by_walk = any(len(v) > 1 for v in walks_of.values())
     return Worker(worker_id_of(rank), rank, model, node_names, comm, tensors, em, node_to_workers=n2w,
+                  publish_persisted=split_by_walk,
                   tp_followers=followers, is_tp_follower=is_follower, max_batch_size=int(cfg.get("max_batch_size", 64)),
                   async_gpu=async_gpu, heartbeat_s=heartbeat_s, log_stats=bool(cfg.get("log_stats")))
 
 
 def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):
+    import faulthandler
+    faulthandler.enable()
     signal.signal(signal.SIGTERM, lambda *_: (_ for _ in ()).throw(SystemExit(0)))
     logging.basicConfig(level=os.environ.get("MSTAR_LOG_LEVEL", "INFO"))
+    # a launcher may have pinned OMP_NUM_THREADS to 1 for its own ranks; weight initialisation / loading and host-side
+    # tensor work in a worker want a few cores
+    try:
+        n_workers = len({r for g in cfg.get("node_groups", []) for r in g.get("ranks", [0])}) or 1
+        torch.set_num_threads(max(1, min(16, (os.cpu_count() or 8) // n_workers)))
+    except Exception:  # noqa: BLE001
+        pass
     model = build_model(cfg)
     comm = make_communicator(worker_id_of(rank), "shm", prefix)
     w = build_worker(cfg, model, rank, comm, prefix=prefix, dist_init=dist_init, heartbeat_s=heartbeat_s)
@@ -123,6 +140,8 @@ def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):
 
 
 def _conductor_process_target(cfg, prefix, heartbeat_timeout_s):
+    import faulthandler
+    faulthandler.enable()
     signal.signal(signal.SIGTERM, lambda *_: (_ for _ in ()).throw(SystemExit(0)))
     logging.basicConfig(level=os.environ.get("MSTAR_LOG_LEVEL", "INFO"))
     model = build_model(cfg)

@@ -13,6 +13,13 @@ struct PeerTable {
     int world, rank;
 };
 
+// The multicast view of the same heaps (null pointers when the group has no NVLS multicast object: kernels then
+// take their plain peer load / store path).
+struct McastTable {
+    char* data;                      // multicast address of the data region (offset 0 = offset 0 of every heap)
+    unsigned int* flags;             // multicast address of the flag region
+};
+
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -20,6 +27,32 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// NVLS: loads, stores and reductions through a MULTICAST address. The symmetric heap of every rank is bound to one
+// multicast object; an access to offset X of the multicast mapping reaches offset X of every rank's heap inside the
+// NVSwitch: a load-reduce returns the sum of all ranks' values with one request, a store or reduction lands on every
+// rank. These are not TMA operations and use no cluster multicast.
+// ---------------------------------------------------------------------------------------------
+// Sum over all ranks of 8 bf16 values at the same heap offset, accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+// Store 16 bytes to the same heap offset on every rank.
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// Release-store of one flag word on every rank (this rank's own copy included).
+__device__ __forceinline__ void multimem_st_release_u32(unsigned int* mc, unsigned int v) {
+    asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
 
 // Wait until *flag >= target (epochs only grow; wrap-around after 2^31 steps is handled by the signed compare).
@@ -34,6 +67,29 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* flag, unsigned int
         }
     }
     return true;
+}
+
+// Signal every rank (one multicast store when available, else one store per peer) on `channel` with `epoch`.
+__device__ __forceinline__ void signal_all(const PeerTable& t, const McastTable& mc, int channel, unsigned int epoch) {
+    if (mc.flags != nullptr) {
+        multimem_st_release_u32(mc.flags + (size_t)channel * MAX_RANKS + t.rank, epoch);
+    } else {
+        for (int p = 0; p < t.world; ++p)
+            if (p != t.rank) st_release_sys(t.flags[p] + (size_t)channel * MAX_RANKS + t.rank, epoch);
+    }
+}
+// Wait (bounded) until every peer has signalled `epoch` on `channel`.
+__device__ __forceinline__ bool wait_all(const PeerTable& t, int channel, unsigned int epoch, KernelStatus* status,
+                                         unsigned long long limit_ns, int phase) {
+    bool ok = true;
+    for (int p = 0; p < t.world; ++p) {
+        if (p == t.rank) continue;
+        if (!wait_flag(t.flags[t.rank] + (size_t)channel * MAX_RANKS + p, epoch, limit_ns)) {
+            report_status(status, KID_COMM, phase, p, channel);
+            ok = false;
+        }
+    }
+    return ok;
 }
 
 // Signal every peer on `channel` with `epoch`, then wait for every peer's signal on the same channel.

@@ -81,7 +81,7 @@ class Worker:
                  tensors: TensorCommunicationManager, engine_manager, *, node_to_workers: dict[str, list[str]],
                  conductor_id: str = "conductor", api_id: str = "api", tp_followers: list[str] | None = None,
                  is_tp_follower: bool = False, max_batch_size: int = 64, async_gpu: bool = True,
-                 heartbeat_s: float = 0.0, log_stats: bool = False):
+                 heartbeat_s: float = 0.0, log_stats: bool = False, publish_persisted: bool = True):
         self.worker_id, self.rank, self.model = worker_id, rank, model
         # per-request profile (node timings, tensor transfers), collected only when the server logs request statistics
         self.profile = None
@@ -106,6 +106,10 @@ class Worker:
         self._last_arrival = 0.0
         self._by_walk_node: dict[tuple[str, str], dict] = {}       # (node, walk) -> live request states that run it
         self.trace = [] if os.environ.get("MSTAR_TRACE_WORKER") else None
+        # persisted tensors (a prefill's last token, ...) come back through the conductor in a later walk. They only
+        # need to be published for other processes when some node is split over node groups by walk (prefill and
+        # decode on different workers); otherwise the request stays on this worker and the store lookup is local
+        self._publish_persisted = publish_persisted
         self._done_queue: list | None = None      # walk-completion messages held back while a batch is being finished
         self.walks = model.get_graph_walk_graphs()
         self.topology = model.get_partition_topology()
@@ -118,7 +122,8 @@ class Worker:
         # it (speculation: its inputs are the ids that burst N leaves on the device), and codec / encoder batches of
         # other engines are queued as soon as their inputs exist. The GPU goes from one batch to the next without
         # waiting for scheduling, routing or bookkeeping.
-        self.gpu_thread = ThreadPoolExecutor(1, thread_name_prefix=f"{worker_id}-gpu") if async_gpu else None
+        self.gpu_thread = ThreadPoolExecutor(1, thread_name_prefix=f"{worker_id}-gpu",
+                                             initializer=self._bind_device) if async_gpu else None
         self._pipes: dict[int, deque] = {}           # id(engine) -> flights in launch order
         self._next_fid = 0
         lockstep = bool(is_tp_follower or tp_followers)
@@ -445,6 +450,13 @@ class Worker:
         b.partitions = {rk.split("|", 1)[0]: rk.split("|", 1)[1] for rk in rkeys}
         return b
 
+    def _bind_device(self) -> None:
+        """The CUDA current device is a per-thread setting and new threads start on device 0: bind the launch thread
+        to this worker's GPU (kernel launches through the C ABI use the thread's current device and stream)."""
+        dev = next((e.device for e in getattr(self.engines, "engines", []) if e.device.type == "cuda"), None)
+        if dev is not None:
+            torch.cuda.set_device(dev)
+
     def _launch(self, fl: _Flight):
         """Launch thread: queue the batch's GPU work; returns the engine's PendingBatch without waiting for it."""
         eng, batch = fl.engine, fl.batch
@@ -562,7 +574,7 @@ class Worker:
                 # a persisted tensor can be handed by the conductor to ANY worker in a later walk (prefill / decode
                 # split): when some worker lives in another process, publish it now (arena block or CUDA IPC handle),
                 # since only the owner can do that
-                peers = {w for ws_ in self.node_to_workers.values() for w in ws_}
+                peers = {w for ws_ in self.node_to_workers.values() for w in ws_} if self._publish_persisted else ()
                 if any(not self.tensors.is_local(w) for w in peers):
                     e.tensor_info = [self.tensors.prepare_for_remote(ti, "*") for ti in e.tensor_info]
                 pri.persist.setdefault(e.name, []).extend(e.tensor_info)
