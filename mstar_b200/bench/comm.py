@@ -118,7 +118,9 @@ def main():
         dist.all_reduce(y)
         y.add_(res)
     t_nccl = timed(nccl_ar, args.iters, args.warmup, dev)
-    report(path="all-reduce + residual, 64x3072 bf16", ranks=W, ours_us=round(t_ours, 2), nccl_us=round(t_nccl, 2))
+    t_nvls = timed(lambda i: heap.all_reduce_nvls(x, residual=res, out=out), args.iters, args.warmup, dev)
+    report(path="all-reduce + residual, 64x3072 bf16", ranks=W, push_us=round(t_ours, 2), nvls_us=round(t_nvls, 2),
+           nccl_us=round(t_nccl, 2), multicast=bool(heap.mc_ptr))
 
     # ---- DiT-sized all-reduce (the tokens of one sequence-parallel rank x hidden), bandwidth bound ----
     xb = torch.randn(21120, 2048, device=dev).to(torch.bfloat16)
@@ -127,8 +129,13 @@ def main():
     yb = xb.clone()
     t_nccl = timed(lambda i: dist.all_reduce(yb), args.iters, args.warmup, dev)
     link_us = 2 * (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
-    report(path="all-reduce, 21120x2048 bf16", ranks=W, ours_us=round(t_ours, 2), nccl_us=round(t_nccl, 2),
-           roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_ours, 3))
+    t_nvls = timed(lambda i: heap.all_reduce_nvls(xb, out=ob), args.iters, args.warmup, dev)
+    # in-switch reduction: a rank pulls its 1/W share reduced and multicasts it: N/W in and N/W out per GPU... the
+    # slower direction carries (W - 1) / W of the message once
+    nvls_link_us = (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
+    report(path="all-reduce, 21120x2048 bf16", ranks=W, push_us=round(t_ours, 2), nvls_us=round(t_nvls, 2),
+           nccl_us=round(t_nccl, 2), roofline_us=round(nvls_link_us, 2),
+           frac_of_roofline=round(nvls_link_us / min(t_ours, t_nvls), 3), multicast=bool(heap.mc_ptr))
 
     # ---- row-parallel projection: GEMM with the all-reduce in its epilogue (o_proj / down_proj of a decode step) ----
     for (M, N, K, name) in [(64, 3072, 3072 // W, "o_proj"), (64, 3072, 8192 // W, "down_proj")]:
@@ -150,6 +157,58 @@ def main():
         report(path=f"GEMM -> all-reduce fused ({name} {M}x{N}x{K} per rank)", ranks=W, fused_us=round(t_f, 2),
                gemm_plus_nccl_us=round(t_b, 2), gemm_alone_us=round(t_g, 2),
                roofline_us=round(max(link_us, hbm_us), 2), frac_of_roofline=round(max(link_us, hbm_us) / t_f, 3))
+
+    # ---- row-parallel projection whose reduction is done by the consumer: the GEMM writes its partial into a heap
+    # slot, the residual-add + RMSNorm kernel that follows reads every row as a sum over the ranks' slots (in the
+    # switch). Baseline: GEMM, NCCL all-reduce, fused add + norm kernel. ----
+    from ..ops import norm as norm_ops
+    from ..parallel.tp_fused import TPFusedContext
+    tpf = TPFusedContext(heap, 3072, 16384)
+    gamma = torch.ones(3072, device=dev, dtype=torch.bfloat16)
+    for (M, N, K, name) in [(64, 3072, 3072 // W, "o_proj"), (64, 3072, 8192 // W, "down_proj"),
+                            (8192, 3072, 8192 // W, "down_proj prefill")]:
+        xa = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        nw = max(2, (192 << 20) // (N * K * 2) + 1)
+        ws = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(nw)]
+        r2 = torch.randn(M, N, device=dev).to(torch.bfloat16)
+
+        def fused_rrn(i):
+            gemm.linear(xa, ws[i % nw], out=tpf.partial_out(i & 1, M))
+            tpf.reduce_norm(i & 1, M, gamma, 1e-5, r2)
+
+        def base_rrn(i):
+            yy = gemm.linear(xa, ws[i % nw])
+            dist.all_reduce(yy)
+            norm_ops.norm(yy, gamma, 1e-5, residual=r2)
+
+        def alone(i):
+            yy = gemm.linear(xa, ws[i % nw])
+            norm_ops.norm(yy, gamma, 1e-5, residual=r2)
+        t_f = timed(fused_rrn, args.iters, args.warmup, dev)
+        t_b = timed(base_rrn, args.iters, args.warmup, dev)
+        t_1 = timed(alone, args.iters, args.warmup, dev)
+        link_us = M * N * 2 * (W - 1) / W / (LINK_GBS * 1e3)
+        hbm_us = N * K * 2 / (_peaks()[1] * 1e3)
+        flop_us = 2.0 * M * N * K / (tflops * 1e6)
+        roof = max(link_us, hbm_us, flop_us)
+        report(path=f"GEMM -> reduce in the consumer norm ({name} {M}x{N}x{K} per rank)", ranks=W,
+               fused_us=round(t_f, 2), gemm_nccl_norm_us=round(t_b, 2), gemm_norm_no_comm_us=round(t_1, 2),
+               roofline_us=round(roof, 2), frac_of_roofline=round(roof / t_f, 3), multicast=bool(tpf.region.mc_ptr))
+
+    # ---- vocabulary-parallel head: logits shard GEMM + multicast all-gather vs the full head on every rank ----
+    V = 156940
+    tpv = TPFusedContext(heap, 3072, 64, vocab=V, max_logit_rows=64)
+    hrows = torch.randn(64, 3072, device=dev).to(torch.bfloat16)
+    w_sh = (torch.randn(tpv.rows_per_rank, 3072, device=dev) * 0.02).to(torch.bfloat16)
+    w_full = (torch.randn(V, 3072, device=dev) * 0.02).to(torch.bfloat16)
+    t_vp = timed(lambda i: tpv.logits(hrows, w_sh), args.iters, args.warmup, dev)
+    t_full = timed(lambda i: gemm.linear(hrows, w_full), args.iters, args.warmup, dev)
+    hbm_us = tpv.rows_per_rank * 3072 * 2 / (_peaks()[1] * 1e3)
+    link_us = 64 * tpv.rows_per_rank * 2 * (W - 1) / (LINK_GBS * 1e3)
+    report(path=f"vocabulary-parallel head 64x{V}x3072: shard GEMM + multicast all-gather", ranks=W,
+           fused_us=round(t_vp, 2), replicated_head_us=round(t_full, 2), roofline_us=round(max(hbm_us, link_us), 2),
+           frac_of_roofline=round(max(hbm_us, link_us) / t_vp, 3))
+    del w_full
 
     # ---- Ulysses head <-> sequence exchange by peer stores ----
     H, D = 8, 128          # the heads of one tensor-parallel rank (16 heads, tp 2)

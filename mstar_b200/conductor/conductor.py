@@ -97,10 +97,16 @@ class Conductor:
             if any(worker_id_of(r) in self.dead_workers for r in wg.ranks):
                 continue
             groups.setdefault(wg.group_id + "|" + ",".join(wg.graph_walks or []), []).append(wg)
+        # Replicas are picked least-loaded first, with rank affinity across the request's node groups: once one group
+        # of the request sits on some ranks, the other groups prefer their replica on the same ranks (an LLM replica
+        # and the codec replica beside it). The request's streaming edges then stay inside one worker process, and a
+        # worker's codec batches stay in step with its own decode bursts.
+        chosen: set[int] = set()
         for gid, reps in groups.items():
-            best = min(reps, key=lambda w: self.load[w.graph_id])
+            best = min(reps, key=lambda w: (0 if chosen and chosen & set(w.ranks) else 1, self.load[w.graph_id]))
             rd.assigned[best.graph_id] = best
             self.load[best.graph_id] += 1
+            chosen |= set(best.ranks)
 
     def _graphs_for_walk(self, rd: RequestData, walk: str) -> list[WorkerGraph]:
         nodes = set(self.walks[walk].nodes())

@@ -67,8 +67,13 @@ def _param(shape, dtype, device):
     return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=False)
 
 
-def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, tp: CommGroup, bias: torch.Tensor | None = None):
-    """y = all_reduce(x_shard @ w_shard.T): fused into the GEMM epilogue over the symmetric heap when attached."""
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, tp: CommGroup, bias: torch.Tensor | None = None,
+                        partial_out: torch.Tensor | None = None):
+    """y = all_reduce(x_shard @ w_shard.T): fused into the GEMM epilogue over the symmetric heap when attached.
+    With ``partial_out`` (a slot of the symmetric heap) only this rank's partial product is written there and
+    nothing is exchanged: the consumer kernel sums the ranks' slots (``TPFusedContext.reduce_norm``)."""
+    if partial_out is not None:
+        return gemm.linear(x, w, bias=bias if tp.rank == 0 else None, out=partial_out)
     if tp.size == 1:
         return gemm.linear(x, w, bias=bias)
     if tp.symm is not None and x.is_cuda:
@@ -101,7 +106,8 @@ class Attention(nn.Module):
         self.q_norm = _param((self.D,), cfg.dtype, device) if cfg.qk_norm else None
         self.k_norm = _param((self.D,), cfg.dtype, device) if cfg.qk_norm else None
 
-    def forward(self, h: torch.Tensor, ctx: BatchContext, rope: "RopeTables") -> torch.Tensor:
+    def forward(self, h: torch.Tensor, ctx: BatchContext, rope: "RopeTables",
+                partial_out: torch.Tensor | None = None) -> torch.Tensor:
         qkv = gemm.linear(h, self.qkv_proj, bias=self.qkv_bias)
         kv = ctx.kv(self.layer_idx) if ctx.kv_layers else None
         q, _, _ = rope_ops.rope_kv(qkv, ctx.positions, rope.inv_freq, self.Hq, self.Hkv, self.D,
@@ -110,7 +116,8 @@ class Attention(nn.Module):
                                    cache_pos=ctx.cache_pos, page_indptr=ctx.plan.page_indptr,
                                    page_indices=ctx.plan.page_indices)
         a = attn_ops.attention(q, ctx.plan, kv_cache=kv)
-        return row_parallel_linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj, self.tp)
+        return row_parallel_linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj, self.tp,
+                                   partial_out=partial_out)
 
 
 class GatedMLP(nn.Module):
@@ -124,11 +131,11 @@ class GatedMLP(nn.Module):
         self.gate_up_proj = _param((2 * self.F, hidden), dtype, device)
         self.down_proj = _param((hidden, self.F), dtype, device)
 
-    def forward(self, h: torch.Tensor, reduce: bool = True) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, reduce: bool = True, partial_out: torch.Tensor | None = None) -> torch.Tensor:
         g = gemm.linear(h, self.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
         if not reduce:
             return gemm.linear(g, self.down_proj)
-        return row_parallel_linear(g, self.down_proj, self.tp)
+        return row_parallel_linear(g, self.down_proj, self.tp, partial_out=partial_out)
 
 
 class DecoderLayer(nn.Module):
@@ -155,6 +162,17 @@ class DecoderLayer(nn.Module):
         h, residual = norm_ops.norm(a, self.post_attention_layernorm, self.cfg.rms_eps, residual=residual)
         return self.mlp(h), residual
 
+    def forward_tp_fused(self, h: torch.Tensor, residual: torch.Tensor, ctx: BatchContext, rope, tpf, site: int,
+                         gamma_next: torch.Tensor):
+        """Tensor-parallel layer without all-reduce kernels. ``h`` is the normalised input, ``residual`` the residual
+        stream. Both row-parallel GEMMs write partial sums into heap slots; the two norm kernels of the layer (the
+        post-attention norm and the NEXT layer's input norm, ``gamma_next``) sum them across ranks as they read."""
+        M = h.shape[0]
+        self.self_attn(h, ctx, rope, partial_out=tpf.partial_out(site, M))
+        h, residual = tpf.reduce_norm(site, M, self.post_attention_layernorm, self.cfg.rms_eps, residual)
+        self.mlp(h, partial_out=tpf.partial_out(site + 1, M))
+        return tpf.reduce_norm(site + 1, M, gamma_next, self.cfg.rms_eps, residual)
+
 
 class RopeTables:
     def __init__(self, cfg: DecoderConfig, device):
@@ -165,21 +183,43 @@ class RopeTables:
 
 
 class DecoderLM(nn.Module):
-    def __init__(self, cfg: DecoderConfig, tp: CommGroup | None = None, device="cpu"):
+    def __init__(self, cfg: DecoderConfig, tp: CommGroup | None = None, device="cpu", tp_max_tokens: int = 16384 + 256,
+                 tp_max_logit_rows: int = 256):
         super().__init__()
+        import os
         self.cfg = cfg
         self.tp = tp or CommGroup.trivial()
         self.device_ = torch.device(device)
         H, V = cfg.hidden_size, cfg.vocab_size
-        self.embed_tokens = _param((V, H), cfg.dtype, device) if cfg.has_embedding else None
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, self.tp, device) for i in range(cfg.num_layers)])
+        # Tensor-parallel fused path (GPU ranks with a symmetric heap, dense layers): row-parallel GEMMs leave partial
+        # sums in heap slots that the following norm kernels reduce; embedding table and output head are cut by
+        # vocabulary rows. MSTAR_TP_FUSED=0 keeps the all-reduce form (fused GEMM epilogue / NCCL) and full tables.
+        self.tpf = None
+        dense = all(isinstance(layer.mlp, GatedMLP) for layer in self.layers)
+        if (self.tp.size > 1 and getattr(self.tp, "symm", None) is not None and self.device_.type == "cuda" and dense
+                and cfg.dtype == torch.bfloat16 and H % 8 == 0 and os.environ.get("MSTAR_TP_FUSED", "1") != "0"):
+            from ..parallel.tp_fused import TPFusedContext
+            vp = cfg.has_embedding and cfg.has_lm_head and os.environ.get("MSTAR_TP_VOCAB_PARALLEL", "1") != "0"
+            self.tpf = TPFusedContext(self.tp.symm, H, tp_max_tokens, vocab=V if vp else 0,
+                                      max_logit_rows=tp_max_logit_rows if vp else 0)
+        self.vocab_parallel = self.tpf is not None and self.tpf.vocab > 0
+        if self.vocab_parallel:
+            self.embed_tokens = nn.Parameter(self.tpf.alloc_table(), requires_grad=False)
+        else:
+            self.embed_tokens = _param((V, H), cfg.dtype, device) if cfg.has_embedding else None
         self.norm = _param((H,), cfg.dtype, device)
         self._head_packed = None
         self._packed = False
         self.lm_head = None
         if cfg.has_lm_head and not cfg.tie_embeddings:
-            self.lm_head = _param((V, H), cfg.dtype, device)
+            self.lm_head = _param((self.tpf.rows_per_rank if self.vocab_parallel else V, H), cfg.dtype, device)
         self.rope = RopeTables(cfg, device)
+
+    def vocab_rows(self, full: torch.Tensor) -> torch.Tensor:
+        """The rows of a [vocab, hidden] checkpoint tensor that this rank keeps (all of them unless the vocabulary
+        is cut over the tensor-parallel ranks)."""
+        return self.tpf.shard_rows(full) if self.vocab_parallel else full
 
     # ---- weights ----
     @torch.no_grad()
@@ -194,7 +234,7 @@ class DecoderLM(nn.Module):
             return torch.randn(shape, generator=g, dtype=torch.float32) * std
 
         if self.embed_tokens is not None:
-            self.embed_tokens.copy_(draw(self.embed_tokens.shape).to(cfg.dtype))
+            self.embed_tokens.copy_(self.vocab_rows(draw((cfg.vocab_size, cfg.hidden_size)).to(cfg.dtype)))
         Hq, Hkv, D, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_size
         for layer in self.layers:
             at = layer.self_attn
@@ -217,7 +257,11 @@ class DecoderLM(nn.Module):
                 layer.mlp.init_random(g, std)
         self.norm.fill_(1.0)
         if self.lm_head is not None:
-            self.lm_head.copy_(draw(self.lm_head.shape).to(cfg.dtype))
+            self.lm_head.copy_(self.vocab_rows(draw((cfg.vocab_size, cfg.hidden_size)).to(cfg.dtype)))
+        if self.vocab_parallel:
+            torch.cuda.synchronize(self.device_)
+            self.tp.symm.barrier()          # every rank's table shard is in place before anyone gathers from it
+            torch.cuda.synchronize(self.device_)
         return self
 
     def head_weight(self):
@@ -267,10 +311,21 @@ class DecoderLM(nn.Module):
 
     # ---- forward ----
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        if self.vocab_parallel:
+            return self.tpf.embed(input_ids.reshape(-1))
         return ew.embed(input_ids.reshape(-1), self.embed_tokens)
 
     def forward_hidden(self, x: torch.Tensor, ctx: BatchContext) -> torch.Tensor:
         """x: [T, H] input embeddings -> final-normed hidden states [T, H]."""
+        if self.tpf is not None and x.shape[0] <= self.tpf.max_tokens:
+            x = x.reshape(-1, x.shape[-1])
+            residual = x
+            h, _ = norm_ops.norm(x, self.layers[0].input_layernorm, self.cfg.rms_eps)
+            n = len(self.layers)
+            for i, layer in enumerate(self.layers):
+                gamma_next = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
+                h, residual = layer.forward_tp_fused(h, residual, ctx, self.rope, self.tpf, 2 * i, gamma_next)
+            return h
         residual = None
         for layer in self.layers:
             x, residual = layer(x, residual, ctx, self.rope)
@@ -278,6 +333,11 @@ class DecoderLM(nn.Module):
         return h
 
     def logits(self, hidden_rows: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+        if self.vocab_parallel and hidden_rows.shape[0] <= self.tpf.max_logit_rows:
+            return self.tpf.logits(hidden_rows, self.head_weight())      # bf16, padded row pitch
+        if self.vocab_parallel:
+            raise ValueError(f"{hidden_rows.shape[0]} logit rows exceed the vocabulary-parallel logits buffer "
+                             f"({self.tpf.max_logit_rows}): raise tp_max_logit_rows or set MSTAR_TP_VOCAB_PARALLEL=0")
         return gemm.linear(hidden_rows, self.head_weight(), out_dtype=out_dtype)
 
     def forward(self, ctx: BatchContext, input_ids: torch.Tensor | None = None,

@@ -96,7 +96,7 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
                 continue
         if name == head_name:
             if lm.lm_head is not None:
-                lm.lm_head.copy_(t.to(cfg.dtype))
+                lm.lm_head.copy_(lm.vocab_rows(t.to(cfg.dtype)))
                 loaded += 1
             continue
         if not name.startswith(prefix):
@@ -104,7 +104,7 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
         key = name[len(prefix):]
         if key == "embed_tokens.weight":
             if lm.embed_tokens is not None:
-                lm.embed_tokens.copy_(t.to(cfg.dtype))
+                lm.embed_tokens.copy_(lm.vocab_rows(t.to(cfg.dtype)))
                 loaded += 1
             continue
         if key == "norm.weight":
@@ -164,4 +164,8 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
         else:
             continue
         loaded += 1
+    if getattr(lm, "vocab_parallel", False):
+        torch.cuda.synchronize(lm.device_)
+        lm.tp.symm.barrier()            # every rank's table shard is in place before anyone gathers rows from it
+        torch.cuda.synchronize(lm.device_)
     return {"loaded": loaded, "incomplete": [k for k in pend.parts]}

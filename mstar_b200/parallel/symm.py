@@ -21,13 +21,53 @@ import torch.distributed as dist
 from ..ops import _lib
 
 MAX_RANKS = 8
-N_CHANNELS = 1024
+N_CHANNELS = 2048
 # channel map
 CH_ALLREDUCE = 0          # [0, 512): all-reduce CTAs (two rounds of up to 256)
 CH_BARRIER = 512
 CH_A2A = 513              # [513, 521)
 CH_CFG = 528
 CH_GEMM_AR = 544          # [544, 1024): fused GEMM + all-reduce tiles
+CH_NVLS_AR = 1024         # [1024, 1280): NVLS all-reduce CTAs (two rounds of up to 128)
+CH_RRN = 1280             # reduce + residual + norm consumers
+CH_AG = 1296              # [1296, 1424): column all-gather CTAs
+# local state words (pairs of [epoch, arrive]) by user
+ST_AR, ST_BARRIER, ST_A2A, ST_CFG, ST_GEMM_AR, ST_NVLS_AR, ST_RRN, ST_AG = range(8)
+
+
+class SymmRegion:
+    """An additional symmetric allocation of a group (same size on every rank, every rank's copy mapped into every
+    rank, bound to one NVLS multicast object when the box has them). Models carve their tensor-parallel buffers out
+    of regions: partial-sum slots of row-parallel projections, vocabulary shards, gathered logits."""
+
+    def __init__(self, heap: "SymmetricHeap", nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.heap = heap
+        self.nbytes = (nbytes + 4095) // 4096 * 4096
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=heap.device)
+        self.buf.zero_()
+        handle = symm_mem.rendezvous(self.buf, group=heap.group_name)
+        self.handle = handle
+        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.mc_ptr = int(getattr(handle, "multicast_ptr", 0) or 0) if heap.use_multicast else 0
+        self.table = (ctypes.c_void_p * MAX_RANKS)(*([ctypes.c_void_p(p) for p in self.ptrs] + [None] * (MAX_RANKS - heap.world)))
+        self._cursor = 0
+        torch.cuda.synchronize(heap.device)
+        dist.barrier(group=heap.group)
+
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        off = (self._cursor + align - 1) // align * align
+        if off + nbytes > self.nbytes:
+            raise MemoryError("symmetric region exhausted")
+        self._cursor = off + nbytes
+        return off
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.buf[offset:offset + nbytes].view(dtype).view(*shape)
 
 
 class SymmetricHeap:
@@ -42,6 +82,11 @@ class SymmetricHeap:
         self.flag_bytes = N_CHANNELS * MAX_RANKS * 4
         total = 2 * slot_bytes + user_bytes + self.flag_bytes
         gname = group.group_name if hasattr(group, "group_name") else group
+        self.group_name = gname
+        self.group = group
+        # NVLS: on when the rendezvous hands back a multicast address (MSTAR_NVLS=0 forces the plain peer paths)
+        import os
+        self.use_multicast = os.environ.get("MSTAR_NVLS", "1") != "0"
         try:
             symm_mem.enable_symm_mem_for_group(gname)      # needed on older torch, a no-op warning on newer
         except Exception:
@@ -52,6 +97,8 @@ class SymmetricHeap:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         assert len(ptrs) == self.world
         self.base_ptrs = ptrs
+        self.mc_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) if self.use_multicast else 0
+        self.mc_flags = (self.mc_ptr + 2 * slot_bytes + user_bytes) if self.mc_ptr else 0
         self._bufs = (ctypes.c_void_p * MAX_RANKS)(*([ctypes.c_void_p(p) for p in ptrs] + [None] * (MAX_RANKS - self.world)))
         fl = [p + 2 * slot_bytes + user_bytes for p in ptrs]
         self._flags = (ctypes.c_void_p * MAX_RANKS)(*([ctypes.c_void_p(p) for p in fl] + [None] * (MAX_RANKS - self.world)))
@@ -67,7 +114,6 @@ class SymmetricHeap:
             *([ctypes.c_void_p(p + goff) for p in ptrs] + [None] * (MAX_RANKS - self.world)))
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
-        self.group = group
 
     # ---- user region carving (same order on every rank => symmetric offsets) ----
     def alloc_user(self, nbytes: int, align: int = 256) -> int:
@@ -109,14 +155,14 @@ class SymmetricHeap:
             rc = _lib.kernels().mstar_allreduce(
                 self._bufs, self._flags, self.world, self.rank, ctypes.c_void_p(xf[a:b].data_ptr()),
                 ctypes.c_void_p(of[a:b].data_ptr()), ctypes.c_void_p(_lib.ptr(rf[a:b]) if rf is not None else 0),
-                ctypes.c_longlong(b - a), ctypes.c_longlong(self.slot_bytes), self._state_ptr(0), CH_ALLREDUCE, 128,
+                ctypes.c_longlong(b - a), ctypes.c_longlong(self.slot_bytes), self._state_ptr(ST_AR), CH_ALLREDUCE, 128,
                 int(mode), ctypes.c_void_p(_lib.stream_ptr()))
             if rc < 0:
                 _lib.check(rc, "mstar_allreduce")
         return out
 
     def barrier(self) -> None:
-        rc = _lib.kernels().mstar_peer_barrier(self._bufs, self._flags, self.world, self.rank, self._state_ptr(1),
+        rc = _lib.kernels().mstar_peer_barrier(self._bufs, self._flags, self.world, self.rank, self._state_ptr(ST_BARRIER),
                                                CH_BARRIER, ctypes.c_void_p(_lib.stream_ptr()))
         _lib.check(rc, "mstar_peer_barrier")
 
@@ -170,6 +216,81 @@ class SymmetricHeap:
                                                      CH_GEMM_AR)
         _lib.check(rc, "mstar_gemm_arm_allreduce")
         return gemm.linear(x, w, bias=bias if self.rank == 0 else None, residual=residual)
+
+    # ---- NVLS paths (multicast loads / stores through the switch, plain peer accesses as the fallback) ----
+    def new_region(self, nbytes: int) -> SymmRegion:
+        """Collective: every rank of the group calls it with the same size, in the same order."""
+        return SymmRegion(self, nbytes)
+
+    def _mc(self, region: SymmRegion | None):
+        data = region.mc_ptr if region is not None else self.mc_ptr
+        return ctypes.c_void_p(data or None), ctypes.c_void_p(self.mc_flags or None)
+
+    def all_reduce_nvls(self, x: torch.Tensor, residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                        mode: int = 0) -> torch.Tensor:
+        """All-reduce whose additions happen inside the NVSwitch (``multimem.ld_reduce``); two-shot form for large
+        messages multicast-stores each rank's share of the sum to all ranks. Staged through the heap's reduce slots."""
+        assert x.dtype == torch.bfloat16 and x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        n = x.numel()
+        piece = (self.slot_bytes // 4) // 8 * 8            # a slot holds [input | gathered result] of one piece
+        xf, of = x.view(-1), out.view(-1)
+        rf = residual.view(-1) if residual is not None else None
+        mc_data, mc_flags = self._mc(None)
+        for a in range(0, n, piece):
+            b = min(n, a + piece)
+            rc = _lib.kernels().mstar_allreduce_nvls(
+                self._bufs, self._flags, self.world, self.rank, mc_data, mc_flags,
+                ctypes.c_void_p(xf[a:b].data_ptr()), ctypes.c_void_p(of[a:b].data_ptr()),
+                ctypes.c_void_p(_lib.ptr(rf[a:b]) if rf is not None else 0), ctypes.c_longlong(b - a),
+                ctypes.c_longlong(0), ctypes.c_longlong(self.slot_bytes), self._state_ptr(ST_NVLS_AR), CH_NVLS_AR, 128,
+                int(mode), ctypes.c_void_p(_lib.stream_ptr()))
+            if rc < 0:
+                _lib.check(rc, "mstar_allreduce_nvls")
+            _lib._counters.bump()
+        return out
+
+    def reduce_residual_norm(self, region: SymmRegion, slot_off: int, M: int, N: int, gamma: torch.Tensor | None,
+                             eps: float, residual: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                             want_residual: bool = True):
+        """Consumer of a row-parallel projection whose PARTIAL output every rank wrote at ``slot_off`` of its copy of
+        ``region``: sum over ranks (in the switch) + bias + residual -> new residual; RMSNorm -> out. Returns
+        (normalised [M, N], new residual or None)."""
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
+        res_out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device) if want_residual else None
+        mc_data, mc_flags = self._mc(region)
+        rc = _lib.kernels().mstar_reduce_residual_norm(
+            region.table, self._flags, self.world, self.rank, mc_data, mc_flags, ctypes.c_longlong(slot_off), int(M),
+            int(N), ctypes.c_void_p(_lib.ptr(residual)), ctypes.c_void_p(_lib.ptr(res_out)),
+            ctypes.c_void_p(_lib.ptr(gamma)), ctypes.c_void_p(_lib.ptr(bias)), ctypes.c_void_p(out.data_ptr()),
+            ctypes.c_float(eps), self._state_ptr(ST_RRN), CH_RRN, ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_reduce_residual_norm")
+        return out, res_out
+
+    def allgather_cols(self, region: SymmRegion, shard_off: int, full_off: int, M: int, Ns: int) -> None:
+        """Every rank's [M, Ns] shard (at ``shard_off`` of its region copy) lands at columns [rank * Ns, ...) of the
+        [M, world * Ns] matrix at ``full_off`` on every rank."""
+        mc_data, mc_flags = self._mc(region)
+        rc = _lib.kernels().mstar_allgather_cols(region.table, self._flags, self.world, self.rank, mc_data, mc_flags,
+                                                 ctypes.c_longlong(shard_off), ctypes.c_longlong(full_off), int(M),
+                                                 int(Ns), self._state_ptr(ST_AG), CH_AG, 128,
+                                                 ctypes.c_void_p(_lib.stream_ptr()))
+        if rc < 0:
+            _lib.check(rc, "mstar_allgather_cols")
+        _lib._counters.bump()
+
+    def embed_gather(self, region: SymmRegion, table_off: int, rows_per_rank: int, H: int, ids: torch.Tensor,
+                     vocab: int) -> torch.Tensor:
+        """Rows of a vocabulary-parallel embedding table, each loaded from the shard of the rank that owns it."""
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty((flat.numel(), H), dtype=torch.bfloat16, device=self.device)
+        rc = _lib.kernels().mstar_embed_gather_p2p(region.table, self.world, self.rank, ctypes.c_longlong(table_off),
+                                                   int(rows_per_rank), int(H), ctypes.c_void_p(flat.data_ptr()),
+                                                   ctypes.c_void_p(out.data_ptr()), int(flat.numel()), int(vocab),
+                                                   ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_embed_gather_p2p")
+        return out
 
     # ---- table for fused kernels ----
     def tables(self):

@@ -51,6 +51,94 @@ def main():
     out = heap.all_reduce(x)
     check("allreduce vs nccl", (out.float() - y.float()).abs().max().item() < 0.1)
 
+    # ---- NVLS all-reduce (in-switch reduction; plain peer loads when the box has no multicast object) ----
+    for mode, n in [(1, 8), (1, 64 * 3072), (2, 64 * 3072), (2, 1024 * 3072 + 8), (0, 4096 * 1024)]:
+        for it in range(3):
+            gen = torch.Generator().manual_seed(300 * it + n % 89)
+            parts = [torch.randn(n, generator=gen).to(torch.bfloat16) for _ in range(W)]
+            res = torch.randn(n, generator=gen).to(torch.bfloat16).to(dev)
+            out = heap.all_reduce_nvls(parts[R].to(dev), residual=res, mode=mode)
+            ref = sum(p.float() for p in parts) + res.float().cpu()
+            err = (out.float().cpu() - ref).abs().max().item()
+            gathered = [torch.empty_like(out) for _ in range(W)]
+            dist.all_gather(gathered, out)
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            check(f"nvls allreduce mc={bool(heap.mc_ptr)} mode={mode} n={n} it={it} err={err:.3g}",
+                  err < 0.05 * max(1.0, ref.abs().max().item()) and same)
+
+    # ---- row-parallel GEMM partials reduced by the consumer norm kernel, column all-gather, embedding gather ----
+    from mstar_b200.ops import gemm as gemm_ops
+    from mstar_b200.ops import norm as norm_ops
+    from mstar_b200.parallel.tp_fused import TPFusedContext
+    Hh = 512
+    tpf = TPFusedContext(heap, Hh, 512, vocab=1003, max_logit_rows=16)
+    table = tpf.alloc_table()
+    gen = torch.Generator().manual_seed(77)
+    full_table = torch.randn(1003, Hh, generator=gen).to(torch.bfloat16)
+    table.copy_(tpf.shard_rows(full_table).to(dev))
+    torch.cuda.synchronize()
+    heap.barrier()
+    torch.cuda.synchronize()
+    ids = torch.randint(0, 1003, (37,), generator=gen)
+    emb = tpf.embed(ids.to(dev))
+    check("vocabulary-parallel embedding gather", torch.equal(emb.cpu(), full_table[ids]))
+    for it, M in enumerate([1, 64, 300, 64]):
+        gen = torch.Generator().manual_seed(900 + it)
+        K = 256
+        xs = [torch.randn(M, K, generator=gen).to(torch.bfloat16) for _ in range(W)]
+        wsr = [(torch.randn(Hh, K, generator=gen) * 0.05).to(torch.bfloat16) for _ in range(W)]
+        gamma = (1.0 + 0.1 * torch.randn(Hh, generator=gen)).to(torch.bfloat16)
+        res = torch.randn(M, Hh, generator=gen).to(torch.bfloat16)
+        gemm_ops.linear(xs[R].to(dev), wsr[R].to(dev), out=tpf.partial_out(it, M))
+        h, newres = tpf.reduce_norm(it, M, gamma.to(dev), 1e-5, res.to(dev))
+        parts = [(x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, wsr)]
+        tot = (sum(parts) + res.float()).to(torch.bfloat16)
+        href, _ = norm_ops.norm(tot, gamma, 1e-5)
+        e1 = (newres.float().cpu() - tot.float()).abs().max().item()
+        e2 = (h.float().cpu() - href.float()).abs().max().item()
+        check(f"reduce+residual+norm M={M} it={it} err={e1:.3g}/{e2:.3g}",
+              e1 < 0.05 * max(1.0, tot.float().abs().max().item()) and e2 < 0.08)
+    for it, M in enumerate([5, 16]):
+        gen = torch.Generator().manual_seed(950 + it)
+        rows = torch.randn(M, Hh, generator=gen).to(torch.bfloat16)
+        lg = tpf.logits(rows.to(dev), table)
+        ref = rows.float() @ full_table.float().t()
+        err = (lg.float().cpu() - ref).abs().max().item()
+        check(f"vocabulary-parallel logits M={M} shape={tuple(lg.shape)} err={err:.3g}",
+              tuple(lg.shape) == (M, 1003) and err < 0.03 * max(1.0, ref.abs().max().item()))
+
+    # ---- tiny decoder: tensor-parallel fused path (partials reduced in the norms, vocabulary cut by rows) vs the
+    # same weights on one GPU ----
+    from mstar_b200.engine.cache_manager import BatchedCacheManager
+    from mstar_b200.engine.kv_store import KVCacheConfig
+    from mstar_b200.models import tiny
+    lm_tp = tiny.build_tiny(device=dev, dtype=torch.bfloat16, tp=g)
+    lm_1 = tiny.build_tiny(device=dev, dtype=torch.bfloat16)
+    check("tiny decoder took the fused tensor-parallel path", lm_tp.tpf is not None and lm_tp.vocab_parallel)
+    cfg = lm_1.cfg
+    prompts = tiny.synthetic_prompts(3)
+    outs = []
+    for lm, kvh in ((lm_tp, cfg.num_kv_heads // W), (lm_1, cfg.num_kv_heads)):
+        kvc = KVCacheConfig(num_layers=cfg.num_layers, num_kv_heads=kvh, head_dim=cfg.head_dim, max_seq_len=256,
+                            max_num_pages=64, page_size=16, num_qo_heads=cfg.num_heads // (W if lm is lm_tp else 1))
+        cm = BatchedCacheManager(kvc, dev, max_batch=8, max_tokens=512)
+        rids = [f"q{i}" for i in range(len(prompts))]
+        for r_ in rids:
+            cm.add_request(r_)
+        ctx = cm.plan(rids, [len(p) for p in prompts], group=cfg.num_heads // cfg.num_kv_heads)
+        idt = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=dev)
+        lg = lm(ctx, input_ids=idt).float()
+        cm.advance_seq_lens(ctx)
+        nxt = lg.argmax(-1)
+        ctx2 = cm.plan(rids, [1] * len(prompts), group=cfg.num_heads // cfg.num_kv_heads)
+        lg2 = lm(ctx2, input_ids=nxt).float()
+        outs.append((lg.clone(), lg2.clone()))
+    d1 = (outs[0][0] - outs[1][0]).abs().max().item()
+    d2 = (outs[0][1] - outs[1][1]).abs().max().item()
+    scale = outs[1][0].abs().max().item()
+    check(f"tiny decoder TP fused vs one GPU: prefill diff {d1:.3g}, decode diff {d2:.3g} (max |logit| {scale:.3g})",
+          d1 < 0.06 * max(1.0, scale) and d2 < 0.06 * max(1.0, scale))
+
     # ---- fused GEMM + all-reduce epilogue vs GEMM + NCCL all-reduce ----
     from mstar_b200.ops import gemm
     for (M, N, K) in [(64, 3072, 1536), (16, 3072, 4096), (1, 1024, 512), (128, 3072, 1536), (300, 1024, 512)]:
