@@ -194,6 +194,37 @@ def main():
         import gc
         gc.collect()
         torch.cuda.empty_cache()
+        # a communicating arm beside the replicas: the same engine with the model cut over PAIRS of GPUs (tensor
+        # parallel 2: row-parallel partial sums reduced in the consumer norm kernels through NVLS, vocabulary cut by
+        # rows), so that a run at N >= 2 also times the fused compute + collective kernels
+        if world >= 2 and world % 2 == 0 and tp.is_trivial and not os.environ.get("MSTAR_BENCH_NO_TP_ARM"):
+            try:
+                from mstar_b200.parallel.symm import attach_symmetric_heap
+                pairs = [dist.new_group([2 * g_, 2 * g_ + 1]) for g_ in range(world // 2)]
+                tp2 = CommGroup(pairs[rank // 2], [rank // 2 * 2, rank // 2 * 2 + 1], rank)
+                attach_symmetric_heap(tp2, dev)
+                h2 = EngineDecodeHarness(dev, C, max_ctx, tp_group=tp2)
+                g2 = torch.Generator().manual_seed(1234 + rank // 2)
+                pl2 = torch.randint(32, 129, (C,), generator=g2).tolist()
+                dn2 = torch.randint(0, max(1, args.gen_tokens - total_new), (C,), generator=g2).tolist()
+                h2.prefill({f"tp{rank // 2}_{i}": torch.randint(0, vocab, (pl2[i] + dn2[i],), generator=g2).tolist()
+                            for i in range(C)})
+                h2.decode(W)
+                torch.cuda.synchronize()
+                dist.barrier()
+                ms2, _, _ = h2.decode(K)
+                v2 = torch.tensor([ms2], dtype=torch.float64, device=dev)
+                dist.all_reduce(v2, op=dist.ReduceOp.MAX)
+                out["tp2_arm"] = {"parallelism": f"dp{world // 2}xtp2", "ms_per_step": round(float(v2[0]) / K, 4),
+                                  "value": round(world // 2 * C * K / (float(v2[0]) / 1e3), 1), "unit": "tokens/s",
+                                  "multicast": bool(tp2.symm.mc_ptr),
+                                  "kernels": "row-parallel GEMM partials summed by multimem.ld_reduce inside the "
+                                             "residual + RMSNorm kernel; vocabulary-parallel embedding and head"}
+                del h2
+                gc.collect()
+                torch.cuda.empty_cache()
+            except Exception as e:  # noqa: BLE001
+                out["tp2_arm"] = {"error": f"{type(e).__name__}: {e}"}
 
     # ---- (2) end to end through the server ----
     if not args.no_e2e:

@@ -171,10 +171,11 @@ def main():
         nw = max(2, (192 << 20) // (N * K * 2) + 1)
         ws = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(nw)]
         r2 = torch.randn(M, N, device=dev).to(torch.bfloat16)
+        r2s = tpf.residual_rows(r2).contiguous()        # large M: the residual stream is cut by rows
 
         def fused_rrn(i):
             gemm.linear(xa, ws[i % nw], out=tpf.partial_out(i & 1, M))
-            tpf.reduce_norm(i & 1, M, gamma, 1e-5, r2)
+            tpf.reduce_norm(i & 1, M, gamma, 1e-5, r2s)
 
         def base_rrn(i):
             yy = gemm.linear(xa, ws[i % nw])

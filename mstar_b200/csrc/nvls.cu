@@ -94,7 +94,14 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
     // stage my input in my own heap (local stores)
     const uint4* src = reinterpret_cast<const uint4*>(p.in);
     uint4* mine = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[R]) + base);
-    for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) mine[v] = src[v];
+    {
+        long long v = v0 + threadIdx.x;
+        for (; v + 3LL * blockDim.x < v1; v += 4LL * blockDim.x) {
+            const uint4 a0 = src[v], a1 = src[v + blockDim.x], a2 = src[v + 2LL * blockDim.x], a3 = src[v + 3LL * blockDim.x];
+            mine[v] = a0; mine[v + blockDim.x] = a1; mine[v + 2LL * blockDim.x] = a2; mine[v + 3LL * blockDim.x] = a3;
+        }
+        for (; v < v1; v += blockDim.x) mine[v] = src[v];
+    }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -108,6 +115,67 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
             load_sum8(p.t, p.mc, base + v * 16, acc);
             if (p.residual != nullptr) add_bf16x8(acc, reinterpret_cast<const uint4*>(p.residual)[v]);
             reinterpret_cast<uint4*>(p.out)[v] = pack8(acc);
+        }
+    } else if (s_ok && p.mc.data != nullptr) {
+        // two-shot through the switch, four load-reduces in flight per thread (one per trip left the loop bound by
+        // the round trip to the switch). The sum goes straight to every rank's OUTPUT region of the slot.
+        const long long share = (v1 > v0 ? (v1 - v0 + W - 1) / W : 0);
+        const long long a = v0 + (long long)R * share;
+        long long b = a + share;
+        if (b > v1) b = v1;
+        const long long goff = base + p.n * 2;
+        long long v = a + threadIdx.x;
+        for (; v + 3LL * blockDim.x < b; v += 4LL * blockDim.x) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) r[u] = multimem_ld_reduce_bf16x8(p.mc.data + base + (v + (long long)u * blockDim.x) * 16);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) multimem_st_v4(p.mc.data + goff + (v + (long long)u * blockDim.x) * 16, r[u]);
+        }
+        for (; v < b; v += blockDim.x)
+            multimem_st_v4(p.mc.data + goff + v * 16, multimem_ld_reduce_bf16x8(p.mc.data + base + v * 16));
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            signal_all(p.t, p.mc, p.channel_base + gridDim.x + blockIdx.x, epoch);
+            if (!wait_all(p.t, p.channel_base + gridDim.x + blockIdx.x, epoch, p.status, p.wait_limit_ns, 0x12)) s_ok = 0;
+        }
+        __syncthreads();
+        if (s_ok) {
+            const uint4* g = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.t.buf[R]) + goff);
+            const uint4* rs = reinterpret_cast<const uint4*>(p.residual);
+            uint4* o = reinterpret_cast<uint4*>(p.out);
+            long long w = v0 + threadIdx.x;
+            for (; w + 3LL * blockDim.x < v1; w += 4LL * blockDim.x) {
+                uint4 x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) x[u] = __ldcg(g + w + (long long)u * blockDim.x);
+                if (rs != nullptr) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float acc[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                        add_bf16x8(acc, x[u]);
+                        add_bf16x8(acc, rs[w + (long long)u * blockDim.x]);
+                        x[u] = pack8(acc);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) o[w + (long long)u * blockDim.x] = x[u];
+            }
+            for (; w < v1; w += blockDim.x) {
+                uint4 x = __ldcg(g + w);
+                if (rs != nullptr) {
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                    add_bf16x8(acc, x);
+                    add_bf16x8(acc, rs[w]);
+                    x = pack8(acc);
+                }
+                o[w] = x;
+            }
         }
     } else if (s_ok) {
         // my share of this CTA's range: reduce in the switch, hand the sum to every rank's gather half
@@ -174,6 +242,11 @@ struct RRNParams {
     const __nv_bfloat16* gamma;          // [N] or null (null: no normalisation, `out` gets the plain sum)
     __nv_bfloat16* out;                  // [M, N] normalised rows
     const __nv_bfloat16* bias;           // [N] or null, added once
+    // two-shot form (large M): this rank reduces and normalises only rows [row_begin, row_end) and multicast-stores
+    // them into every rank's h buffer at h_off of the region; the residual stream stays cut by rows
+    // (residual_in / residual_out then hold this rank's rows only, row 0 = row_begin). out is unused.
+    int two_shot, row_begin, row_end;
+    long long h_off;
     float eps;
     unsigned int* epoch;
     unsigned int* arrive;
@@ -202,8 +275,11 @@ __global__ void __launch_bounds__(RRN_THREADS) reduce_residual_norm_kernel(const
     }
     __syncthreads();
     const int nvec = p.N >> 3;
+    const int m_first = p.two_shot ? p.row_begin : 0;
+    const int m_last = p.two_shot ? p.row_end : p.M;
     if (s_ok) {
-        for (int m = blockIdx.x; m < p.M; m += gridDim.x) {
+        for (int m = m_first + blockIdx.x; m < m_last; m += gridDim.x) {
+            const size_t lm = (size_t)(m - m_first);      // row index inside the (possibly row-cut) residual tensors
             float x[RRN_MAX_VEC][8];
             float ss = 0.f;
 #pragma unroll
@@ -213,9 +289,9 @@ __global__ void __launch_bounds__(RRN_THREADS) reduce_residual_norm_kernel(const
                     load_sum8(p.t, p.mc, p.slot_off + ((long long)m * p.N + c * 8) * 2, x[i]);
                     if (p.bias != nullptr) add_bf16x8(x[i], reinterpret_cast<const uint4*>(p.bias)[c]);
                     if (p.residual_in != nullptr)
-                        add_bf16x8(x[i], reinterpret_cast<const uint4*>(p.residual_in + (size_t)m * p.N)[c]);
+                        add_bf16x8(x[i], reinterpret_cast<const uint4*>(p.residual_in + lm * p.N)[c]);
                     const uint4 r8 = pack8(x[i]);
-                    if (p.residual_out != nullptr) reinterpret_cast<uint4*>(p.residual_out + (size_t)m * p.N)[c] = r8;
+                    if (p.residual_out != nullptr) reinterpret_cast<uint4*>(p.residual_out + lm * p.N)[c] = r8;
                     // the norm sees the bf16-rounded residual stream, exactly as the unfused add + norm kernels do
                     const uint32_t w[4] = {r8.x, r8.y, r8.z, r8.w};
 #pragma unroll
@@ -227,7 +303,7 @@ __global__ void __launch_bounds__(RRN_THREADS) reduce_residual_norm_kernel(const
                     }
                 }
             }
-            if (p.gamma == nullptr) {
+            if (p.gamma == nullptr && !p.two_shot) {
 #pragma unroll
                 for (int i = 0; i < RRN_MAX_VEC; ++i) {
                     const int c = threadIdx.x + i * RRN_THREADS;
@@ -243,24 +319,53 @@ __global__ void __launch_bounds__(RRN_THREADS) reduce_residual_norm_kernel(const
 #pragma unroll
             for (int i = 0; i < RRN_THREADS / 32; ++i) tot += s_part[i];
             __syncthreads();
-            const float inv = rsqrtf(tot / (float)p.N + p.eps);
+            const float inv = p.gamma != nullptr ? rsqrtf(tot / (float)p.N + p.eps) : 1.f;
 #pragma unroll
             for (int i = 0; i < RRN_MAX_VEC; ++i) {
                 const int c = threadIdx.x + i * RRN_THREADS;
                 if (c < nvec) {
-                    const uint4 g8 = reinterpret_cast<const uint4*>(p.gamma)[c];
-                    const uint32_t gw[4] = {g8.x, g8.y, g8.z, g8.w};
                     float y[8];
+                    if (p.gamma != nullptr) {
+                        const uint4 g8 = reinterpret_cast<const uint4*>(p.gamma)[c];
+                        const uint32_t gw[4] = {g8.x, g8.y, g8.z, g8.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 g = unpack_bf16x2(gw[j]);
-                        y[2 * j] = x[i][2 * j] * inv * g.x;
-                        y[2 * j + 1] = x[i][2 * j + 1] * inv * g.y;
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 g = unpack_bf16x2(gw[j]);
+                            y[2 * j] = x[i][2 * j] * inv * g.x;
+                            y[2 * j + 1] = x[i][2 * j + 1] * inv * g.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) y[j] = x[i][j];
                     }
-                    reinterpret_cast<uint4*>(p.out + (size_t)m * p.N)[c] = pack8(y);
+                    const uint4 o8 = pack8(y);
+                    if (!p.two_shot) {
+                        reinterpret_cast<uint4*>(p.out + (size_t)m * p.N)[c] = o8;
+                    } else {
+                        const long long dst = p.h_off + ((long long)m * p.N + c * 8) * 2;
+                        if (p.mc.data != nullptr) {
+                            multimem_st_v4(p.mc.data + dst, o8);
+                        } else {
+                            for (int q = 0; q < p.t.world; ++q)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + dst) = o8;
+                        }
+                    }
                 }
             }
         }
+    }
+    if (p.two_shot) {
+        // second flag round: every rank's rows of h are in place on this rank before the kernel (and with it the
+        // stream) moves on to the GEMM that reads them
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0 && s_ok) {
+            // block b of every rank signals on channel + 1 + b and waits for block b of the peers; all ranks launch the
+            // same grid, so when all blocks of this rank are through, all blocks of all peers have stored their rows
+            signal_all(p.t, p.mc, p.channel + 1 + blockIdx.x, epoch);
+            if (!wait_all(p.t, p.channel + 1 + blockIdx.x, epoch, p.status, p.wait_limit_ns, 0x23)) s_ok = 0;
+        }
+        __syncthreads();
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -412,9 +517,11 @@ MSTAR_API int mstar_allreduce_nvls(void* const* bufs, void* const* flags, int wo
     return (int)ctas;
 }
 
+// two_shot != 0: rows [row_begin, row_end) are this rank's; normalised rows go to h_off of every rank's region copy.
 MSTAR_API int mstar_reduce_residual_norm(void* const* bufs, void* const* flags, int world, int rank, void* mc_data,
                                          void* mc_flags, long long slot_off, int M, int N, const void* residual_in,
                                          void* residual_out, const void* gamma, const void* bias, void* out, float eps,
+                                         int two_shot, int row_begin, int row_end, long long h_off,
                                          void* state, int channel, void* stream_) {
     if (M <= 0) return 0;
     if (N % 8 || N > RRN_THREADS * RRN_MAX_VEC * 8)
@@ -429,13 +536,21 @@ MSTAR_API int mstar_reduce_residual_norm(void* const* bufs, void* const* flags, 
     p.bias = (const __nv_bfloat16*)bias;
     p.out = (__nv_bfloat16*)out;
     p.eps = eps;
+    p.two_shot = two_shot ? 1 : 0;
+    p.row_begin = row_begin;
+    p.row_end = row_end;
+    p.h_off = h_off;
     p.epoch = reinterpret_cast<unsigned int*>(state);
     p.arrive = p.epoch + 1;
     p.channel = channel;
     p.status = status_ptr();
     p.wait_limit_ns = wait_limit_ns();
-    const int cap = 4 * device_sm_count();
-    const int grid = M < cap ? M : cap;
+    // the two-shot form uses one flag channel per block and needs the same grid on every rank: it is sized from the
+    // largest row share, ceil(M / world), not from this rank's own share
+    const int rows = two_shot ? (M + world - 1) / world : M;
+    const int cap = two_shot ? 128 : 4 * device_sm_count();
+    int grid = rows < cap ? rows : cap;
+    if (grid < 1) grid = 1;
     cudaError_t e = launch_pdl(reduce_residual_norm_kernel, dim3(grid), dim3(RRN_THREADS), 0, (cudaStream_t)stream_, p);
     return e == cudaSuccess ? 0 : set_error("reduce_residual_norm launch", e);
 }

@@ -319,7 +319,7 @@ class DecoderLM(nn.Module):
         """x: [T, H] input embeddings -> final-normed hidden states [T, H]."""
         if self.tpf is not None and x.shape[0] <= self.tpf.max_tokens:
             x = x.reshape(-1, x.shape[-1])
-            residual = x
+            residual = self.tpf.residual_rows(x)
             h, _ = norm_ops.norm(x, self.layers[0].input_layernorm, self.cfg.rms_eps)
             n = len(self.layers)
             for i, layer in enumerate(self.layers):

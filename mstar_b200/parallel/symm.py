@@ -29,8 +29,8 @@ CH_A2A = 513              # [513, 521)
 CH_CFG = 528
 CH_GEMM_AR = 544          # [544, 1024): fused GEMM + all-reduce tiles
 CH_NVLS_AR = 1024         # [1024, 1280): NVLS all-reduce CTAs (two rounds of up to 128)
-CH_RRN = 1280             # reduce + residual + norm consumers
-CH_AG = 1296              # [1296, 1424): column all-gather CTAs
+CH_RRN = 1280             # [1280, 1409): reduce + residual + norm consumers (1 + up to 128 blocks of the two-shot form)
+CH_AG = 1536              # [1536, 1664): column all-gather CTAs
 # local state words (pairs of [epoch, arrive]) by user
 ST_AR, ST_BARRIER, ST_A2A, ST_CFG, ST_GEMM_AR, ST_NVLS_AR, ST_RRN, ST_AG = range(8)
 
@@ -251,20 +251,36 @@ class SymmetricHeap:
             _lib._counters.bump()
         return out
 
+    def row_share(self, M: int) -> tuple[int, int]:
+        """Rows [a, b) of an M-row activation that this rank owns in the two-shot (row-cut) forms."""
+        per = (M + self.world - 1) // self.world
+        a = min(M, self.rank * per)
+        return a, min(M, a + per)
+
     def reduce_residual_norm(self, region: SymmRegion, slot_off: int, M: int, N: int, gamma: torch.Tensor | None,
                              eps: float, residual: torch.Tensor | None = None, bias: torch.Tensor | None = None,
-                             want_residual: bool = True):
+                             want_residual: bool = True, h_off: int | None = None):
         """Consumer of a row-parallel projection whose PARTIAL output every rank wrote at ``slot_off`` of its copy of
         ``region``: sum over ranks (in the switch) + bias + residual -> new residual; RMSNorm -> out. Returns
-        (normalised [M, N], new residual or None)."""
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-        res_out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device) if want_residual else None
+        (normalised [M, N], new residual or None).
+
+        With ``h_off`` (two-shot form, for large M): this rank reduces and normalises only its row share
+        (``row_share``), multicast-stores the rows into the [M, N] buffer at ``h_off`` of every rank's region copy,
+        and waits until the peers' rows are in its own copy. ``residual`` and the returned residual then hold this
+        rank's rows only (the residual stream stays cut by rows); the returned ``out`` is the local view at
+        ``h_off``."""
+        two_shot = h_off is not None
+        a, b = self.row_share(M) if two_shot else (0, M)
+        out = region.view(h_off, (M, N), torch.bfloat16) if two_shot else \
+            torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
+        res_out = torch.empty((b - a, N), dtype=torch.bfloat16, device=self.device) if want_residual else None
         mc_data, mc_flags = self._mc(region)
         rc = _lib.kernels().mstar_reduce_residual_norm(
             region.table, self._flags, self.world, self.rank, mc_data, mc_flags, ctypes.c_longlong(slot_off), int(M),
             int(N), ctypes.c_void_p(_lib.ptr(residual)), ctypes.c_void_p(_lib.ptr(res_out)),
-            ctypes.c_void_p(_lib.ptr(gamma)), ctypes.c_void_p(_lib.ptr(bias)), ctypes.c_void_p(out.data_ptr()),
-            ctypes.c_float(eps), self._state_ptr(ST_RRN), CH_RRN, ctypes.c_void_p(_lib.stream_ptr()))
+            ctypes.c_void_p(_lib.ptr(gamma)), ctypes.c_void_p(_lib.ptr(bias)),
+            ctypes.c_void_p(0 if two_shot else out.data_ptr()), ctypes.c_float(eps), 1 if two_shot else 0, int(a),
+            int(b), ctypes.c_longlong(h_off or 0), self._state_ptr(ST_RRN), CH_RRN, ctypes.c_void_p(_lib.stream_ptr()))
         _lib.check(rc, "mstar_reduce_residual_norm")
         return out, res_out
 

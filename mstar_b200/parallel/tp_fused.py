@@ -22,6 +22,8 @@ import torch
 
 
 class TPFusedContext:
+    TWO_SHOT_ROWS = 1024      # from this many rows on, the consumer norm reduces row shares and all-gathers them
+
     def __init__(self, symm, hidden: int, max_tokens: int, *, vocab: int = 0, max_logit_rows: int = 0):
         self.symm, self.hidden, self.max_tokens = symm, hidden, max_tokens
         self.world, self.rank = symm.world, symm.rank
@@ -31,8 +33,9 @@ class TPFusedContext:
         logit_bytes = 0
         if vocab and max_logit_rows:
             logit_bytes = max_logit_rows * self.rows_per_rank * 2 * (1 + self.world) + 1024
-        self.region = symm.new_region(2 * slot + logit_bytes + 1024)
+        self.region = symm.new_region(3 * slot + logit_bytes + 2048)
         self.slot_off = [self.region.alloc(slot), self.region.alloc(slot)]
+        self.h_off = self.region.alloc(slot)        # gathered normalised activations of the two-shot form
         self.max_logit_rows = max_logit_rows
         if logit_bytes:
             self.logit_shard_off = self.region.alloc(max_logit_rows * self.rows_per_rank * 2)
@@ -48,10 +51,23 @@ class TPFusedContext:
             raise ValueError(f"{M} x {N} does not fit the tensor-parallel slots ({self.max_tokens} x {self.hidden})")
         return self.region.view(self.slot_off[site & 1], (M, N), torch.bfloat16)
 
+    def two_shot(self, M: int) -> bool:
+        return M >= self.TWO_SHOT_ROWS
+
+    def residual_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """The rows of a full [M, hidden] activation that enter the residual stream on this rank: all of them in the
+        one-shot form, this rank's row share in the two-shot form."""
+        if not self.two_shot(x.shape[0]):
+            return x
+        a, b = self.symm.row_share(x.shape[0])
+        return x[a:b]
+
     def reduce_norm(self, site: int, M: int, gamma, eps: float, residual, bias=None):
-        """(RMSNorm(sum over ranks + bias + residual), sum + bias + residual)."""
+        """(RMSNorm(sum over ranks + bias + residual), sum + bias + residual). For large M the residual is this
+        rank's row share and the normalised rows are gathered from all ranks (see ``reduce_residual_norm``)."""
         return self.symm.reduce_residual_norm(self.region, self.slot_off[site & 1], M, self.hidden, gamma, eps,
-                                              residual=residual, bias=bias)
+                                              residual=residual, bias=bias,
+                                              h_off=self.h_off if self.two_shot(M) else None)
 
     # ---- vocabulary-parallel embedding and head ----
     def alloc_table(self) -> torch.Tensor:

@@ -71,7 +71,7 @@ def main():
     from mstar_b200.ops import norm as norm_ops
     from mstar_b200.parallel.tp_fused import TPFusedContext
     Hh = 512
-    tpf = TPFusedContext(heap, Hh, 512, vocab=1003, max_logit_rows=16)
+    tpf = TPFusedContext(heap, Hh, 2048, vocab=1003, max_logit_rows=16)
     table = tpf.alloc_table()
     gen = torch.Generator().manual_seed(77)
     full_table = torch.randn(1003, Hh, generator=gen).to(torch.bfloat16)
@@ -82,7 +82,7 @@ def main():
     ids = torch.randint(0, 1003, (37,), generator=gen)
     emb = tpf.embed(ids.to(dev))
     check("vocabulary-parallel embedding gather", torch.equal(emb.cpu(), full_table[ids]))
-    for it, M in enumerate([1, 64, 300, 64]):
+    for it, M in enumerate([1, 64, 300, 64, 1537, 1536, 2048]):
         gen = torch.Generator().manual_seed(900 + it)
         K = 256
         xs = [torch.randn(M, K, generator=gen).to(torch.bfloat16) for _ in range(W)]
@@ -90,13 +90,16 @@ def main():
         gamma = (1.0 + 0.1 * torch.randn(Hh, generator=gen)).to(torch.bfloat16)
         res = torch.randn(M, Hh, generator=gen).to(torch.bfloat16)
         gemm_ops.linear(xs[R].to(dev), wsr[R].to(dev), out=tpf.partial_out(it, M))
-        h, newres = tpf.reduce_norm(it, M, gamma.to(dev), 1e-5, res.to(dev))
+        # large M takes the two-shot form: the residual stream is cut by rows, the normalised rows are gathered
+        ra, rb = heap.row_share(M) if tpf.two_shot(M) else (0, M)
+        h, newres = tpf.reduce_norm(it, M, gamma.to(dev), 1e-5, res[ra:rb].contiguous().to(dev))
+        h = h.clone()
         parts = [(x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, wsr)]
         tot = (sum(parts) + res.float()).to(torch.bfloat16)
         href, _ = norm_ops.norm(tot, gamma, 1e-5)
-        e1 = (newres.float().cpu() - tot.float()).abs().max().item()
+        e1 = (newres.float().cpu() - tot[ra:rb].float()).abs().max().item()
         e2 = (h.float().cpu() - href.float()).abs().max().item()
-        check(f"reduce+residual+norm M={M} it={it} err={e1:.3g}/{e2:.3g}",
+        check(f"reduce+residual+norm M={M} two_shot={tpf.two_shot(M)} it={it} err={e1:.3g}/{e2:.3g}",
               e1 < 0.05 * max(1.0, tot.float().abs().max().item()) and e2 < 0.08)
     for it, M in enumerate([5, 16]):
         gen = torch.Generator().manual_seed(950 + it)
@@ -133,6 +136,18 @@ def main():
         ctx2 = cm.plan(rids, [1] * len(prompts), group=cfg.num_heads // cfg.num_kv_heads)
         lg2 = lm(ctx2, input_ids=nxt).float()
         outs.append((lg.clone(), lg2.clone()))
+    long_ids = torch.randint(0, cfg.vocab_size, (1100,), generator=torch.Generator().manual_seed(3)).tolist()
+    lgs = []
+    for lm, kvh in ((lm_tp, cfg.num_kv_heads // W), (lm_1, cfg.num_kv_heads)):
+        kvc = KVCacheConfig(num_layers=cfg.num_layers, num_kv_heads=kvh, head_dim=cfg.head_dim, max_seq_len=2048,
+                            max_num_pages=128, page_size=16, num_qo_heads=cfg.num_heads // (W if lm is lm_tp else 1))
+        cm = BatchedCacheManager(kvc, dev, max_batch=8, max_tokens=2048)
+        cm.add_request("long")
+        ctxl = cm.plan(["long"], [len(long_ids)], group=cfg.num_heads // cfg.num_kv_heads)
+        lgs.append(lm(ctxl, input_ids=torch.tensor(long_ids, dtype=torch.int64, device=dev)).float().clone())
+    dl = (lgs[0] - lgs[1]).abs().max().item()
+    check(f"tiny decoder TP fused, 1100-token prefill (row-cut residual stream): diff {dl:.3g}",
+          dl < 0.06 * max(1.0, lgs[1].abs().max().item()))
     d1 = (outs[0][0] - outs[1][0]).abs().max().item()
     d2 = (outs[0][1] - outs[1][1]).abs().max().item()
     scale = outs[1][0].abs().max().item()
