@@ -24,6 +24,74 @@ from .openai.protocol import (ChatCompletionRequest, ImageGenerationRequest, Mod
 from .server import APIServer
 
 
+DIRECT_STREAM_EXT = "mstar.direct_stream"
+
+
+class ChunkStream(Response):
+    """Streaming reply built from a request's result chunks. ``fmt(chunk)`` returns the pieces (bytes) a chunk turns
+    into and whether the stream ends with it; ``head`` / ``tail`` frame the stream.
+
+    Under a transport that offers the ``mstar.direct_stream`` ASGI extension (the C++ frontend's bridge) the pieces
+    are handed to the transport on the thread that received them from the workers: between the reply's start and
+    its end the event loop does nothing for this stream. Any other ASGI server gets an ordinary async body iterator.
+    """
+
+    def __init__(self, server: APIServer, rid: str, fmt, media_type: str, head=(), tail=()):
+        super().__init__(content=None, media_type=media_type)
+        self.raw_headers = [h for h in self.raw_headers if h[0] != b"content-length"]
+        self.server, self.rid, self.fmt, self.head, self.tail = server, rid, fmt, list(head), tail
+
+    async def _body(self):
+        for piece in self.head:
+            yield piece
+        async for c in self.server.aiter_result_chunks(self.rid):
+            pieces, last = self.fmt(c)
+            for piece in pieces:
+                yield piece
+            if last:
+                break
+        for piece in (self.tail() if callable(self.tail) else self.tail):
+            yield piece
+
+    async def __call__(self, scope, receive, send):
+        direct = (scope.get("extensions") or {}).get(DIRECT_STREAM_EXT)
+        if direct is None:
+            resp = StreamingResponse(self._body(), media_type=self.media_type)
+            await resp(scope, receive, send)
+            return
+        import asyncio
+        loop, done = asyncio.get_running_loop(), asyncio.Event()
+        await send({"type": "http.response.start", "status": 200, "headers": self.raw_headers})
+        for piece in self.head:
+            direct(piece)
+        state = {"open": True}
+
+        def sink(c):                    # runs on the server's result thread
+            if not state["open"]:
+                return
+            last = True
+            if c.modality != "done":
+                pieces, last = self.fmt(c)
+                for piece in pieces:
+                    direct(piece)
+                last = last or c.final
+            if last:
+                state["open"] = False
+                for piece in (self.tail() if callable(self.tail) else self.tail):
+                    direct(piece)
+                loop.call_soon_threadsafe(done.set)
+        self.server.attach_sink(self.rid, sink)
+        try:
+            await done.wait()
+        except asyncio.CancelledError:  # the client went away: stop generating for it
+            state["open"] = False
+            self.server.abort_request(self.rid)
+            raise
+        finally:
+            self.server.detach_sink(self.rid)
+        await send({"type": "http.response.body", "body": b"", "more_body": False})
+
+
 def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
     app = FastAPI(title="mstar-b200")
     app.add_middleware(CORSMiddleware, allow_origins=["*"], allow_methods=["*"], allow_headers=["*"])
@@ -91,13 +159,12 @@ def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
                 raise HTTPException(400, f"unknown modality {m!r}")
         rid = server.submit_request(text, blobs, in_mods, out_mods, kw, request_id)
         if streaming:
-            def gen():
-                for c in server.iter_result_chunks(rid):
-                    d = {"modality": c.modality, "data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
-                    if c.error_status:
-                        d["error_status"] = c.error_status
-                    yield json.dumps(d) + "\n"
-            return StreamingResponse(gen(), media_type="application/x-ndjson")
+            def fmt(c):
+                d = {"modality": c.modality, "data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
+                if c.error_status:
+                    d["error_status"] = c.error_status
+                return [(json.dumps(d) + "\n").encode()], False
+            return ChunkStream(server, rid, fmt, "application/x-ndjson")
         res = _collect(rid)
         return {"request_id": rid, "outputs": {m: [{"data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
                                                    for c in cs] for m, cs in res.items()}}
@@ -115,28 +182,27 @@ def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
         cid, created = "chatcmpl-" + rid[:24], int(time.time())
         sr = server.model.get_output_sample_rate()
         if req.stream:
-            def sse():
-                first = True
-                for c in server.iter_result_chunks(rid):
-                    if c.modality == "error":
-                        yield f"data: {json.dumps({'error': {'message': c.data.decode(errors='replace'), 'code': c.error_status}})}\n\n"
-                        break
-                    delta = {"role": "assistant"} if first else {}
-                    first = False
-                    if c.modality == "text":
-                        delta["content"] = c.data.decode(errors="replace")
-                    elif c.modality == "audio":
-                        delta["audio"] = {"id": cid, "data": base64.b64encode(c.data).decode()}
-                    elif c.modality == "image":
-                        delta["content"] = [{"type": "image_url", "image_url": {"url": png_to_data_url(c.data)}}]
-                    yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                                 "model": model_name, "choices": [{"index": 0, "delta": delta,
-                                                                                   "finish_reason": None}]}) + "\n\n"
-                yield "data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
-                                             "model": model_name, "choices": [{"index": 0, "delta": {},
-                                                                               "finish_reason": "stop"}]}) + "\n\n"
-                yield "data: [DONE]\n\n"
-            return StreamingResponse(sse(), media_type="text/event-stream")
+            st = {"first": True}
+
+            def fmt(c):
+                if c.modality == "error":
+                    return [f"data: {json.dumps({'error': {'message': c.data.decode(errors='replace'), 'code': c.error_status}})}\n\n".encode()], True
+                delta = {"role": "assistant"} if st["first"] else {}
+                st["first"] = False
+                if c.modality == "text":
+                    delta["content"] = c.data.decode(errors="replace")
+                elif c.modality == "audio":
+                    delta["audio"] = {"id": cid, "data": base64.b64encode(c.data).decode()}
+                elif c.modality == "image":
+                    delta["content"] = [{"type": "image_url", "image_url": {"url": png_to_data_url(c.data)}}]
+                return [("data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                                "model": model_name, "choices": [{"index": 0, "delta": delta,
+                                                                                  "finish_reason": None}]}) + "\n\n").encode()], False
+            tail = [("data: " + json.dumps({"id": cid, "object": "chat.completion.chunk", "created": created,
+                                            "model": model_name, "choices": [{"index": 0, "delta": {},
+                                                                              "finish_reason": "stop"}]}) + "\n\n").encode(),
+                    b"data: [DONE]\n\n"]
+            return ChunkStream(server, rid, fmt, "text/event-stream", tail=tail)
         res = _collect(rid)
         msg: dict = {"role": "assistant", "content": b"".join(c.data for c in res.get("text", [])).decode(errors="replace")}
         if "audio" in res:
@@ -158,13 +224,10 @@ def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
             if req.response_format not in ("wav", "pcm"):
                 raise HTTPException(422, "streaming supports wav and pcm only")
 
-            def stream():
-                if req.response_format == "wav":
-                    yield wav_header(sr, ch, None)
-                for c in server.iter_result_chunks(rid):
-                    if c.modality == "audio":
-                        yield c.data
-            return StreamingResponse(stream(), media_type="audio/wav" if req.response_format == "wav" else "audio/pcm")
+            def fmt(c):
+                return ([bytes(c.data)] if c.modality == "audio" and c.data else []), False
+            return ChunkStream(server, rid, fmt, "audio/wav" if req.response_format == "wav" else "audio/pcm",
+                               head=[wav_header(sr, ch, None)] if req.response_format == "wav" else [])
         res = _collect(rid)
         pcm = b"".join(c.data for c in res.get("audio", []))
         try:

@@ -47,6 +47,10 @@ def wav_header(sample_rate: int, channels: int = 1, n_bytes: int | None = None) 
 
 
 def float_to_pcm16(x: torch.Tensor) -> bytes:
+    if x.dtype == torch.int16:          # already quantised by the producer
+        if x.device.type != "cpu" or not x.is_contiguous():
+            x = x.detach().cpu().contiguous()
+        return x.numpy().tobytes()
     return (x.detach().float().clamp(-1, 1) * 32767.0).round().to(torch.int16).cpu().numpy().tobytes()
 
 

@@ -166,6 +166,15 @@ class NativeFrontend:
         head = json.dumps({"id": rid, "kind": kind, **extra}, separators=(",", ":")).encode() + b"\n"
         self.mesh.send("frontend", head + payload)
 
+    def _direct(self, rid: int):
+        head = json.dumps({"id": rid, "kind": "chunk"}, separators=(",", ":")).encode() + b"\n"
+        send = self.mesh.send
+
+        def push(piece: bytes) -> None:
+            if piece:
+                send("frontend", head + piece)
+        return push
+
     async def _serve(self, rid: int, hdr: dict, body: bytes):
         headers = [(b"host", f"{self.host}:{self.port}".encode()), (b"content-length", str(len(body)).encode())]
         if hdr.get("content_type"):
@@ -173,7 +182,9 @@ class NativeFrontend:
         scope = {"type": "http", "asgi": {"version": "3.0"}, "http_version": "1.1", "method": hdr["method"],
                  "scheme": "http", "path": hdr["path"], "raw_path": hdr["path"].encode(),
                  "query_string": hdr.get("query", "").encode(), "headers": headers, "client": ("frontend", 0),
-                 "server": (self.host, self.port), "root_path": ""}
+                 "server": (self.host, self.port), "root_path": "",
+                 # body pieces may be pushed from any thread, straight to the frontend process
+                 "extensions": {"mstar.direct_stream": self._direct(rid)}}
         sent_body = False
         disconnected = asyncio.Event()
 

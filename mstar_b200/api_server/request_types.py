@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import queue
+import threading
 import time
 from dataclasses import dataclass, field
 
@@ -22,6 +23,9 @@ class PendingRequest:
     model_kwargs: dict
     chunks: "queue.Queue[ResultChunk]" = field(default_factory=queue.Queue)
     done: bool = False
+    wake: object = None                 # callable set by an event-loop consumer parked on an empty queue
+    sink: object = None                 # callable(ResultChunk): chunks bypass the queue and go straight to the transport
+    lock: threading.Lock = field(default_factory=threading.Lock, repr=False)
     t_submit: float = field(default_factory=time.time)
     t_first_chunk: float | None = None
     t_last_chunk: float | None = None

@@ -126,11 +126,45 @@ class APIServer:
         self._finish(pr, ResultChunk("error", b"aborted", final=True, error_status=499))
 
     # ---- results ----
+    @staticmethod
+    def _put(pr: PendingRequest, chunk: ResultChunk) -> None:
+        with pr.lock:
+            if pr.sink is not None:     # a transport took this request over: no queue, no thread hop
+                pr.sink(chunk)
+                return
+            pr.chunks.put(chunk)
+        wake = pr.wake                  # set by an event-loop consumer that found the queue empty
+        if wake is not None:
+            pr.wake = None
+            wake()
+
+    def attach_sink(self, request_id: str, sink) -> None:
+        """From now on every chunk of the request (the terminal one included) is handed to ``sink`` on the thread
+        that produced it, in order, after whatever was already queued. ``sink`` must not block for long."""
+        with self.lock:
+            pr = self.pending.get(request_id)
+        if pr is None:
+            raise KeyError(request_id)
+        with pr.lock:
+            while True:
+                try:
+                    sink(pr.chunks.get_nowait())
+                except queue.Empty:
+                    break
+            pr.sink = sink
+
+    def detach_sink(self, request_id: str) -> None:
+        with self.lock:
+            pr = self.pending.get(request_id)
+        if pr is not None:
+            with pr.lock:
+                pr.sink = None
+
     def _finish(self, pr: PendingRequest, last: ResultChunk | None = None) -> None:
         if pr.done:
             return
         pr.done = True
-        pr.chunks.put(last or ResultChunk("done", final=True))
+        self._put(pr, last or ResultChunk("done", final=True))
         self.tensors.remove_request(pr.request_id)
 
     def _process_messages(self) -> None:
@@ -149,28 +183,33 @@ class APIServer:
         if m.type == AM.SETUP_DONE:
             self.ready.set()
             return
+        if m.type == AM.RESULT_TENSORS_BATCH:
+            acks: dict[str, list] = {}
+            try:
+                for rt in m.body.items:
+                    try:
+                        self._handle_result(rt, acks)
+                    except Exception:  # noqa: BLE001
+                        log.exception("api: result of %s failed", rt.request_id)
+            finally:
+                for src, items in acks.items():
+                    self.comm.send(src, Message(ipc.WorkerMessageType.TENSOR_RECEIVED_BATCH,
+                                                ipc.TensorReceivedBatch(items)))
+            return
         b = m.body
         with self.lock:
             pr = self.pending.get(b.request_id)
-        if pr is None or pr.done:
-            if m.type == AM.RESULT_TENSORS and b.source_entity:     # still acknowledge, so the producer frees them
-                self.comm.send(b.source_entity, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, ipc.TensorReceived(
-                    b.request_id + "#emit", {ti.uuid: 1 for ti in b.tensors})))
-            return
         if m.type == AM.RESULT_TENSORS:
-            ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
-            data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
-            pr.t_last_chunk = time.time()
-            if pr.t_first_chunk is None:
-                pr.t_first_chunk = pr.t_last_chunk
-            rec = pr.outputs.setdefault(b.modality, [0, 0])
-            rec[0] += 1
-            rec[1] += len(data) if isinstance(data, (bytes, bytearray)) else 0
-            pr.chunks.put(ResultChunk(b.modality, data, dict(b.metadata)))
-            if b.source_entity:
-                self.comm.send(b.source_entity, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, ipc.TensorReceived(
-                    b.request_id + "#emit", {ti.uuid: 1 for ti in b.tensors})))
-        elif m.type == AM.REQUEST_COMPLETE:
+            acks = {}
+            try:
+                self._handle_result(b, acks)
+            finally:
+                for src, items in acks.items():
+                    self.comm.send(src, Message(ipc.WorkerMessageType.TENSOR_RECEIVED, items[0]))
+            return
+        if pr is None or pr.done:
+            return
+        if m.type == AM.REQUEST_COMPLETE:
             pr.profile = b.profile
             self.stats["completed"] += 1
             if self.log_stats:
@@ -180,6 +219,26 @@ class APIServer:
         elif m.type == AM.REQUEST_FAILED:
             self.stats["failed"] += 1
             self._finish(pr, ResultChunk("error", b.error_message.encode(), final=True, error_status=b.status))
+
+    def _handle_result(self, b, acks: dict) -> None:
+        """One request's client-bound tensors: read, convert with the model's ``postprocess``, hand to the client.
+        The acknowledgement that lets the producer free them is collected in ``acks`` (also when nobody waits)."""
+        if b.source_entity:
+            acks.setdefault(b.source_entity, []).append(
+                ipc.TensorReceived(b.request_id + "#emit", {ti.uuid: 1 for ti in b.tensors}))
+        with self.lock:
+            pr = self.pending.get(b.request_id)
+        if pr is None or pr.done:
+            return
+        ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
+        data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
+        pr.t_last_chunk = time.time()
+        if pr.t_first_chunk is None:
+            pr.t_first_chunk = pr.t_last_chunk
+        rec = pr.outputs.setdefault(b.modality, [0, 0])
+        rec[0] += 1
+        rec[1] += len(data) if isinstance(data, (bytes, bytearray)) else 0
+        self._put(pr, ResultChunk(b.modality, data, dict(b.metadata)))
 
     def request_profile(self, pr: PendingRequest):
         """The whole-request profile: this server's own timestamps and byte counts, the conductor's admission and
@@ -225,6 +284,41 @@ class APIServer:
                     self.abort_request(request_id)
                     yield ResultChunk("error", b"request timed out", final=True, error_status=500)
                     return
+                continue
+            if c.modality == "done":
+                return
+            yield c
+            if c.final:
+                return
+
+    async def aiter_result_chunks(self, request_id: str, timeout_s: float | None = None):
+        """``iter_result_chunks`` for an event loop: the consumer takes what is queued and otherwise parks on a loop
+        event that the result thread sets, so a stream holds no thread of the server's pool between chunks."""
+        import asyncio
+        with self.lock:
+            pr = self.pending.get(request_id)
+        if pr is None:
+            raise KeyError(request_id)
+        loop = asyncio.get_running_loop()
+        deadline = time.time() + (timeout_s or self.request_timeout_s)
+        ev = asyncio.Event()
+        wake = lambda: loop.call_soon_threadsafe(ev.set)   # noqa: E731
+        while True:
+            try:
+                c = pr.chunks.get_nowait()
+            except queue.Empty:
+                ev.clear()
+                pr.wake = wake
+                if not pr.chunks.empty():       # a chunk slipped in before the hook was visible
+                    pr.wake = None
+                    continue
+                try:
+                    await asyncio.wait_for(ev.wait(), max(0.01, min(1.0, deadline - time.time())))
+                except asyncio.TimeoutError:
+                    if time.time() > deadline:
+                        self.abort_request(request_id)
+                        yield ResultChunk("error", b"request timed out", final=True, error_status=500)
+                        return
                 continue
             if c.modality == "done":
                 return

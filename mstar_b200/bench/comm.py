@@ -133,9 +133,34 @@ def main():
     # in-switch reduction: a rank pulls its 1/W share reduced and multicasts it: N/W in and N/W out per GPU... the
     # slower direction carries (W - 1) / W of the message once
     nvls_link_us = (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
+    # the same message already resident in a symmetric region (where a row-parallel GEMM writes it): in-place
+    big = heap.new_region(xb.numel() * 2 + 4096)
+    boff = big.alloc(xb.numel() * 2)
+    big.view(boff, xb.shape, torch.bfloat16).zero_()
+    t_inpl = timed(lambda i: heap.all_reduce_inplace(big, boff, xb.numel()), args.iters, args.warmup, dev)
     report(path="all-reduce, 21120x2048 bf16", ranks=W, push_us=round(t_ours, 2), nvls_us=round(t_nvls, 2),
-           nccl_us=round(t_nccl, 2), roofline_us=round(nvls_link_us, 2),
-           frac_of_roofline=round(nvls_link_us / min(t_ours, t_nvls), 3), multicast=bool(heap.mc_ptr))
+           nvls_inplace_us=round(t_inpl, 2), nccl_us=round(t_nccl, 2), roofline_us=round(nvls_link_us, 2),
+           frac_of_roofline=round(nvls_link_us / min(t_ours, t_nvls, t_inpl), 3), multicast=bool(heap.mc_ptr))
+    # large row-parallel projection (a DiT block's output projection over one rank's tokens): the GEMM writes its
+    # partial into the region and the in-place all-reduce follows, against GEMM + NCCL all-reduce
+    Mb, Nb, Kb = 21120, 2048, 2048 // W
+    xg = torch.randn(Mb, Kb, device=dev).to(torch.bfloat16)
+    wg = (torch.randn(Nb, Kb, device=dev) * 0.02).to(torch.bfloat16)
+    yv = big.view(boff, (Mb, Nb), torch.bfloat16)
+
+    def gemm_inplace(i):
+        gemm.linear(xg, wg, out=yv)
+        heap.all_reduce_inplace(big, boff, Mb * Nb)
+
+    def gemm_nccl(i):
+        dist.all_reduce(gemm.linear(xg, wg))
+    t_gi = timed(gemm_inplace, args.iters, args.warmup, dev)
+    t_gn = timed(gemm_nccl, args.iters, args.warmup, dev)
+    t_g0 = timed(lambda i: gemm.linear(xg, wg, out=yv), args.iters, args.warmup, dev)
+    report(path=f"GEMM -> in-place all-reduce ({Mb}x{Nb}x{Kb} per rank)", ranks=W, fused_us=round(t_gi, 2),
+           gemm_plus_nccl_us=round(t_gn, 2), gemm_alone_us=round(t_g0, 2),
+           roofline_us=round(max(nvls_link_us, 2.0 * Mb * Nb * Kb / (tflops * 1e6)), 2), multicast=bool(big.mc_ptr))
+    del big
 
     # ---- row-parallel projection: GEMM with the all-reduce in its epilogue (o_proj / down_proj of a decode step) ----
     for (M, N, K, name) in [(64, 3072, 3072 // W, "o_proj"), (64, 3072, 8192 // W, "down_proj")]:

@@ -230,6 +230,89 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------------
+// all-reduce in place, on a tensor that already lives at the same offset of every rank's symmetric region
+// ---------------------------------------------------------------------------------------------
+// The producer (a GEMM) wrote its partial straight into the region, so nothing is staged and nothing is copied out:
+// one flag round ("my partial is complete"), then rank r load-reduces share r of every CTA's range in the switch and
+// multicast-stores the sum over the same addresses of every rank, one more flag round, and every rank holds the sum
+// where its partial was. Per GPU n/W bytes cross NVLink in each direction for the loads and again for the stores;
+// HBM sees one read and one write of the tensor. Eight 16-byte requests are in flight per thread.
+struct ARInplaceParams {
+    PeerTable t;
+    McastTable mc;
+    long long off;               // byte offset of the tensor inside the region, 16-byte aligned
+    long long n;                 // bf16 elements, multiple of 8
+    unsigned int* epoch;
+    unsigned int* arrive;
+    int channel_base;            // flag channels [base, base + 2 * grid)
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+
+__global__ void __launch_bounds__(512) allreduce_inplace_kernel(const __grid_constant__ ARInplaceParams p) {
+    __shared__ int s_ok;
+    __shared__ unsigned int s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) { s_epoch = *p.epoch + 1; s_ok = 1; }
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int W = p.t.world, R = p.t.rank;
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        signal_all(p.t, p.mc, p.channel_base + blockIdx.x, epoch);
+        if (!wait_all(p.t, p.channel_base + blockIdx.x, epoch, p.status, p.wait_limit_ns, 0x31)) s_ok = 0;
+    }
+    __syncthreads();
+    const long long nvec = p.n >> 3;
+    const long long per = (nvec + gridDim.x - 1) / gridDim.x;
+    const long long v0 = (long long)blockIdx.x * per;
+    long long v1 = v0 + per;
+    if (v1 > nvec) v1 = nvec;
+    if (s_ok && v1 > v0) {
+        const long long share = (v1 - v0 + W - 1) / W;
+        const long long a = v0 + (long long)R * share;
+        long long b = a + share;
+        if (b > v1) b = v1;
+        constexpr int U = 8;
+        long long v = a + threadIdx.x;
+        if (p.mc.data != nullptr) {
+            char* base = p.mc.data + p.off;
+            for (; v + (long long)(U - 1) * blockDim.x < b; v += (long long)U * blockDim.x) {
+                uint4 r[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) r[u] = multimem_ld_reduce_bf16x8(base + (v + (long long)u * blockDim.x) * 16);
+#pragma unroll
+                for (int u = 0; u < U; ++u) multimem_st_v4(base + (v + (long long)u * blockDim.x) * 16, r[u]);
+            }
+            for (; v < b; v += blockDim.x) multimem_st_v4(base + v * 16, multimem_ld_reduce_bf16x8(base + v * 16));
+        } else {
+            for (; v < b; v += blockDim.x) {
+                float acc[8];
+                load_sum8(p.t, p.mc, p.off + v * 16, acc);
+                const uint4 o = pack8(acc);
+                for (int q = 0; q < W; ++q)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.t.buf[q]) + p.off + v * 16) = o;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_ok) {
+            signal_all(p.t, p.mc, p.channel_base + gridDim.x + blockIdx.x, epoch);
+            wait_all(p.t, p.channel_base + gridDim.x + blockIdx.x, epoch, p.status, p.wait_limit_ns, 0x32);
+        }
+        __threadfence();
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        if (old == gridDim.x - 1) {
+            *p.arrive = 0u;
+            *p.epoch = epoch;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // reduce + residual + RMSNorm (consumer of a row-parallel GEMM's partial sums)
 // ---------------------------------------------------------------------------------------------
 struct RRNParams {
@@ -517,6 +600,30 @@ MSTAR_API int mstar_allreduce_nvls(void* const* bufs, void* const* flags, int wo
     return (int)ctas;
 }
 
+// In-place sum of the [n] bf16 tensor at byte offset `off` of every rank's region (`bufs` / `mc_data` describe that
+// region). Every rank must launch the same grid: it is sized from n and max_ctas only. Returns the grid size.
+MSTAR_API int mstar_allreduce_inplace(void* const* bufs, void* const* flags, int world, int rank, void* mc_data,
+                                      void* mc_flags, long long off, long long n, void* state, int channel_base,
+                                      int max_ctas, void* stream_) {
+    if (n <= 0) return 0;
+    if (n % 8 || off % 16) return set_error("allreduce_inplace: count must be a multiple of 8, offset of 16", cudaSuccess);
+    ARInplaceParams p;
+    if (fill_tables(&p.t, &p.mc, bufs, flags, world, rank, mc_data, mc_flags)) return -1;
+    p.off = off;
+    p.n = n;
+    p.epoch = reinterpret_cast<unsigned int*>(state);
+    p.arrive = p.epoch + 1;
+    p.channel_base = channel_base;
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    long long ctas = (n / 8 + 4095) / 4096;
+    if (ctas > max_ctas) ctas = max_ctas;
+    if (ctas < 1) ctas = 1;
+    cudaError_t e = launch_pdl(allreduce_inplace_kernel, dim3((unsigned)ctas), dim3(512), 0, (cudaStream_t)stream_, p);
+    if (e != cudaSuccess) return set_error("allreduce_inplace launch", e);
+    return (int)ctas;
+}
+
 // two_shot != 0: rows [row_begin, row_end) are this rank's; normalised rows go to h_off of every rank's region copy.
 MSTAR_API int mstar_reduce_residual_norm(void* const* bufs, void* const* flags, int world, int rank, void* mc_data,
                                          void* mc_flags, long long slot_off, int M, int N, const void* residual_in,
@@ -548,7 +655,7 @@ MSTAR_API int mstar_reduce_residual_norm(void* const* bufs, void* const* flags, 
     // the two-shot form uses one flag channel per block and needs the same grid on every rank: it is sized from the
     // largest row share, ceil(M / world), not from this rank's own share
     const int rows = two_shot ? (M + world - 1) / world : M;
-    const int cap = two_shot ? 128 : 4 * device_sm_count();
+    const int cap = two_shot ? 1024 : 4 * device_sm_count();
     int grid = rows < cap ? rows : cap;
     if (grid < 1) grid = 1;
     cudaError_t e = launch_pdl(reduce_residual_norm_kernel, dim3(grid), dim3(RRN_THREADS), 0, (cudaStream_t)stream_, p);

@@ -80,10 +80,16 @@ class SnacSubmodule(NodeSubmodule):
         """tokens [B, n] (n a multiple of 7, host) -> waveforms [B, n / 7 * 2048] on the device; replayed from a CUDA
         graph per shape. On a GPU the result is a view of the graph's static output: copy it out on the same stream."""
         def fn(tk):
-            if self.compute_dtype != torch.float32 and tk.is_cuda:
+            if not tk.is_cuda:
+                return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+            if self.compute_dtype != torch.float32:
                 with torch.autocast("cuda", dtype=self.compute_dtype):
-                    return self.dec(orpheus_tokens_to_codes(tk, self.base_id)).float()
-            return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+                    wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id)).float()
+            else:
+                wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+            # 16-bit PCM is what leaves the server: quantise inside the captured graph, so the read-back is half
+            # the bytes and the API process only forwards them
+            return (wav.float().clamp(-1, 1) * 32767.0).round().to(torch.int16)
         with torch.no_grad():
             if runner is not None and self.device.type == "cuda":
                 # batch padded to a power of two: a handful of captured graphs serve every batch size
@@ -128,12 +134,14 @@ class SnacSubmodule(NodeSubmodule):
             else:
                 by_len.setdefault(t.numel(), []).append(i)
         for n, idx in by_len.items():
-            wav = self._decode(torch.stack([toks[i] for i in idx]), runner).float()
+            wav = self._decode(torch.stack([toks[i] for i in idx]), runner)
+            if wav.dtype != torch.int16:
+                wav = wav.float()
             if wav.is_cuda:
                 rows = 64 if len(idx) <= 64 else len(idx)
-                host = self._pinned(("wav", rows, wav.shape[1]), (rows, wav.shape[1]), torch.float32)
+                host = self._pinned(("wav", rows, wav.shape[1]), (rows, wav.shape[1]), wav.dtype)
                 host[:len(idx)].copy_(wav, non_blocking=True)
-                io_counters.add_d2h(wav.numel() * 4)
+                io_counters.add_d2h(wav.numel() * wav.element_size())
             else:
                 host = wav
             hb = _HostBatch(host, len(idx))

@@ -21,7 +21,7 @@ import torch.distributed as dist
 from ..ops import _lib
 
 MAX_RANKS = 8
-N_CHANNELS = 2048
+N_CHANNELS = 4096
 # channel map
 CH_ALLREDUCE = 0          # [0, 512): all-reduce CTAs (two rounds of up to 256)
 CH_BARRIER = 512
@@ -29,10 +29,11 @@ CH_A2A = 513              # [513, 521)
 CH_CFG = 528
 CH_GEMM_AR = 544          # [544, 1024): fused GEMM + all-reduce tiles
 CH_NVLS_AR = 1024         # [1024, 1280): NVLS all-reduce CTAs (two rounds of up to 128)
-CH_RRN = 1280             # [1280, 1409): reduce + residual + norm consumers (1 + up to 128 blocks of the two-shot form)
-CH_AG = 1536              # [1536, 1664): column all-gather CTAs
+CH_RRN = 1280             # [1280, 2305): reduce + residual + norm consumers (1 + up to 1024 blocks of the two-shot form)
+CH_AG = 2432              # [2432, 2560): column all-gather CTAs
+CH_AR_INPLACE = 2560      # [2560, 2816): in-place all-reduce CTAs (two rounds of up to 128)
 # local state words (pairs of [epoch, arrive]) by user
-ST_AR, ST_BARRIER, ST_A2A, ST_CFG, ST_GEMM_AR, ST_NVLS_AR, ST_RRN, ST_AG = range(8)
+ST_AR, ST_BARRIER, ST_A2A, ST_CFG, ST_GEMM_AR, ST_NVLS_AR, ST_RRN, ST_AG, ST_AR_INPLACE = range(9)
 
 
 class SymmRegion:
@@ -250,6 +251,19 @@ class SymmetricHeap:
                 _lib.check(rc, "mstar_allreduce_nvls")
             _lib._counters.bump()
         return out
+
+    def all_reduce_inplace(self, region: SymmRegion, off: int, n: int) -> None:
+        """Sum, over the group, of the bf16 tensor of ``n`` elements at byte offset ``off`` of ``region``; the result
+        replaces it on every rank. For producers that write their partial straight into the region (a row-parallel
+        GEMM with ``out=region.view(...)``): nothing is staged or copied, the additions happen in the switch."""
+        mc_data, mc_flags = self._mc(region)
+        rc = _lib.kernels().mstar_allreduce_inplace(
+            region.table, self._flags, self.world, self.rank, mc_data, mc_flags, ctypes.c_longlong(off),
+            ctypes.c_longlong(n), self._state_ptr(ST_AR_INPLACE), CH_AR_INPLACE, 128,
+            ctypes.c_void_p(_lib.stream_ptr()))
+        if rc < 0:
+            _lib.check(rc, "mstar_allreduce_inplace")
+        _lib._counters.bump()
 
     def row_share(self, M: int) -> tuple[int, int]:
         """Rows [a, b) of an M-row activation that this rank owns in the two-shot (row-cut) forms."""

@@ -19,6 +19,7 @@ class WorkerMessageType(str, Enum):
     INPUT_SIGNALS = "input_signals"
     UNPERSIST_TENSORS = "unpersist"
     TENSOR_RECEIVED = "tensor_received"
+    TENSOR_RECEIVED_BATCH = "tensor_received_batch"
     SCHEDULE_TP = "schedule_tp"
     STOP_LOOPS = "stop_loops"
     SHUTDOWN = "shutdown"
@@ -39,6 +40,7 @@ class ConductorMessageType(str, Enum):
 
 class ApiMessageType(str, Enum):
     RESULT_TENSORS = "result_tensors"
+    RESULT_TENSORS_BATCH = "result_tensors_batch"    # the client-bound outputs of one executed batch, all requests
     REQUEST_COMPLETE = "request_complete"
     REQUEST_FAILED = "request_failed"
     SETUP_DONE = "setup_done"
@@ -194,6 +196,16 @@ class ResultTensors:
     tensors: list[TensorPointerInfo]
     metadata: dict = field(default_factory=dict)
     source_entity: str = ""
+
+
+@dataclass
+class ResultTensorsBatch:
+    items: list[ResultTensors] = field(default_factory=list)
+
+
+@dataclass
+class TensorReceivedBatch:
+    items: list = field(default_factory=list)      # TensorReceived records
 
 
 @dataclass

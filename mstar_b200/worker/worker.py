@@ -111,6 +111,7 @@ class Worker:
         # decode on different workers); otherwise the request stays on this worker and the store lookup is local
         self._publish_persisted = publish_persisted
         self._done_queue: list | None = None      # walk-completion messages held back while a batch is being finished
+        self._emit_buf: list | None = None        # client-bound outputs of the batch being finished, sent as one message
         self.walks = model.get_graph_walk_graphs()
         self.topology = model.get_partition_topology()
         self.requests: dict[tuple[str, str], PerRequestInfo] = {}     # (request_id, partition) -> info
@@ -176,6 +177,10 @@ class Worker:
                 elif t == WM.TENSOR_RECEIVED:
                     for u, n in m.body.successful_tensors.items():
                         self.tensors.dereference(m.body.request_id, u, n)
+                elif t == WM.TENSOR_RECEIVED_BATCH:
+                    for r in m.body.items:
+                        for u, n in r.successful_tensors.items():
+                            self.tensors.dereference(r.request_id, u, n)
                 elif t == WM.KV_EXPORT:
                     self._on_kv_export(m.body)
                 elif t == WM.KV_IMPORT:
@@ -586,10 +591,12 @@ class Worker:
                     if self.tensors.store.owner_of(ti.uuid) not in (None, emit_owner):
                         self.tensors.store.adopt(ti.uuid, emit_owner)
                 infos = [self._publish(pri.request_id, e.name, ti, self.api_id) for ti in e.tensor_info]
-                self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS,
-                                                    ipc.ResultTensors(pri.request_id, e.output_modality or "text", infos,
-                                                                      {"name": e.name, "partition": pri.partition_name},
-                                                                      self.worker_id)))
+                rt = ipc.ResultTensors(pri.request_id, e.output_modality or "text", infos,
+                                       {"name": e.name, "partition": pri.partition_name}, self.worker_id)
+                if self._emit_buf is not None:      # inside a batch's read-back: one message for all its requests
+                    self._emit_buf.append(rt)
+                else:
+                    self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS, rt))
                 continue
             for w in self.node_to_workers.get(e.next_node, []):
                 by_worker.setdefault(w, []).append(e)
@@ -880,10 +887,17 @@ class Worker:
             rec[1] += len(batch.request_ids)
             rec[2] += dt
             self._done_queue = []
+            self._emit_buf = []
             try:
                 self._postprocess_batch(batch, out, fl)
             finally:
                 done, self._done_queue = self._done_queue, None
+                emits, self._emit_buf = self._emit_buf, None
+                if len(emits) == 1:
+                    self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS, emits[0]))
+                elif emits:
+                    self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS_BATCH,
+                                                        ipc.ResultTensorsBatch(emits)))
             if self.profile is not None:
                 tm = out.timings
                 self.profile.record_batch(batch.node_name, batch.graph_walk, batch.request_ids,

@@ -66,6 +66,24 @@ def main():
             check(f"nvls allreduce mc={bool(heap.mc_ptr)} mode={mode} n={n} it={it} err={err:.3g}",
                   err < 0.05 * max(1.0, ref.abs().max().item()) and same)
 
+    # ---- in-place all-reduce of a tensor that lives in a symmetric region ----
+    reg = heap.new_region(8 << 20)
+    for n in (8, 64 * 3072, 1024 * 3072 + 8):
+        off = reg.alloc(n * 2)
+        for it in range(3):
+            gen = torch.Generator().manual_seed(500 * it + n % 97)
+            parts = [torch.randn(n, generator=gen).to(torch.bfloat16) for _ in range(W)]
+            v = reg.view(off, (n,), torch.bfloat16)
+            v.copy_(parts[R].to(dev))
+            heap.all_reduce_inplace(reg, off, n)
+            ref = sum(p.float() for p in parts)
+            err = (v.float().cpu() - ref).abs().max().item()
+            gathered = [torch.empty_like(v) for _ in range(W)]
+            dist.all_gather(gathered, v.clone())
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            check(f"in-place allreduce mc={bool(reg.mc_ptr)} n={n} it={it} err={err:.3g}",
+                  err < 0.05 * max(1.0, ref.abs().max().item()) and same)
+
     # ---- row-parallel GEMM partials reduced by the consumer norm kernel, column all-gather, embedding gather ----
     from mstar_b200.ops import gemm as gemm_ops
     from mstar_b200.ops import norm as norm_ops
