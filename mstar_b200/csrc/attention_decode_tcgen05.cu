@@ -38,6 +38,11 @@ struct DecAttnParams {
     long long ws_rows;
     KernelStatus* status;
     unsigned long long wait_limit_ns;
+    // while the K/V pages stream through (marked evict-first with l2_hints), the L2 fetches the weights of the
+    // projections that follow this kernel
+    const void* pf_ptr = nullptr;
+    unsigned long long pf_bytes = 0;
+    int l2_hints = 0;
 };
 
 constexpr int DA_KEYS = 128;
@@ -147,6 +152,12 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     // then run under the rest of the prologue (a CTA of a short context has only ~5 tiles to amortise its start).
     const int ppt = DA_KEYS / p.page_size;
     const int* pages = p.page_indices + p.page_indptr[req];
+    const bool kv_hint = p.l2_hints != 0;
+    const uint64_t pol_kv = kv_hint ? l2_policy_evict_first() : 0ull;
+    auto load_kv = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int x, int kvh_, int page) {
+        if (kv_hint) tma_load_4d_hint(dst, tm, bar, x, 0, kvh_, page, pol_kv);
+        else tma_load_4d(dst, tm, bar, x, 0, kvh_, page);
+    };
     auto issue_k = [&](int i) {
         const int jt = jt0 + i, s = i % KS;
         uint8_t* dst = sK + s * DA_K_BYTES;
@@ -156,8 +167,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
             if (pi >= npages) pi = npages - 1;
             const int page = pages[pi];
             const int row_off = pg * p.page_size * 128;
-            tma_load_4d(dst + row_off, &tmK, &k_full[s], 0, 0, kvh, page);
-            tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, 0, kvh, page);
+            load_kv(dst + row_off, &tmK, &k_full[s], 0, kvh, page);
+            load_kv(dst + DA_KEYS * 128 + row_off, &tmK, &k_full[s], 64, kvh, page);
         }
     };
     auto issue_v = [&](int i) {
@@ -169,8 +180,8 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
             if (pi >= npages) pi = npages - 1;
             const int page = pages[pi];
             const int row_off = pg * p.page_size * 128;
-            tma_load_4d(dst + row_off, &tmV, &v_full[s], 0, 0, kvh, page);
-            tma_load_4d(dst + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, 0, kvh, page);
+            load_kv(dst + row_off, &tmV, &v_full[s], 0, kvh, page);
+            load_kv(dst + DA_KEYS * 128 + row_off, &tmV, &v_full[s], 64, kvh, page);
         }
     };
     if (threadIdx.x == 0 && ntiles > 0) {
@@ -200,6 +211,9 @@ attn_decode_tcgen05_kernel(const __grid_constant__ CUtensorMap tmK, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.pf_bytes != 0 && threadIdx.x == 33)       // second lane of the MMA warp: idle
+        l2_prefetch_slice(p.pf_ptr, p.pf_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                          gridDim.x * gridDim.y * gridDim.z, p.l2_hints != 0);
 
     if (warp == 0) {
         // =========================== TMA producer ===========================
@@ -319,6 +333,7 @@ MSTAR_API int mstar_attention_decode(const void* q, void* out, long long q_tok_s
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)))
         return set_error("attention_decode: page_size must be a power of two in [8, 128]", cudaSuccess);
     DecAttnParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
     p.q_tok_stride = q_tok_stride; p.o_tok_stride = o_tok_stride;
     p.q_indptr = q_indptr; p.kv_lens = kv_lens; p.page_indptr = page_indptr; p.page_indices = page_indices;

@@ -169,6 +169,55 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
+// L2 residency hints. A weight-streaming kernel marks its own operand tiles evict-first (each is read once) and asks
+// the L2 to fetch the NEXT kernel's weights with evict-last priority, so that kernel starts on a warm cache while
+// this one is still bound by its own latency chain. Prefetches are fire-and-forget: nothing waits for them.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y,
+                                                 uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_hint(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z,
+                                                 int w, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "l"(policy)
+        : "memory");
+}
+// One thread per CTA: request chunks cta, cta + nctas, ... (16 KB each) of [ptr, ptr + bytes) into the L2.
+// ptr must be 16-byte aligned; the tail is rounded down to 16 bytes.
+__device__ __forceinline__ void l2_prefetch_slice(const void* ptr, unsigned long long bytes, unsigned int cta,
+                                                  unsigned int nctas, bool evict_last) {
+    constexpr unsigned long long CHUNK = 16384;
+    const unsigned long long nchunks = (bytes + CHUNK - 1) / CHUNK;
+    const uint64_t pol = evict_last ? l2_policy_evict_last() : 0ull;
+    for (unsigned long long c = cta; c < nchunks; c += nctas) {
+        const unsigned long long off = c * CHUNK;
+        unsigned long long len = bytes - off;
+        if (len > CHUNK) len = CHUNK;
+        len &= ~15ull;
+        if (len == 0) break;
+        const char* a = reinterpret_cast<const char*>(ptr) + off;
+        if (evict_last)
+            asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(a), "r"((uint32_t)len), "l"(pol) : "memory");
+        else
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"((uint32_t)len) : "memory");
+    }
+}
 __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
                  "r"(smem_u32(smem_src)), "r"(x), "r"(y)

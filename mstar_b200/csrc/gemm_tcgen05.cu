@@ -66,6 +66,11 @@ struct GemmParams {
     const float* row_scale;         // optional per-token-row factor (routing weight), applied to the output row
     void* const* row_dst;           // optional per-token-row destination pointers (expert-parallel combine: the
                                     // row is stored straight into its owner's buffer, possibly on a peer GPU)
+    // L2 management of the weight-streaming regime: while this kernel runs, its CTAs ask the L2 for the weights of
+    // the kernel that follows; with l2_hints its own weight tiles (decode layout) are marked evict-first
+    const void* pf_ptr = nullptr;
+    unsigned long long pf_bytes = 0;
+    int l2_hints = 0;
 };
 
 #define MSTAR_TRACE(i)                                                                                      \
@@ -495,16 +500,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) MSTAR_TRACE(1);
+    if (p.pf_bytes != 0 && threadIdx.x == 64)       // an epilogue warp, idle until the accumulator is complete
+        l2_prefetch_slice(p.pf_ptr, p.pf_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                          gridDim.x * gridDim.y * gridDim.z, p.l2_hints != 0);
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
+            const bool w_stream = SWAP && p.l2_hints != 0;      // weight tiles are read once: first out of the L2
+            const uint64_t pol_w = w_stream ? l2_policy_evict_first() : 0ull;
             // packed weights: tile (row tile t, K block kb) starts at row (t * kblocks_total + kb) * 128 of a
             // [tiles * 128, 64] matrix; the weight is the P operand in the decode layout, the Q operand otherwise
             const bool p_packed = p.w_packed && SWAP, q_packed = p.w_packed && !SWAP;
             auto load_P = [&](uint8_t* dst, uint64_t* bar, int kb) {
-                if (p_packed) tma_load_2d(dst, &tmP, bar, 0, ((p_row0 / BM) * p.kblocks_total + kb) * BM);
-                else tma_load_2d(dst, &tmP, bar, kb * BK, p_row0);
+                const int x = p_packed ? 0 : kb * BK;
+                const int y = p_packed ? ((p_row0 / BM) * p.kblocks_total + kb) * BM : p_row0;
+                if (w_stream) tma_load_2d_hint(dst, &tmP, bar, x, y, pol_w);
+                else tma_load_2d(dst, &tmP, bar, x, y);
             };
             auto load_Q = [&](uint8_t* dst, uint64_t* bar, int kb) {
                 if (q_packed) {
@@ -1429,6 +1441,7 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
         splits = 1;  // no scratch available: fall back to a single pass over K
     }
     GemmParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     p.M = M; p.N = N; p.K = K;
     p.swap = swap;
     p.splits = splits;
@@ -1499,6 +1512,7 @@ MSTAR_API int mstar_moe_grouped_gemm(const void* A, const void* W, void* C, int 
     if (K % 8 || N % 8 || capacity_rows % block_rows)
         return set_error("moe gemm: K and N must be multiples of 8, capacity a multiple of block_rows", cudaSuccess);
     GemmParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     p.M = capacity_rows; p.N = N; p.K = K;
     p.swap = 1;
     p.splits = 1;
@@ -1623,6 +1637,7 @@ MSTAR_API int mstar_gemm_fp8(const void* A8, const void* a_scale_t, int ld_as, c
         if (ld_as < bn) return set_error("gemm_fp8: activation scale rows must be padded to the token tile", cudaSuccess);
     }
     GemmParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     fill_fp8_params(p, M, N, K, swap, epilogue, out_f32, ldc, C);
     p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
     p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -1657,6 +1672,7 @@ MSTAR_API int mstar_moe_grouped_gemm_fp8(const void* A8, const void* a_scale_t, 
     if (K % 16 || N % 128 || capacity_rows % block_rows || ld_as < capacity_rows)
         return set_error("moe gemm fp8: K % 16, N % 128, capacity % block_rows and ld_as >= capacity are required", cudaSuccess);
     GemmParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     fill_fp8_params(p, capacity_rows, N, K, 1, epilogue, 0, ldc, C);
     p.block_expert = block_expert;
     p.num_blocks = num_blocks;
@@ -1732,6 +1748,7 @@ MSTAR_API int mstar_gemm_bf16_noalloc(const void* A, const void* B, void* C, int
     }
     const int kblocks = (K + BK - 1) / BK;
     GemmParams p;
+    { const PrefetchHint h = take_prefetch_hint(); p.pf_ptr = h.ptr; p.pf_bytes = h.bytes; p.l2_hints = h.l2_hints; }
     p.M = M; p.N = N; p.K = K;
     p.swap = swap;
     p.splits = splits;

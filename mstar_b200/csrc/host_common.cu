@@ -146,6 +146,30 @@ MSTAR_API unsigned int mstar_read_status(unsigned int* out4, int clear) {
 // Queues a copy of the current device's status word (16 bytes) into `host_dst16` (pinned host memory) on `stream`:
 // a serving loop reads the word with the batch's results, after the event it already waits for, instead of paying
 // a synchronous copy per batch. The word is not cleared; mstar_read_status(.., 1) does that once a code was seen.
+namespace mstar {
+static PrefetchHint g_prefetch[kMaxDevices];
+
+PrefetchHint take_prefetch_hint() {
+    PrefetchHint& h = g_prefetch[current_device()];
+    PrefetchHint out = h;
+    h = PrefetchHint{};
+    return out;
+}
+}  // namespace mstar
+using mstar::g_prefetch;
+using mstar::PrefetchHint;
+
+// The next GEMM / decode-attention launch on the current device prefetches [ptr, ptr + bytes) into the L2 while it
+// runs (bytes 0: only the evict-first marking of its own operand, when l2_hints is set). The hint is used once.
+MSTAR_API void mstar_prefetch_hint(const void* ptr, unsigned long long bytes, int l2_hints) {
+    PrefetchHint& h = g_prefetch[current_device()];
+    const unsigned long long mis = reinterpret_cast<unsigned long long>(ptr) & 15ull;
+    if (ptr != nullptr && mis && bytes > 16) { ptr = static_cast<const char*>(ptr) + (16 - mis); bytes -= 16 - mis; }
+    h.ptr = ptr;
+    h.bytes = ptr != nullptr ? bytes : 0;
+    h.l2_hints = l2_hints;
+}
+
 MSTAR_API int mstar_status_copy_async(void* host_dst16, void* stream) {
     KernelStatus* p = status_ptr();
     if (p == nullptr) return set_error("status word could not be allocated", cudaSuccess);

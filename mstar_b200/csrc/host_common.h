@@ -20,6 +20,16 @@ struct PerDeviceFlag {
     bool& operator()() { return done[current_device()]; }
 };
 
+// What the NEXT weight-streaming kernel launched on the current device should ask the L2 to fetch while it runs
+// (the weights of the kernel after it). Set by mstar_prefetch_hint, taken (and cleared) by the next launcher that
+// supports it; l2_hints also makes that kernel mark its own streamed operand evict-first.
+struct PrefetchHint {
+    const void* ptr = nullptr;
+    unsigned long long bytes = 0;
+    int l2_hints = 0;
+};
+PrefetchHint take_prefetch_hint();
+
 int set_error(const char* msg, cudaError_t e);      // stores the message, returns -1
 KernelStatus* status_ptr();                         // status word of the CURRENT device (lazily made, one per device)
 unsigned long long wait_limit_ns();

@@ -24,6 +24,7 @@
 // Reference counterparts: RowParallelLinear all-reduce (mstar/model/components/distributed/linear.py:415), lm_head
 // gather (mstar/model/orpheus/components/language_model.py:95, linear.py:105), VocabParallelEmbedding all-reduce
 // (mstar/model/components/distributed/embedding.py:27-116) — separate NCCL kernels there.
+#include <cstdlib>
 #include "common.cuh"
 #include "host_common.h"
 #include "comm_device.cuh"
@@ -237,6 +238,39 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
 // multicast-stores the sum over the same addresses of every rank, one more flag round, and every rank holds the sum
 // where its partial was. Per GPU n/W bytes cross NVLink in each direction for the loads and again for the stores;
 // HBM sees one read and one write of the tensor. Eight 16-byte requests are in flight per thread.
+// Sum vectors v, v + blockDim, ... of [.., b) over the ranks' regions and store the sum to every rank; UP vectors per
+// thread and trip, all of their WW loads in flight together. Returns the first vector left for the tail loop.
+template <int WW, int UP>
+__device__ __forceinline__ long long p2p_share(const PeerTable& t, long long off, long long v, long long b) {
+    const int W = t.world;
+    for (; v + (long long)(UP - 1) * blockDim.x < b; v += (long long)UP * blockDim.x) {
+        uint4 raw[UP][WW];
+#pragma unroll
+        for (int u = 0; u < UP; ++u)
+#pragma unroll
+            for (int q = 0; q < WW; ++q)
+                if (q < W)
+                    raw[u][q] = __ldcg(reinterpret_cast<const uint4*>(
+                        reinterpret_cast<const char*>(t.buf[q]) + off + (v + (long long)u * blockDim.x) * 16));
+#pragma unroll
+        for (int u = 0; u < UP; ++u) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int q = 0; q < WW; ++q)
+                if (q < W) add_bf16x8(acc, raw[u][q]);
+            const uint4 o = pack8(acc);
+#pragma unroll
+            for (int q = 0; q < WW; ++q)
+                if (q < W)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.buf[q]) + off +
+                                              (v + (long long)u * blockDim.x) * 16) = o;
+        }
+    }
+    return v;
+}
+
 struct ARInplaceParams {
     PeerTable t;
     McastTable mc;
@@ -287,6 +321,11 @@ __global__ void __launch_bounds__(512) allreduce_inplace_kernel(const __grid_con
             }
             for (; v < b; v += blockDim.x) multimem_st_v4(base + v * 16, multimem_ld_reduce_bf16x8(base + v * 16));
         } else {
+            // plain peer loads and stores: this rank's share of every peer's partial comes in over NVLink once and
+            // the sum goes out once, (W - 1) / W * n bytes per direction and nothing crosses the switch twice
+            if (W == 2) v = p2p_share<2, 8>(p.t, p.off, v, b);
+            else if (W <= 4) v = p2p_share<4, 4>(p.t, p.off, v, b);
+            else v = p2p_share<MAX_RANKS, 2>(p.t, p.off, v, b);
             for (; v < b; v += blockDim.x) {
                 float acc[8];
                 load_sum8(p.t, p.mc, p.off + v * 16, acc);
@@ -600,6 +639,20 @@ MSTAR_API int mstar_allreduce_nvls(void* const* bufs, void* const* flags, int wo
     return (int)ctas;
 }
 
+// The bandwidth-bound forms (in-place all-reduce, two-shot consumer reduce) move their DATA through the switch only
+// from this group size on: a load-reduce also pulls the requester's own copy through NVLink and a multicast store
+// comes back to the sender, (W + 1) / W * n bytes per direction against (W - 1) / W * n for plain peer loads and
+// stores, which in small groups costs more than the switch-side addition saves. Flags still use the multicast.
+static int nvls_data_min_world() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MSTAR_NVLS_DATA_MIN_WORLD");
+        v = e != nullptr ? atoi(e) : 4;
+        if (v < 2) v = 2;
+    }
+    return v;
+}
+
 // In-place sum of the [n] bf16 tensor at byte offset `off` of every rank's region (`bufs` / `mc_data` describe that
 // region). Every rank must launch the same grid: it is sized from n and max_ctas only. Returns the grid size.
 MSTAR_API int mstar_allreduce_inplace(void* const* bufs, void* const* flags, int world, int rank, void* mc_data,
@@ -609,6 +662,7 @@ MSTAR_API int mstar_allreduce_inplace(void* const* bufs, void* const* flags, int
     if (n % 8 || off % 16) return set_error("allreduce_inplace: count must be a multiple of 8, offset of 16", cudaSuccess);
     ARInplaceParams p;
     if (fill_tables(&p.t, &p.mc, bufs, flags, world, rank, mc_data, mc_flags)) return -1;
+    if (world < nvls_data_min_world()) p.mc.data = nullptr;
     p.off = off;
     p.n = n;
     p.epoch = reinterpret_cast<unsigned int*>(state);
@@ -644,6 +698,7 @@ MSTAR_API int mstar_reduce_residual_norm(void* const* bufs, void* const* flags, 
     p.out = (__nv_bfloat16*)out;
     p.eps = eps;
     p.two_shot = two_shot ? 1 : 0;
+    if (two_shot && world < nvls_data_min_world()) p.mc.data = nullptr;
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.h_off = h_off;

@@ -163,6 +163,8 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
     {
         unsigned long long* wmass = hist_mass + warp * 256;
         unsigned int* wcnt = hist_cnt + warp * 256;
+        uint2* lane_hist = reinterpret_cast<uint2*>(sp_dyn);     // [256 bins][16 half-warp positions] {low, high} mass
+        const bool need_counts = top_k < p.V;                    // a top-k cut needs exact element counts per bin
         uint32_t prefix = 0;            // key bits decided so far (aligned to the top)
         float acc_mass = 0.f;           // mass / count of keys strictly above the undecided range
         int acc_cnt = 0;
@@ -172,8 +174,13 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
 #pragma unroll 1
         for (int level = 0; level < levels; ++level) {
             const int shift = 16 - 8 * level;
-            for (int i = lane; i < 256; i += 32) { wmass[i] = 0ull; wcnt[i] = 0u; }
-            __syncwarp();
+            if (need_counts) {
+                for (int i = lane; i < 256; i += 32) { wmass[i] = 0ull; wcnt[i] = 0u; }
+                __syncwarp();
+            } else {
+                for (int i = tid; i < 256 * 16; i += SP_NT) lane_hist[i] = make_uint2(0u, 0u);
+                __syncthreads();
+            }
             // Eight elements are loaded before the first warp-wide match: the match / syncwarp pair keeps the compiler
             // from moving the next trip's loads above it, so one element per trip paid a memory round trip each
             // (a row took 270 us however few rows there were).
@@ -203,6 +210,18 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
                         const bool in_range = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
                         if (in_range) { bin = (key >> shift) & 0xffu; fx = (unsigned int)(ev[u] * 16777216.0f); }
                     }
+                    if (!need_counts) {
+                        // nucleus only: no element counts are needed, so the bin update is two native 32-bit
+                        // shared-memory additions (the fixed-point mass split in two 12-bit halves, exact and
+                        // order-independent) into a slot private to the lane's half-warp position: ~8 instructions
+                        // per element instead of the ~50 of the warp-wide match below
+                        if (bin != 0xffffffffu) {
+                            uint2* slot = lane_hist + bin * 16 + (lane & 15);
+                            atomicAdd(&slot->x, fx & 0xfffu);
+                            atomicAdd(&slot->y, fx >> 12);
+                        }
+                        continue;
+                    }
                     // below the first level almost no element lies in the undecided range: skip the warp-wide match
                     if (__any_sync(0xffffffffu, bin != 0xffffffffu)) {
                         const unsigned int peers = __match_any_sync(0xffffffffu, bin);
@@ -218,7 +237,14 @@ __global__ void __launch_bounds__(SP_NT, 4) sample_kernel(const __grid_constant_
             __syncthreads();
             if (tid < 256) {          // this CTA's histogram: thread t owns bin t
                 unsigned long long m = 0ull; unsigned int c = 0u;
-                for (int w = 0; w < SP_NW; ++w) { m += hist_mass[w * 256 + tid]; c += hist_cnt[w * 256 + tid]; }
+                if (need_counts) {
+                    for (int w = 0; w < SP_NW; ++w) { m += hist_mass[w * 256 + tid]; c += hist_cnt[w * 256 + tid]; }
+                } else {
+                    unsigned long long lo = 0ull, hi = 0ull;
+                    for (int l = 0; l < 16; ++l) { const uint2 v = lane_hist[tid * 16 + ((l + tid) & 15)]; lo += v.x; hi += v.y; }
+                    m = lo + (hi << 12);
+                    c = m != 0ull ? 1u : 0u;          // only "is the bin empty" is read from the count on this path
+                }
                 merged_mass[tid] = (float)m * (1.0f / 16777216.0f);
                 merged_cnt[tid] = (int)c;
             }
@@ -376,7 +402,7 @@ MSTAR_API int mstar_sample(const void* logits, long long ld, int is_f32, int B, 
     SampleParams p{logits, ld, is_f32, B, V, temperature, top_k, top_p, rep_penalty, seed, offset, seen, row_slot,
                    out, out_prob, u_override, escratch};
     cudaStream_t s = (cudaStream_t)stream_;
-    constexpr int smem = SP_NW * 256 * 12;
+    constexpr int smem = (SP_NW * 256 * 12) > (256 * 16 * 8) ? (SP_NW * 256 * 12) : (256 * 16 * 8);
     static PerDeviceFlag configured;
     if (!configured()) {
         cudaError_t e1 = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

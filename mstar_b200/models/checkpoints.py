@@ -161,3 +161,147 @@ def wan22_checkpoint_keys(dit) -> dict[str, torch.Tensor]:
                 t = t.reshape(1, 6, H)
             out[f"blocks.{i}.{k}"] = t.contiguous()
     return out
+
+
+# ------------------------------------------------------------------ Cosmos3 (diffusers dual-pathway transformer)
+_C3_TOP = {
+    "proj_in.weight": "proj_in_w", "proj_in.bias": "proj_in_b", "proj_out.weight": "proj_out_w", "proj_out.bias": "proj_out_b",
+    "time_embedder.linear_1.weight": "t1_w", "time_embedder.linear_1.bias": "t1_b",
+    "time_embedder.linear_2.weight": "t2_w", "time_embedder.linear_2.bias": "t2_b",
+    "audio_proj_in.weight": "audio_in_w", "audio_proj_in.bias": "audio_in_b",
+    "audio_proj_out.weight": "audio_out_w", "audio_proj_out.bias": "audio_out_b",
+    "audio_modality_embed": "audio_modality_embed", "action_modality_embed": "action_modality_embed",
+    "action_proj_in.fc.weight": "act_in_fc", "action_proj_in.bias.weight": "act_in_bias",
+    "action_proj_out.fc.weight": "act_out_fc", "action_proj_out.bias.weight": "act_out_bias",
+    "norm.weight": "und.norm", "norm_moe_gen.weight": "gen.final_norm",
+}
+_C3_DROP = ("lm_head.weight",)           # the understanding tower descends from a text model; its head is never used
+# per layer: checkpoint suffix -> (tower, parameter, role)
+_C3_LAYER = {
+    "input_layernorm.weight": ("und", "input_layernorm", None),
+    "post_attention_layernorm.weight": ("und", "post_attention_layernorm", None),
+    "input_layernorm_moe_gen.weight": ("gen", "input_norm", None),
+    "post_attention_layernorm_moe_gen.weight": ("gen", "post_norm", None),
+    "self_attn.norm_q.weight": ("und", "self_attn.q_norm", None), "self_attn.norm_k.weight": ("und", "self_attn.k_norm", None),
+    "self_attn.norm_added_q.weight": ("gen", "q_norm", None), "self_attn.norm_added_k.weight": ("gen", "k_norm", None),
+    "self_attn.to_q.weight": ("und", "qkv", "q"), "self_attn.to_k.weight": ("und", "qkv", "k"),
+    "self_attn.to_v.weight": ("und", "qkv", "v"), "self_attn.to_out.weight": ("und", "o", None),
+    "self_attn.add_q_proj.weight": ("gen", "qkv", "q"), "self_attn.add_k_proj.weight": ("gen", "qkv", "k"),
+    "self_attn.add_v_proj.weight": ("gen", "qkv", "v"), "self_attn.to_add_out.weight": ("gen", "o", None),
+    "mlp.gate_proj.weight": ("und", "mlp", "gate"), "mlp.up_proj.weight": ("und", "mlp", "up"),
+    "mlp.down_proj.weight": ("und", "mlp", "down"),
+    "mlp_moe_gen.gate_proj.weight": ("gen", "mlp", "gate"), "mlp_moe_gen.up_proj.weight": ("gen", "mlp", "up"),
+    "mlp_moe_gen.down_proj.weight": ("gen", "mlp", "down"),
+}
+
+
+@torch.no_grad()
+def load_cosmos3_transformer(m, transformer_dir: str) -> dict:
+    """Fill a ``Cosmos3Transformer`` (any tensor- / sequence-parallel cut) from the published ``transformer/``
+    layout: flat ``layers.N.*`` keys, unfused ``to_q / to_k / to_v`` for the understanding pathway and
+    ``add_q_proj / add_k_proj / add_v_proj`` for the generation pathway, ``*_moe_gen`` MLPs and norms of the generation
+    pathway, domain tables of the action projections. q / k / v become the rows of one fused projection per pathway
+    (this rank's heads), gate and up the interleaved rows of one projection whose epilogue applies SwiGLU. Strict:
+    every parameter must be reached, every key must have a home (except the unused text head)."""
+    import re
+    from ..ops import gemm
+    from .decoder import shard_qkv
+    cfg = m.cfg
+    Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    params = dict(m.named_parameters())
+    filled: set[str] = set()
+    unexpected: list[str] = []
+    bad: list[str] = []
+    groups: dict[tuple, dict] = {}
+    rx = re.compile(r"layers\.(\d+)\.(.+)")
+
+    def put(name: str, t: torch.Tensor, key: str):
+        p = params.get(name)
+        if p is None:
+            unexpected.append(key)
+        elif tuple(p.shape) != tuple(t.shape):
+            bad.append(f"{key} {tuple(t.shape)} -> {name} {tuple(p.shape)}")
+        else:
+            p.copy_(t.to(p.dtype))
+            filled.add(name)
+
+    def tower(which: str):
+        """(module path prefix of layer li, tensor-parallel group, attention module path, mlp module path)."""
+        if which == "und":
+            return m.und.tp, (lambda li: f"und.layers.{li}."), "self_attn.", "mlp."
+        return m.gen.tp, (lambda li: f"gen.layers.{li}."), "", ""
+
+    for key, t in iter_checkpoint(transformer_dir):
+        if key in _C3_DROP:
+            continue
+        if key == "embed_tokens.weight":
+            put("und.embed_tokens", m.und.vocab_rows(t) if hasattr(m.und, "vocab_rows") else t, key)
+            continue
+        if key in _C3_TOP:
+            put(_C3_TOP[key], t, key)
+            continue
+        mt = rx.fullmatch(key)
+        if not mt or mt.group(2) not in _C3_LAYER or int(mt.group(1)) >= cfg.num_layers:
+            unexpected.append(key)
+            continue
+        li, (tw, what, role) = int(mt.group(1)), _C3_LAYER[mt.group(2)]
+        tp, lpre, apre, mpre = tower(tw)
+        if role is None and what != "o":
+            put(lpre(li) + what, t, key)
+        elif what == "o":
+            hq = Hq // tp.size
+            put(lpre(li) + apre + "o_proj", t[:, tp.rank * hq * D:(tp.rank + 1) * hq * D], key)
+        else:
+            g = groups.setdefault((tw, li, what), {})
+            g[role] = (t, key)
+            need = ("q", "k", "v") if what == "qkv" else ("gate", "up", "down")
+            if all(r in g for r in need):
+                if what == "qkv":
+                    fused = shard_qkv(g["q"][0], g["k"][0], g["v"][0], Hq, Hkv, D, tp.rank, tp.size)
+                    put(lpre(li) + apre + "qkv_proj", fused, g["q"][1])
+                else:
+                    F = g["gate"][0].shape[0] // tp.size
+                    sl = slice(tp.rank * F, (tp.rank + 1) * F)
+                    put(lpre(li) + mpre + "gate_up_proj", gemm.interleave_gate_up(g["gate"][0][sl], g["up"][0][sl]), g["gate"][1])
+                    put(lpre(li) + mpre + "down_proj", g["down"][0][:, sl], g["down"][1])
+                del groups[(tw, li, what)]
+    incomplete = [f"{tw}.layers.{li}.{what}: only {sorted(g)}" for (tw, li, what), g in groups.items()]
+    missing = sorted(set(params) - filled)
+    if unexpected or missing or bad or incomplete:
+        raise CheckpointMismatch(
+            f"Cosmos3 transformer: {len(unexpected)} checkpoint keys without a parameter {unexpected[:5]}, "
+            f"{len(missing)} parameters not loaded {missing[:5]}, {len(bad)} shape mismatches {bad[:5]}, "
+            f"{len(incomplete)} incomplete projection groups {incomplete[:3]}")
+    m._domain_w.clear()
+    return {"loaded": len(filled)}
+
+
+def cosmos3_checkpoint_keys(m) -> dict[str, torch.Tensor]:
+    """The published key layout of an (unsharded) ``Cosmos3Transformer``'s weights: the inverse of the loader, for
+    synthetic checkpoints in tests and for export."""
+    from ..ops import gemm
+    cfg = m.cfg
+    Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    sd = {k: v.detach().clone() for k, v in m.named_parameters()}
+    out = {ck: sd[name] for ck, name in _C3_TOP.items()}
+    out["embed_tokens.weight"] = sd["und.embed_tokens"]
+    for li in range(cfg.num_layers):
+        for suffix, (tw, what, role) in _C3_LAYER.items():
+            pre = f"und.layers.{li}." if tw == "und" else f"gen.layers.{li}."
+            apre, mpre = ("self_attn.", "mlp.") if tw == "und" else ("", "")
+            key = f"layers.{li}.{suffix}"
+            if role is None and what != "o":
+                out[key] = sd[pre + what]
+            elif what == "o":
+                out[key] = sd[pre + apre + "o_proj"]
+            elif what == "qkv":
+                w = sd[pre + apre + "qkv_proj"]
+                q, k, v = w[:Hq * D], w[Hq * D:(Hq + Hkv) * D], w[(Hq + Hkv) * D:]
+                out[key] = {"q": q, "k": k, "v": v}[role].clone()
+            else:
+                if role == "down":
+                    out[key] = sd[pre + mpre + "down_proj"]
+                else:
+                    gate, up = gemm.split_gate_up(sd[pre + mpre + "gate_up_proj"])
+                    out[key] = (gate if role == "gate" else up).clone()
+    return out

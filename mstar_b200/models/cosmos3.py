@@ -28,7 +28,7 @@ from ..ops import gemm
 from ..parallel.comm import CommGroup
 from ..parallel.sequence_parallel import gather_sequence, sp_seq_split
 from .base import small_scale, EngineType, ForwardPassArgs, Model
-from .codec import Code2Wav
+from .sound_decoder import SoundDecoder, load_sound_decoder, pcm_layout, sound_decoder_config
 from .decoder import DecoderConfig, DecoderLM, _param
 from .dit import MoTGenTower, grid_positions, patchify, sinusoidal_embedding, unpatchify
 from .schedulers import FlowUniPC
@@ -45,7 +45,8 @@ def cosmos3_nano_config(dtype=torch.bfloat16) -> DecoderConfig:
 
 class Cosmos3Transformer(torch.nn.Module):
     def __init__(self, cfg: DecoderConfig, latent_channels: int, patch=(1, 2, 2), action_dim: int = 32,
-                 tp: CommGroup | None = None, sp: CommGroup | None = None, device="cpu"):
+                 tp: CommGroup | None = None, sp: CommGroup | None = None, device="cpu", sound_dim: int = 64,
+                 num_domains: int = 32):
         super().__init__()
         tp, sp = tp or CommGroup.trivial(), sp or CommGroup.trivial()
         inst = tp.instance or sp.instance or (tp if sp.size == 1 else sp)
@@ -58,7 +59,20 @@ class Cosmos3Transformer(torch.nn.Module):
         self.proj_out_w, self.proj_out_b = _param((pd, H), dt, device), _param((pd,), dt, device)
         self.t1_w, self.t1_b = _param((H, 256), dt, device), _param((H,), dt, device)
         self.t2_w, self.t2_b = _param((H, H), dt, device), _param((H,), dt, device)
-        self.act_in_w, self.act_out_w = _param((H, action_dim), dt, device), _param((action_dim, H), dt, device)
+        # robot actions: one full (weight, bias) pair per embodiment domain, stored as rows of two tables (the
+        # published layout: row d of ``fc`` is that domain's [in, out] matrix, flattened)
+        self.action_dim, self.num_domains = action_dim, num_domains
+        self.act_in_fc, self.act_in_bias = _param((num_domains, action_dim * H), dt, device), _param((num_domains, H), dt, device)
+        self.act_out_fc = _param((num_domains, H * action_dim), dt, device)
+        self.act_out_bias = _param((num_domains, action_dim), dt, device)
+        self.action_modality_embed = _param((H,), dt, device)
+        self.audio_modality_embed = _param((H,), dt, device)
+        self._domain_w: dict = {}
+        # sound latents ([sound_dim] per latent frame) enter and leave the generation tower through their own pair
+        # of projections and are denoised jointly with the video tokens
+        self.sound_dim = sound_dim
+        self.audio_in_w, self.audio_in_b = _param((H, sound_dim), dt, device), _param((H,), dt, device)
+        self.audio_out_w, self.audio_out_b = _param((sound_dim, H), dt, device), _param((sound_dim,), dt, device)
         self.device = torch.device(device)
 
     def init_random(self, seed=0):
@@ -71,15 +85,27 @@ class Cosmos3Transformer(torch.nn.Module):
             p.data.copy_((torch.randn(p.shape, generator=g) * (0.02 if p.dim() == 1 else 1 / math.sqrt(p.shape[-1]))).to(p.dtype))
         return self
 
+    def action_weights(self, domain: int):
+        """(in weight [H, A], in bias [H], out weight [A, H], out bias [A]) of one embodiment domain, in the
+        [out, in] orientation the GEMM takes; built once per domain."""
+        w = self._domain_w.get(domain)
+        if w is None:
+            H, A = self.cfg.hidden_size, self.action_dim
+            w = (self.act_in_fc[domain].view(A, H).t().contiguous(), self.act_in_bias[domain].contiguous(),
+                 self.act_out_fc[domain].view(H, A).t().contiguous(), self.act_out_bias[domain].contiguous())
+            self._domain_w[domain] = w
+        return w
+
     def time_embed(self, t: torch.Tensor) -> torch.Tensor:
         e = sinusoidal_embedding(t, 256).to(self.cfg.dtype)
         e = gemm.linear(e, self.t1_w, bias=self.t1_b)
         return gemm.linear(torch.nn.functional.silu(e.float()).to(e.dtype), self.t2_w, bias=self.t2_b)
 
     def denoise(self, tokens: torch.Tensor, positions: torch.Tensor, t: float, n_branches: int, prefix_ctx,
-                out_w, out_b=None) -> torch.Tensor:
+                out_w=None, out_b=None) -> torch.Tensor:
         """tokens: [S, H] embedded noisy tokens of ONE request; runs ``n_branches`` guidance branches packed as
-        [branch0 | branch1 | ...] and returns [n_branches, S, out] fp32."""
+        [branch0 | branch1 | ...] and returns [n_branches, S, out] fp32 (``out_w=None``: the hidden states
+        [n_branches, S, H], for callers that project bands of the sequence with different heads)."""
         S = tokens.shape[0]
         x = tokens + self.time_embed(torch.tensor([t], device=tokens.device))
         x = x.repeat(n_branches, 1)
@@ -95,6 +121,8 @@ class Cosmos3Transformer(torch.nn.Module):
             h = gather_sequence(h, self.sp, S_tot)
         else:
             h = self.gen(x, pos, plan, prefix_ctx=prefix_ctx, S_total=S_tot)
+        if out_w is None:
+            return h.reshape(n_branches, S, -1)
         out = gemm.linear(h, out_w, bias=out_b, out_dtype=torch.float32)
         return out.reshape(n_branches, S, -1)
 
@@ -181,10 +209,13 @@ class Cosmos3DiTSubmodule(ARNodeSubmodule):
         cond = st.get("cond_latent")
         if cond is not None and not action:
             x[:, :1] = cond[:, :1]
+        if walk == "video_sound_gen":
+            return self._video_sound_step(ei, ni, ctx, x, sched, gs, nb, off, cond)
         if action:                                   # [horizon, action_dim] tokens on a 1-D position ladder
-            tok = gemm.linear(x.to(m.cfg.dtype), m.act_in_w)
+            w_in, b_in, w_out, b_out = m.action_weights(int(md.get("domain_id", 0)))
+            tok = gemm.linear(x.to(m.cfg.dtype), w_in, bias=b_in) + m.action_modality_embed
             pos = (torch.arange(x.shape[0], dtype=torch.int32, device=self.device) + off)[None].repeat(3, 1)
-            v = m.denoise(tok, pos, sched.timestep(), nb, ctx, m.act_out_w)
+            v = m.denoise(tok, pos, sched.timestep(), nb, ctx, w_out, b_out)
         else:
             p, grid = patchify(x, m.patch)
             tok = gemm.linear(p.to(m.cfg.dtype), m.proj_in_w, bias=m.proj_in_b)
@@ -197,29 +228,65 @@ class Cosmos3DiTSubmodule(ARNodeSubmodule):
             x[:, :1] = cond[:, :1]
         return {"latents": x}
 
+    def _video_sound_step(self, ei, ni, ctx, x, sched, gs, nb, off, cond):
+        """One joint step of the [video | sound] sequence: the sound latents ride behind the video tokens as one
+        token per sound latent frame, placed on the video's temporal axis at their own frame rate; both bands share
+        the attention, each leaves through its own head, and ONE scheduler step updates the packed pair."""
+        m, md = self.m, ni.kwargs
+        n_sound = int(md["num_sound"])
+        if ni.tensor_inputs.get("sound_latents"):
+            xs = ni.tensor_inputs["sound_latents"][-1].to(self.device, torch.float32)
+        else:       # first iteration: sound noise from the stream that follows the video noise of the same seed
+            info = ei.per_request_info[ni.request_id]
+            g = torch.Generator().manual_seed(int(md.get("seed", info.random_seed or 0)) + 1)
+            xs = torch.randn((m.sound_dim, n_sound), generator=g).to(self.device)
+        p, grid = patchify(x, m.patch)
+        tok = gemm.linear(p.to(m.cfg.dtype), m.proj_in_w, bias=m.proj_in_b)
+        pos = grid_positions(*grid, self.device, (off, off, off))
+        stok = gemm.linear(xs.t().contiguous().to(m.cfg.dtype), m.audio_in_w, bias=m.audio_in_b) + m.audio_modality_embed
+        ratio = float(md.get("sound_rate_ratio", 1.0))          # video latent frames per sound latent frame
+        st_t = (torch.arange(n_sound, device=self.device, dtype=torch.float32) * ratio).floor().to(torch.int32) + off
+        spos = torch.stack([st_t, torch.full_like(st_t, off), torch.full_like(st_t, off)])
+        Sv = tok.shape[0]
+        h = m.denoise(torch.cat([tok, stok]), torch.cat([pos, spos], dim=1), sched.timestep(), nb, ctx)
+        v = gemm.linear(h[:, :Sv].reshape(nb * Sv, -1), m.proj_out_w, bias=m.proj_out_b, out_dtype=torch.float32)
+        v = torch.stack([unpatchify(vb, grid, m.patch, m.C) for vb in v.reshape(nb, Sv, -1)])
+        vs = gemm.linear(h[:, Sv:].reshape(nb * n_sound, -1), m.audio_out_w, bias=m.audio_out_b,
+                         out_dtype=torch.float32).reshape(nb, n_sound, -1).transpose(1, 2)
+        if nb == 2:
+            v, vs = v[1] + gs * (v[0] - v[1]), vs[1] + gs * (vs[0] - vs[1])
+        else:
+            v, vs = v[0], vs[0]
+        nv = x.numel()
+        packed = sched.step(torch.cat([v.reshape(-1), vs.reshape(-1)]), torch.cat([x.reshape(-1), xs.reshape(-1)]))
+        x, xs = packed[:nv].reshape(x.shape), packed[nv:].reshape(xs.shape)
+        if cond is not None:
+            x[:, :1] = cond[:, :1]
+        return {"latents": x, "sound_latents": xs}
+
     def postprocess(self, request_id, request_info, outputs, inputs):
         outputs.pop("new_token", None)
         outputs.pop("new_token_host", None)
         return outputs
 
 
-class AudioDecodeSubmodule(NodeSubmodule):
-    """Sound track from the video latents' temporal envelope through a code-to-waveform stack."""
+class SoundDecodeSubmodule(NodeSubmodule):
+    """Sound latents [C, T] -> stereo waveform, cut to the requested number of samples, in interleaved sample order."""
 
-    def __init__(self, dec: Code2Wav, device, n_codes: int):
+    def __init__(self, dec: SoundDecoder, device):
         super().__init__(device, torch.float32)
-        self.dec, self.n_codes = dec, n_codes
+        self.dec = dec
 
     def get_stateless_flavor(self):
         return "audio_codec"
 
     def forward(self, graph_walk, engine_inputs, ni, **kw):
-        z = ni.tensor_inputs["latents"][-1].float()
-        env = z.mean(dim=(0, 2, 3))                                   # one value per latent frame
-        codes = ((env - env.min()) / (env.max() - env.min() + 1e-6) * (self.n_codes - 1)).long()
-        with torch.no_grad():
-            wav = self.dec(codes[None, None].to(self.device))[0]
-        return {"audio": wav.float().cpu().reshape(-1)}
+        z = ni.tensor_inputs["sound_latents"][-1].to(self.device, self.dec.conv1.weight.dtype)
+        wav = self.dec.decode(z)
+        n = int((ni.kwargs or {}).get("sound_samples", 0))
+        if 0 < n < wav.shape[-1]:
+            wav = wav[..., :n]
+        return {"audio": pcm_layout(wav.float()).cpu()}
 
 
 class Cosmos3Model(Model):
@@ -240,6 +307,8 @@ class Cosmos3Model(Model):
         else:
             self.cfg = cosmos3_nano_config(dt)
             self.vae_cfg = cosmos3_vae_config()
+        self.sound_cfg = sound_decoder_config(small)
+        self.action_dim = 32 if small else 64
         self.num_steps = num_steps or (3 if small else 35)
         self.page_size, self.max_num_pages = page_size, max_num_pages
         self.dtype = dt
@@ -252,11 +321,13 @@ class Cosmos3Model(Model):
         prefill_c = Sequential([enc, GraphNode("dit", {"input_ids", "neg_input_ids", "image_latent"}, pre_out)])
 
         def gen(modality, sound=False):
-            dit = GraphNode("dit", {"latents"}, [GraphEdge("dit", "latents")], enable_async_scheduling=False)
-            loop_out = [GraphEdge("vae_decoder", "latents")] + ([GraphEdge("audio_decoder", "latents")] if sound else [])
+            names = ["latents"] + (["sound_latents"] if sound else [])
+            dit = GraphNode("dit", set(names), [GraphEdge("dit", n) for n in names], enable_async_scheduling=False)
+            loop_out = [GraphEdge("vae_decoder", "latents")] + ([GraphEdge("audio_decoder", "sound_latents")] if sound else [])
             tail = [GraphNode("vae_decoder", {"latents"}, [GraphEdge(EMIT_TO_CLIENT, modality, output_modality=modality)])]
             if sound:
-                tail.append(GraphNode("audio_decoder", {"latents"}, [GraphEdge(EMIT_TO_CLIENT, "audio", output_modality="audio")]))
+                tail.append(GraphNode("audio_decoder", {"sound_latents"},
+                                      [GraphEdge(EMIT_TO_CLIENT, "audio", output_modality="audio")]))
             return Sequential([Loop(dit, max_iters=self.num_steps, outputs=loop_out, name="denoise_loop"),
                                tail[0] if len(tail) == 1 else Parallel(tail)])
         act = GraphNode("dit", {"latents"}, [GraphEdge("dit", "latents")], enable_async_scheduling=False)
@@ -284,23 +355,37 @@ class Cosmos3Model(Model):
     def get_autocast_dtype(self):
         return self.dtype
 
+    def get_output_sample_rate(self) -> int:
+        return int(self.sound_cfg["sampling_rate"])
+
+    def get_output_audio_channels(self) -> int:
+        return int(self.sound_cfg["dec_out_channels"])
+
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "dit":
-            m = Cosmos3Transformer(self.cfg, self.vae_cfg.latent_channels, tp=tp_group, sp=sp_group, device=device)
+            m = Cosmos3Transformer(self.cfg, self.vae_cfg.latent_channels, tp=tp_group, sp=sp_group, device=device,
+                                   sound_dim=int(self.sound_cfg["vocoder_input_dim"]), action_dim=self.action_dim,
+                                   num_domains=2 if self.small else 32)
             if self.skip_weight_loading or self.model_dir is None:
                 m.init_random(0)
             else:
-                from .loader import load_named_tensors
-                load_named_tensors(m, self.model_dir)
+                import os
+                from .checkpoints import load_cosmos3_transformer
+                load_cosmos3_transformer(m, os.path.join(self.model_dir, "transformer"))
             return Cosmos3DiTSubmodule(m, device, self.num_steps, 5.0)
         if node_name in ("vae_encoder", "vae_decoder"):
             vae = ConvVAE(self.vae_cfg).to(device=device, dtype=self.dtype).eval()
             return (VaeEncodeSubmodule(vae, device, self.dtype) if node_name == "vae_encoder"
                     else _Cosmos3VaeDecode(vae, device, self.dtype))
         if node_name == "audio_decoder":
-            kw = (dict(n_codebooks=1, codebook_size=64, dim=16, rates=(2, 2), channels=32) if self.small
-                  else dict(n_codebooks=1))
-            return AudioDecodeSubmodule(Code2Wav(**kw).to(device).eval(), device, kw.get("codebook_size", 2048))
+            import os
+            if (not self.skip_weight_loading and self.model_dir
+                    and os.path.isdir(os.path.join(self.model_dir, "sound_tokenizer"))):
+                dec = load_sound_decoder(self.model_dir, device=device, dtype=self.dtype)
+            else:
+                torch.manual_seed(11)
+                dec = SoundDecoder(self.sound_cfg).to(device=device, dtype=self.dtype).eval()
+            return SoundDecodeSubmodule(dec, device)
         raise KeyError(node_name)
 
     # ---- request life cycle ----
@@ -336,9 +421,12 @@ class Cosmos3Model(Model):
         outs = md.get("output_modalities") or ["image"]
         step_md = {k: mk[k] for k in ("shift", "seed") if k in mk}
         step_md["guidance_scale"] = float(mk.get("guidance_scale", 6.0))
+        edges = [GraphEdge("dit", "latents", [])]
         if "action" in outs:
             walk, steps = "action_gen", int(mk.get("num_steps", 10))
-            shape = [int(mk.get("horizon", 16)), 32]
+            shape = [int(mk.get("horizon", 16)), self.action_dim]
+            if "domain_id" in mk:
+                step_md["domain_id"] = int(mk["domain_id"])
             step_md["num_tokens"] = shape[0]
         else:
             image = "video" not in outs
@@ -347,9 +435,23 @@ class Cosmos3Model(Model):
             shape = self.latent_shape(mk, image)
             pt, ph, pw = (1, 2, 2)
             step_md["num_tokens"] = (shape[1] // pt) * (shape[2] // ph) * (shape[3] // pw)
+            if walk == "video_sound_gen":
+                # the sound track lasts as long as the video unless the request says otherwise; one latent frame per
+                # hop of the sound decoder
+                import math as _m
+                sr = int(self.sound_cfg["sampling_rate"])
+                hop = _m.prod(self.sound_cfg["dec_strides"])
+                fps = float(mk.get("fps", 24))
+                frames = int(mk.get("num_frames", 5 if self.small else 93))
+                samples = max(1, round(float(mk.get("sound_duration", frames / fps)) * sr))
+                n_sound = max(1, _m.ceil(samples / hop))
+                step_md.update(num_sound=n_sound, sound_samples=samples,
+                               sound_rate_ratio=(fps / self.vae_cfg.temporal_factor) / (sr / hop))
+                step_md["num_tokens"] += n_sound
+                edges.append(GraphEdge("dit", "sound_latents", []))
         step_md.update(num_steps=steps, latent_shape=shape)
         return ForwardPassArgs({"graph_walk": walk, "dynamic_loop_iter_counts": {"denoise_loop": steps}},
-                               [GraphEdge("dit", "latents", [])], step_metadata=step_md)
+                               edges, step_metadata=step_md)
 
     def postprocess(self, output, modality, request_kwargs):
         from ..api_server.media_io import float_to_pcm16, frames_to_video, tensor_to_png
@@ -359,7 +461,7 @@ class Cosmos3Model(Model):
         if modality == "video":
             return frames_to_video(t.permute(1, 0, 2, 3), fps=float(request_kwargs.get("fps", 24)))[0]
         if modality == "audio":
-            return float_to_pcm16(t)
+            return float_to_pcm16(t)                # [samples, channels]: interleaved PCM
         return t.float().numpy().tobytes()          # action chunk: raw float32 [horizon, action_dim]
 
 

@@ -15,6 +15,7 @@ distributed/{linear,attention,mlp,embedding}.py, mstar/model/qwen3_omni/componen
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -23,7 +24,7 @@ from torch import nn
 from ..engine.cache_manager import BatchContext
 from ..ops import attention as attn_ops
 from ..ops import elementwise as ew
-from ..ops import gemm, norm as norm_ops, rope as rope_ops
+from ..ops import _lib, gemm, norm as norm_ops, rope as rope_ops
 from ..parallel.comm import CommGroup
 
 
@@ -91,6 +92,24 @@ def tp_reduce(x: torch.Tensor, tp: CommGroup) -> torch.Tensor:
     return tp.all_reduce(x)
 
 
+# L2 management of the decode step (few token rows: every projection streams its weight once and is bound by its own
+# latency chain, not by HBM). Each weight-streaming kernel asks the L2 for the weights of the kernel after it, so the
+# HBM keeps working through the gaps, and marks what it streams itself evict-first. The amounts keep what is resident
+# plus what is requested inside the 126 MB L2.
+L2_PREFETCH_MAX_ROWS = 256
+L2_BUDGET = 96 << 20
+L2_ATTN_PREFETCH = 64 << 20
+
+
+def _l2_prefetch_on(h: torch.Tensor) -> bool:
+    return (h.is_cuda and h.shape[0] <= L2_PREFETCH_MAX_ROWS and os.environ.get("MSTAR_L2_PREFETCH", "1") != "0")
+
+
+def _wbytes(w) -> int:
+    t = w.data
+    return t.numel() * t.element_size()
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_idx: int, tp: CommGroup, device):
         super().__init__()
@@ -107,7 +126,11 @@ class Attention(nn.Module):
         self.k_norm = _param((self.D,), cfg.dtype, device) if cfg.qk_norm else None
 
     def forward(self, h: torch.Tensor, ctx: BatchContext, rope: "RopeTables",
-                partial_out: torch.Tensor | None = None) -> torch.Tensor:
+                partial_out: torch.Tensor | None = None, next_w=None) -> torch.Tensor:
+        """``next_w``: the weight of the projection that follows this block (the MLP's first), for the L2 requests."""
+        pf = _l2_prefetch_on(h)
+        if pf:
+            _lib.prefetch_hint(self.o_proj)                     # fetched while the QKV projection runs
         qkv = gemm.linear(h, self.qkv_proj, bias=self.qkv_bias)
         kv = ctx.kv(self.layer_idx) if ctx.kv_layers else None
         q, _, _ = rope_ops.rope_kv(qkv, ctx.positions, rope.inv_freq, self.Hq, self.Hkv, self.D,
@@ -115,7 +138,13 @@ class Attention(nn.Module):
                                    norm_eps=self.cfg.rms_eps, cache=kv, token_req=ctx.token_req,
                                    cache_pos=ctx.cache_pos, page_indptr=ctx.plan.page_indptr,
                                    page_indices=ctx.plan.page_indices)
+        if pf and next_w is not None:
+            _lib.prefetch_hint(next_w, 0, L2_ATTN_PREFETCH)     # while the K/V pages stream through, evict-first
         a = attn_ops.attention(q, ctx.plan, kv_cache=kv)
+        if pf and next_w is not None:
+            _lib.prefetch_hint(next_w, L2_ATTN_PREFETCH, max(0, L2_BUDGET - L2_ATTN_PREFETCH - _wbytes(self.o_proj)))
+        elif pf:
+            _lib.prefetch_hint(None, l2_hints=1)
         return row_parallel_linear(a.reshape(a.shape[0], self.Hq * self.D), self.o_proj, self.tp,
                                    partial_out=partial_out)
 
@@ -131,8 +160,18 @@ class GatedMLP(nn.Module):
         self.gate_up_proj = _param((2 * self.F, hidden), dtype, device)
         self.down_proj = _param((hidden, self.F), dtype, device)
 
-    def forward(self, h: torch.Tensor, reduce: bool = True, partial_out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, reduce: bool = True, partial_out: torch.Tensor | None = None,
+                next_w=None) -> torch.Tensor:
+        """``next_w``: the weight that is streamed after this block (the next layer's QKV projection or the head)."""
+        pf = _l2_prefetch_on(h)
+        if pf:
+            _lib.prefetch_hint(self.down_proj, 0, max(16 << 20, L2_BUDGET - _wbytes(self.gate_up_proj)))
         g = gemm.linear(h, self.gate_up_proj, epilogue=gemm.EPILOGUE_SWIGLU)
+        if pf:
+            if next_w is not None:
+                _lib.prefetch_hint(next_w, 0, max(16 << 20, L2_BUDGET - _wbytes(self.down_proj)))
+            else:
+                _lib.prefetch_hint(None, l2_hints=1)
         if not reduce:
             return gemm.linear(g, self.down_proj)
         return row_parallel_linear(g, self.down_proj, self.tp, partial_out=partial_out)
@@ -152,25 +191,26 @@ class DecoderLayer(nn.Module):
         else:
             self.mlp = GatedMLP(cfg.hidden_size, cfg.intermediate_size, tp, cfg.dtype, device)
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor | None, ctx: BatchContext, rope) -> tuple:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None, ctx: BatchContext, rope, next_w=None) -> tuple:
         if residual is None:
             residual = x
             h, _ = norm_ops.norm(x, self.input_layernorm, self.cfg.rms_eps)
         else:
             h, residual = norm_ops.norm(x, self.input_layernorm, self.cfg.rms_eps, residual=residual)
-        a = self.self_attn(h, ctx, rope)
+        dense = isinstance(self.mlp, GatedMLP)
+        a = self.self_attn(h, ctx, rope, next_w=self.mlp.gate_up_proj if dense else None)
         h, residual = norm_ops.norm(a, self.post_attention_layernorm, self.cfg.rms_eps, residual=residual)
-        return self.mlp(h), residual
+        return (self.mlp(h, next_w=next_w) if dense else self.mlp(h)), residual
 
     def forward_tp_fused(self, h: torch.Tensor, residual: torch.Tensor, ctx: BatchContext, rope, tpf, site: int,
-                         gamma_next: torch.Tensor):
+                         gamma_next: torch.Tensor, next_w=None):
         """Tensor-parallel layer without all-reduce kernels. ``h`` is the normalised input, ``residual`` the residual
         stream. Both row-parallel GEMMs write partial sums into heap slots; the two norm kernels of the layer (the
         post-attention norm and the NEXT layer's input norm, ``gamma_next``) sum them across ranks as they read."""
         M = h.shape[0]
-        self.self_attn(h, ctx, rope, partial_out=tpf.partial_out(site, M))
+        self.self_attn(h, ctx, rope, partial_out=tpf.partial_out(site, M), next_w=self.mlp.gate_up_proj)
         h, residual = tpf.reduce_norm(site, M, self.post_attention_layernorm, self.cfg.rms_eps, residual)
-        self.mlp(h, partial_out=tpf.partial_out(site + 1, M))
+        self.mlp(h, partial_out=tpf.partial_out(site + 1, M), next_w=next_w)
         return tpf.reduce_norm(site + 1, M, gamma_next, self.cfg.rms_eps, residual)
 
 
@@ -324,13 +364,20 @@ class DecoderLM(nn.Module):
             n = len(self.layers)
             for i, layer in enumerate(self.layers):
                 gamma_next = self.layers[i + 1].input_layernorm if i + 1 < n else self.norm
-                h, residual = layer.forward_tp_fused(h, residual, ctx, self.rope, self.tpf, 2 * i, gamma_next)
+                h, residual = layer.forward_tp_fused(h, residual, ctx, self.rope, self.tpf, 2 * i, gamma_next,
+                                                     next_w=self._weight_after(i))
             return h
         residual = None
-        for layer in self.layers:
-            x, residual = layer(x, residual, ctx, self.rope)
+        for i, layer in enumerate(self.layers):
+            x, residual = layer(x, residual, ctx, self.rope, next_w=self._weight_after(i))
         h, _ = norm_ops.norm(x, self.norm, self.cfg.rms_eps, residual=residual)
         return h
+
+    def _weight_after(self, i: int):
+        """The weight streamed after layer ``i``: the next layer's QKV projection, or the output head."""
+        if i + 1 < len(self.layers):
+            return self.layers[i + 1].self_attn.qkv_proj
+        return self.head_weight() if self.cfg.has_lm_head else None
 
     def logits(self, hidden_rows: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
         if self.vocab_parallel and hidden_rows.shape[0] <= self.tpf.max_logit_rows:
@@ -338,6 +385,8 @@ class DecoderLM(nn.Module):
         if self.vocab_parallel:
             raise ValueError(f"{hidden_rows.shape[0]} logit rows exceed the vocabulary-parallel logits buffer "
                              f"({self.tpf.max_logit_rows}): raise tp_max_logit_rows or set MSTAR_TP_VOCAB_PARALLEL=0")
+        if _l2_prefetch_on(hidden_rows):
+            _lib.prefetch_hint(None, l2_hints=1)      # the head's weight passes through the L2 once
         return gemm.linear(hidden_rows, self.head_weight(), out_dtype=out_dtype)
 
     def forward(self, ctx: BatchContext, input_ids: torch.Tensor | None = None,

@@ -96,6 +96,21 @@ def status_copy_async(pinned: torch.Tensor) -> None:
         raise RuntimeError("status copy failed: " + kernels().mstar_last_error().decode(errors="replace"))
 
 
+def prefetch_hint(w=None, lo: int = 0, nbytes: int | None = None, l2_hints: int = 1) -> None:
+    """Tell the next GEMM / decode-attention launch on the current device to pull bytes [lo, lo + nbytes) of ``w`` (a
+    tensor or a packed weight: the projection that runs AFTER that launch) into the L2 while it runs, and to mark its
+    own streamed operand evict-first. ``w=None`` asks for the evict-first marking only (``l2_hints=0``: clears a pending hint). Used once by the launch that takes it."""
+    L = kernels()
+    if w is None:
+        L.mstar_prefetch_hint(ctypes.c_void_p(0), ctypes.c_ulonglong(0), int(l2_hints) if nbytes is None else 0)
+        return
+    t = w.data
+    total = t.numel() * t.element_size()
+    lo = min(max(0, int(lo)), total)
+    n = total - lo if nbytes is None else max(0, min(int(nbytes), total - lo))
+    L.mstar_prefetch_hint(ctypes.c_void_p(t.data_ptr() + lo), ctypes.c_ulonglong(n), int(l2_hints))
+
+
 def decode_status(code: int) -> str:
     """Readable form of a status code: which kernel gave up in which phase."""
     names = {1: "gemm", 2: "attention", 3: "decode attention", 4: "expert gemm", 5: "collective", 6: "gemm+all-reduce",

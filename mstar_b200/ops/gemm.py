@@ -44,6 +44,11 @@ def interleave_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor
     return out.reshape(2 * gate_w.shape[0], *gate_w.shape[1:]).contiguous()
 
 
+def split_gate_up(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of ``interleave_gate_up``: (gate rows, up rows)."""
+    return w[0::2].contiguous(), w[1::2].contiguous()
+
+
 class PackedWeight:
     """A [N, K] bf16 weight stored tile by tile for streaming: ``[ceil(N/128)][ceil(K/64)]`` tiles of 128 rows x 64
     columns, each 16 KB contiguous, zero-padded at the ragged edges. One TMA box of the GEMM kernels is then one

@@ -32,3 +32,20 @@ def _kernel_status_clean(request):
         if request.node.get_closest_marker("expects_status") is None:
             code = _lib.read_status(clear=True)[0]
             assert code == 0, f"kernel status word set: {code:#x}"
+
+
+def reference_module(name: str):
+    """Import a module of the reference project installed under ``baseline/_ref`` (the CPU oracle of the parity
+    tests); the test is skipped when the package is not there or does not import on this machine."""
+    import importlib
+    import os
+    import sys
+    ref = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "mstar")):
+        pytest.skip("reference package not installed under baseline/_ref")
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        return importlib.import_module(name)
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"reference module {name} does not import here: {type(e).__name__}: {e}")

@@ -86,3 +86,39 @@ def test_wan22_dit_matches_the_reference_module_on_a_shared_checkpoint(tmp_path)
         got = ours(lat, ts_frame, ctx_kv, [8] * B)
     err = (got - want.float()).abs().max().item()
     assert err < 2e-3 * max(1.0, want.abs().max().item()), err
+
+
+def _tiny_cosmos3(seed):
+    from mstar_b200.models.cosmos3 import Cosmos3Transformer
+    from mstar_b200.models.decoder import DecoderConfig
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                        vocab_size=128, qk_norm=True, mrope_sections=[2, 3, 3], has_lm_head=False, dtype=torch.float32)
+    return Cosmos3Transformer(cfg, 4, action_dim=8, sound_dim=8, num_domains=3).init_random(seed)
+
+
+def test_cosmos3_loader_is_strict_and_round_trips(tmp_path):
+    src = _tiny_cosmos3(5)
+    keys = ck.cosmos3_checkpoint_keys(src)
+    assert {"layers.1.self_attn.add_k_proj.weight", "layers.0.mlp_moe_gen.up_proj.weight", "norm_moe_gen.weight",
+            "layers.1.input_layernorm_moe_gen.weight", "action_proj_in.fc.weight", "audio_proj_out.bias",
+            "time_embedder.linear_2.weight", "layers.0.self_attn.norm_added_q.weight"} <= set(keys)
+    assert keys["action_proj_in.fc.weight"].shape == (3, 8 * 64)
+    keys["lm_head.weight"] = torch.zeros(128, 64)                 # present in published files, never loaded
+    d = tmp_path / "transformer"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in keys.items()}, str(d / "diffusion_pytorch_model.safetensors"))
+    dst = _tiny_cosmos3(6)
+    assert ck.load_cosmos3_transformer(dst, str(d))["loaded"] == len(dict(dst.named_parameters()))
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+    w_in, b_in, w_out, b_out = dst.action_weights(2)
+    assert torch.equal(w_in, keys["action_proj_in.fc.weight"][2].view(8, 64).t())
+    for mutate in (lambda k: k.pop("layers.1.mlp_moe_gen.gate_proj.weight"),
+                   lambda k: k.update({"layers.0.self_attn.to_extra.weight": torch.zeros(1)}),
+                   lambda k: k.update({"audio_proj_in.weight": torch.zeros(64, 9)}),
+                   lambda k: k.pop("norm_moe_gen.weight")):
+        badk = dict(keys)
+        mutate(badk)
+        save_file({k: v.contiguous() for k, v in badk.items()}, str(d / "diffusion_pytorch_model.safetensors"))
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_cosmos3_transformer(_tiny_cosmos3(7), str(d))
