@@ -106,6 +106,44 @@ def reference_arm(args):
     print(json.dumps(run_reference(args)), flush=True)
 
 
+GENERATION_REFERENCE_UNAVAILABLE = {
+    "bagel_t2i": "the reference's BAGEL server loads the published checkpoint directory (tokenizer files, ae.safetensors, "
+                 "ema.safetensors, about 29 GB) at start-up; there is no network and no synthetic checkpoint of that "
+                 "layout is written",
+    "cosmos3_t2v": "the reference's Cosmos3 transformer imports diffusers (diffusers.models.embeddings.Timesteps), "
+                   "which is not installed in this image, and there is no index to install it from",
+}
+
+
+def generation_workload(args) -> None:
+    """Served image / video generation latency (``--workload bagel_t2i | cosmos3_t2v``): rank 0 starts the
+    multi-process deployment over the GPUs of the node and times whole requests through the public API."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "workload": args.workload,
+                          "unavailable": GENERATION_REFERENCE_UNAVAILABLE[args.workload]}), flush=True)
+        return
+    from mstar_b200.bench.serve_workloads import run_workload
+    n_req = max(1, min(args.steps, 3)) if args.steps != 210 else 1
+    tp, sp = (2, 2) if (args.workload == "cosmos3_t2v" and args.gpus >= 4) else ((2, 1) if args.workload == "cosmos3_t2v" and args.gpus >= 2 else (1, 1))
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))).start()
+    r = run_workload(args.workload, args.gpus, requests=n_req, tp=tp, sp=sp)
+    clocks = sampler.stop()
+    out = {"metric": f"{args.workload} served latency", "value": r.get("value"), "unit": r["unit"], "n_gpus": args.gpus,
+           "steps": n_req, "warmup": 1, "ms_per_step": None if r.get("value") is None else round(1e3 * r["value"], 1),
+           "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": r["data"],
+           "config": r["config"], "impl": "ours", "clocks": clocks,
+           "e2e": {"value": r.get("value"), "unit": r["unit"], "timing": "wall clock from submit_request to the last "
+                   "result byte, multi-process deployment", "latencies_s": r.get("latencies_s"),
+                   "s_per_denoise_step": r.get("s_per_step"), "result_bytes": r.get("result_bytes")},
+           "reference": GENERATION_REFERENCE_UNAVAILABLE[args.workload]}
+    if "error" in r:
+        out["error"] = r["error"]
+    print(json.dumps(out), flush=True)
+
+
 def main():
     import faulthandler
     faulthandler.enable()
@@ -119,7 +157,13 @@ def main():
     ap.add_argument("--gen-tokens", type=int, default=1204)
     ap.add_argument("--no-e2e", action="store_true", help="skip the served measurement")
     ap.add_argument("--no-engine", action="store_true", help="skip the device-timed engine measurement")
+    ap.add_argument("--workload", default="orpheus_tts", choices=["orpheus_tts", "bagel_t2i", "cosmos3_t2v"],
+                    help="orpheus_tts is the headline; the other two are served generation latencies (one request at "
+                         "a time through the multi-process deployment; --steps = timed requests)")
     args = ap.parse_args()
+    if args.workload != "orpheus_tts":
+        generation_workload(args)
+        return
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -60,8 +60,16 @@ class APIServer:
     def start(self, wait_ready_s: float = 600.0) -> "APIServer":
         self.deployment.start()
         self._thread.start()
-        if not self.ready.wait(wait_ready_s):
-            raise TimeoutError("workers did not come up")
+        deadline = time.time() + wait_ready_s
+        while not self.ready.wait(0.5):
+            dead = [p for p in self.deployment.procs if p.exitcode is not None]
+            if dead:        # a conductor / worker process that ended during start-up never reports ready
+                codes = [p.exitcode for p in dead]
+                self.shutdown()
+                raise RuntimeError(f"{len(dead)} deployment process(es) ended during start-up (exit codes {codes}); "
+                                   "their log output above says why")
+            if time.time() > deadline:
+                raise TimeoutError("workers did not come up")
         return self
 
     def shutdown(self) -> None:

@@ -186,6 +186,9 @@ class Conductor:
         graphs = self._graphs_for_walk(rd, walk)
         if not graphs:
             raise RuntimeError(f"no worker graph serves walk {walk!r}")
+        unplaced = set(self.walks[walk].nodes()) - {n for wg in self.worker_graphs for n in wg.node_names}
+        if unplaced:
+            raise RuntimeError(f"walk {walk!r} needs nodes that this deployment does not place: {sorted(unplaced)}")
         ps.walk, ps.pending_graphs = walk, {wg.graph_id for wg in graphs}
         ps.fwd_index += 1
         sampling = self.model.resolve_sampling_configs(rd.body.model_kwargs or {})

@@ -455,6 +455,9 @@ class BagelModel(Model):
                                               for lb, n in names.items()])
         return walks
 
+    def get_optional_nodes(self):
+        return {"LLM_cfg_text", "LLM_cfg_img", "combine_cfg"}       # only the guidance-parallel walks use them
+
     def get_node_engine_types(self):
         t = {n: EngineType.KV_CACHE for n in ("LLM", "LLM_cfg_text", "LLM_cfg_img")}
         t.update({n: EngineType.STATELESS for n in ("vit_encoder", "vae_encoder", "vae_decoder", "combine_cfg")})

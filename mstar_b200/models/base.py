@@ -132,9 +132,14 @@ class Model(ABC):
             if unknown:
                 raise ValueError(f"config places unknown nodes {sorted(unknown)}; model has {sorted(nodes)}")
         placed = {n for wg in wgs for n in wg.node_names}
-        if nodes - placed:
-            raise ValueError(f"nodes without placement: {sorted(nodes - placed)}")
+        if nodes - placed - set(self.get_optional_nodes()):
+            raise ValueError(f"nodes without placement: {sorted(nodes - placed - set(self.get_optional_nodes()))}")
         return wgs
+
+    def get_optional_nodes(self) -> set[str]:
+        """Nodes that only some walks use and a deployment may leave out (a request whose walk needs one is then
+        refused with an error that names it)."""
+        return set()
 
     def validate_sharding(self, wg: WorkerGraph) -> None:
         if wg.tp_size * wg.sp_size > 1:

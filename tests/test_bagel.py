@@ -96,3 +96,34 @@ def test_image_editing_uses_three_contexts(server):
     a = _run(server, ["image"], {"image": [img]}, cfg_img_scale=1.5)
     b = _run(server, ["image"], {"image": [img]}, cfg_img_scale=1.0)
     assert a["image"][0].data != b["image"][0].data
+
+
+def test_packed_deployment_without_the_guidance_parallel_nodes():
+    """The guidance-parallel nodes are optional: a one-group deployment serves the packed walks and refuses, by name,
+    a request that asks for the parallel ones."""
+    from mstar_b200.api_server.server import APIServer
+    cfg = {"model": "bagel", "model_kwargs": {"small": True},
+           "node_groups": [{"node_names": ["vit_encoder", "vae_encoder", "LLM", "vae_decoder"], "ranks": [0]}]}
+    s = APIServer(cfg, in_process=True).start(120)
+    try:
+        kw = dict(height=32, width=32, num_steps=3, cfg_text_scale=4.0, seed=0)
+        rid = s.submit_request("a cat", output_modalities=["image"], model_kwargs=kw)
+        assert s.collect_results(rid, 120)["image"][0].data[:4] == b"\x89PNG"
+        rid = s.submit_request("a cat", output_modalities=["image"], model_kwargs=dict(kw, cfg_parallel=True))
+        res = s.collect_results(rid, 120)
+        assert "error" in res and b"LLM_cfg" in res["error"][0].data
+    finally:
+        s.shutdown()
+
+
+def test_a_deployment_whose_process_dies_at_start_up_fails_fast():
+    from mstar_b200.api_server.server import APIServer
+    bad = {"model": "bagel", "model_kwargs": {"small": True}, "node_groups": [{"node_names": ["LLM"], "ranks": [0]}]}
+    import time
+    t0 = time.time()
+    try:
+        APIServer(bad, in_process=False).start(300)
+        raise AssertionError("start-up should have failed: most nodes are not placed")
+    except (RuntimeError, ValueError):
+        pass
+    assert time.time() - t0 < 120
