@@ -156,7 +156,16 @@ def main():
         dist.all_reduce(gemm.linear(xg, wg))
     t_gi = timed(gemm_inplace, args.iters, args.warmup, dev)
     t_gn = timed(gemm_nccl, args.iters, args.warmup, dev)
+    tiles = {}
+    for nc in (16, 24, 32):
+        tiles[nc] = timed(lambda i: heap.linear_all_reduce_tiles(xg, wg, big, boff, n_comm=nc), args.iters, args.warmup, dev)
+    best_nc = min(tiles, key=tiles.get)
     t_g0 = timed(lambda i: gemm.linear(xg, wg, out=yv), args.iters, args.warmup, dev)
+    report(path=f"GEMM with the all-reduce inside, row groups overlapped ({Mb}x{Nb}x{Kb} per rank)", ranks=W,
+           fused_us=round(tiles[best_nc], 2), comm_ctas=best_nc, by_comm_ctas={k: round(v, 2) for k, v in tiles.items()},
+           gemm_plus_nccl_us=round(t_gn, 2), gemm_alone_us=round(t_g0, 2),
+           roofline_us=round(max(nvls_link_us, 2.0 * Mb * Nb * Kb / (tflops * 1e6)), 2),
+           frac_of_roofline=round(max(nvls_link_us, 2.0 * Mb * Nb * Kb / (tflops * 1e6)) / tiles[best_nc], 3))
     report(path=f"GEMM -> in-place all-reduce ({Mb}x{Nb}x{Kb} per rank)", ranks=W, fused_us=round(t_gi, 2),
            gemm_plus_nccl_us=round(t_gn, 2), gemm_alone_us=round(t_g0, 2),
            roofline_us=round(max(nvls_link_us, 2.0 * Mb * Nb * Kb / (tflops * 1e6)), 2), multicast=bool(big.mc_ptr))

@@ -768,16 +768,124 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Row-parallel GEMM with the all-reduce INSIDE the kernel, overlapped tile group by tile group (large M).
+//
+// The persistent kernel below gets two kinds of CTAs in ONE launch: the first n_gemm CTAs walk the tile list and
+// store their output tiles into this rank's copy of a symmetric region; the last n_comm CTAs reduce. Tiles are
+// visited in groups of `group_p` row tiles (all column tiles of a group before the next group), so row groups are
+// completed one after another while later groups are still being multiplied. For each group the communication CTAs
+// wait (bounded) until all of its tiles are stored here (a local counter that the epilogues bump), tell the peers,
+// wait for the peers' same message, and then sum THIS rank's share of the group's rows over all ranks' copies with
+// plain peer loads and store the sum back into every rank's copy (an in-place all-reduce of the group, n (W - 1) / W
+// bytes per direction per GPU). The last group's reduction is the only communication that is not hidden behind
+// tensor-core work. GEMM CTAs never wait for communication CTAs, and all CTAs of the launch are co-resident (the grid
+// is at most one CTA per SM), so no wait can be circular; every wait is bounded and reports through the status word.
+// ---------------------------------------------------------------------------------------------
+struct TileAR {
+    PeerTable t;                 // region bases and flag bases of the group
+    McastTable mc;               // only the flag multicast is used
+    long long off;               // byte offset of C inside the region (C is [M, N] bf16, leading dimension N)
+    int n_comm;                  // communication CTAs (the last CTAs of the grid)
+    int group_p;                 // row tiles per group
+    int channel_base;            // flag channels [base, base + 2 * groups)
+    unsigned int* done;          // [groups] local: output tiles stored, per group
+    unsigned int* red_done;      // [groups] local: communication CTAs finished with the group
+    unsigned int* epoch;         // local: completed calls
+    unsigned int* arrive;        // local: communication CTAs finished
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+
+__device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, const int M, const int N,
+                                               const int tiles_p, const int tiles_q) {
+    __shared__ int s_ok;
+    __shared__ unsigned int s_epoch;
+    if (threadIdx.x == 0) { s_epoch = *ta.epoch + 1; s_ok = 1; }
+    __syncthreads();
+    const unsigned int epoch = s_epoch;
+    const int W = ta.t.world, R = ta.t.rank;
+    const int groups = (tiles_p + ta.group_p - 1) / ta.group_p;
+    for (int g = 0; g < groups && s_ok; ++g) {
+        const int tp0 = g * ta.group_p;
+        const int gp = min(ta.group_p, tiles_p - tp0);
+        if (threadIdx.x == 0) {
+            if (!wait_flag(ta.done + g, (unsigned int)(gp * tiles_q), ta.wait_limit_ns)) {
+                report_status(ta.status, KID_GEMM_AR, 0x41, g, c);
+                s_ok = 0;
+            } else {
+                if (c == 0) { __threadfence_system(); signal_all(ta.t, ta.mc, ta.channel_base + g, epoch); }
+                if (!wait_all(ta.t, ta.channel_base + g, epoch, ta.status, ta.wait_limit_ns, 0x42)) s_ok = 0;
+            }
+        }
+        __syncthreads();
+        if (!s_ok) break;
+        // vectors (8 bf16) of the group's rows; this rank's share of them; this CTA's slice of the share
+        const long long r0 = (long long)tp0 * BM;
+        long long r1 = r0 + (long long)gp * BM;
+        if (r1 > M) r1 = M;
+        const long long v0 = r0 * N / 8, v1 = r1 * N / 8;
+        const long long share = (v1 - v0 + W - 1) / W;
+        const long long a = v0 + (long long)R * share;
+        long long b = a + share;
+        if (b > v1) b = v1;
+        const long long per = (b > a ? (b - a + ta.n_comm - 1) / ta.n_comm : 0);
+        const long long ca = a + (long long)c * per;
+        long long cb = ca + per;
+        if (cb > b) cb = b;
+        long long v = ca + threadIdx.x;
+        if (W == 2) v = p2p_share<2, 16>(ta.t, ta.off, v, cb);
+        else if (W <= 4) v = p2p_share<4, 8>(ta.t, ta.off, v, cb);
+        else v = p2p_share<MAX_RANKS, 4>(ta.t, ta.off, v, cb);
+        for (; v < cb; v += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int q = 0; q < W; ++q)
+                add_bf16x8(acc, __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(ta.t.buf[q]) + ta.off + v * 16)));
+            const uint4 o = pack8(acc);
+            for (int q = 0; q < W; ++q)
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(ta.t.buf[q]) + ta.off + v * 16) = o;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int old = atomicAdd(ta.red_done + g, 1u);
+            if (old == (unsigned int)ta.n_comm - 1u) {          // the group's share is summed and stored everywhere
+                __threadfence_system();
+                signal_all(ta.t, ta.mc, ta.channel_base + groups + g, epoch);
+            }
+        }
+    }
+    // the peers' shares of every group have landed here before the kernel (and with it the stream) moves on
+    if (threadIdx.x == 0 && s_ok) {
+        for (int g = c; g < groups; g += ta.n_comm)
+            if (!wait_all(ta.t, ta.channel_base + groups + g, epoch, ta.status, ta.wait_limit_ns, 0x43)) break;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned int old = atomicAdd(ta.arrive, 1u);
+        if (old == (unsigned int)ta.n_comm - 1u) {
+            for (int g = 0; g < groups; ++g) { ta.done[g] = 0u; ta.red_done[g] = 0u; }
+            *ta.arrive = 0u;
+            __threadfence();
+            *ta.epoch = epoch;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Persistent variant for large token-major GEMMs (M > 128, one K split): one CTA per SM walks the tile list.
 // Two TMEM accumulators of BN columns: while the four epilogue warps drain tile i (TMEM -> registers -> bias /
 // activation / residual -> global), the UMMA warp is already accumulating tile i + 1 into the other buffer and the
 // TMA warp is prefetching its operands; barrier set-up, TMEM allocation and pipeline fill are paid once per CTA
 // instead of once per tile. Tiles are visited in the grouped order of the non-persistent kernel.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool FUSED = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                            const __grid_constant__ GemmParams p, const int tiles_p, const int tiles_q) {
+                            const __grid_constant__ GemmParams p, const int tiles_p, const int tiles_q,
+                            const __grid_constant__ TileAR ta) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int P_BYTES = BM * BK * 2;
@@ -795,9 +903,18 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     const int ntiles = tiles_p * tiles_q;
     const int nkb = p.kblocks_total;
     pdl_launch_dependents();
+    // tile walkers: all CTAs, or all but the communication CTAs at the end of the grid
+    const int n_walk = FUSED ? (int)gridDim.x - ta.n_comm : (int)gridDim.x;
+    if constexpr (FUSED) {
+        if ((int)blockIdx.x >= n_walk) {
+            pdl_wait();
+            tile_ar_comm_role(ta, (int)blockIdx.x - n_walk, p.M, p.N, tiles_p, tiles_q);
+            return;
+        }
+    }
     auto tile_coords = [&](int lin, int& tp, int& tq) {
-        constexpr int GROUP_P = 16;
-        if (tiles_p >= 2 * GROUP_P && tiles_q > 1) {
+        const int GROUP_P = FUSED ? ta.group_p : 16;
+        if (FUSED || (tiles_p >= 2 * GROUP_P && tiles_q > 1)) {
             const int per_group = GROUP_P * tiles_q;
             const int group = lin / per_group, within = lin - group * per_group;
             const int p0 = group * GROUP_P;
@@ -827,7 +944,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
         if (lane == 0) {
             long long g = 0;          // running k-block count over all tiles of this CTA: stage and phase
             int issued = 0;
-            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += gridDim.x) {
+            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += n_walk) {
                 int tp, tq;
                 tile_coords(t, tp, tq);
                 for (int kb = 0; kb < nkb; ++kb, ++g) {
@@ -863,7 +980,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1);
             long long g = 0;
             int it = 0;
-            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += gridDim.x, ++it) {
+            for (int t = blockIdx.x; t < ntiles && !flags[0]; t += n_walk, ++it) {
                 const int a = it & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
                 if (it >= 2 && !mbar_wait(&acc_empty[a], (uint32_t)(((it >> 1) - 1) & 1), p.wait_limit_ns)) {
@@ -900,7 +1017,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;
         int it = 0;
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+        for (int t = blockIdx.x; t < ntiles; t += n_walk, ++it) {
             const int a = it & 1;
             if (!mbar_wait(&acc_full[a], (uint32_t)((it >> 1) & 1), p.wait_limit_ns + 500000000ull)) {
                 report_status(p.status, KID_GEMM, 14, t, it);
@@ -925,6 +1042,13 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
             }
             tc_fence_before();
             mbar_arrive(&acc_empty[a]);
+            if constexpr (FUSED) {
+                // the tile is in this rank's copy of the region: count it for its row group (release: every epilogue
+                // thread fences its own stores, the four warps meet, one thread publishes)
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) atomicAdd(ta.done + tp / ta.group_p, 1u);
+            }
         }
     }
     tc_fence_before();
@@ -1292,8 +1416,27 @@ static int launch_persistent(const CUtensorMap& tmP, const CUtensorMap& tmQ, con
     const int tiles = (int)(grid.x * grid.y);
     const int ctas = tiles < device_sm_count() ? tiles : device_sm_count();
     cudaError_t e = launch_pdl(gemm_bf16_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(192), smem, stream, tmP, tmQ, p,
-                               (int)grid.x, (int)grid.y);
+                               (int)grid.x, (int)grid.y, TileAR{});
     if (e != cudaSuccess) return set_error("gemm: launch failed", e);
+    return 0;
+}
+
+// The fused form: `ta.n_comm` communication CTAs ride at the end of a grid of one CTA per SM.
+template <int BN, int STAGES>
+static int launch_persistent_fused(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int tiles_p,
+                                   int tiles_q, const TileAR& ta, cudaStream_t stream) {
+    constexpr int smem = gemm_smem_bytes(BN, STAGES);
+    static PerDeviceFlag configured;
+    if (!configured()) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, STAGES, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error("gemm+all-reduce: cudaFuncSetAttribute failed", e);
+        configured() = true;
+    }
+    const int ctas = device_sm_count();         // every CTA resident: the communication CTAs wait for the walkers
+    cudaError_t e = launch_pdl(gemm_bf16_persistent_kernel<BN, STAGES, true>, dim3(ctas), dim3(192), smem, stream, tmP, tmQ,
+                               p, tiles_p, tiles_q, ta);
+    if (e != cudaSuccess) return set_error("gemm+all-reduce: launch failed", e);
     return 0;
 }
 
@@ -1494,6 +1637,83 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     } else if (make_tmap_2d_bf16(&tmQ, Qp, rowsQ, K, ldQ, bn, BK)) return -1;
     dim3 grid((rowsP + BM - 1) / BM, (rowsQ + bn - 1) / bn, splits);
     return dispatch_tile(bn, swap, tmP, tmQ, p, grid, stream);
+}
+
+// Row-parallel projection of a tensor-parallel layer at large M with the all-reduce inside the kernel (see TileAR):
+// C = sum over ranks of A_r[M, K] * B_r[N, K]^T (+ bias, + residual: pass them on ONE rank only), bf16, written in
+// place at byte offset `off` of every rank's copy of a symmetric region (`bufs`), leading dimension N. `ctrs` is a
+// local zero-initialised array of 2 * 64 + 4 unsigned ints that belongs to this call site (group counters, epoch,
+// arrival counter). N % 8 == 0, K % 8 == 0, at most 64 row groups. Every rank of the group must make the same call.
+MSTAR_API int mstar_gemm_bf16_allreduce_tiles(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
+                                              const void* bias, const void* residual, int ld_res,
+                                              void* const* bufs, void* const* flags, int world, int rank,
+                                              void* mc_flags, long long off, void* ctrs, int channel_base, int n_comm,
+                                              int group_p, void* stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 || N % 8 || lda % 8 || ldb % 8 || off % 16)
+        return set_error("gemm+all-reduce: K, N and the leading dimensions must be multiples of 8, the offset of 16", cudaSuccess);
+    if (world < 2 || world > MAX_RANKS || rank < 0 || rank >= world)
+        return set_error("gemm+all-reduce: bad group", cudaSuccess);
+    const int sms = device_sm_count();
+    if (n_comm <= 0) n_comm = 24;
+    if (n_comm > sms / 2) n_comm = sms / 2;
+    constexpr int bn = 256;
+    const int tiles_p = (M + BM - 1) / BM, tiles_q = (N + bn - 1) / bn;
+    if (group_p <= 0) {
+        // about as many tiles per group as there are walkers, so that a group is roughly one wave
+        group_p = (sms - n_comm + tiles_q - 1) / tiles_q;
+        if (group_p < 1) group_p = 1;
+    }
+    const int groups = (tiles_p + group_p - 1) / group_p;
+    if (groups > 64) return set_error("gemm+all-reduce: more than 64 row groups", cudaSuccess);
+    GemmParams p;
+    (void)take_prefetch_hint();
+    p.M = M; p.N = N; p.K = K;
+    p.swap = 0;
+    p.splits = 1;
+    p.kblocks_total = (K + BK - 1) / BK;
+    p.kblocks_per_split = p.kblocks_total;
+    p.epilogue = 0;
+    p.out_f32 = 0;
+    p.ldc = N;
+    p.ld_res = ld_res;
+    p.C = static_cast<char*>(bufs[rank]) + off;
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+    p.workspace = nullptr;
+    p.counters = nullptr;
+    p.status = status_ptr();
+    p.wait_limit_ns = wait_limit_ns();
+    p.out_scale = 1.0f;
+    p.ar = GemmAllReduce{};
+    p.block_expert = nullptr;
+    p.num_blocks = nullptr;
+    p.row_scale = nullptr;
+    p.row_dst = nullptr;
+    TileAR ta{};
+    for (int i = 0; i < MAX_RANKS; ++i) {
+        ta.t.buf[i] = i < world ? bufs[i] : nullptr;
+        ta.t.flags[i] = i < world ? static_cast<unsigned int*>(flags[i]) : nullptr;
+    }
+    ta.t.world = world; ta.t.rank = rank;
+    ta.mc.data = nullptr;
+    ta.mc.flags = static_cast<unsigned int*>(mc_flags);
+    ta.off = off;
+    ta.n_comm = n_comm;
+    ta.group_p = group_p;
+    ta.channel_base = channel_base;
+    ta.done = static_cast<unsigned int*>(ctrs);
+    ta.red_done = ta.done + 64;
+    ta.epoch = ta.done + 128;
+    ta.arrive = ta.done + 129;
+    ta.status = p.status;
+    ta.wait_limit_ns = p.wait_limit_ns;
+    CUtensorMap tmP, tmQ;
+    if (make_tmap_2d_bf16(&tmP, A, M, K, lda, BM, BK)) return -1;
+    if (make_tmap_2d_bf16(&tmQ, B, N, K, ldb, bn, BK)) return -1;
+    const int rc = launch_persistent_fused<256, 4>(tmP, tmQ, p, tiles_p, tiles_q, ta, stream);
+    return rc < 0 ? rc : groups;
 }
 
 // Grouped GEMM for mixture-of-experts layers (decode layout): rows of A are token copies sorted by expert in

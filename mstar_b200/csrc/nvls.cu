@@ -31,19 +31,6 @@
 
 namespace mstar {
 
-__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4 v) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
-    }
-}
-__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
-    return make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
-}
-
 // Sum of 8 bf16 values at byte offset `off` of every rank's heap: one switch-side load-reduce, or W plain loads
 // (own heap local, peers over NVLink) added in rank order.
 __device__ __forceinline__ void load_sum8(const PeerTable& t, const McastTable& mc, long long off, float (&acc)[8]) {
@@ -238,39 +225,6 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
 // multicast-stores the sum over the same addresses of every rank, one more flag round, and every rank holds the sum
 // where its partial was. Per GPU n/W bytes cross NVLink in each direction for the loads and again for the stores;
 // HBM sees one read and one write of the tensor. Eight 16-byte requests are in flight per thread.
-// Sum vectors v, v + blockDim, ... of [.., b) over the ranks' regions and store the sum to every rank; UP vectors per
-// thread and trip, all of their WW loads in flight together. Returns the first vector left for the tail loop.
-template <int WW, int UP>
-__device__ __forceinline__ long long p2p_share(const PeerTable& t, long long off, long long v, long long b) {
-    const int W = t.world;
-    for (; v + (long long)(UP - 1) * blockDim.x < b; v += (long long)UP * blockDim.x) {
-        uint4 raw[UP][WW];
-#pragma unroll
-        for (int u = 0; u < UP; ++u)
-#pragma unroll
-            for (int q = 0; q < WW; ++q)
-                if (q < W)
-                    raw[u][q] = __ldcg(reinterpret_cast<const uint4*>(
-                        reinterpret_cast<const char*>(t.buf[q]) + off + (v + (long long)u * blockDim.x) * 16));
-#pragma unroll
-        for (int u = 0; u < UP; ++u) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-            for (int q = 0; q < WW; ++q)
-                if (q < W) add_bf16x8(acc, raw[u][q]);
-            const uint4 o = pack8(acc);
-#pragma unroll
-            for (int q = 0; q < WW; ++q)
-                if (q < W)
-                    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.buf[q]) + off +
-                                              (v + (long long)u * blockDim.x) * 16) = o;
-        }
-    }
-    return v;
-}
-
 struct ARInplaceParams {
     PeerTable t;
     McastTable mc;

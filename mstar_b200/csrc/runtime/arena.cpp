@@ -179,7 +179,6 @@ MSTAR_RT_API int mstar_arena_reserve(void* h, unsigned long long bytes, int* seg
     std::lock_guard<std::mutex> lk(a->mu);
     const uint64_t guard = a->canaries ? ALIGN : 0;
     const uint64_t need = align_up(bytes ? bytes : 1) + 2 * guard;
-    if (need > a->segment_bytes) return -1;
     for (;;) {
         for (size_t i = 0; i < a->segs.size(); ++i) {
             uint64_t off;
@@ -197,7 +196,8 @@ MSTAR_RT_API int mstar_arena_reserve(void* h, unsigned long long bytes, int* seg
         if ((int)a->segs.size() >= a->max_segments) return -1;
         Segment s;
         const std::string path = "/dev/shm/" + a->base_name + ".seg" + std::to_string(a->segs.size());
-        if (!open_segment(&s, path, a->segment_bytes, true)) return -1;
+        // a block larger than the regular segment size (a decoded video) gets a segment of its own size
+        if (!open_segment(&s, path, need > a->segment_bytes ? need : a->segment_bytes, true)) return -1;
         if (a->pin_budget > a->pinned_bytes) {          // a grown arena keeps its segments page-locked while the
             uint64_t left = a->pin_budget - a->pinned_bytes;     // budget lasts; later segments stay pageable
             if (pin_segment(s, &left)) a->pinned_bytes = a->pin_budget - left;

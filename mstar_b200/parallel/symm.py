@@ -32,6 +32,7 @@ CH_NVLS_AR = 1024         # [1024, 1280): NVLS all-reduce CTAs (two rounds of up
 CH_RRN = 1280             # [1280, 2305): reduce + residual + norm consumers (1 + up to 1024 blocks of the two-shot form)
 CH_AG = 2432              # [2432, 2560): column all-gather CTAs
 CH_AR_INPLACE = 2560      # [2560, 2816): in-place all-reduce CTAs (two rounds of up to 128)
+CH_GEMM_TILES = 2816      # [2816, 2944): row groups of the GEMM with the all-reduce inside (two rounds of up to 64)
 # local state words (pairs of [epoch, arrive]) by user
 ST_AR, ST_BARRIER, ST_A2A, ST_CFG, ST_GEMM_AR, ST_NVLS_AR, ST_RRN, ST_AG, ST_AR_INPLACE = range(9)
 
@@ -264,6 +265,31 @@ class SymmetricHeap:
         if rc < 0:
             _lib.check(rc, "mstar_allreduce_inplace")
         _lib._counters.bump()
+
+    def linear_all_reduce_tiles(self, x: torch.Tensor, w: torch.Tensor, region: SymmRegion, off: int,
+                                bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                                n_comm: int = 0, group_p: int = 0) -> torch.Tensor:
+        """Row-parallel projection at large M with the all-reduce inside the GEMM kernel: ``sum_ranks x_r @ w_r.T``
+        (+ bias, + residual: pass them on one rank only) lands, summed, at byte offset ``off`` of ``region`` on every
+        rank; the returned tensor is that view. Communication CTAs of the same launch reduce finished row groups
+        over peer memory while the remaining tiles are still being multiplied."""
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+        M, K = x.shape
+        N = w.shape[0]
+        if not hasattr(self, "_tile_ctrs"):
+            self._tile_ctrs = torch.zeros(160, dtype=torch.int32, device=self.device)
+        _, mc_flags = self._mc(region)
+        rc = _lib.kernels().mstar_gemm_bf16_allreduce_tiles(
+            ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), int(M), int(N), int(K), int(x.stride(0)),
+            int(w.stride(0)), ctypes.c_void_p(_lib.ptr(bias) if bias is not None else 0),
+            ctypes.c_void_p(_lib.ptr(residual) if residual is not None else 0),
+            int(residual.stride(0)) if residual is not None else 0, region.table, self._flags, self.world, self.rank,
+            mc_flags, ctypes.c_longlong(off), ctypes.c_void_p(self._tile_ctrs.data_ptr()), CH_GEMM_TILES, int(n_comm),
+            int(group_p), ctypes.c_void_p(_lib.stream_ptr()))
+        if rc < 0:
+            _lib.check(rc, "mstar_gemm_bf16_allreduce_tiles")
+        _lib._counters.bump()
+        return region.view(off, (M, N), torch.bfloat16)
 
     def row_share(self, M: int) -> tuple[int, int]:
         """Rows [a, b) of an M-row activation that this rank owns in the two-shot (row-cut) forms."""

@@ -84,6 +84,29 @@ def main():
             check(f"in-place allreduce mc={bool(reg.mc_ptr)} n={n} it={it} err={err:.3g}",
                   err < 0.05 * max(1.0, ref.abs().max().item()) and same)
 
+    # ---- row-parallel GEMM with the all-reduce inside the kernel (communication CTAs reduce finished row groups) ----
+    from mstar_b200.ops import gemm as gemm_tiles
+    for (M, N, K, n_comm, gp) in [(300, 256, 64, 2, 1), (1000, 512, 192, 4, 2), (4096 + 77, 1024, 512, 0, 0)]:
+        regt = heap.new_region(M * N * 2 + 4096)
+        offt = regt.alloc(M * N * 2)
+        for it in range(3):
+            gen = torch.Generator().manual_seed(900 * it + M)
+            xs = [(torch.randn(M, K, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(W)]
+            ws = [(torch.randn(N, K, generator=gen) * 0.1).to(torch.bfloat16) for _ in range(W)]
+            bias = torch.randn(N, generator=gen).to(torch.bfloat16)
+            res = torch.randn(M, N, generator=gen).to(torch.bfloat16)
+            y = heap.linear_all_reduce_tiles(xs[R].to(dev), ws[R].to(dev), regt, offt,
+                                             bias=bias.to(dev) if R == 0 else None,
+                                             residual=res.to(dev) if R == 0 else None, n_comm=n_comm, group_p=gp)
+            ref = sum(a.float() @ b.float().t() for a, b in zip(xs, ws)) + bias.float() + res.float()
+            err = (y.float().cpu() - ref).abs().max().item()
+            gathered = [torch.empty_like(y) for _ in range(W)]
+            dist.all_gather(gathered, y.clone())
+            same = all(torch.equal(gathered[0], t) for t in gathered)
+            check(f"gemm + tile all-reduce M={M} N={N} K={K} comm={n_comm} it={it} err={err:.3g}",
+                  err < 0.02 * max(1.0, ref.abs().max().item()) and same)
+        del regt
+
     # ---- row-parallel GEMM partials reduced by the consumer norm kernel, column all-gather, embedding gather ----
     from mstar_b200.ops import gemm as gemm_ops
     from mstar_b200.ops import norm as norm_ops

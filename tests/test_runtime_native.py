@@ -114,6 +114,23 @@ def test_arena_alloc_free_coalesce_and_growth():
         ar.close()
 
 
+def test_arena_block_larger_than_a_segment_gets_its_own_segment():
+    name = _prefix()
+    ar = ShmArena(name, segment_bytes=1 << 20, max_segments=3)
+    r = ShmArenaReader()
+    try:
+        big = torch.arange(3 << 18, dtype=torch.float32)          # 3 MB against 1 MB segments
+        seg, off = ar.write("big", big)
+        assert seg == 1
+        v = r.view(name, seg, off, big.numel() * 4, torch.float32, big.shape)
+        assert torch.equal(v, big)
+        ar.write("small", torch.zeros(1000))                      # regular blocks still go to the regular segments
+        assert ar.free("big")
+    finally:
+        r.close()
+        ar.close()
+
+
 def _child_reader(name, seg, off, nbytes, q):
     r = ShmArenaReader()
     v = r.view(name, seg, off, nbytes, torch.float32, (nbytes // 4,))
