@@ -134,7 +134,7 @@ def main():
     # slower direction carries (W - 1) / W of the message once
     nvls_link_us = (W - 1) / W * xb.numel() * 2 / (LINK_GBS * 1e3)
     # the same message already resident in a symmetric region (where a row-parallel GEMM writes it): in-place
-    big = heap.new_region(xb.numel() * 2 + 4096)
+    big = heap.new_region(2 * xb.numel() * 2 + (1 << 20))        # the tensor, and staging room for the fused GEMM
     boff = big.alloc(xb.numel() * 2)
     big.view(boff, xb.shape, torch.bfloat16).zero_()
     t_inpl = timed(lambda i: heap.all_reduce_inplace(big, boff, xb.numel()), args.iters, args.warmup, dev)

@@ -785,75 +785,209 @@ struct TileAR {
     PeerTable t;                 // region bases and flag bases of the group
     McastTable mc;               // only the flag multicast is used
     long long off;               // byte offset of C inside the region (C is [M, N] bf16, leading dimension N)
+    long long stage_off;         // byte offset of the staging area: [W - 1 sources][groups][share] vectors of 16 bytes
     int n_comm;                  // communication CTAs (the last CTAs of the grid)
     int group_p;                 // row tiles per group
     int channel_base;            // flag channels [base, base + 2 * groups)
     unsigned int* done;          // [groups] local: output tiles stored, per group
-    unsigned int* red_done;      // [groups] local: communication CTAs finished with the group
+    unsigned int* push_done;     // [groups] local: communication CTAs that have pushed their slice of the group
+    unsigned int* red_done;      // [groups] local: communication CTAs that have reduced their slice of the group
     unsigned int* epoch;         // local: completed calls
     unsigned int* arrive;        // local: communication CTAs finished
     KernelStatus* status;
     unsigned long long wait_limit_ns;
 };
 
+// Geometry of one row group: vectors [v0, v1) of C, cut into W shares of `share` vectors (rank q owns share q).
+struct TileARGroup { long long v0, v1, share; };
+__device__ __forceinline__ TileARGroup tile_ar_group(const TileAR& ta, int g, int M, int N, int tiles_p) {
+    const int tp0 = g * ta.group_p;
+    const int gp = min(ta.group_p, tiles_p - tp0);
+    const long long r0 = (long long)tp0 * BM;
+    long long r1 = r0 + (long long)gp * BM;
+    if (r1 > M) r1 = M;
+    TileARGroup G;
+    G.v0 = r0 * N / 8;
+    G.v1 = r1 * N / 8;
+    G.share = (G.v1 - G.v0 + ta.t.world - 1) / ta.t.world;
+    return G;
+}
+
+// Untiled bulk copies (the TMA engine, no tensor map, never multicast): global -> shared with an mbarrier, and
+// shared -> global (local or peer memory) in bulk groups. One thread keeps hundreds of KB in flight, which plain
+// stores from the 192 threads of a CTA cannot (measured: about 6 GB/s of peer stores per communication CTA).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+constexpr int TAR_CHUNK = 8192;          // bytes per bulk copy
+constexpr int TAR_MAX_STAGES = 16;
+
+//   push(g):   for every peer q, copy this rank's partial of q's share of group g into q's staging slot for this rank
+//              (local C -> shared memory -> peer memory, batches of up to 16 chunks in flight)
+//   reduce(g): this rank's share of group g: the local partial and the W - 1 staged copies come into shared memory,
+//              the threads add them in rank order (fp32), the sum leaves for every rank's C
+// The communication CTAs do push(g), then reduce(g - 1): the wait for the peers' pushes of a group is covered by the
+// push of the next. Remote traffic is stores only: a load over NVLink holds an SM's few outstanding-request slots for
+// a round trip (measured: about 2 GB/s per SM when pulling).
 __device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, const int M, const int N,
-                                               const int tiles_p, const int tiles_q) {
+                                               const int tiles_p, const int tiles_q, uint8_t* smem, const int smem_bytes) {
     __shared__ int s_ok;
-    __shared__ unsigned int s_epoch;
-    if (threadIdx.x == 0) { s_epoch = *ta.epoch + 1; s_ok = 1; }
+    __shared__ unsigned int s_epoch, s_batch;
+    __shared__ __align__(8) uint64_t full[TAR_MAX_STAGES];
+    if (threadIdx.x == 0) {
+        s_epoch = *ta.epoch + 1;
+        s_ok = 1;
+        for (int i = 0; i < TAR_MAX_STAGES; ++i) mbar_init(&full[i], 1);
+        mbar_fence_init();
+    }
     __syncthreads();
     const unsigned int epoch = s_epoch;
     const int W = ta.t.world, R = ta.t.rank;
     const int groups = (tiles_p + ta.group_p - 1) / ta.group_p;
-    for (int g = 0; g < groups && s_ok; ++g) {
-        const int tp0 = g * ta.group_p;
-        const int gp = min(ta.group_p, tiles_p - tp0);
-        if (threadIdx.x == 0) {
-            if (!wait_flag(ta.done + g, (unsigned int)(gp * tiles_q), ta.wait_limit_ns)) {
+    const long long share_full = tile_ar_group(ta, 0, M, N, tiles_p).share;      // upper bound of every group's share
+    char* const local = static_cast<char*>(ta.t.buf[R]);
+    constexpr int CV = TAR_CHUNK / 16;                                           // vectors per chunk
+    const int push_stages = min(TAR_MAX_STAGES, smem_bytes / TAR_CHUNK);
+    const int red_stages = min(TAR_MAX_STAGES, smem_bytes / ((W + 1) * TAR_CHUNK));
+    unsigned int batch = 0;              // batches run so far: every stage barrier completes one phase per batch
+    for (int g = 0; g <= groups && s_ok; ++g) {
+        if (g < groups) {
+            // ---- push(g) ----
+            const int gp = min(ta.group_p, tiles_p - g * ta.group_p);
+            if (threadIdx.x == 0 &&
+                !wait_flag(ta.done + g, (unsigned int)(gp * tiles_q), ta.wait_limit_ns)) {
                 report_status(ta.status, KID_GEMM_AR, 0x41, g, c);
                 s_ok = 0;
-            } else {
-                if (c == 0) { __threadfence_system(); signal_all(ta.t, ta.mc, ta.channel_base + g, epoch); }
-                if (!wait_all(ta.t, ta.channel_base + g, epoch, ta.status, ta.wait_limit_ns, 0x42)) s_ok = 0;
             }
-        }
-        __syncthreads();
-        if (!s_ok) break;
-        // vectors (8 bf16) of the group's rows; this rank's share of them; this CTA's slice of the share
-        const long long r0 = (long long)tp0 * BM;
-        long long r1 = r0 + (long long)gp * BM;
-        if (r1 > M) r1 = M;
-        const long long v0 = r0 * N / 8, v1 = r1 * N / 8;
-        const long long share = (v1 - v0 + W - 1) / W;
-        const long long a = v0 + (long long)R * share;
-        long long b = a + share;
-        if (b > v1) b = v1;
-        const long long per = (b > a ? (b - a + ta.n_comm - 1) / ta.n_comm : 0);
-        const long long ca = a + (long long)c * per;
-        long long cb = ca + per;
-        if (cb > b) cb = b;
-        long long v = ca + threadIdx.x;
-        if (W == 2) v = p2p_share<2, 16>(ta.t, ta.off, v, cb);
-        else if (W <= 4) v = p2p_share<4, 8>(ta.t, ta.off, v, cb);
-        else v = p2p_share<MAX_RANKS, 4>(ta.t, ta.off, v, cb);
-        for (; v < cb; v += blockDim.x) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            for (int q = 0; q < W; ++q)
-                add_bf16x8(acc, __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(ta.t.buf[q]) + ta.off + v * 16)));
-            const uint4 o = pack8(acc);
-            for (int q = 0; q < W; ++q)
-                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(ta.t.buf[q]) + ta.off + v * 16) = o;
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned int old = atomicAdd(ta.red_done + g, 1u);
-            if (old == (unsigned int)ta.n_comm - 1u) {          // the group's share is summed and stored everywhere
+            __syncthreads();
+            if (!s_ok) break;
+            if (threadIdx.x == 0) {
+                fence_proxy_async_all();         // the epilogues' stores, seen through the counter, before bulk reads
+                const TileARGroup G = tile_ar_group(ta, g, M, N, tiles_p);
+                for (int q = 0; q < W && s_ok; ++q) {
+                    if (q == R) continue;
+                    const long long a = min(G.v1, G.v0 + (long long)q * G.share), b = min(G.v1, a + G.share);
+                    const long long per = (b > a ? (b - a + ta.n_comm - 1) / ta.n_comm : 0);
+                    const long long ca = a + (long long)c * per, cb = min(b, ca + per);
+                    const int slot = R < q ? R : R - 1;
+                    const uint4* src = reinterpret_cast<const uint4*>(local + ta.off);
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(ta.t.buf[q]) + ta.stage_off) +
+                                 ((long long)slot * groups + g) * share_full - a;
+                    for (long long v = ca; v < cb && s_ok; v += (long long)push_stages * CV, ++batch) {
+                        for (int st = 0; st < push_stages; ++st) {
+                            const long long vs = v + (long long)st * CV;
+                            const long long n = vs < cb ? min((long long)CV, cb - vs) : 0;
+                            mbar_expect_tx(&full[st], (uint32_t)(n * 16));
+                            if (n > 0) bulk_load(smem + st * TAR_CHUNK, src + vs, (uint32_t)(n * 16), &full[st]);
+                        }
+                        for (int st = 0; st < push_stages; ++st) {
+                            const long long vs = v + (long long)st * CV;
+                            const long long n = vs < cb ? min((long long)CV, cb - vs) : 0;
+                            if (!mbar_wait(&full[st], batch & 1u, ta.wait_limit_ns)) {
+                                report_status(ta.status, KID_GEMM_AR, 0x44, g, st);
+                                s_ok = 0;
+                                break;
+                            }
+                            if (n > 0) bulk_store(dst + vs, smem + st * TAR_CHUNK, (uint32_t)(n * 16));
+                        }
+                        tma_store_commit();
+                        bulk_wait_read_all();        // the stages may be refilled
+                        for (int st = push_stages; st < TAR_MAX_STAGES; ++st) mbar_expect_tx(&full[st], 0);
+                    }
+                }
+                tma_store_wait_all();                // this CTA's pushes of the group have been written
+                fence_proxy_async_all();
                 __threadfence_system();
-                signal_all(ta.t, ta.mc, ta.channel_base + groups + g, epoch);
+                const unsigned int old = atomicAdd(ta.push_done + g, 1u);
+                if (old == (unsigned int)ta.n_comm - 1u) {      // every slice of this rank's pushes of group g is out
+                    __threadfence_system();
+                    signal_all(ta.t, ta.mc, ta.channel_base + g, epoch);
+                }
+                s_batch = batch;
             }
+            __syncthreads();
+            batch = s_batch;                     // only thread 0 ran the push batches
+        }
+        if (g >= 1 && s_ok) {
+            // ---- reduce(g - 1) ----
+            const int h = g - 1;
+            if (threadIdx.x == 0) {
+                if (!wait_all(ta.t, ta.channel_base + h, epoch, ta.status, ta.wait_limit_ns, 0x42)) s_ok = 0;
+                fence_proxy_async_all();         // the peers' pushes, seen through their flags, before bulk reads
+            }
+            __syncthreads();
+            if (!s_ok) break;
+            const TileARGroup G = tile_ar_group(ta, h, M, N, tiles_p);
+            const long long a = min(G.v1, G.v0 + (long long)R * G.share), b = min(G.v1, a + G.share);
+            const long long per = (b > a ? (b - a + ta.n_comm - 1) / ta.n_comm : 0);
+            const long long ca = a + (long long)c * per, cb = min(b, ca + per);
+            const uint4* mine = reinterpret_cast<const uint4*>(local + ta.off);
+            const uint4* staged = reinterpret_cast<const uint4*>(local + ta.stage_off) + (long long)h * share_full - a;
+            const long long slot_stride = (long long)groups * share_full;
+            const int stage_bytes = (W + 1) * TAR_CHUNK;        // W inputs in rank order, then the sum
+            for (long long v = ca; v < cb && s_ok; v += (long long)red_stages * CV, ++batch) {
+                if (threadIdx.x == 0) {
+                    for (int st = 0; st < TAR_MAX_STAGES; ++st) {
+                        const long long vs = v + (long long)st * CV;
+                        const long long n = (st < red_stages && vs < cb) ? min((long long)CV, cb - vs) : 0;
+                        mbar_expect_tx(&full[st], (uint32_t)(n * 16 * W));
+                        if (n == 0) continue;
+                        for (int q = 0; q < W; ++q) {
+                            const uint4* srcq = q == R ? mine + vs : staged + (long long)(q < R ? q : q - 1) * slot_stride + vs;
+                            bulk_load(smem + st * stage_bytes + q * TAR_CHUNK, srcq, (uint32_t)(n * 16), &full[st]);
+                        }
+                    }
+                }
+                for (int st = 0; st < red_stages; ++st) {
+                    const long long vs = v + (long long)st * CV;
+                    const long long n = vs < cb ? min((long long)CV, cb - vs) : 0;
+                    if (n == 0) break;                   // uniform: every thread sees the same bounds
+                    const bool landed = mbar_wait(&full[st], batch & 1u, ta.wait_limit_ns);
+                    uint4* in = reinterpret_cast<uint4*>(smem + st * stage_bytes);
+                    uint4* out = in + W * CV;
+                    if (landed) {
+                        for (int i = threadIdx.x; i < (int)n; i += blockDim.x) {
+                            float acc[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                            for (int q = 0; q < W; ++q) add_bf16x8(acc, in[q * CV + i]);
+                            out[i] = pack8(acc);
+                        }
+                    } else {
+                        if (threadIdx.x == 0) report_status(ta.status, KID_GEMM_AR, 0x45, h, st);
+                        s_ok = 0;
+                    }
+                    fence_proxy_async_smem();        // the sums, written by threads, before the bulk stores read them
+                    __syncthreads();
+                    if (threadIdx.x == 0 && s_ok) {
+                        for (int q = 0; q < W; ++q)
+                            bulk_store(reinterpret_cast<uint4*>(static_cast<char*>(ta.t.buf[q]) + ta.off) + vs, out,
+                                       (uint32_t)(n * 16));
+                        tma_store_commit();
+                    }
+                }
+                if (threadIdx.x == 0) bulk_wait_read_all();
+                __syncthreads();                     // stages free, and s_ok agreed on
+            }
+            if (threadIdx.x == 0) {
+                tma_store_wait_all();
+                fence_proxy_async_all();
+                __threadfence_system();
+                const unsigned int old = atomicAdd(ta.red_done + h, 1u);
+                if (old == (unsigned int)ta.n_comm - 1u) {      // this rank's share of the group is summed everywhere
+                    __threadfence_system();
+                    signal_all(ta.t, ta.mc, ta.channel_base + groups + h, epoch);
+                }
+            }
+            __syncthreads();
         }
     }
     // the peers' shares of every group have landed here before the kernel (and with it the stream) moves on
@@ -863,10 +997,11 @@ __device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, co
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        tma_store_wait_all();
         __threadfence();
         const unsigned int old = atomicAdd(ta.arrive, 1u);
         if (old == (unsigned int)ta.n_comm - 1u) {
-            for (int g = 0; g < groups; ++g) { ta.done[g] = 0u; ta.red_done[g] = 0u; }
+            for (int g = 0; g < groups; ++g) { ta.done[g] = 0u; ta.push_done[g] = 0u; ta.red_done[g] = 0u; }
             *ta.arrive = 0u;
             __threadfence();
             *ta.epoch = epoch;
@@ -908,7 +1043,7 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmP, const __gri
     if constexpr (FUSED) {
         if ((int)blockIdx.x >= n_walk) {
             pdl_wait();
-            tile_ar_comm_role(ta, (int)blockIdx.x - n_walk, p.M, p.N, tiles_p, tiles_q);
+            tile_ar_comm_role(ta, (int)blockIdx.x - n_walk, p.M, p.N, tiles_p, tiles_q, smem, STAGES * STAGE_BYTES);
             return;
         }
     }
@@ -1642,13 +1777,14 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
 // Row-parallel projection of a tensor-parallel layer at large M with the all-reduce inside the kernel (see TileAR):
 // C = sum over ranks of A_r[M, K] * B_r[N, K]^T (+ bias, + residual: pass them on ONE rank only), bf16, written in
 // place at byte offset `off` of every rank's copy of a symmetric region (`bufs`), leading dimension N. `ctrs` is a
-// local zero-initialised array of 2 * 64 + 4 unsigned ints that belongs to this call site (group counters, epoch,
-// arrival counter). N % 8 == 0, K % 8 == 0, at most 64 row groups. Every rank of the group must make the same call.
+// local zero-initialised array of 3 * 64 + 4 unsigned ints that belongs to this call site (group counters, epoch,
+// arrival counter); [stage_off, stage_off + stage_bytes) of the region is the staging area the peers push into
+// ((W - 1) / W of C's size, rounded up per row group). N % 8 == 0, K % 8 == 0, at most 64 row groups. Every rank of the group must make the same call.
 MSTAR_API int mstar_gemm_bf16_allreduce_tiles(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
                                               const void* bias, const void* residual, int ld_res,
                                               void* const* bufs, void* const* flags, int world, int rank,
-                                              void* mc_flags, long long off, void* ctrs, int channel_base, int n_comm,
-                                              int group_p, void* stream_) {
+                                              void* mc_flags, long long off, long long stage_off, long long stage_bytes,
+                                              void* ctrs, int channel_base, int n_comm, int group_p, void* stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (M <= 0 || N <= 0) return 0;
     if (K % 8 || N % 8 || lda % 8 || ldb % 8 || off % 16)
@@ -1667,6 +1803,13 @@ MSTAR_API int mstar_gemm_bf16_allreduce_tiles(const void* A, const void* B, int 
     }
     const int groups = (tiles_p + group_p - 1) / group_p;
     if (groups > 64) return set_error("gemm+all-reduce: more than 64 row groups", cudaSuccess);
+    {
+        long long rows0 = (long long)group_p * BM;
+        if (rows0 > M) rows0 = M;
+        const long long share_full = (rows0 * N / 8 + world - 1) / world;
+        if (stage_off % 16 || (long long)(world - 1) * groups * share_full * 16 > stage_bytes)
+            return set_error("gemm+all-reduce: the staging area is too small or misaligned", cudaSuccess);
+    }
     GemmParams p;
     (void)take_prefetch_hint();
     p.M = M; p.N = N; p.K = K;
@@ -1700,13 +1843,15 @@ MSTAR_API int mstar_gemm_bf16_allreduce_tiles(const void* A, const void* B, int 
     ta.mc.data = nullptr;
     ta.mc.flags = static_cast<unsigned int*>(mc_flags);
     ta.off = off;
+    ta.stage_off = stage_off;
     ta.n_comm = n_comm;
     ta.group_p = group_p;
     ta.channel_base = channel_base;
     ta.done = static_cast<unsigned int*>(ctrs);
-    ta.red_done = ta.done + 64;
-    ta.epoch = ta.done + 128;
-    ta.arrive = ta.done + 129;
+    ta.push_done = ta.done + 64;
+    ta.red_done = ta.done + 128;
+    ta.epoch = ta.done + 192;
+    ta.arrive = ta.done + 193;
     ta.status = p.status;
     ta.wait_limit_ns = p.wait_limit_ns;
     CUtensorMap tmP, tmQ;

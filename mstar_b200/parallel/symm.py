@@ -266,26 +266,42 @@ class SymmetricHeap:
             _lib.check(rc, "mstar_allreduce_inplace")
         _lib._counters.bump()
 
+    def scratch(self, nbytes: int) -> tuple[SymmRegion, int]:
+        """A symmetric scratch area of at least ``nbytes`` (region, byte offset). Collective when it has to grow:
+        every rank asks for the same sizes in the same order. A result kept there must be consumed before the next
+        call that uses the scratch (stream order is enough: a kernel that reduces into it returns only after every
+        peer has finished reading and writing this rank's copy)."""
+        reg = getattr(self, "_scratch", None)
+        if reg is None or reg.nbytes < nbytes:
+            self._scratch = reg = self.new_region(max(nbytes, 64 << 20))
+            self._scratch_off = reg.alloc(reg.nbytes - 4096)
+        return reg, self._scratch_off
+
     def linear_all_reduce_tiles(self, x: torch.Tensor, w: torch.Tensor, region: SymmRegion, off: int,
                                 bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
                                 n_comm: int = 0, group_p: int = 0) -> torch.Tensor:
         """Row-parallel projection at large M with the all-reduce inside the GEMM kernel: ``sum_ranks x_r @ w_r.T``
         (+ bias, + residual: pass them on one rank only) lands, summed, at byte offset ``off`` of ``region`` on every
         rank; the returned tensor is that view. Communication CTAs of the same launch reduce finished row groups
-        over peer memory while the remaining tiles are still being multiplied."""
+        over peer memory while the remaining tiles are still being multiplied. The region must have room for C and,
+        behind it, a staging area of about the same size (``2 * M * N * 2`` bytes from ``off`` are always enough)."""
         assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
         M, K = x.shape
         N = w.shape[0]
         if not hasattr(self, "_tile_ctrs"):
-            self._tile_ctrs = torch.zeros(160, dtype=torch.int32, device=self.device)
+            self._tile_ctrs = torch.zeros(256, dtype=torch.int32, device=self.device)
         _, mc_flags = self._mc(region)
+        c_bytes = (M * N * 2 + 255) // 256 * 256
+        stage_off = off + c_bytes                           # the peers' pushes land behind C
+        stage_bytes = region.nbytes - stage_off
         rc = _lib.kernels().mstar_gemm_bf16_allreduce_tiles(
             ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), int(M), int(N), int(K), int(x.stride(0)),
             int(w.stride(0)), ctypes.c_void_p(_lib.ptr(bias) if bias is not None else 0),
             ctypes.c_void_p(_lib.ptr(residual) if residual is not None else 0),
             int(residual.stride(0)) if residual is not None else 0, region.table, self._flags, self.world, self.rank,
-            mc_flags, ctypes.c_longlong(off), ctypes.c_void_p(self._tile_ctrs.data_ptr()), CH_GEMM_TILES, int(n_comm),
-            int(group_p), ctypes.c_void_p(_lib.stream_ptr()))
+            mc_flags, ctypes.c_longlong(off), ctypes.c_longlong(stage_off), ctypes.c_longlong(stage_bytes),
+            ctypes.c_void_p(self._tile_ctrs.data_ptr()), CH_GEMM_TILES, int(n_comm), int(group_p),
+            ctypes.c_void_p(_lib.stream_ptr()))
         if rc < 0:
             _lib.check(rc, "mstar_gemm_bf16_allreduce_tiles")
         _lib._counters.bump()

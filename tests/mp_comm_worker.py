@@ -87,8 +87,8 @@ def main():
     # ---- row-parallel GEMM with the all-reduce inside the kernel (communication CTAs reduce finished row groups) ----
     from mstar_b200.ops import gemm as gemm_tiles
     for (M, N, K, n_comm, gp) in [(300, 256, 64, 2, 1), (1000, 512, 192, 4, 2), (4096 + 77, 1024, 512, 0, 0)]:
-        regt = heap.new_region(M * N * 2 + 4096)
-        offt = regt.alloc(M * N * 2)
+        regt = heap.new_region(2 * M * N * 2 + (1 << 20))        # C and the staging area behind it
+        offt = regt.alloc(2 * M * N * 2 + (1 << 19))
         for it in range(3):
             gen = torch.Generator().manual_seed(900 * it + M)
             xs = [(torch.randn(M, K, generator=gen) * 0.5).to(torch.bfloat16) for _ in range(W)]
