@@ -508,7 +508,7 @@ class BagelModel(Model):
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, **kw):
         v = self.cfg.vocab_size
-        text = [b % 1000 for b in (prompt or "").encode("utf-8")]
+        text = self.encode_text(prompt if "image" in (output_modalities or []) else self.chat_text(prompt), v, 1000)
         ids, out = [], {}
         gen = "image" in (output_modalities or [])
         if tensors.get("image"):
@@ -585,5 +585,4 @@ class BagelModel(Model):
         if modality == "image":
             from ..api_server.media_io import tensor_to_png
             return tensor_to_png(output if isinstance(output, torch.Tensor) else output[-1])
-        ids = output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output)
-        return (" ".join(str(int(i)) for i in ids) + " ").encode()
+        return self.decode_text(output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output))

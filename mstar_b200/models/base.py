@@ -211,6 +211,58 @@ class Model(ABC):
     def get_output_audio_channels(self) -> int:
         return 1
 
+    # ---- text (API server) ----
+    TOKENIZER_SUBDIRS = ("", "tokenizer", "text_tokenizer")
+
+    def tokenizer(self):
+        """The checkpoint's own tokenizer when ``model_dir`` holds one (Hugging Face tokenizer files in the directory
+        or in a ``tokenizer/`` sub-directory), else None: the models then fall back to byte-level ids, which is what
+        the random-init deployments of tests and benchmarks use."""
+        if not hasattr(self, "_hf_tokenizer"):
+            self._hf_tokenizer = None
+            if self.model_dir:
+                import os
+                for sub in self.TOKENIZER_SUBDIRS:
+                    d = os.path.join(self.model_dir, sub) if sub else self.model_dir
+                    if any(os.path.exists(os.path.join(d, f)) for f in ("tokenizer.json", "tokenizer_config.json",
+                                                                        "tokenizer.model", "vocab.json")):
+                        try:
+                            from transformers import AutoTokenizer
+                            self._hf_tokenizer = AutoTokenizer.from_pretrained(d)
+                            break
+                        except Exception as e:  # noqa: BLE001
+                            import logging
+                            logging.getLogger("mstar.model").warning("tokenizer under %s not loaded: %s", d, e)
+        return self._hf_tokenizer
+
+    def encode_text(self, text: str | None, vocab_size: int, byte_modulus: int | None = None,
+                    default: str = "") -> list[int]:
+        """Token ids of ``text``: the checkpoint's tokenizer (no special tokens added: the models place their own),
+        or UTF-8 bytes folded into ``byte_modulus`` (default: the vocabulary) without one."""
+        text = text or default
+        tok = self.tokenizer()
+        if tok is not None:
+            return [int(i) for i in tok(text, add_special_tokens=False)["input_ids"]]
+        m = byte_modulus or vocab_size
+        return [b % m for b in text.encode("utf-8")]
+
+    def chat_text(self, prompt: str | None, system: str | None = None) -> str:
+        """The prompt wrapped in the checkpoint's chat template (user turn + generation prompt) when the tokenizer
+        has one; the plain prompt otherwise."""
+        tok = self.tokenizer()
+        if tok is None or not getattr(tok, "chat_template", None):
+            return prompt or ""
+        msgs = ([{"role": "system", "content": system}] if system else []) + [{"role": "user", "content": prompt or ""}]
+        return tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=True)
+
+    def decode_text(self, ids) -> bytes:
+        """Client-bound form of generated text tokens: decoded text with a tokenizer, else the ids in decimal."""
+        ids = [int(i) for i in ids]
+        tok = self.tokenizer()
+        if tok is not None:
+            return tok.decode(ids, skip_special_tokens=True).encode("utf-8")
+        return (" ".join(str(i) for i in ids) + " ").encode()
+
     # ---- media loading (API server) ----
     def load_image(self, path_or_bytes) -> torch.Tensor:
         from PIL import Image

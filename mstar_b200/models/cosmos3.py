@@ -391,7 +391,7 @@ class Cosmos3Model(Model):
     # ---- request life cycle ----
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, negative_prompt: str = "", **kw):
         v = self.cfg.vocab_size
-        enc = lambda s: torch.tensor([b % v for b in (s or "").encode("utf-8")] or [0], dtype=torch.int64)  # noqa: E731
+        enc = lambda s: torch.tensor(self.encode_text(s, v) or [0], dtype=torch.int64)  # noqa: E731
         out = {"input_ids": [enc(prompt)], "neg_input_ids": [enc(negative_prompt)]}
         if tensors and tensors.get("image"):
             out["image"] = [t.float() for t in tensors["image"]]

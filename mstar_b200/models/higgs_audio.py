@@ -104,7 +104,7 @@ class HiggsAudioModel(Model):
         return int((model_kwargs or {}).get("max_tokens", 512))
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, **kw):
-        text = list((prompt or "Transcribe the audio.").encode("utf-8"))
+        text = self.encode_text(self.chat_text(prompt or "Transcribe the audio."), self.cfg.vocab_size, 256)
         ids = [b % 1000 for b in text]
         out = {}
         if tensors.get("audio"):
@@ -131,5 +131,4 @@ class HiggsAudioModel(Model):
         return self.sm.next(md, persist_signals)
 
     def postprocess(self, output, modality, request_kwargs):
-        ids = output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output)
-        return (" ".join(str(int(i)) for i in ids) + " ").encode()
+        return self.decode_text(output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output))

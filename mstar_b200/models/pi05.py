@@ -273,7 +273,7 @@ class Pi05Model(Model):
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, state: list | None = None, **kw):
         v = self.kw["vocab"]
-        ids = [b % (v - 300) for b in (prompt or "do the task").encode("utf-8")]
+        ids = self.encode_text(prompt, v, v - 300, default="do the task")
         if state:            # robot state, discretised into 256 bins over [-1, 1], as trailing tokens
             ids += [v - 300 + int(min(255, max(0, (float(s) + 1) * 128))) for s in state]
         if not tensors.get("image"):

@@ -257,7 +257,7 @@ class Qwen3OmniModel(Model):
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, **kw):
         v = self.t_cfg.vocab_size
-        ids = [b % 1000 for b in (prompt or "").encode("utf-8")]
+        ids = self.encode_text(self.chat_text(prompt), v, 1000)
         out = {}
         if tensors.get("audio"):
             wavs = [w.float().reshape(-1) for w in tensors["audio"]]
@@ -314,5 +314,4 @@ class Qwen3OmniModel(Model):
     def postprocess(self, output, modality, request_kwargs):
         if modality == "audio":
             return float_to_pcm16(output if isinstance(output, torch.Tensor) else torch.cat(list(output)))
-        ids = output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output)
-        return (" ".join(str(int(i)) for i in ids) + " ").encode()
+        return self.decode_text(output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output))

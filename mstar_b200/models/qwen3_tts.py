@@ -153,7 +153,7 @@ class Qwen3TTSModel(Model):
         return 24000
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, **kw):
-        ids = [b % self.text_vocab for b in (prompt or " ").encode("utf-8")]
+        ids = self.encode_text(prompt, self.text_vocab, default=" ")
         return {"text_ids": [torch.tensor(ids, dtype=torch.int64)]}
 
     def get_initial_forward_pass_args(self, partition_name, input_modalities, output_modalities, input_signals,

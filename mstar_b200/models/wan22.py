@@ -174,7 +174,7 @@ class Wan22Model(Model):
     # ---- request life cycle ----
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, negative_prompt: str = "", **kw):
         v = self.text.get("vocab_size", 256384)
-        enc = lambda s: torch.tensor([b % v for b in (s or " ").encode("utf-8")] + [1], dtype=torch.int64)  # noqa: E731
+        enc = lambda s: torch.tensor(self.encode_text(s, v, default=" ") + [1], dtype=torch.int64)  # noqa: E731
         out = {"input_ids": [enc(prompt)], "neg_input_ids": [enc(negative_prompt)]}
         if tensors and tensors.get("image"):
             out["image"] = [t.float() for t in tensors["image"]]
