@@ -130,6 +130,10 @@ def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):
         torch.set_num_threads(max(1, min(16, (os.cpu_count() or 8) // n_workers)))
     except Exception:  # noqa: BLE001
         pass
+    if os.environ.get("MSTAR_CUDNN_BENCHMARK", "0") == "1":
+        # library convolutions (codecs, VAEs): let cuDNN time its algorithms on the first call of each shape, which
+        # happens in the eager warm-up run before a shape's graph is captured
+        torch.backends.cudnn.benchmark = True
     model = build_model(cfg)
     comm = make_communicator(worker_id_of(rank), "shm", prefix)
     w = build_worker(cfg, model, rank, comm, prefix=prefix, dist_init=dist_init, heartbeat_s=heartbeat_s)

@@ -305,3 +305,167 @@ def cosmos3_checkpoint_keys(m) -> dict[str, torch.Tensor]:
                     gate, up = gemm.split_gate_up(sd[pre + mpre + "gate_up_proj"])
                     out[key] = (gate if role == "gate" else up).clone()
     return out
+
+
+# ------------------------------------------------------------------ helpers for the Hugging Face encoder layouts
+def _tensors_of(src) -> dict[str, torch.Tensor]:
+    return dict(src) if isinstance(src, dict) else dict(iter_checkpoint(src))
+
+
+class _Strict:
+    """Copy checkpoint tensors into parameters and account for both sides: ``done()`` raises unless every parameter
+    was written and every checkpoint key was taken (or explicitly ignored)."""
+
+    def __init__(self, module: torch.nn.Module, tensors: dict[str, torch.Tensor], what: str):
+        self.params = dict(module.named_parameters())
+        self.tensors, self.what = tensors, what
+        self.written: set[str] = set()
+        self.taken: set[str] = set()
+        self.bad: list[str] = []
+
+    def take(self, key: str, optional: bool = False) -> torch.Tensor | None:
+        t = self.tensors.get(key)
+        if t is None:
+            if not optional:
+                self.bad.append(f"missing {key}")
+            return None
+        self.taken.add(key)
+        return t
+
+    @torch.no_grad()
+    def write(self, name: str, t: torch.Tensor | None) -> None:
+        p = self.params.get(name)
+        if t is None or p is None:
+            if p is None:
+                self.bad.append(f"no parameter {name}")
+            return
+        if tuple(p.shape) != tuple(t.shape):
+            self.bad.append(f"{name}: checkpoint {tuple(t.shape)} vs parameter {tuple(p.shape)}")
+            return
+        p.copy_(t.to(p.dtype))
+        self.written.add(name)
+
+    def done(self, ignore_keys=()) -> dict:
+        left = sorted(k for k in set(self.tensors) - self.taken if not any(k.startswith(i) or k == i for i in ignore_keys))
+        missing = sorted(set(self.params) - self.written)
+        if left or missing or self.bad:
+            raise CheckpointMismatch(f"{self.what}: {len(left)} checkpoint keys without a parameter {left[:5]}, "
+                                     f"{len(missing)} parameters not loaded {missing[:5]}, problems {self.bad[:5]}")
+        return {"loaded": len(self.written)}
+
+
+def _cat_bias(parts: list[torch.Tensor | None], like: list[torch.Tensor]) -> torch.Tensor:
+    """Fused bias of stacked projections; a projection without a bias (Whisper's key projection) contributes zeros."""
+    return torch.cat([b if b is not None else torch.zeros(w.shape[0], dtype=w.dtype) for b, w in zip(parts, like)])
+
+
+# ------------------------------------------------------------------ T5 / UMT5 encoder (Hugging Face names)
+@torch.no_grad()
+def load_t5_encoder(enc, src) -> dict:
+    """``T5Encoder`` from a Hugging Face ``T5EncoderModel`` / ``UMT5EncoderModel`` checkpoint (directory or name ->
+    tensor dict): q / k / v stacked into one projection, ``wi_0`` (gate) and ``wi_1`` (up) interleaved by rows, the
+    relative-position table of every block (UMT5) or of block 0 only (T5)."""
+    from ..ops import gemm
+    T = _tensors_of(src)
+    st = _Strict(enc, T, "T5 encoder")
+    emb = st.take("shared.weight", optional=True)
+    alt = st.take("encoder.embed_tokens.weight", optional=True)
+    st.write("embed", emb if emb is not None else alt)
+    if emb is None and alt is None:
+        st.bad.append("missing shared.weight / encoder.embed_tokens.weight")
+    L = len(enc.enc.layers)
+    tables = []
+    for i in range(L):
+        a, f = f"encoder.block.{i}.layer.0.", f"encoder.block.{i}.layer.1."
+        q, k, v = (st.take(a + f"SelfAttention.{n}.weight") for n in "qkv")
+        if None not in (q, k, v):
+            st.write(f"enc.layers.{i}.qkv_w", torch.cat([q, k, v]))
+        st.write(f"enc.layers.{i}.o_w", st.take(a + "SelfAttention.o.weight"))
+        st.write(f"enc.layers.{i}.n1_w", st.take(a + "layer_norm.weight"))
+        g, u = st.take(f + "DenseReluDense.wi_0.weight"), st.take(f + "DenseReluDense.wi_1.weight")
+        if g is not None and u is not None:
+            st.write(f"enc.layers.{i}.fc1_w", gemm.interleave_gate_up(g, u))
+        st.write(f"enc.layers.{i}.fc2_w", st.take(f + "DenseReluDense.wo.weight"))
+        st.write(f"enc.layers.{i}.n2_w", st.take(f + "layer_norm.weight"))
+        tb = st.take(a + "SelfAttention.relative_attention_bias.weight", optional=i > 0 or enc.rel_bias.shape[0] > 1)
+        if tb is not None:
+            tables.append(tb)
+    if len(tables) == enc.rel_bias.shape[0]:
+        st.write("rel_bias", torch.stack(tables))
+    else:
+        st.bad.append(f"{len(tables)} relative-position tables for {enc.rel_bias.shape[0]} expected")
+    st.write("enc.fn_w", st.take("encoder.final_layer_norm.weight"))
+    return st.done()
+
+
+# ------------------------------------------------------------------ Whisper (Hugging Face names)
+def _whisper_attn(st: _Strict, src: str, dst_w: str, dst_b: str, names=("q_proj", "k_proj", "v_proj")) -> None:
+    ws = [st.take(f"{src}{n}.weight") for n in names]
+    bs = [st.take(f"{src}{n}.bias", optional=n == "k_proj") for n in names]      # only the key projection has none
+    if None not in ws:
+        st.write(dst_w, torch.cat(ws))
+        st.write(dst_b, _cat_bias(bs, ws))
+
+
+@torch.no_grad()
+def load_whisper_encoder(enc, src, prefix: str = "model.encoder.") -> dict:
+    """``AudioEncoder`` from the encoder half of a Hugging Face Whisper checkpoint. Keys outside ``prefix`` are
+    left alone (the decoder loads them)."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(enc, T, "Whisper encoder")
+    for n in ("conv1", "conv2"):
+        st.write(f"{n}.weight", st.take(f"{n}.weight"))
+        st.write(f"{n}.bias", st.take(f"{n}.bias"))
+    pos = st.take("embed_positions.weight")
+    if pos is not None:
+        if tuple(pos.shape) != tuple(enc.pos.shape):
+            st.bad.append(f"embed_positions {tuple(pos.shape)} vs {tuple(enc.pos.shape)}")
+        else:
+            enc.pos.copy_(pos.to(enc.pos.dtype))
+    for i in range(len(enc.enc.layers)):
+        p, d = f"layers.{i}.", f"enc.layers.{i}."
+        _whisper_attn(st, p + "self_attn.", d + "qkv_w", d + "qkv_b")
+        st.write(d + "o_w", st.take(p + "self_attn.out_proj.weight"))
+        st.write(d + "o_b", st.take(p + "self_attn.out_proj.bias"))
+        for hf, ours in (("self_attn_layer_norm", "n1"), ("final_layer_norm", "n2")):
+            st.write(d + ours + "_w", st.take(p + hf + ".weight"))
+            st.write(d + ours + "_b", st.take(p + hf + ".bias"))
+        for hf, ours in (("fc1", "fc1"), ("fc2", "fc2")):
+            st.write(d + ours + "_w", st.take(p + hf + ".weight"))
+            st.write(d + ours + "_b", st.take(p + hf + ".bias"))
+    st.write("enc.fn_w", st.take("layer_norm.weight"))
+    st.write("enc.fn_b", st.take("layer_norm.bias"))
+    return st.done()
+
+
+@torch.no_grad()
+def load_whisper_decoder(dec, src, prefix: str = "model.decoder.") -> dict:
+    """``WhisperDecoder`` from the decoder half of a Hugging Face Whisper checkpoint (the output head is the token
+    embedding, as in the checkpoint; a separate ``proj_out.weight`` is accepted when it equals it)."""
+    full = _tensors_of(src)
+    T = {k[len(prefix):]: v for k, v in full.items() if k.startswith(prefix)}
+    st = _Strict(dec, T, "Whisper decoder")
+    st.write("tok", st.take("embed_tokens.weight"))
+    st.write("pos", st.take("embed_positions.weight"))
+    for i in range(len(dec.layers)):
+        p, d = f"layers.{i}.", f"layers.{i}."
+        _whisper_attn(st, p + "self_attn.", d + "qkv_w", d + "qkv_b")
+        st.write(d + "o_w", st.take(p + "self_attn.out_proj.weight"))
+        st.write(d + "o_b", st.take(p + "self_attn.out_proj.bias"))
+        st.write(d + "cq_w", st.take(p + "encoder_attn.q_proj.weight"))
+        st.write(d + "cq_b", st.take(p + "encoder_attn.q_proj.bias"))
+        _whisper_attn(st, p + "encoder_attn.", d + "ckv_w", d + "ckv_b", names=("k_proj", "v_proj"))
+        st.write(d + "co_w", st.take(p + "encoder_attn.out_proj.weight"))
+        st.write(d + "co_b", st.take(p + "encoder_attn.out_proj.bias"))
+        for hf, ours in (("self_attn_layer_norm", "ln1"), ("encoder_attn_layer_norm", "ln2"), ("final_layer_norm", "ln3")):
+            st.write(d + ours + "_w", st.take(p + hf + ".weight"))
+            st.write(d + ours + "_b", st.take(p + hf + ".bias"))
+        for n in ("fc1", "fc2"):
+            st.write(d + n + "_w", st.take(p + n + ".weight"))
+            st.write(d + n + "_b", st.take(p + n + ".bias"))
+    st.write("lnf_w", st.take("layer_norm.weight"))
+    st.write("lnf_b", st.take("layer_norm.bias"))
+    head = full.get("proj_out.weight")
+    if head is not None and "embed_tokens.weight" in T and not torch.equal(head, T["embed_tokens.weight"]):
+        st.bad.append("proj_out.weight differs from the token embedding (untied heads are not supported)")
+    return st.done()

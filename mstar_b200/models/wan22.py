@@ -155,18 +155,27 @@ class Wan22Model(Model):
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "text_encoder":
             enc = T5Encoder(dtype=self.dtype, device=device, **self.text)
-            return TextEncoderSubmodule(self._init(enc), device, self.dit_cfg.text_len)
+            return TextEncoderSubmodule(self._init(enc, "text_encoder"), device, self.dit_cfg.text_len)
         if node_name in ("vae_encoder", "vae_decoder"):
             vae = ConvVAE(self.vae_cfg).to(device=device, dtype=self.dtype).eval()
             return (VaeEncodeSubmodule(vae, device, self.dtype) if node_name == "vae_encoder"
                     else VaeDecodeSubmodule(vae, device, self.dtype, self.vae_tile))
         if node_name == "dit":
-            return WanDiTSubmodule(self._init(AdaLNDiT(self.dit_cfg, device)), device, self.num_steps, 5.0)
+            return WanDiTSubmodule(self._init(AdaLNDiT(self.dit_cfg, device), "transformer"), device, self.num_steps, 5.0)
         raise KeyError(node_name)
 
-    def _init(self, module):
+    def _init(self, module, component: str):
+        """Random-init weights, or the published (diffusers) checkpoint: ``model_dir/transformer`` in the
+        ``WanTransformer3DModel`` layout, ``model_dir/text_encoder`` in the Hugging Face UMT5 layout. Both loads are
+        strict. A directory without those components is read as tensors saved under this library's own names."""
         if self.skip_weight_loading or self.model_dir is None:
             return module.init_random(0)
+        import os
+        sub = os.path.join(self.model_dir, component)
+        if os.path.isdir(sub):
+            from .checkpoints import load_t5_encoder, load_wan22_transformer
+            (load_wan22_transformer if component == "transformer" else load_t5_encoder)(module, sub)
+            return module
         from .loader import load_named_tensors
         load_named_tensors(module, self.model_dir)
         return module

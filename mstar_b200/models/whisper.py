@@ -215,18 +215,19 @@ class WhisperModel(Model):
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "audio_encoder":
             enc = AudioEncoder(self.enc_cfg, n_mels=self.n_mels, max_frames=self.max_audio, device=device)
-            enc = self._load(enc, "model.encoder.")
+            enc = self._load(enc, "encoder")
             return WhisperEncoderSubmodule(enc, device, self.n_mels, chunk_s=4.0 if self.small else 30.0)
         if node_name == "decoder":
-            dec = self._load(WhisperDecoder(dtype=self.dtype, device=device, **self.dec_kw), "model.decoder.")
+            dec = self._load(WhisperDecoder(dtype=self.dtype, device=device, **self.dec_kw), "decoder")
             return WhisperDecoderSubmodule(dec, device, 2 * self.max_batch, self.max_audio, len(dec.layers))
         raise KeyError(node_name)
 
-    def _load(self, module, prefix):
+    def _load(self, module, half):
+        """Random-init weights, or the Hugging Face checkpoint under ``model_dir`` (strict, original tensor names)."""
         if self.skip_weight_loading or self.model_dir is None:
             return module.init_random(0)
-        from .loader import load_named_tensors
-        load_named_tensors(module, self.model_dir, rename=lambda n: n[len(prefix):] if n.startswith(prefix) else None)
+        from .checkpoints import load_whisper_decoder, load_whisper_encoder
+        (load_whisper_encoder if half == "encoder" else load_whisper_decoder)(module, self.model_dir)
         return module
 
     def get_max_output_tokens(self, model_kwargs=None):

@@ -122,3 +122,71 @@ def test_cosmos3_loader_is_strict_and_round_trips(tmp_path):
         save_file({k: v.contiguous() for k, v in badk.items()}, str(d / "diffusion_pytorch_model.safetensors"))
         with pytest.raises(ck.CheckpointMismatch):
             ck.load_cosmos3_transformer(_tiny_cosmos3(7), str(d))
+
+
+def test_t5_encoder_matches_hugging_face_umt5_on_shared_weights():
+    """Our T5 / UMT5 encoder, loaded from a Hugging Face state dict, reproduces ``UMT5EncoderModel`` (fp32, CPU)."""
+    transformers = pytest.importorskip("transformers")
+    from mstar_b200.models.encoders import T5Encoder
+    cfg = transformers.UMT5Config(vocab_size=96, d_model=64, d_kv=16, d_ff=128, num_layers=2, num_heads=4,
+                                  relative_attention_num_buckets=32, relative_attention_max_distance=128,
+                                  feed_forward_proj="gated-gelu", dropout_rate=0.0)
+    torch.manual_seed(0)
+    hf = transformers.UMT5EncoderModel(cfg).float().eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.copy_(torch.randn_like(p) * (0.3 if p.dim() > 1 else 0.2) + (1.0 if p.dim() == 1 else 0.0))
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    ours = T5Encoder(vocab_size=96, hidden=64, layers=2, heads=4, head_dim=16, ffn=128, buckets=32, max_distance=128,
+                     per_layer_bias=True, dtype=torch.float32)
+    assert ck.load_t5_encoder(ours, sd)["loaded"] == len(dict(ours.named_parameters()))
+    ids = torch.randint(0, 96, (23,))
+    with torch.no_grad():
+        want = hf(input_ids=ids[None]).last_hidden_state[0]
+    got = ours(ids)
+    assert torch.allclose(got, want, atol=2e-4, rtol=2e-4), (got - want).abs().max()
+    bad = dict(sd)
+    bad.pop("encoder.block.1.layer.1.DenseReluDense.wi_1.weight")
+    with pytest.raises(ck.CheckpointMismatch):
+        ck.load_t5_encoder(T5Encoder(vocab_size=96, hidden=64, layers=2, heads=4, head_dim=16, ffn=128,
+                                     dtype=torch.float32), bad)
+
+
+def test_whisper_loaders_are_strict_and_the_encoder_matches_hugging_face():
+    transformers = pytest.importorskip("transformers")
+    from mstar_b200.models.encoders import AudioEncoder, EncoderConfig
+    from mstar_b200.models.whisper import WhisperDecoder
+    cfg = transformers.WhisperConfig(vocab_size=120, num_mel_bins=16, d_model=64, encoder_layers=2, decoder_layers=2,
+                                     encoder_attention_heads=4, decoder_attention_heads=4, encoder_ffn_dim=128,
+                                     decoder_ffn_dim=128, max_source_positions=40, max_target_positions=24,
+                                     dropout=0.0, attention_dropout=0.0, activation_dropout=0.0, pad_token_id=0, bos_token_id=1,
+                                     eos_token_id=2, decoder_start_token_id=1)
+    torch.manual_seed(1)
+    hf = transformers.WhisperForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "embed_positions" not in n:
+                p.copy_(torch.randn_like(p) * (0.15 if p.dim() > 1 else 0.1) + (1.0 if "layer_norm.weight" in n else 0.0))
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    ec = EncoderConfig(hidden_size=64, num_layers=2, num_heads=4, head_dim=16, ffn_dim=128, norm="layernorm", act="gelu",
+                       qkv_bias=True, eps=1e-5, dtype=torch.float32)
+    enc = AudioEncoder(ec, n_mels=16, max_frames=40)
+    assert ck.load_whisper_encoder(enc, sd)["loaded"] == len(dict(enc.named_parameters()))
+    mel = torch.randn(16, 80)                                   # 80 frames -> 40 positions
+    with torch.no_grad():
+        want = hf.model.encoder(mel[None]).last_hidden_state[0]
+    got, lens = enc([mel])
+    assert lens == [40]
+    # the MLP activation here is the tanh form of GELU (the GEMM epilogue), the checkpoint's is the erf form
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (got - want).abs().max()
+    dec = WhisperDecoder(vocab=120, hidden=64, layers=2, heads=4, ffn=128, max_pos=24, dtype=torch.float32)
+    assert ck.load_whisper_decoder(dec, sd)["loaded"] == len(dict(dec.named_parameters()))
+    assert torch.equal(dec.layers[1].ckv_w[:64], sd["model.decoder.layers.1.encoder_attn.k_proj.weight"])
+    assert torch.equal(dec.layers[0].qkv_b[64:128], torch.zeros(64))            # the key projection has no bias
+    for mutate in (lambda k: k.pop("model.decoder.layers.0.encoder_attn.v_proj.bias"),
+                   lambda k: k.update({"model.decoder.layers.0.extra.weight": torch.zeros(1)})):
+        bad = dict(sd)
+        mutate(bad)
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_whisper_decoder(WhisperDecoder(vocab=120, hidden=64, layers=2, heads=4, ffn=128, max_pos=24,
+                                                   dtype=torch.float32), bad)
