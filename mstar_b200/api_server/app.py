@@ -160,10 +160,12 @@ def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
         rid = server.submit_request(text, blobs, in_mods, out_mods, kw, request_id)
         if streaming:
             def fmt(c):
-                d = {"modality": c.modality, "data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
+                # base64 needs no JSON escaping: the line is assembled from bytes instead of serialising a 5 KB string
+                tail = b'","metadata":' + json.dumps(c.metadata).encode()
                 if c.error_status:
-                    d["error_status"] = c.error_status
-                return [(json.dumps(d) + "\n").encode()], False
+                    tail += b',"error_status":' + json.dumps(c.error_status).encode()
+                return [b'{"modality":' + json.dumps(c.modality).encode() + b',"data":"' + base64.b64encode(c.data) +
+                        tail + b"}\n"], False
             return ChunkStream(server, rid, fmt, "application/x-ndjson")
         res = _collect(rid)
         return {"request_id": rid, "outputs": {m: [{"data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
