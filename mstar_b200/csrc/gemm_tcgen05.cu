@@ -71,6 +71,16 @@ struct GemmParams {
     const void* pf_ptr = nullptr;
     unsigned long long pf_bytes = 0;
     int l2_hints = 0;
+    // RMSNorm folded into its neighbours (decode layout): a projection whose output is the new residual stream also
+    // accumulates, per token, the sum of squares of the bf16 values it stores (ss_out); the projection that consumes
+    // the stream takes it un-normalised (its weight carries the norm's gain) and multiplies every output row by
+    // rsqrt(ss_in[token] * ss_inv_h + ss_eps). ss_zero: ss_zero_n floats that this kernel clears after the previous
+    // kernel has finished (the accumulator that the NEXT producer will add into).
+    const float* ss_in = nullptr;
+    float* ss_out = nullptr;
+    float* ss_zero = nullptr;
+    int ss_zero_n = 0;
+    float ss_inv_h = 0.f, ss_eps = 0.f;
 };
 
 #define MSTAR_TRACE(i)                                                                                      \
@@ -161,6 +171,101 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int m, int 
     }
 }
 
+// copy_out_staged for a projection with a folded RMSNorm on either side (see GemmParams::ss_in / ss_out). bf16 output
+// only. Every lane of a warp runs the same number of trips (lanes beyond the last unit idle through them), because
+// the sum of squares of a token row is first added up over the 16 lanes (8 for SwiGLU) that hold the row's units
+// and only then sent to the accumulator: one atomic per token row and tile slice.
+template <bool OUT_F32>
+__device__ __noinline__ void copy_out_staged_norm(const GemmParams& pp, const float* stage, int rows, int m_base,
+                                                  int n_in_base, int tid, bool dry) {
+    struct {
+        int M, N, ldc, ld_res, epilogue;
+        float out_scale;
+        void* C;
+        const __nv_bfloat16* bias;
+        const __nv_bfloat16* residual;
+        const float* ss_in;
+        float* ss_out;
+        float inv_h, eps;
+    } p = {pp.M, pp.N, pp.ldc, pp.ld_res, pp.epilogue, pp.out_scale, pp.C, pp.bias, pp.residual, pp.ss_in, pp.ss_out,
+           pp.ss_inv_h, pp.ss_eps};
+    constexpr int EPV = 8;
+    const int ipo = p.epilogue == 1 ? 2 : 1;
+    const int row_out = BM / ipo;
+    const int units_per_row = row_out / EPV;             // 16, or 8 with SwiGLU: a power of two that divides 32
+    const int total = rows * units_per_row;
+    const int total_up = (total + 31) & ~31;
+    const int n_out_base = n_in_base / ipo;
+    const int n_limit = p.N / ipo;
+    const bool vec_ok = (p.ldc % EPV == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                        (p.residual == nullptr || (p.ld_res % 8 == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0));
+    for (int u = tid; u < total_up; u += 128) {
+        const int r = u / units_per_row, c = (u - r * units_per_row) * EPV;
+        const int m = m_base + r, n = n_out_base + c;
+        const bool live = u < total && m < p.M && n < n_limit;
+        float ssq = 0.f;
+        if (live) {
+            const float* sp = stage + r * BM + c * ipo;
+            const float sc = p.out_scale * (p.ss_in != nullptr ? rsqrtf(p.ss_in[m] * p.inv_h + p.eps) : 1.f);
+            float x[EPV];
+            if (ipo == 2) {
+                float in[2 * EPV];
+#pragma unroll
+                for (int j = 0; j < 2 * EPV; j += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(sp + j);
+                    in[j] = t.x; in[j + 1] = t.y; in[j + 2] = t.z; in[j + 3] = t.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 2 * EPV; ++j) {
+                    const int nb = n_in_base + c * 2 + j;
+                    in[j] = in[j] * sc + ((p.bias != nullptr && nb < p.N) ? __bfloat162float(p.bias[nb]) : 0.f);
+                }
+#pragma unroll
+                for (int j = 0; j < EPV; ++j) x[j] = silu_f(in[2 * j]) * in[2 * j + 1];
+            } else {
+#pragma unroll
+                for (int j = 0; j < EPV; j += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(sp + j);
+                    x[j] = t.x; x[j + 1] = t.y; x[j + 2] = t.z; x[j + 3] = t.w;
+                }
+#pragma unroll
+                for (int j = 0; j < EPV; ++j)
+                    x[j] = x[j] * sc + ((p.bias != nullptr && n + j < n_limit) ? __bfloat162float(p.bias[n + j]) : 0.f);
+                if (p.epilogue == 2) {
+#pragma unroll
+                    for (int j = 0; j < EPV; ++j) x[j] = gelu_tanh_f(x[j]);
+                }
+            }
+            if (p.residual != nullptr) {
+#pragma unroll
+                for (int j = 0; j < EPV; ++j)
+                    if (n + j < n_limit) x[j] += __bfloat162float(p.residual[(size_t)m * p.ld_res + n + j]);
+            }
+            // what is stored is what the next norm sees: square the bf16-rounded values
+            __align__(16) __nv_bfloat16 o[EPV];
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) {
+                o[j] = __float2bfloat16(x[j]);
+                const float f = __bfloat162float(o[j]);
+                if (n + j < n_limit) ssq += f * f;
+            }
+            if (!dry) {
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)m * p.ldc + n;
+                if (vec_ok && n + EPV <= n_limit) {
+                    *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(o);
+                } else {
+                    for (int j = 0; j < EPV; ++j)
+                        if (n + j < n_limit) out[j] = o[j];
+                }
+            }
+        }
+        if (p.ss_out != nullptr) {
+            for (int d = units_per_row >> 1; d > 0; d >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, d);
+            if (live && !dry && (tid & (units_per_row - 1)) == 0) atomicAdd(p.ss_out + m, ssq);
+        }
+    }
+}
+
 // Swapped layout epilogue. Accumulators are first dumped raw into a shared-memory tile [token][weight row] (fp32;
 // a few dozen instructions, so that the once-per-CTA epilogue does not pay instruction-cache misses for 32
 // unrolled copies of the activation code), then one compact loop applies scale / bias / activation / residual
@@ -183,6 +288,10 @@ __device__ __noinline__ void copy_out_staged(const GemmParams& pp, const float* 
         const float* row_scale;
         void* const* row_dst;
     } p = {pp.M, pp.N, pp.ldc, pp.ld_res, pp.epilogue, pp.out_scale, pp.C, pp.bias, pp.residual, pp.row_scale, pp.row_dst};
+    if (pp.ss_in != nullptr || pp.ss_out != nullptr) {
+        copy_out_staged_norm<OUT_F32>(pp, stage, rows, m_base, n_in_base, tid, dry);
+        return;
+    }
     constexpr int EPV = OUT_F32 ? 4 : 8;                 // outputs per 16-byte store
     const int ipo = p.epilogue == 1 ? 2 : 1;             // accumulator columns per output (SwiGLU pairs)
     const int row_out = BM / ipo;
@@ -609,6 +718,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_c
         const int q4 = warp & 3;
         const int row = q4 * 32 + lane;  // accumulator row (TMEM lane) owned by this thread
         pdl_wait();
+        if (p.ss_zero != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            // the previous kernel is complete: nobody reads this accumulator any more, the next producer adds into it
+            for (int i = threadIdx.x - 64; i < p.ss_zero_n; i += 128) p.ss_zero[i] = 0.f;
+        }
         if (SWAP && !p.ar.enabled) {
             // instruction-cache warm-up (see copy_out_staged); reads an untouched corner of the staging area
             if (p.out_f32) copy_out_staged<true>(p, reinterpret_cast<const float*>(smem), 1, tile_q * BN, tile_p * BM, threadIdx.x - 64, true);
@@ -1627,6 +1740,11 @@ static int dispatch_tile(int bn, int swap, const CUtensorMap& tmP, const CUtenso
 
 using namespace mstar;
 static GemmAllReduce g_next_ar = {};
+
+// Folded-norm arguments of the NEXT mstar_gemm_bf16 call on the current device (see GemmParams::ss_in): set by
+// mstar_gemm_norm_hint, taken once. A call that cannot honour them (not the decode layout, fp32 output) fails.
+struct NormHint { const float* ss_in; float* ss_out; float* ss_zero; int ss_zero_n; float inv_h, eps; int set; };
+static NormHint g_norm_hint[kMaxDevices] = {};
 static unsigned long long* g_trace = nullptr;
 
 // Phase stamps for the benchmark: a device buffer of [CTAs][8] 64-bit words filled by later mstar_gemm_bf16 launches
@@ -1694,6 +1812,21 @@ MSTAR_API int mstar_gemm_plan(int M, int N, int K, int* swap_out, int* bn_out, i
     return 0;
 }
 
+// Fold RMSNorms into the next mstar_gemm_bf16 call on this device. ss_in: per-token sums of squares of the activation
+// rows (the call multiplies output row t by rsqrt(ss_in[t] * inv_h + eps)); ss_out: per-token accumulator that gets the
+// sum of squares of the bf16 output rows (its N tiles add into it atomically: it must be zero on entry);
+// ss_zero / ss_zero_n: floats cleared by the call once the previous kernel has finished. Any of the three may be null.
+MSTAR_API void mstar_gemm_norm_hint(const void* ss_in, void* ss_out, void* ss_zero, int ss_zero_n, float inv_h, float eps) {
+    NormHint& nh = g_norm_hint[current_device()];
+    nh.ss_in = static_cast<const float*>(ss_in);
+    nh.ss_out = static_cast<float*>(ss_out);
+    nh.ss_zero = static_cast<float*>(ss_zero);
+    nh.ss_zero_n = ss_zero != nullptr ? ss_zero_n : 0;
+    nh.inv_h = inv_h;
+    nh.eps = eps;
+    nh.set = 1;
+}
+
 // C[M,N] = A[M,K] * B[N,K]^T with optional bias[N], residual[M,N] and epilogue.
 // A, B bf16 row-major with leading dimensions lda, ldb (elements, multiples of 8); C bf16 or fp32.
 // epilogue 1 (SwiGLU): B's rows interleave (gate_j, up_j); C has N/2 columns.
@@ -1743,6 +1876,16 @@ MSTAR_API int mstar_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     p.row_dst = nullptr;
     p.ar = g_next_ar;
     g_next_ar.enabled = 0;
+    {
+        NormHint& nh = g_norm_hint[current_device()];
+        if (nh.set) {
+            nh.set = 0;
+            if (!swap || out_f32 || p.ar.enabled)
+                return set_error("gemm: a folded norm needs the decode layout (M <= 128), bf16 output and no fused all-reduce", cudaSuccess);
+            p.ss_in = nh.ss_in; p.ss_out = nh.ss_out; p.ss_zero = nh.ss_zero; p.ss_zero_n = nh.ss_zero_n;
+            p.ss_inv_h = nh.inv_h; p.ss_eps = nh.eps;
+        }
+    }
     if (p.ar.enabled) {
         if (!swap || epilogue != 0 || out_f32 || (N % 8) || ldc % 8 || (residual && ld_res % 8))
             return set_error("gemm+allreduce: needs the decode layout (M <= 128), bf16 output, no activation, N % 8 == 0", cudaSuccess);

@@ -224,6 +224,9 @@ class OrpheusModel(Model):
             else:
                 from .loader import load_decoder_from_hf
                 load_decoder_from_hf(lm, self.model_dir)
+            import os
+            if os.environ.get("MSTAR_FOLD_NORMS", "0") == "1":      # decode steps without norm kernels: no gain measured
+                lm.fold_norms()
             return DecoderSubmodule(lm, device, eos_ids=END_TOKEN_IDS, token_edge="audio_tokens")
         if node_name == "snac_decoder":
             return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small, self.codec_dtype)

@@ -49,7 +49,7 @@ class TinyLM(Model):
         return self._dtype_for(None)
 
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
-        lm = build_tiny(device=device, dtype=self._dtype_for(device), tp=tp_group)
+        lm = build_tiny(device=device, dtype=self._dtype_for(device), tp=tp_group).fold_norms()
         return DecoderSubmodule(lm, device, eos_ids=self.model_kwargs.get("eos_ids", ()))
 
     def process_prompt(self, prompt, input_modalities, output_modalities, tensors, **kw):

@@ -109,16 +109,67 @@ def gemm_plan(M: int, N: int, K: int) -> dict:
     return dict(swap=swap.value, bn=bn.value, splits=splits.value, ws_bytes=ws.value, tiles=tiles.value)
 
 
+class FoldedNorm:
+    """RMSNorms folded into one projection of a decode step (see ``mstar_gemm_norm_hint``).
+
+    ``ss_in``:  fp32 [rows] sums of squares of the activation rows: the projection's weight already carries the norm's
+                gain, the kernel multiplies output row t by ``rsqrt(ss_in[t] / hidden + eps)``.
+    ``ss_out``: fp32 [rows] accumulator that receives the sums of squares of the bf16 output rows (the new residual
+                stream); must be zero when the kernel runs.
+    ``ss_zero``: an accumulator that this kernel clears for the next producer (nobody reads it any more by then).
+    """
+
+    def __init__(self, hidden: int, eps: float, ss_in=None, ss_out=None, ss_zero=None):
+        self.hidden, self.eps, self.ss_in, self.ss_out, self.ss_zero = hidden, eps, ss_in, ss_out, ss_zero
+
+    def arm(self) -> None:
+        _lib.kernels().mstar_gemm_norm_hint(
+            ctypes.c_void_p(_lib.ptr(self.ss_in)), ctypes.c_void_p(_lib.ptr(self.ss_out)),
+            ctypes.c_void_p(_lib.ptr(self.ss_zero)), int(self.ss_zero.numel()) if self.ss_zero is not None else 0,
+            ctypes.c_float(1.0 / self.hidden), ctypes.c_float(self.eps))
+
+    def linear_ref(self, x, w, bias, residual, epilogue, out):
+        """The same arithmetic in PyTorch (CPU path and test oracle)."""
+        x2 = x.reshape(-1, x.shape[-1])
+        rows = x2.shape[0]
+        y = x2.float() @ w.float().t()
+        if self.ss_in is not None:
+            y = y * torch.rsqrt(self.ss_in[:rows].float() / self.hidden + self.eps)[:, None]
+        if bias is not None:
+            y = y + bias.float()
+        if epilogue == EPILOGUE_SWIGLU:
+            y = F.silu(y[:, 0::2]) * y[:, 1::2]
+        elif epilogue == EPILOGUE_GELU:
+            y = F.gelu(y, approximate="tanh")
+        if residual is not None:
+            y = y + residual.reshape(rows, -1).float()
+        y = y.to(x.dtype)
+        if self.ss_zero is not None:
+            self.ss_zero.zero_()
+        if self.ss_out is not None:
+            self.ss_out[:rows] += (y.float() ** 2).sum(-1)
+        if out is not None:
+            out.reshape(rows, -1).copy_(y)
+            return out
+        return y.reshape(*x.shape[:-1], y.shape[-1])
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
            residual: torch.Tensor | None = None, epilogue: int = EPILOGUE_NONE,
            out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None,
-           out_scale: float = 1.0, force_splits: int = 0) -> torch.Tensor:
-    """x: [..., K], w: [N, K] (or a ``PackedWeight``) -> [..., N] (N/2 for the SwiGLU epilogue)."""
+           out_scale: float = 1.0, force_splits: int = 0, norm: "FoldedNorm | None" = None) -> torch.Tensor:
+    """x: [..., K], w: [N, K] (or a ``PackedWeight``) -> [..., N] (N/2 for the SwiGLU epilogue).
+    ``norm``: RMSNorms folded into this projection (``FoldedNorm``; decode sizes, at most 128 rows)."""
     packed = isinstance(w, PackedWeight)
     if packed and not _lib.use_cuda(x, w.data):
         w, packed = w.unpack(), False
     if not packed and not _lib.use_cuda(x, w):
+        if norm is not None:
+            return norm.linear_ref(x, w, bias, residual, epilogue, out)
         return linear_ref(x, w, bias, residual, epilogue, out_dtype, out_scale)
+    if norm is not None:
+        assert x.numel() // x.shape[-1] <= 128 and (out_dtype in (None, torch.bfloat16)), "folded norms are a decode-size path"
+        norm.arm()
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tcgen05 GEMM takes bf16 operands"
     K = x.shape[-1]
     N = w.shape[0]

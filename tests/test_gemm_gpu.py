@@ -60,3 +60,43 @@ def test_gemm_splitk_deterministic_and_counter_reset():
     _check(y1, gemm.linear_ref(x, w), K)
     y3 = gemm.linear(x, w, force_splits=1)
     _check(y3, gemm.linear_ref(x, w), K)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,epilogue", [(64, 3072, 3072, 0), (64, 3072, 8192, 0), (64, 16384, 3072, 1),
+                                             (17, 5120, 3072, 0), (128, 1024, 512, 0)])
+def test_gemm_with_folded_norms_matches_the_pytorch_statement(M, N, K, epilogue):
+    """Decode-layout projection with RMSNorms folded in: output rows scaled by 1 / rms from the incoming sums of
+    squares, residual added in place, sums of squares of the stored bf16 rows accumulated (one atomic per row and
+    tile slice), the other accumulator cleared."""
+    from mstar_b200.ops import gemm
+    torch.manual_seed(M + N)
+    dev = "cuda"
+    x = (torch.randn(M, K, device=dev) * 2).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev).to(torch.bfloat16) if epilogue == 0 and N == 5120 else None
+    n_out = N // 2 if epilogue else N
+    ss_in = (x.float() ** 2).sum(-1).contiguous()
+    for consumer in (True, False):
+        if consumer:        # scales by 1 / rms of the activation rows; SwiGLU or plain
+            fn = gemm.FoldedNorm(K, 1e-5, ss_in=ss_in)
+            ref_fn = gemm.FoldedNorm(K, 1e-5, ss_in=ss_in.clone())
+            got = gemm.linear(x, w, bias=bias, epilogue=epilogue, norm=fn)
+            want = ref_fn.linear_ref(x, w, bias, None, epilogue, None)
+            assert got.shape == (M, n_out)
+            err = (got.float() - want.float()).abs().max().item()
+            assert err <= 0.02 * max(1.0, want.float().abs().max().item()), err
+        elif epilogue == 0:  # adds into the residual stream in place, accumulates its sums of squares, clears `other`
+            r = torch.randn(M, N, device=dev).to(torch.bfloat16)
+            r_ref = r.clone()
+            acc, other = torch.zeros(128, device=dev), torch.full((128,), 7.0, device=dev)
+            acc_ref, other_ref = acc.clone(), other.clone()
+            gemm.linear(x, w, bias=bias, residual=r, out=r, norm=gemm.FoldedNorm(N, 1e-5, ss_out=acc, ss_zero=other))
+            gemm.FoldedNorm(N, 1e-5, ss_out=acc_ref, ss_zero=other_ref).linear_ref(x, w, bias, r_ref, 0, r_ref)
+            torch.cuda.synchronize()
+            assert (r.float() - r_ref.float()).abs().max().item() <= 0.03 * max(1.0, r_ref.float().abs().max().item())
+            assert float(other.abs().sum()) == 0.0
+            # the accumulator holds the sums of squares of what was STORED
+            stored = (r.float() ** 2).sum(-1)
+            assert torch.allclose(acc[:M], stored, rtol=2e-3, atol=1e-2), (acc[:M] - stored).abs().max()
+            assert float(acc[M:].abs().sum()) == 0.0

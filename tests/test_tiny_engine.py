@@ -50,3 +50,24 @@ def test_preemption_when_pool_is_small():
         eng.add_request(f"r{i}", p, 20)
     out = eng.run_to_completion()
     assert [out[f"r{i}"] for i in range(3)] == ref
+
+
+def test_folded_norms_generate_the_same_tokens():
+    """Norm gains folded into the next projection, residual add and sum of squares in the previous one: the decode
+    path without norm kernels reproduces the oracle of the ORIGINAL weights token for token (fp32, CPU: the PyTorch
+    statement of the fused epilogues)."""
+    torch.manual_seed(0)
+    model = tiny.build_tiny()
+    for layer in model.layers:                      # non-trivial gains, so that folding them matters
+        layer.input_layernorm.data.uniform_(0.5, 1.5)
+        layer.post_attention_layernorm.data.uniform_(0.5, 1.5)
+    prompts = tiny.synthetic_prompts()
+    ref = tiny.oracle_generate(model, prompts, 24)
+    model.fold_norms()
+    assert model._norms_folded and float(model.layers[0].input_layernorm.min()) == 1.0
+    eng = _engine(model)
+    for i, p in enumerate(prompts):
+        eng.add_request(f"r{i}", p, 24)
+    out = eng.run_to_completion()
+    assert [out[f"r{i}"] for i in range(len(prompts))] == ref
+    assert float(model._ss.abs().sum()) > 0         # the folded path ran (its accumulators were used)
