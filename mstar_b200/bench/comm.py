@@ -264,6 +264,36 @@ def main():
            nccl_us=round(t_na, 2), roofline_us=round(link_us, 2), frac_of_roofline=round(link_us / t_a2a, 3),
            gbs_out_per_rank=round(mine.numel() * 2 * (W - 1) / W / t_a2a / 1e3, 1))
 
+    # ---- QK-norm + RoPE whose stores are the head scatter, against the RoPE kernel + three exchange kernels ----
+    from ..ops import rope as rope_ops
+    from ..parallel.comm import CommGroup
+    from ..parallel.sequence_parallel import UlyssesExchange
+    Hq_, Hkv_, Sx = 16, 4, (args.tokens // 2) // W * W          # one tensor-parallel shard of 32 / 8 heads, sp = W
+    try:
+        spg = CommGroup(dist.group.WORLD, list(range(W)), R)
+        spg.symm = heap
+        ex = UlyssesExchange(spg, Sx, Hq_, Hkv_, D)
+        Tl = ex.off[R + 1] - ex.off[R]
+        qkv_l = torch.randn(Tl, (Hq_ + 2 * Hkv_) * D, device=dev).to(torch.bfloat16)
+        pos_l = torch.randint(0, 4096, (3, Tl), device=dev, dtype=torch.int32)
+        inv_f = (1.0 / (10000.0 ** (torch.arange(0, D, 2, device=dev).float() / D)))
+        axis = (torch.arange(D // 2, device=dev) % 3).to(torch.int8)
+        gq = torch.ones(D, device=dev, dtype=torch.bfloat16)
+
+        def separate(i):
+            q0, k0, v0 = rope_ops.rope_kv(qkv_l, pos_l, inv_f, Hq_, Hkv_, D, axis_of_freq=axis, q_norm_w=gq, k_norm_w=gq,
+                                          norm_eps=1e-6, dense_kv=True)
+            ex.to_heads(q0, k0, v0)
+        t_sep = timed(separate, args.iters, args.warmup, dev)
+        t_fus = timed(lambda i: ex.rope_to_heads(qkv_l, pos_l, inv_f, axis, gq, gq, 1e-6), args.iters, args.warmup, dev)
+        out_bytes = Tl * (Hq_ + 2 * Hkv_) * D * 2 * (W - 1) / W
+        report(path=f"QK-norm + RoPE + Ulysses head scatter in one kernel, {Sx} tokens x ({Hq_}+2x{Hkv_}) heads x {D}",
+               ranks=W, fused_us=round(t_fus, 2), rope_then_three_exchanges_us=round(t_sep, 2),
+               roofline_us=round(out_bytes / (LINK_GBS * 1e3), 2),
+               frac_of_roofline=round(out_bytes / (LINK_GBS * 1e3) / t_fus, 3))
+    except MemoryError:
+        report(path="QK-norm + RoPE + Ulysses head scatter", skipped="symmetric heap user region too small")
+
     # ---- CFG-parallel gather fused with the guidance combine + Euler step (rank 0 combines) ----
     rws, cols = 4096, 64 * 16          # a 1024x1024 image: 4096 latent tokens x (2x2x16) channels, fp32 velocities
     v_off = heap.alloc_user(rws * cols * 4)

@@ -333,6 +333,142 @@ __global__ void __launch_bounds__(256) a2a_heads_kernel(const __grid_constant__ 
     }
 }
 
+// QK-norm + RoPE with the Ulysses head scatter as its store: the rows of this sequence-parallel rank ([T_local,
+// (Hq + 2 Hkv) * D], all heads of the tensor-parallel shard) are normalised and rotated, and every head's 256 bytes
+// go straight into the buffer of the rank that attends with that head: q head h -> rank h / (Hq / P), row
+// seq_off[R] + t of its [S_total, Hq / P, D] tensor; k and v likewise. No [T_local, H, D] intermediate and no
+// stand-alone exchange kernel. One CTA per token; a head is handled by 16 lanes with 8 consecutive elements each
+// (one 16-byte load and one 16-byte store per lane); the rotate-half partner sits 8 lanes away. Full rotary only
+// (rot_dim == D). The end of the kernel is the exchange's flag round: the last CTA tells the peers that this rank's
+// stores are out and waits (bounded) for theirs.
+struct RopeScatterParams {
+    PeerTable t;
+    const __nv_bfloat16* qkv;
+    long long ld_qkv;
+    const int* positions;            // [n_axes, pos_stride]: positions of the LOCAL tokens
+    long long pos_stride;
+    const float* inv_freq;           // [D / 2]
+    const signed char* axis_of_freq; // [D / 2] or null
+    const __nv_bfloat16* q_norm_w;   // [D] or null
+    const __nv_bfloat16* k_norm_w;
+    long long q_off, k_off, v_off;   // byte offsets of the destination tensors inside every rank's data region
+    int T, Hq, Hkv, D, interleaved;
+    float norm_eps;
+    int seq_off[MAX_RANKS + 1];
+    unsigned int* epoch;
+    unsigned int* arrive;
+    int channel;
+    KernelStatus* status;
+    unsigned long long wait_limit_ns;
+};
+
+__global__ void __launch_bounds__(256) rope_scatter_kernel(const __grid_constant__ RopeScatterParams p) {
+    __shared__ float s_cos[128], s_sin[128];
+    __shared__ unsigned int s_epoch;
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) s_epoch = *p.epoch + 1;
+    const int W = p.t.world, R = p.t.rank;
+    const int D = p.D, half = D >> 1;
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        __syncthreads();                 // the previous token's table is no longer read
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int axis = p.axis_of_freq ? p.axis_of_freq[i] : 0;
+            const float ang = (float)p.positions[(size_t)axis * p.pos_stride + t] * p.inv_freq[i];
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            s_cos[i] = cs;
+            s_sin[i] = sn;
+        }
+        __syncthreads();
+        const int lanes = D >> 3;                        // lanes per head: 16 for D = 128, 8 for D = 64
+        const int sub = threadIdx.x % lanes;             // which 8 elements of the head
+        const int slot = threadIdx.x / lanes, nslots = blockDim.x / lanes;
+        const int nheads = p.Hq + 2 * p.Hkv;
+        const __nv_bfloat16* row = p.qkv + (size_t)t * p.ld_qkv;
+        const long long drow = p.seq_off[R] + t;
+        for (int h0 = 0; h0 < nheads; h0 += nslots) {
+            const int h = h0 + slot;
+            const bool on = h < nheads;
+            const bool is_q = h < p.Hq, is_k = !is_q && h < p.Hq + p.Hkv;
+            float x[8];
+            if (on) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(row + (size_t)h * D + sub * 8);
+                const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack_bf16x2(w4[j]);
+                    x[2 * j] = f.x; x[2 * j + 1] = f.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = 0.f;
+            }
+            const bool rotate = on && (is_q || is_k);
+            const __nv_bfloat16* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+            if (p.q_norm_w != nullptr || p.k_norm_w != nullptr) {
+                // per-head RMS norm (every lane of the warp takes part in the reduction, whatever its head is); the
+                // norm's output is rounded to bf16 before the rotation, as a separate norm op would do
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+                for (int d = lanes >> 1; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+                if (rotate && nw != nullptr) {
+                    const float inv = rsqrtf(ss / D + p.norm_eps);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        x[j] = __bfloat162float(__float2bfloat16(x[j] * inv * __bfloat162float(nw[sub * 8 + j])));
+                }
+            }
+            float y[8];
+            if (p.interleaved) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = sub * 4 + j;           // pair index: elements (2i, 2i + 1)
+                    const float cs = s_cos[i], sn = s_sin[i];
+                    y[2 * j] = rotate ? x[2 * j] * cs - x[2 * j + 1] * sn : x[2 * j];
+                    y[2 * j + 1] = rotate ? x[2 * j + 1] * cs + x[2 * j] * sn : x[2 * j + 1];
+                }
+            } else {
+                // rotate-half: element i pairs with i + D / 2, held by the lane lanes / 2 away
+                const bool first = sub < (lanes >> 1);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float other = __shfl_xor_sync(0xffffffffu, x[j], lanes >> 1);
+                    const int i = (sub * 8 + j) % half;
+                    const float cs = s_cos[i], sn = s_sin[i];
+                    y[j] = !rotate ? x[j] : (first ? x[j] * cs - other * sn : x[j] * cs + other * sn);
+                }
+            }
+            if (on) {
+                const int Hn = is_q ? p.Hq : p.Hkv;      // heads of this kind on this rank (before the exchange)
+                const int hk = is_q ? h : (is_k ? h - p.Hq : h - p.Hq - p.Hkv);
+                const int Hp = Hn / W;
+                const int q = hk / Hp, hl = hk - q * Hp;
+                const long long off = is_q ? p.q_off : (is_k ? p.k_off : p.v_off);
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.t.buf[q]) + off) +
+                                     ((size_t)drow * Hp + hl) * D + sub * 8;
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                            pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int old = atomicAdd(p.arrive, 1u);
+        s_last = (old == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence_system();
+        signal_and_wait_all(p.t, p.channel, s_epoch, p.status, p.wait_limit_ns, 6);
+        *p.arrive = 0u;
+        *p.epoch = s_epoch;
+    }
+}
+
 // CFG-parallel combine: velocities of the branches live at `v_offset_bytes` in the data region of ranks
 // cond_rank / uncond_rank / img_rank (img_rank < 0: two-branch guidance). Runs on the combine rank after the
 // branch ranks have raised their flags on `channel`; reads the peers' tensors over NVLink.

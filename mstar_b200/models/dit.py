@@ -391,10 +391,16 @@ class MoTGenTower(nn.Module):
             if residual is None:
                 residual = x.clone()      # the residual stream is updated in place; keep the caller's tensor
             qkv = gemm.linear(h, L.qkv_proj, bias=L.qkv_bias)
-            q, k, v = rope_ops.rope_kv(qkv, positions, self.inv_freq, L.Hq, L.Hkv, D, axis_of_freq=self.axis_of_freq,
-                                       q_norm_w=L.q_norm, k_norm_w=L.k_norm, norm_eps=cfg.rms_eps, dense_kv=True)
-            if sp:
-                q, k, v = ex.to_heads(q, k, v)
+            if sp and ex.can_fuse_rope(qkv, 2 * self.inv_freq.numel()):
+                # QK-norm + RoPE whose stores are the Ulysses exchange: no [T, H, D] intermediate, no exchange kernels
+                q, k, v = ex.rope_to_heads(qkv, positions, self.inv_freq, self.axis_of_freq, L.q_norm, L.k_norm,
+                                           cfg.rms_eps)
+            else:
+                q, k, v = rope_ops.rope_kv(qkv, positions, self.inv_freq, L.Hq, L.Hkv, D,
+                                           axis_of_freq=self.axis_of_freq, q_norm_w=L.q_norm, k_norm_w=L.k_norm,
+                                           norm_eps=cfg.rms_eps, dense_kv=True)
+                if sp:
+                    q, k, v = ex.to_heads(q, k, v)
             if prefix_ctx is not None:
                 o_f, l_f = attn_ops.attention(q, self_plan, k=k, v=v, lse=True)
                 o_p, l_p = attn_ops.attention(q, prefix_ctx.plan, kv_cache=prefix_ctx.kv(li), lse=True)

@@ -102,6 +102,23 @@ class UlyssesExchange:
             outs.append(sp_head_slice(full, sp, 1))
         return tuple(outs)
 
+    def can_fuse_rope(self, qkv: torch.Tensor, rot_dim: int) -> bool:
+        """The fused QK-norm + RoPE + head scatter kernel applies: peer heap, bf16 on a GPU, full rotary, head width
+        64 or 128 (``MSTAR_ROPE_SCATTER=0`` keeps the separate RoPE kernel and exchange kernels)."""
+        import os
+        return (self.sp.size > 1 and self.heap is not None and qkv.is_cuda and qkv.dtype == torch.bfloat16
+                and rot_dim == self.D and self.D in (64, 128) and os.environ.get("MSTAR_ROPE_SCATTER", "1") != "0")
+
+    def rope_to_heads(self, qkv, positions, inv_freq, axis_of_freq, q_norm_w, k_norm_w, norm_eps, interleaved=False):
+        """[S_loc, (Hq + 2 Hkv) * D] projection rows -> normalised, rotated q / k / v of this rank's head group over
+        the full sequence ([S, H/P, D] x3), in ONE kernel whose stores are the exchange."""
+        P, h = self.sp.size, self.heap
+        h.rope_scatter(qkv, positions, inv_freq, axis_of_freq, q_norm_w, k_norm_w, norm_eps, self.Hq, self.Hkv, self.D,
+                       self.q_off, self.k_off, self.v_off, self.off, interleaved)
+        return (h.local_view(self.q_off, (self.S, self.Hq // P, self.D), self.dtype),
+                h.local_view(self.k_off, (self.S, self.Hkv // P, self.D), self.dtype),
+                h.local_view(self.v_off, (self.S, self.Hkv // P, self.D), self.dtype))
+
     def to_sequence(self, o):
         """[S, Hq/P, D] -> [S_loc, Hq, D]."""
         sp, P = self.sp, self.sp.size

@@ -179,6 +179,27 @@ class SymmetricHeap:
                                             ctypes.c_void_p(_lib.stream_ptr()))
         _lib.check(rc, "mstar_a2a_heads")
 
+    def rope_scatter(self, qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                     axis_of_freq: torch.Tensor | None, q_norm_w, k_norm_w, norm_eps: float, Hq: int, Hkv: int, D: int,
+                     q_off: int, k_off: int, v_off: int, seq_off: list[int], interleaved: bool = False) -> None:
+        """QK-norm + RoPE of this rank's projection rows with the Ulysses head scatter as the store: every head goes
+        straight into the q / k / v tensor (at ``q_off`` / ``k_off`` / ``v_off`` of the heap) of the rank that attends
+        with it. Returns after the peers' stores into this rank's tensors are visible to later kernels."""
+        assert qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.stride(1) == 1
+        pos = positions if positions.dim() == 2 else positions[None]
+        assert pos.dtype == torch.int32 and pos.stride(1) == 1
+        so = (ctypes.c_int * (MAX_RANKS + 1))(*(list(seq_off) + [seq_off[-1]] * (MAX_RANKS + 1 - len(seq_off))))
+        rc = _lib.kernels().mstar_rope_scatter(
+            self._bufs, self._flags, self.world, self.rank, ctypes.c_void_p(qkv.data_ptr()),
+            ctypes.c_longlong(qkv.stride(0)), ctypes.c_void_p(pos.data_ptr()), ctypes.c_longlong(pos.stride(0)),
+            ctypes.c_void_p(inv_freq.data_ptr()), ctypes.c_void_p(_lib.ptr(axis_of_freq)),
+            ctypes.c_void_p(_lib.ptr(q_norm_w)), ctypes.c_void_p(_lib.ptr(k_norm_w)), ctypes.c_longlong(q_off),
+            ctypes.c_longlong(k_off), ctypes.c_longlong(v_off), int(qkv.shape[0]), int(Hq), int(Hkv), int(D),
+            1 if interleaved else 0, ctypes.c_float(norm_eps), so, self._state_ptr(2), CH_A2A,
+            ctypes.c_void_p(_lib.stream_ptr()))
+        _lib.check(rc, "mstar_rope_scatter")
+        _lib._counters.bump()
+
     def signal(self, dst_rank: int, channel: int = CH_CFG, state_idx: int = 3, bump: bool = True) -> None:
         rc = _lib.kernels().mstar_peer_signal(self._bufs, self._flags, self.world, self.rank,
                                               self._state_ptr(state_idx), int(channel), int(dst_rank),

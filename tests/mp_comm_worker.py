@@ -258,6 +258,36 @@ def main():
     back = heap.local_view(off_b, (shards[R], H, D), torch.bfloat16)
     check("a2a backward", torch.equal(back, mine))
 
+    # ---- QK-norm + RoPE whose stores are the head scatter, against the RoPE kernel followed by the exchange ----
+    from mstar_b200.ops import rope as rope_ops
+    from mstar_b200.parallel.comm import CommGroup as _CG
+    from mstar_b200.parallel.sequence_parallel import UlyssesExchange
+    for (Hq_, Hkv_, D_, qk_norm, inter, axes) in [(8, 4, 128, True, False, 3), (4, 2, 64, False, True, 1),
+                                                  (8, 8, 128, False, False, 1)]:
+        spg = _CG(dist.group.WORLD, list(range(W)), R)
+        spg.symm = heap
+        ex = UlyssesExchange(spg, S, Hq_, Hkv_, D_)
+        gen = torch.Generator().manual_seed(13 + Hq_)
+        qkv_full = (torch.randn(S, (Hq_ + 2 * Hkv_) * D_, generator=gen) * 1.5).to(torch.bfloat16)
+        pos_full = torch.randint(0, 500, (axes, S), generator=gen, dtype=torch.int32)
+        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D_, 2).float() / D_))).to(dev)
+        axis = (torch.arange(D_ // 2) % axes).to(torch.int8).to(dev) if axes > 1 else None
+        qn = (torch.rand(D_, generator=gen) + 0.5).to(torch.bfloat16).to(dev) if qk_norm else None
+        kn = (torch.rand(D_, generator=gen) + 0.5).to(torch.bfloat16).to(dev) if qk_norm else None
+        lo, hi = ex.off[R], ex.off[R + 1]            # the exchange's own (balanced) split of the sequence
+        qkv_l = qkv_full[lo:hi].contiguous().to(dev)
+        pos_l = pos_full[:, lo:hi].contiguous().to(dev)
+        q0, k0, v0 = rope_ops.rope_kv(qkv_l, pos_l if axes > 1 else pos_l[0], inv_freq, Hq_, Hkv_, D_, axis_of_freq=axis,
+                                      q_norm_w=qn, k_norm_w=kn, norm_eps=1e-6, interleaved=inter, dense_kv=True)
+        want = [t.clone() for t in ex.to_heads(q0, k0, v0)]
+        assert ex.can_fuse_rope(qkv_l, D_)
+        got = ex.rope_to_heads(qkv_l, pos_l, inv_freq, axis, qn, kn, 1e-6, interleaved=inter)
+        torch.cuda.synchronize()
+        ok = all(torch.equal(a, b) for a, b in zip(got, want))
+        err = max((a.float() - b.float()).abs().max().item() for a, b in zip(got, want))
+        check(f"rope + head scatter Hq={Hq_} Hkv={Hkv_} D={D_} qk_norm={qk_norm} interleaved={inter} err={err:.3g}",
+              ok or err < 0.02)
+
     # ---- CFG-parallel combine: rank 0 = cond + combine, rank 1 = uncond ----
     from mstar_b200.ops.elementwise import cfg_combine_ref
     rows, cols = 256, 64
