@@ -898,7 +898,7 @@ struct TileAR {
     PeerTable t;                 // region bases and flag bases of the group
     McastTable mc;               // only the flag multicast is used
     long long off;               // byte offset of C inside the region (C is [M, N] bf16, leading dimension N)
-    long long stage_off;         // byte offset of the staging area: [W - 1 sources][groups][share] vectors of 16 bytes
+    long long stage_off;         // byte offset of the staging area: [W - 1 sources][the groups' shares, back to back] (16-byte vectors)
     int n_comm;                  // communication CTAs (the last CTAs of the grid)
     int group_p;                 // row tiles per group
     int channel_base;            // flag channels [base, base + 2 * groups)
@@ -965,7 +965,10 @@ __device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, co
     const unsigned int epoch = s_epoch;
     const int W = ta.t.world, R = ta.t.rank;
     const int groups = (tiles_p + ta.group_p - 1) / ta.group_p;
-    const long long share_full = tile_ar_group(ta, 0, M, N, tiles_p).share;      // upper bound of every group's share
+    // every group but the last has the same share; a source's slot in the staging area holds the groups' shares
+    // back to back
+    const long long share_full = tile_ar_group(ta, 0, M, N, tiles_p).share;
+    const long long slot_stride = (long long)(groups - 1) * share_full + tile_ar_group(ta, groups - 1, M, N, tiles_p).share;
     char* const local = static_cast<char*>(ta.t.buf[R]);
     constexpr int CV = TAR_CHUNK / 16;                                           // vectors per chunk
     const int push_stages = min(TAR_MAX_STAGES, smem_bytes / TAR_CHUNK);
@@ -993,7 +996,7 @@ __device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, co
                     const int slot = R < q ? R : R - 1;
                     const uint4* src = reinterpret_cast<const uint4*>(local + ta.off);
                     uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(ta.t.buf[q]) + ta.stage_off) +
-                                 ((long long)slot * groups + g) * share_full - a;
+                                 (long long)slot * slot_stride + (long long)g * share_full - a;
                     for (long long v = ca; v < cb && s_ok; v += (long long)push_stages * CV, ++batch) {
                         for (int st = 0; st < push_stages; ++st) {
                             const long long vs = v + (long long)st * CV;
@@ -1044,7 +1047,6 @@ __device__ __noinline__ void tile_ar_comm_role(const TileAR& ta, const int c, co
             const long long ca = a + (long long)c * per, cb = min(b, ca + per);
             const uint4* mine = reinterpret_cast<const uint4*>(local + ta.off);
             const uint4* staged = reinterpret_cast<const uint4*>(local + ta.stage_off) + (long long)h * share_full - a;
-            const long long slot_stride = (long long)groups * share_full;
             const int stage_bytes = (W + 1) * TAR_CHUNK;        // W inputs in rank order, then the sum
             for (long long v = ca; v < cb && s_ok; v += (long long)red_stages * CV, ++batch) {
                 if (threadIdx.x == 0) {
@@ -1950,7 +1952,9 @@ MSTAR_API int mstar_gemm_bf16_allreduce_tiles(const void* A, const void* B, int 
         long long rows0 = (long long)group_p * BM;
         if (rows0 > M) rows0 = M;
         const long long share_full = (rows0 * N / 8 + world - 1) / world;
-        if (stage_off % 16 || (long long)(world - 1) * groups * share_full * 16 > stage_bytes)
+        const long long rows_last = M - (long long)(groups - 1) * group_p * BM;
+        const long long share_last = (rows_last * N / 8 + world - 1) / world;
+        if (stage_off % 16 || (long long)(world - 1) * ((groups - 1) * share_full + share_last) * 16 > stage_bytes)
             return set_error("gemm+all-reduce: the staging area is too small or misaligned", cudaSuccess);
     }
     GemmParams p;
