@@ -84,9 +84,12 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
         tp_group.instance = sp_group.instance = inst
         if device.type == "cuda":
             from ..parallel.symm import attach_symmetric_heap
+            # the sequence-parallel group's heap holds the Ulysses exchange buffers (q / k / v of this rank's heads
+            # over the full sequence and the attention output of its rows): hundreds of MB at video sizes
+            user_mb = int(os.environ.get("MSTAR_SYMM_USER_MB", "1024" if wg.sp_size > 1 else "64"))
             for g in {id(x): x for x in (tp_group, sp_group, inst)}.values():
                 if g.size > 1 and g.symm is None:
-                    attach_symmetric_heap(g, device)
+                    attach_symmetric_heap(g, device, user_bytes=(user_mb if g is sp_group else 64) << 20)
     tensors = TensorCommunicationManager(worker_id_of(rank), device, arena_prefix=prefix)
     kv = cfg.get("kv_cache", {}) or {}
     em = EngineManager(model, device, node_names, tp_group=tp_group, sp_group=sp_group, kv_overrides=kv,
