@@ -75,6 +75,10 @@ def run_workload(workload: str, n_gpus: int = 1, *, requests: int = 1, warm_step
         desc["steps"] = steps
     out = {"bench": "serve_workloads", "workload": workload, "n_gpus": n_gpus, "unit": unit, "config": desc,
            "data": "synthetic (short text prompt, random-init weights of the published shapes)"}
+    if tp * sp > 1:
+        # seconds-long steps on a mesh: the ranks' first steps differ by more than the 2 s default of the device waits
+        import os
+        os.environ.setdefault("MSTAR_WAIT_LIMIT_MS", "60000")
     srv = APIServer(cfg, in_process=False).start(3600)
     try:
         # warm-up: the same request with a few steps (kernel attributes, graph capture of the step, allocator pools)

@@ -3,13 +3,22 @@
 #include <stdlib.h>
 #include <stdio.h>
 #include <mutex>
+#include <cstdlib>
 #include "host_common.h"
 
 namespace mstar {
 
 static char g_err[512] = "";
 static KernelStatus* g_status[kMaxDevices] = {};
-static unsigned long long g_wait_limit = MSTAR_WAIT_LIMIT_NS_DEFAULT;
+// Limit of every bounded device wait. 2 s suits decode-sized steps; deployments whose steps take seconds (video DiTs
+// on a tensor- / sequence-parallel mesh: the ranks' first steps differ by allocator growth alone) raise it with
+// MSTAR_WAIT_LIMIT_MS or mstar_set_wait_limit_ns.
+static unsigned long long initial_wait_limit() {
+    const char* e = getenv("MSTAR_WAIT_LIMIT_MS");
+    const long long ms = e != nullptr ? atoll(e) : 0;
+    return ms > 0 ? (unsigned long long)ms * 1000000ull : MSTAR_WAIT_LIMIT_NS_DEFAULT;
+}
+static unsigned long long g_wait_limit = initial_wait_limit();
 static int g_sms[kMaxDevices] = {};
 static std::mutex g_mu;
 
