@@ -471,6 +471,11 @@ class Worker:
                 st = self._streams.get(id(eng))
                 if st is None:
                     prio = 0 if hasattr(eng, "cache") else -1
+                    if self.tp_followers or self.is_tp_follower:
+                        # a tensor- / sequence-parallel instance runs in lockstep: its kernels wait (bounded) for the
+                        # peers', so on this rank nothing may hold them back. The instance's engine gets the high
+                        # priority here and the other engines of the rank (a VAE decode of seconds) the low one.
+                        prio = -1 if hasattr(eng, "cache") else 0      # the sharded model sits on the KV-cache engine
                     st = self._streams[id(eng)] = torch.cuda.Stream(device=eng.device, priority=prio)
                 for ins in batch.inputs.values():
                     for ts in ins.values():
