@@ -130,12 +130,16 @@ class BatchedCacheManager:
              causal: bool = True, window: int = 0, write_cache: bool = True,
              custom_positions: torch.Tensor | None = None, row_slots: list[int] | None = None,
              pad_to_batch: int | None = None, lookahead_tokens: int = 0, group: int = 1,
-             slot: int = 0, splits: int | None = None, pad_row_slot: int = 0) -> BatchContext:
+             slot: int = 0, splits: int | None = None, pad_row_slot: int = 0,
+             pad_to_tokens: int | None = None) -> BatchContext:
         """Reserve pages for the new tokens and write the device plan. Entries are (request, label) pairs.
         ``pad_to_batch`` pads with empty entries (one token, no keys, no cache write) up to a captured batch size;
         ``lookahead_tokens`` reserves pages for that many future decode tokens so that device-side advance can run
         ahead of the host. ``pad_row_slot`` is the sampler slot that padding rows use: it must belong to no request,
-        because the captured step samples every row and updates the slot's seen-token mask and draw counter."""
+        because the captured step samples every row and updates the slot's seen-token mask and draw counter.
+        ``pad_to_tokens`` (with ``pad_to_batch``, prefill buckets) also pads the TOKEN count: the last padding entry
+        takes the missing tokens; the tile count and the longest query length are then those of the bucket, so that
+        every plan of a bucket launches the same grids and kernel variants."""
         B = len(request_ids)
         labels = labels or ["main"] * B
         cfg = self.config
@@ -144,7 +148,13 @@ class BatchedCacheManager:
             self.alloc.alloc_batch([(r, lb, n + lookahead_tokens) for r, lb, n in zip(request_ids, labels, q_lens)])
         states = [self.alloc.get_state(r, lb) for r, lb in zip(request_ids, labels)]
         Bp = max(B, pad_to_batch or 0)
-        T = sum(q_lens) + (Bp - B)
+        pad_lens = [1] * (Bp - B)
+        if pad_to_tokens is not None:
+            missing = int(pad_to_tokens) - sum(q_lens) - len(pad_lens)
+            if not pad_lens or missing < 0:
+                raise ValueError("token padding needs a padding entry and a bucket at least as large as the batch")
+            pad_lens[-1] += missing
+        T = sum(q_lens) + sum(pad_lens)
         buf = self._slots[slot]
         if Bp > buf.max_batch or T > buf.max_tokens:
             raise ValueError(f"batch {Bp} / tokens {T} exceed the plan buffer ({buf.max_batch} / {buf.max_tokens})")
@@ -156,7 +166,7 @@ class BatchedCacheManager:
         pos, treq, cpos = sec("positions").reshape(self.n_pos_axes, -1), sec("token_req"), sec("cache_pos")
         rslot, lrows, kvi = sec("row_slot"), sec("logit_rows64").view(np.int64), sec("kv_indptr")
         pad = Bp - B
-        ql = np.asarray(list(q_lens) + [1] * pad, dtype=np.int64)
+        ql = np.asarray(list(q_lens) + pad_lens, dtype=np.int64)
         seq = np.asarray([st.seq_len for st in states], dtype=np.int64)
         poff = np.asarray([st.pos_offset for st in states], dtype=np.int64)
         qi[0] = 0
@@ -192,13 +202,17 @@ class BatchedCacheManager:
             if cp.shape[0] < self.n_pos_axes:
                 pos[cp.shape[0]:, :cp.shape[1]] = cp[0]
         buf.upload()
-        ntiles = attn_ops.count_q_tiles(list(q_lens) + [1] * (Bp - B), group)
+        if pad_to_tokens is not None:
+            tpt = max(1, 128 // group)
+            ntiles = (int(pad_to_tokens) + tpt - 1) // tpt + Bp      # upper bound over every plan of the bucket
+        else:
+            ntiles = attn_ops.count_q_tiles(list(q_lens) + pad_lens, group)
         if splits is None:
             splits = attn_ops.choose_splits(Bp, cfg.num_kv_heads, ntiles, max_kv) if max(q_lens, default=1) == 1 else 1
         plan = attn_ops.AttnPlan(q_indptr=buf.d("q_indptr"), kv_lens=buf.d("kv_lens"), batch=Bp, num_q_tokens=T,
                                  num_q_tiles=ntiles, page_indptr=buf.d("page_indptr"),
                                  page_indices=buf.d("page_indices"), splits=splits, causal=causal, window=window,
-                                 max_q_len=max(list(q_lens) + [1]))
+                                 max_q_len=int(pad_to_tokens) if pad_to_tokens is not None else max(list(q_lens) + [1]))
         ctx = BatchContext(plan=plan, positions=buf.d("positions").view(self.n_pos_axes, -1)[:, :T]
                            if self.n_pos_axes > 1 else buf.d("positions")[:T],
                            token_req=buf.d("token_req")[:T], cache_pos=buf.d("cache_pos")[:T],

@@ -26,6 +26,9 @@ from .cache_manager import BatchedCacheManager
 from .kv_store import AllocationFailedError, KVCacheConfig
 
 CAPTURE_BATCH_SIZES = [1, 2, 4, 8, 16, 32, 64]
+# prefill graphs: (batch bucket, token bucket) pairs; a packed prompt batch is padded with empty entries, the last
+# of which takes the missing tokens
+PREFILL_TOKEN_BUCKETS = [128, 256, 512, 1024, 2048]
 
 
 class KVCacheEngine(BaseEngine):
@@ -63,6 +66,9 @@ class KVCacheEngine(BaseEngine):
         self._graphs: dict[tuple, tuple] = {}
         self.launches_per_graph: dict[tuple, int] = {}     # this library's kernels recorded in each captured step
         self._static_ids = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
+        self._static_prefill_ids = torch.zeros(PREFILL_TOKEN_BUCKETS[-1], dtype=torch.int64, device=self.device)
+        self.prefill_graphs = os.environ.get("MSTAR_PREFILL_GRAPHS", "1") != "0"
+        self.prefill_graph_hits = 0
         self._static_tok = torch.zeros(max_batch, dtype=torch.int64, device=self.device)
         self.graph_hits = 0
         self.graph_misses: dict[str, int] = {}
@@ -198,7 +204,18 @@ class KVCacheEngine(BaseEngine):
             bucket = next((s for s in CAPTURE_BATCH_SIZES if s >= B and s <= self.max_batch), None)
             if bucket is None:
                 self.graph_misses["batch larger than the largest bucket"] = self.graph_misses.get("batch larger than the largest bucket", 0) + 1
-        elif self.use_graphs:
+        token_bucket = None
+        if (not decode and self.use_graphs and self.prefill_graphs and not b.speculative
+                and sub.can_use_cuda_graphs(b.graph_walk) and sub.can_graph_prefill(b.graph_walk)
+                and all(ni.custom_pos_ids is None and ni.input_ids is not None and ni.input_embeds is None
+                        for ni in prepared.node_inputs)):
+            # prefill replayed from a graph: smallest (batch, token) bucket with room for one padding entry
+            T = sum(q_lens)
+            bp = next((s_ for s_ in CAPTURE_BATCH_SIZES if s_ > B and s_ <= self.max_batch), None)
+            tb = next((t_ for t_ in PREFILL_TOKEN_BUCKETS if bp is not None and t_ >= T + (bp - B)), None)
+            if bp is not None and tb is not None:
+                bucket, token_bucket = bp, tb
+        if bucket is None and self.use_graphs:
             why = "prefill / multi-token step" if not decode else "node opted out"
             self.graph_misses[why] = self.graph_misses.get(why, 0) + 1
         custom = None
@@ -207,16 +224,22 @@ class KVCacheEngine(BaseEngine):
                                 for ni in prepared.node_inputs], dim=-1)
         splits = None
         burst = 1
-        if bucket is not None:
+        if token_bucket is not None:
+            splits = 1
+        elif bucket is not None:
             splits = attn_ops.choose_splits(bucket, self.kv_config.num_kv_heads, bucket, self.kv_config.max_seq_len,
                                             sm_count=3 * 148)
-            if self.decode_burst > 1:       # no request may run past its loop budget inside the burst
+            if self.decode_burst > 1 and token_bucket is None:       # no request may run past its loop budget inside the burst
                 burst = max(1, min([self.decode_burst] + [int(ni.kwargs.get("_loop_remaining", 1))
                                                            for ni in prepared.node_inputs]))
+        # decode buckets live in plan slot 0 (the captured decode step advances it on the device), everything else,
+        # prefill buckets included, in slot 1
         ctx = self.cache.plan(prepared.request_ids, q_lens, labels=labels, row_slots=slots, pad_to_batch=bucket,
-                              group=self.group, slot=0 if bucket is not None else 1, custom_positions=custom,
-                              splits=splits, lookahead_tokens=burst - 1, pad_row_slot=self.sampler.pad_slot)
+                              group=self.group, slot=0 if (bucket is not None and token_bucket is None) else 1,
+                              custom_positions=custom, splits=splits, lookahead_tokens=burst - 1,
+                              pad_row_slot=self.sampler.pad_slot, pad_to_tokens=token_bucket)
         prepared.ctx, prepared.bucket, prepared.q_lens, prepared.burst = ctx, bucket, q_lens, burst
+        prepared.token_bucket = token_bucket
         return prepared
 
     def _forward_logits(self, sub, walk, ei, node_inputs):
@@ -234,6 +257,10 @@ class KVCacheEngine(BaseEngine):
                                    per_request_states={r: self.states.setdefault(r, {}) for r in planned.request_ids})
         B = len(planned.request_ids)
         with torch.no_grad():
+            if getattr(planned, "token_bucket", None) is not None:
+                raw = self._replay_prefill(sub, b, ei, planned)
+                self.cache.advance_seq_lens(ctx)
+                return raw
             if planned.bucket is not None:
                 sub.preprocess(b.graph_walk, ei, planned.node_inputs)
                 key = (b.node_name, b.graph_walk, planned.bucket)
@@ -304,7 +331,37 @@ class KVCacheEngine(BaseEngine):
         self.cache.advance_seq_lens(ctx)
         return raw
 
-    def _capture(self, key, sub, walk, ei, planned):
+    def _replay_prefill(self, sub, b, ei, planned):
+        """A packed prompt batch through the graph of its (batch, token) bucket: the prompt ids go into the static id
+        buffer (padding tokens are id 0 on rows that write no K/V), the plan sits in its slot, the graph runs the
+        model and samples every entry's last row."""
+        ctx, Bp, Tb = planned.ctx, planned.bucket, planned.token_bucket
+        B = len(planned.request_ids)
+        self._last_graph_key = None
+        sub.preprocess(b.graph_walk, ei, planned.node_inputs)
+        ids = torch.cat([ni.input_ids.reshape(-1) for ni in planned.node_inputs])
+        stage = torch.zeros(Tb, dtype=torch.int64)
+        stage[:ids.numel()] = ids
+        self._static_prefill_ids[:Tb].copy_(stage.to(self.device, non_blocking=True))
+        key = (b.node_name, b.graph_walk, Bp, Tb)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._capture(key, sub, b.graph_walk, ei, planned, ids_buf=self._static_prefill_ids[:Tb],
+                                  plan_slot=1, advance=False)
+        entry[0].replay()
+        self.graph_hits += 1
+        self.prefill_graph_hits += 1
+        tokens = self._static_tok[:B].clone()
+        raw = {"tokens": tokens, "extra": {k_: v[:B].clone() if isinstance(v, torch.Tensor) else v
+                                           for k_, v in entry[1].items()}}
+        self._host_i = (self._host_i + 1) % len(self._host_ring)
+        hb = self._host_ring[self._host_i]
+        hb[0, :B].copy_(tokens, non_blocking=True)
+        raw["tokens_host"] = hb[0, :B]
+        io_counters.add_d2h(B * 8)
+        return raw
+
+    def _capture(self, key, sub, walk, ei, planned, ids_buf=None, plan_slot=0, advance=True):
         """Capture model forward + sampling for one (node, walk, bucket). Inputs: the static id buffer and the
         plan slot; outputs: the static token buffer (+ any extra tensors the node returns)."""
         Bp = planned.bucket
@@ -314,8 +371,9 @@ class KVCacheEngine(BaseEngine):
                                      max(1, ctx.plan.splits), Bp * self.kv_config.num_kv_heads)
         saved_off = self.sampler.offset.clone()
         saved_seen = None if self.sampler.seen is None else self.sampler.seen.clone()
-        saved_plan = self.cache.plan_snapshot(0)
+        saved_plan = self.cache.plan_snapshot(plan_slot)
         saved_ids = self._static_ids.clone()
+        ids_in = self._static_ids[:Bp] if ids_buf is None else ids_buf
         # device state that the node carries from step to step: the warm-up and capture runs must not advance it
         node_state = list(sub.capture_state()) if hasattr(sub, "capture_state") else []
         saved_state = [t.clone() for t in node_state]
@@ -324,12 +382,13 @@ class KVCacheEngine(BaseEngine):
             pass
 
         def body():
-            outs = sub.forward_graph(walk, ei, self._static_ids[:Bp], ctx)
+            outs = sub.forward_graph(walk, ei, ids_in, ctx)
             self.sampler.sample(outs[BATCHED_LOGITS], ctx.row_slot, out=self._static_tok[:Bp], advance=False)
             self.sampler.offset.index_add_(0, ctx.row_slot.long(), torch.ones(Bp, dtype=torch.int64, device=self.device))
-            # leave the device plan one token further and the sampled ids as the next input: a following replay
-            # (decode burst) continues without the host; a following plan() simply rewrites the plan
-            self.cache.advance_on_device(ctx, self._static_ids[:Bp], self._static_tok[:Bp])
+            if advance:
+                # leave the device plan one token further and the sampled ids as the next input: a following replay
+                # (decode burst) continues without the host; a following plan() simply rewrites the plan
+                self.cache.advance_on_device(ctx, self._static_ids[:Bp], self._static_tok[:Bp])
             return {k: v for k, v in outs.items() if k != BATCHED_LOGITS}
 
         if self.emulate_graphs:
@@ -359,7 +418,7 @@ class KVCacheEngine(BaseEngine):
         self.sampler.offset.copy_(saved_off)
         if saved_seen is not None:
             self.sampler.seen.copy_(saved_seen)
-        self.cache.plan_restore(0, saved_plan)
+        self.cache.plan_restore(plan_slot, saved_plan)
         self._static_ids.copy_(saved_ids)
         for t, sv in zip(node_state, saved_state):
             t.copy_(sv)

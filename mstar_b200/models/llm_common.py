@@ -29,6 +29,9 @@ class DecoderSubmodule(ARNodeSubmodule):
     def can_use_cuda_graphs(self, graph_walk):
         return True
 
+    def can_graph_prefill(self, graph_walk):
+        return type(self).forward_batched is DecoderSubmodule.forward_batched      # plain token prompts only
+
     def postprocess(self, request_id, request_info, outputs, inputs):
         tok = outputs["new_token"].to(torch.int64)          # device view: feeds the next step
         host = outputs.get("new_token_host")

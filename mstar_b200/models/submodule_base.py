@@ -94,6 +94,12 @@ class NodeSubmodule:
     def can_use_cuda_graphs(self, graph_walk: str) -> bool:
         return False
 
+    def can_graph_prefill(self, graph_walk: str) -> bool:
+        """Multi-token (prefill) batches of this walk may be replayed from a captured graph over (batch, token)
+        buckets: ``forward_graph`` must then work from the static id buffer alone for any packed batch (no per-request
+        tensors, no host-side row surgery)."""
+        return False
+
     def cleanup_request(self, request_id: str) -> None:
         pass
 

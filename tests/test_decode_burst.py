@@ -138,3 +138,32 @@ def test_padding_rows_do_not_disturb_a_seeded_penalised_request():
     for p in prompts:
         alone = _run_requests([p], **kw)
         assert alone[p] == together[p], p
+
+
+def test_prefill_through_bucket_graphs_gives_the_same_tokens():
+    """Packed prompt batches replayed from the graph of their (batch, token) bucket (padding entries take the missing
+    rows and tokens, write no K/V and sample into the spare sampler slot) produce the tokens of the eager prefill."""
+    kw = dict(max_tokens=12, ignore_eos=True, temperature=0.0)
+    os.environ["MSTAR_PREFILL_GRAPHS"] = "0"
+    try:
+        ref, _ = _tokens(1, True, **kw)
+    finally:
+        os.environ.pop("MSTAR_PREFILL_GRAPHS", None)
+    os.environ["MSTAR_EMULATE_GRAPHS"] = "1"
+    os.environ["MSTAR_DECODE_BURST"] = "1"
+    try:
+        cfg = {"model": "tiny", "model_kwargs": {"dtype": "float32", "max_num_pages": 256},
+               "node_groups": [{"node_names": ["LLM"], "ranks": [0]}]}
+        s = APIServer(cfg, in_process=True).start(60)
+        try:
+            rids = [s.submit_request(p, output_modalities=["text"], model_kwargs=dict(kw)) for p in ("1 2 3", "7 8 9 10 11")]
+            got = [b"".join(c.data for c in s.collect_results(r, 120)["text"]).decode().split() for r in rids]
+            eng = s.deployment.workers[0].engines.engine_for("LLM")
+            assert eng.prefill_graph_hits >= 1
+            assert any(len(k) == 4 for k in eng._graphs), list(eng._graphs)       # a (node, walk, batch, tokens) bucket
+        finally:
+            s.shutdown()
+    finally:
+        os.environ.pop("MSTAR_EMULATE_GRAPHS", None)
+        os.environ.pop("MSTAR_DECODE_BURST", None)
+    assert got == ref
