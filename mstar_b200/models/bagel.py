@@ -482,9 +482,11 @@ class BagelModel(Model):
             if self.skip_weight_loading or self.model_dir is None:
                 m.init_random(0)
             else:
-                from .loader import load_decoder_from_hf
-                load_decoder_from_hf(m.und, self.model_dir, prefix="language_model.model.",
-                                     head_name="language_model.lm_head.weight")
+                # the published checkpoint: both experts, the latent / timestep projections (strict)
+                import os
+                from .checkpoints import load_bagel_mot
+                ema = os.path.join(self.model_dir, "ema.safetensors")
+                load_bagel_mot(m, ema if os.path.exists(ema) else self.model_dir)
             branch = {"LLM": None, "LLM_cfg_text": "cfg_text", "LLM_cfg_img": "cfg_img"}[node_name]
             sub = BagelLLMSubmodule(m, device, self.vae_cfg.latent_channels, self.num_steps, 3.0, branch)
             sub.node_name = node_name
@@ -492,6 +494,8 @@ class BagelModel(Model):
         if node_name == "vit_encoder":
             enc = VisionEncoder(self.vit_cfg, patch=self.vit_patch, pos="learned", pos_grid=8 if self.small else 70,
                                 out_dim=self.cfg.hidden_size, device=device).init_random(0)
+            if not (self.skip_weight_loading or self.model_dir is None):
+                self._load_vit(enc)
             return VitSubmodule(enc, device)
         if node_name in ("vae_encoder", "vae_decoder"):
             vae = ConvVAE(self.vae_cfg).to(device=device, dtype=self.dtype).eval()
@@ -501,6 +505,27 @@ class BagelModel(Model):
         if node_name == "combine_cfg":
             return CombineCfgSubmodule(device, self.num_steps, 3.0)
         raise KeyError(node_name)
+
+    def _load_vit(self, enc) -> None:
+        """Vision tower + connector of the published checkpoint: SigLIP names under ``vit_model.``, the two-layer
+        connector under ``connector.`` (this encoder's output projector), the learned position table under
+        ``vit_pos_embed.pos_embed``."""
+        import os
+        from .checkpoints import CheckpointMismatch, iter_checkpoint, load_siglip_vision
+        ema = os.path.join(self.model_dir, "ema.safetensors")
+        tensors = {k: v for k, v in iter_checkpoint(ema if os.path.exists(ema) else self.model_dir)
+                   if k.startswith(("vit_model.", "connector.", "vit_pos_embed."))}
+        side = {"connector.fc1.weight": enc.proj1_w, "connector.fc1.bias": enc.proj1_b,
+                "connector.fc2.weight": enc.proj2_w, "connector.fc2.bias": enc.proj2_b,
+                "vit_pos_embed.pos_embed": enc.pos_table}
+        for k, p in side.items():
+            t = tensors.pop(k, None)
+            if t is None or tuple(t.shape) != tuple(p.shape):
+                raise CheckpointMismatch(f"BAGEL vision tower: {k} missing or of shape {None if t is None else tuple(t.shape)}"
+                                         f" (parameter {tuple(p.shape)})")
+            p.data.copy_(t.to(p.dtype))
+        vit = {k[len("vit_model."):]: v for k, v in tensors.items() if k.startswith("vit_model.")}
+        load_siglip_vision(enc, vit, position_table=False)
 
     # ---- request life cycle ----
     def get_max_output_tokens(self, model_kwargs=None):

@@ -345,9 +345,9 @@ class _Strict:
         p.copy_(t.to(p.dtype))
         self.written.add(name)
 
-    def done(self, ignore_keys=()) -> dict:
+    def done(self, ignore_keys=(), ignore_params=()) -> dict:
         left = sorted(k for k in set(self.tensors) - self.taken if not any(k.startswith(i) or k == i for i in ignore_keys))
-        missing = sorted(set(self.params) - self.written)
+        missing = sorted(n for n in set(self.params) - self.written if not any(n.startswith(i) for i in ignore_params))
         if left or missing or self.bad:
             raise CheckpointMismatch(f"{self.what}: {len(left)} checkpoint keys without a parameter {left[:5]}, "
                                      f"{len(missing)} parameters not loaded {missing[:5]}, problems {self.bad[:5]}")
@@ -469,3 +469,126 @@ def load_whisper_decoder(dec, src, prefix: str = "model.decoder.") -> dict:
     if head is not None and "embed_tokens.weight" in T and not torch.equal(head, T["embed_tokens.weight"]):
         st.bad.append("proj_out.weight differs from the token embedding (untied heads are not supported)")
     return st.done()
+
+
+# ------------------------------------------------------------------ SigLIP vision tower (Hugging Face names)
+@torch.no_grad()
+def load_siglip_vision(enc, src, prefix: str = "vision_model.", position_table: bool = True) -> dict:
+    """``VisionEncoder`` (learned positions, pre-LN blocks, tanh-GELU MLP) from a Hugging Face ``SiglipVisionModel``
+    checkpoint — the vision tower of BAGEL and of the PaliGemma-based policies. The Conv2d patch embedding becomes a
+    GEMM weight over flattened patches; the position table must have the encoder's ``pos_grid``² rows. The pooling
+    head of the checkpoint (``head.*``), when present, is not used by these models and is ignored; a projector
+    (``proj1`` / ``proj2``) of the encoder is not part of this layout: the caller loads it. ``position_table=False``
+    leaves the position table to the caller as well (BAGEL keeps its own NaViT table next to the tower)."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(enc, T, "SigLIP vision tower")
+    w = st.take("embeddings.patch_embedding.weight")
+    st.write("patch_w", None if w is None else w.reshape(w.shape[0], -1))
+    st.write("patch_b", st.take("embeddings.patch_embedding.bias"))
+    if position_table:
+        st.write("pos_table", st.take("embeddings.position_embedding.weight"))
+    else:
+        st.take("embeddings.position_embedding.weight", optional=True)
+    for i in range(len(enc.enc.layers)):
+        p, d = f"encoder.layers.{i}.", f"enc.layers.{i}."
+        ws = [st.take(f"{p}self_attn.{n}_proj.weight") for n in "qkv"]
+        bs = [st.take(f"{p}self_attn.{n}_proj.bias") for n in "qkv"]
+        if None not in ws and None not in bs:
+            st.write(d + "qkv_w", torch.cat(ws))
+            st.write(d + "qkv_b", torch.cat(bs))
+        st.write(d + "o_w", st.take(p + "self_attn.out_proj.weight"))
+        st.write(d + "o_b", st.take(p + "self_attn.out_proj.bias"))
+        for hf, ours in (("layer_norm1", "n1"), ("layer_norm2", "n2")):
+            st.write(d + ours + "_w", st.take(p + hf + ".weight"))
+            st.write(d + ours + "_b", st.take(p + hf + ".bias"))
+        for n in ("fc1", "fc2"):
+            st.write(d + n + "_w", st.take(f"{p}mlp.{n}.weight"))
+            st.write(d + n + "_b", st.take(f"{p}mlp.{n}.bias"))
+    st.write("enc.fn_w", st.take("post_layernorm.weight"))
+    st.write("enc.fn_b", st.take("post_layernorm.bias"))
+    return st.done(ignore_keys=("head.",), ignore_params=("proj",) + (() if position_table else ("pos_table",)))
+
+
+# ------------------------------------------------------------------ BAGEL mixture-of-transformers (original names)
+_BAGEL_SIDE = {"vae2llm.weight": "vae2llm_w", "vae2llm.bias": "vae2llm_b", "llm2vae.weight": "llm2vae_w",
+               "llm2vae.bias": "llm2vae_b", "time_embedder.mlp.0.weight": "t1_w", "time_embedder.mlp.0.bias": "t1_b",
+               "time_embedder.mlp.2.weight": "t2_w", "time_embedder.mlp.2.bias": "t2_b"}
+# fixed sine-cosine tables stored as frozen parameters (computed on the fly here) and the parts that other nodes load
+_BAGEL_IGNORE = ("latent_pos_embed.", "vit_pos_embed.", "vit_model.", "connector.")
+
+
+@torch.no_grad()
+def load_bagel_mot(m, src) -> dict:
+    """``BagelMoT`` (understanding expert ``und`` + generation expert ``gen`` + latent / timestep projections) from the
+    published BAGEL ``ema.safetensors`` names: ``language_model.model.layers.N.*`` with the generation expert's
+    copies under ``*_moe_gen``, unfused q / k / v (+ biases) and gate / up, per-head ``q_norm`` / ``k_norm``. One
+    tensor-parallel rank (the reference does not shard BAGEL either). Strict."""
+    from ..ops import gemm
+    import re
+    T = _tensors_of(src)
+    st = _Strict(m, T, "BAGEL mixture of transformers")
+    L = "language_model.model."
+    st.write("und.embed_tokens", st.take(L + "embed_tokens.weight"))
+    st.write("und.norm", st.take(L + "norm.weight"))
+    st.write("gen.final_norm", st.take(L + "norm_moe_gen.weight"))
+    if m.und.lm_head is not None:
+        st.write("und.lm_head", st.take("language_model.lm_head.weight"))
+    else:
+        st.take("language_model.lm_head.weight", optional=True)
+    for ckpt, name in _BAGEL_SIDE.items():
+        st.write(name, st.take(ckpt))
+    qk_norm = m.cfg.qk_norm
+    for i in range(m.cfg.num_layers):
+        for sfx, dst, attn, mlp in (("", f"und.layers.{i}.", "self_attn.", "mlp."), ("_moe_gen", f"gen.layers.{i}.", "", "")):
+            p = f"{L}layers.{i}."
+            ws = [st.take(f"{p}self_attn.{n}_proj{sfx}.weight") for n in "qkv"]
+            bs = [st.take(f"{p}self_attn.{n}_proj{sfx}.bias") for n in "qkv"]
+            if None not in ws and None not in bs:
+                st.write(dst + attn + "qkv_proj", torch.cat(ws))
+                st.write(dst + attn + "qkv_bias", torch.cat(bs))
+            st.write(dst + attn + "o_proj", st.take(f"{p}self_attn.o_proj{sfx}.weight"))
+            if qk_norm:
+                st.write(dst + attn + "q_norm", st.take(f"{p}self_attn.q_norm{sfx}.weight"))
+                st.write(dst + attn + "k_norm", st.take(f"{p}self_attn.k_norm{sfx}.weight"))
+            g, u = st.take(f"{p}mlp{sfx}.gate_proj.weight"), st.take(f"{p}mlp{sfx}.up_proj.weight")
+            if g is not None and u is not None:
+                st.write(dst + mlp + "gate_up_proj", gemm.interleave_gate_up(g, u))
+            st.write(dst + mlp + "down_proj", st.take(f"{p}mlp{sfx}.down_proj.weight"))
+            und = sfx == ""
+            st.write(dst + ("input_layernorm" if und else "input_norm"), st.take(f"{p}input_layernorm{sfx}.weight"))
+            st.write(dst + ("post_attention_layernorm" if und else "post_norm"),
+                     st.take(f"{p}post_attention_layernorm{sfx}.weight"))
+    return st.done(ignore_keys=_BAGEL_IGNORE)
+
+
+def bagel_checkpoint_keys(m) -> dict[str, torch.Tensor]:
+    """The published key layout of a ``BagelMoT``'s weights (inverse of ``load_bagel_mot``)."""
+    from ..ops import gemm
+    cfg = m.cfg
+    Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    sd = {k: v.detach().clone() for k, v in m.named_parameters()}
+    L = "language_model.model."
+    out = {L + "embed_tokens.weight": sd["und.embed_tokens"], L + "norm.weight": sd["und.norm"],
+           L + "norm_moe_gen.weight": sd["gen.final_norm"]}
+    if "und.lm_head" in sd:
+        out["language_model.lm_head.weight"] = sd["und.lm_head"]
+    out.update({ck_: sd[name] for ck_, name in _BAGEL_SIDE.items()})
+    for i in range(cfg.num_layers):
+        for sfx, dst, attn, mlp in (("", f"und.layers.{i}.", "self_attn.", "mlp."), ("_moe_gen", f"gen.layers.{i}.", "", "")):
+            p = f"{L}layers.{i}."
+            w, b = sd[dst + attn + "qkv_proj"], sd[dst + attn + "qkv_bias"]
+            cuts = {"q": (0, Hq * D), "k": (Hq * D, (Hq + Hkv) * D), "v": ((Hq + Hkv) * D, (Hq + 2 * Hkv) * D)}
+            for n, (a, e) in cuts.items():
+                out[f"{p}self_attn.{n}_proj{sfx}.weight"] = w[a:e].clone()
+                out[f"{p}self_attn.{n}_proj{sfx}.bias"] = b[a:e].clone()
+            out[f"{p}self_attn.o_proj{sfx}.weight"] = sd[dst + attn + "o_proj"]
+            if cfg.qk_norm:
+                out[f"{p}self_attn.q_norm{sfx}.weight"] = sd[dst + attn + "q_norm"]
+                out[f"{p}self_attn.k_norm{sfx}.weight"] = sd[dst + attn + "k_norm"]
+            g, u = gemm.split_gate_up(sd[dst + mlp + "gate_up_proj"])
+            out[f"{p}mlp{sfx}.gate_proj.weight"], out[f"{p}mlp{sfx}.up_proj.weight"] = g, u
+            out[f"{p}mlp{sfx}.down_proj.weight"] = sd[dst + mlp + "down_proj"]
+            und = sfx == ""
+            out[f"{p}input_layernorm{sfx}.weight"] = sd[dst + ("input_layernorm" if und else "input_norm")]
+            out[f"{p}post_attention_layernorm{sfx}.weight"] = sd[dst + ("post_attention_layernorm" if und else "post_norm")]
+    return out

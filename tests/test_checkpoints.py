@@ -190,3 +190,85 @@ def test_whisper_loaders_are_strict_and_the_encoder_matches_hugging_face():
         with pytest.raises(ck.CheckpointMismatch):
             ck.load_whisper_decoder(WhisperDecoder(vocab=120, hidden=64, layers=2, heads=4, ffn=128, max_pos=24,
                                                    dtype=torch.float32), bad)
+
+
+def test_siglip_vision_tower_matches_hugging_face_on_shared_weights():
+    transformers = pytest.importorskip("transformers")
+    from mstar_b200.models.encoders import EncoderConfig, VisionEncoder
+    cfg = transformers.SiglipVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                          num_channels=3, image_size=32, patch_size=8, hidden_act="gelu_pytorch_tanh",
+                                          layer_norm_eps=1e-6, attention_dropout=0.0, vision_use_head=False)
+    torch.manual_seed(2)
+    hf = transformers.SiglipVisionModel(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.copy_(torch.randn_like(p) * (0.15 if p.dim() > 1 else 0.1) + (1.0 if ("layer_norm" in n or "layernorm" in n) and n.endswith("weight") else 0.0))
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    ec = EncoderConfig(hidden_size=64, num_layers=2, num_heads=4, head_dim=16, ffn_dim=128, norm="layernorm", act="gelu",
+                       qkv_bias=True, eps=1e-6, dtype=torch.float32)
+    enc = VisionEncoder(ec, patch=8, pos="learned", pos_grid=4)
+    assert ck.load_siglip_vision(enc, sd)["loaded"] == len(dict(enc.named_parameters()))
+    img = torch.randn(3, 32, 32)
+    with torch.no_grad():
+        want = hf(pixel_values=img[None]).last_hidden_state[0]
+    got, lens, grids = enc([img])
+    assert lens == [16] and grids == [(1, 4, 4)]
+    assert torch.allclose(got, want, atol=2e-4, rtol=2e-4), (got - want).abs().max()
+    bad = dict(sd)
+    bad.pop("vision_model.encoder.layers.1.mlp.fc2.bias")
+    with pytest.raises(ck.CheckpointMismatch):
+        ck.load_siglip_vision(VisionEncoder(ec, patch=8, pos="learned", pos_grid=4), bad)
+
+
+def test_bagel_loader_round_trips_the_published_layout_and_is_strict():
+    from mstar_b200.models.bagel import BagelMoT
+    from mstar_b200.models.decoder import DecoderConfig
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                        vocab_size=128, qkv_bias=True, qk_norm=True, dtype=torch.float32)
+    src = BagelMoT(cfg, 8).init_random(1)
+    keys = ck.bagel_checkpoint_keys(src)
+    assert {"language_model.model.layers.1.self_attn.k_proj_moe_gen.bias", "language_model.model.norm_moe_gen.weight",
+            "language_model.model.layers.0.mlp_moe_gen.up_proj.weight", "time_embedder.mlp.2.weight",
+            "language_model.model.layers.1.self_attn.q_norm_moe_gen.weight", "vae2llm.weight"} <= set(keys)
+    # what other nodes load, and the frozen sine-cosine tables, are accepted and skipped
+    keys.update({"latent_pos_embed.pos_embed": torch.zeros(16, 64), "vit_model.vision_model.post_layernorm.weight": torch.ones(8),
+                 "connector.fc1.weight": torch.zeros(4, 4), "vit_pos_embed.pos_embed": torch.zeros(4, 4)})
+    dst = BagelMoT(cfg, 8).init_random(2)
+    assert ck.load_bagel_mot(dst, keys)["loaded"] == len(dict(dst.named_parameters()))
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+    for mutate in (lambda k: k.pop("language_model.model.layers.0.self_attn.v_proj_moe_gen.bias"),
+                   lambda k: k.update({"language_model.model.layers.0.mlp_moe_gen.extra.weight": torch.zeros(1)}),
+                   lambda k: k.update({"llm2vae.weight": torch.zeros(8, 63)})):
+        bad = dict(keys)
+        mutate(bad)
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_bagel_mot(BagelMoT(cfg, 8), bad)
+
+
+def test_bagel_vision_tower_and_connector_load_from_the_published_names(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from mstar_b200.models.bagel import BagelModel
+    m = BagelModel(model_dir=str(tmp_path), skip_weight_loading=False, small=True)
+    c = m.vit_cfg
+    hf_cfg = transformers.SiglipVisionConfig(hidden_size=c.hidden_size, intermediate_size=c.ffn_dim,
+                                             num_hidden_layers=c.num_layers, num_attention_heads=c.num_heads, num_channels=3,
+                                             image_size=m.vit_patch * 8, patch_size=m.vit_patch, vision_use_head=False)
+    torch.manual_seed(4)
+    hf = transformers.SiglipVisionModel(hf_cfg).float()
+    H, out = c.hidden_size, m.cfg.hidden_size
+    keys = {"vit_model." + k: v.detach().clone() for k, v in hf.state_dict().items()}
+    keys.update({"connector.fc1.weight": torch.randn(H, H), "connector.fc1.bias": torch.randn(H),
+                 "connector.fc2.weight": torch.randn(out, H), "connector.fc2.bias": torch.randn(out),
+                 "vit_pos_embed.pos_embed": torch.randn(64, H), "llm2vae.bias": torch.zeros(3)})
+    save_file({k: v.contiguous() for k, v in keys.items()}, str(tmp_path / "ema.safetensors"))
+    sub = m.get_submodule("vit_encoder", "cpu")
+    enc = sub.enc
+    assert torch.allclose(enc.proj2_w.float(), keys["connector.fc2.weight"], atol=1e-2)
+    assert torch.allclose(enc.pos_table.float(), keys["vit_pos_embed.pos_embed"], atol=1e-2)
+    q = keys["vit_model.vision_model.encoder.layers.0.self_attn.q_proj.weight"]
+    assert torch.allclose(enc.enc.layers[0].qkv_w[:q.shape[0]].float(), q, atol=1e-2)
+    keys.pop("connector.fc2.bias")
+    save_file({k: v.contiguous() for k, v in keys.items()}, str(tmp_path / "ema.safetensors"))
+    with pytest.raises(ck.CheckpointMismatch):
+        m.get_submodule("vit_encoder", "cpu")
