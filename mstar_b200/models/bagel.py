@@ -498,7 +498,12 @@ class BagelModel(Model):
                 self._load_vit(enc)
             return VitSubmodule(enc, device)
         if node_name in ("vae_encoder", "vae_decoder"):
-            vae = ConvVAE(self.vae_cfg).to(device=device, dtype=self.dtype).eval()
+            vae = ConvVAE(self.vae_cfg)
+            if not (self.skip_weight_loading or self.model_dir is None):
+                import os
+                from .checkpoints import load_image_autoencoder
+                load_image_autoencoder(vae, os.path.join(self.model_dir, "ae.safetensors"))
+            vae = vae.to(device=device, dtype=self.dtype).eval()
             if node_name == "vae_decoder":
                 return ImageDecodeSubmodule(vae, device, self.dtype)
             return _BagelVaeEncode(vae, device, self.dtype)

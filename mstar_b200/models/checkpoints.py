@@ -8,6 +8,8 @@ silently skipped weight is a wrong-output bug, not a warning.
                                  Conv3d patch embedding flattened to a GEMM weight, scale-shift tables kept fp32.
   * ``load_whisper``             Hugging Face ``WhisperForConditionalGeneration`` names.
   * ``load_t5_encoder``          Hugging Face ``UMT5EncoderModel`` / ``T5EncoderModel`` names.
+  * ``load_siglip_vision``, ``load_bagel_mot``, ``load_image_autoencoder``   the three files of a published BAGEL
+                                 checkpoint (vision tower, both experts, latent autoencoder).
 
 Reference counterparts: mstar/model/wan22/weight_loader.py:34-138 (key remap and completeness contract),
 mstar/model/cosmos3/loader.py:25-126, mstar/model/loader/base.py (stacked-parameter rules).
@@ -592,3 +594,86 @@ def bagel_checkpoint_keys(m) -> dict[str, torch.Tensor]:
             out[f"{p}input_layernorm{sfx}.weight"] = sd[dst + ("input_layernorm" if und else "input_norm")]
             out[f"{p}post_attention_layernorm{sfx}.weight"] = sd[dst + ("post_attention_layernorm" if und else "post_norm")]
     return out
+
+
+# ------------------------------------------------------------------ image autoencoder (latent-diffusion names)
+def _ae_conv(st: _Strict, src: str, dst: str) -> None:
+    st.write(dst + ".weight", st.take(src + ".weight"))
+    st.write(dst + ".bias", st.take(src + ".bias"))
+
+
+def _ae_res(st: _Strict, src: str, dst: str, res) -> None:
+    for a, b in (("norm1", "n1"), ("norm2", "n2")):
+        _ae_conv(st, f"{src}.{a}", f"{dst}.{b}")
+    for a, b in (("conv1", "c1"), ("conv2", "c2")):
+        _ae_conv(st, f"{src}.{a}", f"{dst}.{b}.conv")
+    if res.skip is not None:
+        _ae_conv(st, f"{src}.nin_shortcut", f"{dst}.skip.conv")
+
+
+def _ae_mid(st: _Strict, src: str, dst: str, mid) -> None:
+    _ae_res(st, src + ".block_1", dst + ".0", mid[0])
+    _ae_conv(st, src + ".attn_1.norm", dst + ".1.norm")
+    ws = [st.take(f"{src}.attn_1.{n}.weight") for n in "qkv"]          # 1x1 convolutions -> one stacked projection
+    bs = [st.take(f"{src}.attn_1.{n}.bias") for n in "qkv"]
+    if None not in ws and None not in bs:
+        if len({tuple(w.shape) for w in ws}) > 1:
+            st.bad.append(f"{src}.attn_1: q / k / v of different shapes {[tuple(w.shape) for w in ws]}")
+        else:
+            st.write(dst + ".1.qkv.weight", torch.cat([w.reshape(w.shape[0], -1) for w in ws]))
+            st.write(dst + ".1.qkv.bias", torch.cat(bs))
+    w = st.take(src + ".attn_1.proj_out.weight")
+    st.write(dst + ".1.proj.weight", None if w is None else w.reshape(w.shape[0], -1))
+    st.write(dst + ".1.proj.bias", st.take(src + ".attn_1.proj_out.bias"))
+    _ae_res(st, src + ".block_2", dst + ".2", mid[2])
+
+
+def _ae_names(vae):
+    """(checkpoint prefix, parameter prefix, module) of every residual block and resampling conv of a 2D ``ConvVAE``
+    in the latent-diffusion numbering: ``encoder.down.L.block.J`` / ``.downsample``; ``decoder.up.L.block.J`` /
+    ``.upsample`` with L counted from the full-resolution end while the modules run from the coarse end."""
+    from .vae import _Res, _Up
+    c = vae.cfg
+    n_lv = len(c.channel_mult)
+    out, it = [], iter(enumerate(vae.encoder.down))
+    for lv in range(n_lv):
+        for j in range(c.num_res_blocks):
+            i, m = next(it)
+            out.append((f"encoder.down.{lv}.block.{j}", f"encoder.down.{i}", m))
+        if lv < n_lv - 1:
+            i, m = next(it)
+            out.append((f"encoder.down.{lv}.downsample.conv", f"encoder.down.{i}.conv", m))
+    it = iter(enumerate(vae.decoder.up))
+    for lv in reversed(range(n_lv)):
+        for j in range(c.num_res_blocks + 1):
+            i, m = next(it)
+            out.append((f"decoder.up.{lv}.block.{j}", f"decoder.up.{i}", m))
+        if lv > 0:
+            i, m = next(it)
+            out.append((f"decoder.up.{lv}.upsample.conv", f"decoder.up.{i}.conv.conv", m))
+    assert all(isinstance(m, _Res) or isinstance(m, _Up) or hasattr(m, "conv") for _, _, m in out)
+    return out
+
+
+@torch.no_grad()
+def load_image_autoencoder(vae, src) -> dict:
+    """2D ``ConvVAE`` from the latent-diffusion autoencoder layout that BAGEL publishes as ``ae.safetensors``
+    (``encoder.down.L.block.J.{norm1,conv1,norm2,conv2,nin_shortcut}``, ``down.L.downsample.conv``,
+    ``mid.{block_1,attn_1,block_2}``, ``norm_out``, ``conv_out``; the decoder mirrors it with ``up.L``). The mid-block
+    attention's q / k / v / proj_out 1x1 convolutions become two linear layers. Strict.
+    Reference module: mstar/model/bagel/components/autoencoder.py:107-257."""
+    from .vae import _Res
+    if vae.cfg.dims != 2:
+        raise CheckpointMismatch("the latent-diffusion image autoencoder layout is 2D")
+    st = _Strict(vae, _tensors_of(src), "image autoencoder")
+    for half, mod in (("encoder", vae.encoder), ("decoder", vae.decoder)):
+        _ae_conv(st, half + ".conv_in", half + ".inp.conv")
+        _ae_mid(st, half + ".mid", half + ".mid", mod.mid)
+        _ae_conv(st, half + ".norm_out", half + ".norm")
+        _ae_conv(st, half + ".conv_out", half + ".out.conv")
+    for ck, name, m in _ae_names(vae):
+        if isinstance(m, _Res):
+            _ae_res(st, ck, name, m)
+        else:
+            _ae_conv(st, ck, name)
+    return st.done()

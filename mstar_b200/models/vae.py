@@ -40,19 +40,24 @@ class VAEConfig:
 
 
 class _Conv(nn.Module):
-    """2D conv, or 3D conv that pads time on the past side only (frame t never sees frame t+1)."""
+    """2D conv, or 3D conv that pads time on the past side only (frame t never sees frame t+1). A strided 2D conv
+    pads on the right and bottom only, as the published image autoencoder weights were trained
+    (mstar/model/bagel/components/autoencoder.py:83-93)."""
 
     def __init__(self, dims, cin, cout, k=3, stride=1, t_stride=1):
         super().__init__()
         self.dims, self.k = dims, k
+        self.one_sided = dims == 2 and stride > 1
         if dims == 2:
-            self.conv = nn.Conv2d(cin, cout, k, stride=stride, padding=k // 2)
+            self.conv = nn.Conv2d(cin, cout, k, stride=stride, padding=0 if self.one_sided else k // 2)
         else:
             self.conv = nn.Conv3d(cin, cout, k, stride=(t_stride, stride, stride), padding=(0, k // 2, k // 2))
 
     def forward(self, x):
         if self.dims == 3 and self.k > 1:
             x = F.pad(x, (0, 0, 0, 0, self.k - 1, 0), mode="replicate")
+        elif self.one_sided:
+            x = F.pad(x, (0, self.k // 2, 0, self.k // 2))
         return self.conv(x)
 
 

@@ -272,3 +272,39 @@ def test_bagel_vision_tower_and_connector_load_from_the_published_names(tmp_path
     save_file({k: v.contiguous() for k, v in keys.items()}, str(tmp_path / "ema.safetensors"))
     with pytest.raises(ck.CheckpointMismatch):
         m.get_submodule("vit_encoder", "cpu")
+
+
+def test_image_autoencoder_matches_the_reference_module_on_a_shared_checkpoint():
+    """The reference's own ``BagelAutoEncoder`` (fp32, CPU) and ``ConvVAE`` loaded from its state dict (the
+    ``ae.safetensors`` names) encode and decode to the same tensors; a missing, extra or mis-shaped tensor raises."""
+    _ref_modules()
+    from mstar.model.bagel.components.autoencoder import BagelAutoEncoder
+    from mstar.model.bagel.config import BagelAutoEncoderConfig
+    from mstar_b200.models.vae import ConvVAE, VAEConfig
+    torch.manual_seed(0)
+    rc = BagelAutoEncoderConfig(resolution=32, ch=32, ch_mult=(1, 2, 2), num_res_blocks=1, z_channels=4)
+    ref = BagelAutoEncoder(rc).float().eval()
+    ref.reg.sample = False
+    for n, p in ref.named_parameters():
+        torch.nn.init.normal_(p, std=0.08 if p.dim() > 1 else 0.05)
+        if "norm" in n and n.endswith("weight"):
+            p.data.add_(1.0)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    cfg = VAEConfig(dims=2, latent_channels=4, base_channels=32, channel_mult=(1, 2, 2), num_res_blocks=1,
+                    scaling_factor=rc.scale_factor, shift_factor=rc.shift_factor)
+    ours = ConvVAE(cfg).float().eval()
+    ck.load_image_autoencoder(ours, sd)
+    x = torch.rand(2, 3, 32, 48) * 2 - 1
+    with torch.no_grad():
+        z_ref, z = ref.encode(x), ours.encode(x)
+        assert z.shape == z_ref.shape == (2, 4, 8, 12)
+        assert (z - z_ref).abs().max().item() < 1e-4 * max(1.0, z_ref.abs().max().item())
+        px_ref, px = ref.decode(z_ref).clamp(-1, 1), ours.decode(z_ref)
+        assert (px - px_ref).abs().max().item() < 1e-4
+    for mutate in (lambda d: d.pop("decoder.up.1.upsample.conv.weight"),
+                   lambda d: d.update({"encoder.down.0.attn.0.norm.weight": torch.zeros(32)}),
+                   lambda d: d.update({"encoder.mid.attn_1.q.weight": torch.zeros(64, 32, 1, 1)})):
+        bad = dict(sd)
+        mutate(bad)
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_image_autoencoder(ConvVAE(cfg), bad)
