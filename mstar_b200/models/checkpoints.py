@@ -677,3 +677,101 @@ def load_image_autoencoder(vae, src) -> dict:
         else:
             _ae_conv(st, ck, name)
     return st.done()
+
+
+# ------------------------------------------------------------------ Pi0.5 policy (lerobot names)
+_PI05_PALI = "paligemma_with_expert.paligemma.model."
+_PI05_EXPERT = "paligemma_with_expert.gemma_expert.model."
+_PI05_TOP = {"action_in_proj.weight": "a_in_w", "action_in_proj.bias": "a_in_b", "action_out_proj.weight": "a_out_w",
+             "action_out_proj.bias": "a_out_b", "time_mlp_in.weight": "t1_w", "time_mlp_in.bias": "t1_b",
+             "time_mlp_out.weight": "t2_w", "time_mlp_out.bias": "t2_b"}
+
+
+def _gemma_layer(st: _Strict, src: str, dst: str, adaptive: bool) -> None:
+    q, k, v = (st.take(f"{src}self_attn.{n}_proj.weight") for n in "qkv")
+    if None not in (q, k, v):
+        st.write(dst + "qkv", torch.cat([q, k, v]))
+    st.write(dst + "o", st.take(src + "self_attn.o_proj.weight"))
+    g, u = st.take(src + "mlp.gate_proj.weight"), st.take(src + "mlp.up_proj.weight")
+    if g is not None and u is not None:
+        st.write(dst + "gate_up", torch.cat([g, u]))                     # gate rows, then up rows
+    st.write(dst + "down", st.take(src + "mlp.down_proj.weight"))
+    for ck_, ours in (("input_layernorm", "1"), ("post_attention_layernorm", "2")):
+        if adaptive:                # dense: condition -> (scale, shift, gate)
+            st.write(f"{dst}mod{ours}_w", st.take(f"{src}{ck_}.dense.weight"))
+            st.write(f"{dst}mod{ours}_b", st.take(f"{src}{ck_}.dense.bias"))
+        else:
+            st.write(f"{dst}n{ours}", st.take(f"{src}{ck_}.weight"))
+
+
+@torch.no_grad()
+def load_pi05_policy(m, src) -> dict:
+    """``Pi05Policy`` (PaliGemma prefix tower ``und``, adaptive-norm action expert ``act``, action / time projections)
+    from the published lerobot layout: ``paligemma_with_expert.paligemma.model.language_model.*`` and
+    ``paligemma_with_expert.gemma_expert.model.*`` in Hugging Face Gemma names, the expert's norms as
+    ``*.dense.{weight,bias}``, the tied token table under ``paligemma.lm_head.weight``, ``action_in_proj``,
+    ``action_out_proj``, ``time_mlp_in`` / ``time_mlp_out``. The vision tower and projector are another node's
+    (``load_pi05_vision``); the expert's unused ``lm_head`` / token table are ignored. Strict.
+    Reference key map: mstar/model/pi05/pi05_model.py:300-347."""
+    T = {k: v for k, v in _tensors_of(src).items()
+         if not k.startswith((_PI05_PALI + "vision_tower.", _PI05_PALI + "multi_modal_projector."))}
+    st = _Strict(m, T, "Pi0.5 policy")
+    head = st.take("paligemma_with_expert.paligemma.lm_head.weight", optional=True)
+    table = st.take(_PI05_PALI + "language_model.embed_tokens.weight", optional=True)
+    if head is None and table is None:
+        st.bad.append("missing the token table (paligemma.lm_head.weight / language_model.embed_tokens.weight)")
+    st.write("embed", head if head is not None else table)
+    for ck_, name in _PI05_TOP.items():
+        st.write(name, st.take(ck_))
+    for i in range(len(m.und.layers)):
+        _gemma_layer(st, f"{_PI05_PALI}language_model.layers.{i}.", f"und.layers.{i}.", False)
+        _gemma_layer(st, f"{_PI05_EXPERT}layers.{i}.", f"act.layers.{i}.", True)
+    st.write("und.nf", st.take(_PI05_PALI + "language_model.norm.weight"))
+    st.write("act.modf_w", st.take(_PI05_EXPERT + "norm.dense.weight"))
+    st.write("act.modf_b", st.take(_PI05_EXPERT + "norm.dense.bias"))
+    return st.done(ignore_keys=("paligemma_with_expert.gemma_expert.lm_head.weight", _PI05_EXPERT + "embed_tokens.weight"))
+
+
+@torch.no_grad()
+def load_pi05_vision(enc, src) -> dict:
+    """The policy's camera encoder from the same file: SigLIP names under
+    ``paligemma_with_expert.paligemma.model.vision_tower.vision_model.`` and the one-layer projector under
+    ``…multi_modal_projector.linear``. Strict over those two prefixes.
+    Reference: mstar/model/pi05/pi05_model.py:349-377."""
+    T = _tensors_of(src)
+    vt, mp = _PI05_PALI + "vision_tower.vision_model.", _PI05_PALI + "multi_modal_projector.linear."
+    w, b = T.get(mp + "weight"), T.get(mp + "bias")
+    for t, p, n in ((w, enc.proj2_w, "weight"), (b, enc.proj2_b, "bias")):
+        if t is None or tuple(t.shape) != tuple(p.shape):
+            raise CheckpointMismatch(f"Pi0.5 vision projector: {mp}{n} missing or of shape "
+                                     f"{None if t is None else tuple(t.shape)} (parameter {tuple(p.shape)})")
+        p.data.copy_(t.to(p.dtype))
+    return load_siglip_vision(enc, {k[len(vt):]: v for k, v in T.items() if k.startswith(vt)}, prefix="")
+
+
+def pi05_checkpoint_keys(m, enc=None) -> dict[str, torch.Tensor]:
+    """The published key layout of a ``Pi05Policy`` (and, with ``enc``, of its camera encoder's projector): inverse
+    of ``load_pi05_policy``."""
+    sd = {k: v.detach().clone() for k, v in m.named_parameters()}
+    nh, nkv, D = m.und.nh, m.und.nkv, m.und.D
+    out = {"paligemma_with_expert.paligemma.lm_head.weight": sd["embed"]}
+    out.update({ck_: sd[name] for ck_, name in _PI05_TOP.items()})
+    for tower, pre, adaptive in (("und", _PI05_PALI + "language_model.", False), ("act", _PI05_EXPERT, True)):
+        for i in range(len(m.und.layers)):
+            s, d = f"{tower}.layers.{i}.", f"{pre}layers.{i}."
+            qkv = sd[s + "qkv"]
+            out[d + "self_attn.q_proj.weight"] = qkv[:nh * D].clone()
+            out[d + "self_attn.k_proj.weight"] = qkv[nh * D:(nh + nkv) * D].clone()
+            out[d + "self_attn.v_proj.weight"] = qkv[(nh + nkv) * D:].clone()
+            out[d + "self_attn.o_proj.weight"] = sd[s + "o"]
+            gu = sd[s + "gate_up"]
+            out[d + "mlp.gate_proj.weight"], out[d + "mlp.up_proj.weight"] = gu[:gu.shape[0] // 2].clone(), gu[gu.shape[0] // 2:].clone()
+            out[d + "mlp.down_proj.weight"] = sd[s + "down"]
+            for ck_, ours in (("input_layernorm", "1"), ("post_attention_layernorm", "2")):
+                if adaptive:
+                    out[f"{d}{ck_}.dense.weight"], out[f"{d}{ck_}.dense.bias"] = sd[f"{s}mod{ours}_w"], sd[f"{s}mod{ours}_b"]
+                else:
+                    out[f"{d}{ck_}.weight"] = sd[f"{s}n{ours}"]
+    out[_PI05_PALI + "language_model.norm.weight"] = sd["und.nf"]
+    out[_PI05_EXPERT + "norm.dense.weight"], out[_PI05_EXPERT + "norm.dense.bias"] = sd["act.modf_w"], sd["act.modf_b"]
+    return out

@@ -186,7 +186,10 @@ class VisionEncoder(nn.Module):
     to each image's grid (NaViT style); "rope2d" rotates q/k halves by the patch's (row, col)."""
 
     def __init__(self, c: EncoderConfig, patch: int = 14, in_channels: int = 3, temporal_patch: int = 1,
-                 pos: str = "learned", pos_grid: int = 70, out_dim: int | None = None, merge: int = 1, device="cpu"):
+                 pos: str = "learned", pos_grid: int = 70, out_dim: int | None = None, merge: int = 1, device="cpu",
+                 projector: str = "mlp"):
+        """``projector``: "mlp" (linear, GELU, linear — BAGEL's connector, the Qwen mergers) or "linear" (one layer,
+        PaliGemma's multi-modal projector); used when ``out_dim`` is given."""
         super().__init__()
         self.c, self.patch, self.tp, self.pos, self.merge = c, patch, temporal_patch, pos, merge
         pdim = in_channels * temporal_patch * patch * patch
@@ -195,9 +198,10 @@ class VisionEncoder(nn.Module):
         self.pos_grid = pos_grid
         self.enc = TransformerEncoder(c, device)
         md = c.hidden_size * merge * merge
-        self.out_dim = out_dim
+        self.out_dim, self.projector = out_dim, projector
         if out_dim:
-            self.proj1_w, self.proj1_b = _p((md, md), c.dtype, device), _p((md,), c.dtype, device)
+            if projector == "mlp":
+                self.proj1_w, self.proj1_b = _p((md, md), c.dtype, device), _p((md,), c.dtype, device)
             self.proj2_w, self.proj2_b = _p((out_dim, md), c.dtype, device), _p((out_dim,), c.dtype, device)
 
     def init_random(self, seed=0):
@@ -265,8 +269,9 @@ class VisionEncoder(nn.Module):
             taps = [self._merge(t, grids) for t in taps]
             lens = [n // m for n in lens]
         if self.out_dim:
-            x = gemm.linear(gemm.linear(x, self.proj1_w, bias=self.proj1_b, epilogue=gemm.EPILOGUE_GELU),
-                            self.proj2_w, bias=self.proj2_b)
+            if self.projector == "mlp":
+                x = gemm.linear(x, self.proj1_w, bias=self.proj1_b, epilogue=gemm.EPILOGUE_GELU)
+            x = gemm.linear(x, self.proj2_w, bias=self.proj2_b)
         return (x, lens, grids, taps) if collect else (x, lens, grids)
 
     def _merge(self, x, grids):

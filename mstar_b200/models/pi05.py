@@ -23,7 +23,6 @@ from ..ops import gemm
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
 from .base import small_scale, EngineType, ForwardPassArgs, Model
-from .dit import sinusoidal_embedding
 from .encoders import EncoderConfig, VisionEncoder
 from .submodule_base import ARNodeInputs, ARNodeSubmodule, NodeSubmodule
 
@@ -93,6 +92,22 @@ class GemmaTower(nn.Module):
         return norm_ops.norm(x, self.nf, 1e-6, gemma=True)[0]
 
 
+def flow_time_embedding(t: torch.Tensor, dim: int, min_period: float = 4e-3, max_period: float = 4.0) -> torch.Tensor:
+    """fp32 [n, dim], sine half then cosine half, periods spaced geometrically from ``min_period`` to ``max_period``
+    (computed in fp64: the short periods lose digits otherwise and the error compounds through the adaptive norms).
+    Reference: mstar/model/pi05/components/flow_matching.py:7-42."""
+    frac = torch.linspace(0.0, 1.0, dim // 2, dtype=torch.float64, device=t.device)
+    omega = 2.0 * math.pi / (min_period * (max_period / min_period) ** frac)
+    ang = t.to(torch.float64).reshape(-1, 1) * omega
+    return torch.cat([torch.sin(ang), torch.cos(ang)], dim=-1).float()
+
+
+def state_bins(state, bins: int = 256) -> list[int]:
+    """Robot state in [-1, 1] -> bin indices (mstar/model/pi05/components/flow_matching.py:53-75)."""
+    s = torch.as_tensor(state, dtype=torch.float32).clamp(-1.0, 1.0)
+    return ((s + 1.0) / 2.0 * (bins - 1)).round().long().clamp(0, bins - 1).tolist()
+
+
 class Pi05Policy(nn.Module):
     def __init__(self, *, vocab, hidden, layers, heads, kv_heads, head_dim, ffn, a_hidden, a_ffn, action_dim, dtype, device):
         super().__init__()
@@ -128,7 +143,7 @@ class Pi05Policy(nn.Module):
         """actions: [horizon, action_dim] fp32 -> velocity, same shape (fp32)."""
         n = actions.shape[0]
         x = gemm.linear(actions.to(self.dtype), self.a_in_w, bias=self.a_in_b)
-        e = sinusoidal_embedding(torch.tensor([t], device=x.device), x.shape[-1], max_period=4.0).to(self.dtype)
+        e = flow_time_embedding(torch.tensor([t], device=x.device), x.shape[-1]).to(self.dtype)
         c = gemm.linear(e, self.t1_w, bias=self.t1_b)
         c = gemm.linear(torch.nn.functional.silu(c.float()).to(c.dtype), self.t2_w, bias=self.t2_b)
         cond = torch.nn.functional.silu(c.float()).to(c.dtype)                      # [1, a_hidden]
@@ -193,8 +208,12 @@ class Pi05LLMSubmodule(ARNodeSubmodule):
         ni, ctx, m = inputs[0], engine_inputs.batch_context, self.m
         st = engine_inputs.per_request_states[ni.request_id]
         if graph_walk == "prefill":
-            parts = [t.reshape(-1, m.H).to(self.device, m.dtype) for t in ni.tensor_inputs.get("image_features", [])]
-            parts.append(ew.embed(ni.input_ids.to(self.device), m.embed, scale=math.sqrt(m.H)))
+            # the published weights expect image tokens scaled by sqrt(H) and text rows by H (the checkpoint's own
+            # embedding layer scales by sqrt(H) once and the policy's prefix builder a second time:
+            # mstar/model/pi05/submodules.py:306-326)
+            parts = [ew.affine(t.reshape(-1, m.H).to(self.device, m.dtype).contiguous(), math.sqrt(m.H), 0.0, out_dtype=m.dtype)
+                     for t in ni.tensor_inputs.get("image_features", [])]
+            parts.append(ew.embed(ni.input_ids.to(self.device), m.embed, scale=float(m.H)))
             m.prefix(torch.cat(parts).contiguous(), ctx)
             st["prefix_len"] = ni.input_seq_len
             return [{"prefill_done": torch.tensor([ni.input_seq_len], dtype=torch.int64)}]
@@ -261,21 +280,42 @@ class Pi05Model(Model):
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "vit_encoder":
             enc = VisionEncoder(self.vit_cfg, patch=self.patch, pos="learned", pos_grid=4 if self.small else 16,
-                                out_dim=self.kw["hidden"], device=device).init_random(0)
+                                out_dim=self.kw["hidden"], device=device, projector="linear").init_random(0)
+            if not (self.skip_weight_loading or self.model_dir is None):
+                from .checkpoints import load_pi05_vision
+                load_pi05_vision(enc, self._checkpoint())
             return Pi05VitSubmodule(enc, device)
         if node_name == "LLM":
             m = Pi05Policy(action_dim=self.action_dim, dtype=self.dtype, device=device, **self.kw).init_random(0)
             if not (self.skip_weight_loading or self.model_dir is None):
-                from .loader import load_named_tensors
-                load_named_tensors(m, self.model_dir)
+                from .checkpoints import load_pi05_policy
+                load_pi05_policy(m, self._checkpoint())
             return Pi05LLMSubmodule(m, device, self.horizon, self.num_steps)
         raise KeyError(node_name)
 
-    def process_prompt(self, prompt, input_modalities, output_modalities, tensors, state: list | None = None, **kw):
+    def _checkpoint(self) -> str:
+        """The published policy is one ``model.safetensors`` in the snapshot directory."""
+        import os
+        one = os.path.join(self.model_dir, "model.safetensors")
+        return one if os.path.exists(one) else self.model_dir
+
+    MAX_LANG_TOKENS = 200
+
+    def process_prompt(self, prompt, input_modalities, output_modalities, tensors, state: list | None = None,
+                       robot_state: list | None = None, **kw):
         v = self.kw["vocab"]
-        ids = self.encode_text(prompt, v, v - 300, default="do the task")
-        if state:            # robot state, discretised into 256 bins over [-1, 1], as trailing tokens
-            ids += [v - 300 + int(min(255, max(0, (float(s) + 1) * 128))) for s in state]
+        state = state if state is not None else robot_state
+        if self.tokenizer() is not None:
+            # the published prompt format: lower-cased task, the state's bin indices as text
+            # (mstar/model/pi05/pi05_model.py:470-505, components/tokenization.py:12-34)
+            text = (prompt or "").strip().replace("_", " ").replace("\n", " ")
+            if state is not None and len(state):
+                text = f"Task: {text}, State: {' '.join(str(b) for b in state_bins(state))};\nAction: "
+            ids = list(self.tokenizer()(text.strip().lower(), add_special_tokens=True).input_ids)[:self.MAX_LANG_TOKENS]
+        else:
+            ids = self.encode_text(prompt, v, v - 300, default="do the task")
+            if state is not None and len(state):        # without a tokenizer: one reserved id per state bin
+                ids += [v - 300 + b for b in state_bins(state)]
         if not tensors.get("image"):
             raise ValueError("the policy needs at least one camera image")
         return {"input_ids": [torch.tensor(ids, dtype=torch.int64)], "image": [t.float() for t in tensors["image"]]}
