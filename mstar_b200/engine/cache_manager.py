@@ -221,6 +221,33 @@ class BatchedCacheManager:
                            labels=list(labels), q_lens=list(q_lens), write_cache=write_cache)
         return ctx
 
+    def span_plan(self, ctx: BatchContext, spans: list[tuple[int, int, int]], group: int = 1):
+        """A second, non-causal plan over row ranges of a batch that ``plan`` has just laid out (before the forward
+        advances the sequence lengths): every span ``(entry, start, end)`` — rows ``start … end-1`` of that entry's new
+        tokens — becomes an entry whose queries see the entry's cached keys and the new ones up to ``end``. A packed
+        prompt runs its causal pass over all rows and then this pass over the spans that attend among themselves
+        (the rows between an image's start and end markers). Returns (plan, int64 rows of the spans in the batch's
+        token order); built from fresh device tensors, so it is not for captured graphs."""
+        qi, kl, pi, pidx, rows, off = [0], [], [0], [], [], [0]
+        for n in ctx.q_lens:
+            off.append(off[-1] + n)
+        for e, a, b in spans:
+            if not (0 <= a < b <= ctx.q_lens[e]):
+                raise ValueError(f"span {(e, a, b)} outside entry of {ctx.q_lens[e]} rows")
+            st = self.alloc.get_state(ctx.request_ids[e], ctx.labels[e])
+            qi.append(qi[-1] + (b - a))
+            kl.append(st.seq_len + b)
+            pidx += list(st.pages)
+            pi.append(len(pidx))
+            rows += range(off[e] + a, off[e] + b)
+        i32 = dict(dtype=torch.int32, device=self.device)
+        lens = [b - a for _, a, b in spans]
+        plan = attn_ops.AttnPlan(q_indptr=torch.tensor(qi, **i32), kv_lens=torch.tensor(kl, **i32), batch=len(spans),
+                                 num_q_tokens=qi[-1], num_q_tiles=attn_ops.count_q_tiles(lens, group),
+                                 page_indptr=torch.tensor(pi, **i32), page_indices=torch.tensor(pidx, **i32), splits=1,
+                                 causal=False, window=0, max_q_len=max(lens))
+        return plan, torch.tensor(rows, dtype=torch.int64, device=self.device)
+
     def plan_snapshot(self, slot: int) -> torch.Tensor:
         return self._slots[slot].dev.clone()
 

@@ -93,9 +93,12 @@ class BagelMoT(torch.nn.Module):
         x = x + self.time_embed(torch.tensor([t], device=x.device))
         return x + sincos_2d(grid[0], grid[1], self.cfg.hidden_size, x.device).to(x.dtype)
 
-    def forward_mixed(self, x: torch.Tensor, is_gen: torch.Tensor, ctx) -> torch.Tensor:
+    def forward_mixed(self, x: torch.Tensor, is_gen: torch.Tensor, ctx, spans=None) -> torch.Tensor:
         """Packed prefill with per-row experts. x: [T, H]; is_gen: bool [T]. K/V of every row go to the paged
-        pool; returns final-normed hidden states [T, H] (understanding rows normed by the understanding expert)."""
+        pool; returns final-normed hidden states [T, H] (understanding rows normed by the understanding expert).
+        ``spans`` = (plan, rows) from ``BatchedCacheManager.span_plan``: those rows attend to everything up to the
+        end of their span (an image's marker + patch rows see one another), every other row is causal — the same
+        result as prefilling text, image, text as separate passes (mstar/model/bagel/submodules.py:378-380)."""
         cfg = self.cfg
         u_idx, g_idx = (~is_gen).nonzero().reshape(-1), is_gen.nonzero().reshape(-1)
         pos = ctx.positions if ctx.positions.dim() == 1 else ctx.positions[0]
@@ -119,6 +122,8 @@ class BagelMoT(torch.nn.Module):
                     q, p["res"] = self._und_qkv(li, p["x"], p["res"], p["pos"], sub)
                 q_full[p["idx"]] = q
             a = attn_ops.attention(q_full, ctx.plan, kv_cache=kv)
+            if spans is not None:
+                a.index_copy_(0, spans[1], attn_ops.attention(q_full.index_select(0, spans[1]), spans[0], kv_cache=kv))
             for name, p in parts.items():
                 ai = a.index_select(0, p["idx"])
                 if name == "g":
@@ -164,6 +169,25 @@ class BagelMoT(torch.nn.Module):
         h = self.gen(x, pos, plan, prefix_ctx=prefix_ctx)
         v = gemm.linear(h, self.llm2vae_w, bias=self.llm2vae_b, out_dtype=torch.float32)
         return v.reshape(n_branches, S, -1)
+
+
+def image_span_positions(ids: list[int]):
+    """Rotary positions of a packed prompt and its image spans. Text tokens advance the position by one; the rows
+    from an image's start marker to its end marker share one position. Returns (int64 [T], [(start, end)] with
+    ``end`` exclusive); an unterminated span runs to the end of the prompt."""
+    pos, spans, p, open_at = [], [], 0, None
+    for i, t in enumerate(ids):
+        if i and (open_at is None or t == VISION_START):
+            p += 1
+        if t == VISION_START and open_at is None:
+            open_at = i
+        pos.append(p)
+        if t == VISION_END and open_at is not None:
+            spans.append((open_at, i + 1))
+            open_at = None
+    if open_at is not None:
+        spans.append((open_at, len(ids)))
+    return torch.tensor(pos, dtype=torch.int64), spans
 
 
 def patchify2d(z: torch.Tensor, p: int = 2):
@@ -244,16 +268,11 @@ class BagelLLMSubmodule(ARNodeSubmodule):
             rows = {lb: self._context_rows(ni.input_ids, lb) for lb in labels}
             labels = [lb for lb in labels if rows[lb].numel()]
             ni.kwargs["_rows"], ni.kwargs["_labels"] = rows, labels
-            # rotary position: text tokens advance by one, every token of an image span shares one position
+            # rotary position: text tokens advance by one; an image's start marker, patch rows and end marker share
+            # one position (mstar/model/bagel/submodules.py:444-455, custom_advance_pos_id=1 at :833)
             ids = ni.input_ids
-            pos_all = torch.zeros(ids.numel(), dtype=torch.int64)
-            p, prev_img = 0, False
-            for i, t in enumerate(ids.tolist()):
-                is_img = t in (IMG_PLACEHOLDER, VAE_PLACEHOLDER)
-                if i and not (is_img and prev_img):
-                    p += 1
-                pos_all[i], prev_img = p, is_img
-            ni.kwargs["_pos_end"] = p + 1
+            pos_all, img_spans = image_span_positions(ids.tolist())
+            ni.kwargs["_pos_end"] = int(pos_all[-1]) + 1 if ids.numel() else 0
             custom = torch.cat([pos_all[rows[lb]] for lb in labels]) if labels else None
             if not labels:
                 labels, rows = ["main"], {"main": torch.zeros(0, dtype=torch.int64)}
@@ -262,6 +281,12 @@ class BagelLLMSubmodule(ARNodeSubmodule):
                              custom_positions=custom[None].to(torch.int32) if custom is not None else None)
             for lb in labels:
                 cache.set_custom_pos_advance(ni.request_id, lb, int(ni.kwargs["_pos_end"]) - int(rows[lb].numel()))
+            # rows of an image span attend among themselves: a second, non-causal pass over those rows
+            spans = []
+            for e, lb in enumerate(labels):
+                where = {int(r): i for i, r in enumerate(rows[lb].tolist())}
+                spans += [(e, where[a], where[b - 1] + 1) for a, b in img_spans if a in where and (b - 1) in where]
+            ni.kwargs["_spans"] = cache.span_plan(ctx, spans, group=G) if spans else None
             return ctx
         if graph_walk == "decode":
             return None
@@ -304,7 +329,8 @@ class BagelLLMSubmodule(ARNodeSubmodule):
         if not labels:
             return {"prefill_done": torch.zeros(1, dtype=torch.int64)}
         sel = torch.cat([rows[lb] for lb in labels]).to(self.device)
-        h = m.forward_mixed(x.index_select(0, sel).contiguous(), is_gen.index_select(0, sel), ctx)
+        h = m.forward_mixed(x.index_select(0, sel).contiguous(), is_gen.index_select(0, sel), ctx,
+                            spans=ni.kwargs.pop("_spans", None))
         out = {"prefill_done": torch.tensor([ids.numel()], dtype=torch.int64)}
         if labels[0] == "main" and not ni.kwargs.get("gen"):          # first text token of an understanding request
             last = int(rows["main"].numel()) - 1

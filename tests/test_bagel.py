@@ -51,6 +51,37 @@ def test_experts_differ_when_weights_differ():
     assert (a[2:] - b[2:]).abs().max().item() > 1e-3
 
 
+def test_packed_prefill_with_an_image_span_equals_text_image_text_passes():
+    """One packed pass (causal rows + the span's rows redone without a mask up to the span's end) gives the hidden
+    states of the reference's procedure: causal text pass, bidirectional image pass, causal text pass, each
+    extending the cache; the rows of a span share one rotary position."""
+    from mstar_b200.models.bagel import IMG_PLACEHOLDER, VAE_PLACEHOLDER, VISION_END, VISION_START, image_span_positions
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=128,
+                        vocab_size=300, qkv_bias=True, qk_norm=True, dtype=torch.float32)
+    m = BagelMoT(cfg, 16).init_random(0)
+    ids = [5, 6, 7, VISION_START] + [VAE_PLACEHOLDER] * 4 + [VISION_END, 8, 9]
+    pos, spans = image_span_positions(ids)
+    assert pos.tolist() == [0, 1, 2, 3, 3, 3, 3, 3, 3, 4, 5] and spans == [(3, 9)]
+    assert image_span_positions([VISION_START, IMG_PLACEHOLDER, VISION_END, 4])[0].tolist() == [0, 0, 0, 1]
+    x = torch.randn(len(ids), 64, generator=torch.Generator().manual_seed(2))
+    is_gen = torch.tensor([t == VAE_PLACEHOLDER for t in ids])
+    cm = _cm()
+    ctx = cm.plan(["a"], [len(ids)], custom_positions=pos[None].to(torch.int32), group=2)
+    one = m.forward_mixed(x.clone(), is_gen, ctx, spans=cm.span_plan(ctx, [(0, 3, 9)], group=2))
+    causal_only = m.forward_mixed(x.clone(), is_gen, _cm().plan(["a"], [len(ids)], custom_positions=pos[None].to(torch.int32)))
+    cm2, parts = _cm(), []
+    for a, b, causal in ((0, 3, True), (3, 9, False), (9, 11, True)):
+        c = cm2.plan(["a"], [b - a], causal=causal, custom_positions=pos[None, a:b].to(torch.int32), group=2)
+        parts.append(m.forward_mixed(x[a:b].clone(), is_gen[a:b], c))
+        cm2.advance_seq_lens(c)
+    want = torch.cat(parts)
+    assert (one - want).abs().max().item() < 1e-4
+    assert (causal_only[:3] - want[:3]).abs().max().item() < 1e-5       # rows before the span never see it
+    assert (causal_only[3:8] - want[3:8]).abs().max().item() > 1e-3     # rows inside the span see its later rows
+    with pytest.raises(ValueError):
+        cm.span_plan(ctx, [(0, 9, 12)])
+
+
 @pytest.fixture(scope="module")
 def server():
     from mstar_b200.api_server.server import APIServer
