@@ -775,3 +775,69 @@ def pi05_checkpoint_keys(m, enc=None) -> dict[str, torch.Tensor]:
     out[_PI05_PALI + "language_model.norm.weight"] = sd["und.nf"]
     out[_PI05_EXPERT + "norm.dense.weight"], out[_PI05_EXPERT + "norm.dense.bias"] = sd["act.modf_w"], sd["act.modf_b"]
     return out
+
+
+# ------------------------------------------------------------------ Qwen3-Omni towers (Hugging Face names)
+@torch.no_grad()
+def load_qwen3_omni_audio(enc, src, prefix: str = "thinker.audio_tower.") -> dict:
+    """``OmniAudioEncoder`` from the ``thinker.audio_tower.*`` tensors of a Qwen3-Omni checkpoint: three Conv2d,
+    ``conv_out``, Whisper-named layers (separate q / k / v with biases), ``ln_post``, ``proj1`` / ``proj2``. Strict
+    over the prefix. Reference: mstar/model/qwen3_omni/qwen3_omni_model.py:1507-1539."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(enc, T, "Qwen3-Omni audio tower")
+    for n in ("conv2d1", "conv2d2", "conv2d3"):
+        st.write(n + ".weight", st.take(n + ".weight"))
+        st.write(n + ".bias", st.take(n + ".bias"))
+    st.write("conv_out_w", st.take("conv_out.weight"))
+    for i in range(len(enc.enc.layers)):
+        p, d = f"layers.{i}.", f"enc.layers.{i}."
+        ws = [st.take(f"{p}self_attn.{n}_proj.weight") for n in "qkv"]
+        bs = [st.take(f"{p}self_attn.{n}_proj.bias") for n in "qkv"]
+        if None not in ws and None not in bs:
+            st.write(d + "qkv_w", torch.cat(ws))
+            st.write(d + "qkv_b", torch.cat(bs))
+        st.write(d + "o_w", st.take(p + "self_attn.out_proj.weight"))
+        st.write(d + "o_b", st.take(p + "self_attn.out_proj.bias"))
+        for hf, ours in (("self_attn_layer_norm", "n1"), ("final_layer_norm", "n2")):
+            st.write(d + ours + "_w", st.take(p + hf + ".weight"))
+            st.write(d + ours + "_b", st.take(p + hf + ".bias"))
+        for n in ("fc1", "fc2"):
+            st.write(d + n + "_w", st.take(f"{p}{n}.weight"))
+            st.write(d + n + "_b", st.take(f"{p}{n}.bias"))
+    st.write("enc.fn_w", st.take("ln_post.weight"))
+    st.write("enc.fn_b", st.take("ln_post.bias"))
+    for n in ("proj1", "proj2"):
+        st.write(n + "_w", st.take(n + ".weight"))
+        st.write(n + "_b", st.take(n + ".bias"))
+    return st.done()
+
+
+def _omni_merger(st: _Strict, src: str, dst: str) -> None:
+    st.write(dst + "norm_w", st.take(src + "ln_q.weight"))
+    st.write(dst + "norm_b", st.take(src + "ln_q.bias"))
+    for hf, ours in (("mlp.0", "fc1"), ("mlp.2", "fc2")):
+        st.write(f"{dst}{ours}_w", st.take(f"{src}{hf}.weight"))
+        st.write(f"{dst}{ours}_b", st.take(f"{src}{hf}.bias"))
+
+
+@torch.no_grad()
+def load_qwen3_omni_vision(enc, src, prefix: str = "thinker.visual.") -> dict:
+    """``OmniVisionEncoder`` from the ``thinker.visual.*`` tensors of a Qwen3-Omni checkpoint: Conv3d patch embedding
+    (flattened to a GEMM weight), the learned position table, blocks with a fused ``attn.qkv``, ``merger`` and the
+    deepstack ``merger_list``. Strict over the prefix. Reference: mstar/model/qwen3_omni/qwen3_omni_model.py:1546-1580."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(enc, T, "Qwen3-Omni vision tower")
+    w = st.take("patch_embed.proj.weight")
+    st.write("patch_w", None if w is None else w.reshape(w.shape[0], -1))
+    st.write("patch_b", st.take("patch_embed.proj.bias"))
+    st.write("pos_table", st.take("pos_embed.weight"))
+    for i in range(len(enc.enc.layers)):
+        p, d = f"blocks.{i}.", f"enc.layers.{i}."
+        for hf, ours in (("norm1", "n1"), ("norm2", "n2"), ("attn.qkv", "qkv"), ("attn.proj", "o"),
+                         ("mlp.linear_fc1", "fc1"), ("mlp.linear_fc2", "fc2")):
+            st.write(f"{d}{ours}_w", st.take(f"{p}{hf}.weight"))
+            st.write(f"{d}{ours}_b", st.take(f"{p}{hf}.bias"))
+    _omni_merger(st, "merger.", "merger.")
+    for k in range(len(enc.deep_mergers)):
+        _omni_merger(st, f"merger_list.{k}.", f"deep_mergers.{k}.")
+    return st.done()

@@ -421,8 +421,18 @@ class DecoderLM(nn.Module):
             return self.tpf.embed(input_ids.reshape(-1))
         return ew.embed(input_ids.reshape(-1), self.embed_tokens)
 
-    def forward_hidden(self, x: torch.Tensor, ctx: BatchContext) -> torch.Tensor:
-        """x: [T, H] input embeddings -> final-normed hidden states [T, H]."""
+    def forward_hidden(self, x: torch.Tensor, ctx: BatchContext, deepstack=None) -> torch.Tensor:
+        """x: [T, H] input embeddings -> final-normed hidden states [T, H]. ``deepstack`` = (int64 rows, [features
+        [len(rows), H] per tapped encoder layer]): features k are added to the output of decoder layer k at those
+        rows (the vision tower's intermediate taps of Qwen3-Omni / Qwen3-VL prompts)."""
+        if deepstack is not None:
+            rows, feats = deepstack
+            residual = None
+            for i, layer in enumerate(self.layers):
+                x, residual = layer(x, residual, ctx, self.rope, next_w=self._weight_after(i))
+                if i < len(feats):      # hidden = residual + x: adding to x adds to the hidden state
+                    x = x.index_add(0, rows, feats[i].to(x.dtype))
+            return norm_ops.norm(x, self.norm, self.cfg.rms_eps, residual=residual)[0]
         if self.tpf is not None and x.shape[0] <= self.tpf.max_tokens:
             x = x.reshape(-1, x.shape[-1])
             residual = self.tpf.residual_rows(x)
@@ -459,9 +469,9 @@ class DecoderLM(nn.Module):
 
     def forward(self, ctx: BatchContext, input_ids: torch.Tensor | None = None,
                 inputs_embeds: torch.Tensor | None = None, all_logits: bool = False,
-                return_hidden: bool = False):
+                return_hidden: bool = False, deepstack=None):
         x = inputs_embeds if inputs_embeds is not None else self.embed(input_ids)
-        h = self.forward_hidden(x, ctx)
+        h = self.forward_hidden(x, ctx, deepstack=deepstack)
         if return_hidden and not self.cfg.has_lm_head:
             return h
         rows = h if all_logits else h.index_select(0, ctx.logit_rows)

@@ -34,7 +34,7 @@ class EncoderConfig:
     head_dim: int = 64
     ffn_dim: int = 4096
     norm: str = "layernorm"            # layernorm | rmsnorm
-    act: str = "gelu"                  # gelu | gated_gelu | silu_gated
+    act: str = "gelu"                  # gelu (tanh form, fused) | gelu_erf (exact) | gated_gelu | silu_gated
     qkv_bias: bool = True
     eps: float = 1e-6
     dtype: torch.dtype = torch.bfloat16
@@ -81,6 +81,8 @@ class EncoderLayer(nn.Module):
         h = self._norm(x, self.n2_w, self.n2_b)
         if c.act == "gelu":
             h = gemm.linear(h, self.fc1_w, bias=self.fc1_b, epilogue=gemm.EPILOGUE_GELU)
+        elif c.act == "gelu_erf":
+            h = F.gelu(gemm.linear(h, self.fc1_w, bias=self.fc1_b).float()).to(x.dtype)
         elif c.act == "silu_gated":
             h = gemm.linear(h, self.fc1_w, epilogue=gemm.EPILOGUE_SWIGLU)
         else:   # gated gelu (T5 v1.1): gelu(gate) * up, rows interleaved

@@ -112,9 +112,13 @@ class MultimodalDecoderSubmodule(DecoderSubmodule):
     """
 
     def __init__(self, lm, device, placeholders: dict[str, int], eos_ids=(), loop_name="decode_loop",
-                 token_edge="new_token", position_fn=None, emit_hidden: str | None = None):
+                 token_edge="new_token", position_fn=None, emit_hidden: str | None = None,
+                 deepstack: dict[str, int] | None = None):
+        """``deepstack``: edge name -> number of tapped encoder layers whose features ride in the same rows, after
+        the main features (row width (1 + taps) x hidden); they are added to the first decoder layers' outputs."""
         super().__init__(lm, device, eos_ids=eos_ids, loop_name=loop_name, token_edge=token_edge)
         self.placeholders, self.position_fn, self.emit_hidden = dict(placeholders), position_fn, emit_hidden
+        self.deepstack = dict(deepstack or {})
 
     def prepare_inputs(self, graph_walk, fwd_info, inputs):
         ni = super().prepare_inputs(graph_walk, fwd_info, inputs)
@@ -135,20 +139,30 @@ class MultimodalDecoderSubmodule(DecoderSubmodule):
     def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
         ids = torch.cat([ni.input_ids.reshape(-1) for ni in inputs]).to(self.device)
         x = self.lm.embed(ids)
-        off = 0
+        H, off = x.shape[-1], 0
+        deep_rows, deep_feats = [], []
         for ni in inputs:
             n = ni.input_ids.numel()
             for edge, pid in self.placeholders.items():
                 feats = ni.tensor_inputs.get(edge)
                 if not feats:
                     continue
-                f = torch.cat([t.reshape(-1, x.shape[-1]) for t in feats]).to(self.device, x.dtype)
+                taps = self.deepstack.get(edge, 0)
+                f = torch.cat([t.reshape(-1, H * (1 + taps)) for t in feats]).to(self.device, x.dtype)
                 rows = (ids[off:off + n] == pid).nonzero().reshape(-1) + off
                 if rows.numel() != f.shape[0]:
                     raise ValueError(f"{edge}: {f.shape[0]} feature rows for {rows.numel()} placeholder tokens")
-                x[rows] = f
+                x[rows] = f[:, :H]
+                if taps:
+                    deep_rows.append(rows)
+                    deep_feats.append(f[:, H:].reshape(-1, taps, H))
             off += n
-        out = self.lm(engine_inputs.batch_context, inputs_embeds=x, return_hidden=self.emit_hidden is not None)
+        deep = None
+        if deep_rows:
+            d = torch.cat(deep_feats)
+            deep = (torch.cat(deep_rows), [d[:, k].contiguous() for k in range(d.shape[1])])
+        out = self.lm(engine_inputs.batch_context, inputs_embeds=x, return_hidden=self.emit_hidden is not None,
+                      deepstack=deep)
         if self.emit_hidden is None:
             return {BATCHED_LOGITS: out}
         logits, hidden = out

@@ -28,7 +28,8 @@ from ..streaming import (Connection, FixedChunkPolicy, LeftContextChunkPolicy, P
 from .base import small_scale, EngineType, ForwardPassArgs, Model
 from .codec import Code2Wav
 from .decoder import DecoderConfig, DecoderLM
-from .encoders import AudioEncoder, EncoderConfig, VisionEncoder, log_mel_spectrogram
+from .encoders import EncoderConfig, log_mel_spectrogram
+from .qwen3_omni_encoders import OmniAudioEncoder, OmniVisionEncoder, audio_output_length
 from .llm_common import MultimodalDecoderSubmodule, expand_placeholders, lm_walks
 from .qwen3_tts import CodecChunkSubmodule, talker_walks
 from .submodule_base import NodeSubmodule
@@ -65,7 +66,7 @@ def talker_config(dtype, small=False, expert_parallel=False) -> DecoderConfig:
 
 
 class AudioFeatureSubmodule(NodeSubmodule):
-    def __init__(self, enc: AudioEncoder, device, n_mels: int):
+    def __init__(self, enc: OmniAudioEncoder, device, n_mels: int):
         super().__init__(device, enc.c.dtype)
         self.enc, self.n_mels = enc, n_mels
 
@@ -77,18 +78,22 @@ class AudioFeatureSubmodule(NodeSubmodule):
 
 
 class VisionFeatureSubmodule(NodeSubmodule):
-    def __init__(self, enc: VisionEncoder, device):
+    """Rows of ``image_features``: the merged patch features followed by the features of every tapped layer (the
+    thinker adds those to its first layers' outputs at the image rows)."""
+
+    def __init__(self, enc: OmniVisionEncoder, device):
         super().__init__(device, enc.c.dtype)
         self.enc = enc
 
     def forward(self, graph_walk, engine_inputs, ni, **kw):
         imgs = [t.to(self.device) for t in ni.tensor_inputs.get("image", []) + ni.tensor_inputs.get("video", [])]
-        feats, _, _ = self.enc(imgs)
-        return {"image_features": feats}
+        feats, deep, _, _ = self.enc(imgs)
+        return {"image_features": torch.cat([feats] + deep, dim=-1) if deep else feats}
 
 
 def audio_rows(n_samples: int) -> int:
-    return (n_samples // 160 + 1) // 2 if n_samples >= 160 else 1
+    """Rows the audio tower gives for a 16 kHz waveform (one mel frame per 160 samples)."""
+    return max(1, audio_output_length(n_samples // 160))
 
 
 def mrope_positions(ids: torch.Tensor, grids: list[tuple[int, int, int]], image_token: int):
@@ -136,15 +141,19 @@ class Qwen3OmniModel(Model):
             self.pred_cfg = DecoderConfig(hidden_size=32 * k, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16 * k,
                                           intermediate_size=64 * k, vocab_size=8, qk_norm=True, dtype=dt)
             self.n_sub, self.codebook, self.codec_eos = 3, 64, 63
-            self.a_cfg, self.n_mels = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 16
-            self.v_cfg, self.patch, self.merge = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4, 2
+            self.a_cfg, self.n_mels = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, act="gelu_erf", eps=1e-5, dtype=dt), 16
+            self.v_cfg, self.patch, self.merge = EncoderConfig(32 * k, 2, 2, 16 * k, 64 * k, dtype=dt), 4, 2
+            self.a_kw = dict(conv_channels=8, max_positions=64)
+            self.v_kw = dict(pos_grid=6, deepstack=(0, 1))
             self.chunk, self.left = 6, 2
         else:
             self.pred_cfg = DecoderConfig(hidden_size=1024, num_layers=5, num_heads=16, num_kv_heads=8, head_dim=64,
                                           intermediate_size=3072, vocab_size=8, qk_norm=True, dtype=dt)
             self.n_sub, self.codebook, self.codec_eos = 15, 2048, 2150
-            self.a_cfg, self.n_mels = EncoderConfig(1280, 32, 20, 64, 5120, dtype=dt), 128
+            self.a_cfg, self.n_mels = EncoderConfig(1280, 32, 20, 64, 5120, act="gelu_erf", eps=1e-5, dtype=dt), 128
             self.v_cfg, self.patch, self.merge = EncoderConfig(1152, 27, 16, 72, 4304, dtype=dt), 16, 2
+            self.a_kw = dict(conv_channels=480, max_positions=1500)
+            self.v_kw = dict(pos_grid=48, deepstack=(8, 16, 24))
             self.chunk, self.left = 300, 25
         self.max_num_pages = max_num_pages or (64 if small else 2048)
 
@@ -209,12 +218,18 @@ class Qwen3OmniModel(Model):
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         load = not (self.skip_weight_loading or self.model_dir is None)
         if node_name == "audio_encoder":
-            enc = AudioEncoder(self.a_cfg, n_mels=self.n_mels, max_frames=3000, out_dim=self.t_cfg.hidden_size,
-                               device=device).init_random(0)
+            enc = OmniAudioEncoder(self.a_cfg, n_mels=self.n_mels, out_dim=self.t_cfg.hidden_size, n_window=50,
+                                   n_window_infer=800, device=device, **self.a_kw).init_random(0)
+            if load:
+                from .checkpoints import load_qwen3_omni_audio
+                load_qwen3_omni_audio(enc, self.model_dir)
             return AudioFeatureSubmodule(enc, device, self.n_mels)
         if node_name == "vision_encoder":
-            enc = VisionEncoder(self.v_cfg, patch=self.patch, temporal_patch=2, pos="rope2d", out_dim=self.t_cfg.hidden_size,
-                                merge=self.merge, device=device).init_random(0)
+            enc = OmniVisionEncoder(self.v_cfg, patch=self.patch, temporal_patch=2, merge=self.merge,
+                                    out_dim=self.t_cfg.hidden_size, device=device, **self.v_kw).init_random(0)
+            if load:
+                from .checkpoints import load_qwen3_omni_vision
+                load_qwen3_omni_vision(enc, self.model_dir)
             return VisionFeatureSubmodule(enc, device)
         if node_name == "Thinker":
             lm = DecoderLM(self.t_cfg, tp=tp_group, device=device)
@@ -227,7 +242,8 @@ class Qwen3OmniModel(Model):
                 lm.quantize_moe_fp8()
             return MultimodalDecoderSubmodule(lm, device, {"audio_features": AUDIO_TOKEN, "image_features": IMAGE_TOKEN},
                                               eos_ids=(IM_END, ENDOFTEXT), loop_name="thinker_loop",
-                                              position_fn=self._position_fn, emit_hidden="thinker_out")
+                                              position_fn=self._position_fn, emit_hidden="thinker_out",
+                                              deepstack={"image_features": len(self.v_kw["deepstack"])})
         if node_name == "Talker":
             lm = DecoderLM(self.k_cfg, tp=tp_group, device=device)
             if load:
