@@ -841,3 +841,56 @@ def load_qwen3_omni_vision(enc, src, prefix: str = "thinker.visual.") -> dict:
     for k in range(len(enc.deep_mergers)):
         _omni_merger(st, f"merger_list.{k}.", f"deep_mergers.{k}.")
     return st.done()
+
+
+@torch.no_grad()
+def load_qwen3_omni_code2wav(m, src, prefix: str = "code2wav.") -> dict:
+    """``OmniCode2Wav`` from the ``code2wav.*`` tensors of a Qwen3-Omni checkpoint: ``code_embedding``,
+    ``pre_transformer`` (Hugging Face decoder names plus the two ``*_layer_scale.scale`` vectors),
+    ``upsample.N.{0,1}`` and the ``decoder.N`` list (input convolution, up blocks ``block.0 … block.4``, final
+    activation and convolution). Strict over the prefix.
+    Reference module: mstar/model/qwen3_omni/components/code2wav.py."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(m, T, "Qwen3-Omni code2wav")
+
+    def same(src_, dst, names):
+        for n in names:
+            st.write(f"{dst}.{n}", st.take(f"{src_}.{n}"))
+    wb, ab = ("weight", "bias"), ("alpha", "beta")
+    st.write("code_embedding", st.take("code_embedding.weight"))
+    for i in range(len(m.pre.layers)):
+        p, d = f"pre_transformer.layers.{i}.", f"pre.layers.{i}."
+        ws = [st.take(f"{p}self_attn.{n}_proj.weight") for n in "qkv"]
+        if None not in ws:
+            st.write(d + "qkv", torch.cat(ws))
+        st.write(d + "o", st.take(p + "self_attn.o_proj.weight"))
+        g, u = st.take(p + "mlp.gate_proj.weight"), st.take(p + "mlp.up_proj.weight")
+        if g is not None and u is not None:
+            st.write(d + "gate_up", torch.cat([g, u]))
+        st.write(d + "down", st.take(p + "mlp.down_proj.weight"))
+        st.write(d + "n1", st.take(p + "input_layernorm.weight"))
+        st.write(d + "n2", st.take(p + "post_attention_layernorm.weight"))
+        st.write(d + "s1", st.take(p + "self_attn_layer_scale.scale"))
+        st.write(d + "s2", st.take(p + "mlp_layer_scale.scale"))
+    st.write("pre.norm", st.take("pre_transformer.norm.weight"))
+    for i in range(len(m.upsample)):
+        same(f"upsample.{i}.0.conv", f"upsample.{i}.0.conv", wb)
+        same(f"upsample.{i}.1.dwconv.conv", f"upsample.{i}.1.dwconv.conv", wb)
+        for n in ("norm", "pwconv1", "pwconv2"):
+            same(f"upsample.{i}.1.{n}", f"upsample.{i}.1.{n}", wb)
+        st.write(f"upsample.{i}.1.gamma", st.take(f"upsample.{i}.1.gamma"))
+    same("decoder.0.conv", "inp.conv", wb)
+    nb = len(m.blocks)
+    for i in range(nb):
+        p, d = f"decoder.{i + 1}.block.", f"blocks.{i}."
+        same(p + "0", d + "act", ab)
+        same(p + "1.conv", d + "up.conv", wb)
+        for r in range(3):
+            q, e = f"{p}{r + 2}.", f"{d}res.{r}."
+            same(q + "act1", e + "act1", ab)
+            same(q + "conv1.conv", e + "conv1.conv", wb)
+            same(q + "act2", e + "act2", ab)
+            same(q + "conv2.conv", e + "conv2.conv", wb)
+    same(f"decoder.{nb + 1}", "out_act", ab)
+    same(f"decoder.{nb + 2}.conv", "out.conv", wb)
+    return st.done()

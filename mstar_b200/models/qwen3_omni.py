@@ -26,7 +26,7 @@ from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, GraphNode, 
 from ..streaming import (Connection, FixedChunkPolicy, LeftContextChunkPolicy, PartitionDefinition, PartitionTopology,
                          StreamingGraphEdge)
 from .base import small_scale, EngineType, ForwardPassArgs, Model
-from .codec import Code2Wav
+from .code2wav import OmniCode2Wav
 from .decoder import DecoderConfig, DecoderLM
 from .encoders import EncoderConfig, log_mel_spectrogram
 from .qwen3_omni_encoders import OmniAudioEncoder, OmniVisionEncoder, audio_output_length
@@ -257,9 +257,15 @@ class Qwen3OmniModel(Model):
             return TalkerSubmodule(lm, pred, device, num_slots=64, codec_eos=self.codec_eos, cond_edge="thinker_out",
                                    cond_is_ids=False, cond_dim=self.t_cfg.hidden_size, loop_name="talker_loop")
         if node_name == "Code2Wav":
-            kw = (dict(n_codebooks=self.n_sub + 1, codebook_size=self.codebook, dim=16, rates=(2, 2), channels=32)
-                  if self.small else dict(n_codebooks=16, codebook_size=2048, dim=512, rates=(8, 5, 4, 3, 4)))
-            return CodecChunkSubmodule(Code2Wav(**kw).to(device).eval(), device, "codec_frames", self.left, "code2wav_loop")
+            k = small_scale()
+            kw = (dict(n_codebooks=self.n_sub + 1, codebook_size=self.codebook, hidden=32 * k, layers=1, heads=2,
+                       head_dim=16 * k, ffn=64 * k, window=4, upsampling_ratios=(2,), upsample_rates=(2,), decoder_dim=16 * k)
+                  if self.small else {})                   # the published shapes are the defaults
+            dec = OmniCode2Wav(dtype=self.dtype, device=device, **kw).init_random(5)
+            if load:
+                from .checkpoints import load_qwen3_omni_code2wav
+                load_qwen3_omni_code2wav(dec, self.model_dir)
+            return CodecChunkSubmodule(dec.eval(), device, "codec_frames", self.left, "code2wav_loop")
         raise KeyError(node_name)
 
     # ---- request life cycle ----

@@ -159,3 +159,41 @@ def test_thinker_decoder_matches_hugging_face_with_interleaved_mrope_and_deepsta
     assert (outs[0] - want).abs().max().item() < 1e-4
     assert (outs[1] - plain).abs().max().item() < 1e-4
     assert (want - plain).abs().max().item() > 1e-2
+
+
+def test_code2wav_matches_hugging_face_and_chunks_continue_each_other():
+    from mstar_b200.models.code2wav import OmniCode2Wav
+    torch.manual_seed(0)
+    hc = hf_cfg.Qwen3OmniMoeCode2WavConfig(codebook_size=32, hidden_size=32, num_attention_heads=2, num_key_value_heads=2,
+                                           sliding_window=5, intermediate_size=48, num_hidden_layers=2, num_quantizers=4,
+                                           upsample_rates=[3, 2], upsampling_ratios=[2, 2], decoder_dim=16,
+                                           max_position_embeddings=256)
+    hf = hf_omni.Qwen3OmniMoeCode2Wav(hc).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.08)
+        if "norm" in n and n.endswith("weight"):
+            p.data.add_(1.0)
+    ours = OmniCode2Wav(n_codebooks=4, codebook_size=32, hidden=32, layers=2, heads=2, head_dim=16, ffn=48, window=5,
+                        upsampling_ratios=(2, 2), upsample_rates=(3, 2), decoder_dim=16).init_random(0)
+    sd = {"code2wav." + k: v.clone() for k, v in hf.state_dict().items()}
+    assert ck.load_qwen3_omni_code2wav(ours, sd)["loaded"] == len(list(ours.parameters()))
+    assert ours.pre.inv_freq.dtype == torch.float32
+    codes = torch.randint(0, 32, (2, 4, 13))                  # 13 frames: longer than the attention window of 5
+    with torch.no_grad():
+        want, got = hf(codes)[:, 0], ours(codes)
+        assert want.abs().max().item() < 1.0                  # not saturated: the comparison sees the whole stack
+        assert got.shape == want.shape and (got - want).abs().max().item() < 1e-5
+        whole = hf.chunked_decode(codes, chunk_size=6, left_context_size=2)[:, 0]
+        parts, start = [], 0
+        while start < 13:
+            ctx = 2 if start - 2 > 0 else start
+            parts.append(ours(codes[..., start - ctx:min(start + 6, 13)])[:, ctx * ours.hop:])
+            start += 6
+        assert (torch.cat(parts, dim=-1) - whole).abs().max().item() < 1e-5
+    for mutate in (lambda d: d.pop("code2wav.decoder.2.block.3.act2.beta"),
+                   lambda d: d.update({"code2wav.pre_transformer.layers.0.self_attn.q_norm.weight": torch.ones(16)}),
+                   lambda d: d.update({"code2wav.upsample.1.1.gamma": torch.zeros(31)})):
+        bad = dict(sd)
+        mutate(bad)
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_qwen3_omni_code2wav(ours, bad)
