@@ -45,12 +45,36 @@ class DecoderBlock(nn.Module):
         self.noise = nn.Conv1d(cout, cout, 1, bias=False) if noise else None
         self.res = nn.Sequential(ResidualUnit(cout, 1), ResidualUnit(cout, 3), ResidualUnit(cout, 9))
 
+    HALO = 3 * (1 + 3 + 9)          # inputs that the three residual units (kernel 7, dilations 1, 3, 9) reach per side
+
     def forward(self, x, noise_gen: torch.Generator | None = None):
         x = self.up(x)
         if self.noise is not None:
             n = torch.randn((x.shape[0], 1, x.shape[2]), device=x.device, dtype=x.dtype, generator=noise_gen)
             x = x + n * self.noise(x)
         return self.res(x)
+
+    def input_range(self, a: int, b: int, length_in: int) -> tuple[int, int, int, int]:
+        """For output positions [a, b): the range [ra, rb) that the residual units must see (their halo, clipped to
+        the signal) and the input range [ia, ib) whose transposed-convolution outputs cover it."""
+        conv = self.up[1]
+        r, p, k = conv.stride[0], conv.padding[0], conv.kernel_size[0]
+        ra, rb = max(0, a - self.HALO), min(length_in * r, b + self.HALO)
+        ia = max(0, -((-(ra + p - k + 1)) // r))                # ceil((ra + p - k + 1) / r)
+        ib = min(length_in, (rb - 1 + p) // r + 1)
+        return ra, rb, ia, ib
+
+    def forward_range(self, x, x_off: int, length_in: int, a: int, b: int, noise_gen=None):
+        """``x`` holds input positions [x_off, x_off + x.shape[-1]) of a signal of ``length_in`` positions; returns the
+        block's output on [ra, rb) ⊇ [a, b) — exact on [a, b), the halo towards a cut edge is not — and ra."""
+        ra, rb, ia, ib = self.input_range(a, b, length_in)
+        r = self.up[1].stride[0]
+        y = self.up(x[..., ia - x_off:ib - x_off])                 # output positions [ia * r, ib * r)
+        y = y[..., ra - ia * r:rb - ia * r]
+        if self.noise is not None:
+            n = torch.randn((y.shape[0], 1, y.shape[2]), device=y.device, dtype=y.dtype, generator=noise_gen)
+            y = y + n * self.noise(y)
+        return self.res(y), ra
 
 
 class SnacDecoder(nn.Module):
@@ -80,11 +104,29 @@ class SnacDecoder(nn.Module):
             z = z + e.repeat_interleave(s, dim=-1)
         return z
 
-    def forward(self, codes: list[torch.Tensor], noise_gen=None) -> torch.Tensor:
+    def forward(self, codes: list[torch.Tensor], noise_gen=None, keep: tuple[int, int] | None = None) -> torch.Tensor:
+        """Waveform [B, T_fine * hop], or with ``keep`` = (lo, hi) only its samples [lo, hi): every stage then computes
+        just the positions that those samples depend on (their receptive field), which for the middle frame of a
+        4-frame streaming window is about a quarter of the two finest stages. The kept samples are the same numbers
+        as the slice of the full decode (noise aside)."""
         x = self.inp(self.latent(codes))
+        if keep is None:
+            for b in self.blocks:
+                x = b(x, noise_gen)
+            return self.out(x)[:, 0]
+        lens = [x.shape[-1]]
         for b in self.blocks:
-            x = b(x, noise_gen)
-        return self.out(x)[:, 0]
+            lens.append(lens[-1] * b.up[1].stride[0])
+        lo, hi = max(0, keep[0]), min(lens[-1], keep[1])
+        need = [(max(0, lo - 3), min(lens[-1], hi + 3))]           # the output convolution has kernel 7
+        for i in reversed(range(len(self.blocks))):
+            _, _, ia, ib = self.blocks[i].input_range(*need[0], lens[i])
+            need.insert(0, (ia, ib))
+        off = 0
+        for i, b in enumerate(self.blocks):
+            x, off = b.forward_range(x, off, lens[i], *need[i + 1], noise_gen)
+        y = self.out(x)[:, 0]
+        return y[..., lo - off:hi - off]
 
 
 def orpheus_tokens_to_codes(tokens: torch.Tensor, base_id: int, codebook_size: int = 4096) -> list[torch.Tensor]:

@@ -10,6 +10,8 @@ Reference counterparts: mstar/model/orpheus/orpheus_model.py (walks :111-167, pa
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..api_server.media_io import float_to_pcm16
@@ -63,6 +65,8 @@ class SnacSubmodule(NodeSubmodule):
 
         self.base_id = base_id
         self.gen = None
+        # MSTAR_SNAC_FULL_WINDOW=1 decodes all four frames of a streaming window and slices the second one out
+        self.middle_only = os.environ.get("MSTAR_SNAC_FULL_WINDOW", "0") != "1"
 
     def get_stateless_flavor(self):
         return "audio_codec"
@@ -76,17 +80,18 @@ class SnacSubmodule(NodeSubmodule):
         t = torch.cat([x.reshape(-1) for x in toks]).cpu() if toks else torch.zeros(0, dtype=torch.int64)
         return t[:(t.numel() // 7) * 7]
 
-    def _decode(self, tokens: torch.Tensor, runner) -> torch.Tensor:
-        """tokens [B, n] (n a multiple of 7, host) -> waveforms [B, n / 7 * 2048] on the device; replayed from a CUDA
-        graph per shape. On a GPU the result is a view of the graph's static output: copy it out on the same stream."""
+    def _decode(self, tokens: torch.Tensor, runner, keep: tuple[int, int] | None = None) -> torch.Tensor:
+        """tokens [B, n] (n a multiple of 7, host) -> waveforms [B, n / 7 * 2048] on the device (with ``keep`` only
+        those samples, computed from their receptive field alone); replayed from a CUDA graph per shape. On a GPU the
+        result is a view of the graph's static output: copy it out on the same stream."""
         def fn(tk):
             if not tk.is_cuda:
-                return self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+                return self.dec(orpheus_tokens_to_codes(tk, self.base_id), keep=keep)
             if self.compute_dtype != torch.float32:
                 with torch.autocast("cuda", dtype=self.compute_dtype):
-                    wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id)).float()
+                    wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id), keep=keep).float()
             else:
-                wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id))
+                wav = self.dec(orpheus_tokens_to_codes(tk, self.base_id), keep=keep)
             # 16-bit PCM is what leaves the server: quantise inside the captured graph, so the read-back is half
             # the bytes and the API process only forwards them
             return (wav.float().clamp(-1, 1) * 32767.0).round().to(torch.int16)
@@ -101,7 +106,7 @@ class SnacSubmodule(NodeSubmodule):
                     stage[B:] = stage[0]
                 tk = stage.to(self.device, non_blocking=True)
                 io_counters.add_h2d(stage.numel() * 8)
-                return runner.run(("snac", tuple(tk.shape)), fn, [tk])[:B]
+                return runner.run(("snac", tuple(tk.shape), keep), fn, [tk])[:B]
             return fn(tokens.to(self.device))
 
     def _pinned(self, key, shape, dtype) -> torch.Tensor:
@@ -127,14 +132,17 @@ class SnacSubmodule(NodeSubmodule):
         runner = (engine_inputs.preallocated_buffers or {}).get("graph_runner")
         toks = [self._tokens(ni) for ni in inputs]
         outs: list[dict | None] = [None] * len(inputs)
-        by_len: dict[int, list[int]] = {}
+        by_len: dict[tuple[int, bool], list[int]] = {}
         for i, t in enumerate(toks):
+            final = bool(inputs[i].kwargs.get("final_chunk"))
             if t.numel() == 0:
-                outs[i] = {"audio": torch.zeros(0), "final": bool(inputs[i].kwargs.get("final_chunk"))}
+                outs[i] = {"audio": torch.zeros(0), "final": final}
             else:
-                by_len.setdefault(t.numel(), []).append(i)
-        for n, idx in by_len.items():
-            wav = self._decode(torch.stack([toks[i] for i in idx]), runner)
+                # steady state: a full 4-frame window yields its second frame, and only that frame is decoded (the
+                # positions its samples depend on); shorter (first / flush) windows yield everything
+                by_len.setdefault((t.numel(), self.middle_only and t.numel() == 28 and not final), []).append(i)
+        for (n, middle), idx in by_len.items():
+            wav = self._decode(torch.stack([toks[i] for i in idx]), runner, keep=(2048, 4096) if middle else None)
             if wav.dtype != torch.int16:
                 wav = wav.float()
             if wav.is_cuda:
@@ -147,8 +155,7 @@ class SnacSubmodule(NodeSubmodule):
             hb = _HostBatch(host, len(idx))
             for row, i in enumerate(idx):
                 final = bool(inputs[i].kwargs.get("final_chunk"))
-                # steady state: a full 4-frame window yields its second frame; shorter (first / flush) windows all
-                lo, hi = (2048, 4096) if n == 28 and not final else (0, host.shape[1])
+                lo, hi = (2048, 4096) if n == 28 and not final and not middle else (0, host.shape[1])
                 outs[i] = {"audio": _HostRows(hb, row, lo, hi), "final": final}
         return outs
 

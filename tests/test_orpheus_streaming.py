@@ -73,3 +73,33 @@ def test_colocated_partitions_share_one_worker():
         assert sizes.count(4096) >= 5 and sum(sizes) >= 4096 * 8, sizes
     finally:
         s.shutdown()
+
+
+def test_middle_frame_decode_equals_the_slice_of_the_full_window():
+    """A streaming window of four frames yields its second frame; decoding only the positions that frame depends on
+    (receptive field of the residual stacks and transposed convolutions, stage by stage) gives the same samples as
+    slicing them out of the full decode — also at the signal's edges and for odd upsampling rates."""
+    import torch
+    from mstar_b200.models.codec import SnacDecoder
+    torch.manual_seed(0)
+    for kw in (dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)), dict(latent_dim=32, channels=32, rates=(3, 5, 2))):
+        d = SnacDecoder(noise=False, **kw).eval()
+        for p in d.parameters():
+            p.data.normal_(0, 0.04)
+        codes = [torch.randint(0, 4096, (2, 4)), torch.randint(0, 4096, (2, 8)), torch.randint(0, 4096, (2, 16))]
+        with torch.no_grad():
+            full = d(codes)
+            hop = d.hop
+            assert full.shape[1] == 16 * hop and full.abs().max().item() > 1e-3
+            for lo, hi in ((4 * hop, 8 * hop), (0, 4 * hop), (12 * hop, 16 * hop), (5, 77)):
+                part = d(codes, keep=(lo, hi))
+                assert part.shape == (2, hi - lo)
+                assert (part - full[:, lo:hi]).abs().max().item() < 1e-6
+        # at the codec's own rates the finest stage sees about a quarter of the window
+        need = [(max(0, 4 * hop - 3), 8 * hop + 3)]
+        lens = [16]
+        for b in d.blocks:
+            lens.append(lens[-1] * b.up[1].stride[0])
+        ra, rb, _, _ = d.blocks[-1].input_range(*need[0], lens[-2])
+        if hop == 512:
+            assert (rb - ra) < 0.3 * lens[-1]
