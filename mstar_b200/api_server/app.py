@@ -34,12 +34,16 @@ class ChunkStream(Response):
     Under a transport that offers the ``mstar.direct_stream`` ASGI extension (the C++ frontend's bridge) the pieces
     are handed to the transport on the thread that received them from the workers: between the reply's start and
     its end the event loop does nothing for this stream. Any other ASGI server gets an ordinary async body iterator.
+    ``raw(chunk)`` -> (prefix, data, suffix) or None, when given, states a chunk as prefix + base64(data) + suffix: a
+    transport whose sink has a ``b64`` method then encodes the binary field itself and may send the chunks of many
+    requests as one frame.
     """
 
-    def __init__(self, server: APIServer, rid: str, fmt, media_type: str, head=(), tail=()):
+    def __init__(self, server: APIServer, rid: str, fmt, media_type: str, head=(), tail=(), raw=None):
         super().__init__(content=None, media_type=media_type)
         self.raw_headers = [h for h in self.raw_headers if h[0] != b"content-length"]
         self.server, self.rid, self.fmt, self.head, self.tail = server, rid, fmt, list(head), tail
+        self.raw = raw
 
     async def _body(self):
         for piece in self.head:
@@ -66,14 +70,21 @@ class ChunkStream(Response):
             direct(piece)
         state = {"open": True}
 
+        b64 = getattr(direct, "b64", None) if self.raw is not None else None
+
         def sink(c):                    # runs on the server's result thread
             if not state["open"]:
                 return
             last = True
             if c.modality != "done":
-                pieces, last = self.fmt(c)
-                for piece in pieces:
-                    direct(piece)
+                parts = self.raw(c) if b64 is not None else None
+                if parts is not None:   # the transport encodes the binary field and sends a batch's chunks together
+                    b64(*parts)
+                    last = False
+                else:
+                    pieces, last = self.fmt(c)
+                    for piece in pieces:
+                        direct(piece)
                 last = last or c.final
             if last:
                 state["open"] = False
@@ -81,6 +92,7 @@ class ChunkStream(Response):
                     direct(piece)
                 loop.call_soon_threadsafe(done.set)
         self.server.attach_sink(self.rid, sink)
+        getattr(direct, "flush", lambda: None)()      # chunks that were queued before the sink took over
         try:
             await done.wait()
         except asyncio.CancelledError:  # the client went away: stop generating for it
@@ -94,6 +106,7 @@ class ChunkStream(Response):
 
 def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
     app = FastAPI(title="mstar-b200")
+    app.state.mstar_server = server
     app.add_middleware(CORSMiddleware, allow_origins=["*"], allow_methods=["*"], allow_headers=["*"])
     model_name = server.deployment.cfg["model"]
     adapter = get_adapter(model_name)
@@ -159,14 +172,19 @@ def create_app(server: APIServer, allow_remote_media: bool = False) -> FastAPI:
                 raise HTTPException(400, f"unknown modality {m!r}")
         rid = server.submit_request(text, blobs, in_mods, out_mods, kw, request_id)
         if streaming:
-            def fmt(c):
-                # base64 needs no JSON escaping: the line is assembled from bytes instead of serialising a 5 KB string
+            def raw(c):
+                # a line is prefix + base64(data) + suffix; base64 needs no JSON escaping, so the line is assembled
+                # from bytes instead of serialising a 5 KB string
                 tail = b'","metadata":' + json.dumps(c.metadata).encode()
                 if c.error_status:
                     tail += b',"error_status":' + json.dumps(c.error_status).encode()
-                return [b'{"modality":' + json.dumps(c.modality).encode() + b',"data":"' + base64.b64encode(c.data) +
-                        tail + b"}\n"], False
-            return ChunkStream(server, rid, fmt, "application/x-ndjson")
+                data = c.data if isinstance(c.data, (bytes, bytearray)) else bytes(c.data)
+                return b'{"modality":' + json.dumps(c.modality).encode() + b',"data":"', data, tail + b"}\n"
+
+            def fmt(c):
+                prefix, data, suffix = raw(c)
+                return [prefix + base64.b64encode(data) + suffix], False
+            return ChunkStream(server, rid, fmt, "application/x-ndjson", raw=raw)
         res = _collect(rid)
         return {"request_id": rid, "outputs": {m: [{"data": base64.b64encode(c.data).decode(), "metadata": c.metadata}
                                                    for c in cs] for m, cs in res.items()}}

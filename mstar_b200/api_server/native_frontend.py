@@ -15,6 +15,7 @@ import asyncio
 import ctypes
 import json
 import os
+import struct
 import subprocess
 import threading
 import time
@@ -85,10 +86,34 @@ class NativeFrontend:
         self.loop = asyncio.new_event_loop()
         self.tasks: dict[int, asyncio.Task] = {}
         self.running = False
-        self.stats = dict(requests=0, aborted=0)
+        self.stats = dict(requests=0, aborted=0, batches=0, batched_chunks=0)
+        # body chunks whose binary field the frontend encodes: collected while the API server handles one message of a
+        # worker (the chunks of all requests of a batch) and sent as one frame when it is done with the message
+        self._batch: list[bytes] = []
+        self._batch_n = 0
+        self._batch_lock = threading.Lock()
+        self._batching = False
 
     # ---- life cycle ----
+    BATCH_MAX = 256
+
+    def _flush_batch(self) -> None:
+        if not self._batch_n:
+            return
+        with self._batch_lock:             # the send stays inside: frames of two flushes must not swap
+            if not self._batch_n:
+                return
+            n, pieces = self._batch_n, self._batch
+            self._batch, self._batch_n = [], 0
+            self.stats["batches"] += 1
+            self.stats["batched_chunks"] += n
+            self.mesh.send("frontend", b'{"kind":"b64_batch","n":%d}\n' % n + b"".join(pieces))
+
     def start(self, wait_s: float = 10.0) -> "NativeFrontend":
+        server = getattr(getattr(self.app, "state", None), "mstar_server", None)
+        if server is not None and hasattr(server, "after_message_hooks") and os.environ.get("MSTAR_FRONTEND_BATCH", "1") != "0":
+            server.after_message_hooks.append(self._flush_batch)
+            self._batching = True
         self.proc = subprocess.Popen([self.binary, "--prefix", self.prefix, "--host", self.host, "--port", str(self.port),
                                       "--max-connections", str(self.max_connections)])
         self.running = True
@@ -164,15 +189,30 @@ class NativeFrontend:
 
     def _send(self, rid: int, kind: str, payload: bytes = b"", **extra) -> None:
         head = json.dumps({"id": rid, "kind": kind, **extra}, separators=(",", ":")).encode() + b"\n"
+        self._flush_batch()                # a frame never overtakes chunks that were collected before it
         self.mesh.send("frontend", head + payload)
 
     def _direct(self, rid: int):
+        """The body sink handed to a streaming response: ``push(piece)`` sends one chunk; ``push.b64(prefix, data,
+        suffix)``, when present, queues the chunk prefix + base64(data) + suffix for the frontend to encode."""
         head = json.dumps({"id": rid, "kind": "chunk"}, separators=(",", ":")).encode() + b"\n"
         send = self.mesh.send
 
         def push(piece: bytes) -> None:
             if piece:
+                self._flush_batch()
                 send("frontend", head + piece)
+        if self._batching:
+            pack = struct.Struct("<QIII").pack
+
+            def b64(prefix: bytes, data: bytes, suffix: bytes) -> None:
+                with self._batch_lock:
+                    self._batch += (pack(rid, len(prefix), len(data), len(suffix)), prefix, data, suffix)
+                    self._batch_n += 1
+                    full = self._batch_n >= self.BATCH_MAX
+                if full:
+                    self._flush_batch()
+            push.b64, push.flush = b64, self._flush_batch
         return push
 
     async def _serve(self, rid: int, hdr: dict, body: bytes):

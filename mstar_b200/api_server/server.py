@@ -54,6 +54,7 @@ class APIServer:
         self.pre_pool = ThreadPoolExecutor(4, thread_name_prefix="preprocess")
         self.running = True
         self.stats = dict(submitted=0, completed=0, failed=0, aborted=0)
+        self.after_message_hooks: list = []        # called on the result thread after every handled message
         self._thread = threading.Thread(target=self._process_messages, daemon=True, name="api-results")
 
     # ---- lifecycle ----
@@ -183,6 +184,11 @@ class APIServer:
                     self._handle(m)
                 except Exception:  # noqa: BLE001
                     log.exception("api: message %s failed", m.type)
+                for hook in self.after_message_hooks:      # transports that collect a message's chunks send them now
+                    try:
+                        hook()
+                    except Exception:  # noqa: BLE001
+                        log.exception("api: after-message hook failed")
             if time.time() - last_prune > 5.0:
                 last_prune = time.time()
                 self._prune()

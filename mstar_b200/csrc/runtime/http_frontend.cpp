@@ -5,6 +5,10 @@
 //   frontend -> api_bridge :  {"id":N,"method":"POST","path":"/generate","query":"..","content_type":"..","len":L}\n<body>
 //   api_bridge -> frontend :  {"id":N,"kind":"head","status":200,"content_type":"..","streaming":true}\n
 //                             {"id":N,"kind":"chunk"}\n<bytes>            (any number)
+//                             {"kind":"b64_batch","n":K}\n<K records>     body chunks of K requests in one message:
+//                               record = u64 id, u32 prefix_len, u32 data_len, u32 suffix_len (little endian), then the
+//                               three byte strings; the chunk is prefix + base64(data) + suffix (an NDJSON line whose
+//                               binary field is encoded here instead of in the API process)
 //                             {"id":N,"kind":"end"}\n
 //
 // Streaming responses go out with chunked transfer encoding as the chunks arrive; other responses are buffered and
@@ -104,6 +108,24 @@ bool json_get(const std::string& j, const std::string& key, std::string* out) {
     while (e < j.size() && j[e] != ',' && j[e] != '}') ++e;
     *out = j.substr(p, e - p);
     return true;
+}
+
+void base64_append(std::string& out, const unsigned char* p, size_t n) {
+    static const char T[] = "ABCDEFGHIJKLMNOPQRSTUVWXYZabcdefghijklmnopqrstuvwxyz0123456789+/";
+    size_t o = out.size();
+    out.resize(o + (n + 2) / 3 * 4);
+    char* w = &out[o];
+    size_t i = 0;
+    for (; i + 2 < n; i += 3) {
+        const unsigned v = (p[i] << 16) | (p[i + 1] << 8) | p[i + 2];
+        *w++ = T[v >> 18]; *w++ = T[(v >> 12) & 63]; *w++ = T[(v >> 6) & 63]; *w++ = T[v & 63];
+    }
+    if (i < n) {
+        const unsigned v = (p[i] << 16) | (i + 1 < n ? p[i + 1] << 8 : 0);
+        *w++ = T[v >> 18]; *w++ = T[(v >> 12) & 63];
+        *w++ = i + 1 < n ? T[(v >> 6) & 63] : '=';
+        *w++ = '=';
+    }
 }
 
 bool send_all(int fd, const char* p, size_t n) {
@@ -339,6 +361,38 @@ void mailbox_loop(Server* S) {
         if (v == "shutdown") {
             S->running = false;
             break;
+        }
+        if (v == "b64_batch") {
+            const unsigned char* q = (const unsigned char*)nl + 1;
+            const unsigned char* end = (const unsigned char*)buf.data() + n;
+            while ((size_t)(end - q) >= 20) {
+                uint64_t id;
+                uint32_t lens[3];
+                memcpy(&id, q, 8);
+                memcpy(lens, q + 8, 12);
+                q += 20;
+                if ((uint64_t)lens[0] + lens[1] + lens[2] > (uint64_t)(end - q)) break;       // malformed: drop the rest
+                Frame f;
+                f.kind = "chunk";
+                f.payload.reserve(lens[0] + (lens[1] + 2) / 3 * 4 + lens[2]);
+                f.payload.assign((const char*)q, lens[0]);
+                base64_append(f.payload, q + lens[0], lens[1]);
+                f.payload.append((const char*)q + lens[0] + lens[1], lens[2]);
+                q += (size_t)lens[0] + lens[1] + lens[2];
+                std::shared_ptr<Pending> p;
+                {
+                    std::lock_guard<std::mutex> g(S->map_m);
+                    auto it = S->pending.find(id);
+                    if (it != S->pending.end()) p = it->second;
+                }
+                if (!p) continue;
+                {
+                    std::lock_guard<std::mutex> g(p->m);
+                    p->frames.push_back(std::move(f));
+                }
+                p->cv.notify_one();
+            }
+            continue;
         }
         Frame f;
         f.kind = v;

@@ -95,3 +95,46 @@ def test_many_concurrent_connections(base_url):
     for t in ts:
         t.join()
     assert not errs and out.count(200) == 24
+
+
+def test_frontend_encodes_batched_binary_chunks_like_python():
+    """Chunks stated as prefix + base64(data) + suffix are collected, sent to the frontend as ONE frame and encoded
+    there: every padding case, binary bytes, chunks of several requests in one batch, and frame order (head, batched
+    chunks, a plain piece, end) survive."""
+    datas = [bytes(range(n)) for n in range(8)] + [os.urandom(5461), os.urandom(4096)]
+    fe_box = {}
+
+    async def app(scope, receive, send):
+        await receive()
+        direct = scope["extensions"]["mstar.direct_stream"]
+        await send({"type": "http.response.start", "status": 200, "headers": [(b"content-type", b"text/plain")]})
+        for d in datas:
+            direct.b64(b"<", d, b">\n")
+        fe_box["fe"]._flush_batch()         # what the API server's after-message hook does
+        direct.b64(b"<", b"late", b">\n")
+        direct(b"plain\n")                  # a plain piece flushes what was collected before it
+        await send({"type": "http.response.body", "body": b"", "more_body": False})
+
+    class _State:
+        pass
+
+    class _Srv:
+        after_message_hooks: list = []
+    app.state = _State()
+    app.state.mstar_server = _Srv()
+    port = _free_port()
+    fe = fe_box["fe"] = NativeFrontend(app, "127.0.0.1", port).start()
+    try:
+        assert fe._batching and _Srv.after_message_hooks == [fe._flush_batch]
+        bodies = []
+
+        def get():
+            bodies.append(requests.get(f"http://127.0.0.1:{port}/x", timeout=20).content)
+        ts = [threading.Thread(target=get) for _ in range(3)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        want = b"".join(b"<" + base64.b64encode(d) + b">\n" for d in datas + [b"late"]) + b"plain\n"
+        assert bodies == [want] * 3
+        assert fe.stats["batched_chunks"] == 3 * (len(datas) + 1) and fe.stats["batches"] >= 3
+    finally:
+        fe.stop()
