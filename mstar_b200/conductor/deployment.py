@@ -115,8 +115,16 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
         for n in g.get("node_names", []):
             walks_of.setdefault(n, set()).add(tuple(sorted(g.get("graph_walks") or [])))
     split_by_walk = any(len(v) > 1 for v in walks_of.values())
+    # the walks in which THIS rank runs each of its nodes (None: every walk)
+    node_walks: dict[str, set | None] = {}
+    for wg in mine:
+        for n in wg.node_names:
+            if wg.graph_walks is None or node_walks.get(n, set()) is None:
+                node_walks[n] = None
+            else:
+                node_walks.setdefault(n, set()).update(wg.graph_walks)
     return Worker(worker_id_of(rank), rank, model, node_names, comm, tensors, em, node_to_workers=n2w,
-                  publish_persisted=split_by_walk,
+                  publish_persisted=split_by_walk, node_walks=node_walks,
                   tp_followers=followers, is_tp_follower=is_follower, max_batch_size=int(cfg.get("max_batch_size", 64)),
                   async_gpu=async_gpu, heartbeat_s=heartbeat_s, log_stats=bool(cfg.get("log_stats")))
 

@@ -355,7 +355,16 @@ class BagelLLMSubmodule(ARNodeSubmodule):
         grid = (shape[1] // 2, shape[2] // 2)
         labels = ni.kwargs.pop("_labels")
         tok = m.latent_tokens(x, grid, t)
-        pos_end = int(st.get("pos_end", md.get("pos_end", 0)))
+        pos_end = st.get("pos_end", md.get("pos_end"))
+        if pos_end is None:
+            # the prompt passes ran in another pool (per-walk placement): the position after the prompt is what every
+            # non-empty context of the request continues from
+            alloc, pos_end = ei.cache_manager.alloc, 0
+            for lb in alloc.get_labels(ni.request_id):
+                s_ = alloc.get_state(ni.request_id, lb)
+                pos_end = max(pos_end, s_.seq_len + s_.pos_offset if s_.seq_len else 0)
+            st["pos_end"] = pos_end
+        pos_end = int(pos_end)
         v = m.gen_velocity(tok, [pos_end] * len(labels), len(labels), ctx)
         vd = {lb: v[b] for b, lb in enumerate(labels)}
         branch = self.my_branch(md)

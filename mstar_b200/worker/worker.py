@@ -81,8 +81,13 @@ class Worker:
                  tensors: TensorCommunicationManager, engine_manager, *, node_to_workers: dict[str, list[str]],
                  conductor_id: str = "conductor", api_id: str = "api", tp_followers: list[str] | None = None,
                  is_tp_follower: bool = False, max_batch_size: int = 64, async_gpu: bool = True,
-                 heartbeat_s: float = 0.0, log_stats: bool = False, publish_persisted: bool = True):
+                 heartbeat_s: float = 0.0, log_stats: bool = False, publish_persisted: bool = True,
+                 node_walks: dict[str, set | None] | None = None):
         self.worker_id, self.rank, self.model = worker_id, rank, model
+        # node -> the walks in which this worker runs it (None / absent: every walk). A node placed per walk (prompt
+        # passes here, decoding elsewhere) must stay out of the other walks even when the walk reaches this worker
+        # for another of its nodes.
+        self.node_walks = dict(node_walks or {})
         # per-request profile (node timings, tensor transfers), collected only when the server logs request statistics
         self.profile = None
         if log_stats or os.environ.get("MSTAR_LOG_STATS"):
@@ -237,17 +242,19 @@ class Worker:
         sec = self.walks.get(walk)
         if sec is None:
             raise KeyError(f"unknown graph walk {walk!r}")
-        return restrict_section(sec, self.node_names)
+        mine = {n for n in self.node_names if self.node_walks.get(n) is None or walk in self.node_walks[n]}
+        return restrict_section(sec, mine)
 
     def _on_new_request(self, b: ipc.NewRequest) -> None:
         info = b.request_info
         sec = self._section_for(info.graph_walk)
         if sec is None:
             return
-        imports = (info.step_metadata or {}).pop("_kv_import", {}).get(self.worker_id, {})
+        # read, not popped: workers of an in-process deployment receive the same message object
+        imports = (info.step_metadata or {}).get("_kv_import", {}).get(self.worker_id, {})
         remote_kv: set[str] = set()
         for node, src_worker in imports.items():
-            if node in self.node_names:
+            if node in self.node_names and (self.node_walks.get(node) is None or info.graph_walk in self.node_walks[node]):
                 from .engine_manager import lookup_kv_engine
                 src = lookup_kv_engine(src_worker, node)
                 if src is None:

@@ -158,3 +158,44 @@ def test_a_deployment_whose_process_dies_at_start_up_fails_fast():
     except (RuntimeError, ValueError):
         pass
     assert time.time() - t0 < 120
+
+
+def test_per_walk_placement_gives_the_same_tokens_and_images_as_one_gpu():
+    """The prompt passes on one rank, decoding and image generation on others (the LLM node placed per walk): the
+    request's KV pages of every guidance context move at the walk switch, the node runs only where its walk is
+    placed, and understanding, text-to-image and editing give what the single-rank placement gives — repeatedly."""
+    import hashlib
+    import yaml
+    import torch
+    from mstar_b200.api_server.server import APIServer
+
+    def run(path):
+        cfg = yaml.safe_load(open(path))
+        cfg.update(model_kwargs={"small": True}, use_cuda_graphs=False)
+        torch.manual_seed(0)                      # the test-sized autoencoder takes torch's default initialisation
+        s = APIServer(cfg, in_process=True).start(120)
+        out = []
+        try:
+            mk = dict(max_tokens=5, ignore_eos=True, num_steps=3, height=16, width=16, seed=1, temperature=0.0)
+            img = torch.rand(3, 16, 16, generator=torch.Generator().manual_seed(3))
+            for _ in range(2):
+                for prompt, outs, tens in (("a cat", ["text"], {"image": [img]}), ("a cat", ["image"], None),
+                                           ("make it blue", ["image"], {"image": [img]})):
+                    r = s.collect_results(s.submit_request(prompt, output_modalities=outs, model_kwargs=mk, tensors=tens), 120)
+                    assert "error" not in r, r
+                    out.append(hashlib.md5(b"".join(c.data for c in r[outs[0]])).hexdigest())
+            assert out[:3] == out[3:]
+            import time
+            for w in s.deployment.workers:       # every page goes back, on every rank (the teardown message follows the result)
+                eng = w.engines.engine_for("LLM")
+                for _ in range(100):
+                    if eng.cache.alloc.num_free_pages == eng.cache.alloc.total_pages:
+                        break
+                    time.sleep(0.02)
+                assert eng.cache.alloc.num_free_pages == eng.cache.alloc.total_pages
+        finally:
+            s.shutdown()
+        return out
+    single = run("configs/bagel_single_gpu.yaml")
+    assert run("configs/bagel_pd_disaggregated.yaml") == single
+    assert run("configs/bagel_img_disaggregated.yaml") == single
