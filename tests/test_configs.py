@@ -75,3 +75,30 @@ def _nodes(section):
         for s in (v if isinstance(v, (list, tuple)) else [v]):
             out += _nodes(s)
     return out
+
+
+def test_qwen3_omni_placements_give_the_same_answer():
+    """One GPU, two GPUs, colocated groups and prompt / decode disaggregation of the thinker: the same text and the
+    same amount of speech for a request with audio and image input (test-sized weights, in-process ranks)."""
+    import torch
+    from mstar_b200.api_server.server import APIServer
+
+    def run(name):
+        cfg = load_config(os.path.join(ROOT, name))
+        cfg.update(model_kwargs=dict(cfg.get("model_kwargs") or {}, small=True), use_cuda_graphs=False)
+        torch.manual_seed(0)
+        s = APIServer(cfg, in_process=True).start(120)
+        try:
+            kw = dict(max_tokens=6, ignore_eos=True, temperature=0.0, max_audio_tokens=12)
+            tens = {"audio": [torch.randn(8000, generator=torch.Generator().manual_seed(1)) * 0.1],
+                    "image": [torch.rand(3, 16, 16, generator=torch.Generator().manual_seed(2))]}
+            r = s.collect_results(s.submit_request("describe", output_modalities=["text", "audio"], model_kwargs=kw,
+                                                   tensors=tens), 120)
+            assert "error" not in r, r
+            return b"".join(c.data for c in r["text"]), sum(len(c.data) for c in r["audio"])
+        finally:
+            s.shutdown()
+    want = run("qwen3_omni.yaml")
+    assert len(want[0].split()) == 6 and want[1] > 0
+    for name in ("qwen3_omni_colocated.yaml", "qwen3_omni_2gpu.yaml", "qwen3_omni_pd_disaggregated.yaml"):
+        assert run(name) == want, name
