@@ -63,9 +63,10 @@ def default_pin_budget() -> int:
 
 
 def _tensor_at(ptr: int, nbytes: int, dtype: torch.dtype, dims) -> torch.Tensor:
-    buf = (ctypes.c_uint8 * max(nbytes, 1)).from_address(ptr)
-    t = torch.frombuffer(buf, dtype=torch.uint8, count=nbytes)
-    return t.view(dtype).view(*dims) if nbytes else torch.empty(tuple(dims), dtype=dtype)
+    if not nbytes:          # an empty tensor (a codec chunk without frames) has a block but no bytes to view
+        return torch.empty(tuple(dims), dtype=dtype)
+    buf = (ctypes.c_uint8 * nbytes).from_address(ptr)
+    return torch.frombuffer(buf, dtype=torch.uint8, count=nbytes).view(dtype).view(*dims)
 
 
 class ShmArena:

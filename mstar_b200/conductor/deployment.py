@@ -67,14 +67,22 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
     tp_group = sp_group = None
     par = [wg for wg in mine if wg.tp_size * wg.sp_size > 1]
     if par and dist_init:
-        groups = WorkerParallelGroups(rank, world)
+        # the process group spans only the ranks that belong to some tensor- / sequence-parallel instance, numbered in
+        # rank order: a rank that runs single-GPU nodes only (an encoder, a codec) never joins, so it cannot hold
+        # the others' rendezvous up
+        dist_ranks = sorted({r for w in wgs if w.tp_size * w.sp_size > 1 for r in w.ranks})
+        dr = {r: i for i, r in enumerate(dist_ranks)}
+        groups = WorkerParallelGroups(dr[rank], len(dist_ranks))
+        _group_for = groups.group_for
+        groups.group_for = lambda ranks: _group_for(tuple(dr[r] for r in ranks))
         def instance_tp_major(w):
             # all ranks of the instance, tensor-parallel index slowest: shard i of a weight cut tp*sp ways is the
             # sp-th part of tensor-parallel shard t (the head order that Ulysses produces inside a TP shard)
             return tuple(w.ranks[s * w.tp_size + t] for t in range(w.tp_size) for s in range(w.sp_size))
-        tuples = sorted({tuple(wg.tp_ranks(r)) for wg in wgs for r in wg.ranks} |
-                        {tuple(wg.sp_ranks(r)) for wg in wgs for r in wg.ranks} |
-                        {instance_tp_major(wg) for wg in wgs if wg.tp_size > 1 and wg.sp_size > 1})
+        pw = [w for w in wgs if w.tp_size * w.sp_size > 1]
+        tuples = sorted({tuple(dr[x] for x in wg.tp_ranks(r)) for wg in pw for r in wg.ranks} |
+                        {tuple(dr[x] for x in wg.sp_ranks(r)) for wg in pw for r in wg.ranks} |
+                        {tuple(dr[x] for x in instance_tp_major(wg)) for wg in pw if wg.tp_size > 1 and wg.sp_size > 1})
         groups.init_dist(dist_init, all_rank_tuples=[t for t in tuples if len(t) > 1])
         wg = par[0]
         tp_group = groups.group_for(wg.tp_ranks(rank))
@@ -124,7 +132,11 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
             else:
                 node_walks.setdefault(n, set()).update(wg.graph_walks)
     return Worker(worker_id_of(rank), rank, model, node_names, comm, tensors, em, node_to_workers=n2w,
-                  publish_persisted=split_by_walk, node_walks=node_walks,
+                  # persisted tensors come back from the conductor in a later walk: to another worker when a node is
+                  # split by walk, and to the other ranks of a tensor- / sequence-parallel instance always
+                  publish_persisted=split_by_walk or bool(followers), node_walks=node_walks,
+                  parallel_nodes={n for wg in par for n in wg.node_names},
+                  instance_workers={worker_id_of(r) for wg in par for r in wg.ranks},
                   tp_followers=followers, is_tp_follower=is_follower, max_batch_size=int(cfg.get("max_batch_size", 64)),
                   async_gpu=async_gpu, heartbeat_s=heartbeat_s, log_stats=bool(cfg.get("log_stats")))
 
@@ -132,6 +144,8 @@ def build_worker(cfg: dict, model, rank: int, comm, *, prefix: str, async_gpu: b
 def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):
     import faulthandler
     faulthandler.enable()
+    if os.environ.get("MSTAR_DUMP_STACKS_S"):        # debugging aid: every thread's stack of this worker after N seconds
+        faulthandler.dump_traceback_later(float(os.environ["MSTAR_DUMP_STACKS_S"]), repeat=False)
     signal.signal(signal.SIGTERM, lambda *_: (_ for _ in ()).throw(SystemExit(0)))
     logging.basicConfig(level=os.environ.get("MSTAR_LOG_LEVEL", "INFO"))
     # a launcher may have pinned OMP_NUM_THREADS to 1 for its own ranks; weight initialisation / loading and host-side
@@ -157,6 +171,8 @@ def _worker_process_target(cfg, rank, prefix, dist_init, heartbeat_s):
 def _conductor_process_target(cfg, prefix, heartbeat_timeout_s):
     import faulthandler
     faulthandler.enable()
+    if os.environ.get("MSTAR_DUMP_STACKS_S"):
+        faulthandler.dump_traceback_later(float(os.environ["MSTAR_DUMP_STACKS_S"]), repeat=False)
     signal.signal(signal.SIGTERM, lambda *_: (_ for _ in ()).throw(SystemExit(0)))
     logging.basicConfig(level=os.environ.get("MSTAR_LOG_LEVEL", "INFO"))
     model = build_model(cfg)

@@ -20,10 +20,15 @@ class MicroScheduler:
         self.policy = policy
         self.priorities = priorities or {}
         self.is_tp_follower = is_tp_follower
+        # nodes whose batches replay the instance leader's decisions (None: every node); a follower rank's other
+        # nodes (a codec or encoder placed on that rank alone) are scheduled here like on any worker
+        self.follow_nodes: set | None = None
         self.ready: "OrderedDict[tuple[str, str], OrderedDict[str, None]]" = OrderedDict()
         self._rr: deque = deque()
         self._held: dict[str, float] = {}
         self._tp_queue: deque = deque()          # leader decisions waiting to be replayed
+        self._follow_wait = None                  # (decision, since, warned): a decision that cannot be replayed yet
+        self.stalled = None
         self.node_limits: dict[str, int] = {}
         self.limit_fn = None                      # optional (node, walk) -> largest batch the node accepts
         # optional (node, walk, ready request ids, seconds since the first of them became ready) -> True to hold the
@@ -75,8 +80,12 @@ class MicroScheduler:
     def get_next_batch(self, exclude: set | None = None):
         """(node, walk, request_ids) or None."""
         if self.is_tp_follower:
-            return self._follow()
+            nxt = self._follow()
+            if nxt is not None or self.follow_nodes is None:
+                return nxt
         keys = [k for k in self._rr if self.ready.get(k)]
+        if self.is_tp_follower:
+            keys = [k for k in keys if k[0] not in self.follow_nodes]
         if not keys:
             return None
         if self.policy == "priority":
@@ -111,6 +120,17 @@ class MicroScheduler:
         node, walk, rids = self._tp_queue[0]
         q = self.ready.get((node, walk), {})
         if not all(r in q for r in rids):
+            now = time.monotonic()
+            if self._follow_wait is None or self._follow_wait[0] is not self._tp_queue[0]:
+                self._follow_wait = (self._tp_queue[0], now, False)
+            elif now - self._follow_wait[1] > 5.0 and not self._follow_wait[2]:
+                self._follow_wait = (self._tp_queue[0], self._follow_wait[1], True)
+                self.stalled = (node, walk, list(rids))          # the worker adds what the requests still miss
+                import logging
+                logging.getLogger("mstar.worker").warning(
+                    "lockstep: the leader's batch %s:%s %s waits for requests that are not ready on this rank: %s "
+                    "(ready here: %s)", node, walk, rids, [r for r in rids if r not in q],
+                    {k: list(v) for k, v in self.ready.items() if v})
             return None
         self._tp_queue.popleft()
         for r in rids:

@@ -82,8 +82,14 @@ class Worker:
                  conductor_id: str = "conductor", api_id: str = "api", tp_followers: list[str] | None = None,
                  is_tp_follower: bool = False, max_batch_size: int = 64, async_gpu: bool = True,
                  heartbeat_s: float = 0.0, log_stats: bool = False, publish_persisted: bool = True,
-                 node_walks: dict[str, set | None] | None = None):
+                 node_walks: dict[str, set | None] | None = None, parallel_nodes: set | None = None,
+                 instance_workers: set | None = None):
         self.worker_id, self.rank, self.model = worker_id, rank, model
+        # nodes that run on every rank of this worker's tensor- / sequence-parallel instance in lockstep, and the
+        # workers of that instance. Every rank keeps such a node's outputs for itself; what leaves the instance
+        # (client, nodes elsewhere, the conductor) is sent by the instance's first rank only.
+        self.parallel_nodes = set(parallel_nodes) if parallel_nodes is not None else None
+        self.instance_workers = set(instance_workers or ())
         # node -> the walks in which this worker runs it (None / absent: every walk). A node placed per walk (prompt
         # passes here, decoding elsewhere) must stay out of the other walks even when the walk reaches this worker
         # for another of its nodes.
@@ -101,6 +107,7 @@ class Worker:
         self.tp_followers = tp_followers or []
         self.is_tp_follower = is_tp_follower
         self.scheduler = MicroScheduler(max_batch_size=max_batch_size, is_tp_follower=is_tp_follower)
+        self.scheduler.follow_nodes = self.parallel_nodes
         self.scheduler.limit_fn = self._node_batch_limit
         self.scheduler.defer_fn = self._defer_batch
         # batch gathering: a batch is held back for a moment while requests that would join it are still on the GPU in
@@ -115,6 +122,9 @@ class Worker:
         # need to be published for other processes when some node is split over node groups by walk (prefill and
         # decode on different workers); otherwise the request stays on this worker and the store lookup is local
         self._publish_persisted = publish_persisted
+        self._stall_log_s = float(os.environ.get("MSTAR_STALL_LOG_S", "15"))
+        self._last_stall_scan, self._stall_logged = time.monotonic(), set()
+        self._deferred_new: dict[tuple[str, str], list] = {}   # NEW_REQUEST of a walk whose predecessor is still in flight here
         self._done_queue: list | None = None      # walk-completion messages held back while a batch is being finished
         self._emit_buf: list | None = None        # client-bound outputs of the batch being finished, sent as one message
         self.walks = model.get_graph_walk_graphs()
@@ -250,6 +260,13 @@ class Worker:
         sec = self._section_for(info.graph_walk)
         if sec is None:
             return
+        prev = self.requests.get((b.request_id, info.partition_name))
+        if prev is not None and prev.in_flight > 0 and prev.fwd_info.graph_walk != info.graph_walk:
+            # the previous walk's last batch has not been read back on THIS rank yet (a rank of a parallel instance
+            # can trail the rank that reported the walk's end): the new walk starts when it has, or that batch's
+            # completion would be booked on the new walk's state
+            self._deferred_new.setdefault((b.request_id, info.partition_name), []).append(b)
+            return
         # read, not popped: workers of an in-process deployment receive the same message object
         imports = (info.step_metadata or {}).get("_kv_import", {}).get(self.worker_id, {})
         remote_kv: set[str] = set()
@@ -304,6 +321,9 @@ class Worker:
     def _on_input_signals(self, b: ipc.InputSignals) -> None:
         pri = self.requests.get((b.request_id, b.partition_name))
         if pri is None:
+            # normal for stream edges towards a partition the request does not use (text-only output of an omni model)
+            log.debug("worker %s: inputs %s for a request it does not hold (%s, partition %s)", self.worker_id,
+                      [e.name for e in b.inputs], b.request_id, b.partition_name)
             return
         if b.request_info is not None and b.request_info.graph_walk != pri.fwd_info.graph_walk:
             pri.fwd_info = b.request_info
@@ -526,6 +546,7 @@ class Worker:
                     self.spec_stats["discarded_rows"] += 1
                     if pri.remove_pending and pri.in_flight == 0:
                         self._drop((rid, pri.partition_name))
+                    self._start_deferred_walk(rid, pri)
                     continue
                 pri.spec[node].remove(fl.fid)
                 pri.spec_marked.discard(node)
@@ -539,6 +560,38 @@ class Worker:
                 self._fail_requests({rid: f"{type(e).__name__}: {e}"})
             if pri.remove_pending and pri.in_flight == 0:
                 self._drop((rid, pri.partition_name))
+            self._start_deferred_walk(rid, pri)
+
+    def _log_stalled_requests(self) -> None:
+        """Diagnostic: requests that hold a walk here, have nothing on the device and no node ready, logged once with
+        what every unfinished node still misses (an input that was routed elsewhere, a walk that never got its
+        first edge)."""
+        for key, pri in self.requests.items():
+            ws = pri.walk_state
+            if pri.in_flight or ws.done or key in self._stall_logged or time.perf_counter() - pri.t_start < self._stall_log_s:
+                continue
+            ready = ws.ready_nodes(allow_streaming=False)
+            if ready:
+                self._stall_logged.add(key)
+                log.warning("worker %s: request %s idle in walk %s for %.0f s with nodes ready but not running: %s "
+                            "(waiting for pages of another pool: %s; scheduler queue: %s; leader decisions pending: %d)",
+                            self.worker_id, key[0], pri.fwd_info.graph_walk, time.perf_counter() - pri.t_start, ready,
+                            sorted(pri.kv_wait), {k: list(v) for k, v in self.scheduler.ready.items() if v},
+                            len(self.scheduler._tp_queue))
+                continue
+            if ws.ready_nodes(allow_streaming=True):
+                continue
+            waiting = {n: sorted(st.missing()) for n, st in ws.nodes.items()
+                       if not st.done and not st.running and not st.scope.done}
+            if waiting:
+                self._stall_logged.add(key)
+                log.warning("worker %s: request %s idle in walk %s for %.0f s; nodes waiting for inputs: %s",
+                            self.worker_id, key[0], pri.fwd_info.graph_walk, time.perf_counter() - pri.t_start, waiting)
+
+    def _start_deferred_walk(self, rid: str, pri: PerRequestInfo) -> None:
+        if pri.in_flight == 0 and self._deferred_new:
+            for nb in self._deferred_new.pop((rid, pri.partition_name), []):
+                self._on_new_request(nb)
 
     def _complete_node(self, pri: PerRequestInfo, batch: NodeBatch, tensors: dict, stops: set,
                        iterations: int = 1) -> None:
@@ -564,7 +617,8 @@ class Worker:
             ne.tensor_info = [self.tensors.store_and_return_tensor_info(owner, x, refs=refs, persist=e.persist)
                               for x in t if isinstance(x, torch.Tensor)]
             edges.append(ne)
-            if e.conductor_new_token:
+            if e.conductor_new_token and not (self.is_tp_follower and self.instance_workers and
+                                              (self.parallel_nodes is None or node in self.parallel_nodes)):
                 pri.new_token_counts[e.name] = pri.new_token_counts.get(e.name, 0) + max(1, iterations)
         comp = ws.complete(node, edges, iterations=iterations)
         if pri.stream_buffers:
@@ -579,15 +633,32 @@ class Worker:
             else:
                 ws.mark_running(node)       # iteration N+1 is already queued on the GPU, fed from the device
                 pri.spec_marked.add(node)
-        self._send_outputs(pri, comp.route)
+        self._send_outputs(pri, comp.route, producer=node)
+        if self.instance_workers and self.parallel_nodes and node not in self.parallel_nodes:
+            # a node of this rank alone (an encoder) fed a node that runs on every rank of the instance: the local
+            # hand-over reached this rank only, the other ranks get the edge as a message
+            peers = [e for e in comp.delivered if e.next_node in self.parallel_nodes]
+            if peers:
+                self._send_outputs(pri, peers, producer=node, skip_self=True)
         self._refresh_ready(pri)
         if comp.walk_done:
             self._walk_done(pri)
 
-    def _send_outputs(self, pri: PerRequestInfo, edges: list[GraphEdge]) -> None:
+    def _send_outputs(self, pri: PerRequestInfo, edges: list[GraphEdge], producer: str | None = None,
+                      skip_self: bool = False) -> None:
         by_worker: dict[str, list[GraphEdge]] = {}
+        # the producer ran on every rank of a parallel instance: each rank feeds itself, the first rank speaks for all
+        lockstep = bool(self.instance_workers) and producer is not None and \
+            (self.parallel_nodes is None or producer in self.parallel_nodes)
         for e in edges:
-            if e.persist:
+            if skip_self:           # already handed over and booked on this rank: only the other workers of the node
+                for w in self.node_to_workers.get(e.next_node, []):
+                    if w != self.worker_id:
+                        by_worker.setdefault(w, []).append(e)
+                continue
+            if e.persist and lockstep and self.is_tp_follower:
+                pass        # the instance's first rank reports (and publishes) its copy
+            elif e.persist:
                 # a persisted tensor can be handed by the conductor to ANY worker in a later walk (prefill / decode
                 # split): when some worker lives in another process, publish it now (arena block or CUDA IPC handle),
                 # since only the owner can do that
@@ -598,6 +669,8 @@ class Worker:
             if e.next_node == EMPTY_DESTINATION:
                 continue
             if e.next_node == EMIT_TO_CLIENT:
+                if lockstep and self.is_tp_follower:
+                    continue
                 emit_owner = pri.request_id + "#emit"
                 for ti in e.tensor_info:        # a loop's last output was stored as an intermediate: re-own it
                     if self.tensors.store.owner_of(ti.uuid) not in (None, emit_owner):
@@ -611,6 +684,8 @@ class Worker:
                     self.comm.send(self.api_id, Message(ipc.ApiMessageType.RESULT_TENSORS, rt))
                 continue
             for w in self.node_to_workers.get(e.next_node, []):
+                if lockstep and w != self.worker_id and (w in self.instance_workers or self.is_tp_follower):
+                    continue
                 by_worker.setdefault(w, []).append(e)
         for w, es in by_worker.items():
             # edges of a streaming connection belong to the CONSUMER partition's request state, also when producer
@@ -669,9 +744,14 @@ class Worker:
         for eng in self.engines.engines:
             if hasattr(eng, "get_per_label_seq_info"):
                 seq.update(eng.get_per_label_seq_info(pri.request_id))
-        if not self.is_tp_follower:
+        # a rank reports the worker graphs whose first rank it is: the instance it follows is reported by its leader,
+        # a single-rank group that shares this rank (a decoder beside a sharded model) by this rank itself
+        led = [g for g in pri.worker_graph_ids
+               if (pri.worker_graph_to_workers.get(g) or [self.worker_id])[0] == self.worker_id]
+        if led or not self.is_tp_follower:
             body = ipc.WorkerGraphsDone(
-                pri.request_id, list(pri.worker_graph_ids), True, dict(pri.persist), dict(pri.new_token_counts), seq,
+                pri.request_id, led if self.is_tp_follower else list(pri.worker_graph_ids), True, dict(pri.persist),
+                dict(pri.new_token_counts), seq,
                 pri.partition_name, False, {}, pri.walk_state.loop_indices(),
                 {"walk_s": time.perf_counter() - pri.t_start}, pri.fwd_info.graph_walk)
             if self._done_queue is not None:
@@ -756,13 +836,27 @@ class Worker:
             T["build"] += time.perf_counter() - tb
             if batch is None:
                 continue
-            if not self.is_tp_follower:
+            if not self.is_tp_follower and (self.parallel_nodes is None or node in self.parallel_nodes):
                 for f in self.tp_followers:
                     self.comm.send(f, Message(WM.SCHEDULE_TP, ipc.ScheduleTPNode(node, walk, list(rkeys))))
             did = True
             self._submit(batch)
             if self.gpu_thread is None:
                 break
+        if self.scheduler.stalled is not None:
+            node, walk, rks = self.scheduler.stalled
+            self.scheduler.stalled = None
+            for rk in rks:
+                rid, part = rk.split("|", 1)
+                pri = self.requests.get((rid, part))
+                st = pri.walk_state.nodes.get(node) if pri is not None else None
+                log.warning("worker %s: %s of %s in walk %s: %s", self.worker_id, node, rid, walk,
+                            "request not held" if pri is None else
+                            f"walk here {pri.fwd_info.graph_walk}, node state "
+                            f"{None if st is None else dict(done=st.done, running=st.running, missing=sorted(st.missing()))}")
+        if not did and self._stall_log_s > 0 and time.monotonic() - self._last_stall_scan > self._stall_log_s:
+            self._last_stall_scan = time.monotonic()
+            self._log_stalled_requests()
         if self.heartbeat_s and time.monotonic() - self._last_beat > self.heartbeat_s:
             self._last_beat = time.monotonic()
             self.comm.send(self.conductor_id, Message(CM.HEARTBEAT, ipc.SetupDone(self.worker_id)))
