@@ -68,3 +68,18 @@ def test_cosmos3_tp2_x_sp2_served_video_equals_the_single_rank_video():
     req = ("a robot", ["video"], dict(height=32, width=32, num_frames=5, num_steps=3, guidance_scale=4.0, seed=1), None)
     want = _serve("cosmos3_nano.yaml", True, req)
     assert _serve("cosmos3_nano_tp2_sp2.yaml", False, req) == want       # dit on four ranks, decoders on the last one
+
+
+def test_qwen3_omni_experts_cut_by_expert_over_four_ranks():
+    """The layout of ``configs/qwen3_omni_ep8.yaml`` at test size: thinker and talker share ONE four-rank instance
+    (attention tensor-parallel, every rank holding a quarter of the experts), encoders beside the first rank, the codec
+    beside the last."""
+    tens = {"audio": [torch.randn(8000, generator=torch.Generator().manual_seed(1)) * 0.1]}
+    req = ("describe", ["text", "audio"], dict(max_tokens=6, ignore_eos=True, temperature=0.0, max_audio_tokens=12), tens)
+    want = _serve("qwen3_omni.yaml", True, req)
+    ep = {"model": "qwen3_omni", "model_kwargs": {"expert_parallel": True},
+          "node_groups": [{"node_names": ["Thinker", "Talker"], "ranks": [0, 1, 2, 3], "tp_size": 4},
+                          {"node_names": ["audio_encoder", "vision_encoder"], "ranks": [0]},
+                          {"node_names": ["Code2Wav"], "ranks": [3]}]}
+    got = _serve(ep, False, req)
+    assert got["text"] == want["text"] and got["audio"][:2] == want["audio"][:2]
