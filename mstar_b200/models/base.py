@@ -30,6 +30,14 @@ def small_scale() -> int:
     return 4 if torch.cuda.is_available() else 1
 
 
+def seeded_init(build, seed: int = 0):
+    """``build()`` under its own generator state: modules that take torch's default random initialisation (codecs,
+    autoencoders before a checkpoint is loaded) then get the same weights in every process and replica."""
+    with torch.random.fork_rng(devices=[]):
+        torch.manual_seed(seed)
+        return build()
+
+
 class EngineType(str, Enum):
     KV_CACHE = "kv_cache"
     STATELESS = "stateless"

@@ -27,7 +27,7 @@ from ..ops import attention as attn_ops
 from ..ops import gemm
 from ..parallel.comm import CommGroup
 from ..parallel.sequence_parallel import gather_sequence, sp_seq_split
-from .base import small_scale, EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model, seeded_init
 from .sound_decoder import SoundDecoder, load_sound_decoder, pcm_layout, sound_decoder_config
 from .decoder import DecoderConfig, DecoderLM, _param
 from .dit import MoTGenTower, grid_positions, patchify, sinusoidal_embedding, unpatchify
@@ -388,8 +388,7 @@ class Cosmos3Model(Model):
                     and os.path.isdir(os.path.join(self.model_dir, "sound_tokenizer"))):
                 dec = load_sound_decoder(self.model_dir, device=device, dtype=self.dtype)
             else:
-                torch.manual_seed(11)
-                dec = SoundDecoder(self.sound_cfg).to(device=device, dtype=self.dtype).eval()
+                dec = seeded_init(lambda: SoundDecoder(self.sound_cfg), 11).to(device=device, dtype=self.dtype).eval()
             return SoundDecodeSubmodule(dec, device)
         raise KeyError(node_name)
 

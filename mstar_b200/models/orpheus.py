@@ -18,7 +18,7 @@ from ..api_server.media_io import float_to_pcm16
 from ..engine.kv_store import KVCacheConfig
 from ..graph.ir import EMIT_TO_CLIENT, GraphEdge, GraphNode, Loop
 from ..streaming import Connection, PartitionDefinition, PartitionTopology, SlidingWindowChunkPolicy, StreamingGraphEdge
-from .base import EngineType, ForwardPassArgs, Model
+from .base import EngineType, ForwardPassArgs, Model, seeded_init
 from .codec import SnacDecoder, orpheus_tokens_to_codes
 from .decoder import DecoderConfig, DecoderLM
 from .llm_common import DecoderSubmodule, LMStateMachine, lm_walks
@@ -61,7 +61,7 @@ class SnacSubmodule(NodeSubmodule):
         super().__init__(device, torch.float32)
         self.compute_dtype = compute_dtype         # fp32 weights; bf16 runs the convolutions under autocast
         kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
-        self.dec = SnacDecoder(**kw).to(device=device, dtype=torch.float32).eval()
+        self.dec = seeded_init(lambda: SnacDecoder(**kw)).to(device=device, dtype=torch.float32).eval()
 
         self.base_id = base_id
         self.gen = None

@@ -14,7 +14,7 @@ from ..api_server.media_io import float_to_pcm16
 from ..engine.kv_store import KVCacheConfig
 from ..graph.ir import EMIT_TO_CLIENT, EMPTY_DESTINATION, GraphEdge, GraphNode, Loop
 from ..streaming import Connection, LeftContextChunkPolicy, PartitionDefinition, PartitionTopology, StreamingGraphEdge
-from .base import small_scale, EngineType, ForwardPassArgs, Model
+from .base import small_scale, EngineType, ForwardPassArgs, Model, seeded_init
 from .codec import Code2Wav
 from .decoder import DecoderConfig, DecoderLM
 from .submodule_base import NodeSubmodule
@@ -136,7 +136,7 @@ class Qwen3TTSModel(Model):
         if node_name == "Codec":
             kw = (dict(n_codebooks=self.n_sub + 1, codebook_size=self.codebook, dim=16, rates=(2, 2), channels=32)
                   if self.small else dict(n_codebooks=N_CODEBOOKS, codebook_size=2048, dim=512, rates=(8, 5, 4, 3, 4)))
-            return CodecChunkSubmodule(Code2Wav(**kw).to(device).eval(), device, "codec_frames", self.left, "codec_loop")
+            return CodecChunkSubmodule(seeded_init(lambda: Code2Wav(**kw)).to(device).eval(), device, "codec_frames", self.left, "codec_loop")
         raise KeyError(node_name)
 
     def get_sampling_config(self, model_kwargs):

@@ -189,10 +189,17 @@ class Decoder(nn.Module):
 
 
 class ConvVAE(nn.Module):
-    def __init__(self, cfg: VAEConfig):
+    def __init__(self, cfg: VAEConfig, seed: int | None = 0):
+        """``seed``: the random initialisation (before a checkpoint is loaded) is drawn from its own generator state,
+        so that every process and every replica of a deployment builds the same weights."""
         super().__init__()
         self.cfg = cfg
-        self.encoder, self.decoder = Encoder(cfg), Decoder(cfg)
+        if seed is None:
+            self.encoder, self.decoder = Encoder(cfg), Decoder(cfg)
+        else:
+            with torch.random.fork_rng(devices=[]):
+                torch.manual_seed(seed)
+                self.encoder, self.decoder = Encoder(cfg), Decoder(cfg)
 
     @torch.no_grad()
     def encode(self, x: torch.Tensor, sample: bool = False, generator=None) -> torch.Tensor:

@@ -124,6 +124,7 @@ class Worker:
         self._publish_persisted = publish_persisted
         self._stall_log_s = float(os.environ.get("MSTAR_STALL_LOG_S", "15"))
         self._last_stall_scan, self._stall_logged = time.monotonic(), set()
+        self._deferred_stream_end: dict[tuple[str, str], list] = {}    # stream ends waiting for this rank's own producer
         self._deferred_new: dict[tuple[str, str], list] = {}   # NEW_REQUEST of a walk whose predecessor is still in flight here
         self._done_queue: list | None = None      # walk-completion messages held back while a batch is being finished
         self._emit_buf: list | None = None        # client-bound outputs of the batch being finished, sent as one message
@@ -329,9 +330,20 @@ class Worker:
             pri.fwd_info = b.request_info
         for name in b.producer_done or ():
             sb = pri.stream_buffers.get(name)
-            if sb is not None:
-                sb.signal_done()
-                self._stream_dirty.add((b.request_id, b.partition_name))
+            if sb is None:
+                continue
+            if self.is_tp_follower and self.topology is not None:
+                # the end of a stream is announced when the producing instance's FIRST rank has finished; a rank that
+                # follows that instance and feeds this consumer from its own copy may still have the last items in
+                # flight: the end then takes effect when this rank's own producer walk is done
+                src = next((self.requests.get((b.request_id, c.from_partition))
+                            for c in self.topology.incoming(b.partition_name) if c.edge_name == name), None)
+                if src is not None and (src.in_flight > 0 or not src.walk_state.done):
+                    self._deferred_stream_end.setdefault((b.request_id, src.partition_name), []).append(
+                        (b.partition_name, name))
+                    continue
+            sb.signal_done()
+            self._stream_dirty.add((b.request_id, b.partition_name))
         for e in b.inputs:
             self._ingest(pri, e)
         self._refresh_ready(pri)
@@ -760,6 +772,12 @@ class Worker:
                 self._send_walk_done(body)
         pri.persist = {}
         pri.new_token_counts = {}
+        for part, name in self._deferred_stream_end.pop((pri.request_id, pri.partition_name), []):
+            dst = self.requests.get((pri.request_id, part))
+            sb = dst.stream_buffers.get(name) if dst is not None else None
+            if sb is not None:
+                sb.signal_done()
+                self._stream_dirty.add((pri.request_id, part))
 
     def _send_walk_done(self, body) -> None:
         if self.profile is not None:

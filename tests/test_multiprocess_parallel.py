@@ -19,7 +19,7 @@ from mstar_b200.conductor.deployment import load_config
 ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs")
 
 
-def _serve(cfg_or_name, in_process, request, timeout=120):
+def _serve(cfg_or_name, in_process, request, timeout=120, keep_bytes=False):
     cfg = load_config(os.path.join(ROOT, cfg_or_name)) if isinstance(cfg_or_name, str) else dict(cfg_or_name)
     if cfg["model"] != "tiny":
         cfg["model_kwargs"] = dict(cfg.get("model_kwargs") or {}, small=True)
@@ -30,6 +30,8 @@ def _serve(cfg_or_name, in_process, request, timeout=120):
         prompt, outs, kw, tensors = request
         r = s.collect_results(s.submit_request(prompt, output_modalities=outs, model_kwargs=kw, tensors=tensors), timeout)
         assert "error" not in r, r["error"][0].data
+        if keep_bytes:
+            return {m: b"".join(c.data for c in r[m]) for m in outs}
         return {m: (len(r[m]), sum(len(c.data) for c in r[m]), hashlib.md5(b"".join(c.data for c in r[m])).hexdigest())
                 for m in outs}
     finally:
@@ -66,8 +68,28 @@ def test_qwen3_omni_thinker_and_talker_tp2_with_encoders_and_codec_beside_them()
 
 def test_cosmos3_tp2_x_sp2_served_video_equals_the_single_rank_video():
     req = ("a robot", ["video"], dict(height=32, width=32, num_frames=5, num_steps=3, guidance_scale=4.0, seed=1), None)
-    want = _serve("cosmos3_nano.yaml", True, req)
-    assert _serve("cosmos3_nano_tp2_sp2.yaml", False, req) == want       # dit on four ranks, decoders on the last one
+    want = _frames(_serve("cosmos3_nano.yaml", True, req, keep_bytes=True)["video"])
+    got = _frames(_serve("cosmos3_nano_tp2_sp2.yaml", False, req, keep_bytes=True)["video"])   # dit on four ranks
+    assert got.shape == want.shape and got.shape[0] == 5
+    # the sharded sums round differently in the last bit: a pixel that flips a grey level moves its JPEG block a little
+    diff = abs(got.astype(int) - want.astype(int))
+    assert diff.max() <= 6 and diff.mean() < 0.05 and want.std() > 10
+
+
+def _frames(avi: bytes):
+    """The JPEG frames of a Motion-JPEG AVI as one uint8 array [frames, H, W, 3]."""
+    import io
+    import numpy as np
+    from PIL import Image
+    out, pos = [], 0
+    while True:
+        a = avi.find(b"\xff\xd8", pos)
+        if a < 0:
+            break
+        b = avi.find(b"\xff\xd9", a)
+        out.append(np.asarray(Image.open(io.BytesIO(avi[a:b + 2])).convert("RGB")))
+        pos = b + 2
+    return np.stack(out)
 
 
 def test_qwen3_omni_experts_cut_by_expert_over_four_ranks():
