@@ -894,3 +894,49 @@ def load_qwen3_omni_code2wav(m, src, prefix: str = "code2wav.") -> dict:
     same(f"decoder.{nb + 1}", "out_act", ab)
     same(f"decoder.{nb + 2}.conv", "out.conv", wb)
     return st.done()
+
+
+# ------------------------------------------------------------------ V-JEPA 2 (Hugging Face names)
+def _vjepa2_layers(st: _Strict, n: int, src: str, dst: str) -> None:
+    for i in range(n):
+        p, d = f"{src}layer.{i}.", f"{dst}layers.{i}."
+        ws = [st.take(f"{p}attention.{n_}.weight") for n_ in ("query", "key", "value")]
+        bs = [st.take(f"{p}attention.{n_}.bias") for n_ in ("query", "key", "value")]
+        if None not in ws and None not in bs:
+            st.write(d + "qkv_w", torch.cat(ws))
+            st.write(d + "qkv_b", torch.cat(bs))
+        for hf, ours in (("attention.proj", "o"), ("norm1", "n1"), ("norm2", "n2"), ("mlp.fc1", "fc1"), ("mlp.fc2", "fc2")):
+            st.write(f"{d}{ours}_w", st.take(f"{p}{hf}.weight"))
+            st.write(f"{d}{ours}_b", st.take(f"{p}{hf}.bias"))
+    st.write(dst + "fn_w", st.take(src + "layernorm.weight"))
+    st.write(dst + "fn_b", st.take(src + "layernorm.bias"))
+
+
+@torch.no_grad()
+def load_vjepa2_encoder(enc, src, prefix: str = "encoder.") -> dict:
+    """``VJepa2Encoder`` from the ``encoder.*`` tensors of a Hugging Face V-JEPA 2 checkpoint
+    (``facebook/vjepa2-vit*-fpc64-*``): Conv3d tubelet embedding flattened to a GEMM weight, separate query / key /
+    value projections stacked. Strict over the prefix. Reference: mstar/model/vjepa2/weight_loader.py:1-60."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(enc, T, "V-JEPA 2 encoder")
+    w = st.take("embeddings.patch_embeddings.proj.weight")
+    st.write("patch_w", None if w is None else w.reshape(w.shape[0], -1))
+    st.write("patch_b", st.take("embeddings.patch_embeddings.proj.bias"))
+    _vjepa2_layers(st, len(enc.enc.layers), "", "enc.")
+    return st.done()
+
+
+@torch.no_grad()
+def load_vjepa2_predictor(pred, src, prefix: str = "predictor.") -> dict:
+    """``MaskedPredictor`` from the ``predictor.*`` tensors of the same checkpoint: ``predictor_embeddings``, the mask
+    tokens ([n, 1, 1, hidden] -> [n, hidden]), the layers, ``layernorm`` and ``proj``. Strict over the prefix."""
+    T = {k[len(prefix):]: v for k, v in _tensors_of(src).items() if k.startswith(prefix)}
+    st = _Strict(pred, T, "V-JEPA 2 predictor")
+    st.write("inp_w", st.take("embeddings.predictor_embeddings.weight"))
+    st.write("inp_b", st.take("embeddings.predictor_embeddings.bias"))
+    m = st.take("embeddings.mask_tokens")
+    st.write("mask_tokens", None if m is None else m.reshape(m.shape[0], -1))
+    _vjepa2_layers(st, len(pred.blocks.layers), "", "blocks.")
+    st.write("out_w", st.take("proj.weight"))
+    st.write("out_b", st.take("proj.bias"))
+    return st.done()

@@ -24,7 +24,7 @@ from ..engine.piecewise_graph import PiecewiseCudaGraphRunner
 from ..graph.ir import EMIT_TO_CLIENT, GraphEdge, GraphNode, Loop, Sequential
 from ..ops import gemm
 from .base import small_scale, EngineType, ForwardPassArgs, Model
-from .encoders import EncoderConfig, TransformerEncoder, VisionEncoder
+from .encoders import EncoderConfig, TransformerEncoder
 from .submodule_base import NodeSubmodule
 
 
@@ -32,32 +32,108 @@ def _p(shape, dtype, device):
     return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=False)
 
 
-class MaskedPredictor(nn.Module):
-    """Narrow transformer over [context tokens ‖ mask tokens at the target positions] -> embeddings of the targets."""
+def rope3d(ids: torch.Tensor, grid_hw: tuple[int, int], head_dim: int):
+    """The published rotary embedding of V-JEPA 2 for tokens at flat tubelet indices ``ids`` (frame-major, then rows,
+    then columns): the head is cut into three bands of 2 * ((D // 3) // 2) channels for the frame, row and column
+    position (what is left over is not rotated). Inside a band adjacent channels (2i, 2i+1) form the rotated pair,
+    while the angle of channel j is position x 10000^(-(j mod s/2) / (s/2)) — the angle table is tiled over the band,
+    not repeated per pair (transformers/models/vjepa2/modeling_vjepa2.py: rotate_queries_or_keys). Returns a function
+    for [T, heads, D] tensors."""
+    h, w = grid_hw
+    ids = ids.long()
+    frame = ids // (h * w)
+    row = (ids - frame * h * w) // w
+    col = ids - frame * h * w - row * w
+    s = 2 * ((head_dim // 3) // 2)
+    omega = 1.0 / 10000 ** (torch.arange(s // 2, dtype=torch.float32, device=ids.device) / (s / 2.0))
+    ang = torch.cat([(p.float()[:, None] * omega).repeat(1, 2) for p in (frame, row, col)], dim=-1)     # [T, 3s]
+    cs, sn = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
 
-    def __init__(self, enc_dim: int, c: EncoderConfig, max_tokens: int, device):
+    def apply(x):
+        xf = x.float()
+        r = xf[..., :3 * s]
+        pair = r.unflatten(-1, (-1, 2))
+        y = torch.stack((-pair[..., 1], pair[..., 0]), dim=-1).flatten(-2)
+        return torch.cat([r * cs + y * sn, xf[..., 3 * s:]], dim=-1).to(x.dtype)
+    return apply
+
+
+class VJepa2Encoder(nn.Module):
+    """ViT over tubelets (2 frames x patch x patch pixels) with the 3-axis rotary embedding and no position table;
+    pre-LN blocks, exact GELU, final LayerNorm. Reference: mstar/model/vjepa2/components/vit_encoder.py."""
+
+    def __init__(self, c: EncoderConfig, patch: int = 16, tubelet: int = 2, in_channels: int = 3, device="cpu"):
+        super().__init__()
+        self.c, self.patch, self.tp = c, patch, tubelet
+        pdim = in_channels * tubelet * patch * patch
+        self.patch_w, self.patch_b = _p((c.hidden_size, pdim), c.dtype, device), _p((c.hidden_size,), c.dtype, device)
+        self.enc = TransformerEncoder(c, device)
+
+    def init_random(self, seed=0):
+        g = torch.Generator().manual_seed(seed)
+        self.patch_w.data.copy_((torch.randn(self.patch_w.shape, generator=g) / math.sqrt(self.patch_w.shape[-1])).to(self.c.dtype))
+        self.patch_b.data.zero_()
+        self.enc.init_random(seed + 1)
+        return self
+
+    def patches(self, vid: torch.Tensor):
+        """[C, T, H, W] clip (or [C, H, W] image, repeated over the tubelet) -> ([t*h*w, C*tp*p*p], (t, h, w))."""
+        if vid.dim() == 3:
+            vid = vid[:, None].expand(-1, self.tp, -1, -1)
+        if vid.shape[1] < self.tp:
+            vid = vid.repeat(1, self.tp, 1, 1)
+        C, T, H, W = vid.shape
+        p, tp = self.patch, self.tp
+        t, h, w = T // tp, H // p, W // p
+        x = vid[:, :t * tp, :h * p, :w * p].reshape(C, t, tp, h, p, w, p).permute(1, 3, 5, 0, 2, 4, 6)
+        return x.reshape(t * h * w, C * tp * p * p), (t, h, w)
+
+    def forward(self, videos: list[torch.Tensor]):
+        """Returns (features [sum tokens, hidden], tokens per clip, grids)."""
+        toks, grids, ids = [], [], []
+        for v in videos:
+            pt, g = self.patches(v.to(self.c.dtype))
+            toks.append(pt), grids.append(g)
+            ids.append(torch.arange(pt.shape[0], device=pt.device))
+        x = gemm.linear(torch.cat(toks).contiguous(), self.patch_w, bias=self.patch_b)
+        lens = [g[0] * g[1] * g[2] for g in grids]
+        if len({(g[1], g[2]) for g in grids}) != 1:
+            raise ValueError("clips of one batch must share their frame size")
+        rope = rope3d(torch.cat(ids), (grids[0][1], grids[0][2]), self.c.head_dim)
+        return self.enc(x, lens, rope=rope), lens, grids
+
+
+class MaskedPredictor(nn.Module):
+    """Narrow transformer over [context tokens ‖ mask tokens at the target positions] -> embeddings of the targets;
+    positions enter through the same 3-axis rotary embedding as in the encoder (the published predictor sorts the
+    tokens by position first, which changes nothing for full attention). Reference:
+    mstar/model/vjepa2/components/predictor.py."""
+
+    def __init__(self, enc_dim: int, c: EncoderConfig, device, num_mask_tokens: int = 10):
         super().__init__()
         self.c = c
-        self.inp = _p((c.hidden_size, enc_dim), c.dtype, device)
-        self.out = _p((enc_dim, c.hidden_size), c.dtype, device)
-        self.mask_token = _p((1, c.hidden_size), c.dtype, device)
-        self.pos = _p((max_tokens, c.hidden_size), c.dtype, device)
+        self.inp_w, self.inp_b = _p((c.hidden_size, enc_dim), c.dtype, device), _p((c.hidden_size,), c.dtype, device)
+        self.out_w, self.out_b = _p((enc_dim, c.hidden_size), c.dtype, device), _p((enc_dim,), c.dtype, device)
+        self.mask_tokens = _p((num_mask_tokens, c.hidden_size), c.dtype, device)
         self.blocks = TransformerEncoder(c, device)
 
     def init_random(self, seed=0):
         g = torch.Generator().manual_seed(seed)
-        for p in (self.inp, self.out, self.mask_token, self.pos):
+        for p in (self.inp_w, self.out_w, self.mask_tokens):
             p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
+        self.inp_b.data.zero_(), self.out_b.data.zero_()
         self.blocks.init_random(seed + 1)
         return self
 
-    def forward(self, ctx_tokens, ctx_idx, tgt_idx, runner: PiecewiseCudaGraphRunner):
-        x = gemm.linear(ctx_tokens, self.inp) + self.pos[ctx_idx]
-        m = self.mask_token.expand(tgt_idx.numel(), -1) + self.pos[tgt_idx]
-        seq = torch.cat([x, m]).contiguous()
+    def forward(self, ctx_tokens, ctx_idx, tgt_idx, runner: PiecewiseCudaGraphRunner, grid_hw: tuple[int, int],
+                mask_index: int = 1):
+        x = gemm.linear(ctx_tokens, self.inp_w, bias=self.inp_b)
+        m = self.mask_tokens[mask_index % self.mask_tokens.shape[0]].expand(tgt_idx.numel(), -1)
+        seq = torch.cat([x, m.to(x.dtype)]).contiguous()
         n = seq.shape[0]
-        h = runner.run("predictor_blocks", lambda s: self.blocks(s, [n]), seq)
-        return gemm.linear(h[x.shape[0]:].contiguous(), self.out)
+        rope = rope3d(torch.cat([ctx_idx, tgt_idx]), grid_hw, self.c.head_dim)
+        h = runner.run("predictor_blocks", lambda s_: self.blocks(s_, [n], rope=rope), seq)
+        return gemm.linear(h[x.shape[0]:].contiguous(), self.out_w, bias=self.out_b)
 
 
 class ActionConditionedPredictor(nn.Module):
@@ -97,7 +173,7 @@ class ActionConditionedPredictor(nn.Module):
 
 
 class VideoEncoderSubmodule(NodeSubmodule):
-    def __init__(self, enc: VisionEncoder, device):
+    def __init__(self, enc: VJepa2Encoder, device):
         super().__init__(device, enc.c.dtype)
         self.enc = enc
 
@@ -120,13 +196,14 @@ class PredictorSubmodule(NodeSubmodule):
         md = ni.kwargs
         st = engine_inputs.per_request_states[ni.request_id]
         if graph_walk == "prefill_video":
+            grid = [int(x) for x in ni.tensor_inputs["grid"][0].tolist()]
             feats = ni.tensor_inputs["video_features"][0].to(self.device)
             n = feats.shape[0]
             g = torch.Generator().manual_seed(int(md.get("seed", 0)))
             perm = torch.randperm(n, generator=g)
             k = max(1, int(n * float(md.get("mask_ratio", 0.5))))
             tgt, ctx = perm[:k].sort().values.to(self.device), perm[k:].sort().values.to(self.device)
-            pred = self.masked(feats[ctx].contiguous(), ctx, tgt, self.runner)
+            pred = self.masked(feats[ctx].contiguous(), ctx, tgt, self.runner, (grid[1], grid[2]))
             return {"embeddings": pred.float().cpu(), "target_index": tgt.cpu()}
         grid = [int(x) for x in ni.tensor_inputs["grid"][0].tolist()]
         P = grid[1] * grid[2]
@@ -168,13 +245,11 @@ class VJepa2Model(Model):
         self.small, self.dtype = small, dt
         k = small_scale()
         if small:
-            self.enc_cfg, self.patch = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt), 4
-            self.pred_cfg = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt)
-            self.max_tokens = 256
+            self.enc_cfg, self.patch = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, act="gelu_erf", dtype=dt), 4
+            self.pred_cfg = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, act="gelu_erf", dtype=dt)
         else:      # ViT-L encoder, 12-layer 384-wide predictor
-            self.enc_cfg, self.patch = EncoderConfig(1024, 24, 16, 64, 4096, dtype=dt), 16
-            self.pred_cfg = EncoderConfig(384, 12, 12, 32, 1536, dtype=dt)
-            self.max_tokens = 32 * 16 * 16
+            self.enc_cfg, self.patch = EncoderConfig(1024, 24, 16, 64, 4096, act="gelu_erf", dtype=dt), 16
+            self.pred_cfg = EncoderConfig(384, 12, 12, 32, 1536, act="gelu_erf", dtype=dt)
         self.ac_cfg = EncoderConfig(32 * k, 1, 2, 16 * k, 64 * k, dtype=dt) if small else EncoderConfig(1024, 24, 16, 64, 4096, dtype=dt)
         self.action_dim, self.state_dim = 7, 7
 
@@ -183,8 +258,7 @@ class VJepa2Model(Model):
             return GraphNode("video_encoder", {"video"}, [GraphEdge("predictor", n) for n in ("video_features", "grid") + tuple(extra)])
         emb = [GraphEdge(EMIT_TO_CLIENT, "embeddings", output_modality="embeddings")]
         walks = {
-            "prefill_video": Sequential([GraphNode("video_encoder", {"video"}, [GraphEdge("predictor", "video_features")]),
-                                         GraphNode("predictor", {"video_features"}, emb)]),
+            "prefill_video": Sequential([enc(), GraphNode("predictor", {"video_features", "grid"}, emb)]),
             "prefill_video_encoder_only": GraphNode("video_encoder", {"video"},
                                                     [GraphEdge(EMIT_TO_CLIENT, "video_features", output_modality="embeddings")]),
         }
@@ -212,10 +286,16 @@ class VJepa2Model(Model):
 
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "video_encoder":
-            enc = VisionEncoder(self.enc_cfg, patch=self.patch, temporal_patch=2, pos="rope2d", device=device).init_random(0)
+            enc = VJepa2Encoder(self.enc_cfg, patch=self.patch, tubelet=2, device=device).init_random(0)
+            if not (self.skip_weight_loading or self.model_dir is None):
+                from .checkpoints import load_vjepa2_encoder
+                load_vjepa2_encoder(enc, self.model_dir)
             return VideoEncoderSubmodule(enc, device)
         if node_name == "predictor":
-            masked = MaskedPredictor(self.enc_cfg.hidden_size, self.pred_cfg, self.max_tokens, device).init_random(1)
+            masked = MaskedPredictor(self.enc_cfg.hidden_size, self.pred_cfg, device).init_random(1)
+            if not (self.skip_weight_loading or self.model_dir is None):
+                from .checkpoints import load_vjepa2_predictor
+                load_vjepa2_predictor(masked, self.model_dir)
             ac = (ActionConditionedPredictor(self.enc_cfg.hidden_size, self.ac_cfg, self.action_dim, self.state_dim,
                                              device).init_random(2) if self.action_conditioned else None)
             return PredictorSubmodule(masked, ac, device)
