@@ -55,6 +55,9 @@ class APIServer:
         self.running = True
         self.stats = dict(submitted=0, completed=0, failed=0, aborted=0)
         self.after_message_hooks: list = []        # called on the result thread after every handled message
+        # modality -> dtype name of client-bound tensors whose bytes ARE the payload (the model's ``postprocess`` would
+        # only copy them out): 16-bit PCM quantised by the codec
+        self._raw_payload: dict[str, str] = dict(getattr(self.model, "raw_payload_dtypes", None) or {})
         self._thread = threading.Thread(target=self._process_messages, daemon=True, name="api-results")
 
     # ---- lifecycle ----
@@ -244,8 +247,11 @@ class APIServer:
             pr = self.pending.get(b.request_id)
         if pr is None or pr.done:
             return
-        ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
-        data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
+        if len(b.tensors) == 1 and self._raw_payload.get(b.modality) == b.tensors[0].dtype:
+            data = self.tensors.read_bytes(b.tensors[0])       # already in its wire format: bytes straight from the block
+        else:
+            ts = [self.tensors.read(ti, "cpu") for ti in b.tensors]
+            data = self.model.postprocess(ts[0] if len(ts) == 1 else ts, b.modality, pr.model_kwargs)
         pr.t_last_chunk = time.time()
         if pr.t_first_chunk is None:
             pr.t_first_chunk = pr.t_last_chunk

@@ -145,7 +145,16 @@ class ShmArenaReader:
         self.pin = pin          # page-lock producers' segments as they are mapped (consumer uploads to a GPU)
         self.pinned_segments = 0
 
+    def read_bytes(self, base_name: str, seg: int, off: int, nbytes: int) -> bytes:
+        """The block's bytes as one ``bytes`` object (one copy, no tensor in between)."""
+        if not nbytes:
+            return b""
+        return ctypes.string_at(self._ptr(base_name, seg, off), nbytes)
+
     def view(self, base_name: str, seg: int, off: int, nbytes: int, dtype: torch.dtype, dims) -> torch.Tensor:
+        return _tensor_at(self._ptr(base_name, seg, off), nbytes, dtype, dims)
+
+    def _ptr(self, base_name: str, seg: int, off: int) -> int:
         key = (base_name, seg)
         h = self._segs.get(key)
         if h is None:
@@ -158,7 +167,7 @@ class ShmArenaReader:
         ptr = self.lib.mstar_arena_view_ptr(h, off)
         if not ptr:
             raise ValueError("arena: offset outside the segment")
-        return _tensor_at(ptr, nbytes, dtype, dims)
+        return ptr
 
     def close(self) -> None:
         for h in self._segs.values():

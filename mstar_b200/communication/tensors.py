@@ -206,6 +206,23 @@ class TensorCommunicationManager:
             t = t.to(device, non_blocking=True)      # GPU -> GPU: peer copy over NVLink
         return t
 
+    def read_bytes(self, info: TensorPointerInfo) -> bytes:
+        """The tensor's raw bytes (row-major), without building a tensor when it sits in a shared-memory block: what
+        the API process needs from payloads that are already in their wire format (16-bit PCM)."""
+        src_store = _PROCESS_STORES.get(info.source_entity)
+        t = src_store.get(info.uuid) if src_store is not None else None
+        if t is None and info.shm_segment and info.shm_segment != "cuda_ipc":
+            base, seg = info.shm_segment.rsplit("#", 1)
+            with self._arena_lock:
+                if self._reader is None:
+                    self._reader = ShmArenaReader(pin=self.device.type == "cuda")
+                reader = self._reader
+            self.rx_bytes += info.nbytes
+            return reader.read_bytes(base, int(seg), info.shm_offset, info.nbytes)
+        if t is None:
+            t = self.read(info, "cpu")
+        return t.detach().cpu().contiguous().numpy().tobytes()
+
     def _read_cuda_ipc(self, info: TensorPointerInfo) -> torch.Tensor:
         from torch.multiprocessing.reductions import rebuild_cuda_tensor
         handle, storage_offset = info.cuda_ipc      # type: ignore[attr-defined]

@@ -169,6 +169,7 @@ class SnacSubmodule(NodeSubmodule):
 
 class OrpheusModel(Model):
     name = "orpheus"
+    raw_payload_dtypes = {"audio": "int16"}        # the codec's graph quantises to 16-bit PCM: its bytes go out as they are
 
     def __init__(self, model_dir=None, skip_weight_loading=False, small: bool = False, page_size: int = 128,
                  max_num_pages: int = 2048, codec_dtype: str = "float32", **kw):
