@@ -91,7 +91,7 @@ class HiggsAudioModel(Model):
                 lm.init_random(0)
             else:
                 from .loader import load_decoder_from_hf
-                load_decoder_from_hf(lm, self.model_dir)
+                load_decoder_from_hf(lm, self.model_dir, strict=False)    # layout not checked against a published file
             return MultimodalDecoderSubmodule(lm, device, {"audio_features": AUDIO_TOKEN}, eos_ids=(EOS,))
         raise KeyError(node_name)
 

@@ -80,14 +80,22 @@ class _Pending:
 
 @torch.no_grad()
 def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", head_name: str = "lm_head.weight",
-                         layer_filter: Callable[[str], str | None] | None = None) -> dict:
+                         layer_filter: Callable[[str], str | None] | None = None, embed_name: str = "embed_tokens.weight",
+                         strict: bool = True, ignore: tuple[str, ...] = ("rotary_emb.inv_freq",)) -> dict:
     """Fill a (possibly tensor-parallel) ``DecoderLM`` from a Hugging Face Llama / Qwen2 / Qwen3 / Qwen3-MoE style
     checkpoint. ``layer_filter`` may rewrite or drop names first (towers that live under another prefix, e.g.
-    ``thinker.model.``)."""
+    ``thinker.model.``); ``embed_name`` is the token table's name under the prefix (``codec_embedding.weight`` for a
+    speech-token decoder). ``strict``: every parameter of the decoder must have been written (a tied head may take the
+    token table) and every tensor under the prefix must have found a parameter, else ``CheckpointMismatch``; the
+    result lists both in any case."""
     cfg, tp = lm.cfg, lm.tp
     Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
     pend = _Pending()
     loaded = 0
+    unused: list[str] = []
+    for p_ in lm.parameters():          # a parameter that no tensor reaches still holds this after the load
+        if p_.is_floating_point():
+            p_.data.fill_(float("nan"))
     rx = re.compile(r"layers\.(\d+)\.(.+)")
     for name, t in iter_safetensors(model_dir):
         if layer_filter is not None:
@@ -102,7 +110,7 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
         if not name.startswith(prefix):
             continue
         key = name[len(prefix):]
-        if key == "embed_tokens.weight":
+        if key == embed_name:
             if lm.embed_tokens is not None:
                 lm.embed_tokens.copy_(lm.vocab_rows(t.to(cfg.dtype)))
                 loaded += 1
@@ -113,6 +121,8 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
             continue
         m = rx.match(key)
         if not m or int(m.group(1)) >= len(lm.layers):
+            if not key.endswith(ignore):
+                unused.append(name)
             continue
         li, sub = int(m.group(1)), m.group(2)
         layer = lm.layers[li]
@@ -162,10 +172,23 @@ def load_decoder_from_hf(lm: DecoderLM, model_dir: str, prefix: str = "model.", 
         elif sub == "mlp.shared_expert_gate.weight" and getattr(layer.mlp, "shared", None) is not None:
             layer.mlp.shared_gate.copy_(t.to(cfg.dtype))
         else:
+            if not sub.endswith(ignore):
+                unused.append(name)
             continue
         loaded += 1
     if getattr(lm, "vocab_parallel", False):
         torch.cuda.synchronize(lm.device_)
         lm.tp.symm.barrier()            # every rank's table shard is in place before anyone gathers rows from it
         torch.cuda.synchronize(lm.device_)
-    return {"loaded": loaded, "incomplete": [k for k in pend.parts]}
+    # a head that the checkpoint does not store is tied to the token table
+    if lm.lm_head is not None and lm.embed_tokens is not None and bool(torch.isnan(lm.lm_head).all()) \
+            and lm.lm_head.shape == lm.embed_tokens.shape and not bool(torch.isnan(lm.embed_tokens).any()):
+        lm.lm_head.copy_(lm.embed_tokens)
+    missing = [n for n, p_ in lm.named_parameters() if p_.is_floating_point() and bool(torch.isnan(p_).any())]
+    incomplete = [str(k) for k in pend.parts]
+    if strict and (missing or unused or incomplete):
+        from .checkpoints import CheckpointMismatch
+        raise CheckpointMismatch(f"decoder checkpoint under {prefix!r}: {len(missing)} parameters not loaded {missing[:5]}, "
+                                 f"{len(unused)} tensors without a parameter {unused[:5]}, incomplete fused groups "
+                                 f"{incomplete[:5]}")
+    return {"loaded": loaded, "incomplete": incomplete, "missing": missing, "unused": unused}

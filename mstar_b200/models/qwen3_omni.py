@@ -248,7 +248,8 @@ class Qwen3OmniModel(Model):
             lm = DecoderLM(self.k_cfg, tp=tp_group, device=device)
             if load:
                 from .loader import load_decoder_from_hf
-                load_decoder_from_hf(lm, self.model_dir, prefix="talker.model.", head_name="talker.codec_head.weight")
+                load_decoder_from_hf(lm, self.model_dir, prefix="talker.model.", head_name="talker.codec_head.weight",
+                                     embed_name="codec_embedding.weight")
             else:
                 lm.init_random(2)
             if self.fp8_experts:

@@ -130,7 +130,8 @@ class Qwen3TTSModel(Model):
             pred = CodePredictor(self.pred_cfg, self.cfg.hidden_size, self.n_sub, self.codebook, device).init_random(1)
             if not (self.skip_weight_loading or self.model_dir is None):
                 from .loader import load_decoder_from_hf
-                load_decoder_from_hf(lm, self.model_dir, prefix="talker.model.", head_name="talker.codec_head.weight")
+                load_decoder_from_hf(lm, self.model_dir, prefix="talker.model.", head_name="talker.codec_head.weight",
+                                     strict=False)       # this checkpoint layout has not been checked against a published file
             return TalkerSubmodule(lm, pred, device, num_slots=64, codec_eos=self.codec_eos, cond_edge="text_ids",
                                    cond_is_ids=True, cond_dim=0, loop_name="talker_loop", text_vocab=self.text_vocab)
         if node_name == "Codec":

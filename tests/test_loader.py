@@ -75,3 +75,34 @@ def test_named_tensor_loader_reports_mismatches(tmp_path):
     save_file({"weight": torch.ones(3, 4), "extra": torch.zeros(2)}, str(tmp_path / "model.safetensors"))
     rep = load_named_tensors(m, str(tmp_path))
     assert rep["missing"] == ["bias"] and rep["unexpected"] == ["extra"] and torch.equal(m.weight.data, torch.ones(3, 4))
+
+
+def test_decoder_loader_is_strict_and_ties_a_missing_head(tmp_path):
+    import pytest
+    from safetensors.torch import save_file
+    from mstar_b200.models.checkpoints import CheckpointMismatch
+    cfg = DecoderConfig(hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8, intermediate_size=64,
+                        vocab_size=50, dtype=torch.float32)
+    sd = _write_hf(tmp_path, cfg)
+    for f in tmp_path.iterdir():
+        f.unlink()
+    for mutate in (lambda d: d.pop("model.layers.1.post_attention_layernorm.weight"),          # a parameter stays unloaded
+                   lambda d: d.update({"model.layers.0.self_attn.rotary.weight": torch.zeros(2)}),  # a tensor finds no home
+                   lambda d: d.pop("model.layers.0.mlp.up_proj.weight")):                          # half of a fused group
+        bad = dict(sd)
+        mutate(bad)
+        d = tmp_path / f"bad{len(list(tmp_path.iterdir()))}"
+        d.mkdir()
+        save_file({k: v.contiguous() for k, v in bad.items()}, str(d / "model.safetensors"))
+        with pytest.raises(CheckpointMismatch):
+            load_decoder_from_hf(DecoderLM(cfg), str(d))
+        info = load_decoder_from_hf(DecoderLM(cfg), str(d), strict=False)
+        assert info["missing"] or info["unused"] or info["incomplete"]
+    tied = {k: v for k, v in sd.items() if k != "lm_head.weight"}
+    tied["model.rotary_emb.inv_freq"] = torch.zeros(4)                  # old checkpoints carry this buffer: ignored
+    d = tmp_path / "tied"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in tied.items()}, str(d / "model.safetensors"))
+    lm = DecoderLM(cfg)
+    info = load_decoder_from_hf(lm, str(d))
+    assert not info["missing"] and torch.equal(lm.lm_head, lm.embed_tokens)

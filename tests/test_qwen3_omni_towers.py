@@ -197,3 +197,56 @@ def test_code2wav_matches_hugging_face_and_chunks_continue_each_other():
         mutate(bad)
         with pytest.raises(ck.CheckpointMismatch):
             ck.load_qwen3_omni_code2wav(ours, bad)
+
+
+def test_talker_backbone_with_its_gated_shared_expert_matches_hugging_face(tmp_path):
+    """``talker.model.*`` (routed experts plus a sigmoid-gated shared expert, token table under ``codec_embedding``)
+    loaded by the strict decoder loader against ``Qwen3OmniMoeTalkerModel``."""
+    from mstar_b200.engine.cache_manager import BatchedCacheManager
+    from mstar_b200.engine.kv_store import KVCacheConfig
+    from mstar_b200.models.decoder import DecoderConfig, DecoderLM
+    from mstar_b200.models.loader import load_decoder_from_hf
+    torch.manual_seed(0)
+    hc = hf_cfg.Qwen3OmniMoeTalkerTextConfig(
+        vocab_size=96, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, num_experts=4, num_experts_per_tok=2,
+        moe_intermediate_size=32, shared_expert_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1,
+        mlp_only_layers=[], attention_bias=False, pad_token_id=0,
+        rope_parameters={"rope_type": "default", "rope_theta": 1e6, "mrope_section": [2, 3, 3], "mrope_interleaved": True})
+    hf = hf_omni.Qwen3OmniMoeTalkerModel(hc).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.1)
+        if "norm" in n:
+            p.data.add_(1.0)
+    sd = {"talker.codec_head.weight": torch.randn(96, 64) * 0.1}
+    for k, v in hf.state_dict().items():
+        if k.endswith("mlp.experts.gate_up_proj"):
+            for e in range(v.shape[0]):
+                g, u = v[e].chunk(2, dim=0)
+                base = "talker.model." + k[:-len("gate_up_proj")] + f"{e}."
+                sd[base + "gate_proj.weight"], sd[base + "up_proj.weight"] = g.clone(), u.clone()
+        elif k.endswith("mlp.experts.down_proj"):
+            for e in range(v.shape[0]):
+                sd["talker.model." + k[:-len("down_proj")] + f"{e}.down_proj.weight"] = v[e].clone()
+        else:
+            sd["talker.model." + k] = v.clone()
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(tmp_path / "model.safetensors"))
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                        vocab_size=96, rope_theta=1e6, qk_norm=True, num_experts=4, num_experts_per_tok=2,
+                        moe_intermediate_size=32, shared_expert_intermediate_size=48, norm_topk_prob=True,
+                        dtype=torch.float32)
+    lm = DecoderLM(cfg)
+    info = load_decoder_from_hf(lm, str(tmp_path), prefix="talker.model.", head_name="talker.codec_head.weight",
+                                embed_name="codec_embedding.weight")
+    assert not info["missing"] and torch.equal(lm.embed_tokens, sd["talker.model.codec_embedding.weight"])
+    assert torch.equal(lm.lm_head, sd["talker.codec_head.weight"])
+    T = 9
+    ids = torch.randint(0, 96, (T,))
+    kvc = KVCacheConfig(2, 2, 16, max_seq_len=64, max_num_pages=8, page_size=16, num_qo_heads=4, dtype=torch.float32)
+    with torch.no_grad():
+        x = hf.codec_embedding(ids)
+        want = hf(inputs_embeds=x[None], position_ids=torch.arange(T)[None, None].expand(3, 1, T)).last_hidden_state[0]
+        cm = BatchedCacheManager(kvc, "cpu", max_batch=2, max_tokens=64)
+        cm.add_request("r")
+        got = lm.forward_hidden(lm.embed(ids), cm.plan(["r"], [T], group=2))
+    assert (got - want).abs().max().item() < 1e-4
