@@ -122,7 +122,8 @@ class WhisperDecoder(nn.Module):
             a = attn_ops.attention(q, cplan, k=pool.k[i], v=pool.v[i])
             x = gemm.linear(a.reshape(-1, H), L.co_w, bias=L.co_b, residual=x)
             h, _ = norm_ops.norm(x, L.ln3_w, 1e-5, bias=L.ln3_b, layernorm=True)
-            h = gemm.linear(h, L.fc1_w, bias=L.fc1_b, epilogue=gemm.EPILOGUE_GELU)
+            # the published weights were trained with the exact (erf) GELU; the GEMM's fused epilogue is the tanh form
+            h = torch.nn.functional.gelu(gemm.linear(h, L.fc1_w, bias=L.fc1_b).float()).to(x.dtype)
             x = gemm.linear(h, L.fc2_w, bias=L.fc2_b, residual=x)
         h, _ = norm_ops.norm(x, self.lnf_w, 1e-5, bias=self.lnf_b, layernorm=True)
         rows = h.index_select(0, ctx.logit_rows)
@@ -184,11 +185,11 @@ class WhisperModel(Model):
         self.small, self.dtype, self.max_batch = small, dt, max_batch
         if small:
             k = small_scale()
-            self.enc_cfg = EncoderConfig(64 * k, 2, 4, 16 * k, 128 * k, dtype=dt, eps=1e-5)
+            self.enc_cfg = EncoderConfig(64 * k, 2, 4, 16 * k, 128 * k, act="gelu_erf", dtype=dt, eps=1e-5)
             self.dec_kw = dict(vocab=51866, hidden=64 * k, layers=2, heads=4, ffn=128 * k)
             self.n_mels, self.max_audio = 16, 200
         else:
-            self.enc_cfg = EncoderConfig(1280, 32, 20, 64, 5120, dtype=dt, eps=1e-5)
+            self.enc_cfg = EncoderConfig(1280, 32, 20, 64, 5120, act="gelu_erf", dtype=dt, eps=1e-5)
             self.dec_kw = dict()
             self.n_mels, self.max_audio = 128, 1500
         self.sm = LMStateMachine("decoder")

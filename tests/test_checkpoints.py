@@ -168,8 +168,8 @@ def test_whisper_loaders_are_strict_and_the_encoder_matches_hugging_face():
             if "embed_positions" not in n:
                 p.copy_(torch.randn_like(p) * (0.15 if p.dim() > 1 else 0.1) + (1.0 if "layer_norm.weight" in n else 0.0))
     sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
-    ec = EncoderConfig(hidden_size=64, num_layers=2, num_heads=4, head_dim=16, ffn_dim=128, norm="layernorm", act="gelu",
-                       qkv_bias=True, eps=1e-5, dtype=torch.float32)
+    ec = EncoderConfig(hidden_size=64, num_layers=2, num_heads=4, head_dim=16, ffn_dim=128, norm="layernorm",
+                       act="gelu_erf", qkv_bias=True, eps=1e-5, dtype=torch.float32)        # the checkpoint's exact GELU
     enc = AudioEncoder(ec, n_mels=16, max_frames=40)
     assert ck.load_whisper_encoder(enc, sd)["loaded"] == len(dict(enc.named_parameters()))
     mel = torch.randn(16, 80)                                   # 80 frames -> 40 positions
@@ -177,8 +177,7 @@ def test_whisper_loaders_are_strict_and_the_encoder_matches_hugging_face():
         want = hf.model.encoder(mel[None]).last_hidden_state[0]
     got, lens = enc([mel])
     assert lens == [40]
-    # the MLP activation here is the tanh form of GELU (the GEMM epilogue), the checkpoint's is the erf form
-    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2), (got - want).abs().max()
+    assert torch.allclose(got, want, atol=2e-4, rtol=2e-4), (got - want).abs().max()
     dec = WhisperDecoder(vocab=120, hidden=64, layers=2, heads=4, ffn=128, max_pos=24, dtype=torch.float32)
     assert ck.load_whisper_decoder(dec, sd)["loaded"] == len(dict(dec.named_parameters()))
     assert torch.equal(dec.layers[1].ckv_w[:64], sd["model.decoder.layers.1.encoder_attn.k_proj.weight"])
