@@ -106,3 +106,39 @@ def test_decoder_loader_is_strict_and_ties_a_missing_head(tmp_path):
     lm = DecoderLM(cfg)
     info = load_decoder_from_hf(lm, str(d))
     assert not info["missing"] and torch.equal(lm.lm_head, lm.embed_tokens)
+
+
+def test_llama3_rope_scaled_decoder_matches_hugging_face_llama(tmp_path):
+    """The Orpheus backbone's layout at test size (grouped KV heads, head_dim x heads != hidden, tied head, Llama-3
+    frequency-dependent rotary scaling) loaded from Hugging Face names against ``transformers.LlamaModel``."""
+    import pytest
+    transformers = pytest.importorskip("transformers")
+    from safetensors.torch import save_file
+    scaling = dict(factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=64)
+    hc = transformers.LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-5,
+                                  tie_word_embeddings=True, attention_bias=False, max_position_embeddings=512,
+                                  rope_parameters=dict(rope_type="llama3", rope_theta=500000.0, **scaling))
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(hc).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.1)
+        if "norm" in n:
+            p.data.add_(1.0)
+    sd = {k: v.detach().clone().contiguous() for k, v in hf.state_dict().items() if k != "lm_head.weight"}
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, intermediate_size=96,
+                        vocab_size=300, rms_eps=1e-5, rope_theta=500000.0, rope_llama3=scaling, tie_embeddings=True,
+                        dtype=torch.float32)
+    lm = DecoderLM(cfg)
+    assert not load_decoder_from_hf(lm, str(tmp_path))["missing"]
+    T = 100                                              # past the original context length: every band of the scaling
+    ids = torch.randint(0, 300, (T,), generator=torch.Generator().manual_seed(1))
+    kvc = KVCacheConfig(2, 2, 32, max_seq_len=256, max_num_pages=16, page_size=16, num_qo_heads=4, dtype=torch.float32)
+    cm = BatchedCacheManager(kvc, "cpu", max_batch=2, max_tokens=256)
+    cm.add_request("r")
+    with torch.no_grad():
+        want = hf(input_ids=ids[None]).logits[0]
+        got = lm(cm.plan(["r"], [T], group=2), input_ids=ids, all_logits=True)
+    assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
+    assert torch.equal(got.argmax(-1), want.argmax(-1))
