@@ -940,3 +940,85 @@ def load_vjepa2_predictor(pred, src, prefix: str = "predictor.") -> dict:
     st.write("out_w", st.take("proj.weight"))
     st.write("out_b", st.take("proj.bias"))
     return st.done()
+
+
+# ------------------------------------------------------------------ SNAC decoder (published names)
+def _fold_weight_norm(T: dict, key: str) -> torch.Tensor | None:
+    """The plain weight of a weight-normalised convolution: ``key.weight`` if stored, else g * v / ||v|| from
+    ``key.parametrizations.weight.original{0,1}`` or the older ``key.weight_{g,v}`` (norm over all but dim 0)."""
+    if key + ".weight" in T:
+        return T.pop(key + ".weight")
+    for g_name, v_name in ((".parametrizations.weight.original0", ".parametrizations.weight.original1"),
+                           (".weight_g", ".weight_v")):
+        if key + g_name in T and key + v_name in T:
+            g, v = T.pop(key + g_name).float(), T.pop(key + v_name).float()
+            return g * v / v.flatten(1).norm(dim=1).reshape(-1, *([1] * (v.dim() - 1)))
+    return None
+
+
+@torch.no_grad()
+def load_snac_decoder(dec, src) -> dict:
+    """``SnacDecoder`` from the published SNAC checkpoint (``pytorch_model.bin`` of ``hubertsiuzdak/snac_24khz``, a
+    directory holding it, or its state dict): codebooks and their output projections, the decoder's
+    ``decoder.model.N`` list (input convolutions, up blocks with noise projection and three residual units, final
+    activation and convolution). Weight normalisation is folded into plain weights; the encoder and the quantiser's
+    input projections are not part of a decoder and are ignored. Strict over everything else.
+    Reference: mstar/model/orpheus/components/snac.py:239-272, 317-358, 399-424."""
+    import os
+    if isinstance(src, str):
+        path = os.path.join(src, "pytorch_model.bin") if os.path.isdir(src) else src
+        raw = torch.load(path, map_location="cpu", weights_only=True)
+    else:
+        raw = dict(src)
+    T = {k: v for k, v in raw.items() if not k.startswith("encoder.") and ".in_proj." not in k}
+    params = dict(dec.named_parameters())
+    written: set[str] = set()
+    bad: list[str] = []
+
+    def put(name: str, t: torch.Tensor | None, what: str) -> None:
+        p = params.get(name)
+        if t is None or p is None or tuple(p.shape) != tuple(t.shape):
+            bad.append(f"{what} -> {name}: {None if t is None else tuple(t.shape)} vs {None if p is None else tuple(p.shape)}")
+            return
+        p.copy_(t.to(p.dtype))
+        written.add(name)
+
+    def conv(src_, dst, bias=True):
+        put(dst + ".weight", _fold_weight_norm(T, src_), src_)
+        if bias:
+            put(dst + ".bias", T.pop(src_ + ".bias", None), src_ + ".bias")
+
+    for i in range(len(dec.codebooks)):
+        q = f"quantizer.quantizers.{i}."
+        put(f"codebooks.{i}.weight", T.pop(q + "codebook.weight", None), q + "codebook.weight")
+        conv(q + "out_proj", f"out_proj.{i}")
+    n = 0
+    if isinstance(dec.inp, torch.nn.Sequential):
+        conv("decoder.model.0", "inp.0")
+        conv("decoder.model.1", "inp.1")
+        n = 2
+    else:
+        conv("decoder.model.0", "inp")
+        n = 1
+    for i, blk in enumerate(dec.blocks):
+        b = f"decoder.model.{n + i}.block."
+        put(f"blocks.{i}.up.0.alpha", T.pop(b + "0.alpha", None), b + "0.alpha")
+        conv(b + "1", f"blocks.{i}.up.1")
+        k = 2
+        if blk.noise is not None:
+            conv(b + "2.linear", f"blocks.{i}.noise", bias=False)
+            k = 3
+        for r in range(3):
+            u, d = f"{b}{k + r}.block.", f"blocks.{i}.res.{r}.block."
+            put(d + "0.alpha", T.pop(u + "0.alpha", None), u + "0.alpha")
+            conv(u + "1", d + "1")
+            put(d + "2.alpha", T.pop(u + "2.alpha", None), u + "2.alpha")
+            conv(u + "3", d + "3")
+    n += len(dec.blocks)
+    put("out.0.alpha", T.pop(f"decoder.model.{n}.alpha", None), f"decoder.model.{n}.alpha")
+    conv(f"decoder.model.{n + 1}", "out.1")
+    missing = sorted(set(params) - written)
+    if T or missing or bad:
+        raise CheckpointMismatch(f"SNAC decoder: {len(T)} checkpoint tensors without a parameter {sorted(T)[:5]}, "
+                                 f"{len(missing)} parameters not loaded {missing[:5]}, problems {bad[:5]}")
+    return {"loaded": len(written)}

@@ -27,10 +27,12 @@ class Snake1d(nn.Module):
 
 
 class ResidualUnit(nn.Module):
-    def __init__(self, dim: int, dilation: int, kernel: int = 7):
+    """Snake, dilated kernel-7 convolution (depthwise when ``groups`` = ``dim``), Snake, 1x1 convolution, skip."""
+
+    def __init__(self, dim: int, dilation: int, kernel: int = 7, groups: int = 1):
         super().__init__()
         pad = (kernel - 1) * dilation // 2
-        self.block = nn.Sequential(Snake1d(dim), nn.Conv1d(dim, dim, kernel, dilation=dilation, padding=pad),
+        self.block = nn.Sequential(Snake1d(dim), nn.Conv1d(dim, dim, kernel, dilation=dilation, padding=pad, groups=groups),
                                    Snake1d(dim), nn.Conv1d(dim, dim, 1))
 
     def forward(self, x):
@@ -38,12 +40,13 @@ class ResidualUnit(nn.Module):
 
 
 class DecoderBlock(nn.Module):
-    def __init__(self, cin: int, cout: int, stride: int, noise: bool = False):
+    def __init__(self, cin: int, cout: int, stride: int, noise: bool = False, groups: int = 1):
         super().__init__()
         self.up = nn.Sequential(Snake1d(cin), nn.ConvTranspose1d(cin, cout, 2 * stride, stride=stride,
                                                                  padding=math.ceil(stride / 2), output_padding=stride % 2))
         self.noise = nn.Conv1d(cout, cout, 1, bias=False) if noise else None
-        self.res = nn.Sequential(ResidualUnit(cout, 1), ResidualUnit(cout, 3), ResidualUnit(cout, 9))
+        self.res = nn.Sequential(ResidualUnit(cout, 1, groups=groups), ResidualUnit(cout, 3, groups=groups),
+                                 ResidualUnit(cout, 9, groups=groups))
 
     HALO = 3 * (1 + 3 + 9)          # inputs that the three residual units (kernel 7, dilations 1, 3, 9) reach per side
 
@@ -78,19 +81,25 @@ class DecoderBlock(nn.Module):
 
 
 class SnacDecoder(nn.Module):
-    """Codes of 3 resolutions (1 / 2 / 4 per 7-token frame) -> 24 kHz waveform; 2048 samples per frame."""
+    """Codes of 3 resolutions (1 / 2 / 4 per 7-token frame) -> 24 kHz waveform; 2048 samples per frame. The defaults
+    are the published 24 kHz model: depthwise kernel-7 convolutions (in the input stage and in every residual unit)
+    with 1x1 convolutions between them, noise injection after every upsampling, no attention layer."""
 
     def __init__(self, codebook_size: int = 4096, codebook_dim: int = 8, latent_dim: int = 768, channels: int = 1024,
-                 rates=(8, 8, 4, 2), vq_strides=(4, 2, 1), noise: bool = True):
+                 rates=(8, 8, 4, 2), vq_strides=(4, 2, 1), noise: bool = True, depthwise: bool = True):
         super().__init__()
         self.vq_strides = list(vq_strides)
         self.codebook_size = codebook_size
         self.codebooks = nn.ModuleList([nn.Embedding(codebook_size, codebook_dim) for _ in vq_strides])
         self.out_proj = nn.ModuleList([nn.Conv1d(codebook_dim, latent_dim, 1) for _ in vq_strides])
-        self.inp = nn.Conv1d(latent_dim, channels, 7, padding=3)
+        if depthwise:
+            self.inp = nn.Sequential(nn.Conv1d(latent_dim, latent_dim, 7, padding=3, groups=latent_dim),
+                                     nn.Conv1d(latent_dim, channels, 1))
+        else:
+            self.inp = nn.Conv1d(latent_dim, channels, 7, padding=3)
         blocks, c = [], channels
         for r in rates:
-            blocks.append(DecoderBlock(c, c // 2, r, noise))
+            blocks.append(DecoderBlock(c, c // 2, r, noise, groups=c // 2 if depthwise else 1))
             c //= 2
         self.blocks = nn.ModuleList(blocks)
         self.out = nn.Sequential(Snake1d(c), nn.Conv1d(c, 1, 7, padding=3), nn.Tanh())

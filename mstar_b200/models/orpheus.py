@@ -57,11 +57,16 @@ class _HostRows:
 
 
 class SnacSubmodule(NodeSubmodule):
-    def __init__(self, device, base_id: int, small: bool, compute_dtype: torch.dtype = torch.float32):
+    def __init__(self, device, base_id: int, small: bool, compute_dtype: torch.dtype = torch.float32,
+                 snac_dir: str | None = None):
         super().__init__(device, torch.float32)
         self.compute_dtype = compute_dtype         # fp32 weights; bf16 runs the convolutions under autocast
         kw = dict(latent_dim=64, channels=64, rates=(8, 8, 4, 2)) if small else {}
-        self.dec = seeded_init(lambda: SnacDecoder(**kw)).to(device=device, dtype=torch.float32).eval()
+        self.dec = seeded_init(lambda: SnacDecoder(**kw))
+        if snac_dir:            # the published codec checkpoint (config.json + pytorch_model.bin): strict load
+            from .checkpoints import load_snac_decoder
+            load_snac_decoder(self.dec, snac_dir)
+        self.dec = self.dec.to(device=device, dtype=torch.float32).eval()
 
         self.base_id = base_id
         self.gen = None
@@ -172,9 +177,9 @@ class OrpheusModel(Model):
     raw_payload_dtypes = {"audio": "int16"}        # the codec's graph quantises to 16-bit PCM: its bytes go out as they are
 
     def __init__(self, model_dir=None, skip_weight_loading=False, small: bool = False, page_size: int = 128,
-                 max_num_pages: int = 2048, codec_dtype: str = "float32", **kw):
+                 max_num_pages: int = 2048, codec_dtype: str = "float32", snac_dir: str | None = None, **kw):
         super().__init__(model_dir, skip_weight_loading, **kw)
-        self.small = small
+        self.small, self.snac_dir = small, snac_dir
         self.codec_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}[codec_dtype]
         if small:      # test-sized backbone with the real vocabulary layout
             self.cfg = DecoderConfig(hidden_size=128, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
@@ -237,7 +242,7 @@ class OrpheusModel(Model):
                 lm.fold_norms()
             return DecoderSubmodule(lm, device, eos_ids=END_TOKEN_IDS, token_edge="audio_tokens")
         if node_name == "snac_decoder":
-            return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small, self.codec_dtype)
+            return SnacSubmodule(device, CUSTOM_TOKEN_BASE, self.small, self.codec_dtype, self._snac_dir())
         raise KeyError(node_name)
 
     # ---- request life cycle ----
@@ -261,6 +266,20 @@ class OrpheusModel(Model):
             ids = [int(p) for p in parts] if parts and all(p.isdigit() for p in parts) else list(text.encode("utf-8"))
         ids = [128259] + [i % self.cfg.vocab_size for i in ids] + [128009, 128260]
         return {"input_ids": [torch.tensor(ids, dtype=torch.int64)]}
+
+    def _snac_dir(self) -> str | None:
+        """Where the codec's checkpoint is: ``snac_dir`` of the model kwargs, or a ``snac_24khz`` / ``snac`` directory
+        beside the language model's files (the reference downloads ``hubertsiuzdak/snac_24khz`` separately)."""
+        import os
+        if self.skip_weight_loading:
+            return None
+        if self.snac_dir:
+            return self.snac_dir
+        for sub in ("snac_24khz", "snac"):
+            d = os.path.join(self.model_dir or "", sub)
+            if self.model_dir and os.path.exists(os.path.join(d, "pytorch_model.bin")):
+                return d
+        return None
 
     def _tokenizer(self):
         if self.model_dir is None:

@@ -103,3 +103,46 @@ def test_middle_frame_decode_equals_the_slice_of_the_full_window():
         ra, rb, _, _ = d.blocks[-1].input_range(*need[0], lens[-2])
         if hop == 512:
             assert (rb - ra) < 0.3 * lens[-1]
+
+
+def test_snac_decoder_loads_the_published_layout_and_matches_the_reference_module():
+    """The reference's own ``SNAC`` (the published 24 kHz architecture at test width: depthwise convolutions, noise
+    blocks, weight normalisation) and ``SnacDecoder`` loaded from its state dict decode the same codes to the same
+    waveform, with the noise drawn from the same generator state; the loader refuses what does not fit."""
+    import inspect
+    import pytest
+    import torch
+    from conftest import reference_module
+    snac_mod = reference_module("mstar.model.orpheus.components.snac")
+    from mstar_b200.models import checkpoints as ck
+    from mstar_b200.models.codec import SnacDecoder
+    cfg = dict(sampling_rate=24000, encoder_dim=8, encoder_rates=[2, 4, 8, 8], latent_dim=48, decoder_dim=64,
+               decoder_rates=[8, 8, 4, 2], attn_window_size=None, codebook_size=4096, codebook_dim=8,
+               vq_strides=[4, 2, 1], noise=True, depthwise=True)
+    ok = set(inspect.signature(snac_mod.SNAC.__init__).parameters)
+    torch.manual_seed(0)
+    ref = snac_mod.SNAC(**{k: v for k, v in cfg.items() if k in ok}).eval()
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            if "alpha" in n:
+                p.uniform_(0.5, 1.5)
+            elif n.endswith("bias"):
+                p.normal_(0, 0.05)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    ours = SnacDecoder(latent_dim=48, channels=64, rates=(8, 8, 4, 2)).eval()
+    assert ck.load_snac_decoder(ours, sd)["loaded"] == len(list(ours.parameters()))
+    codes = [torch.randint(0, 4096, (2, 4)), torch.randint(0, 4096, (2, 8)), torch.randint(0, 4096, (2, 16))]
+    with torch.no_grad():
+        torch.manual_seed(7)
+        want = ref.decode(codes)[:, 0]
+        torch.manual_seed(7)
+        got = ours(codes)
+        assert got.shape == want.shape == (2, 16 * 512)
+        assert (got - want).abs().max().item() < 1e-5 and want.abs().max().item() > 1e-3
+    for mutate in (lambda d: d.pop("decoder.model.3.block.2.linear.parametrizations.weight.original1"),
+                   lambda d: d.update({"decoder.model.9.extra": torch.zeros(1)}),
+                   lambda d: d.update({"quantizer.quantizers.1.codebook.weight": torch.zeros(4096, 9)})):
+        bad = dict(sd)
+        mutate(bad)
+        with pytest.raises(ck.CheckpointMismatch):
+            ck.load_snac_decoder(SnacDecoder(latent_dim=48, channels=64, rates=(8, 8, 4, 2)), bad)
