@@ -142,3 +142,34 @@ def test_llama3_rope_scaled_decoder_matches_hugging_face_llama(tmp_path):
         got = lm(cm.plan(["r"], [T], group=2), input_ids=ids, all_logits=True)
     assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
     assert torch.equal(got.argmax(-1), want.argmax(-1))
+
+
+def test_qwen2_style_decoder_with_qkv_bias_matches_hugging_face(tmp_path):
+    """Fused q / k / v biases and untied head (the layout of BAGEL's understanding expert and of Qwen2.5 backbones)
+    against ``transformers.Qwen2ForCausalLM``."""
+    import pytest
+    transformers = pytest.importorskip("transformers")
+    from safetensors.torch import save_file
+    hc = transformers.Qwen2Config(vocab_size=200, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                                  max_position_embeddings=256, use_sliding_window=False,
+                                  rope_parameters=dict(rope_type="default", rope_theta=1e6))
+    torch.manual_seed(0)
+    hf = transformers.Qwen2ForCausalLM(hc).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.1)
+        if "norm" in n:
+            p.data.add_(1.0)
+    save_file({k: v.detach().clone().contiguous() for k, v in hf.state_dict().items()}, str(tmp_path / "model.safetensors"))
+    cfg = DecoderConfig(hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16, intermediate_size=96,
+                        vocab_size=200, rms_eps=1e-6, rope_theta=1e6, qkv_bias=True, dtype=torch.float32)
+    lm = DecoderLM(cfg)
+    assert not load_decoder_from_hf(lm, str(tmp_path))["missing"]
+    ids = torch.randint(0, 200, (23,), generator=torch.Generator().manual_seed(1))
+    kvc = KVCacheConfig(2, 2, 16, max_seq_len=64, max_num_pages=8, page_size=16, num_qo_heads=4, dtype=torch.float32)
+    cm = BatchedCacheManager(kvc, "cpu", max_batch=2, max_tokens=64)
+    cm.add_request("r")
+    with torch.no_grad():
+        want = hf(input_ids=ids[None]).logits[0]
+        got = lm(cm.plan(["r"], [23], group=2), input_ids=ids, all_logits=True)
+    assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
