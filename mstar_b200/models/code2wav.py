@@ -128,10 +128,16 @@ class FrameTransformer(nn.Module):
         self.layers = nn.ModuleList([_FrameLayer(H, heads, head_dim, ffn, dtype, device) for _ in range(layers)])
         self.norm = _p((H,), dtype, device)
         self.register_buffer("inv_freq", rope_ops.make_inv_freq(head_dim, theta, device), persistent=False)
+        self._plans: dict = {}
 
     def forward(self, x: torch.Tensor, seq_lens: list[int]) -> torch.Tensor:
-        plan = attn_ops.dense_plan(seq_lens, seq_lens, 1, x.device, causal=True, window=self.window)
-        pos = torch.cat([torch.arange(n, dtype=torch.int32, device=x.device) for n in seq_lens])
+        key = (tuple(seq_lens), str(x.device))          # per shape: nothing is built from host data on a repeat
+        if key not in self._plans:
+            if len(self._plans) > 64:
+                self._plans.clear()
+            self._plans[key] = (attn_ops.dense_plan(seq_lens, seq_lens, 1, x.device, causal=True, window=self.window),
+                                torch.cat([torch.arange(n, dtype=torch.int32, device=x.device) for n in seq_lens]))
+        plan, pos = self._plans[key]
         nh, D = self.heads, self.D
         for L in self.layers:
             h = norm_ops.norm(x, L.n1, self.eps)[0]

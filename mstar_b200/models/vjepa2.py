@@ -32,13 +32,12 @@ def _p(shape, dtype, device):
     return nn.Parameter(torch.empty(shape, dtype=dtype, device=device), requires_grad=False)
 
 
-def rope3d(ids: torch.Tensor, grid_hw: tuple[int, int], head_dim: int):
-    """The published rotary embedding of V-JEPA 2 for tokens at flat tubelet indices ``ids`` (frame-major, then rows,
-    then columns): the head is cut into three bands of 2 * ((D // 3) // 2) channels for the frame, row and column
-    position (what is left over is not rotated). Inside a band adjacent channels (2i, 2i+1) form the rotated pair,
-    while the angle of channel j is position x 10000^(-(j mod s/2) / (s/2)) — the angle table is tiled over the band,
-    not repeated per pair (transformers/models/vjepa2/modeling_vjepa2.py: rotate_queries_or_keys). Returns a function
-    for [T, heads, D] tensors."""
+def rope3d_tables(ids: torch.Tensor, grid_hw: tuple[int, int], head_dim: int):
+    """Cosine / sine tables [T, 1, 3s] of the published rotary embedding of V-JEPA 2 for tokens at flat tubelet
+    indices ``ids`` (frame-major, then rows, then columns): the head is cut into three bands of s = 2 * ((D // 3) // 2)
+    channels for the frame, row and column position (what is left over is not rotated); the angle of channel j of a
+    band is position x 10000^(-(j mod s/2) / (s/2)) — the angle table is tiled over the band, not repeated per pair
+    (transformers/models/vjepa2/modeling_vjepa2.py: rotate_queries_or_keys)."""
     h, w = grid_hw
     ids = ids.long()
     frame = ids // (h * w)
@@ -47,15 +46,24 @@ def rope3d(ids: torch.Tensor, grid_hw: tuple[int, int], head_dim: int):
     s = 2 * ((head_dim // 3) // 2)
     omega = 1.0 / 10000 ** (torch.arange(s // 2, dtype=torch.float32, device=ids.device) / (s / 2.0))
     ang = torch.cat([(p.float()[:, None] * omega).repeat(1, 2) for p in (frame, row, col)], dim=-1)     # [T, 3s]
-    cs, sn = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+    return torch.cos(ang)[:, None].contiguous(), torch.sin(ang)[:, None].contiguous()
+
+
+def rope3d_apply(cs: torch.Tensor, sn: torch.Tensor):
+    """The rotation for [T, heads, D] tensors: inside a band adjacent channels (2i, 2i+1) form the rotated pair."""
+    n = cs.shape[-1]
 
     def apply(x):
         xf = x.float()
-        r = xf[..., :3 * s]
+        r = xf[..., :n]
         pair = r.unflatten(-1, (-1, 2))
         y = torch.stack((-pair[..., 1], pair[..., 0]), dim=-1).flatten(-2)
-        return torch.cat([r * cs + y * sn, xf[..., 3 * s:]], dim=-1).to(x.dtype)
+        return torch.cat([r * cs + y * sn, xf[..., n:]], dim=-1).to(x.dtype)
     return apply
+
+
+def rope3d(ids: torch.Tensor, grid_hw: tuple[int, int], head_dim: int):
+    return rope3d_apply(*rope3d_tables(ids, grid_hw, head_dim))
 
 
 class VJepa2Encoder(nn.Module):
@@ -131,8 +139,10 @@ class MaskedPredictor(nn.Module):
         m = self.mask_tokens[mask_index % self.mask_tokens.shape[0]].expand(tgt_idx.numel(), -1)
         seq = torch.cat([x, m.to(x.dtype)]).contiguous()
         n = seq.shape[0]
-        rope = rope3d(torch.cat([ctx_idx, tgt_idx]), grid_hw, self.c.head_dim)
-        h = runner.run("predictor_blocks", lambda s_: self.blocks(s_, [n], rope=rope), seq)
+        # the position tables are INPUTS of the captured piece: a replay for other masks of the same size must rotate
+        # by its own positions
+        cs, sn = rope3d_tables(torch.cat([ctx_idx, tgt_idx]), grid_hw, self.c.head_dim)
+        h = runner.run("predictor_blocks", lambda s_, c_, n_: self.blocks(s_, [n], rope=rope3d_apply(c_, n_)), seq, cs, sn)
         return gemm.linear(h[x.shape[0]:].contiguous(), self.out_w, bias=self.out_b)
 
 
