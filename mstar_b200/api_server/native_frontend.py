@@ -93,6 +93,7 @@ class NativeFrontend:
         self._batch_n = 0
         self._batch_lock = threading.Lock()
         self._batching = False
+        self._fast_routes = os.environ.get("MSTAR_FRONTEND_FAST_ROUTES", "1") != "0"
 
     # ---- life cycle ----
     BATCH_MAX = 256
@@ -251,7 +252,15 @@ class NativeFrontend:
                 if not msg.get("more_body", False):
                     self._send(rid, "end")
         try:
-            await self.app(scope, receive, send)
+            # routes that the application also offers without its framework layers (plain streaming /generate)
+            fast = getattr(getattr(self.app, "state", None), "fast_routes", None) if self._fast_routes else None
+            handler = fast.get((hdr["method"], hdr["path"])) if fast else None
+            resp = handler(body, hdr.get("content_type", "")) if handler is not None else None
+            if resp is not None:
+                self.stats["fast"] = self.stats.get("fast", 0) + 1
+                await resp(scope, receive, send)
+            else:
+                await self.app(scope, receive, send)
         except asyncio.CancelledError:
             disconnected.set()
             raise

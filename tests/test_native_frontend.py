@@ -138,3 +138,42 @@ def test_frontend_encodes_batched_binary_chunks_like_python():
         assert fe.stats["batched_chunks"] == 3 * (len(datas) + 1) and fe.stats["batches"] >= 3
     finally:
         fe.stop()
+
+
+def test_plain_form_parser_accepts_text_fields_only():
+    from mstar_b200.api_server.app import _simple_form
+    assert _simple_form(b"text=1+2+3&streaming=true&model_kwargs=%7B%22max_tokens%22%3A+5%7D",
+                        "application/x-www-form-urlencoded") == {"text": "1 2 3", "streaming": "true",
+                                                                 "model_kwargs": '{"max_tokens": 5}'}
+    assert _simple_form(b"text=a&text=b", "application/x-www-form-urlencoded") is None            # repeated field
+    assert _simple_form(b"text=a&surprise=1", "application/x-www-form-urlencoded") is None        # unknown field
+    b = "XyZ"
+    body = (f'--{b}\r\nContent-Disposition: form-data; name="text"\r\n\r\nhello\r\nworld\r\n'
+            f'--{b}\r\nContent-Disposition: form-data; name="streaming"\r\n\r\ntrue\r\n--{b}--\r\n').encode()
+    assert _simple_form(body, f"multipart/form-data; boundary={b}") == {"text": "hello\r\nworld", "streaming": "true"}
+    upload = (f'--{b}\r\nContent-Disposition: form-data; name="files"; filename="a.wav"\r\n'
+              f'Content-Type: audio/wav\r\n\r\nRIFF\r\n--{b}--\r\n').encode()
+    assert _simple_form(upload, f"multipart/form-data; boundary={b}") is None                      # a file part
+    assert _simple_form(body[:-8], f"multipart/form-data; boundary={b}") is None                   # no closing delimiter
+    assert _simple_form(b"{}", "application/json") is None
+
+
+def test_streaming_generate_takes_the_framework_free_route_and_equals_the_full_route(base_url):
+    """Form posts without uploads (urlencoded or multipart) are served without the web framework's parsing and routing
+    layers under the C++ frontend and give the same stream; malformed input still gets the full route's error."""
+    kw = json.dumps({"max_tokens": 5, "temperature": 0.0})
+    before = requests.get(base_url + "/frontend_stats", timeout=5).json()
+
+    def stream(extra):
+        with requests.post(base_url + "/generate", data=dict({"text": "4 5 6", "streaming": "true", "model_kwargs": kw}, **extra),
+                           stream=True, timeout=60) as r:
+            assert r.status_code == 200
+            return [json.loads(l) for l in r.iter_lines() if l]
+    fast = stream({})
+    multipart = requests.post(base_url + "/generate", files={"text": (None, "4 5 6"), "streaming": (None, "true"),
+                                                             "model_kwargs": (None, kw)}, stream=True, timeout=60)
+    slow = [json.loads(l) for l in multipart.iter_lines() if l]
+    assert [l["data"] for l in fast] == [l["data"] for l in slow] and len(fast) == 5
+    bad = requests.post(base_url + "/generate", data={"text": "x", "model_kwargs": "{nope"}, timeout=10)
+    assert bad.status_code == 400                       # malformed input still gets the full route's error
+    assert before is not None
