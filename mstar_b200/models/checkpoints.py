@@ -1022,3 +1022,48 @@ def load_snac_decoder(dec, src) -> dict:
         raise CheckpointMismatch(f"SNAC decoder: {len(T)} checkpoint tensors without a parameter {sorted(T)[:5]}, "
                                  f"{len(missing)} parameters not loaded {missing[:5]}, problems {bad[:5]}")
     return {"loaded": len(written)}
+
+
+@torch.no_grad()
+def load_qwen3_omni_code_predictor(pred, src, prefix: str = "talker.code_predictor.",
+                                   talker_table: str = "talker.model.codec_embedding.weight") -> dict:
+    """``CodePredictor`` from the ``talker.code_predictor.*`` tensors of a Qwen3-Omni checkpoint: a dense Qwen3-style
+    stack (``model.layers``, ``model.norm``), one embedding table per residual code layer
+    (``model.codec_embedding.N``) and one head per layer (``lm_head.N``). The first code of a frame is embedded with
+    the TALKER's table (``talker_table``, its first ``codebook`` rows); the talker's hidden state enters unprojected,
+    so predictor and talker must have the same width. Strict over the prefix."""
+    from ..ops import gemm
+    allT = _tensors_of(src)
+    T = {k[len(prefix):]: v for k, v in allT.items() if k.startswith(prefix)}
+    st = _Strict(pred, T, "Qwen3-Omni code predictor")
+    H = pred.cfg.hidden_size
+    if tuple(pred.in_proj.shape) != (H, H):
+        st.bad.append(f"the talker's width {pred.in_proj.shape[1]} differs from the predictor's {H}")
+    else:
+        st.write("in_proj", torch.eye(H))
+    tbl = allT.get(talker_table)
+    embeds = [None if tbl is None else tbl[:pred.codebook]]
+    embeds += [st.take(f"model.codec_embedding.{j}.weight") for j in range(pred.n_sub)]
+    if any(e is None for e in embeds):
+        st.bad.append(f"missing {talker_table} or a codec_embedding table")
+    else:
+        st.write("embed", torch.stack([e[:pred.codebook] for e in embeds]))
+    heads = [st.take(f"lm_head.{j}.weight") for j in range(pred.n_sub)]
+    if None not in heads:
+        st.write("heads", torch.stack([h[:pred.codebook] for h in heads]))
+    for i in range(len(pred.tower.layers)):
+        p, d = f"model.layers.{i}.", f"tower.layers.{i}."
+        ws = [st.take(f"{p}self_attn.{n}_proj.weight") for n in "qkv"]
+        if None not in ws:
+            st.write(d + "qkv_proj", torch.cat(ws))
+        st.write(d + "o_proj", st.take(p + "self_attn.o_proj.weight"))
+        st.write(d + "q_norm", st.take(p + "self_attn.q_norm.weight"))
+        st.write(d + "k_norm", st.take(p + "self_attn.k_norm.weight"))
+        g, u = st.take(p + "mlp.gate_proj.weight"), st.take(p + "mlp.up_proj.weight")
+        if g is not None and u is not None:
+            st.write(d + "gate_up_proj", gemm.interleave_gate_up(g, u))
+        st.write(d + "down_proj", st.take(p + "mlp.down_proj.weight"))
+        st.write(d + "input_norm", st.take(p + "input_layernorm.weight"))
+        st.write(d + "post_norm", st.take(p + "post_attention_layernorm.weight"))
+    st.write("tower.final_norm", st.take("model.norm.weight"))
+    return st.done()

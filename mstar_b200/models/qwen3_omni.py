@@ -255,6 +255,9 @@ class Qwen3OmniModel(Model):
             if self.fp8_experts:
                 lm.quantize_moe_fp8()
             pred = CodePredictor(self.pred_cfg, self.k_cfg.hidden_size, self.n_sub, self.codebook, device).init_random(3)
+            if load:
+                from .checkpoints import load_qwen3_omni_code_predictor
+                load_qwen3_omni_code_predictor(pred, self.model_dir)
             return TalkerSubmodule(lm, pred, device, num_slots=64, codec_eos=self.codec_eos, cond_edge="thinker_out",
                                    cond_is_ids=False, cond_dim=self.t_cfg.hidden_size, loop_name="talker_loop")
         if node_name == "Code2Wav":

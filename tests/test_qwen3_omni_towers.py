@@ -250,3 +250,45 @@ def test_talker_backbone_with_its_gated_shared_expert_matches_hugging_face(tmp_p
         cm.add_request("r")
         got = lm.forward_hidden(lm.embed(ids), cm.plan(["r"], [T], group=2))
     assert (got - want).abs().max().item() < 1e-4
+
+
+def test_code_predictor_gives_hugging_face_greedy_codes():
+    """``talker.code_predictor.*`` loaded into ``CodePredictor``: the residual codes of a frame, decoded greedily from
+    the talker's hidden state and first code, equal the Hugging Face module's cached generation (prefill over
+    [hidden, first-code embedding], then one step per code layer through its own embedding table and head)."""
+    from mstar_b200.models.decoder import DecoderConfig
+    from mstar_b200.models.talker import CodePredictor
+    torch.manual_seed(0)
+    hc = hf_cfg.Qwen3OmniMoeTalkerCodePredictorConfig(
+        vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+        num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, num_code_groups=4, attention_bias=False,
+        max_position_embeddings=64, rope_parameters={"rope_type": "default", "rope_theta": 1e6}, pad_token_id=0)
+    hf = hf_omni.Qwen3OmniMoeTalkerCodePredictorModelForConditionalGeneration(hc).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.2)
+        if "norm" in n:
+            p.data.add_(1.0)
+    talker_table = torch.randn(96, 32) * 0.3                 # the talker's own token table embeds the first code
+    sd = {"talker.code_predictor." + k: v.clone() for k, v in hf.state_dict().items()}
+    sd["talker.model.codec_embedding.weight"] = talker_table
+    cfg = DecoderConfig(hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16, intermediate_size=48,
+                        vocab_size=8, qk_norm=True, rope_theta=1e6, rms_eps=1e-6, dtype=torch.float32)
+    pred = CodePredictor(cfg, 32, 3, 64, "cpu").init_random(0)
+    assert ck.load_qwen3_omni_code_predictor(pred, sd)["loaded"] == len(list(pred.parameters()))
+    hidden, code0 = torch.randn(3, 32), torch.randint(0, 64, (3,))
+    with torch.no_grad():
+        got = pred(hidden, code0, None, None)
+        out = hf(inputs_embeds=torch.stack([hidden, talker_table[code0]], dim=1), use_cache=True)
+        codes = [code0]
+        for g in range(3):
+            codes.append(out.logits[:, -1].argmax(-1))
+            if g < 2:
+                out = hf(input_ids=codes[-1][:, None], past_key_values=out.past_key_values, use_cache=True,
+                         generation_steps=g + 1)
+    assert torch.equal(got, torch.stack(codes, dim=1))
+    bad = dict(sd)
+    bad.pop("talker.code_predictor.lm_head.2.weight")
+    with pytest.raises(ck.CheckpointMismatch):
+        ck.load_qwen3_omni_code_predictor(pred, bad)
+    with pytest.raises(ck.CheckpointMismatch):               # a predictor narrower than the talker has no such layout
+        ck.load_qwen3_omni_code_predictor(CodePredictor(cfg, 48, 3, 64, "cpu").init_random(0), sd)
