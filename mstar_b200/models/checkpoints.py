@@ -124,7 +124,16 @@ _WAN_BLOCK = {
 
 @torch.no_grad()
 def load_wan22_transformer(dit, transformer_dir: str) -> dict:
-    """Fill an ``AdaLNDiT`` from a diffusers Wan2.2 transformer directory (or file)."""
+    """Fill an ``AdaLNDiT`` from a diffusers Wan2.2 transformer directory (or file). A tensor-parallel model is
+    filled through a full-size copy on the host (strict there), of which every rank keeps its heads and MLP columns."""
+    if getattr(dit, "tp", None) is not None and dit.tp.size > 1:
+        from .dit import AdaLNDiT, adaln_shard
+        full = AdaLNDiT(dit.cfg, "cpu")
+        info = load_wan22_transformer(full, transformer_dir)
+        src = dict(full.named_parameters())
+        for n, p in dit.named_parameters():
+            p.copy_(adaln_shard(n, src[n], dit.tp.rank, dit.tp.size).to(p.dtype))
+        return info
     H = dit.cfg.hidden_size
     fill = _Filler(dit, f"Wan2.2 transformer at {transformer_dir}")
     for key, t in iter_checkpoint(transformer_dir):

@@ -147,33 +147,77 @@ def wan22_5b_config() -> DiTConfig:
 
 # ------------------------------------------------------------------ AdaLN DiT (Wan2.2-class)
 class AdaLNBlock(nn.Module):
-    def __init__(self, cfg: DiTConfig, device):
+    """``tp``: tensor-parallel group. Attention heads (self and cross) and the MLP's inner dimension are cut over it;
+    the output projections are row-parallel sums. The q / k norms of this architecture normalise over ALL heads, so
+    the ranks exchange the per-token sums of squares (two floats per token) before scaling their own heads."""
+
+    def __init__(self, cfg: DiTConfig, device, tp: CommGroup | None = None):
         super().__init__()
-        H, Fd, dt = cfg.hidden_size, cfg.ffn_dim, cfg.dtype
-        self.cfg = cfg
+        self.tp = tp or CommGroup.trivial()
+        t = self.tp.size
+        if cfg.num_heads % t or cfg.ffn_dim % t:
+            raise ValueError(f"{cfg.num_heads} heads / MLP width {cfg.ffn_dim} cannot be cut {t} ways")
+        H, Fd, dt = cfg.hidden_size, cfg.ffn_dim // t, cfg.dtype
+        A = cfg.num_heads * cfg.head_dim // t               # this rank's attention width
+        self.cfg, self.A = cfg, A
         self.modulation = _param((6, H), torch.float32, device)
-        self.qkv_w, self.qkv_b = _param((3 * H, H), dt, device), _param((3 * H,), dt, device)
-        self.norm_q, self.norm_k = _param((H,), dt, device), _param((H,), dt, device)
-        self.o_w, self.o_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.qkv_w, self.qkv_b = _param((3 * A, H), dt, device), _param((3 * A,), dt, device)
+        self.norm_q, self.norm_k = _param((A,), dt, device), _param((A,), dt, device)
+        self.o_w, self.o_b = _param((H, A), dt, device), _param((H,), dt, device)
         self.norm3_w, self.norm3_b = _param((H,), dt, device), _param((H,), dt, device)
-        self.cq_w, self.cq_b = _param((H, H), dt, device), _param((H,), dt, device)
-        self.ckv_w, self.ckv_b = _param((2 * H, H), dt, device), _param((2 * H,), dt, device)
-        self.cnorm_q, self.cnorm_k = _param((H,), dt, device), _param((H,), dt, device)
-        self.co_w, self.co_b = _param((H, H), dt, device), _param((H,), dt, device)
+        self.cq_w, self.cq_b = _param((A, H), dt, device), _param((A,), dt, device)
+        self.ckv_w, self.ckv_b = _param((2 * A, H), dt, device), _param((2 * A,), dt, device)
+        self.cnorm_q, self.cnorm_k = _param((A,), dt, device), _param((A,), dt, device)
+        self.co_w, self.co_b = _param((H, A), dt, device), _param((H,), dt, device)
         self.ffn1_w, self.ffn1_b = _param((Fd, H), dt, device), _param((Fd,), dt, device)
         self.ffn2_w, self.ffn2_b = _param((H, Fd), dt, device), _param((H,), dt, device)
+
+    def _norm_all_heads(self, parts: list[torch.Tensor], weights: list[torch.Tensor]) -> list[torch.Tensor]:
+        """RMS norm over the full attention width of tensors of which this rank holds its heads' columns."""
+        ss = torch.stack([p.float().pow(2).sum(-1) for p in parts], dim=-1)
+        ss = self.tp.all_reduce(ss)
+        full = self.A * self.tp.size
+        return [(p.float() * torch.rsqrt(ss[:, i:i + 1] / full + self.cfg.eps) * w.float()).to(p.dtype)
+                for i, (p, w) in enumerate(zip(parts, weights))]
 
     def project_context(self, ctx: torch.Tensor):
         """K/V of the text context for this block: [L_total, heads, D] each (done once per request)."""
         c = self.cfg
         kv = gemm.linear(ctx, self.ckv_w, bias=self.ckv_b)
-        H = c.hidden_size
-        k, _ = norm_ops.norm(kv[:, :H], self.cnorm_k, c.eps)
-        return (k.reshape(-1, c.num_heads, c.head_dim).contiguous(),
-                kv[:, H:].reshape(-1, c.num_heads, c.head_dim).contiguous())
+        A = self.A
+        if self.tp.size > 1:
+            k = self._norm_all_heads([kv[:, :A]], [self.cnorm_k])[0]
+        else:
+            k, _ = norm_ops.norm(kv[:, :A], self.cnorm_k, c.eps)
+        return (k.reshape(-1, A // c.head_dim, c.head_dim).contiguous(),
+                kv[:, A:].reshape(-1, A // c.head_dim, c.head_dim).contiguous())
+
+    def forward_tp(self, x, mod, positions, rope, self_plan, cross_plan, ctx_kv):
+        """The block over this rank's heads and MLP columns (same signature and result as ``forward``)."""
+        c, A, tp = self.cfg, self.A, self.tp
+        nh, D = A // c.head_dim, c.head_dim
+        inv_freq, axis = rope
+        h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 1], shift=mod[:, 0])
+        qkv = gemm.linear(h, self.qkv_w, bias=self.qkv_b)
+        qn, kn = self._norm_all_heads([qkv[:, :A], qkv[:, A:2 * A]], [self.norm_q, self.norm_k])
+        qkv = torch.cat([qn, kn, qkv[:, 2 * A:]], dim=-1).contiguous()
+        q, k, v = rope_ops.rope_kv(qkv, positions, inv_freq, nh, nh, D, axis_of_freq=axis, interleaved=True, dense_kv=True)
+        a = attn_ops.attention(q, self_plan, k=k, v=v)
+        y = row_parallel(a.reshape(-1, A), self.o_w, tp, bias=self.o_b)
+        x = ew_ops.gated_residual(x, y, mod[:, 2])
+        h, _ = norm_ops.norm(x, self.norm3_w, c.eps, layernorm=True, bias=self.norm3_b)
+        q = self._norm_all_heads([gemm.linear(h, self.cq_w, bias=self.cq_b)], [self.cnorm_q])[0]
+        a = attn_ops.attention(q.reshape(-1, nh, D), cross_plan, k=ctx_kv[0], v=ctx_kv[1])
+        x = row_parallel(a.reshape(-1, A), self.co_w, tp, bias=self.co_b, residual=x)
+        h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 4], shift=mod[:, 3])
+        h = gemm.linear(h, self.ffn1_w, bias=self.ffn1_b, epilogue=gemm.EPILOGUE_GELU)
+        y = row_parallel(h, self.ffn2_w, tp, bias=self.ffn2_b)
+        return ew_ops.gated_residual(x, y, mod[:, 5])
 
     def forward(self, x, mod, positions, rope, self_plan, cross_plan, ctx_kv):
         """x: [T, H]; mod: [n_mod, 6, H] bf16 = modulation + timestep projection; T rows split evenly over n_mod."""
+        if self.tp.size > 1:
+            return self.forward_tp(x, mod, positions, rope, self_plan, cross_plan, ctx_kv)
         c = self.cfg
         H, nh, D = c.hidden_size, c.num_heads, c.head_dim
         inv_freq, axis = rope
@@ -200,10 +244,31 @@ class AdaLNBlock(nn.Module):
         return ew_ops.gated_residual(x, y, mod[:, 5])
 
 
+# parameters of a block that are cut over the tensor-parallel group: name -> (dimension, number of stacked sections)
+_ADALN_CUTS = {"qkv_w": (0, 3), "qkv_b": (0, 3), "norm_q": (0, 1), "norm_k": (0, 1), "o_w": (1, 1), "cq_w": (0, 1),
+               "cq_b": (0, 1), "ckv_w": (0, 2), "ckv_b": (0, 2), "cnorm_q": (0, 1), "cnorm_k": (0, 1), "co_w": (1, 1),
+               "ffn1_w": (0, 1), "ffn1_b": (0, 1), "ffn2_w": (1, 1)}
+
+
+def adaln_shard(name: str, full: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    """This rank's part of a full ``AdaLNDiT`` parameter (``blocks.N.<param>``): stacked projections (q | k | v,
+    k | v) are cut section by section so that every rank keeps whole heads of each."""
+    leaf = name.rsplit(".", 1)[-1]
+    if size == 1 or not name.startswith("blocks.") or leaf not in _ADALN_CUTS:
+        return full
+    dim, sections = _ADALN_CUTS[leaf]
+    parts = []
+    for sec in full.chunk(sections, dim=dim):
+        n = sec.shape[dim] // size
+        parts.append(sec.narrow(dim, rank * n, n))
+    return torch.cat(parts, dim=dim)
+
+
 class AdaLNDiT(nn.Module):
-    def __init__(self, cfg: DiTConfig, device="cpu"):
+    def __init__(self, cfg: DiTConfig, device="cpu", tp: CommGroup | None = None):
         super().__init__()
         self.cfg, self.device = cfg, torch.device(device)
+        self.tp = tp or CommGroup.trivial()
         H, dt = cfg.hidden_size, cfg.dtype
         pdim = cfg.in_channels * math.prod(cfg.patch_size)
         self.patch_w, self.patch_b = _param((H, pdim), dt, device), _param((H,), dt, device)
@@ -212,23 +277,31 @@ class AdaLNDiT(nn.Module):
         self.time1_w, self.time1_b = _param((H, cfg.freq_dim), dt, device), _param((H,), dt, device)
         self.time2_w, self.time2_b = _param((H, H), dt, device), _param((H,), dt, device)
         self.tproj_w, self.tproj_b = _param((6 * H, H), dt, device), _param((6 * H,), dt, device)
-        self.blocks = nn.ModuleList([AdaLNBlock(cfg, device) for _ in range(cfg.num_layers)])
+        self.blocks = nn.ModuleList([AdaLNBlock(cfg, device, self.tp) for _ in range(cfg.num_layers)])
         self.head_mod = _param((2, H), torch.float32, device)
         odim = cfg.out_channels * math.prod(cfg.patch_size)
         self.head_w, self.head_b = _param((odim, H), dt, device), _param((odim,), dt, device)
         self.rope = rope_axes_tables(cfg.head_dim, cfg.axes(), cfg.rope_theta, self.device)
 
     def init_random(self, seed: int = 0) -> "AdaLNDiT":
+        """Every rank draws the FULL tensors from the same generator, in the same order, and keeps its part: a sharded
+        model holds the weights of the single-rank model with the same seed."""
         g = torch.Generator().manual_seed(seed)
+        t, r = self.tp.size, self.tp.rank
         for n, p in self.named_parameters():
+            shape = list(p.shape)
+            leaf = n.rsplit(".", 1)[-1]
+            if t > 1 and n.startswith("blocks.") and leaf in _ADALN_CUTS:
+                shape[_ADALN_CUTS[leaf][0]] *= t
             if "norm" in n and n.endswith(("_q", "_k", "3_w")):
-                p.data.fill_(1.0)
+                full = torch.ones(shape)
             elif p.dim() == 1:
-                p.data.copy_((torch.randn(p.shape, generator=g) * 0.02).to(p.dtype))
+                full = torch.randn(shape, generator=g) * 0.02
             elif "modulation" in n or "head_mod" in n:
-                p.data.copy_((torch.randn(p.shape, generator=g) * 0.1).to(p.dtype))
+                full = torch.randn(shape, generator=g) * 0.1
             else:
-                p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
+                full = torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+            p.data.copy_(adaln_shard(n, full, r, t).to(p.dtype))
         return self
 
     # -- once per request --

@@ -152,6 +152,9 @@ class Wan22Model(Model):
     def get_kv_cache_config(self):
         return []
 
+    def get_default_sharding_config(self):
+        return {"dit": {"tp": True, "sp": False}}
+
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "text_encoder":
             enc = T5Encoder(dtype=self.dtype, device=device, **self.text)
@@ -161,7 +164,8 @@ class Wan22Model(Model):
             return (VaeEncodeSubmodule(vae, device, self.dtype) if node_name == "vae_encoder"
                     else VaeDecodeSubmodule(vae, device, self.dtype, self.vae_tile))
         if node_name == "dit":
-            return WanDiTSubmodule(self._init(AdaLNDiT(self.dit_cfg, device), "transformer"), device, self.num_steps, 5.0)
+            dit = AdaLNDiT(self.dit_cfg, device, tp=tp_group)
+            return WanDiTSubmodule(self._init(dit, "transformer"), device, self.num_steps, 5.0)
         raise KeyError(node_name)
 
     def _init(self, module, component: str):

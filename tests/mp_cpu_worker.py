@@ -64,6 +64,22 @@ def main():
             return m(cm.plan(["r"], [9]), input_ids=mids)
         d = (mlogits(one, 2) - mlogits(two, 1)).abs().max().item()
         assert d < 1e-4, (ep_mode, d)
+    # AdaLN DiT (Wan2.2-class): heads and MLP columns cut over the ranks, q / k norms over all heads through an
+    # exchange of the sums of squares; same weights by seed, same velocity as one rank
+    from mstar_b200.models.dit import AdaLNDiT, DiTConfig
+    dc = DiTConfig(hidden_size=48, num_layers=2, num_heads=4, head_dim=12, ffn_dim=64, in_channels=4, out_channels=4,
+                   text_dim=16, text_len=8, freq_dim=32, dtype=torch.float32)
+    one = AdaLNDiT(dc).init_random(5)
+    two = AdaLNDiT(dc, tp=g).init_random(5)
+    assert two.blocks[0].qkv_w.shape == (3 * 24, 48) and one.blocks[0].qkv_w.shape == (3 * 48, 48)
+    assert torch.equal(two.blocks[1].ffn2_w, one.blocks[1].ffn2_w[:, R * 32:(R + 1) * 32])
+    lat = torch.randn(2, 4, 2, 4, 6, generator=gen)
+    text = torch.randn(2 * 8, 16, generator=gen)
+    ts = torch.tensor([[900.0, 0.0], [500.0, 500.0]])
+    with torch.no_grad():
+        want = one(lat, ts, one.encode_context(text), [8, 8])
+        got = two(lat, ts, two.encode_context(text), [8, 8])
+    assert (got - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), (got - want).abs().max().item()
     dist.barrier()
     dist.destroy_process_group()
 

@@ -307,3 +307,25 @@ def test_image_autoencoder_matches_the_reference_module_on_a_shared_checkpoint()
         mutate(bad)
         with pytest.raises(ck.CheckpointMismatch):
             ck.load_image_autoencoder(ConvVAE(cfg), bad)
+
+
+def test_wan22_loader_fills_a_tensor_parallel_model_with_its_shards(tmp_path):
+    """Every rank of a tensor-parallel ``AdaLNDiT`` gets, from the diffusers-named checkpoint, exactly the slices of
+    the single-rank model's parameters that ``adaln_shard`` names (whole heads of q, k and v; MLP columns)."""
+    from mstar_b200.models.dit import adaln_shard
+    from mstar_b200.parallel.comm import CommGroup
+    cfg = _tiny_dit_cfg()
+    one = AdaLNDiT(cfg).init_random(3)
+    d = tmp_path / "transformer"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in ck.wan22_checkpoint_keys(one).items()}, str(d / "diffusion_pytorch_model.safetensors"))
+    full = dict(one.named_parameters())
+    for rank in range(2):
+        tp = CommGroup(None, [0, 1], rank)
+        two = AdaLNDiT(cfg, tp=tp)
+        ck.load_wan22_transformer(two, str(d))
+        for n, p in two.named_parameters():
+            assert torch.equal(p, adaln_shard(n, full[n], rank, 2)), n
+        A = cfg.num_heads * cfg.head_dim // 2
+        assert two.blocks[0].qkv_w.shape[0] == 3 * A
+        assert torch.equal(two.blocks[0].qkv_w[A:2 * A], full["blocks.0.qkv_w"][2 * A + rank * A:2 * A + (rank + 1) * A])

@@ -105,3 +105,14 @@ def test_qwen3_omni_experts_cut_by_expert_over_four_ranks():
                           {"node_names": ["Code2Wav"], "ranks": [3]}]}
     got = _serve(ep, False, req)
     assert got["text"] == want["text"] and got["audio"][:2] == want["audio"][:2]
+
+
+def test_wan22_dit_tp2_served_video_matches_the_single_rank_video():
+    """``configs/wan22_tp2.yaml`` at test size: the AdaLN transformer on two ranks, text encoder beside the first,
+    autoencoder beside the second."""
+    req = ("a boat", ["video"], dict(height=32, width=32, num_frames=5, num_steps=3, guidance_scale=4.0, seed=1), None)
+    want = _frames(_serve("wan22.yaml", True, req, keep_bytes=True)["video"])
+    got = _frames(_serve("wan22_tp2.yaml", False, req, keep_bytes=True)["video"])
+    assert got.shape == want.shape
+    diff = abs(got.astype(int) - want.astype(int))
+    assert diff.max() <= 6 and diff.mean() < 0.05 and want.std() > 10
