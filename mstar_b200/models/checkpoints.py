@@ -126,7 +126,7 @@ _WAN_BLOCK = {
 def load_wan22_transformer(dit, transformer_dir: str) -> dict:
     """Fill an ``AdaLNDiT`` from a diffusers Wan2.2 transformer directory (or file). A tensor-parallel model is
     filled through a full-size copy on the host (strict there), of which every rank keeps its heads and MLP columns."""
-    if getattr(dit, "tp", None) is not None and dit.tp.size > 1:
+    if getattr(dit, "tp", None) is not None and dit.tp.size > 1:      # (sequence-parallel ranks hold whole weights)
         from .dit import AdaLNDiT, adaln_shard
         full = AdaLNDiT(dit.cfg, "cpu")
         info = load_wan22_transformer(full, transformer_dir)

@@ -192,21 +192,33 @@ class AdaLNBlock(nn.Module):
         return (k.reshape(-1, A // c.head_dim, c.head_dim).contiguous(),
                 kv[:, A:].reshape(-1, A // c.head_dim, c.head_dim).contiguous())
 
-    def forward_tp(self, x, mod, positions, rope, self_plan, cross_plan, ctx_kv):
-        """The block over this rank's heads and MLP columns (same signature and result as ``forward``)."""
+    def forward_tp(self, x, mod, positions, rope, self_plan, cross_plan, ctx_kv, exchange=None):
+        """The block over this rank's heads and MLP columns and, with ``exchange`` (a ``UlyssesExchange``), over this
+        rank's rows of the packed sequence: everything is row-local except the self-attention, around which heads
+        and rows are swapped (every rank then attends over the full sequence for a part of its heads). Same
+        result as ``forward``."""
         c, A, tp = self.cfg, self.A, self.tp
         nh, D = A // c.head_dim, c.head_dim
         inv_freq, axis = rope
         h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 1], shift=mod[:, 0])
         qkv = gemm.linear(h, self.qkv_w, bias=self.qkv_b)
-        qn, kn = self._norm_all_heads([qkv[:, :A], qkv[:, A:2 * A]], [self.norm_q, self.norm_k])
-        qkv = torch.cat([qn, kn, qkv[:, 2 * A:]], dim=-1).contiguous()
+        if tp.size > 1:
+            qn, kn = self._norm_all_heads([qkv[:, :A], qkv[:, A:2 * A]], [self.norm_q, self.norm_k])
+            qkv = torch.cat([qn, kn, qkv[:, 2 * A:]], dim=-1).contiguous()
+        else:
+            norm_ops.norm(qkv[:, :A], self.norm_q, c.eps, out=qkv[:, :A])
+            norm_ops.norm(qkv[:, A:2 * A], self.norm_k, c.eps, out=qkv[:, A:2 * A])
         q, k, v = rope_ops.rope_kv(qkv, positions, inv_freq, nh, nh, D, axis_of_freq=axis, interleaved=True, dense_kv=True)
-        a = attn_ops.attention(q, self_plan, k=k, v=v)
+        if exchange is not None:
+            q, k, v = exchange.to_heads(q, k, v)
+        a = attn_ops.attention(q.contiguous(), self_plan, k=k.contiguous(), v=v.contiguous())
+        if exchange is not None:
+            a = exchange.to_sequence(a)
         y = row_parallel(a.reshape(-1, A), self.o_w, tp, bias=self.o_b)
         x = ew_ops.gated_residual(x, y, mod[:, 2])
         h, _ = norm_ops.norm(x, self.norm3_w, c.eps, layernorm=True, bias=self.norm3_b)
-        q = self._norm_all_heads([gemm.linear(h, self.cq_w, bias=self.cq_b)], [self.cnorm_q])[0]
+        q = gemm.linear(h, self.cq_w, bias=self.cq_b)
+        q = self._norm_all_heads([q], [self.cnorm_q])[0] if tp.size > 1 else norm_ops.norm(q, self.cnorm_q, c.eps)[0]
         a = attn_ops.attention(q.reshape(-1, nh, D), cross_plan, k=ctx_kv[0], v=ctx_kv[1])
         x = row_parallel(a.reshape(-1, A), self.co_w, tp, bias=self.co_b, residual=x)
         h, _ = norm_ops.norm(x, None, c.eps, layernorm=True, scale=mod[:, 4], shift=mod[:, 3])
@@ -265,10 +277,12 @@ def adaln_shard(name: str, full: torch.Tensor, rank: int, size: int) -> torch.Te
 
 
 class AdaLNDiT(nn.Module):
-    def __init__(self, cfg: DiTConfig, device="cpu", tp: CommGroup | None = None):
+    def __init__(self, cfg: DiTConfig, device="cpu", tp: CommGroup | None = None, sp: CommGroup | None = None):
         super().__init__()
         self.cfg, self.device = cfg, torch.device(device)
         self.tp = tp or CommGroup.trivial()
+        self.sp = sp or CommGroup.trivial()
+        self._exchange: dict = {}
         H, dt = cfg.hidden_size, cfg.dtype
         pdim = cfg.in_channels * math.prod(cfg.patch_size)
         self.patch_w, self.patch_b = _param((H, pdim), dt, device), _param((H,), dt, device)
@@ -334,6 +348,8 @@ class AdaLNDiT(nn.Module):
                          out_dtype=torch.float32).reshape(B * n_per, 6, cfg.hidden_size)
         pos = grid_positions(*grid, self.device).repeat(1, B)
         G = 1
+        if self.sp.size > 1:
+            return self._forward_sp(x, e, e6, pos, B, S, n_per, grid, ctx_kv, ctx_lens)
         self_plan = attn_ops.dense_plan([S] * B, [S] * B, G, self.device, causal=False)
         cross_plan = attn_ops.dense_plan([S] * B, ctx_lens, G, self.device, causal=False)
         for i, blk in enumerate(self.blocks):
@@ -342,6 +358,53 @@ class AdaLNDiT(nn.Module):
         hm = (self.head_mod.float()[None] + e.float().reshape(B * n_per, 1, -1)).to(cfg.dtype)
         h, _ = norm_ops.norm(x, None, cfg.eps, layernorm=True, scale=hm[:, 1], shift=hm[:, 0])
         out = gemm.linear(h, self.head_w, bias=self.head_b, out_dtype=torch.float32)
+        return torch.stack([unpatchify(out[b * S:(b + 1) * S], grid, cfg.patch_size, cfg.out_channels)
+                            for b in range(B)])
+
+
+    def _forward_sp(self, x, e, e6, pos, B, S, n_per, grid, ctx_kv, ctx_lens):
+        """Sequence-parallel blocks: this rank keeps a contiguous range of the packed rows (B branches x S tokens).
+        Norms, modulation, projections, cross-attention and MLP work on those rows; the self-attention swaps rows
+        for heads (Ulysses). A rank's rows must be whole modulation groups or lie inside one (a group = the tokens
+        of one branch that share a timestep)."""
+        from ..parallel.sequence_parallel import UlyssesExchange, gather_sequence, sp_seq_split
+        cfg, sp = self.cfg, self.sp
+        T = B * S
+        nh_local = cfg.num_heads // self.tp.size
+        if nh_local % sp.size:
+            raise ValueError(f"{nh_local} heads per tensor-parallel rank cannot be cut over {sp.size} sequence ranks")
+        off = sp_seq_split(T, sp.size)
+        r0, r1 = off[sp.rank], off[sp.rank + 1]
+        gsz = S // n_per                                   # rows per modulation group
+        if (r0 % gsz == 0 and r1 % gsz == 0):
+            groups = slice(r0 // gsz, r1 // gsz)
+        elif r0 // gsz == (r1 - 1) // gsz:
+            groups = slice(r0 // gsz, r0 // gsz + 1)
+        else:
+            raise ValueError(f"rows {r0}..{r1} of {T} split modulation groups of {gsz} rows unevenly: use a sequence-"
+                             f"parallel degree that divides the branches or the frames")
+        key = (T, nh_local)
+        ex = self._exchange.get(key)
+        if ex is None:
+            ex = self._exchange[key] = UlyssesExchange(sp, T, nh_local, nh_local, cfg.head_dim, cfg.dtype)
+        x = x[r0:r1].contiguous()
+        pos = pos[:, r0:r1].contiguous()
+        self_plan = attn_ops.dense_plan([S] * B, [S] * B, 1, self.device, causal=False)
+        q_loc = [max(0, min(r1, (b + 1) * S) - max(r0, b * S)) for b in range(B)]
+        keep = [b for b in range(B) if q_loc[b] > 0]
+        cross_plan = attn_ops.dense_plan([q_loc[b] for b in keep], [ctx_lens[b] for b in keep], 1, self.device, causal=False)
+        c_off = [0]
+        for n in ctx_lens:
+            c_off.append(c_off[-1] + n)
+        rows = torch.cat([torch.arange(c_off[b], c_off[b + 1], device=self.device) for b in keep])
+        for i, blk in enumerate(self.blocks):
+            mod = (blk.modulation.float()[None] + e6[groups]).to(cfg.dtype)
+            kv = ctx_kv[i] if len(keep) == B else (ctx_kv[i][0].index_select(0, rows), ctx_kv[i][1].index_select(0, rows))
+            x = blk.forward_tp(x, mod, pos, self.rope, self_plan, cross_plan, kv, exchange=ex)
+        hm = (self.head_mod.float()[None] + e.float().reshape(B * n_per, 1, -1)[groups]).to(cfg.dtype)
+        h, _ = norm_ops.norm(x, None, cfg.eps, layernorm=True, scale=hm[:, 1], shift=hm[:, 0])
+        out = gemm.linear(h, self.head_w, bias=self.head_b, out_dtype=torch.float32)
+        out = gather_sequence(out, sp, T)                  # only the head's [rows, patch] result travels
         return torch.stack([unpatchify(out[b * S:(b + 1) * S], grid, cfg.patch_size, cfg.out_channels)
                             for b in range(B)])
 

@@ -153,7 +153,7 @@ class Wan22Model(Model):
         return []
 
     def get_default_sharding_config(self):
-        return {"dit": {"tp": True, "sp": False}}
+        return {"dit": {"tp": True, "sp": True}}
 
     def get_submodule(self, node_name, device, tp_group=None, autocast_dtype=None, sp_group=None):
         if node_name == "text_encoder":
@@ -164,7 +164,7 @@ class Wan22Model(Model):
             return (VaeEncodeSubmodule(vae, device, self.dtype) if node_name == "vae_encoder"
                     else VaeDecodeSubmodule(vae, device, self.dtype, self.vae_tile))
         if node_name == "dit":
-            dit = AdaLNDiT(self.dit_cfg, device, tp=tp_group)
+            dit = AdaLNDiT(self.dit_cfg, device, tp=tp_group, sp=sp_group)
             return WanDiTSubmodule(self._init(dit, "transformer"), device, self.num_steps, 5.0)
         raise KeyError(node_name)
 

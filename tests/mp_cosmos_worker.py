@@ -67,6 +67,18 @@ def main():
     else:
         err = (out - ref).abs().max().item()
         assert err < 1e-3 * max(1.0, ref.abs().max().item()), err
+        # the AdaLN transformer (Wan2.2-class) on the same tp2 x sp2 mesh against one rank
+        from mstar_b200.models.dit import AdaLNDiT, DiTConfig
+        dc = DiTConfig(hidden_size=48, num_layers=2, num_heads=4, head_dim=12, ffn_dim=64, in_channels=4, out_channels=4,
+                       text_dim=16, text_len=8, freq_dim=32, dtype=torch.float32)
+        lat, text = torch.randn(2, 4, 2, 4, 6, generator=gen), torch.randn(16, 16, generator=gen)
+        ts = torch.tensor([[900.0, 0.0], [500.0, 500.0]])
+        one, mesh = AdaLNDiT(dc).init_random(5), AdaLNDiT(dc, tp=tp, sp=sp).init_random(5)
+        with torch.no_grad():
+            want = one(lat, ts, one.encode_context(text), [8, 8])
+            got = mesh(lat, ts, mesh.encode_context(text), [8, 8])
+        err = (got - want).abs().max().item()
+        assert err < 1e-4 * max(1.0, want.abs().max().item()), err
     dist.barrier()
     dist.destroy_process_group()
 

@@ -80,6 +80,16 @@ def main():
         want = one(lat, ts, one.encode_context(text), [8, 8])
         got = two(lat, ts, two.encode_context(text), [8, 8])
     assert (got - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), (got - want).abs().max().item()
+    # the same model sequence-parallel: every rank keeps one guidance branch's rows, attention swaps rows for heads
+    sq = AdaLNDiT(dc, sp=g).init_random(5)
+    with torch.no_grad():
+        got = sq(lat, torch.tensor([900.0, 500.0]), sq.encode_context(text), [8, 8])
+        want = one(lat, torch.tensor([900.0, 500.0]), one.encode_context(text), [8, 8])
+    assert (got - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), (got - want).abs().max().item()
+    with torch.no_grad():                                  # per-frame timesteps: a rank's rows are whole groups
+        got = sq(lat, ts, sq.encode_context(text), [8, 8])
+        want = one(lat, ts, one.encode_context(text), [8, 8])
+    assert (got - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), (got - want).abs().max().item()
     dist.barrier()
     dist.destroy_process_group()
 

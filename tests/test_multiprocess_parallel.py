@@ -116,3 +116,12 @@ def test_wan22_dit_tp2_served_video_matches_the_single_rank_video():
     assert got.shape == want.shape
     diff = abs(got.astype(int) - want.astype(int))
     assert diff.max() <= 6 and diff.mean() < 0.05 and want.std() > 10
+
+
+def test_wan22_dit_tp2_x_sp2_served_video_matches_the_single_rank_video():
+    req = ("a boat", ["video"], dict(height=32, width=32, num_frames=5, num_steps=3, guidance_scale=4.0, seed=1), None)
+    want = _frames(_serve("wan22.yaml", True, req, keep_bytes=True)["video"])
+    got = _frames(_serve("wan22_tp2_sp2.yaml", False, req, keep_bytes=True)["video"])
+    assert got.shape == want.shape
+    diff = abs(got.astype(int) - want.astype(int))
+    assert diff.max() <= 6 and diff.mean() < 0.05 and want.std() > 10
