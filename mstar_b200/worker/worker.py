@@ -451,6 +451,9 @@ class Worker:
             return
         self.scheduler.remove_request(_rk(pri))
         pri.walk_state.clear()
+        self._deferred_new.pop(key, None)
+        self._deferred_stream_end.pop(key, None)
+        self._stall_logged.discard(key)
         if not any(k[0] == key[0] for k in self.requests):
             self.engines.remove_request(key[0])
             self.tensors.remove_request(key[0])
