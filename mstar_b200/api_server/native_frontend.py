@@ -175,18 +175,17 @@ class NativeFrontend:
                     self.loop.call_soon_threadsafe(t.cancel)
                 continue
             self.stats["requests"] += 1
-            fut = asyncio.run_coroutine_threadsafe(self._spawn(rid, hdr, body), self.loop)
-            fut.add_done_callback(lambda f: f.exception())
+            self.loop.call_soon_threadsafe(self._spawn, rid, hdr, body)      # one callback, one task per request
 
-    async def _spawn(self, rid: int, hdr: dict, body: bytes):
-        task = asyncio.ensure_future(self._serve(rid, hdr, body))
+    def _spawn(self, rid: int, hdr: dict, body: bytes) -> None:
+        task = self.loop.create_task(self._serve(rid, hdr, body))
         self.tasks[rid] = task
-        try:
-            await task
-        except asyncio.CancelledError:
-            pass
-        finally:
+
+        def done(t, rid=rid):
             self.tasks.pop(rid, None)
+            if not t.cancelled():
+                t.exception()              # retrieved: failures were answered inside _serve
+        task.add_done_callback(done)
 
     def _send(self, rid: int, kind: str, payload: bytes = b"", **extra) -> None:
         head = json.dumps({"id": rid, "kind": kind, **extra}, separators=(",", ":")).encode() + b"\n"
