@@ -482,6 +482,22 @@ def load_whisper_decoder(dec, src, prefix: str = "model.decoder.") -> dict:
     return st.done()
 
 
+@torch.no_grad()
+def load_higgs_audio_tower(enc, proj, src) -> dict:
+    """The audio tower (``audio_tower.*``: Whisper encoder names, position table included) and the projector
+    (``audio_encoder_proj.temporal`` depthwise convolution, ``linear1`` / ``linear2``) of a Higgs-Audio speech-to-text
+    checkpoint. Reference: mstar/model/higgs_audio/components/audio_tower.py:27-87."""
+    T = _tensors_of(src)
+    res = load_whisper_encoder(enc, {k: v for k, v in T.items() if k.startswith("audio_tower.")}, prefix="audio_tower.")
+    pre = "audio_encoder_proj."
+    st = _Strict(proj, {k[len(pre):]: v for k, v in T.items() if k.startswith(pre)}, "Higgs-Audio projector")
+    for a, b in (("temporal.weight", "temporal.weight"), ("temporal.bias", "temporal.bias"), ("linear1.weight", "w1"),
+                 ("linear1.bias", "b1"), ("linear2.weight", "w2"), ("linear2.bias", "b2")):
+        st.write(b, st.take(a))
+    res2 = st.done()
+    return {"tower": res, "projector": res2}
+
+
 # ------------------------------------------------------------------ SigLIP vision tower (Hugging Face names)
 @torch.no_grad()
 def load_siglip_vision(enc, src, prefix: str = "vision_model.", position_table: bool = True) -> dict:

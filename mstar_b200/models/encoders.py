@@ -119,7 +119,13 @@ class TransformerEncoder(nn.Module):
                 p.data.copy_((torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1])).to(p.dtype))
         return self
 
-    def forward(self, x: torch.Tensor, seq_lens: list[int], bias=None, rope=None, collect: list[int] | None = None):
+    def final_norm(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fn_w is None:
+            return x
+        return norm_ops.norm(x, self.fn_w, self.c.eps, bias=self.fn_b, layernorm=self.c.norm == "layernorm")[0]
+
+    def forward(self, x: torch.Tensor, seq_lens: list[int], bias=None, rope=None, collect: list[int] | None = None,
+                final: bool = True):
         # plans are cached per shape: a captured piece must not create tensors from host data
         key = (tuple(seq_lens), str(x.device))
         plan = self._plans.get(key)
@@ -132,8 +138,8 @@ class TransformerEncoder(nn.Module):
             x = L(x, plan, bias, seq_lens, rope)
             if collect and i in collect:
                 taps.append(x)
-        if self.fn_w is not None:
-            x = norm_ops.norm(x, self.fn_w, self.c.eps, bias=self.fn_b, layernorm=self.c.norm == "layernorm")[0]
+        if final:
+            x = self.final_norm(x)
         return (x, taps) if collect else x
 
 
@@ -299,27 +305,43 @@ def log_mel_spectrogram(wav: torch.Tensor, sample_rate: int = 16000, n_fft: int 
     return (mel + 4.0) / 4.0
 
 
+_MEL_BANKS: dict = {}
+
+
 def _mel_filterbank(sr, n_fft, n_mels, device):
+    key = (sr, n_fft, n_mels, str(device))
+    if key not in _MEL_BANKS:
+        _MEL_BANKS[key] = _build_mel_filterbank(sr, n_fft, n_mels).to(device)
+    return _MEL_BANKS[key]
+
+
+def _build_mel_filterbank(sr, n_fft, n_mels):
+    """Triangular filters on the Slaney mel scale (linear below 1 kHz, logarithmic above), each scaled by 2 / width:
+    the bank Whisper's feature extractor uses."""
+    step, knee, logstep = 200.0 / 3.0, 1000.0, math.log(6.4) / 27.0
+
     def hz2mel(f):
-        return 2595.0 * math.log10(1.0 + f / 700.0)
-    mels = torch.linspace(hz2mel(0.0), hz2mel(sr / 2), n_mels + 2)
-    hz = 700.0 * (10 ** (mels / 2595.0) - 1.0)
-    bins = torch.linspace(0, sr / 2, n_fft // 2 + 1)
-    fb = torch.zeros(n_mels, n_fft // 2 + 1)
+        return f / step if f < knee else knee / step + math.log(f / knee) / logstep
+
+    mels = torch.linspace(hz2mel(0.0), hz2mel(sr / 2), n_mels + 2, dtype=torch.float64)
+    hz = torch.where(mels < knee / step, mels * step, knee * torch.exp(logstep * (mels - knee / step)))
+    bins = torch.linspace(0, sr / 2, n_fft // 2 + 1, dtype=torch.float64)
+    fb = torch.zeros(n_mels, n_fft // 2 + 1, dtype=torch.float64)
     for i in range(n_mels):
         lo, ce, hi = hz[i], hz[i + 1], hz[i + 2]
         fb[i] = torch.clamp(torch.minimum((bins - lo) / (ce - lo), (hi - bins) / (hi - ce)), min=0) * (2.0 / (hi - lo))
-    return fb.to(device)
+    return fb.float()
 
 
 class AudioEncoder(nn.Module):
     """Whisper-class encoder: two conv1d (second with stride 2) + sinusoidal positions + pre-LN transformer;
-    optional projection to the language model's width."""
+    optional projection to the language model's width. ``pool`` > 1 averages that many consecutive frames of each
+    sequence between the last layer and the final norm (a trailing remainder is dropped)."""
 
     def __init__(self, c: EncoderConfig, n_mels: int = 128, max_frames: int = 1500, out_dim: int | None = None,
-                 device="cpu"):
+                 device="cpu", pool: int = 1):
         super().__init__()
-        self.c = c
+        self.c, self.pool = c, pool
         self.conv1 = nn.Conv1d(n_mels, c.hidden_size, 3, padding=1).to(device=device, dtype=c.dtype)
         self.conv2 = nn.Conv1d(c.hidden_size, c.hidden_size, 3, stride=2, padding=1).to(device=device, dtype=c.dtype)
         half = c.hidden_size // 2
@@ -345,7 +367,15 @@ class AudioEncoder(nn.Module):
             n = min(h.shape[0], self.pos.shape[0])
             xs.append(h[:n] + self.pos[:n])
             lens.append(n)
-        x = self.enc(torch.cat(xs).contiguous(), lens)
+        if self.pool > 1:
+            x = self.enc(torch.cat(xs).contiguous(), lens, final=False)
+            k, parts = self.pool, []
+            for h in x.split(lens):
+                parts.append(h[:h.shape[0] // k * k].reshape(h.shape[0] // k, k, -1).float().mean(1).to(h.dtype))
+            lens = [n // k for n in lens]
+            x = self.enc.final_norm(torch.cat(parts).contiguous())
+        else:
+            x = self.enc(torch.cat(xs).contiguous(), lens)
         if self.out_w is not None:
             x = gemm.linear(x, self.out_w)
         return x, lens

@@ -74,7 +74,7 @@ def test_higgs_audio_placeholders_are_replaced_by_encoder_frames():
             res = s.collect_results(rid, 120)
             assert "error" not in res and len(res["text"]) == 4, res
             outs.append(b"".join(c.data for c in res["text"]))
-        # 5 s of audio = two 4 s chunks = 2 * 200 placeholder rows; different audio changes the continuation
+        # 5 s of audio = a 4 s chunk (50 rows) and a 1 s chunk (13 rows); different audio changes the continuation
         assert outs[0] != outs[1] or outs[0] != outs[2]
     finally:
         s.shutdown()
