@@ -264,12 +264,45 @@ class Model(ABC):
         return tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=True)
 
     def decode_text(self, ids) -> bytes:
-        """Client-bound form of generated text tokens: decoded text with a tokenizer, else the ids in decimal."""
+        """Client-bound form of generated text tokens. With a byte-level BPE tokenizer (GPT-2 / Qwen / Llama-3 /
+        Whisper vocabularies) the tokens' own bytes: streamed one token at a time, a multi-byte character split across
+        tokens then reaches the client intact instead of as replacement characters. Other tokenizers: decoded text.
+        Without a tokenizer: the ids in decimal. Reference: mstar/model/utils.py:331-366."""
         ids = [int(i) for i in ids]
         tok = self.tokenizer()
-        if tok is not None:
-            return tok.decode(ids, skip_special_tokens=True).encode("utf-8")
-        return (" ".join(str(i) for i in ids) + " ").encode()
+        if tok is None:
+            return (" ".join(str(i) for i in ids) + " ").encode()
+        table = self._byte_table(tok)
+        if table is not None:
+            special = self._special_ids
+            raw = bytearray()
+            for t in tok.convert_ids_to_tokens([i for i in ids if i not in special]):
+                try:
+                    raw.extend(table[c] for c in (t or ""))
+                except KeyError:                     # an added token written in plain text
+                    raw.extend(t.encode("utf-8"))
+            return bytes(raw)
+        return tok.decode(ids, skip_special_tokens=True).encode("utf-8")
+
+    def _byte_table(self, tok):
+        """Character -> byte map of a byte-level BPE vocabulary, or None when the tokenizer is of another kind (probed
+        once: such a vocabulary writes a leading space as U+0120)."""
+        if not hasattr(self, "_byte_table_cache"):
+            self._byte_table_cache, self._special_ids = None, set(getattr(tok, "all_special_ids", []) or [])
+            try:
+                probe = tok.convert_ids_to_tokens(tok.encode(" a", add_special_tokens=False))
+                if probe and probe[0].startswith("\u0120"):
+                    keep = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+                    chars, n = keep[:], 0
+                    for b in range(256):
+                        if b not in keep:
+                            keep.append(b)
+                            chars.append(256 + n)
+                            n += 1
+                    self._byte_table_cache = {chr(c): b for b, c in zip(keep, chars)}
+            except Exception:  # noqa: BLE001
+                self._byte_table_cache = None
+        return self._byte_table_cache
 
     # ---- media loading (API server) ----
     def load_image(self, path_or_bytes) -> torch.Tensor:

@@ -256,18 +256,6 @@ class WhisperModel(Model):
 
     def postprocess(self, output, modality, request_kwargs):
         ids = output.reshape(-1).tolist() if isinstance(output, torch.Tensor) else list(output)
-        tok = self._tokenizer()
-        if tok is not None:
-            return tok.decode([i for i in ids if i < SOT - 1]).encode()
+        if self.tokenizer() is not None:          # the tokens' own bytes: a character split across tokens streams intact
+            return self.decode_text([i for i in ids if i < SOT - 1])
         return (" ".join(str(int(i)) for i in ids) + " ").encode()
-
-    def _tokenizer(self):
-        if self.model_dir is None:
-            return None
-        if not hasattr(self, "_tok"):
-            try:
-                from transformers import AutoTokenizer
-                self._tok = AutoTokenizer.from_pretrained(self.model_dir)
-            except Exception:  # noqa: BLE001
-                self._tok = None
-        return self._tok
