@@ -259,7 +259,8 @@ class Qwen3OmniModel(Model):
                 from .checkpoints import load_qwen3_omni_code_predictor
                 load_qwen3_omni_code_predictor(pred, self.model_dir)
             return TalkerSubmodule(lm, pred, device, num_slots=64, codec_eos=self.codec_eos, cond_edge="thinker_out",
-                                   cond_is_ids=False, cond_dim=self.t_cfg.hidden_size, loop_name="talker_loop")
+                                   cond_is_ids=False, cond_dim=self.t_cfg.hidden_size, loop_name="talker_loop",
+                                   suppress_from=self.codebook)
         if node_name == "Code2Wav":
             k = small_scale()
             kw = (dict(n_codebooks=self.n_sub + 1, codebook_size=self.codebook, hidden=32 * k, layers=1, heads=2,

@@ -91,8 +91,17 @@ class TalkerSubmodule(ARNodeSubmodule):
 
     def __init__(self, lm: DecoderLM, predictor: CodePredictor, device, *, num_slots: int, codec_eos: int,
                  cond_edge: str, cond_is_ids: bool, cond_dim: int, loop_name: str, frame_edge: str = "codec_frames",
-                 text_vocab: int = 0, aux_cfg: SamplingConfig | None = None):
+                 text_vocab: int = 0, aux_cfg: SamplingConfig | None = None, suppress_from: int | None = None):
         super().__init__(device, lm.cfg.dtype)
+        # ids from ``suppress_from`` up are the codec's control tokens: never sampled as a frame's first code, except
+        # the end-of-speech id (reference: mstar/model/qwen3_omni/submodules.py:1290-1309)
+        self.suppress = None
+        if suppress_from is not None and suppress_from < lm.cfg.vocab_size:
+            m = torch.zeros(lm.cfg.vocab_size, dtype=torch.bool, device=device)
+            m[suppress_from:] = True
+            if 0 <= codec_eos < lm.cfg.vocab_size:
+                m[codec_eos] = False
+            self.suppress = m
         self.lm, self.pred, self.codec_eos, self.loop_name, self.frame_edge = lm, predictor, codec_eos, loop_name, frame_edge
         self.cond_edge, self.cond_is_ids = cond_edge, cond_is_ids
         H, dt = lm.cfg.hidden_size, lm.cfg.dtype
@@ -154,6 +163,17 @@ class TalkerSubmodule(ARNodeSubmodule):
     def capture_state(self):
         return [self.prev_hidden, self.aux.offset]
 
+    def _suppress(self, logits: torch.Tensor) -> torch.Tensor:
+        """In place (a vocabulary-parallel head hands out a view of its own buffer, whose layout the sampler knows)."""
+        if self.suppress is None:
+            return logits
+        if self.suppress.numel() != logits.shape[-1]:          # a head padded past the vocabulary: pad columns stay
+            m = torch.zeros(logits.shape[-1], dtype=torch.bool, device=self.suppress.device)
+            n = min(m.numel(), self.suppress.numel())
+            m[:n] = self.suppress[:n]
+            self.suppress = m
+        return logits.masked_fill_(self.suppress[None], -1e30)
+
     def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
         ctx = engine_inputs.batch_context
         if "prefill" in graph_walk:
@@ -163,7 +183,7 @@ class TalkerSubmodule(ARNodeSubmodule):
                 xs.append(self.bos_embed if rows is None else torch.cat([rows, self.bos_embed]))
             logits, hidden = self.lm(ctx, inputs_embeds=torch.cat(xs).contiguous(), return_hidden=True)
             self.prev_hidden[ctx.row_slot.long()] = hidden.index_select(0, ctx.logit_rows)
-            return {BATCHED_LOGITS: logits}
+            return {BATCHED_LOGITS: self._suppress(logits)}
         ids = torch.cat([ni.input_ids.reshape(-1)[-1:] for ni in inputs]).to(self.device)
         return self._decode_step(ids, ctx)
 
@@ -176,7 +196,7 @@ class TalkerSubmodule(ARNodeSubmodule):
         x = gemm.linear(self.pred.frame_embedding(codes), self.frame_proj) + self.cond_next[slots]
         logits, hidden = self.lm(ctx, inputs_embeds=x.contiguous(), return_hidden=True)
         self.prev_hidden[slots] = hidden.index_select(0, ctx.logit_rows)
-        return {BATCHED_LOGITS: logits, "codes": codes}
+        return {BATCHED_LOGITS: self._suppress(logits), "codes": codes}
 
     def postprocess(self, request_id, request_info, outputs, inputs):
         tok = outputs["new_token"].to(torch.int64)

@@ -141,3 +141,20 @@ def test_mrope_positions_for_image_spans():
     assert pos[:, :2].tolist() == [[0, 1]] * 3
     assert pos[:, 2:6].tolist() == [[2, 2, 2, 2], [2, 2, 3, 3], [2, 3, 2, 3]]
     assert pos[:, 6:].tolist() == [[4, 5]] * 3 and delta == 6 - 8
+
+
+def test_qwen3_omni_talker_never_samples_control_codes():
+    """The first code of a frame comes from the codebook or is the end-of-speech id: the other ids of the talker's
+    vocabulary above the codebook are masked before sampling."""
+    from mstar_b200.models.qwen3_omni import Qwen3OmniModel
+    m = Qwen3OmniModel(small=True, skip_weight_loading=True)
+    t = m.get_submodule("Talker", "cpu")
+    V = m.k_cfg.vocab_size
+    assert t.suppress is not None and int(t.suppress.sum()) == V - m.codebook - (1 if m.codec_eos >= m.codebook else 0)
+    lg = torch.zeros(2, V)
+    lg[:, V - 1] = 50.0                                   # a control id would win
+    out = t._suppress(lg)
+    assert m.codec_eos < m.codebook                       # the test-sized talker ends on a codebook id
+    assert out.argmax(-1).max() < m.codebook and (out[:, m.codebook:] < -1e29).all()
+    wide = t._suppress(torch.zeros(1, V + 8))             # a padded head keeps its pad columns
+    assert wide.shape[-1] == V + 8 and (wide[0, V:] == 0).all()
