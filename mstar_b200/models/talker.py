@@ -167,11 +167,10 @@ class TalkerSubmodule(ARNodeSubmodule):
         """In place (a vocabulary-parallel head hands out a view of its own buffer, whose layout the sampler knows)."""
         if self.suppress is None:
             return logits
-        if self.suppress.numel() != logits.shape[-1]:          # a head padded past the vocabulary: pad columns stay
-            m = torch.zeros(logits.shape[-1], dtype=torch.bool, device=self.suppress.device)
-            n = min(m.numel(), self.suppress.numel())
-            m[:n] = self.suppress[:n]
-            self.suppress = m
+        n = min(self.suppress.numel(), logits.shape[-1])        # a head padded past the vocabulary keeps its pad columns
+        if n != logits.shape[-1] or n != self.suppress.numel():
+            logits[..., :n].masked_fill_(self.suppress[None, :n], -1e30)     # a view: nothing is allocated or cached
+            return logits
         return logits.masked_fill_(self.suppress[None], -1e30)
 
     def forward_batched(self, graph_walk, engine_inputs, inputs, **kw):
